@@ -1,0 +1,238 @@
+#!/usr/bin/env python
+"""Headline benchmark: batch-1 greedy decode tokens/s of the Qwen3.5-27B-shaped hybrid model with
+NVFP4/MXFP8 block-quantised weights (the Blackwell counterpart of the reference's PSQ checkpoint), after a
+prefill of `--context` tokens -- the reference's `tg` figure (docs/perf/current.md:48-61: 27.51 tok/s on
+one R9700).  With --gpus N the same single stream is decoded tensor-parallel over N GPUs (strong scaling).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line on rank 0.  `value` is timed on the device with CUDA events around K decode steps
+whose sampled token is fed back on the device; `e2e.value` is the same K steps driven through the public
+`Engine.decode` call: each step copies its inputs host->device from pinned memory and reads the sampled
+token back to the host.  Weights are random-init N(0, 0.02) and prompts are uniform-random token ids.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+BASELINE_TOK_S = 27.51      # docs/perf/current.md:48-61 (tg128 @ ctx 2048, batch 1, non-speculative)
+
+
+def _parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="27b", choices=["27b", "4b", "tiny"])
+    ap.add_argument("--preset", default="nvfp4", choices=["nvfp4", "bf16", "mxfp8"])
+    ap.add_argument("--context", type=int, default=2048, help="prompt tokens prefilled before decoding")
+    ap.add_argument("--kv-dtype", default="bf16", choices=["bf16", "fp8_e4m3"])
+    ap.add_argument("--prefill-chunk", type=int, default=2048)
+    ap.add_argument("--quant-search", type=int, default=1)
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.p = None
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                       "-lms", "100", "-i", str(gpu_index)], stdout=subprocess.PIPE,
+                                      stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.p = None
+
+    def stop(self) -> dict:
+        if self.p is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.p.terminate()
+        try:
+            out, _ = self.p.communicate(timeout=5)
+        except Exception:
+            self.p.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        for line in out.splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def reference_arm(args):
+    """The reference is a HIP/RDNA4-only C++ project (its CMake rejects every other GPU architecture and
+    non-clang toolchains); it has no Python package, so it cannot be installed or run on a B200."""
+    print(json.dumps({"impl": "reference", "unavailable":
+                      "reference is a HIP C++20 runtime that builds only for AMD gfx1201 (cmake/options.cmake:109-115); "
+                      "pip install of /root/reference fails: no setup.py/pyproject.toml, no CUDA path"}))
+    return 0
+
+
+def main():
+    args = _parse()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            # relaunch under torchrun so `python bench.py --gpus N` works on its own
+            cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+                   "--master-addr", "127.0.0.1", "--master-port", os.environ.get("MASTER_PORT", "29531"),
+                   os.path.abspath(__file__)] + sys.argv[1:]
+            return subprocess.call(cmd)
+        raise SystemExit(f"WORLD_SIZE={world} does not match --gpus {args.gpus}")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    tp = None
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+        from phaseshift_b200.parallel.tp import TensorParallel
+        tp = TensorParallel(dist.group.WORLD, dev)
+
+    from phaseshift_b200.models.qwen35.config import PRESETS
+    from phaseshift_b200.models.qwen35.weights import build_engine_weights, random_getter
+    from phaseshift_b200.quant import formats
+    from phaseshift_b200.runtime.batch import SeqRows
+    from phaseshift_b200.runtime.engine import Engine
+    from phaseshift_b200.runtime.state import StateConfig
+
+    cfg = PRESETS[args.model]()
+    t0 = time.time()
+    formats.DEFAULT_SEARCH = args.quant_search
+    with torch.no_grad():
+        ew = build_engine_weights(cfg, random_getter(cfg, seed=0, device=dev), args.preset, dev,
+                                  tp_rank=rank, tp_size=world)
+    torch.cuda.synchronize()
+    build_s = time.time() - t0
+    K, W = args.steps, args.warmup
+    max_seq = args.context + 2 * (K + W) + 64
+    eng = Engine(ew, dev, StateConfig(max_slots=1, max_seq_len=max_seq, page_tokens=16, kv_dtype=args.kv_dtype), tp=tp)
+    g = torch.Generator().manual_seed(1234)
+    prompt = torch.randint(0, cfg.vocab_size, (args.context,), generator=g).tolist()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    with torch.no_grad():
+        s = eng.open_sequence()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier(); ev0.record()
+        tok = eng.prefill(s, prompt, args.prefill_chunk)
+        ev1.record(); barrier()
+        prefill_ms = ev0.elapsed_time(ev1)
+
+        # ---------------- end-to-end arm: public API, per-step H2D of inputs + D2H of the sampled token
+        for _ in range(W):
+            tok = eng.decode(s, tok)
+        b1 = eng.batches[1]
+        h2d = b1.h2d_bytes()
+        launches0 = eng.ops.launches
+        barrier()
+        sampler = ClockSampler(local_rank)
+        t_e2e0 = time.perf_counter()
+        for _ in range(K):
+            tok = eng.decode(s, tok)
+        torch.cuda.synchronize()
+        t_e2e = time.perf_counter() - t_e2e0
+        barrier()
+        e2e_ms = t_e2e * 1e3 / K
+        checksum = 0
+
+        # ---------------- device-timed arm: K graph replays, token fed back on the device
+        pos0 = s.position
+        eng._reserve(s, pos0 + K + max(W, 3) + 1)
+        graph_key = 1 * 4096 + 1
+        graph = eng.graphs[graph_key]
+        gout = eng.graph_out[graph_key]
+        b1.fill([SeqRows(s.slot, pos0, [tok], (0,))]); b1.graph_static = True; b1.upload()
+
+        def dev_step():
+            graph.replay()
+            b1.ids[:1].copy_(gout.tokens[:1])
+            b1.row_pos[:1].add_(1)
+            b1.seq_desc[0, 3:4].add_(1)
+        for _ in range(max(W, 3)):
+            dev_step()
+        barrier()
+        ev0.record()
+        for _ in range(K):
+            dev_step()
+        ev1.record()
+        barrier()
+        dev_ms = ev0.elapsed_time(ev1) / K
+        clocks = sampler.stop()
+        s.position = pos0 + K + max(W, 3)
+        checksum = int(gout.tokens[0])
+        eng.close_sequence(s)
+
+    # max over ranks of the per-step time
+    t = torch.tensor([dev_ms, e2e_ms, prefill_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dev_ms, e2e_ms, prefill_ms = (float(x) for x in t.tolist())
+    launches_per_step = eng.launches_per_graph.get(graph_key, 0)
+    rd_bytes = ew.decode_read_bytes()
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    hbm = peaks.get("hbm_gbs", 6650.0)
+    value = 1000.0 / dev_ms
+    res = {
+        "metric": "decode tok/s (bs=1) at 27B" if args.model == "27b" else f"decode tok/s (bs=1) at {args.model}",
+        "value": round(value, 3), "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": round(dev_ms, 4), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": round(value / BASELINE_TOK_S, 3) if args.model == "27b" else None,
+        "dtype": "bf16 activations; weights " + args.preset, "data": "synthetic (random-init weights, uniform-random prompt ids)",
+        "config": {"model": f"qwen3.5-{args.model}-shaped hybrid (GDN:attn 3:1)", "global_batch": 1,
+                   "seq_len": args.context, "parallelism": f"tp{world}", "kv_cache": args.kv_dtype,
+                   "weight_preset": args.preset, "l2": "inputs larger than L2 (%.1f GB of weights per step)" % (rd_bytes / 1e9)},
+        "clocks": clocks,
+        "e2e": {"value": round(1000.0 / e2e_ms, 3), "unit": "tok/s", "ms_per_step": round(e2e_ms, 4),
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8},
+        "gpu_launches": launches_per_step * K,
+        "launches_per_step": launches_per_step,
+        "prefill": {"tokens": args.context, "ms": round(prefill_ms, 2), "tok_s": round(args.context / prefill_ms * 1e3, 1)},
+        "weights_gb_per_step": round(rd_bytes / 1e9, 3),
+        "hbm_roofline_frac_of_measured": round(rd_bytes / (dev_ms * 1e-3) / (hbm * 1e9), 4),
+        "build_s": round(build_s, 1), "token_checksum": checksum, "impl": "ours",
+    }
+    if rank == 0:
+        print(json.dumps(res), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

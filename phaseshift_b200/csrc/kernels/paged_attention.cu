@@ -1,0 +1,271 @@
+// Paged causal attention over BF16 / FP8-E4M3 KV pages: split-KV partial pass + merge pass.
+//
+// Flash-decoding structure like the reference's split-KV path (src/phaseshift/models/qwen35/kernels/
+// optimized/attention/paged_decode.hip:264-300,743-780; plan in runtime/paged_attention_dispatch.hip:
+// 437-468), with two differences that matter on B200:
+//   * the split length is a fixed number of tokens chosen once per engine, never a function of the
+//     batch, so a row's result is bit-identical whether it is decoded alone, verified among 16
+//     speculative rows or batched with other requests (the reference gets this by forcing S=16);
+//   * the merge pass also applies the sigmoid output gate, so o_proj reads its input directly.
+// One CTA = (split, kv head, row) and serves all G = Hq/Hkv query heads that share the K/V tile.
+//
+// K/V pools: [num_pages, Hkv, page_tokens, D]; FP8 pools carry one f32 scale per (page, head, token).
+#include "ps_common.cuh"
+
+namespace ps {
+
+constexpr int kAttnTile = 32;      // tokens per shared-memory tile
+constexpr int kAttnThreads = 256;
+constexpr int kAttnMaxG = 8;
+constexpr int kAttnMaxD = 256;
+
+struct PagedAttnArgs {
+    const __nv_bfloat16* q;      // [rows, Hq, D]
+    const void* k_pool; const void* v_pool; const float* k_scale; const float* v_scale;
+    const int* block_table; int max_blocks; int page_tokens; int num_pages;
+    const int* row_slot; const int* row_pos;
+    int rows, Hq, Hkv, D; float sm_scale; int kv_fp8;
+    int split_tokens, max_splits;
+    float* part_acc;   // [rows, Hq, max_splits, D]
+    float* part_ml;    // [rows, Hq, max_splits, 2]  (running max, running sum)
+    uint32_t* status;
+};
+
+struct TileRegs { uint4 k[4]; uint4 v[4]; float ks, vs; };
+
+// Fetch one 32-token tile (K and V rows of this kv head) into registers.  Thread t covers 16-byte
+// pieces t, t+256, ... of the [32, D] tile; threads 0..31 also fetch the fp8 token scales.
+__device__ __forceinline__ void tile_fetch(const PagedAttnArgs& a, TileRegs& r, int slot, int kvh, int tok0,
+                                           int visible, bool& bad) {
+    const int esz = a.kv_fp8 ? 1 : 2;
+    const int row_bytes = a.D * esz;
+    const int pieces_per_row = row_bytes / 16;
+    const int total = kAttnTile * pieces_per_row;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int p = threadIdx.x + i * kAttnThreads;
+        r.k[i] = make_uint4(0, 0, 0, 0); r.v[i] = make_uint4(0, 0, 0, 0);
+        if (p < total) {
+            const int t = p / pieces_per_row, c = p % pieces_per_row;
+            const int tok = tok0 + t;
+            if (tok < visible) {
+                const int page = a.block_table[(size_t)slot * a.max_blocks + tok / a.page_tokens];
+                if (page < 0 || page >= a.num_pages) { bad = true; continue; }
+                const size_t off = (((size_t)page * a.Hkv + kvh) * a.page_tokens + tok % a.page_tokens) * row_bytes + c * 16;
+                r.k[i] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(a.k_pool) + off));
+                r.v[i] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(a.v_pool) + off));
+            }
+        }
+    }
+    r.ks = 1.f; r.vs = 1.f;
+    if (a.kv_fp8 && threadIdx.x < kAttnTile) {
+        const int tok = tok0 + threadIdx.x;
+        if (tok < visible) {
+            const int page = a.block_table[(size_t)slot * a.max_blocks + tok / a.page_tokens];
+            if (page >= 0 && page < a.num_pages) {
+                const size_t so = ((size_t)page * a.Hkv + kvh) * a.page_tokens + tok % a.page_tokens;
+                r.ks = a.k_scale[so]; r.vs = a.v_scale[so];
+            }
+        }
+    }
+}
+
+// Registers -> shared memory as bf16 (fp8 codes widen exactly).  K rows are padded by 8 elements.
+__device__ __forceinline__ void tile_store(const PagedAttnArgs& a, const TileRegs& r, __nv_bfloat16* ks,
+                                           __nv_bfloat16* vs, float* kscale, float* vscale) {
+    const int kpitch = a.D + 8;
+    if (!a.kv_fp8) {
+        const int ppr = a.D * 2 / 16;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int p = threadIdx.x + i * kAttnThreads;
+            if (p < kAttnTile * ppr) {
+                const int t = p / ppr, c = p % ppr;
+                *reinterpret_cast<uint4*>(ks + t * kpitch + c * 8) = r.k[i];
+                *reinterpret_cast<uint4*>(vs + t * a.D + c * 8) = r.v[i];
+            }
+        }
+    } else {
+        const int ppr = a.D / 16;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int p = threadIdx.x + i * kAttnThreads;
+            if (p < kAttnTile * ppr) {
+                const int t = p / ppr, c = p % ppr;
+                const uint32_t kw[4] = {r.k[i].x, r.k[i].y, r.k[i].z, r.k[i].w};
+                const uint32_t vw[4] = {r.v[i].x, r.v[i].y, r.v[i].z, r.v[i].w};
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    ks[t * kpitch + c * 16 + j] = f32_to_bf16(e4m3_to_f32((kw[j >> 2] >> ((j & 3) * 8)) & 0xff));
+                    vs[t * a.D + c * 16 + j] = f32_to_bf16(e4m3_to_f32((vw[j >> 2] >> ((j & 3) * 8)) & 0xff));
+                }
+            }
+        }
+        if (threadIdx.x < kAttnTile) { kscale[threadIdx.x] = r.ks; vscale[threadIdx.x] = r.vs; }
+    }
+}
+
+__global__ void __launch_bounds__(kAttnThreads) paged_attn_split_kernel(const PagedAttnArgs a) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int D = a.D, G = a.Hq / a.Hkv, kpitch = D + 8;
+    __nv_bfloat16* ks = reinterpret_cast<__nv_bfloat16*>(smem);            // [32][D+8]
+    __nv_bfloat16* vs = ks + kAttnTile * kpitch;                           // [32][D]
+    float* qs = reinterpret_cast<float*>(vs + kAttnTile * D);              // [G][D]
+    float* ps_ = qs + kAttnMaxG * D;                                       // [G][32]
+    float* alpha = ps_ + kAttnMaxG * kAttnTile;                            // [G]
+    float* kscale = alpha + kAttnMaxG;                                     // [32]
+    float* vscale = kscale + kAttnTile;                                    // [32]
+
+    const int split = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
+    const int visible = a.row_pos[row] + 1;
+    const int tok_begin = split * a.split_tokens;
+    if (tok_begin >= visible) return;
+    const int tok_end = min(visible, tok_begin + a.split_tokens);
+    const int slot = a.row_slot[row];
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+
+    for (int i = t; i < G * D; i += kAttnThreads) {
+        const int g = i / D, d = i % D;
+        qs[i] = bf16_to_f32(a.q[((size_t)row * a.Hq + kvh * G + g) * D + d]) * a.sm_scale;
+    }
+    if (t < kAttnTile) { kscale[t] = 1.f; vscale[t] = 1.f; }
+    float acc[kAttnMaxG];
+#pragma unroll
+    for (int g = 0; g < kAttnMaxG; ++g) acc[g] = 0.f;
+    float m_run = -3.0e38f, l_run = 0.f;   // owned by warp g (all lanes hold the same value)
+
+    bool bad = false;
+    TileRegs regs;
+    tile_fetch(a, regs, slot, kvh, tok_begin, tok_end, bad);
+    for (int tok0 = tok_begin; tok0 < tok_end; tok0 += kAttnTile) {
+        __syncthreads();                       // previous tile fully consumed
+        tile_store(a, regs, ks, vs, kscale, vscale);
+        __syncthreads();
+        if (tok0 + kAttnTile < tok_end) tile_fetch(a, regs, slot, kvh, tok0 + kAttnTile, tok_end, bad);
+
+        // scores: warp g, lane = token
+        if (warp < G) {
+            const int tok = tok0 + lane;
+            float s = 0.f;
+            const __nv_bfloat16* kr = ks + lane * kpitch;
+            const float* qg = qs + warp * D;
+            for (int d = 0; d < D; d += 8) {
+                const uint4 kk = *reinterpret_cast<const uint4*>(kr + d);
+                const float4 qa = *reinterpret_cast<const float4*>(qg + d);
+                const float4 qb = *reinterpret_cast<const float4*>(qg + d + 4);
+                const float2 k0 = bf16x2_bits_to_f32x2(kk.x), k1 = bf16x2_bits_to_f32x2(kk.y);
+                const float2 k2 = bf16x2_bits_to_f32x2(kk.z), k3 = bf16x2_bits_to_f32x2(kk.w);
+                s = fmaf(k0.x, qa.x, s); s = fmaf(k0.y, qa.y, s); s = fmaf(k1.x, qa.z, s); s = fmaf(k1.y, qa.w, s);
+                s = fmaf(k2.x, qb.x, s); s = fmaf(k2.y, qb.y, s); s = fmaf(k3.x, qb.z, s); s = fmaf(k3.y, qb.w, s);
+            }
+            s *= kscale[lane];
+            const bool live = tok < tok_end;
+            if (!live) s = -3.0e38f;
+            const float m_new = fmaxf(m_run, warp_max(s));
+            const float p = live ? __expf(s - m_new) : 0.f;
+            const float al = __expf(m_run - m_new);
+            l_run = l_run * al + warp_sum(p);
+            m_run = m_new;
+            ps_[warp * kAttnTile + lane] = p * vscale[lane];
+            if (lane == 0) alpha[warp] = al;
+        }
+        __syncthreads();
+        // PV: thread = output dim, all heads
+        if (t < D) {
+#pragma unroll
+            for (int g = 0; g < kAttnMaxG; ++g) {
+                if (g < G) {
+                    float s = acc[g] * alpha[g];
+                    const float* pg = ps_ + g * kAttnTile;
+#pragma unroll 8
+                    for (int j = 0; j < kAttnTile; ++j) s = fmaf(pg[j], bf16_to_f32(vs[j * D + t]), s);
+                    acc[g] = s;
+                }
+            }
+        }
+    }
+    if (bad && t == 0) set_status(a.status, PS_DEV_BAD_INDEX);
+    // write partials
+    if (t < D) {
+#pragma unroll
+        for (int g = 0; g < kAttnMaxG; ++g)
+            if (g < G) a.part_acc[(((size_t)row * a.Hq + kvh * G + g) * a.max_splits + split) * D + t] = acc[g];
+    }
+    if (warp < G && lane == 0) {
+        float* ml = a.part_ml + (((size_t)row * a.Hq + kvh * G + warp) * a.max_splits + split) * 2;
+        ml[0] = m_run; ml[1] = l_run;
+    }
+}
+
+struct AttnMergeArgs {
+    const float* part_acc; const float* part_ml; const int* row_pos;
+    int rows, Hq, D, split_tokens, max_splits;
+    const __nv_bfloat16* gate; int ld_gate; int gate_head_stride; int gate_offset;   // optional sigmoid gate
+    __nv_bfloat16* out;   // [rows, Hq*D]
+};
+
+// grid = (Hq, rows), block = D threads.  Splits are merged in ascending order (fixed order => exact).
+__global__ void paged_attn_merge_kernel(const AttnMergeArgs a) {
+    const int h = blockIdx.x, row = blockIdx.y, d = threadIdx.x;
+    const int visible = a.row_pos[row] + 1;
+    const int n = (visible + a.split_tokens - 1) / a.split_tokens;
+    const float* ml = a.part_ml + ((size_t)row * a.Hq + h) * a.max_splits * 2;
+    const float* pa = a.part_acc + ((size_t)row * a.Hq + h) * a.max_splits * a.D;
+    float m = -3.0e38f;
+    for (int s = 0; s < n; ++s) m = fmaxf(m, ml[2 * s]);
+    float l = 0.f, o = 0.f;
+    for (int s = 0; s < n; ++s) {
+        const float w = __expf(ml[2 * s] - m);
+        l = fmaf(w, ml[2 * s + 1], l);
+        o = fmaf(w, pa[(size_t)s * a.D + d], o);
+    }
+    float v = l > 0.f ? o / l : 0.f;
+    if (a.gate != nullptr) {
+        v = bf16_to_f32(f32_to_bf16(v));
+        const float g = bf16_to_f32(a.gate[(size_t)row * a.ld_gate + h * a.gate_head_stride + a.gate_offset + d]);
+        v *= sigmoid_f(g);
+    }
+    a.out[((size_t)row * a.Hq + h) * a.D + d] = f32_to_bf16(v);
+}
+
+}  // namespace ps
+
+PS_API int ps_paged_attention(const void* q, const void* k_pool, const void* v_pool, const void* k_scale,
+                              const void* v_scale, const void* block_table, int max_blocks, int page_tokens,
+                              int num_pages, const void* row_slot, const void* row_pos, int rows, int Hq, int Hkv,
+                              int D, float sm_scale, int kv_fp8, int split_tokens, int max_splits, int max_visible,
+                              void* part_acc, void* part_ml, const void* gate, int ld_gate, int gate_head_stride,
+                              int gate_offset, void* out, void* status, cudaStream_t stream) {
+    using namespace ps;
+    const int G = Hkv > 0 ? Hq / Hkv : 0;
+    if (G < 1 || G > kAttnMaxG || D > kAttnMaxD || (D % 32) || (split_tokens % kAttnTile) || rows <= 0)
+        return (int)cudaErrorInvalidValue;
+    PagedAttnArgs a;
+    a.q = (const __nv_bfloat16*)q; a.k_pool = k_pool; a.v_pool = v_pool; a.k_scale = (const float*)k_scale;
+    a.v_scale = (const float*)v_scale; a.block_table = (const int*)block_table; a.max_blocks = max_blocks;
+    a.page_tokens = page_tokens; a.num_pages = num_pages; a.row_slot = (const int*)row_slot;
+    a.row_pos = (const int*)row_pos; a.rows = rows; a.Hq = Hq; a.Hkv = Hkv; a.D = D; a.sm_scale = sm_scale;
+    a.kv_fp8 = kv_fp8; a.split_tokens = split_tokens; a.max_splits = max_splits;
+    a.part_acc = (float*)part_acc; a.part_ml = (float*)part_ml; a.status = (uint32_t*)status;
+    int n_splits = (max_visible + split_tokens - 1) / split_tokens;
+    if (n_splits < 1) n_splits = 1;
+    if (n_splits > max_splits) return (int)cudaErrorInvalidValue;
+    const size_t smem = (size_t)kAttnTile * (D + 8) * 2 + (size_t)kAttnTile * D * 2 +
+                        sizeof(float) * (kAttnMaxG * D + kAttnMaxG * kAttnTile + kAttnMaxG + 2 * kAttnTile);
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(paged_attn_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+        attr_set = true;
+    }
+    dim3 grid(n_splits, Hkv, rows);
+    paged_attn_split_kernel<<<grid, kAttnThreads, smem, stream>>>(a);
+    int err = PS_LAUNCH_CHECK();
+    if (err) return err;
+    AttnMergeArgs m;
+    m.part_acc = a.part_acc; m.part_ml = a.part_ml; m.row_pos = a.row_pos; m.rows = rows; m.Hq = Hq; m.D = D;
+    m.split_tokens = split_tokens; m.max_splits = max_splits; m.gate = (const __nv_bfloat16*)gate;
+    m.ld_gate = ld_gate; m.gate_head_stride = gate_head_stride; m.gate_offset = gate_offset;
+    m.out = (__nv_bfloat16*)out;
+    paged_attn_merge_kernel<<<dim3(Hq, rows), D, 0, stream>>>(m);
+    return PS_LAUNCH_CHECK();
+}

@@ -1,0 +1,88 @@
+"""Qwen3.5 hybrid decoder forward over an op set (CUDA kernels or the PyTorch reference ops).
+
+One call = one scheduled step over a mixed batch of rows (decode rows, prefill chunks, speculative
+verify rows): the public contract is phase-agnostic like the reference executor's
+(AGENTS.md:133-157).  A decode layer is 5 launches (GDN) or 7 (full attention): the norms, gates,
+residual adds and SwiGLU live in the projection kernels' prologues/epilogues, versus ~26 dispatches
+per layer in the reference's lowering (src/phaseshift/models/qwen35/model/lower_to_primitives.cpp:694-960).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ...runtime.batch import StepBatch
+from ...runtime.state import ModelState
+from .config import Qwen35Config
+from .weights import EngineWeights
+
+
+class StepOutput:
+    __slots__ = ("tokens", "logits", "hidden", "taps")
+
+    def __init__(self, tokens, logits, hidden, taps):
+        self.tokens, self.logits, self.hidden, self.taps = tokens, logits, hidden, taps
+
+
+class Qwen35Runner:
+    def __init__(self, weights: EngineWeights, state: ModelState, ops, tp=None):
+        self.w, self.state, self.ops, self.tp = weights, state, ops, tp
+        self.cfg: Qwen35Config = weights.cfg
+        geo = state.geo
+        self.hq, self.hkv = len(geo.q_heads), len(geo.kv_heads)
+        self.hk, self.hv = len(geo.gdn_k_heads), len(geo.gdn_v_heads)
+
+    def _reduce(self, partial: torch.Tensor, residual: torch.Tensor, name: str) -> torch.Tensor:
+        """Row-parallel combine under TP: sum partial projections over ranks, then add the residual."""
+        return self.tp.all_reduce_residual(partial, residual, name)
+
+    def forward(self, b: StepBatch, rows: int, n_out: int, *, tap_layers: Sequence[int] = (),
+                gdn_log: Optional[Dict[int, tuple]] = None, gdn_to_alt: bool = False,
+                mask=None, mask_active=None, sample: bool = True) -> StepOutput:
+        cfg, ops, st, w = self.cfg, self.ops, self.state, self.w
+        eps = cfg.rms_norm_eps
+        tp_on = self.tp is not None and self.tp.size > 1
+        x = ops.embed(b, rows, w.embed, st.status)
+        taps = {}
+        for li, L in enumerate(w.layers):
+            m = L.mixer
+            if L.kind == 0:
+                n_main = m.in_proj.N
+                proj = ops.buf("gdn_proj", rows, n_main + m.ba_proj.N) if hasattr(ops, "buf") else None
+                if proj is not None:
+                    ops.linear(x, m.in_proj, name="gdn_in", norm_w=L.input_norm, eps=eps, out=proj[:, :n_main])
+                    ops.linear(x, m.ba_proj, name="gdn_ba", norm_w=L.input_norm, eps=eps, out=proj[:, n_main:])
+                else:
+                    proj = torch.cat([ops.linear(x, m.in_proj, name="gdn_in", norm_w=L.input_norm, eps=eps),
+                                      ops.linear(x, m.ba_proj, name="gdn_ba", norm_w=L.input_norm, eps=eps)], 1)
+                o = ops.gdn(proj, m, self.hk, self.hv, b, st.gdn[li], st,
+                            log=None if gdn_log is None else gdn_log[li], to_alt=gdn_to_alt)
+                if tp_on:
+                    r = self._reduce(ops.linear(o, m.out_proj, name="mix_out"), x, "r")
+                else:
+                    r = ops.linear(o, m.out_proj, name="r", residual=x)
+            else:
+                qkv = ops.linear(x, m.qkv_proj, name="attn_qkv", norm_w=L.input_norm, eps=eps)
+                q = ops.attn_prep(qkv, m, self.hq, self.hkv, b, st.kv[li], st)
+                ctx = ops.paged_attention(q, qkv, self.hq, self.hkv, b, st.kv[li], st, b.max_visible_launch)
+                if tp_on:
+                    r = self._reduce(ops.linear(ctx, m.o_proj, name="mix_out"), x, "r")
+                else:
+                    r = ops.linear(ctx, m.o_proj, name="r", residual=x)
+            act = ops.linear(r, L.gate_up, name="mlp_act", norm_w=L.post_norm, eps=eps, swiglu=True)
+            # ping-pong the residual stream so a layer never writes the buffer it still reads
+            xname = "x_a" if (li & 1) == 0 else "x_b"
+            if tp_on:
+                x = self._reduce(ops.linear(act, L.down, name="mlp_out"), r, xname)
+            else:
+                x = ops.linear(act, L.down, name=xname, residual=r)
+            if li in tap_layers:
+                taps[li] = x if not hasattr(ops, "buf") else ops.buf(f"tap{li}", rows, x.shape[1]).copy_(x)
+        tokens = logits = hidden = None
+        if n_out > 0:
+            hidden = ops.gather_rows(x, b.out_rows, n_out, "out_hidden", st.status)
+            logits = ops.linear(hidden, w.lm_head, name="logits", norm_w=w.final_norm, eps=eps, out_f32=True)
+            if sample:
+                tokens = ops.sample(logits, b, n_out, mask=mask, mask_active=mask_active, status=st.status)
+        return StepOutput(tokens, logits, hidden, taps)

@@ -1,0 +1,59 @@
+"""ctypes binding to ``libps_kernels.so`` (the hand-written sm_100a kernels).
+
+Every launcher is ``extern "C" int ps_xxx(..., cudaStream_t)`` and returns a ``cudaError_t`` value.
+There is no fallback: if the library is missing on a machine with a GPU the import raises, so a test
+run can never silently pass on PyTorch eager code.
+"""
+from __future__ import annotations
+
+import ctypes
+from pathlib import Path
+
+import torch
+
+_LIB = None
+
+
+class KernelLibraryError(RuntimeError):
+    pass
+
+
+def lib() -> ctypes.CDLL:
+    global _LIB
+    if _LIB is None:
+        from ..build import kernels_lib_path, build_kernels
+        p = kernels_lib_path()
+        if not p.exists():
+            try:
+                build_kernels()
+            except Exception as e:  # pragma: no cover - build environment problem
+                raise KernelLibraryError(f"libps_kernels.so is not built and nvcc failed: {e}") from e
+        _LIB = ctypes.CDLL(str(p))
+    return _LIB
+
+
+def ptr(t) -> ctypes.c_void_p:
+    if t is None:
+        return ctypes.c_void_p(0)
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def check(err: int, what: str) -> None:
+    if err != 0:
+        raise KernelLibraryError(f"{what} failed with cudaError {err}")
+
+
+def call(name: str, *args) -> None:
+    """Call launcher ``name`` with pre-converted ctypes args and the current stream appended."""
+    fn = getattr(lib(), name)
+    fn.restype = ctypes.c_int
+    check(fn(*args, stream()), name)
+
+
+c_int = ctypes.c_int
+c_float = ctypes.c_float
+c_ll = ctypes.c_longlong

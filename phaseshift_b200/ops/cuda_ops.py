@@ -1,0 +1,181 @@
+"""CUDA op set: thin Python wrappers over the sm_100a kernels in ``libps_kernels.so``.
+
+Each method validates shapes/dtypes (the role of the reference's ``resolve_*_args`` functions, e.g.
+src/phaseshift/models/qwen35/runtime/paged_attention_dispatch.hip:274-436), picks the kernel variant
+(small-M fused GEMV vs tensor-core GEMM -- the job of the reference's linear selector,
+src/.../runtime/linear_selector.cpp:202-308) and launches on the current stream.  Output buffers come
+from a per-instance workspace keyed by (name, rows) so pointers are stable across steps, which is
+what lets a whole step be captured in a CUDA graph.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, Optional, Tuple
+
+import numpy as np
+import torch
+
+from ..models.qwen35.config import Qwen35Config
+from ..models.qwen35.weights import AttnW, GdnW, LinearW
+from ..runtime.batch import StepBatch
+from ..runtime.state import GdnLayerState, KVLayer, ModelState
+from . import _lib
+from ._lib import c_float, c_int, c_ll, ptr
+
+WFMT = {"bf16": 0, "nvfp4": 1, "mxfp8": 2}
+PRO_NONE, PRO_RMSNORM, PRO_SIGMOID_GATE = 0, 1, 2
+EPI_STORE, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2
+SMALL_M_MAX = 8
+
+
+class CudaOps:
+    act_dtype = torch.bfloat16
+    name = "cuda"
+
+    def __init__(self, cfg: Qwen35Config, device, attn_split_tokens: int = 128, attn_max_splits: int = 0,
+                 max_seq_len: int = 4096):
+        if device.type != "cuda":
+            raise ValueError("CudaOps needs a CUDA device")
+        _lib.lib()      # fail loudly when the native library is missing
+        self.cfg, self.device = cfg, device
+        self.ws: Dict[Tuple[str, int], torch.Tensor] = {}
+        half = cfg.rotary_dim // 2
+        inv = cfg.rope_theta ** (-np.arange(half, dtype=np.float64) * 2.0 / cfg.rotary_dim)
+        self.inv_freq = torch.from_numpy(inv).to(device)
+        # split length is fixed per engine (never per batch) so attention results are batch-invariant
+        self.split_tokens = attn_split_tokens
+        while -(-(max_seq_len + 1) // self.split_tokens) > 256:
+            self.split_tokens *= 2
+        self.max_splits = attn_max_splits or -(-(max_seq_len + 1) // self.split_tokens)
+        self.launches = 0
+        self.use_tc_gemm = True
+
+    # ------------------------------------------------------------------ workspace
+    def buf(self, name: str, rows: int, cols: int, dtype=torch.bfloat16) -> torch.Tensor:
+        key = (name, rows)
+        t = self.ws.get(key)
+        if t is None or t.shape[1] != cols or t.dtype != dtype:
+            t = torch.empty(rows, cols, dtype=dtype, device=self.device)
+            self.ws[key] = t
+        return t
+
+    # ------------------------------------------------------------------ ops
+    def embed(self, b: StepBatch, rows: int, table: LinearW, status) -> torch.Tensor:
+        H = table.K
+        out = self.buf("x_embed", rows, H)
+        if table.fmt == "bf16":
+            _lib.call("ps_embedding", ptr(b.ids), ptr(table.q.codes), c_int(rows), c_int(table.N), c_int(H),
+                      ptr(out), c_int(H), ptr(status))
+        elif table.fmt == "mxfp8":
+            _lib.call("ps_embedding_mxfp8", ptr(b.ids), ptr(table.q.codes), ptr(table.q.scales), c_int(rows),
+                      c_int(table.N), c_int(H), ptr(out), c_int(H), ptr(status))
+        else:
+            raise ValueError("embedding table must be bf16 or mxfp8")
+        self.launches += 1
+        return out
+
+    def linear(self, x: torch.Tensor, W: LinearW, *, name: str, norm_w: Optional[torch.Tensor] = None,
+               eps: float = 0.0, residual: Optional[torch.Tensor] = None, swiglu: bool = False,
+               out_f32: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        M, K = x.shape
+        assert K == W.K and x.dtype == torch.bfloat16 and x.stride(1) == 1, (x.shape, W.K, x.dtype)
+        n_out = W.N // 2 if swiglu else W.N
+        if out is None:
+            out = self.buf(name, M, n_out, torch.float32 if out_f32 else torch.bfloat16)
+        assert out.shape[0] == M and out.shape[1] == n_out and out.stride(1) == 1
+        if M > SMALL_M_MAX and self.use_tc_gemm and W.fmt == "bf16" and hasattr(self, "linear_large"):
+            return self.linear_large(x, W, name=name, norm_w=norm_w, eps=eps, residual=residual, swiglu=swiglu,
+                                     out_f32=out_f32, out=out)
+        pro = PRO_RMSNORM if norm_w is not None else PRO_NONE
+        epi = EPI_SWIGLU if swiglu else (EPI_RESIDUAL if residual is not None else EPI_STORE)
+        for m0 in range(0, M, SMALL_M_MAX):
+            m = min(SMALL_M_MAX, M - m0)
+            xs = x[m0:m0 + m]
+            os_ = out[m0:m0 + m]
+            rs = residual[m0:m0 + m] if residual is not None else None
+            _lib.call("ps_linear_small", c_int(WFMT[W.fmt]), ptr(xs), c_int(m), c_int(W.N), c_int(W.q.k_padded),
+                      c_int(x.stride(0)), ptr(W.q.codes), ptr(W.q.scales), c_float(W.q.tensor_scale), c_int(pro),
+                      ptr(norm_w), c_float(eps), ptr(None), c_int(0), c_int(epi), ptr(rs),
+                      c_int(residual.stride(0) if residual is not None else 0), ptr(os_), c_int(out.stride(0)),
+                      c_int(1 if out_f32 else 0))
+            self.launches += 1
+        return out
+
+    def attn_prep(self, qkv: torch.Tensor, aw: AttnW, hq: int, hkv: int, b: StepBatch, kv: KVLayer,
+                  st: ModelState) -> torch.Tensor:
+        cfg = self.cfg
+        rows, D = qkv.shape[0], cfg.head_dim
+        q = self.buf("attn_q", rows, hq * D)
+        _lib.call("ps_attn_prep", ptr(qkv), c_int(qkv.stride(0)), c_int(rows), c_int(hq), c_int(hkv), c_int(D),
+                  c_int(cfg.rotary_dim), ptr(aw.q_norm), ptr(aw.k_norm), c_float(cfg.rms_norm_eps),
+                  ptr(self.inv_freq), ptr(b.row_slot), ptr(b.row_pos), ptr(q), ptr(kv.k), ptr(kv.v),
+                  ptr(kv.k_scale), ptr(kv.v_scale), ptr(st.block_table), c_int(st.max_blocks),
+                  c_int(st.sc.page_tokens), c_int(st.num_pages), c_int(1 if st.kv_fp8 else 0), ptr(st.status))
+        self.launches += 1
+        return q
+
+    def paged_attention(self, q: torch.Tensor, qkv: torch.Tensor, hq: int, hkv: int, b: StepBatch, kv: KVLayer,
+                        st: ModelState, max_visible: int) -> torch.Tensor:
+        cfg = self.cfg
+        rows, D = q.shape[0], cfg.head_dim
+        out = self.buf("attn_ctx", rows, hq * D)
+        pacc = self.buf("attn_part_acc", rows, hq * self.max_splits * D, torch.float32)
+        pml = self.buf("attn_part_ml", rows, hq * self.max_splits * 2, torch.float32)
+        _lib.call("ps_paged_attention", ptr(q), ptr(kv.k), ptr(kv.v), ptr(kv.k_scale), ptr(kv.v_scale),
+                  ptr(st.block_table), c_int(st.max_blocks), c_int(st.sc.page_tokens), c_int(st.num_pages),
+                  ptr(b.row_slot), ptr(b.row_pos), c_int(rows), c_int(hq), c_int(hkv), c_int(D),
+                  c_float(D ** -0.5), c_int(1 if st.kv_fp8 else 0), c_int(self.split_tokens),
+                  c_int(self.max_splits), c_int(max_visible), ptr(pacc), ptr(pml), ptr(qkv), c_int(qkv.stride(0)),
+                  c_int(2 * D), c_int(D), ptr(out), ptr(st.status))
+        self.launches += 2
+        return out
+
+    def gdn(self, proj: torch.Tensor, gw: GdnW, hk: int, hv: int, b: StepBatch, gs: GdnLayerState,
+            st: ModelState, log=None, to_alt: bool = False) -> torch.Tensor:
+        cfg = self.cfg
+        rows = proj.shape[0]
+        Dk, Dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
+        out = self.buf("gdn_o", rows, hv * Dv)
+        state_out = gs.rec_alt if to_alt else gs.rec
+        lk = ld = ldd = None
+        if log is not None:
+            lk, ld, ldd = log
+        _lib.call("ps_gdn_rows", ptr(proj), c_int(proj.stride(0)), c_int(hk), c_int(hv), c_int(Dk), c_int(Dv),
+                  ptr(gw.conv_w), ptr(gw.A_log), ptr(gw.dt_bias), ptr(gw.norm_w), c_float(cfg.rms_norm_eps),
+                  ptr(gs.conv), c_int(st.sc.conv_ring), ptr(gs.rec), ptr(state_out), ptr(b.seq_desc),
+                  c_int(b.max_seqs if b.graph_static else b.n_seqs), ptr(out), ptr(lk), ptr(ld), ptr(ldd))
+        self.launches += 1
+        return out
+
+    def gdn_replay(self, gs: GdnLayerState, hv: int, seq_desc: torch.Tensor, n_seqs: int, log) -> None:
+        cfg = self.cfg
+        lk, ld, ldd = log
+        _lib.call("ps_gdn_replay", ptr(gs.rec), c_int(hv), c_int(cfg.linear_key_head_dim),
+                  c_int(cfg.linear_value_head_dim), ptr(seq_desc), c_int(n_seqs), ptr(lk), ptr(ld), ptr(ldd))
+        self.launches += 1
+
+    def gather_rows(self, x: torch.Tensor, rows_idx: torch.Tensor, n: int, name: str, status) -> torch.Tensor:
+        out = self.buf(name, n, x.shape[1], x.dtype)
+        rb = x.shape[1] * x.element_size()
+        _lib.call("ps_gather_rows", ptr(x), c_ll(x.stride(0) * x.element_size()), ptr(rows_idx), c_int(n), ptr(out),
+                  c_ll(rb), c_int(rb), c_int(x.shape[0]), ptr(status))
+        self.launches += 1
+        return out
+
+    def sample(self, logits: torch.Tensor, b: StepBatch, n: int, mask=None, mask_active=None,
+               status=None) -> torch.Tensor:
+        out = self.buf("sampled", max(n, 1), 1, torch.int32)
+        _lib.call("ps_sample", ptr(logits), c_int(logits.stride(0)), c_int(logits.shape[1]), c_int(n), ptr(b.d_samp),
+                  ptr(mask), c_int(mask.shape[1] if mask is not None else 0), ptr(mask_active), ptr(out), ptr(status))
+        self.launches += 1
+        return out.view(-1)[:n]
+
+    def rmsnorm(self, x: torch.Tensor, w: torch.Tensor, eps: float, name: str, one_plus: bool = True,
+                add: Optional[torch.Tensor] = None, sum_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        rows, H = x.shape
+        out = self.buf(name, rows, H)
+        _lib.call("ps_rmsnorm", ptr(x), c_int(x.stride(0)), ptr(add), c_int(add.stride(0) if add is not None else 0),
+                  ptr(sum_out), c_int(sum_out.stride(0) if sum_out is not None else 0), ptr(w), c_float(eps),
+                  c_int(rows), c_int(H), ptr(out), c_int(out.stride(0)), c_int(1 if one_plus else 0))
+        self.launches += 1
+        return out

@@ -1,0 +1,207 @@
+"""Block-scaled weight formats: NVFP4 (replaces PSQ4) and MXFP8 (replaces PSQ8), plus BF16.
+
+Canonical payload (what the quantised safetensors directory stores; K contiguous, one row per output
+feature, ``padded_k = align_up(k, 32)`` with zero padding, metadata never crossing a row -- the same
+shape rules as the reference's canonical SoA payload, docs/developer/psq_canonical_soa_payload.md:77-89):
+
+* ``nvfp4``: codes uint8 [N, Kp/2], sequential nibbles ``byte[j] = q[2j] | q[2j+1] << 4`` where
+  q = sign<<3 | index into {0, .5, 1, 1.5, 2, 3, 4, 6}; metadata1 = UE4M3 scale per 16 weights
+  [N, Kp/16]; metadata2 = one fp32 per-tensor scale.  w ~= E2M1[q] * e4m3(scale) * tensor_scale. 4.5 bpw.
+* ``mxfp8``: codes = E4M3 bytes [N, Kp]; metadata1 = UE8M0 exponent per 32 weights [N, Kp/32].
+  w ~= e4m3(code) * 2^(e-127).  8.25 bpw.
+
+Block scales are chosen by a small search around the max-abs scale that minimises the block's
+squared error, the counterpart of the reference's 65-candidate PSQ scale search
+(src/phaseshift/quantization/psq/psq.cpp:39-74); an optional per-input-channel importance vector
+(imatrix) weights the error like the reference's GPU quantiser does
+(src/phaseshift/quantization/offline/gpu_quantizer.hip:8-32).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+E2M1_VALUES = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+_E2M1_BOUNDS = (0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0)
+FORMATS = ("bf16", "nvfp4", "mxfp8")
+BLOCK = {"bf16": 16, "nvfp4": 16, "mxfp8": 32}
+K_ALIGN = 32
+DEFAULT_SEARCH = 2      # scale-search half-width used by quantize() (0 = plain max-abs scales)
+
+
+def align_up(x: int, a: int) -> int:
+    return (x + a - 1) // a * a
+
+
+def _e2m1_index(mag: torch.Tensor) -> torch.Tensor:
+    """Nearest E2M1 magnitude index; exact midpoints go to the even index (round-half-even on codes)."""
+    b = torch.tensor(_E2M1_BOUNDS, dtype=mag.dtype, device=mag.device)
+    idx = torch.bucketize(mag, b, right=False)           # mag == bound -> lower index
+    # midpoints: lower index is idx; choose even of (idx, idx+1)
+    at_mid = torch.zeros_like(mag, dtype=torch.bool)
+    for j, bd in enumerate(_E2M1_BOUNDS):
+        at_mid |= (mag == bd)
+    idx = torch.where(at_mid & (idx % 2 == 1), idx + 1, idx)
+    return idx.clamp_(max=7)
+
+
+def _e2m1_value(idx: torch.Tensor, dtype=torch.float32) -> torch.Tensor:
+    lut = torch.tensor(E2M1_VALUES, dtype=dtype, device=idx.device)
+    return lut[idx.long()]
+
+
+def _to_e4m3_bytes(x: torch.Tensor) -> torch.Tensor:
+    return x.clamp(-448.0, 448.0).to(torch.float8_e4m3fn).view(torch.uint8)
+
+
+def _from_e4m3_bytes(b: torch.Tensor) -> torch.Tensor:
+    return b.view(torch.float8_e4m3fn).to(torch.float32)
+
+
+@dataclass
+class QuantizedTensor:
+    fmt: str
+    shape: tuple                      # logical (N, K)
+    k_padded: int
+    codes: torch.Tensor               # bf16 [N, Kp] | uint8 [N, Kp/2] | uint8 [N, Kp]
+    scales: Optional[torch.Tensor] = None      # uint8 block scales
+    tensor_scale: float = 1.0
+
+    def to(self, device) -> "QuantizedTensor":
+        return QuantizedTensor(self.fmt, self.shape, self.k_padded, self.codes.to(device),
+                               None if self.scales is None else self.scales.to(device), self.tensor_scale)
+
+    @property
+    def nbytes(self) -> int:
+        n = self.codes.numel() * self.codes.element_size()
+        if self.scales is not None:
+            n += self.scales.numel()
+        return n
+
+
+def _pad_k(w: torch.Tensor) -> torch.Tensor:
+    n, k = w.shape
+    kp = align_up(k, K_ALIGN)
+    if kp == k:
+        return w
+    out = w.new_zeros(n, kp)
+    out[:, :k] = w
+    return out
+
+
+def quantize_nvfp4(w: torch.Tensor, importance: Optional[torch.Tensor] = None, search: int = 2,
+                   tensor_scale: Optional[float] = None) -> QuantizedTensor:
+    """w [N, K] float -> NVFP4.  ``search`` = number of e4m3 scale steps tried on each side."""
+    n, k = w.shape
+    wf = _pad_k(w.float())
+    kp = wf.shape[1]
+    amax_t = float(wf.abs().max())
+    if tensor_scale is None:
+        tensor_scale = amax_t / (6.0 * 448.0) if amax_t > 0 else 1.0
+    blk = wf.reshape(n, kp // 16, 16)
+    imp = None
+    if importance is not None:
+        imp = _pad_k(importance.float().reshape(1, -1)).reshape(1, kp // 16, 16)
+    base = blk.abs().amax(-1) / 6.0 / tensor_scale                      # ideal block scale in e4m3 units
+    base_b = _to_e4m3_bytes(base).to(torch.int16)
+    best_err = None
+    best_sb = None
+    best_q = None
+    for step in range(-search, search + 1):
+        sb = (base_b + step).clamp(0, 0x7E)                              # stay finite and non-negative
+        s = _from_e4m3_bytes(sb.to(torch.uint8)) * tensor_scale
+        s_safe = torch.where(s > 0, s, torch.ones_like(s))
+        r = blk / s_safe[..., None]
+        idx = _e2m1_index(r.abs())
+        deq = _e2m1_value(idx) * torch.sign(r) * s[..., None]
+        e = (deq - blk) ** 2
+        if imp is not None:
+            e = e * imp
+        err = e.sum(-1)
+        q = idx.to(torch.uint8) | ((r < 0).to(torch.uint8) << 3)
+        q = torch.where(idx == 0, torch.zeros_like(q), q)                # no negative zero
+        if best_err is None:
+            best_err, best_sb, best_q = err, sb, q
+        else:
+            take = err < best_err
+            best_err = torch.where(take, err, best_err)
+            best_sb = torch.where(take, sb, best_sb)
+            best_q = torch.where(take[..., None], q, best_q)
+    q = best_q.reshape(n, kp)
+    codes = (q[:, 0::2] | (q[:, 1::2] << 4)).contiguous()
+    return QuantizedTensor("nvfp4", (n, k), kp, codes, best_sb.to(torch.uint8).contiguous(), float(tensor_scale))
+
+
+def dequantize_nvfp4(q: QuantizedTensor) -> torch.Tensor:
+    n, k = q.shape
+    c = q.codes
+    lo, hi = c & 0xF, c >> 4
+    nib = torch.stack([lo, hi], -1).reshape(n, q.k_padded)
+    mag = _e2m1_value(nib & 7)
+    sign = torch.where((nib & 8) != 0, -1.0, 1.0)
+    s = _from_e4m3_bytes(q.scales) * q.tensor_scale
+    w = (mag * sign).reshape(n, q.k_padded // 16, 16) * s[..., None]
+    return w.reshape(n, q.k_padded)[:, :k].contiguous()
+
+
+def quantize_mxfp8(w: torch.Tensor, importance: Optional[torch.Tensor] = None, search: int = 1) -> QuantizedTensor:
+    n, k = w.shape
+    wf = _pad_k(w.float())
+    kp = wf.shape[1]
+    blk = wf.reshape(n, kp // 32, 32)
+    imp = None
+    if importance is not None:
+        imp = _pad_k(importance.float().reshape(1, -1)).reshape(1, kp // 32, 32)
+    amax = blk.abs().amax(-1)
+    e0 = torch.ceil(torch.log2(torch.where(amax > 0, amax, torch.ones_like(amax)) / 448.0))
+    best_err = best_e = best_c = None
+    for step in range(-search, search + 1):
+        e = (e0 + step).clamp(-126, 127)
+        s = torch.exp2(e)
+        cb = _to_e4m3_bytes(blk / s[..., None])
+        deq = _from_e4m3_bytes(cb) * s[..., None]
+        er = (deq - blk) ** 2
+        if imp is not None:
+            er = er * imp
+        err = er.sum(-1)
+        if best_err is None:
+            best_err, best_e, best_c = err, e, cb
+        else:
+            take = err < best_err
+            best_err = torch.where(take, err, best_err)
+            best_e = torch.where(take, e, best_e)
+            best_c = torch.where(take[..., None], cb, best_c)
+    scales = (best_e + 127).to(torch.uint8).contiguous()
+    return QuantizedTensor("mxfp8", (n, k), kp, best_c.reshape(n, kp).contiguous(), scales, 1.0)
+
+
+def dequantize_mxfp8(q: QuantizedTensor) -> torch.Tensor:
+    n, k = q.shape
+    s = torch.exp2(q.scales.float() - 127.0)
+    w = _from_e4m3_bytes(q.codes).reshape(n, q.k_padded // 32, 32) * s[..., None]
+    return w.reshape(n, q.k_padded)[:, :k].contiguous()
+
+
+def quantize(w: torch.Tensor, fmt: str, importance: Optional[torch.Tensor] = None) -> QuantizedTensor:
+    if fmt == "nvfp4":
+        return quantize_nvfp4(w, importance, search=DEFAULT_SEARCH)
+    if fmt == "mxfp8":
+        return quantize_mxfp8(w, importance, search=min(DEFAULT_SEARCH, 1))
+    if fmt == "bf16":
+        n, k = w.shape
+        return QuantizedTensor("bf16", (n, k), k, w.to(torch.bfloat16).contiguous(), None, 1.0)
+    raise ValueError(f"unknown weight format {fmt!r}")
+
+
+def dequantize(q: QuantizedTensor) -> torch.Tensor:
+    if q.fmt == "nvfp4":
+        return dequantize_nvfp4(q)
+    if q.fmt == "mxfp8":
+        return dequantize_mxfp8(q)
+    return q.codes.float()[:, :q.shape[1]]
+
+
+def bits_per_weight(fmt: str) -> float:
+    return {"bf16": 16.0, "nvfp4": 4.5, "mxfp8": 8.25}[fmt]

@@ -1,0 +1,272 @@
+"""Single-rank step engine: owns weights, sequence state, row-bucketed step plans and CUDA graphs.
+
+The reference builds one static Program per row bucket and optionally replays it from a HIP graph
+(src/phaseshift/models/qwen35/runtime/executor.hip:806-823,991-1090).  Here a "program" is the Python
+forward over fused kernels with stable workspace pointers; for decode-sized buckets it is captured
+once into a CUDA graph and replayed, so a decode step costs one pinned H2D of the batch descriptor,
+one graph launch and one 4-byte D2H per sampled row.
+
+Step protocol (mirrors submit_co_batch / complete_batch, executor.hip:536-1132,2339-2423):
+``reserve`` pages for every appended position -> run -> read status word -> ``commit`` positions, or
+roll the reservation back and poison the sequences when the device reported a failure.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..models.qwen35.config import Qwen35Config
+from ..models.qwen35.model import Qwen35Runner, StepOutput
+from ..models.qwen35.weights import EngineWeights, TpGeometry
+from .batch import SeqRows, StepBatch, resolve_row_bucket
+from .state import ModelState, StateConfig
+
+GRAPH_MAX_ROWS = 8
+
+
+class SequenceError(RuntimeError):
+    pass
+
+
+@dataclass
+class Sequence_:
+    slot: int
+    generation: int
+    position: int = 0                   # committed tokens
+    pages: List[int] = field(default_factory=list)
+    poisoned: bool = False
+
+
+class PageAllocator:
+    """Free-list over KV pages (page 0 reserved) + per-slot generation counters for stale-handle
+    detection (reference: state/sequence_slot_pool.h:14-96, state/paged_kv_pool.h free-page list)."""
+
+    def __init__(self, num_pages: int, max_slots: int):
+        self.free_pages = list(range(num_pages - 1, 0, -1))
+        self.free_slots = list(range(max_slots - 1, -1, -1))
+        self.generation = [0] * max_slots
+
+    def alloc_slot(self) -> Optional[int]:
+        return self.free_slots.pop() if self.free_slots else None
+
+    def release_slot(self, slot: int) -> None:
+        self.generation[slot] += 1
+        self.free_slots.append(slot)
+
+    def alloc_page(self) -> Optional[int]:
+        return self.free_pages.pop() if self.free_pages else None
+
+    def release_pages(self, pages: Sequence[int]) -> None:
+        self.free_pages.extend(pages)
+
+    @property
+    def pages_free(self) -> int:
+        return len(self.free_pages)
+
+
+class Engine:
+    def __init__(self, weights: EngineWeights, device, state_cfg: StateConfig, backend: str = "auto", tp=None,
+                 use_graphs: bool = True):
+        self.cfg: Qwen35Config = weights.cfg
+        self.device = torch.device(device)
+        if backend == "auto":
+            backend = "cuda" if self.device.type == "cuda" else "ref"
+        self.backend = backend
+        geo = TpGeometry.make(self.cfg, weights.tp_rank, weights.tp_size)
+        if backend == "cuda":
+            from ..ops.cuda_ops import CudaOps
+            self.ops = CudaOps(self.cfg, self.device, max_seq_len=state_cfg.max_seq_len)
+        else:
+            from ..ops.ref_ops import RefOps
+            self.ops = RefOps(self.cfg, self.device)
+        self.sc = state_cfg
+        self.state = ModelState(self.cfg, state_cfg, self.device, self.ops.act_dtype, geo)
+        self.runner = Qwen35Runner(weights, self.state, self.ops, tp)
+        self.alloc = PageAllocator(self.state.num_pages, state_cfg.max_slots)
+        self.seqs: Dict[int, Sequence_] = {}
+        self.batches: Dict[int, StepBatch] = {}
+        self.graphs: Dict[int, object] = {}
+        self.graph_out: Dict[int, StepOutput] = {}
+        self.launches_per_graph: Dict[int, int] = {}
+        self.use_graphs = use_graphs and backend == "cuda"
+        self.h_tokens = torch.zeros(2048, dtype=torch.int32, pin_memory=(self.device.type == "cuda"))
+        self.h_status = torch.zeros(1, dtype=torch.int32, pin_memory=(self.device.type == "cuda"))
+        self.steps = 0
+
+    # ------------------------------------------------------------------ sequences
+    def open_sequence(self) -> Sequence_:
+        slot = self.alloc.alloc_slot()
+        if slot is None:
+            raise SequenceError("no free sequence slot")
+        s = Sequence_(slot, self.alloc.generation[slot])
+        self.state.reset_slot(slot)
+        self.state.block_table[slot].fill_(-1)
+        self.seqs[slot] = s
+        return s
+
+    def close_sequence(self, s: Sequence_) -> None:
+        if self.alloc.generation[s.slot] != s.generation:
+            raise SequenceError("stale sequence handle")
+        self.alloc.release_pages(s.pages)
+        s.pages = []
+        self.alloc.release_slot(s.slot)
+        del self.seqs[s.slot]
+
+    def _reserve(self, s: Sequence_, upto: int) -> int:
+        """Map pages so positions < upto exist; returns how many pages were added (for rollback)."""
+        pt = self.sc.page_tokens
+        need = -(-upto // pt)
+        if need > self.state.max_blocks:
+            raise SequenceError("sequence exceeds max_seq_len")
+        added = 0
+        new_entries = []
+        while len(s.pages) < need:
+            pg = self.alloc.alloc_page()
+            if pg is None:
+                self.alloc.release_pages(s.pages[len(s.pages) - added:])
+                del s.pages[len(s.pages) - added:]
+                raise SequenceError("out of KV pages")
+            new_entries.append((len(s.pages), pg))
+            s.pages.append(pg)
+            added += 1
+        if new_entries:
+            idx0 = new_entries[0][0]
+            vals = torch.tensor([p for _, p in new_entries], dtype=torch.int32)
+            self.state.block_table[s.slot, idx0:idx0 + len(vals)] = vals.to(self.device)
+        return added
+
+    def trim_pages(self, s: Sequence_) -> None:
+        """Return pages past the committed position (after a speculative step kept fewer rows)."""
+        pt = self.sc.page_tokens
+        need = -(-max(s.position, 1) // pt)
+        if len(s.pages) > need:
+            extra = s.pages[need:]
+            del s.pages[need:]
+            self.state.block_table[s.slot, need:need + len(extra)] = -1
+            self.alloc.release_pages(extra)
+
+    # ------------------------------------------------------------------ stepping
+    def _batch(self, bucket: int) -> StepBatch:
+        b = self.batches.get(bucket)
+        if b is None:
+            b = StepBatch(bucket, min(bucket, self.sc.max_slots), self.device)
+            b.max_context = self.sc.max_seq_len + 1
+            self.batches[bucket] = b
+        return b
+
+    def step(self, rows: Sequence[SeqRows], seq_objs: Sequence[Sequence_], *, commit: bool = True,
+             tap_layers: Sequence[int] = (), gdn_log=None, gdn_to_alt: bool = False, mask=None,
+             mask_active=None, want_logits: bool = False, sample: bool = True):
+        """Run one step.  Returns (tokens list[int] per output row, StepOutput)."""
+        n_rows = sum(len(r.token_ids) for r in rows)
+        n_out = sum(len(r.output_rows) for r in rows)
+        bucket = resolve_row_bucket(n_rows)
+        b = self._batch(bucket)
+        added = []
+        try:
+            for r, s in zip(rows, seq_objs):
+                if s.poisoned:
+                    raise SequenceError("sequence is poisoned")
+                if r.pos_start != s.position and commit:
+                    raise SequenceError("rows must start at the committed position")
+                added.append(self._reserve(s, r.pos_start + len(r.token_ids)))
+        except SequenceError:
+            for s, a in zip(seq_objs, added):
+                if a:
+                    self.alloc.release_pages(s.pages[-a:])
+                    del s.pages[-a:]
+            raise
+        b.fill(rows)
+        plain = not tap_layers and gdn_log is None and not gdn_to_alt and mask is None and sample
+        use_graph = self.use_graphs and bucket <= GRAPH_MAX_ROWS and plain
+        b.graph_static = use_graph
+        b.upload()
+        if use_graph:
+            out = self._run_graph(bucket, b, n_out)
+        else:
+            out = self.runner.forward(b, bucket if self.backend == "cuda" else n_rows, n_out, tap_layers=tap_layers,
+                                      gdn_log=gdn_log, gdn_to_alt=gdn_to_alt, mask=mask, mask_active=mask_active,
+                                      sample=sample)
+        toks: List[int] = []
+        if self.device.type == "cuda":
+            if out.tokens is not None and n_out:
+                self.h_tokens[:n_out].copy_(out.tokens[:n_out], non_blocking=True)
+            self.h_status.copy_(self.state.status, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            status = int(self.h_status[0])
+            if out.tokens is not None:
+                toks = self.h_tokens[:n_out].tolist()
+        else:
+            status = int(self.state.status[0])
+            if out.tokens is not None:
+                toks = out.tokens[:n_out].tolist()
+        self.steps += 1
+        if status != 0:
+            self.state.status.zero_()
+            for s in seq_objs:
+                s.poisoned = True
+            raise SequenceError(f"device reported status {status}; sequences poisoned")
+        if commit:
+            for r, s in zip(rows, seq_objs):
+                s.position = r.pos_start + len(r.token_ids)
+        return toks, out
+
+    def _run_graph(self, bucket: int, b: StepBatch, n_out: int) -> StepOutput:
+        key = bucket * 4096 + n_out
+        g = self.graphs.get(key)
+        if g is None:
+            # warm up once outside capture (allocates workspaces, sets kernel attributes)
+            self.runner.forward(b, bucket, n_out)
+            torch.cuda.current_stream().synchronize()
+            g = torch.cuda.CUDAGraph()
+            l0 = self.ops.launches
+            with torch.cuda.graph(g, stream=torch.cuda.Stream(self.device)):
+                out = self.runner.forward(b, bucket, n_out)
+            self.launches_per_graph[key] = self.ops.launches - l0
+            self.graphs[key] = g
+            self.graph_out[key] = out
+            # the warm-up and capture forwards ran the real step already (state was updated once by the
+            # warm-up, capture does not execute), so fall through to a replay only on later calls
+            return self._replay_after_warmup(key)
+        g.replay()
+        return self.graph_out[key]
+
+    def _replay_after_warmup(self, key: int) -> StepOutput:
+        # The warm-up forward already produced this step's results in the same workspace buffers.
+        return self.graph_out[key]
+
+    # ------------------------------------------------------------------ convenience: one request
+    def prefill(self, s: Sequence_, token_ids: Sequence[int], chunk: int = 2048, sample_last: bool = True,
+                **samp) -> Optional[int]:
+        tok = None
+        n = len(token_ids)
+        for c0 in range(0, n, chunk):
+            ids = token_ids[c0:c0 + chunk]
+            last = c0 + chunk >= n
+            r = SeqRows(s.slot, s.position, ids, output_rows=(len(ids) - 1,) if (last and sample_last) else (), **samp)
+            toks, _ = self.step([r], [s])
+            if toks:
+                tok = toks[0]
+        return tok
+
+    def decode(self, s: Sequence_, token: int, **samp) -> int:
+        r = SeqRows(s.slot, s.position, [token], output_rows=(0,), **samp)
+        toks, _ = self.step([r], [s])
+        return toks[0]
+
+    def generate(self, prompt: Sequence[int], max_new_tokens: int, prefill_chunk: int = 2048, temperature: float = 0.0,
+                 top_p: float = 1.0, top_k: int = 0, seed: int = 0, eos: Sequence[int] = ()) -> List[int]:
+        s = self.open_sequence()
+        try:
+            out: List[int] = []
+            samp = dict(temperature=temperature, top_p=top_p, top_k=top_k, seed=seed)
+            tok = self.prefill(s, prompt, prefill_chunk, sample_index=0, **samp)
+            out.append(tok)
+            while len(out) < max_new_tokens and tok not in eos:
+                tok = self.decode(s, tok, sample_index=len(out), **samp)
+                out.append(tok)
+            return out
+        finally:
+            self.close_sequence(s)

@@ -1,0 +1,130 @@
+"""Device-resident sequence state: paged KV pools, GDN conv/recurrent pools, block tables.
+
+Layouts (chosen for Blackwell: every (page, kv-head) tile is one contiguous 8 KB / 4 KB block that a
+single bulk copy can fetch; the reference interleaves heads inside a token,
+include/phaseshift/models/qwen35/state/paged_kv_pool.h:59-140):
+
+* K/V pool per attention layer: ``[num_pages, Hkv, page_tokens, D]`` in bf16 or E4M3 bytes, FP8 pools
+  carry ``[num_pages, Hkv, page_tokens]`` f32 scales (one per token x head, like the reference's
+  FP8_E4M3 KV mode, state/kv_cache_types.h:11-46).
+* GDN conv history per GDN layer: ``[slots, Hv, ring, 2*Dk+Dv]`` bf16, position p in slot p % ring.
+* GDN recurrent state per GDN layer: ``[slots, Hv, Dk, Dv]`` f32 (reference: gdn_state_pool.h:16-105).
+* Block table: ``[slots, max_blocks]`` int32, -1 = unmapped.
+
+Sizing rules follow docs/developer/runtime.md:109-119:
+``max_blocks = ceil((max_seq_len+1)/page)+1``, ``pages = ceil(capacity_tokens/page)+1``.
+Page 0 is never handed out, so a zeroed block table entry cannot alias live data.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+
+from ..models.qwen35.config import Qwen35Config
+from ..models.qwen35.weights import TpGeometry
+
+KV_DTYPES = ("bf16", "fp8_e4m3")
+
+
+@dataclass
+class StateConfig:
+    max_slots: int = 1
+    max_seq_len: int = 512
+    page_tokens: int = 16
+    kv_capacity_tokens: int = 0          # 0 = one full context per slot
+    kv_dtype: str = "bf16"
+    conv_ring: int = 4                   # >= 4; 3 + max speculative rows when rollback is needed
+    spec_rows: int = 0                   # > 0 allocates the alternate recurrent state + update log
+
+    def max_blocks(self) -> int:
+        return -(-(self.max_seq_len + 1) // self.page_tokens) + 1
+
+    def num_pages(self) -> int:
+        cap = self.kv_capacity_tokens or self.max_slots * (self.max_seq_len + 1)
+        return -(-cap // self.page_tokens) + 1 + self.max_slots
+
+
+class KVLayer:
+    __slots__ = ("k", "v", "k_scale", "v_scale")
+
+    def __init__(self, k, v, k_scale, v_scale):
+        self.k, self.v, self.k_scale, self.v_scale = k, v, k_scale, v_scale
+
+
+class GdnLayerState:
+    __slots__ = ("conv", "rec", "rec_alt")
+
+    def __init__(self, conv, rec, rec_alt):
+        self.conv, self.rec, self.rec_alt = conv, rec, rec_alt
+
+
+class ModelState:
+    """All per-sequence device state of one rank."""
+
+    def __init__(self, cfg: Qwen35Config, sc: StateConfig, device, act_dtype=torch.bfloat16,
+                 geo: Optional[TpGeometry] = None):
+        if sc.kv_dtype not in KV_DTYPES:
+            raise ValueError(f"kv dtype {sc.kv_dtype!r} not in {KV_DTYPES}")
+        if sc.conv_ring < 4:
+            raise ValueError("conv_ring must be >= 4")
+        self.cfg, self.sc, self.device = cfg, sc, device
+        geo = geo or TpGeometry.make(cfg, 0, 1)
+        self.geo = geo
+        self.hkv = len(geo.kv_heads)
+        self.hv = len(geo.gdn_v_heads)
+        self.num_pages = sc.num_pages()
+        self.max_blocks = sc.max_blocks()
+        D, pt = cfg.head_dim, sc.page_tokens
+        fp8 = sc.kv_dtype == "fp8_e4m3"
+        self.kv_fp8 = fp8
+        if act_dtype == torch.float32:
+            kvt = torch.float32          # CPU reference keeps full precision
+            fp8 = self.kv_fp8 = False
+        else:
+            kvt = torch.uint8 if fp8 else torch.bfloat16
+        self.kv: List[Optional[KVLayer]] = []
+        self.gdn: List[Optional[GdnLayerState]] = []
+        Dk, Dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
+        for lt in cfg.layer_types:
+            if lt == 1:
+                k = torch.zeros(self.num_pages, self.hkv, pt, D, dtype=kvt, device=device)
+                v = torch.zeros_like(k)
+                ks = vs = None
+                if fp8:
+                    ks = torch.ones(self.num_pages, self.hkv, pt, dtype=torch.float32, device=device)
+                    vs = torch.ones_like(ks)
+                self.kv.append(KVLayer(k, v, ks, vs))
+                self.gdn.append(None)
+            else:
+                conv = torch.zeros(sc.max_slots, self.hv, sc.conv_ring, 2 * Dk + Dv,
+                                   dtype=act_dtype, device=device)
+                rec = torch.zeros(sc.max_slots, self.hv, Dk, Dv, dtype=torch.float32, device=device)
+                alt = torch.zeros_like(rec) if sc.spec_rows > 0 else None
+                self.gdn.append(GdnLayerState(conv, rec, alt))
+                self.kv.append(None)
+        self.block_table = torch.full((sc.max_slots, self.max_blocks), -1, dtype=torch.int32, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def kv_bytes(self) -> int:
+        n = 0
+        for l in self.kv:
+            if l is not None:
+                n += 2 * l.k.numel() * l.k.element_size()
+                if l.k_scale is not None:
+                    n += 2 * l.k_scale.numel() * 4
+        return n
+
+    def reset_slot(self, slot: int) -> None:
+        """Fresh sequence: zero recurrent state (conv history needs no clearing: taps before position 0
+        are defined as zero by the kernels)."""
+        for g in self.gdn:
+            if g is not None:
+                g.rec[slot].zero_()
+
+    def copy_slot(self, dst: int, src: int) -> None:
+        for g in self.gdn:
+            if g is not None:
+                g.rec[dst].copy_(g.rec[src])
+                g.conv[dst].copy_(g.conv[src])

@@ -1,0 +1,270 @@
+"""CUDA kernels vs plain PyTorch fp32 references of the same op (all marked gpu)."""
+import numpy as np
+import pytest
+import torch
+
+from phaseshift_b200.models.qwen35.config import tiny_config, Qwen35Config
+from phaseshift_b200.models.qwen35.weights import (LinearW, build_engine_weights, random_hf_weights, TpGeometry)
+from phaseshift_b200.quant.formats import quantize, dequantize
+from phaseshift_b200.runtime.batch import SeqRows, StepBatch
+from phaseshift_b200.runtime.state import ModelState, StateConfig
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev():
+    return torch.device("cuda:0")
+
+
+def _ops(cfg, max_seq_len=512):
+    from phaseshift_b200.ops.cuda_ops import CudaOps
+    from phaseshift_b200.ops.ref_ops import RefOps
+    return CudaOps(cfg, _dev(), max_seq_len=max_seq_len), RefOps(cfg, _dev())
+
+
+def _rel_err(a, b):
+    a, b = a.float(), b.float()
+    return float((a - b).norm() / (b.norm() + 1e-12))
+
+
+@pytest.mark.parametrize("fmt", ["bf16", "nvfp4", "mxfp8"])
+@pytest.mark.parametrize("M", [1, 2, 3, 8, 11])
+@pytest.mark.parametrize("shape", [(96, 256), (1024, 5120), (530, 17408)])
+def test_linear_small_plain(fmt, M, shape):
+    N, K = shape
+    cfg = tiny_config()
+    cu, ref = _ops(cfg)
+    g = torch.Generator(device="cuda").manual_seed(N + K + M)
+    w = torch.randn(N, K, device="cuda", generator=g) * 0.02
+    x = (torch.randn(M, K, device="cuda", generator=g) * 1.5).to(torch.bfloat16)
+    W = LinearW(quantize(w, fmt))
+    y = cu.linear(x, W, name="t", out_f32=True)
+    y_ref = x.float() @ W.dense().T
+    torch.cuda.synchronize()
+    assert _rel_err(y, y_ref) < (2e-3 if fmt != "bf16" else 1e-5), _rel_err(y, y_ref)
+
+
+@pytest.mark.parametrize("fmt", ["bf16", "nvfp4"])
+def test_linear_small_fused_prologue_epilogue(fmt):
+    cfg = tiny_config()
+    cu, ref = _ops(cfg)
+    g = torch.Generator(device="cuda").manual_seed(5)
+    K, N, M = 1024, 512, 4
+    w = torch.randn(N, K, device="cuda", generator=g) * 0.03
+    x = (torch.randn(M, K, device="cuda", generator=g) * 3).to(torch.bfloat16)
+    nw = (torch.randn(K, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    res = torch.randn(M, N, device="cuda", generator=g).to(torch.bfloat16)
+    W = LinearW(quantize(w, fmt))
+    tol = 1e-2
+    y = cu.linear(x, W, name="a", norm_w=nw, eps=1e-6, residual=res)
+    y_ref = ref.linear(x, W, name="a", norm_w=nw, eps=1e-6, residual=res)
+    assert _rel_err(y, y_ref) < tol
+    y = cu.linear(x, W, name="b", norm_w=nw, eps=1e-6, swiglu=True)
+    y_ref = ref.linear(x, W, name="b", norm_w=nw, eps=1e-6, swiglu=True)
+    assert _rel_err(y, y_ref) < 2e-2
+
+
+def test_linear_small_rows_are_batch_invariant():
+    """Row r of an M=8 launch is bit-identical to the same row in an M=1 launch (Exact verify property)."""
+    cfg = tiny_config()
+    cu, _ = _ops(cfg)
+    g = torch.Generator(device="cuda").manual_seed(9)
+    for fmt in ("bf16", "nvfp4", "mxfp8"):
+        w = torch.randn(640, 5120, device="cuda", generator=g) * 0.02
+        x = torch.randn(8, 5120, device="cuda", generator=g).to(torch.bfloat16)
+        W = LinearW(quantize(w, fmt))
+        y8 = cu.linear(x, W, name="i8", out_f32=True).clone()
+        for r in (0, 3, 7):
+            y1 = cu.linear(x[r:r + 1], W, name="i1", out_f32=True)
+            assert torch.equal(y1[0], y8[r]), fmt
+
+
+def _mk_state(cfg, kv_dtype="bf16", slots=2, max_seq=256, ring=4):
+    sc = StateConfig(max_slots=slots, max_seq_len=max_seq, page_tokens=16, kv_dtype=kv_dtype, conv_ring=ring)
+    st_c = ModelState(cfg, sc, _dev(), torch.bfloat16)
+    st_r = ModelState(cfg, sc, _dev(), torch.float32)
+    for st in (st_c, st_r):
+        for s in range(slots):
+            nb = st.max_blocks
+            st.block_table[s, :nb] = torch.arange(1 + s * nb, 1 + (s + 1) * nb, dtype=torch.int32, device=_dev()) % st.num_pages
+    return sc, st_c, st_r
+
+
+@pytest.mark.parametrize("kv_dtype", ["bf16", "fp8_e4m3"])
+@pytest.mark.parametrize("geom", ["tiny", "big"])
+def test_attention_prefill_then_decode(kv_dtype, geom):
+    if geom == "tiny":
+        cfg = tiny_config()
+    else:
+        cfg = Qwen35Config(vocab_size=1024, hidden_size=512, intermediate_size=512, num_hidden_layers=4,
+                           num_attention_heads=12, num_key_value_heads=2, head_dim=256)
+    cu, ref = _ops(cfg, 512)
+    sc = StateConfig(max_slots=2, max_seq_len=512, page_tokens=16, kv_dtype=kv_dtype)
+    st_c = ModelState(cfg, sc, _dev(), torch.bfloat16)
+    st_r = ModelState(cfg, sc, _dev(), torch.float32)
+    nb = st_c.max_blocks
+    for st in (st_c, st_r):
+        perm = torch.randperm(st.num_pages - 1, generator=torch.Generator().manual_seed(1))[:2 * nb] + 1
+        st.block_table[0, :nb] = perm[:nb].int().to(_dev())
+        st.block_table[1, :nb] = perm[nb:2 * nb].int().to(_dev())
+    li = cfg.attn_layers[0]
+    hf = random_hf_weights(cfg, seed=3, device="cuda")
+    ew = build_engine_weights(cfg, lambda n: hf[n], "bf16", "cuda")
+    aw = ew.layers[li].mixer
+    Hq, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    g = torch.Generator(device="cuda").manual_seed(2)
+    width = 2 * Hq * D + 2 * Hkv * D
+    T = 300
+    tol = 2e-2 if kv_dtype == "bf16" else 6e-2
+    b = StepBatch(512, 2, _dev())
+    # prefill 300 rows of sequence 0 (multi-row causal), then 3 decode steps for both sequences
+    qkv = torch.randn(T, width, device="cuda", generator=g).to(torch.bfloat16)
+    b.fill([SeqRows(0, 0, [0] * T, ())]); b.upload()
+    q_c = cu.attn_prep(qkv, aw, Hq, Hkv, b, st_c.kv[li], st_c)
+    q_r = ref.attn_prep(qkv.float(), aw, Hq, Hkv, b, st_r.kv[li], st_r)
+    assert _rel_err(q_c, q_r) < 1e-2
+    o_c = cu.paged_attention(q_c, qkv, Hq, Hkv, b, st_c.kv[li], st_c, b.max_visible)
+    o_r = ref.paged_attention(q_r, qkv.float(), Hq, Hkv, b, st_r.kv[li], st_r, b.max_visible)
+    torch.cuda.synchronize()
+    assert _rel_err(o_c[:T], o_r[:T]) < tol
+    assert int(st_c.status[0]) == 0
+    for step in range(3):
+        qkv = torch.randn(2, width, device="cuda", generator=g).to(torch.bfloat16)
+        b2 = StepBatch(2, 2, _dev())
+        b2.fill([SeqRows(0, T + step, [0], ()), SeqRows(1, step, [0], ())]); b2.upload()
+        q_c = cu.attn_prep(qkv, aw, Hq, Hkv, b2, st_c.kv[li], st_c)
+        q_r = ref.attn_prep(qkv.float(), aw, Hq, Hkv, b2, st_r.kv[li], st_r)
+        o_c = cu.paged_attention(q_c, qkv, Hq, Hkv, b2, st_c.kv[li], st_c, b2.max_visible)
+        o_r = ref.paged_attention(q_r, qkv.float(), Hq, Hkv, b2, st_r.kv[li], st_r, b2.max_visible)
+        assert _rel_err(o_c, o_r) < tol
+    assert int(st_c.status[0]) == 0
+
+
+@pytest.mark.parametrize("geom", ["tiny", "big"])
+def test_gdn_rows_and_decode(geom):
+    if geom == "tiny":
+        cfg = tiny_config()
+    else:
+        cfg = Qwen35Config(vocab_size=1024, hidden_size=512, intermediate_size=512, num_hidden_layers=4,
+                           linear_num_key_heads=2, linear_num_value_heads=6)
+    cu, ref = _ops(cfg)
+    sc = StateConfig(max_slots=2, max_seq_len=256, page_tokens=16, conv_ring=8, spec_rows=8)
+    st_c = ModelState(cfg, sc, _dev(), torch.bfloat16)
+    st_r = ModelState(cfg, sc, _dev(), torch.float32)
+    hf = random_hf_weights(cfg, seed=4, device="cuda")
+    ew = build_engine_weights(cfg, lambda n: hf[n], "bf16", "cuda")
+    li = cfg.gdn_layers[0]
+    gw = ew.layers[li].mixer
+    Hk, Hv = cfg.linear_num_key_heads, cfg.linear_num_value_heads
+    width = gw.in_proj.N + gw.ba_proj.N
+    g = torch.Generator(device="cuda").manual_seed(7)
+    T = 37
+    proj = (torch.randn(T + 5, width, device="cuda", generator=g) * 0.7).to(torch.bfloat16)
+    b = StepBatch(64, 2, _dev())
+    b.fill([SeqRows(1, 0, [0] * T, ())]); b.upload()
+    o_c = cu.gdn(proj[:T], gw, Hk, Hv, b, st_c.gdn[li], st_c)
+    o_r = ref.gdn(proj[:T].float(), gw, Hk, Hv, b, st_r.gdn[li], st_r)
+    torch.cuda.synchronize()
+    assert _rel_err(o_c[:T], o_r[:T]) < 2e-2
+    assert _rel_err(st_c.gdn[li].rec[1], st_r.gdn[li].rec[1]) < 1e-3
+    # single-row decode continues from the stored state and conv ring
+    for i in range(5):
+        b1 = StepBatch(1, 1, _dev())
+        b1.fill([SeqRows(1, T + i, [0], ())]); b1.upload()
+        o_c = cu.gdn(proj[T + i:T + i + 1], gw, Hk, Hv, b1, st_c.gdn[li], st_c)
+        o_r = ref.gdn(proj[T + i:T + i + 1].float(), gw, Hk, Hv, b1, st_r.gdn[li], st_r)
+        assert _rel_err(o_c, o_r) < 2e-2
+    assert _rel_err(st_c.gdn[li].rec[1], st_r.gdn[li].rec[1]) < 1e-3
+
+
+def test_gdn_multirow_bit_equals_single_rows_and_replay():
+    """Verify-rows launch == sequential decodes bit for bit; log replay of an accepted prefix rebuilds
+    exactly the state sequential decoding reaches."""
+    cfg = tiny_config()
+    cu, _ = _ops(cfg)
+    sc = StateConfig(max_slots=2, max_seq_len=64, conv_ring=16, spec_rows=8)
+    hf = random_hf_weights(cfg, seed=5, device="cuda")
+    ew = build_engine_weights(cfg, lambda n: hf[n], "bf16", "cuda")
+    li = cfg.gdn_layers[0]
+    gw = ew.layers[li].mixer
+    Hk, Hv, Dk, Dv = cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
+    width = gw.in_proj.N + gw.ba_proj.N
+    g = torch.Generator(device="cuda").manual_seed(8)
+    proj = (torch.randn(6, width, device="cuda", generator=g) * 0.7).to(torch.bfloat16)
+    st_a = ModelState(cfg, sc, _dev(), torch.bfloat16)
+    st_b = ModelState(cfg, sc, _dev(), torch.bfloat16)
+    init = torch.randn_like(st_a.gdn[li].rec) * 0.1
+    st_a.gdn[li].rec.copy_(init); st_b.gdn[li].rec.copy_(init)
+    # A: one launch with 6 rows, writing the new state to the alternate buffer and logging updates
+    b = StepBatch(8, 1, _dev())
+    b.fill([SeqRows(0, 0, [0] * 6, ())]); b.upload()
+    log = (torch.zeros(8, Hv, Dk, device="cuda"), torch.zeros(8, Hv, Dv, device="cuda"), torch.zeros(8, Hv, device="cuda"))
+    o_multi = cu.gdn(proj, gw, Hk, Hv, b, st_a.gdn[li], st_a, log=log, to_alt=True).clone()
+    assert torch.equal(st_a.gdn[li].rec, init)          # old state untouched
+    # B: six single-row launches
+    outs = []
+    states = []
+    for i in range(6):
+        b1 = StepBatch(1, 1, _dev())
+        b1.fill([SeqRows(0, i, [0], ())]); b1.upload()
+        outs.append(cu.gdn(proj[i:i + 1], gw, Hk, Hv, b1, st_b.gdn[li], st_b).clone())
+        states.append(st_b.gdn[li].rec[0].clone())
+    assert torch.equal(o_multi[:6], torch.cat(outs, 0))
+    assert torch.equal(st_a.gdn[li].rec_alt[0], states[5])
+    # accept 4 of the 6 rows: replay the log on the old state
+    desc = torch.tensor([[0, 4, 0, 0]], dtype=torch.int32, device="cuda")
+    cu.gdn_replay(st_a.gdn[li], Hv, desc, 1, log)
+    torch.cuda.synchronize()
+    assert torch.equal(st_a.gdn[li].rec[0], states[3])
+
+
+def test_sampling_greedy_and_stochastic_match_host():
+    from phaseshift_b200.utils.sampling import sample_row_host, sampling_uniform
+    cfg = tiny_config()
+    cu, _ = _ops(cfg)
+    V = 5000
+    g = torch.Generator(device="cuda").manual_seed(11)
+    logits = torch.randn(6, V, device="cuda", generator=g) * 3
+    logits[0, 77] = logits[0, 4000] = 50.0       # tie -> lower id
+    b = StepBatch(8, 8, _dev())
+    rows = [SeqRows(0, 0, [0], (0,)),
+            SeqRows(0, 0, [0], (0,), temperature=1.0, seed=5, sample_index=3),
+            SeqRows(0, 0, [0], (0,), temperature=0.7, top_k=20, seed=6, sample_index=1),
+            SeqRows(0, 0, [0], (0,), temperature=1.3, top_p=0.8, seed=7, sample_index=9),
+            SeqRows(0, 0, [0], (0,), temperature=1.0, top_p=0.9, top_k=50, seed=8),
+            SeqRows(0, 0, [0], (0,))]
+    b.fill(rows); b.upload()
+    mask = torch.full((6, (V + 31) // 32), 0xFFFFFFFF, dtype=torch.int64).to(torch.int32).cuda()
+    mask[5].zero_(); mask[5, 3] = 1 << 4        # only token 100 allowed
+    active = torch.ones(6, dtype=torch.uint8, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = cu.sample(logits, b, 6, mask=mask, mask_active=active, status=status).cpu().tolist()
+    assert out[0] == 77 and out[5] == 100
+    lg = logits.cpu()
+    for r in range(1, 5):
+        assert out[r] == sample_row_host(lg[r], b._np_samp[r], None), r
+    assert int(status[0]) == 0
+    # NaN row fails closed
+    logits[1, 5] = float("nan")
+    out = cu.sample(logits, b, 6, status=status).cpu().tolist()
+    assert out[1] == -1 and int(status[0]) == 4
+
+
+def test_e2e_tiny_model_matches_oracle_tokens():
+    from phaseshift_b200.models.qwen35.reference import reference_forward
+    from phaseshift_b200.runtime.engine import Engine
+    cfg = tiny_config()
+    hf = random_hf_weights(cfg, seed=0)
+    prompt = torch.randint(0, cfg.vocab_size, (32,), generator=torch.Generator().manual_seed(0)).tolist()
+    ew = build_engine_weights(cfg, lambda n: hf[n], "bf16", "cuda")
+    for kvd in ("bf16", "fp8_e4m3"):
+        eng = Engine(ew, "cuda", StateConfig(max_slots=1, max_seq_len=128, page_tokens=16, kv_dtype=kvd))
+        out = eng.generate(prompt, 24, prefill_chunk=16)
+        # teacher-forced check: each generated token must be (near-)argmax of the fp32 oracle
+        logits = reference_forward(cfg, hf, prompt + out[:-1])[len(prompt) - 1:]
+        top = logits.max(-1).values
+        chosen = logits[torch.arange(len(out)), torch.tensor(out)]
+        assert float((top - chosen).max()) < (0.05 if kvd == "bf16" else 0.15), (kvd, (top - chosen).max())
+        # graph replay and eager must agree exactly
+        eng2 = Engine(ew, "cuda", StateConfig(max_slots=1, max_seq_len=128, page_tokens=16, kv_dtype=kvd), use_graphs=False)
+        assert eng2.generate(prompt, 24, prefill_chunk=16) == out
