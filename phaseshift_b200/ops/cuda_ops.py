@@ -88,8 +88,13 @@ class CudaOps:
                                      out_f32=out_f32, out=out)
         pro = PRO_RMSNORM if norm_w is not None else PRO_NONE
         epi = EPI_SWIGLU if swiglu else (EPI_RESIDUAL if residual is not None else EPI_STORE)
-        for m0 in range(0, M, SMALL_M_MAX):
-            m = min(SMALL_M_MAX, M - m0)
+        fn = _lib.lib().ps_linear_small_max_rows
+        fn.restype = ctypes.c_int
+        mmax = fn(c_int(WFMT[W.fmt]), c_int(W.q.k_padded))
+        if mmax < 1:
+            raise ValueError(f"K={W.K} is too large for the small-M linear kernel")
+        for m0 in range(0, M, mmax):
+            m = min(mmax, M - m0)
             xs = x[m0:m0 + m]
             os_ = out[m0:m0 + m]
             rs = residual[m0:m0 + m] if residual is not None else None

@@ -99,7 +99,7 @@ def test_attention_prefill_then_decode(kv_dtype, geom):
         cfg = Qwen35Config(vocab_size=1024, hidden_size=512, intermediate_size=512, num_hidden_layers=4,
                            num_attention_heads=12, num_key_value_heads=2, head_dim=256)
     cu, ref = _ops(cfg, 512)
-    sc = StateConfig(max_slots=2, max_seq_len=512, page_tokens=16, kv_dtype=kv_dtype)
+    sc = StateConfig(max_slots=2, max_seq_len=512, page_tokens=16, kv_dtype=kv_dtype, kv_capacity_tokens=2048)
     st_c = ModelState(cfg, sc, _dev(), torch.bfloat16)
     st_r = ModelState(cfg, sc, _dev(), torch.float32)
     nb = st_c.max_blocks
