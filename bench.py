@@ -128,7 +128,7 @@ def main():
     formats.DEFAULT_SEARCH = args.quant_search
     with torch.no_grad():
         ew = build_engine_weights(cfg, random_getter(cfg, seed=0, device=dev), args.preset, dev,
-                                  tp_rank=rank, tp_size=world)
+                                  tp_rank=rank, tp_size=world, keep_canonical=False)
     torch.cuda.synchronize()
     build_s = time.time() - t0
     K, W = args.steps, args.warmup

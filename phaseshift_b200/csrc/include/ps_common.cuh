@@ -6,6 +6,8 @@
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
+#include <utility>
 
 #define PS_API extern "C" __attribute__((visibility("default")))
 
@@ -92,6 +94,25 @@ __device__ __forceinline__ uint8_t f32_to_e4m3(float v) {
 
 __device__ __forceinline__ void set_status(uint32_t* status, uint32_t code) {
     if (status != nullptr) atomicCAS(status, 0u, code);
+}
+
+// Launch with programmatic dependent launch allowed: the kernel may be scheduled while its stream
+// predecessor is still draining; it must call cudaGridDependencySynchronize() before touching anything
+// the predecessor wrote.  PS_PDL=0 in the environment turns the attribute off.
+inline bool pdl_enabled() {
+    static int v = -1;
+    if (v < 0) { const char* e = getenv("PS_PDL"); v = (e == nullptr || e[0] != '0') ? 1 : 0; }
+    return v != 0;
+}
+template <typename... KArgs, typename... Args>
+inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
 }  // namespace ps

@@ -33,6 +33,8 @@ struct AttnPrepArgs {
 __global__ void attn_prep_kernel(const AttnPrepArgs a) {
     __shared__ float red[32];
     __shared__ float vals[512];
+    cudaTriggerProgrammaticLaunchCompletion();
+    cudaGridDependencySynchronize();
     const int row = blockIdx.y, hh = blockIdx.x, t = threadIdx.x, D = a.D;
     const int q_span = 2 * a.Hq * D;
     const __nv_bfloat16* src;
@@ -112,6 +114,5 @@ PS_API int ps_attn_prep(const void* qkv, int ld_qkv, int rows, int Hq, int Hkv, 
     a.v_scale = (float*)v_scale; a.block_table = (const int*)block_table; a.max_blocks = max_blocks;
     a.page_tokens = page_tokens; a.num_pages = num_pages; a.kv_fp8 = kv_fp8; a.status = (uint32_t*)status;
     dim3 grid(Hq + 2 * Hkv, rows);
-    attn_prep_kernel<<<grid, D / 2, 0, stream>>>(a);
-    return PS_LAUNCH_CHECK();
+    return launch_pdl(attn_prep_kernel, grid, dim3(D / 2), 0, stream, a);
 }

@@ -36,6 +36,9 @@ struct GdnArgs {
     const GdnSeqDesc* seqs;
     __nv_bfloat16* out;                         // [rows, Hv*Dv]
     float* log_k; float* log_delta; float* log_d;   // optional: [rows, Hv, Dk], [rows, Hv, Dv], [rows, Hv]
+    // optional in-kernel beta/decay projections: b = xn . ba_w[h], a = xn . ba_w[Hv + h] (bf16 weights);
+    // when null the kernel reads b and a from `proj`
+    const __nv_bfloat16* ba_w; const __nv_bfloat16* xn; int ba_k;
 };
 
 template <int DK, int DV>
@@ -57,8 +60,10 @@ __global__ void __launch_bounds__(256) gdn_rows_kernel(const GdnArgs a) {
     const int z_off = 2 * a.Hk * DK + a.Hv * DV + h * DV;
     const int b_off = 2 * a.Hk * DK + 2 * a.Hv * DV + h, a_off = b_off + a.Hv;
 
+    cudaTriggerProgrammaticLaunchCompletion();
     float S[R][4];
     {
+        // the recurrent state was last written by an earlier step, not by the stream predecessor
         const float* sp = a.state_in + ((size_t)sd.slot * a.Hv + h) * DK * DV;
 #pragma unroll
         for (int r = 0; r < R; ++r) {
@@ -66,6 +71,7 @@ __global__ void __launch_bounds__(256) gdn_rows_kernel(const GdnArgs a) {
             S[r][0] = v.x; S[r][1] = v.y; S[r][2] = v.z; S[r][3] = v.w;
         }
     }
+    cudaGridDependencySynchronize();
     __nv_bfloat16* hist = a.conv_state + ((size_t)sd.slot * a.Hv + h) * a.ring * CH;
     const float neg_expA = -__expf(a.A_log[h]);
     const float dtb = a.dt_bias[h];
@@ -109,8 +115,26 @@ __global__ void __launch_bounds__(256) gdn_rows_kernel(const GdnArgs a) {
         kk = block_sum(kk, s_red);
         const float qn = rsqrtf(qq + 1e-6f) * rsqrtf((float)DK);
         const float kn = rsqrtf(kk + 1e-6f);
-        const float beta = sigmoid_f(bf16_to_f32(pr[b_off]));
-        const float gate = neg_expA * softplus_f(bf16_to_f32(pr[a_off]) + dtb);
+        float b_in, a_in;
+        if (a.ba_w != nullptr) {
+            const __nv_bfloat16* xr = a.xn + (size_t)row * a.ba_k;
+            const __nv_bfloat16* wb = a.ba_w + (size_t)h * a.ba_k;
+            const __nv_bfloat16* wa = a.ba_w + (size_t)(a.Hv + h) * a.ba_k;
+            float sb = 0.f, sa = 0.f;
+            for (int i = t * 2; i < a.ba_k; i += 512) {
+                const float2 xv = bf16x2_bits_to_f32x2(*reinterpret_cast<const uint32_t*>(xr + i));
+                const float2 bv = bf16x2_bits_to_f32x2(*reinterpret_cast<const uint32_t*>(wb + i));
+                const float2 av = bf16x2_bits_to_f32x2(*reinterpret_cast<const uint32_t*>(wa + i));
+                sb = fmaf(xv.x, bv.x, sb); sb = fmaf(xv.y, bv.y, sb);
+                sa = fmaf(xv.x, av.x, sa); sa = fmaf(xv.y, av.y, sa);
+            }
+            b_in = bf16_to_f32(f32_to_bf16(block_sum(sb, s_red)));
+            a_in = bf16_to_f32(f32_to_bf16(block_sum(sa, s_red)));
+        } else {
+            b_in = bf16_to_f32(pr[b_off]); a_in = bf16_to_f32(pr[a_off]);
+        }
+        const float beta = sigmoid_f(b_in);
+        const float gate = neg_expA * softplus_f(a_in + dtb);
         const float d = __expf(gate);
         // ---- kv = (d S)^T k
         float kreg[R], qreg[R];
@@ -215,7 +239,8 @@ __global__ void __launch_bounds__(256) gdn_replay_kernel(const GdnReplayArgs a) 
 PS_API int ps_gdn_rows(const void* proj, int ld_proj, int Hk, int Hv, int Dk, int Dv, const void* conv_w,
                        const void* A_log, const void* dt_bias, const void* norm_w, float eps, void* conv_state,
                        int ring, const void* state_in, void* state_out, const void* seqs, int n_seqs, void* out,
-                       void* log_k, void* log_delta, void* log_d, cudaStream_t stream) {
+                       void* log_k, void* log_delta, void* log_d, const void* ba_w, const void* xn, int ba_k,
+                       cudaStream_t stream) {
     using namespace ps;
     if (n_seqs <= 0 || Hk <= 0 || (Hv % Hk) || ring < 4) return (int)cudaErrorInvalidValue;
     GdnArgs a;
@@ -224,11 +249,12 @@ PS_API int ps_gdn_rows(const void* proj, int ld_proj, int Hk, int Hv, int Dk, in
     a.norm_w = (const __nv_bfloat16*)norm_w; a.eps = eps; a.conv_state = (__nv_bfloat16*)conv_state; a.ring = ring;
     a.state_in = (const float*)state_in; a.state_out = (float*)state_out; a.seqs = (const GdnSeqDesc*)seqs;
     a.out = (__nv_bfloat16*)out; a.log_k = (float*)log_k; a.log_delta = (float*)log_delta; a.log_d = (float*)log_d;
+    a.ba_w = (const __nv_bfloat16*)ba_w; a.xn = (const __nv_bfloat16*)xn; a.ba_k = ba_k;
+    if (ba_w != nullptr && (ba_k & 1)) return (int)cudaErrorInvalidValue;
     dim3 grid(Hv, n_seqs);
-    if (Dk == 128 && Dv == 128) gdn_rows_kernel<128, 128><<<grid, 256, 0, stream>>>(a);
-    else if (Dk == 64 && Dv == 64) gdn_rows_kernel<64, 64><<<grid, 256, 0, stream>>>(a);
-    else return (int)cudaErrorInvalidValue;
-    return PS_LAUNCH_CHECK();
+    if (Dk == 128 && Dv == 128) return launch_pdl(gdn_rows_kernel<128, 128>, grid, dim3(256), 0, stream, a);
+    if (Dk == 64 && Dv == 64) return launch_pdl(gdn_rows_kernel<64, 64>, grid, dim3(256), 0, stream, a);
+    return (int)cudaErrorInvalidValue;
 }
 
 PS_API int ps_gdn_replay(void* state, int Hv, int Dk, int Dv, const void* seqs, int n_seqs, const void* log_k,

@@ -5,30 +5,26 @@
 // projection (RMSNorm, sigmoid gate, residual add, SwiGLU) is folded into the prologue/epilogue so a
 // transformer layer needs no standalone elementwise launches.
 //
-// Work decomposition (persistent CTAs, <= 2 per SM):
-//   * output rows are taken in pairs; CTA c owns a contiguous range of pairs, processed in waves of
-//     at most kWavePairs pairs;
-//   * inside a wave the (pair, k-step) units are split into 8 contiguous, equal ranges, one per
-//     warp, so every warp streams the same number of bytes whatever N and K are (a 48-row projection
-//     and a 152k-row lm_head both keep all warps busy);
-//   * each lane keeps kPrefetch 16-byte weight loads in flight at all times: a register ring is
-//     refilled with the unit kPrefetch ahead right after a slot is consumed, across pair and wave
-//     boundaries, and the first ring fill is issued before the activations are even staged;
-//   * a warp's partial sums for a pair go to shared memory and are combined in warp order.
-// The assignment of units to warps and the combination order are functions of (N, K, gridDim) only,
-// never of M, so a row computed in an M=1 launch and the same row inside an M=8 launch are
-// bit-identical: the property the reference obtains with its ExactRows GEMM
-// (src/phaseshift/models/qwen35/kernels/optimized/linear/bf16.hip:429-512) and that greedy
-// speculative verification relies on.
+// Weight storage ("tiled" layout, produced once at load time from the canonical row-major payload;
+// the counterpart of the reference's mandatory native preshuffle,
+// docs/developer/psq_canonical_soa_payload.md:674-708): output rows are grouped in quads, K in
+// k-steps of 32 lanes x 16 bytes, and the bytes one warp consumes together are contiguous:
+//     block(quad q, step s) at byte offset (q * steps + s) * kBlockBytes
+//       [4 rows x 512 B of codes][4 rows x kScaleRow B of block scales]
+// so a unit is ONE contiguous bulk copy and consecutive units of a warp form one sequential stream
+// (DRAM sees long bursts instead of 512-byte fragments 10 KB apart).  N is padded to a multiple of 4
+// and K to a whole k-step with zeros.
+//   W_BF16  : 256 weights per row-step, no scales, 2048 B blocks
+//   W_NVFP4 : 1024 E2M1 weights per row-step (byte j = q[2j] | q[2j+1] << 4), 64 UE4M3 scales per
+//             row-step (one per 16 weights), 2304 B blocks, plus one fp32 scale per tensor.
+//             Replaces PSQ4 (src/phaseshift/models/qwen35/kernels/optimized/linear/psq4.hip).
+//   W_MXFP8 : 512 E4M3 weights per row-step, 16 UE8M0 scales (one per 32), 2112 B blocks.  Replaces PSQ8.
 //
-// Weight formats (K contiguous, one row per output feature):
-//   W_BF16  : bf16 [N,K]
-//   W_NVFP4 : E2M1 nibbles [N,K/2] (byte j = q[2j] | q[2j+1] << 4), UE4M3 scale per 16 weights
-//             [N,K/16], one fp32 scale per tensor.  Replaces PSQ4 (src/.../linear/psq4.hip).
-//   W_MXFP8 : E4M3 bytes [N,K], UE8M0 scale per 32 weights [N,K/32].  Replaces PSQ8.
+// Arithmetic: the assignment of (quad, k-step) units to warps and the order in which partial sums
+// are combined are functions of (N, K, grid) only, never of M, so a row computed in an M=1 launch
+// and the same row inside an M=4 launch are bit-identical: the property the reference obtains with
+// its ExactRows GEMM (linear/bf16.hip:429-512) and that greedy speculative verification relies on.
 #pragma once
-
-#include <cuda_fp4.h>
 
 #include "ps_common.cuh"
 
@@ -40,9 +36,8 @@ enum LinearEpilogue : int { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2 };
 
 struct LinearSmallArgs {
     const __nv_bfloat16* x;   // [M, ldx]
-    int M, N, K, ldx;
-    const void* w;            // weight codes (format dependent)
-    const uint8_t* w_scale;   // block scales (NVFP4 / MXFP8) or nullptr
+    int M, N, K, ldx;         // K = logical reduction length (multiple of 32)
+    const uint8_t* w;         // tiled weight blocks
     float w_gscale;           // per-tensor scale (NVFP4), 1 otherwise
     int prologue;
     const __nv_bfloat16* norm_w;  // [K] for PRO_RMSNORM_ONEPLUS
@@ -55,18 +50,35 @@ struct LinearSmallArgs {
     void* out;                // [M, ldo] bf16 or f32 ; EPI_SWIGLU writes N/2 features
     int ldo;
     int out_f32;
+    __nv_bfloat16* xn_out;    // optional [M, K]: the prologue's output row(s), written by CTA 0
 };
 
-template <int WF> struct WTraits;
-template <> struct WTraits<W_BF16>  { static constexpr int kChunk = 8;  using XS = float; };
-template <> struct WTraits<W_NVFP4> { static constexpr int kChunk = 32; using XS = __half; };
-template <> struct WTraits<W_MXFP8> { static constexpr int kChunk = 16; using XS = __half; };
+constexpr int kQuadRows = 4;
 
-constexpr int kGemvThreads = 256;
-constexpr int kGemvWarps = kGemvThreads / 32;
-constexpr int kRowsPerUnit = 2;      // a unit = one k-step of a pair of output rows
-constexpr int kWavePairs = 32;
-constexpr int kPrefetch = 4;
+template <int WF> struct WTraits;
+template <> struct WTraits<W_BF16> {
+    static constexpr int kChunk = 8, kScaleRow = 0, kBlockBytes = 2048;
+    using XS = float;
+};
+template <> struct WTraits<W_NVFP4> {
+    static constexpr int kChunk = 32, kScaleRow = 64, kBlockBytes = 2048 + 4 * 64;
+    using XS = __half;
+};
+template <> struct WTraits<W_MXFP8> {
+    static constexpr int kChunk = 16, kScaleRow = 16, kBlockBytes = 2048 + 4 * 16;
+    using XS = __half;
+};
+
+template <int WF> __host__ __device__ constexpr int step_k() { return 32 * WTraits<WF>::kChunk; }
+template <int WF> __host__ __device__ inline int gemv_steps(int K) { return (K + step_k<WF>() - 1) / step_k<WF>(); }
+template <int WF> __host__ __device__ inline int gemv_kpad(int K) { return gemv_steps<WF>(K) * step_k<WF>(); }
+
+// CTA c of `grid` owns items [begin, end): an even split with the remainder spread over the first CTAs.
+__host__ __device__ inline void cta_range(int n_items, int grid, int c, int& begin, int& end) {
+    const int base = n_items / grid, rem = n_items % grid;
+    begin = c * base + (c < rem ? c : rem);
+    end = begin + base + (c < rem ? 1 : 0);
+}
 
 // Largest |x| the staged fp16 activations may take so that an 8-term half2 partial sum (|w| <= 6 for
 // NVFP4, <= 448 for MXFP8) cannot overflow fp16.
@@ -74,9 +86,13 @@ template <int WF> __device__ __forceinline__ float stage_target_absmax() {
     return WF == W_NVFP4 ? 512.f : (WF == W_MXFP8 ? 8.f : 0.f);
 }
 
-// Row statistics + staging of prologue(x) into shared memory (XS type), one pass over x per row:
-// sum of squares (RMSNorm) and max |x (1+w)| (fp16 range scaling; the sigmoid gate only shrinks |x|).
-template <int WF, int MT>
+// Row statistics + staging of prologue(x) into shared memory (XS type), zero-padded to kpad.
+// Pass 1 reads x from global once, parks the raw bf16 bits in the staging buffer and accumulates the
+// sum of squares (RMSNorm) and max |x (1+w)| (fp16 range scaling; the sigmoid gate only shrinks |x|);
+// pass 2 rewrites the buffer in place in its final form, so only one global round trip sits on the
+// kernel's critical path.  With `xn_out` set, CTA 0 also stores the normalised row (bf16) to global
+// for a consumer that needs it again (the GDN kernel's in-kernel b/a projections).
+template <int WF, int MT, int THREADS>
 __device__ __forceinline__ void stage_rows(const LinearSmallArgs& a, typename WTraits<WF>::XS* xs, int kpad,
                                            float* xscale_inv, float* red) {
     using XS = typename WTraits<WF>::XS;
@@ -85,10 +101,13 @@ __device__ __forceinline__ void stage_rows(const LinearSmallArgs& a, typename WT
     for (int m = 0; m < MT; ++m) {
         const bool live = m < a.M;
         const __nv_bfloat16* xr = a.x + (size_t)m * a.ldx;
+        XS* xrow = xs + (size_t)m * kpad;
         float ss = 0.f, amax = 0.f;
-        if (live && (norm || target > 0.f)) {
-            for (int k = threadIdx.x * 2; k < a.K; k += kGemvThreads * 2) {
-                float2 xv = bf16x2_bits_to_f32x2(*reinterpret_cast<const uint32_t*>(xr + k));
+        for (int k = threadIdx.x * 2; k < kpad; k += THREADS * 2) {
+            uint32_t bits = 0u;
+            if (live && k < a.K) {
+                bits = *reinterpret_cast<const uint32_t*>(xr + k);
+                float2 xv = bf16x2_bits_to_f32x2(bits);
                 ss += xv.x * xv.x + xv.y * xv.y;
                 if (norm) {
                     const float2 wv = bf16x2_bits_to_f32x2(*reinterpret_cast<const uint32_t*>(a.norm_w + k));
@@ -96,6 +115,10 @@ __device__ __forceinline__ void stage_rows(const LinearSmallArgs& a, typename WT
                 }
                 amax = fmaxf(amax, fmaxf(fabsf(xv.x), fabsf(xv.y)));
             }
+            if constexpr (sizeof(XS) == 4) xrow[k] = __uint_as_float(bits);            // raw bits parked in word k
+            else *reinterpret_cast<uint32_t*>(xrow + k) = bits;
+        }
+        if (norm || target > 0.f) {
             ss = block_sum(ss, red);
             amax = block_max(amax, red);
         }
@@ -109,11 +132,13 @@ __device__ __forceinline__ void stage_rows(const LinearSmallArgs& a, typename WT
             }
         }
         if (threadIdx.x == 0) xscale_inv[m] = 1.f / s;
-        for (int k = threadIdx.x * 2; k < kpad; k += kGemvThreads * 2) {
-            float v0 = 0.f, v1 = 0.f;
+        for (int k = threadIdx.x * 2; k < kpad; k += THREADS * 2) {
+            uint32_t bits;
+            if constexpr (sizeof(XS) == 4) bits = __float_as_uint(xrow[k]);
+            else bits = *reinterpret_cast<const uint32_t*>(xrow + k);
+            float2 xv = bf16x2_bits_to_f32x2(bits);
+            float v0 = xv.x, v1 = xv.y;
             if (live && k < a.K) {
-                const float2 xv = bf16x2_bits_to_f32x2(*reinterpret_cast<const uint32_t*>(xr + k));
-                v0 = xv.x; v1 = xv.y;
                 if (norm) {
                     const float2 wv = bf16x2_bits_to_f32x2(*reinterpret_cast<const uint32_t*>(a.norm_w + k));
                     // rounded to bf16 like a standalone norm kernel would store it
@@ -125,165 +150,182 @@ __device__ __forceinline__ void stage_rows(const LinearSmallArgs& a, typename WT
                     v0 = bf16_to_f32(f32_to_bf16(v0 * sigmoid_f(gv.x)));
                     v1 = bf16_to_f32(f32_to_bf16(v1 * sigmoid_f(gv.y)));
                 }
-                v0 *= s; v1 *= s;
+                if (a.xn_out != nullptr && blockIdx.x == 0)
+                    *reinterpret_cast<uint32_t*>(a.xn_out + (size_t)m * a.K + k) = f32x2_to_bf16x2_bits(v0, v1);
             }
-            if constexpr (sizeof(XS) == 4) *reinterpret_cast<float2*>(xs + (size_t)m * kpad + k) = make_float2(v0, v1);
-            else *reinterpret_cast<__half2*>(xs + (size_t)m * kpad + k) = __floats2half2_rn(v0, v1);
+            v0 *= s; v1 *= s;
+            if constexpr (sizeof(XS) == 4) *reinterpret_cast<float2*>(xrow + k) = make_float2(v0, v1);
+            else *reinterpret_cast<__half2*>(xrow + k) = __floats2half2_rn(v0, v1);
         }
     }
 }
 
-__device__ __forceinline__ __half2 e2m1x2_to_half2(uint32_t byte) {
-    __half2_raw r = __nv_cvt_fp4x2_to_halfraw2((__nv_fp4x2_storage_t)byte, __NV_E2M1);
-    return *reinterpret_cast<__half2*>(&r);
+// ---- packed conversions straight from 32-bit words (no per-byte shift/mask in front of the cvt)
+// 8 E2M1 nibbles -> 4 half2; nibble 2j is the low half of h[j].
+__device__ __forceinline__ void cvt_e2m1x8(uint32_t w, uint32_t (&h)[4]) {
+    asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+        "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t}"
+        : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3]) : "r"(w));
 }
-__device__ __forceinline__ __half2 e4m3x2_to_half2(uint32_t two_bytes) {
-    __half2_raw r = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)two_bytes, __NV_E4M3);
-    return *reinterpret_cast<__half2*>(&r);
+// 4 E4M3 bytes -> 2 half2; byte 2j is the low half of h[j].
+__device__ __forceinline__ void cvt_e4m3x4(uint32_t w, uint32_t (&h)[2]) {
+    asm("{\n\t.reg .b16 lo, hi;\n\t"
+        "mov.b32 {lo, hi}, %2;\n\t"
+        "cvt.rn.f16x2.e4m3x2 %0, lo;\n\t"
+        "cvt.rn.f16x2.e4m3x2 %1, hi;\n\t}"
+        : "=r"(h[0]), "=r"(h[1]) : "r"(w));
 }
+__device__ __forceinline__ __half2 as_half2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
+__device__ __forceinline__ float half2_hsum_f32(__half2 p) { return __half2float(__hadd(__low2half(p), __high2half(p))); }
 
-// One lane's share of a unit: kChunk consecutive weights of one output row against the staged
-// activations of every batch row.
-template <int WF, int MT> struct DotChunk;
+// One lane's share of one weight row inside a block: kChunk weights against one batch row's staged
+// activations (`xm` = this lane's activations for that k range, as 32-bit words, shared by the rows
+// of the quad).  Identical code serves the register-ring and the TMA-ring kernels.
+template <int WF> struct RowDot;
 
-template <int MT> struct DotChunk<W_BF16, MT> {
-    struct Frag { uint4 w; };
-    __device__ static __forceinline__ void load(Frag& f, const LinearSmallArgs& a, int n, int k) {
-        f.w = __ldcs(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.w) + (size_t)n * a.K + k));
+template <> struct RowDot<W_BF16> {
+    static constexpr int kXWords = 8;       // 8 fp32 activations
+    __device__ static __forceinline__ void load_x(const float* xs, uint32_t (&xm)[kXWords]) {
+        const uint4 a = *reinterpret_cast<const uint4*>(xs);
+        const uint4 b = *reinterpret_cast<const uint4*>(xs + 4);
+        xm[0] = a.x; xm[1] = a.y; xm[2] = a.z; xm[3] = a.w; xm[4] = b.x; xm[5] = b.y; xm[6] = b.z; xm[7] = b.w;
     }
-    __device__ static __forceinline__ void fma(const Frag& f, const float* xs, int kpad, int k, float* acc) {
-        const float2 w0 = bf16x2_bits_to_f32x2(f.w.x), w1 = bf16x2_bits_to_f32x2(f.w.y);
-        const float2 w2 = bf16x2_bits_to_f32x2(f.w.z), w3 = bf16x2_bits_to_f32x2(f.w.w);
+    __device__ static __forceinline__ float dot(uint4 w, uint32_t /*scale_bits*/, const uint32_t (&xm)[kXWords], float acc) {
+        const float2 w0 = bf16x2_bits_to_f32x2(w.x), w1 = bf16x2_bits_to_f32x2(w.y);
+        const float2 w2 = bf16x2_bits_to_f32x2(w.z), w3 = bf16x2_bits_to_f32x2(w.w);
+        float s = acc;
+        s = fmaf(w0.x, __uint_as_float(xm[0]), s); s = fmaf(w0.y, __uint_as_float(xm[1]), s);
+        s = fmaf(w1.x, __uint_as_float(xm[2]), s); s = fmaf(w1.y, __uint_as_float(xm[3]), s);
+        s = fmaf(w2.x, __uint_as_float(xm[4]), s); s = fmaf(w2.y, __uint_as_float(xm[5]), s);
+        s = fmaf(w3.x, __uint_as_float(xm[6]), s); s = fmaf(w3.y, __uint_as_float(xm[7]), s);
+        return s;
+    }
+    __device__ static __forceinline__ uint32_t load_scale(const uint8_t*, int, int) { return 0u; }
+};
+
+template <> struct RowDot<W_NVFP4> {
+    static constexpr int kXWords = 16;      // 32 fp16 activations
+    __device__ static __forceinline__ void load_x(const __half* xs, uint32_t (&xm)[kXWords]) {
+        const uint4* xp = reinterpret_cast<const uint4*>(xs);
 #pragma unroll
-        for (int m = 0; m < MT; ++m) {
-            const float4 xa = *reinterpret_cast<const float4*>(xs + (size_t)m * kpad + k);
-            const float4 xb = *reinterpret_cast<const float4*>(xs + (size_t)m * kpad + k + 4);
-            float s = acc[m];
-            s = fmaf(w0.x, xa.x, s); s = fmaf(w0.y, xa.y, s);
-            s = fmaf(w1.x, xa.z, s); s = fmaf(w1.y, xa.w, s);
-            s = fmaf(w2.x, xb.x, s); s = fmaf(w2.y, xb.y, s);
-            s = fmaf(w3.x, xb.z, s); s = fmaf(w3.y, xb.w, s);
-            acc[m] = s;
+        for (int q = 0; q < 4; ++q) {
+            const uint4 v = xp[q];
+            xm[q * 4] = v.x; xm[q * 4 + 1] = v.y; xm[q * 4 + 2] = v.z; xm[q * 4 + 3] = v.w;
         }
+    }
+    __device__ static __forceinline__ float dot(uint4 w, uint32_t scale_bits, const uint32_t (&xm)[kXWords], float acc) {
+        uint32_t sh[2];
+        cvt_e4m3x4(scale_bits, sh);                       // low 16 bits hold this lane's two UE4M3 scales
+        const float2 sc = __half22float2(as_half2(sh[0]));
+        const uint32_t wq[4] = {w.x, w.y, w.z, w.w};
+        float s = acc;
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+            uint32_t h0[4], h1[4];
+            cvt_e2m1x8(wq[2 * b], h0);
+            cvt_e2m1x8(wq[2 * b + 1], h1);
+            __half2 p = __hmul2(as_half2(h0[0]), as_half2(xm[b * 8 + 0]));
+            p = __hfma2(as_half2(h0[1]), as_half2(xm[b * 8 + 1]), p);
+            p = __hfma2(as_half2(h0[2]), as_half2(xm[b * 8 + 2]), p);
+            p = __hfma2(as_half2(h0[3]), as_half2(xm[b * 8 + 3]), p);
+            p = __hfma2(as_half2(h1[0]), as_half2(xm[b * 8 + 4]), p);
+            p = __hfma2(as_half2(h1[1]), as_half2(xm[b * 8 + 5]), p);
+            p = __hfma2(as_half2(h1[2]), as_half2(xm[b * 8 + 6]), p);
+            p = __hfma2(as_half2(h1[3]), as_half2(xm[b * 8 + 7]), p);
+            s = fmaf(half2_hsum_f32(p), b == 0 ? sc.x : sc.y, s);
+        }
+        return s;
+    }
+    __device__ static __forceinline__ uint32_t load_scale(const uint8_t* block, int r, int lane) {
+        return *reinterpret_cast<const uint16_t*>(block + 2048 + r * 64 + lane * 2);
     }
 };
 
-template <int MT> struct DotChunk<W_NVFP4, MT> {
-    struct Frag { uint4 w; uint32_t sc; };
-    __device__ static __forceinline__ void load(Frag& f, const LinearSmallArgs& a, int n, int k) {
-        f.w = __ldcs(reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(a.w) + (size_t)n * (a.K >> 1) + (k >> 1)));
-        f.sc = __ldcs(reinterpret_cast<const uint16_t*>(a.w_scale + (size_t)n * (a.K >> 4) + (k >> 4)));
+template <> struct RowDot<W_MXFP8> {
+    static constexpr int kXWords = 8;       // 16 fp16 activations
+    __device__ static __forceinline__ void load_x(const __half* xs, uint32_t (&xm)[kXWords]) {
+        const uint4* xp = reinterpret_cast<const uint4*>(xs);
+        const uint4 a = xp[0], b = xp[1];
+        xm[0] = a.x; xm[1] = a.y; xm[2] = a.z; xm[3] = a.w; xm[4] = b.x; xm[5] = b.y; xm[6] = b.z; xm[7] = b.w;
     }
-    __device__ static __forceinline__ void fma(const Frag& f, const __half* xs, int kpad, int k, float* acc) {
-        const float2 sc = __half22float2(e4m3x2_to_half2(f.sc));
-        const uint32_t wq[4] = {f.w.x, f.w.y, f.w.z, f.w.w};
-        __half2 wh[16];
+    __device__ static __forceinline__ float dot(uint4 w, uint32_t scale_bits, const uint32_t (&xm)[kXWords], float acc) {
+        const float sc = __uint_as_float(scale_bits << 23);   // UE8M0: 2^(e-127)
+        const uint32_t wq[4] = {w.x, w.y, w.z, w.w};
+        uint32_t h[2];
+        cvt_e4m3x4(wq[0], h);
+        __half2 p = __hmul2(as_half2(h[0]), as_half2(xm[0]));
+        p = __hfma2(as_half2(h[1]), as_half2(xm[1]), p);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) wh[j] = e2m1x2_to_half2((wq[j >> 2] >> ((j & 3) * 8)) & 0xffu);
+        for (int j = 1; j < 4; ++j) {
+            cvt_e4m3x4(wq[j], h);
+            p = __hfma2(as_half2(h[0]), as_half2(xm[2 * j]), p);
+            p = __hfma2(as_half2(h[1]), as_half2(xm[2 * j + 1]), p);
+        }
+        return fmaf(half2_hsum_f32(p), sc, acc);
+    }
+    __device__ static __forceinline__ uint32_t load_scale(const uint8_t* block, int r, int lane) {
+        return block[2048 + r * 16 + (lane >> 1)];
+    }
+};
+
+// Apply the epilogue for one quad (4 consecutive output rows) and one batch row.
+__device__ __forceinline__ void quad_epilogue(const LinearSmallArgs& a, int n0, int m, const float (&v)[kQuadRows]) {
+    if (a.epilogue == EPI_SWIGLU) {
+        // rows (2j, 2j+1) hold (gate_j, up_j); both rounded to bf16 as separate projections would be
 #pragma unroll
-        for (int m = 0; m < MT; ++m) {
-            const uint4* xp = reinterpret_cast<const uint4*>(xs + (size_t)m * kpad + k);
-            float s = acc[m];
-#pragma unroll
-            for (int b = 0; b < 2; ++b) {
-                const uint4 x0 = xp[b * 2], x1 = xp[b * 2 + 1];
-                const uint32_t xr[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-                __half2 p = __floats2half2_rn(0.f, 0.f);
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    p = __hfma2(wh[b * 8 + j], *reinterpret_cast<const __half2*>(&xr[j]), p);
-                const float2 pf = __half22float2(p);
-                s = fmaf(pf.x + pf.y, b == 0 ? sc.x : sc.y, s);
+        for (int h = 0; h < kQuadRows / 2; ++h) {
+            if (n0 + 2 * h + 1 < a.N) {
+                const float g = bf16_to_f32(f32_to_bf16(v[2 * h])), up = bf16_to_f32(f32_to_bf16(v[2 * h + 1]));
+                const float y = silu_f(g) * up;
+                const int j = (n0 >> 1) + h;
+                if (a.out_f32) reinterpret_cast<float*>(a.out)[(size_t)m * a.ldo + j] = y;
+                else reinterpret_cast<__nv_bfloat16*>(a.out)[(size_t)m * a.ldo + j] = f32_to_bf16(y);
             }
-            acc[m] = s;
         }
+        return;
     }
-};
-
-template <int MT> struct DotChunk<W_MXFP8, MT> {
-    struct Frag { uint4 w; uint32_t sc; };
-    __device__ static __forceinline__ void load(Frag& f, const LinearSmallArgs& a, int n, int k) {
-        f.w = __ldcs(reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(a.w) + (size_t)n * a.K + k));
-        f.sc = __ldcs(a.w_scale + (size_t)n * (a.K >> 5) + (k >> 5));
+#pragma unroll
+    for (int r = 0; r < kQuadRows; ++r) {
+        const int n = n0 + r;
+        if (n >= a.N) continue;
+        float y = v[r];
+        if (a.epilogue == EPI_RESIDUAL)   // y rounded to bf16 before the add, like projection-then-add
+            y = bf16_to_f32(f32_to_bf16(y)) + bf16_to_f32(a.residual[(size_t)m * a.ld_res + n]);
+        if (a.out_f32) reinterpret_cast<float*>(a.out)[(size_t)m * a.ldo + n] = y;
+        else reinterpret_cast<__nv_bfloat16*>(a.out)[(size_t)m * a.ldo + n] = f32_to_bf16(y);
     }
-    __device__ static __forceinline__ void fma(const Frag& f, const __half* xs, int kpad, int k, float* acc) {
-        const float sc = __uint_as_float(f.sc << 23);   // UE8M0: 2^(e-127)
-        const uint32_t wq[4] = {f.w.x, f.w.y, f.w.z, f.w.w};
-        __half2 wh[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) wh[j] = e4m3x2_to_half2((wq[j >> 1] >> ((j & 1) * 16)) & 0xffffu);
-#pragma unroll
-        for (int m = 0; m < MT; ++m) {
-            const uint4* xp = reinterpret_cast<const uint4*>(xs + (size_t)m * kpad + k);
-            const uint4 x0 = xp[0], x1 = xp[1];
-            const uint32_t xr[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-            __half2 p = __floats2half2_rn(0.f, 0.f);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) p = __hfma2(wh[j], *reinterpret_cast<const __half2*>(&xr[j]), p);
-            const float2 pf = __half22float2(p);
-            acc[m] = fmaf(pf.x + pf.y, sc, acc[m]);
-        }
-    }
-};
-
-// Geometry shared by host and device: which pairs a CTA owns.
-struct GemvGeom {
-    int n_pairs, steps, kpad;
-    __host__ __device__ static int steps_for(int K, int chunk) { return (K + 32 * chunk - 1) / (32 * chunk); }
-};
-__host__ __device__ inline int gemv_grid(int N, int max_ctas) {
-    const int n_pairs = (N + kRowsPerUnit - 1) / kRowsPerUnit;
-    return n_pairs < max_ctas ? n_pairs : max_ctas;
-}
-template <int WF>
-__host__ __device__ inline int gemv_kpad(int K) {
-    constexpr int unit = 32 * WTraits<WF>::kChunk;
-    return (K + unit - 1) / unit * unit;
 }
 
-// Walks one warp's unit stream in "padded" positions: the CTA's pairs are processed in waves of at
-// most kWavePairs pairs; inside a wave the (pair, k-step) units are cut into kGemvWarps contiguous
-// slices, and every slice is padded with null units to a multiple of kPrefetch so that stream
-// position q always lives in ring slot q % kPrefetch (static register indexing).
-struct UnitWalker {
-    int pair_end, steps, warp;
-    int wave_pair0, wave_pairs;   // current wave (wave_pairs <= 0: stream exhausted)
-    int u0, u_end, q, q_end;      // slice [u0, u_end) of the wave, padded position q in [0, q_end)
-    __device__ __forceinline__ void set_wave(int p0) {
-        wave_pair0 = p0;
-        wave_pairs = min(kWavePairs, pair_end - p0);
-        q = 0;
-        if (wave_pairs <= 0) { u0 = u_end = q_end = 0; return; }
-        const int total = wave_pairs * steps;
-        u0 = (total * warp) / kGemvWarps;
-        u_end = (total * (warp + 1)) / kGemvWarps;
-        q_end = (u_end - u0 + kPrefetch - 1) / kPrefetch * kPrefetch;
+// One warp's (quad, k-step) unit stream: the CTA's quads are processed in waves of at most
+// `wave_max` quads; inside a wave the units are cut into `n_warps` contiguous slices.
+struct QuadWalker {
+    int quad_end, steps, warp, n_warps, wave_max;
+    int wave_q0, wave_quads, u, u_end, q, st;     // current unit = (q, st)
+    __device__ __forceinline__ void set_wave(int q0) {
+        wave_q0 = q0;
+        wave_quads = min(wave_max, quad_end - q0);
+        if (wave_quads <= 0) { u = u_end = 0; return; }
+        const int total = wave_quads * steps;
+        u = (total * warp) / n_warps;
+        u_end = (total * (warp + 1)) / n_warps;
+        q = wave_q0 + u / steps; st = u % steps;
     }
-    __device__ __forceinline__ void init(int pair_begin, int pair_end_, int steps_, int warp_) {
-        pair_end = pair_end_; steps = steps_; warp = warp_;
-        set_wave(pair_begin);
-        while (wave_pairs > 0 && q >= q_end) set_wave(wave_pair0 + kWavePairs);
+    __device__ __forceinline__ void init(int qb, int qe, int steps_, int warp_, int n_warps_, int wave_max_) {
+        quad_end = qe; steps = steps_; warp = warp_; n_warps = n_warps_; wave_max = wave_max_;
+        set_wave(qb);
+        while (wave_quads > 0 && u >= u_end) set_wave(wave_q0 + wave_max);
     }
-    __device__ __forceinline__ bool exhausted() const { return wave_pairs <= 0; }
-    // true when the current padded position is a real unit; then (pair, step) identify it
-    __device__ __forceinline__ bool unit(int& pair, int& step) const {
-        const int u = u0 + q;
-        if (wave_pairs <= 0 || u >= u_end) return false;
-        pair = wave_pair0 + u / steps; step = u % steps;
-        return true;
-    }
+    __device__ __forceinline__ bool valid() const { return wave_quads > 0; }
     __device__ __forceinline__ void next() {
-        if (wave_pairs <= 0) return;
-        ++q;
-        while (wave_pairs > 0 && q >= q_end) set_wave(wave_pair0 + kWavePairs);
+        if (wave_quads <= 0) return;
+        ++u;
+        if (++st == steps) { st = 0; ++q; }
+        while (wave_quads > 0 && u >= u_end) set_wave(wave_q0 + wave_max);
     }
 };
-
-// CTA c of `grid` owns pairs [begin, end): an even split with the remainder spread over the first CTAs.
-__host__ __device__ inline void gemv_cta_pairs(int n_pairs, int grid, int c, int& begin, int& end) {
-    const int base = n_pairs / grid, rem = n_pairs % grid;
-    begin = c * base + (c < rem ? c : rem);
-    end = begin + base + (c < rem ? 1 : 0);
-}
 
 }  // namespace ps

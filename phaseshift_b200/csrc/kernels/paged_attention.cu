@@ -116,6 +116,8 @@ __global__ void __launch_bounds__(kAttnThreads) paged_attn_split_kernel(const Pa
     float* kscale = alpha + kAttnMaxG;                                     // [32]
     float* vscale = kscale + kAttnTile;                                    // [32]
 
+    cudaTriggerProgrammaticLaunchCompletion();
+    cudaGridDependencySynchronize();
     const int split = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
     const int visible = a.row_pos[row] + 1;
     const int tok_begin = split * a.split_tokens;
@@ -206,6 +208,8 @@ struct AttnMergeArgs {
 
 // grid = (Hq, rows), block = D threads.  Splits are merged in ascending order (fixed order => exact).
 __global__ void paged_attn_merge_kernel(const AttnMergeArgs a) {
+    cudaTriggerProgrammaticLaunchCompletion();
+    cudaGridDependencySynchronize();
     const int h = blockIdx.x, row = blockIdx.y, d = threadIdx.x;
     const int visible = a.row_pos[row] + 1;
     const int n = (visible + a.split_tokens - 1) / a.split_tokens;
@@ -258,14 +262,12 @@ PS_API int ps_paged_attention(const void* q, const void* k_pool, const void* v_p
         attr_set = true;
     }
     dim3 grid(n_splits, Hkv, rows);
-    paged_attn_split_kernel<<<grid, kAttnThreads, smem, stream>>>(a);
-    int err = PS_LAUNCH_CHECK();
+    int err = launch_pdl(paged_attn_split_kernel, grid, dim3(kAttnThreads), smem, stream, a);
     if (err) return err;
     AttnMergeArgs m;
     m.part_acc = a.part_acc; m.part_ml = a.part_ml; m.row_pos = a.row_pos; m.rows = rows; m.Hq = Hq; m.D = D;
     m.split_tokens = split_tokens; m.max_splits = max_splits; m.gate = (const __nv_bfloat16*)gate;
     m.ld_gate = ld_gate; m.gate_head_stride = gate_head_stride; m.gate_offset = gate_offset;
     m.out = (__nv_bfloat16*)out;
-    paged_attn_merge_kernel<<<dim3(Hq, rows), D, 0, stream>>>(m);
-    return PS_LAUNCH_CHECK();
+    return launch_pdl(paged_attn_merge_kernel, dim3(Hq, rows), dim3(D), 0, stream, m);
 }

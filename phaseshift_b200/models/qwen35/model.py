@@ -18,6 +18,9 @@ from .config import Qwen35Config
 from .weights import EngineWeights
 
 
+FUSED_BA_MAX_ROWS = 8
+
+
 class StepOutput:
     __slots__ = ("tokens", "logits", "hidden", "taps")
 
@@ -49,15 +52,25 @@ class Qwen35Runner:
             m = L.mixer
             if L.kind == 0:
                 n_main = m.in_proj.N
-                proj = ops.buf("gdn_proj", rows, n_main + m.ba_proj.N) if hasattr(ops, "buf") else None
-                if proj is not None:
-                    ops.linear(x, m.in_proj, name="gdn_in", norm_w=L.input_norm, eps=eps, out=proj[:, :n_main])
-                    ops.linear(x, m.ba_proj, name="gdn_ba", norm_w=L.input_norm, eps=eps, out=proj[:, n_main:])
+                if hasattr(ops, "buf"):
+                    proj = ops.buf("gdn_proj", rows, n_main + m.ba_proj.N)
+                    if rows <= FUSED_BA_MAX_ROWS:
+                        # decode / verify: the GDN kernel projects beta/decay inputs itself from the
+                        # normalised row that in_proj leaves behind -> one launch fewer per layer
+                        xn = ops.buf("gdn_xn", rows, x.shape[1])
+                        ops.linear(x, m.in_proj, name="gdn_in", norm_w=L.input_norm, eps=eps, out=proj[:, :n_main],
+                                   xn_out=xn)
+                    else:
+                        xn = None
+                        ops.linear(x, m.in_proj, name="gdn_in", norm_w=L.input_norm, eps=eps, out=proj[:, :n_main])
+                        ops.linear(x, m.ba_proj, name="gdn_ba", norm_w=L.input_norm, eps=eps, out=proj[:, n_main:])
+                    o = ops.gdn(proj, m, self.hk, self.hv, b, st.gdn[li], st,
+                                log=None if gdn_log is None else gdn_log[li], to_alt=gdn_to_alt, xn=xn)
                 else:
                     proj = torch.cat([ops.linear(x, m.in_proj, name="gdn_in", norm_w=L.input_norm, eps=eps),
                                       ops.linear(x, m.ba_proj, name="gdn_ba", norm_w=L.input_norm, eps=eps)], 1)
-                o = ops.gdn(proj, m, self.hk, self.hv, b, st.gdn[li], st,
-                            log=None if gdn_log is None else gdn_log[li], to_alt=gdn_to_alt)
+                    o = ops.gdn(proj, m, self.hk, self.hv, b, st.gdn[li], st,
+                                log=None if gdn_log is None else gdn_log[li], to_alt=gdn_to_alt)
                 if tp_on:
                     r = self._reduce(ops.linear(o, m.out_proj, name="mix_out"), x, "r")
                 else:

@@ -97,25 +97,64 @@ def random_getter(cfg: Qwen35Config, seed: int = 0, device="cpu") -> Callable[[s
 
 @dataclass
 class LinearW:
+    """One projection.  ``q`` is the canonical row-major payload (what files store, what the CPU ops and
+    dequantisation use); ``tiled`` is the kernel-side layout built from it on a CUDA device
+    (quant/tiling.py).  ``drop_canonical()`` frees ``q``'s device tensors once ``tiled`` exists."""
     q: QuantizedTensor
     _deq: Optional[torch.Tensor] = None
+    tiled: Optional[torch.Tensor] = None
+    _shape: Optional[tuple] = None
+    _kpad: int = 0
+    _fmt: str = ""
+    _tscale: float = 1.0
+
+    def __post_init__(self):
+        self._shape, self._kpad, self._fmt, self._tscale = self.q.shape, self.q.k_padded, self.q.fmt, self.q.tensor_scale
+
+    def make_tiled(self, keep_canonical: bool = True) -> "LinearW":
+        from ...quant.tiling import tile_weight
+        if self.tiled is None:
+            self.tiled = tile_weight(self.q)
+        if not keep_canonical:
+            self.q = None
+        return self
 
     @property
     def N(self) -> int:
-        return self.q.shape[0]
+        return self._shape[0]
 
     @property
     def K(self) -> int:
-        return self.q.shape[1]
+        return self._shape[1]
+
+    @property
+    def k_padded(self) -> int:
+        return self._kpad
 
     @property
     def fmt(self) -> str:
-        return self.q.fmt
+        return self._fmt
+
+    @property
+    def tensor_scale(self) -> float:
+        return self._tscale
+
+    @property
+    def nbytes(self) -> int:
+        if self.tiled is not None:
+            return self.tiled.numel()
+        return self.q.nbytes
 
     def dense(self) -> torch.Tensor:
         """fp32 [N, K] (dequantised); cached, used by the CPU/reference ops."""
         if self._deq is None:
-            self._deq = dequantize(self.q)
+            q = self.q
+            if q is None:
+                from ...quant.tiling import untile_weight
+                q = untile_weight(self.tiled, self._fmt, self._shape[0], self._kpad)
+                q.tensor_scale = self._tscale
+                q.shape = self._shape
+            self._deq = dequantize(q)
         return self._deq
 
 
@@ -160,19 +199,19 @@ class EngineWeights:
     preset: str = "bf16"
 
     def weight_bytes(self) -> int:
-        n = self.embed.q.nbytes + self.lm_head.q.nbytes
+        n = self.embed.nbytes + self.lm_head.nbytes
         for l in self.layers:
-            n += l.gate_up.q.nbytes + l.down.q.nbytes
+            n += l.gate_up.nbytes + l.down.nbytes
             m = l.mixer
             if l.kind == 0:
-                n += m.in_proj.q.nbytes + m.ba_proj.q.nbytes + m.out_proj.q.nbytes
+                n += m.in_proj.nbytes + m.ba_proj.nbytes + m.out_proj.nbytes
             else:
-                n += m.qkv_proj.q.nbytes + m.o_proj.q.nbytes
+                n += m.qkv_proj.nbytes + m.o_proj.nbytes
         return n
 
     def decode_read_bytes(self) -> int:
         """Weight bytes one decode step must stream from HBM (everything except the embedding table)."""
-        return self.weight_bytes() - self.embed.q.nbytes
+        return self.weight_bytes() - self.embed.nbytes
 
 
 # role -> format.  "nvfp4" mirrors the reference's `psq` preset with NVFP4 for PSQ4 and MXFP8 for PSQ8
@@ -235,8 +274,7 @@ def _rows(t: torch.Tensor, heads: range, dim: int) -> torch.Tensor:
 def build_engine_weights(cfg: Qwen35Config, get: Callable[[str], torch.Tensor], preset: str = "bf16",
                          device="cpu", tp_rank: int = 0, tp_size: int = 1,
                          importance: Optional[Callable[[str], Optional[torch.Tensor]]] = None,
-                         get_quantized: Optional[Callable[[str], Optional[QuantizedTensor]]] = None
-                         ) -> EngineWeights:
+                         keep_canonical: bool = True) -> EngineWeights:
     """``get(name)`` returns the full HF tensor; slicing, fusing and quantisation happen here, one layer
     at a time so a 27B model never needs more than one layer of BF16 weights resident."""
     geo = TpGeometry.make(cfg, tp_rank, tp_size)
@@ -246,7 +284,10 @@ def build_engine_weights(cfg: Qwen35Config, get: Callable[[str], torch.Tensor], 
     def lin(w: torch.Tensor, role: str, layer: int, name: str = "") -> LinearW:
         fmt = format_for(preset, role, layer)
         imp = importance(name) if (importance is not None and name) else None
-        return LinearW(quantize(w.to(device), fmt, imp))
+        lw = LinearW(quantize(w.to(device), fmt, imp))
+        if torch.device(device).type == "cuda" and role != "embed":
+            lw.make_tiled(keep_canonical or role == "gdn_small")   # the GDN kernel reads b/a rows row-major
+        return lw
 
     def dev(t: torch.Tensor, dtype=torch.bfloat16) -> torch.Tensor:
         return t.to(device=device, dtype=dtype).contiguous()
@@ -291,7 +332,9 @@ def build_engine_weights(cfg: Qwen35Config, get: Callable[[str], torch.Tensor], 
     embed_w = get(P + "embed_tokens.weight")
     embed = lin(embed_w, "embed", 0)
     if cfg.tie_word_embeddings:
-        lm_head = embed
+        lm_head = LinearW(embed.q)
+        if torch.device(device).type == "cuda":
+            lm_head.make_tiled(True)
     else:
         lm_head = lin(get(P + "lm_head.weight"), "lm_head", 0, P + "lm_head.weight")
     return EngineWeights(cfg, embed, layers, dev(get(P + "norm.weight")), lm_head, tp_rank, tp_size, preset)

@@ -49,6 +49,7 @@ class CudaOps:
         self.max_splits = attn_max_splits or -(-(max_seq_len + 1) // self.split_tokens)
         self.launches = 0
         self.use_tc_gemm = True
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)   # kernels' own bounded-wait status word
 
     # ------------------------------------------------------------------ workspace
     def buf(self, name: str, rows: int, cols: int, dtype=torch.bfloat16) -> torch.Tensor:
@@ -76,7 +77,8 @@ class CudaOps:
 
     def linear(self, x: torch.Tensor, W: LinearW, *, name: str, norm_w: Optional[torch.Tensor] = None,
                eps: float = 0.0, residual: Optional[torch.Tensor] = None, swiglu: bool = False,
-               out_f32: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+               out_f32: bool = False, out: Optional[torch.Tensor] = None,
+               xn_out: Optional[torch.Tensor] = None) -> torch.Tensor:
         M, K = x.shape
         assert K == W.K and x.dtype == torch.bfloat16 and x.stride(1) == 1, (x.shape, W.K, x.dtype)
         n_out = W.N // 2 if swiglu else W.N
@@ -88,21 +90,22 @@ class CudaOps:
                                      out_f32=out_f32, out=out)
         pro = PRO_RMSNORM if norm_w is not None else PRO_NONE
         epi = EPI_SWIGLU if swiglu else (EPI_RESIDUAL if residual is not None else EPI_STORE)
-        fn = _lib.lib().ps_linear_small_max_rows
-        fn.restype = ctypes.c_int
-        mmax = fn(c_int(WFMT[W.fmt]), c_int(W.q.k_padded))
+        if W.tiled is None:
+            W.make_tiled()
+        L = _lib.lib()
+        L.ps_linear_stream_max_rows.restype = ctypes.c_int
+        mmax = L.ps_linear_stream_max_rows(c_int(WFMT[W.fmt]), c_int(W.k_padded))
         if mmax < 1:
-            raise ValueError(f"K={W.K} is too large for the small-M linear kernel")
+            raise ValueError(f"K={W.K} is too large for the streaming small-M linear kernel")
         for m0 in range(0, M, mmax):
             m = min(mmax, M - m0)
-            xs = x[m0:m0 + m]
-            os_ = out[m0:m0 + m]
             rs = residual[m0:m0 + m] if residual is not None else None
-            _lib.call("ps_linear_small", c_int(WFMT[W.fmt]), ptr(xs), c_int(m), c_int(W.N), c_int(W.q.k_padded),
-                      c_int(x.stride(0)), ptr(W.q.codes), ptr(W.q.scales), c_float(W.q.tensor_scale), c_int(pro),
+            _lib.call("ps_linear_stream", c_int(WFMT[W.fmt]), ptr(x[m0:m0 + m]), c_int(m), c_int(W.N),
+                      c_int(W.k_padded), c_int(x.stride(0)), ptr(W.tiled), c_float(W.tensor_scale), c_int(pro),
                       ptr(norm_w), c_float(eps), ptr(None), c_int(0), c_int(epi), ptr(rs),
-                      c_int(residual.stride(0) if residual is not None else 0), ptr(os_), c_int(out.stride(0)),
-                      c_int(1 if out_f32 else 0))
+                      c_int(residual.stride(0) if residual is not None else 0), ptr(out[m0:m0 + m]),
+                      c_int(out.stride(0)), c_int(1 if out_f32 else 0),
+                      ptr(xn_out[m0:m0 + m] if xn_out is not None else None), ptr(self.status))
             self.launches += 1
         return out
 
@@ -136,7 +139,9 @@ class CudaOps:
         return out
 
     def gdn(self, proj: torch.Tensor, gw: GdnW, hk: int, hv: int, b: StepBatch, gs: GdnLayerState,
-            st: ModelState, log=None, to_alt: bool = False) -> torch.Tensor:
+            st: ModelState, log=None, to_alt: bool = False, xn: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``xn`` given: the kernel projects beta/decay inputs itself from the normalised rows (bf16
+        ``ba_proj`` weights); otherwise they are read from the last 2*hv columns of ``proj``."""
         cfg = self.cfg
         rows = proj.shape[0]
         Dk, Dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
@@ -148,7 +153,8 @@ class CudaOps:
         _lib.call("ps_gdn_rows", ptr(proj), c_int(proj.stride(0)), c_int(hk), c_int(hv), c_int(Dk), c_int(Dv),
                   ptr(gw.conv_w), ptr(gw.A_log), ptr(gw.dt_bias), ptr(gw.norm_w), c_float(cfg.rms_norm_eps),
                   ptr(gs.conv), c_int(st.sc.conv_ring), ptr(gs.rec), ptr(state_out), ptr(b.seq_desc),
-                  c_int(b.max_seqs if b.graph_static else b.n_seqs), ptr(out), ptr(lk), ptr(ld), ptr(ldd))
+                  c_int(b.max_seqs if b.graph_static else b.n_seqs), ptr(out), ptr(lk), ptr(ld), ptr(ldd),
+                  ptr(gw.ba_proj.q.codes if xn is not None else None), ptr(xn), c_int(gw.ba_proj.K))
         self.launches += 1
         return out
 

@@ -268,3 +268,36 @@ def test_e2e_tiny_model_matches_oracle_tokens():
         # graph replay and eager must agree exactly
         eng2 = Engine(ew, "cuda", StateConfig(max_slots=1, max_seq_len=128, page_tokens=16, kv_dtype=kvd), use_graphs=False)
         assert eng2.generate(prompt, 24, prefill_chunk=16) == out
+
+
+@pytest.mark.parametrize("fmt", ["bf16", "nvfp4", "mxfp8"])
+def test_stream_gemv_shapes_and_row_invariance(fmt):
+    """Odd N / K tails, K larger than one staging pass allows for M=8, and row invariance across M."""
+    cfg = tiny_config()
+    cu, _ = _ops(cfg)
+    g = torch.Generator(device="cuda").manual_seed(21)
+    for (N, K) in [(1030, 5120), (510, 17408), (98, 2560), (7, 96)]:
+        w = torch.randn(N, K, device="cuda", generator=g) * 0.02
+        x = torch.randn(8, K, device="cuda", generator=g).to(torch.bfloat16)
+        nw = (torch.randn(K, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+        W = LinearW(quantize(w, fmt))
+        y8 = cu.linear(x, W, name="s8", norm_w=nw, eps=1e-6, out_f32=True).clone()
+        y1 = cu.linear(x[5:6], W, name="s1", norm_w=nw, eps=1e-6, out_f32=True).clone()
+        assert torch.equal(y1[0], y8[5])
+        ref = (x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-6) * (1 + nw.float())) @ W.dense().T
+        assert _rel_err(y8, ref) < 1e-2
+        assert int(cu.status[0]) == 0
+
+
+@pytest.mark.parametrize("fmt", ["bf16", "nvfp4", "mxfp8"])
+def test_tiled_layout_roundtrip(fmt):
+    from phaseshift_b200.quant.tiling import tile_weight, untile_weight, tiled_nbytes
+    g = torch.Generator(device="cuda").manual_seed(3)
+    for (N, K) in [(10, 96), (33, 2560), (8, 1024)]:
+        q = quantize(torch.randn(N, K, device="cuda", generator=g), fmt)
+        t = tile_weight(q)
+        assert t.numel() == tiled_nbytes(fmt, N, q.k_padded)
+        u = untile_weight(t, fmt, N, q.k_padded)
+        assert torch.equal(u.codes.view(torch.uint8), q.codes.view(torch.uint8))
+        if q.scales is not None:
+            assert torch.equal(u.scales, q.scales)
