@@ -65,6 +65,32 @@ __device__ __forceinline__ float block_max(float v, float* red) {
     return r;
 }
 
+// Fused block reduction of N sums (and optionally one max) with two barriers in total.
+// `red` needs 32 * (N + 1) floats.  Every thread receives all results.
+template <int N>
+__device__ __forceinline__ void block_sum_n(float (&v)[N], float* red) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+#pragma unroll
+    for (int i = 0; i < N; ++i) v[i] = warp_sum(v[i]);
+    __syncthreads();
+    if (lane == 0) {
+#pragma unroll
+        for (int i = 0; i < N; ++i) red[i * 32 + w] = v[i];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < N; ++i) v[i] = warp_sum(lane < nw ? red[i * 32 + lane] : 0.f);
+}
+__device__ __forceinline__ void block_sum_max(float& s, float& m, float* red) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    s = warp_sum(s); m = warp_max(m);
+    __syncthreads();
+    if (lane == 0) { red[w] = s; red[32 + w] = m; }
+    __syncthreads();
+    s = warp_sum(lane < nw ? red[lane] : 0.f);
+    m = warp_max(lane < nw ? red[32 + lane] : -3.4e38f);
+}
+
 __device__ __forceinline__ float bf16_to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
 __device__ __forceinline__ __nv_bfloat16 f32_to_bf16(float v) { return __float2bfloat16_rn(v); }
 

@@ -47,7 +47,7 @@ __global__ void __launch_bounds__(256) gdn_rows_kernel(const GdnArgs a) {
     constexpr int RG = 256 / CG;        // row groups
     constexpr int R = DK / RG;          // rows per thread
     constexpr int CH = 2 * DK + DV;     // conv channels owned by this head
-    __shared__ float s_q[DK], s_k[DK], s_v[DV], s_red[32];
+    __shared__ float s_q[DK], s_k[DK], s_v[DV], s_red[32], s_red4[160];
     __shared__ float s_part[RG][DV];
     __shared__ float s_vec[DV];
 
@@ -108,28 +108,27 @@ __global__ void __launch_bounds__(256) gdn_rows_kernel(const GdnArgs a) {
             const int gc = c < DK ? q_off + c : (c < 2 * DK ? k_off + (c - DK) : v_off + (c - 2 * DK));
             hist[(size_t)(pos % a.ring) * CH + c] = pr[gc];
         }
-        // ---- L2 norms
-        float qq = 0.f, kk = 0.f;
-        for (int i = t; i < DK; i += 256) { qq += s_q[i] * s_q[i]; kk += s_k[i] * s_k[i]; }
-        qq = block_sum(qq, s_red);
-        kk = block_sum(kk, s_red);
-        const float qn = rsqrtf(qq + 1e-6f) * rsqrtf((float)DK);
-        const float kn = rsqrtf(kk + 1e-6f);
-        float b_in, a_in;
+        // ---- L2 norms and (optionally) the beta / decay input projections: one fused block reduction
+        float red4[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int i = t; i < DK; i += 256) { red4[0] += s_q[i] * s_q[i]; red4[1] += s_k[i] * s_k[i]; }
         if (a.ba_w != nullptr) {
             const __nv_bfloat16* xr = a.xn + (size_t)row * a.ba_k;
             const __nv_bfloat16* wb = a.ba_w + (size_t)h * a.ba_k;
             const __nv_bfloat16* wa = a.ba_w + (size_t)(a.Hv + h) * a.ba_k;
-            float sb = 0.f, sa = 0.f;
             for (int i = t * 2; i < a.ba_k; i += 512) {
                 const float2 xv = bf16x2_bits_to_f32x2(*reinterpret_cast<const uint32_t*>(xr + i));
-                const float2 bv = bf16x2_bits_to_f32x2(*reinterpret_cast<const uint32_t*>(wb + i));
-                const float2 av = bf16x2_bits_to_f32x2(*reinterpret_cast<const uint32_t*>(wa + i));
-                sb = fmaf(xv.x, bv.x, sb); sb = fmaf(xv.y, bv.y, sb);
-                sa = fmaf(xv.x, av.x, sa); sa = fmaf(xv.y, av.y, sa);
+                const float2 bv = bf16x2_bits_to_f32x2(__ldg(reinterpret_cast<const uint32_t*>(wb + i)));
+                const float2 av = bf16x2_bits_to_f32x2(__ldg(reinterpret_cast<const uint32_t*>(wa + i)));
+                red4[2] = fmaf(xv.x, bv.x, red4[2]); red4[2] = fmaf(xv.y, bv.y, red4[2]);
+                red4[3] = fmaf(xv.x, av.x, red4[3]); red4[3] = fmaf(xv.y, av.y, red4[3]);
             }
-            b_in = bf16_to_f32(f32_to_bf16(block_sum(sb, s_red)));
-            a_in = bf16_to_f32(f32_to_bf16(block_sum(sa, s_red)));
+        }
+        block_sum_n<4>(red4, s_red4);
+        const float qn = rsqrtf(red4[0] + 1e-6f) * rsqrtf((float)DK);
+        const float kn = rsqrtf(red4[1] + 1e-6f);
+        float b_in, a_in;
+        if (a.ba_w != nullptr) {
+            b_in = bf16_to_f32(f32_to_bf16(red4[2])); a_in = bf16_to_f32(f32_to_bf16(red4[3]));
         } else {
             b_in = bf16_to_f32(pr[b_off]); a_in = bf16_to_f32(pr[a_off]);
         }

@@ -118,10 +118,7 @@ __device__ __forceinline__ void stage_rows(const LinearSmallArgs& a, typename WT
             if constexpr (sizeof(XS) == 4) xrow[k] = __uint_as_float(bits);            // raw bits parked in word k
             else *reinterpret_cast<uint32_t*>(xrow + k) = bits;
         }
-        if (norm || target > 0.f) {
-            ss = block_sum(ss, red);
-            amax = block_max(amax, red);
-        }
+        if (norm || target > 0.f) block_sum_max(ss, amax, red);
         const float ir = norm ? rsqrtf(ss / (float)a.K + a.eps) : 1.f;
         float s = 1.f;
         if (target > 0.f) {

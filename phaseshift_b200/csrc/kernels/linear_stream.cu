@@ -42,7 +42,7 @@ __global__ void __launch_bounds__(kStThreads, 1) linear_stream_kernel(const Line
     XS* xs = reinterpret_cast<XS*>(smem_raw + (size_t)kStWarps * n_slots * kSlot);
     float* partial = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(xs) + (size_t)kpad * MT * sizeof(XS));
     __shared__ __align__(8) uint64_t s_bar[kStWarps][kStMaxSlots];
-    __shared__ float s_xscale_inv[MT], s_red[32];
+    __shared__ float s_xscale_inv[MT], s_red[64];
 
     // Programmatic dependent launch: the next kernel in the stream may start (and prefetch its own
     // weights) while this one runs; it blocks in cudaGridDependencySynchronize() until this grid is done.
@@ -74,9 +74,9 @@ __global__ void __launch_bounds__(kStThreads, 1) linear_stream_kernel(const Line
         }
     }
 
+    for (int i = threadIdx.x; i < kStWaveQuads * kStWarps * R * MT; i += kStThreads) partial[i] = 0.f;
     cudaGridDependencySynchronize();
     stage_rows<WF, MT, kStThreads>(a, xs, kpad, s_xscale_inv, s_red);
-    for (int i = threadIdx.x; i < kStWaveQuads * kStWarps * R * MT; i += kStThreads) partial[i] = 0.f;
     __syncthreads();
 
     int consumed = 0;

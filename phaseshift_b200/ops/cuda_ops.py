@@ -49,6 +49,7 @@ class CudaOps:
         self.max_splits = attn_max_splits or -(-(max_seq_len + 1) // self.split_tokens)
         self.launches = 0
         self.use_tc_gemm = True
+        self.wscratch = None
         self.status = torch.zeros(1, dtype=torch.int32, device=device)   # kernels' own bounded-wait status word
 
     # ------------------------------------------------------------------ workspace
@@ -85,7 +86,7 @@ class CudaOps:
         if out is None:
             out = self.buf(name, M, n_out, torch.float32 if out_f32 else torch.bfloat16)
         assert out.shape[0] == M and out.shape[1] == n_out and out.stride(1) == 1
-        if M > SMALL_M_MAX and self.use_tc_gemm and W.fmt == "bf16" and hasattr(self, "linear_large"):
+        if M > SMALL_M_MAX and self.use_tc_gemm:
             return self.linear_large(x, W, name=name, norm_w=norm_w, eps=eps, residual=residual, swiglu=swiglu,
                                      out_f32=out_f32, out=out)
         pro = PRO_RMSNORM if norm_w is not None else PRO_NONE
@@ -107,6 +108,27 @@ class CudaOps:
                       c_int(out.stride(0)), c_int(1 if out_f32 else 0),
                       ptr(xn_out[m0:m0 + m] if xn_out is not None else None), ptr(self.status))
             self.launches += 1
+        return out
+
+    def linear_large(self, x: torch.Tensor, W: LinearW, *, name: str, norm_w, eps, residual, swiglu, out_f32, out):
+        """Prefill-sized projection: (RMSNorm kernel) -> weight expansion to a bf16 scratch matrix -> tcgen05
+        GEMM with the residual / SwiGLU / dtype epilogue fused."""
+        M, K = x.shape
+        a = x if norm_w is None else self.rmsnorm(x, norm_w, eps, "gemm_norm_in")
+        if W.tiled is None:
+            W.make_tiled()
+        kp = W.k_padded
+        need = W.N * kp
+        if self.wscratch is None or self.wscratch.numel() < need:
+            self.wscratch = torch.empty(need, dtype=torch.bfloat16, device=self.device)
+        wd = self.wscratch[:need].view(W.N, kp)
+        _lib.call("ps_dequant_tiled", c_int(WFMT[W.fmt]), ptr(W.tiled), c_int(W.N), c_int(kp),
+                  c_float(W.tensor_scale), ptr(wd), c_int(kp))
+        epi = EPI_SWIGLU if swiglu else (EPI_RESIDUAL if residual is not None else EPI_STORE)
+        _lib.call("ps_gemm_bf16_tc", ptr(a), c_int(a.stride(0)), ptr(wd), c_int(kp), c_int(M), c_int(W.N), c_int(kp),
+                  c_int(epi), ptr(residual), c_int(residual.stride(0) if residual is not None else 0), ptr(out),
+                  c_int(out.stride(0)), c_int(1 if out_f32 else 0), ptr(self.status))
+        self.launches += 2
         return out
 
     def attn_prep(self, qkv: torch.Tensor, aw: AttnW, hq: int, hkv: int, b: StepBatch, kv: KVLayer,

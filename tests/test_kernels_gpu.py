@@ -41,7 +41,9 @@ def test_linear_small_plain(fmt, M, shape):
     y = cu.linear(x, W, name="t", out_f32=True)
     y_ref = x.float() @ W.dense().T
     torch.cuda.synchronize()
-    assert _rel_err(y, y_ref) < (2e-3 if fmt != "bf16" else 1e-5), _rel_err(y, y_ref)
+    # M > 8 goes through the tensor-core path whose weights are rounded to bf16 once
+    tol = (2e-3 if fmt != "bf16" else 1e-5) if M <= 8 else 8e-3
+    assert _rel_err(y, y_ref) < tol, _rel_err(y, y_ref)
 
 
 @pytest.mark.parametrize("fmt", ["bf16", "nvfp4"])
@@ -301,3 +303,37 @@ def test_tiled_layout_roundtrip(fmt):
         assert torch.equal(u.codes.view(torch.uint8), q.codes.view(torch.uint8))
         if q.scales is not None:
             assert torch.equal(u.scales, q.scales)
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 64), (200, 384, 512), (2048, 5120, 5120), (77, 96, 2560), (1024, 1000, 17408)])
+def test_tcgen05_gemm_matches_matmul(shape):
+    M, N, K = shape
+    cfg = tiny_config()
+    cu, _ = _ops(cfg)
+    g = torch.Generator(device="cuda").manual_seed(M + N)
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    W = LinearW(quantize(w.float(), "bf16"))
+    y = cu.linear(x, W, name="g", out_f32=True)
+    ref = x.float() @ w.float().T
+    torch.cuda.synchronize()
+    assert int(cu.status[0]) == 0
+    assert _rel_err(y, ref) < 2e-3, _rel_err(y, ref)
+
+
+@pytest.mark.parametrize("fmt", ["nvfp4", "mxfp8"])
+def test_large_m_linear_fused_epilogues(fmt):
+    cfg = tiny_config()
+    cu, ref = _ops(cfg)
+    g = torch.Generator(device="cuda").manual_seed(31)
+    M, K, N = 300, 2560, 1536
+    w = torch.randn(N, K, device="cuda", generator=g) * 0.03
+    x = (torch.randn(M, K, device="cuda", generator=g) * 2).to(torch.bfloat16)
+    nw = (torch.randn(K, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    res = torch.randn(M, N, device="cuda", generator=g).to(torch.bfloat16)
+    W = LinearW(quantize(w, fmt))
+    y = cu.linear(x, W, name="a", norm_w=nw, eps=1e-6, residual=res)
+    assert _rel_err(y, ref.linear(x, W, name="a", norm_w=nw, eps=1e-6, residual=res)) < 1e-2
+    y = cu.linear(x, W, name="b", norm_w=nw, eps=1e-6, swiglu=True)
+    assert _rel_err(y, ref.linear(x, W, name="b", norm_w=nw, eps=1e-6, swiglu=True)) < 2e-2
+    assert int(cu.status[0]) == 0
