@@ -36,6 +36,8 @@ def _parse():
     ap.add_argument("--kv-dtype", default="bf16", choices=["bf16", "fp8_e4m3"])
     ap.add_argument("--prefill-chunk", type=int, default=2048)
     ap.add_argument("--quant-search", type=int, default=1)
+    ap.add_argument("--watchdog", type=int, default=1500,
+                    help="seconds after which a hung run dumps every thread's stack to stderr and exits")
     return ap.parse_args()
 
 
@@ -93,6 +95,9 @@ def main():
     if args.impl == "reference":
         return reference_arm(args)
 
+    import faulthandler
+    if args.watchdog > 0:
+        faulthandler.dump_traceback_later(args.watchdog, exit=True)
     import torch
     import torch.distributed as dist
 

@@ -34,6 +34,23 @@ enum WeightFormat : int { W_BF16 = 0, W_NVFP4 = 1, W_MXFP8 = 2 };
 enum LinearPrologue : int { PRO_NONE = 0, PRO_RMSNORM_ONEPLUS = 1, PRO_SIGMOID_GATE = 2 };
 enum LinearEpilogue : int { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2 };
 
+constexpr int kTpMaxRanks = 8;
+// Tensor-parallel combine fused into a row-parallel projection's epilogue (one-shot all-reduce over
+// NVLink peer memory).  Every rank runs the same kernel with the same grid, so CTA c owns the same
+// output rows everywhere: it pushes its fp32 partial sums into every rank's receive buffer with plain
+// peer stores, raises a per-(CTA, source rank) flag with a system-scope release, waits (bounded) for
+// the same CTA of every peer, then adds the partials in rank order 0..size-1 -- the identical order on
+// every rank, so all ranks hold bit-identical results -- plus the residual.
+// The reference combines with a separate leader-reduce + broadcast per projection and a host
+// rendezvous (src/phaseshift/runtime/tp/hip_peer_tp_transport.hip:314-369, tp_barrier_group.cpp:74-119).
+struct TpCombine {
+    int size, rank;                       // size <= 1: disabled
+    float* recv[kTpMaxRanks];             // rank r's receive buffer: [2 parities][size][max_rows][n_pad] f32
+    uint32_t* flags[kTpMaxRanks];         // rank r's flags: [grid][size]
+    uint32_t* counter;                    // local, [grid]: collectives this CTA has taken part in
+    int max_rows, n_pad;
+};
+
 struct LinearSmallArgs {
     const __nv_bfloat16* x;   // [M, ldx]
     int M, N, K, ldx;         // K = logical reduction length (multiple of 32)
@@ -51,6 +68,7 @@ struct LinearSmallArgs {
     int ldo;
     int out_f32;
     __nv_bfloat16* xn_out;    // optional [M, K]: the prologue's output row(s), written by CTA 0
+    TpCombine tp;
 };
 
 constexpr int kQuadRows = 4;

@@ -135,21 +135,82 @@ __global__ void __launch_bounds__(kStThreads, 1) linear_stream_kernel(const Line
         if (dirty) flush();
         __syncthreads();
         // ---- combine the warps' partial sums in warp order, apply the epilogue
-        for (int i = threadIdx.x; i < wave_quads * MT; i += kStThreads) {
-            const int ql = i / MT, m = i % MT;
-            float v[R];
+        if (a.tp.size <= 1) {
+            for (int i = threadIdx.x; i < wave_quads * MT; i += kStThreads) {
+                const int ql = i / MT, m = i % MT;
+                float v[R];
 #pragma unroll
-            for (int r = 0; r < R; ++r) {
-                float s = 0.f;
+                for (int r = 0; r < R; ++r) {
+                    float s = 0.f;
 #pragma unroll
-                for (int w2 = 0; w2 < kStWarps; ++w2) {
-                    float* pp = &partial[(ql * kStWarps + w2) * (R * MT) + r * MT + m];
-                    s += *pp;
-                    *pp = 0.f;
+                    for (int w2 = 0; w2 < kStWarps; ++w2) {
+                        float* pp = &partial[(ql * kStWarps + w2) * (R * MT) + r * MT + m];
+                        s += *pp;
+                        *pp = 0.f;
+                    }
+                    v[r] = s * (a.w_gscale * s_xscale_inv[m]);
                 }
-                v[r] = s * (a.w_gscale * s_xscale_inv[m]);
+                if (m < a.M) quad_epilogue(a, (wave_q0 + ql) * R, m, v);
             }
-            if (m < a.M) quad_epilogue(a, (wave_q0 + ql) * R, m, v);
+        } else {
+            // ---- tensor-parallel combine (see TpCombine)
+            const TpCombine& tp = a.tp;
+            __shared__ uint32_t s_val;
+            if (threadIdx.x == 0) s_val = tp.counter[blockIdx.x] + 1u;
+            __syncthreads();
+            const uint32_t val = s_val;
+            const size_t par_off = (size_t)(val & 1u) * tp.size * tp.max_rows * tp.n_pad;
+            // 1. push this CTA's partial rows into every rank's receive buffer (slot = my rank)
+            for (int i = threadIdx.x; i < wave_quads * MT; i += kStThreads) {
+                const int ql = i / MT, m = i % MT;
+                float v[R];
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    float s = 0.f;
+#pragma unroll
+                    for (int w2 = 0; w2 < kStWarps; ++w2) {
+                        float* pp = &partial[(ql * kStWarps + w2) * (R * MT) + r * MT + m];
+                        s += *pp;
+                        *pp = 0.f;
+                    }
+                    v[r] = s * (a.w_gscale * s_xscale_inv[m]);
+                }
+                if (m < a.M) {
+                    const size_t off = par_off + ((size_t)tp.rank * tp.max_rows + m) * tp.n_pad + (size_t)(wave_q0 + ql) * R;
+                    const float4 pk = make_float4(v[0], v[1], v[2], v[3]);
+                    for (int pr = 0; pr < tp.size; ++pr) *reinterpret_cast<float4*>(tp.recv[pr] + off) = pk;
+                }
+            }
+            __syncthreads();
+            // 2. publish: one system-scope release per peer, then 3. wait for the same CTA of every peer
+            if (threadIdx.x < tp.size) {
+                __threadfence_system();
+                uint32_t* f = tp.flags[threadIdx.x] + (size_t)blockIdx.x * tp.size + tp.rank;
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(val) : "memory");
+                const uint32_t* mine = tp.flags[tp.rank] + (size_t)blockIdx.x * tp.size + threadIdx.x;
+                const long long t0 = clock64();
+                uint32_t seen;
+                do {
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+                    if ((int32_t)(seen - val) >= 0) break;
+                    if (clock64() - t0 > tc::kWaitBudgetCycles) { timed_out = true; break; }
+                } while (true);
+            }
+            __syncthreads();
+            if (threadIdx.x == 0) tp.counter[blockIdx.x] = val;
+            // 4. add the partials in rank order (identical on every rank), then the residual epilogue
+            const float* rbuf = tp.recv[tp.rank] + par_off;
+            for (int i = threadIdx.x; i < wave_quads * MT; i += kStThreads) {
+                const int ql = i / MT, m = i % MT;
+                if (m >= a.M) continue;
+                const int n0 = (wave_q0 + ql) * R;
+                float v[R] = {0.f, 0.f, 0.f, 0.f};
+                for (int pr = 0; pr < tp.size; ++pr) {
+                    const float4 pk = __ldcv(reinterpret_cast<const float4*>(rbuf + ((size_t)pr * tp.max_rows + m) * tp.n_pad + n0));
+                    v[0] += pk.x; v[1] += pk.y; v[2] += pk.z; v[3] += pk.w;
+                }
+                quad_epilogue(a, n0, m, v);
+            }
         }
         if (__syncthreads_or(timed_out ? 1 : 0)) break;
     }
@@ -214,7 +275,7 @@ static void stream_init_once() {
 PS_API int ps_linear_stream(int wfmt, const void* x, int M, int N, int K, int ldx, const void* w_tiled,
                             float w_gscale, int prologue, const void* norm_w, float eps, const void* gate,
                             int ld_gate, int epilogue, const void* residual, int ld_res, void* out, int ldo,
-                            int out_f32, void* xn_out, void* status, cudaStream_t stream) {
+                            int out_f32, void* xn_out, const void* tp_combine, void* status, cudaStream_t stream) {
     using namespace ps;
     stream_init_once();
     if (M < 1 || M > 8 || (K % 32) != 0 || (ldx % 8) != 0 || ((uintptr_t)w_tiled % 16) != 0)
@@ -227,6 +288,13 @@ PS_API int ps_linear_stream(int wfmt, const void* x, int M, int N, int K, int ld
     a.gate = (const __nv_bfloat16*)gate; a.ld_gate = ld_gate;
     a.epilogue = epilogue; a.residual = (const __nv_bfloat16*)residual; a.ld_res = ld_res;
     a.out = out; a.ldo = ldo; a.out_f32 = out_f32; a.xn_out = (__nv_bfloat16*)xn_out;
+    if (tp_combine != nullptr) {
+        a.tp = *reinterpret_cast<const TpCombine*>(tp_combine);
+        if (a.tp.size > kTpMaxRanks || M > a.tp.max_rows || ((N + 3) / 4 * 4) > a.tp.n_pad || epilogue == EPI_SWIGLU)
+            return (int)cudaErrorInvalidValue;
+    } else {
+        a.tp.size = 0;
+    }
     switch (wfmt) {
         case W_BF16: return stream_dispatch_m<W_BF16>(a, (uint32_t*)status, stream);
         case W_NVFP4: return stream_dispatch_m<W_NVFP4>(a, (uint32_t*)status, stream);

@@ -36,16 +36,26 @@ class Qwen35Runner:
         self.hq, self.hkv = len(geo.q_heads), len(geo.kv_heads)
         self.hk, self.hv = len(geo.gdn_k_heads), len(geo.gdn_v_heads)
 
-    def _reduce(self, partial: torch.Tensor, residual: torch.Tensor, name: str) -> torch.Tensor:
-        """Row-parallel combine under TP: sum partial projections over ranks, then add the residual."""
-        return self.tp.all_reduce_residual(partial, residual, name)
+    def _row_parallel(self, inp: torch.Tensor, W, residual: torch.Tensor, name: str, rows: int) -> torch.Tensor:
+        """Row-parallel projection + residual.  Single rank: residual fused in the projection epilogue.
+        Tensor parallel, <= 8 rows: the projection kernel also performs the cross-rank sum (fused
+        one-shot all-reduce over NVLink); otherwise the partial goes through the library all-reduce."""
+        ops, tp = self.ops, self.tp
+        if tp is None or tp.size <= 1:
+            return ops.linear(inp, W, name=name, residual=residual)
+        comb = tp.combine_for(W.N) if (rows <= 8 and hasattr(ops, "buf")) else None
+        if comb is not None:
+            tp.stats["fused"] += 1
+            return ops.linear(inp, W, name=name, residual=residual, tp_combine=comb)
+        part = ops.linear(inp, W, name="tp_partial")
+        out = ops.buf(name, rows, W.N) if hasattr(ops, "buf") else torch.empty_like(part)
+        return tp.all_reduce_residual(part, residual, out)
 
     def forward(self, b: StepBatch, rows: int, n_out: int, *, tap_layers: Sequence[int] = (),
                 gdn_log: Optional[Dict[int, tuple]] = None, gdn_to_alt: bool = False,
                 mask=None, mask_active=None, sample: bool = True) -> StepOutput:
         cfg, ops, st, w = self.cfg, self.ops, self.state, self.w
         eps = cfg.rms_norm_eps
-        tp_on = self.tp is not None and self.tp.size > 1
         x = ops.embed(b, rows, w.embed, st.status)
         taps = {}
         for li, L in enumerate(w.layers):
@@ -71,25 +81,16 @@ class Qwen35Runner:
                                       ops.linear(x, m.ba_proj, name="gdn_ba", norm_w=L.input_norm, eps=eps)], 1)
                     o = ops.gdn(proj, m, self.hk, self.hv, b, st.gdn[li], st,
                                 log=None if gdn_log is None else gdn_log[li], to_alt=gdn_to_alt)
-                if tp_on:
-                    r = self._reduce(ops.linear(o, m.out_proj, name="mix_out"), x, "r")
-                else:
-                    r = ops.linear(o, m.out_proj, name="r", residual=x)
+                r = self._row_parallel(o, m.out_proj, x, "r", rows)
             else:
                 qkv = ops.linear(x, m.qkv_proj, name="attn_qkv", norm_w=L.input_norm, eps=eps)
                 q = ops.attn_prep(qkv, m, self.hq, self.hkv, b, st.kv[li], st)
                 ctx = ops.paged_attention(q, qkv, self.hq, self.hkv, b, st.kv[li], st, b.max_visible_launch)
-                if tp_on:
-                    r = self._reduce(ops.linear(ctx, m.o_proj, name="mix_out"), x, "r")
-                else:
-                    r = ops.linear(ctx, m.o_proj, name="r", residual=x)
+                r = self._row_parallel(ctx, m.o_proj, x, "r", rows)
             act = ops.linear(r, L.gate_up, name="mlp_act", norm_w=L.post_norm, eps=eps, swiglu=True)
             # ping-pong the residual stream so a layer never writes the buffer it still reads
             xname = "x_a" if (li & 1) == 0 else "x_b"
-            if tp_on:
-                x = self._reduce(ops.linear(act, L.down, name="mlp_out"), r, xname)
-            else:
-                x = ops.linear(act, L.down, name=xname, residual=r)
+            x = self._row_parallel(act, L.down, r, xname, rows)
             if li in tap_layers:
                 taps[li] = x if not hasattr(ops, "buf") else ops.buf(f"tap{li}", rows, x.shape[1]).copy_(x)
         tokens = logits = hidden = None

@@ -79,13 +79,17 @@ class CudaOps:
     def linear(self, x: torch.Tensor, W: LinearW, *, name: str, norm_w: Optional[torch.Tensor] = None,
                eps: float = 0.0, residual: Optional[torch.Tensor] = None, swiglu: bool = False,
                out_f32: bool = False, out: Optional[torch.Tensor] = None,
-               xn_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+               xn_out: Optional[torch.Tensor] = None, tp_combine=None) -> torch.Tensor:
+        """``tp_combine`` (a parallel.tp.TpCombineStruct): the projection is row-parallel and the kernel sums
+        the ranks' partial results over NVLink before the residual epilogue (rows <= 8 only)."""
         M, K = x.shape
         assert K == W.K and x.dtype == torch.bfloat16 and x.stride(1) == 1, (x.shape, W.K, x.dtype)
         n_out = W.N // 2 if swiglu else W.N
         if out is None:
             out = self.buf(name, M, n_out, torch.float32 if out_f32 else torch.bfloat16)
         assert out.shape[0] == M and out.shape[1] == n_out and out.stride(1) == 1
+        if tp_combine is not None and M > SMALL_M_MAX:
+            raise ValueError("the fused tensor-parallel combine handles at most 8 rows")
         if M > SMALL_M_MAX and self.use_tc_gemm:
             return self.linear_large(x, W, name=name, norm_w=norm_w, eps=eps, residual=residual, swiglu=swiglu,
                                      out_f32=out_f32, out=out)
@@ -106,7 +110,8 @@ class CudaOps:
                       ptr(norm_w), c_float(eps), ptr(None), c_int(0), c_int(epi), ptr(rs),
                       c_int(residual.stride(0) if residual is not None else 0), ptr(out[m0:m0 + m]),
                       c_int(out.stride(0)), c_int(1 if out_f32 else 0),
-                      ptr(xn_out[m0:m0 + m] if xn_out is not None else None), ptr(self.status))
+                      ptr(xn_out[m0:m0 + m] if xn_out is not None else None),
+                      ctypes.byref(tp_combine) if tp_combine is not None else ptr(None), ptr(self.status))
             self.launches += 1
         return out
 

@@ -91,6 +91,9 @@ class Engine:
         self.graph_out: Dict[int, StepOutput] = {}
         self.launches_per_graph: Dict[int, int] = {}
         self.use_graphs = use_graphs and backend == "cuda"
+        if tp is not None and tp.size > 1 and tp.transport != "fused":
+            # the library all-reduce is not captured into CUDA graphs; only the in-kernel combine is
+            self.use_graphs = False
         self.h_tokens = torch.zeros(2048, dtype=torch.int32, pin_memory=(self.device.type == "cuda"))
         self.h_status = torch.zeros(1, dtype=torch.int32, pin_memory=(self.device.type == "cuda"))
         self.steps = 0

@@ -1,0 +1,44 @@
+"""Tensor parallel on real GPUs (needs >= 2): the fused in-kernel combine against the NCCL transport and
+against the single-GPU engine.  Ranks run as torchrun children with a hard timeout."""
+import json
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _run(world, preset, transport, tmp_path, n_new=12):
+    out = tmp_path / f"tp_{world}_{preset}_{transport}.json"
+    env = dict(os.environ, PS_TP_TRANSPORT=transport, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
+           os.path.join(HERE, "tp_worker.py"), str(out), preset, str(n_new)]
+    p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
+    assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
+    return json.loads(out.read_text())
+
+
+@pytest.mark.parametrize("preset", ["bf16", "nvfp4"])
+def test_tp2_fused_matches_nccl_and_ranks_agree(preset, tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    fused = _run(2, preset, "fused", tmp_path)
+    nccl = _run(2, preset, "nccl", tmp_path)
+    assert fused[0]["tokens"] == fused[1]["tokens"], "ranks must produce identical tokens"
+    assert all(r["transport"] == "fused" and r["stats"]["fused"] > 0 and r["status"] == 0 for r in fused)
+    assert fused[0]["graphs"] > 0, "the fused combine must be graph-capturable"
+    assert all(r["transport"] == "nccl" for r in nccl) and nccl[0]["tokens"] == nccl[1]["tokens"]
+    # same partial sums, different summation order: only a late divergence is tolerable
+    assert fused[0]["tokens"][:4] == nccl[0]["tokens"][:4]
