@@ -86,6 +86,8 @@ PYBIND11_MODULE(ps_runtime, m) {
             d["restored_tokens"] = r->restored_tokens; d["prefill_tokens"] = r->prefill_tokens;
             d["checkpoint_position"] = r->checkpoint_position; d["checkpoint_saved"] = r->checkpoint_saved;
             d["error"] = r->error; d["prompt"] = r->prompt; d["poisoned"] = r->seq.poisoned;
+            d["temperature"] = r->sampling.temperature; d["top_p"] = r->sampling.top_p; d["top_k"] = r->sampling.top_k;
+            d["seed"] = r->sampling.seed; d["max_new_tokens"] = r->max_new_tokens;
             return d; })
         .def("retire", &Batcher::retire).def("active_count", &Batcher::active_count).def("queued_count", &Batcher::queued_count)
         .def("free_pages", &Batcher::free_pages).def("idle", &Batcher::idle)

@@ -240,6 +240,60 @@ class Engine:
         # The warm-up forward already produced this step's results in the same workspace buffers.
         return self.graph_out[key]
 
+    # ------------------------------------------------------------------ externally managed sequences
+    def apply_block_updates(self, updates) -> None:
+        """Write (slot, block, page) entries produced by the host runtime into the device block table."""
+        if not updates:
+            return
+        u = torch.tensor(updates, dtype=torch.int64)
+        bt = self.state.block_table
+        vals = u[:, 2].to(torch.int32)
+        if self.device.type == "cuda":
+            bt.index_put_((u[:, 0].to(self.device), u[:, 1].to(self.device)), vals.to(self.device))
+        else:
+            bt[u[:, 0], u[:, 1]] = vals
+
+    def run_rows(self, rows: Sequence[SeqRows], *, mask=None, mask_active=None, tap_layers: Sequence[int] = (),
+                 gdn_log=None, gdn_to_alt: bool = False, sample: bool = True):
+        """Execute one step for sequences whose slots/pages are managed by the caller (the batcher).
+        Returns (tokens, StepOutput, device_status)."""
+        n_rows = sum(len(r.token_ids) for r in rows)
+        n_out = sum(len(r.output_rows) for r in rows)
+        bucket = resolve_row_bucket(n_rows)
+        b = self._batch(bucket)
+        b.fill(rows)
+        plain = not tap_layers and gdn_log is None and not gdn_to_alt and mask is None and sample
+        use_graph = self.use_graphs and bucket <= GRAPH_MAX_ROWS and plain
+        b.graph_static = use_graph
+        b.upload()
+        if use_graph:
+            out = self._run_graph(bucket, b, n_out)
+        else:
+            out = self.runner.forward(b, bucket if self.backend == "cuda" else n_rows, n_out, tap_layers=tap_layers,
+                                      gdn_log=gdn_log, gdn_to_alt=gdn_to_alt, mask=mask, mask_active=mask_active,
+                                      sample=sample)
+        toks: List[int] = []
+        if self.device.type == "cuda":
+            if out.tokens is not None and n_out:
+                self.h_tokens[:n_out].copy_(out.tokens[:n_out], non_blocking=True)
+            self.h_status.copy_(self.state.status, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            status = int(self.h_status[0])
+            if out.tokens is not None:
+                toks = self.h_tokens[:n_out].tolist()
+            if status == 0 and hasattr(self.ops, "status"):
+                status = int(self.ops.status[0])
+        else:
+            status = int(self.state.status[0])
+            if out.tokens is not None:
+                toks = out.tokens[:n_out].tolist()
+        self.steps += 1
+        if status != 0:
+            self.state.status.zero_()
+            if hasattr(self.ops, "status"):
+                self.ops.status.zero_()
+        return toks, out, status
+
     # ------------------------------------------------------------------ convenience: one request
     def prefill(self, s: Sequence_, token_ids: Sequence[int], chunk: int = 2048, sample_last: bool = True,
                 **samp) -> Optional[int]:

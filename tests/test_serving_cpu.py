@@ -1,0 +1,75 @@
+"""Continuous batching + prefix cache through the public serving loop on CPU (reference ops, fp32)."""
+import pytest
+import torch
+
+from phaseshift_b200.models.qwen35.config import tiny_config
+from phaseshift_b200.models.qwen35.reference import reference_greedy
+from phaseshift_b200.models.qwen35.weights import build_engine_weights, random_hf_weights
+from phaseshift_b200.runtime.engine import Engine
+from phaseshift_b200.runtime.serving import ServingEngine
+from phaseshift_b200.runtime.state import StateConfig
+
+
+@pytest.fixture(scope="module")
+def tiny():
+    cfg = tiny_config()
+    hf = random_hf_weights(cfg, seed=0)
+    return cfg, hf, build_engine_weights(cfg, lambda n: hf[n], "bf16", "cpu")
+
+
+def _prompt(cfg, n, seed):
+    return torch.randint(0, cfg.vocab_size, (n,), generator=torch.Generator().manual_seed(seed)).tolist()
+
+
+def _collect(events):
+    toks, done = {}, {}
+    for e in events:
+        if e.kind == "token":
+            toks.setdefault(e.request_id, []).append(e.token_id)
+        else:
+            done[e.request_id] = e
+    return toks, done
+
+
+def test_concurrent_requests_match_oracle(tiny):
+    cfg, hf, ew = tiny
+    eng = Engine(ew, "cpu", StateConfig(max_slots=3, max_seq_len=96, page_tokens=16))
+    srv = ServingEngine(eng, max_step_tokens=24)
+    prompts = [_prompt(cfg, n, s) for n, s in [(20, 1), (33, 2), (9, 3), (17, 4)]]
+    ids = [srv.submit(p, 6) for p in prompts]          # 4 requests, 3 slots: the last one queues
+    toks, done = _collect(srv.run_until_idle())
+    for rid, p in zip(ids, prompts):
+        assert toks[rid] == reference_greedy(cfg, hf, p, 6)
+        assert done[rid].info["generated_ids"] == toks[rid] and done[rid].info["finish_reason"] == "length"
+    assert eng.state.block_table.max().item() == -1      # every page returned
+
+
+def test_prefix_cache_hit_gives_identical_tokens(tiny):
+    cfg, hf, ew = tiny
+    eng = Engine(ew, "cpu", StateConfig(max_slots=2, max_seq_len=160, page_tokens=16))
+    srv = ServingEngine(eng, max_step_tokens=64, prefix_cache_tokens=512, prefix_cache_entries=4, prefix_min_tokens=16)
+    shared = _prompt(cfg, 70, 9)
+    p1, p2 = shared + _prompt(cfg, 11, 10), shared + _prompt(cfg, 8, 11)
+    r1 = srv.submit(p1, 5, checkpoint_position=70)
+    toks, done = _collect(srv.run_until_idle())
+    assert toks[r1] == reference_greedy(cfg, hf, p1, 5)
+    assert done[r1].info["cache_checkpoint_tokens"] == 70 and done[r1].info["restored_tokens"] == 0
+    r2 = srv.submit(p2, 5, checkpoint_position=70)
+    toks, done = _collect(srv.run_until_idle())
+    assert done[r2].info["restored_tokens"] == 70 and done[r2].info["prefill_tokens"] == len(p2) - 70
+    assert toks[r2] == reference_greedy(cfg, hf, p2, 5)
+    assert srv.prefix.summary()["hits"] == 1
+
+
+def test_cancel_and_stop_token(tiny):
+    cfg, hf, ew = tiny
+    eng = Engine(ew, "cpu", StateConfig(max_slots=2, max_seq_len=64))
+    srv = ServingEngine(eng)
+    p = _prompt(cfg, 12, 5)
+    ref = reference_greedy(cfg, hf, p, 6)
+    r1 = srv.submit(p, 6, stop_tokens=[ref[2]])
+    r2 = srv.submit(_prompt(cfg, 10, 6), 50)
+    ev = srv.step()
+    assert srv.cancel(r2) and srv.request(r2)["finish_reason"] == "cancelled"
+    toks, done = _collect(ev + srv.run_until_idle())
+    assert toks[r1] == ref[:3] and done[r1].info["finish_reason"] == "stop"
