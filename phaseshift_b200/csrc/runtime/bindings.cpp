@@ -1,4 +1,5 @@
 // pybind11 module `ps_runtime`: the host runtime exposed to Python.
+#include <pybind11/numpy.h>
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
@@ -122,9 +123,9 @@ PYBIND11_MODULE(ps_runtime, m) {
         .def("data", [](py::object self, const std::string& n) {
             auto& r = self.cast<SafetensorsReader&>();
             const auto& s = r.spec(n);
-            // zero-copy view into the mapping; keeps the reader alive through the memoryview's owner
-            return py::memoryview::from_memory((const void*)r.data(n), (py::ssize_t)(s.end - s.begin)); },
-             py::keep_alive<0, 1>())
+            // zero-copy uint8 view into the mapping; the array's base is the reader, so the mapping outlives
+            // every tensor derived from it (do not call close() while such tensors are alive)
+            return py::array_t<uint8_t>({(py::ssize_t)(s.end - s.begin)}, {(py::ssize_t)1}, r.data(n), self); })
         .def("crc32", [](const SafetensorsReader& r, const std::string& n) { const auto& s = r.spec(n); return crc32(r.data(n), s.end - s.begin); })
         .def("close", &SafetensorsReader::close);
     py::class_<SafetensorsWriter>(m, "SafetensorsWriter").def(py::init<const std::string&>())

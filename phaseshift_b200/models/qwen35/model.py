@@ -35,6 +35,15 @@ class Qwen35Runner:
         geo = state.geo
         self.hq, self.hkv = len(geo.q_heads), len(geo.kv_heads)
         self.hk, self.hv = len(geo.gdn_k_heads), len(geo.gdn_v_heads)
+        # optional callable(tag, activations[rows, K]): importance-matrix collection at projection inputs
+        self.imatrix_collector = None
+
+    def _tap(self, tag: str, x: torch.Tensor, n_rows: int, norm_w=None) -> None:
+        if self.imatrix_collector is None:
+            return
+        if norm_w is not None:
+            x = self.ops.rmsnorm(x, norm_w, self.cfg.rms_norm_eps, "imatrix_norm")
+        self.imatrix_collector(tag, x[:n_rows])
 
     def _row_parallel(self, inp: torch.Tensor, W, residual: torch.Tensor, name: str, rows: int) -> torch.Tensor:
         """Row-parallel projection + residual.  Single rank: residual fused in the projection epilogue.
@@ -58,9 +67,12 @@ class Qwen35Runner:
         eps = cfg.rms_norm_eps
         x = ops.embed(b, rows, w.embed, st.status)
         taps = {}
+        from .weights import P as _P
         for li, L in enumerate(w.layers):
             m = L.mixer
+            lp = f"{_P}layers.{li}."
             if L.kind == 0:
+                self._tap(lp + "linear_attn.in_proj_qkv.weight", x, b.n_rows, L.input_norm)
                 n_main = m.in_proj.N
                 if hasattr(ops, "buf"):
                     proj = ops.buf("gdn_proj", rows, n_main + m.ba_proj.N)
@@ -81,13 +93,18 @@ class Qwen35Runner:
                                       ops.linear(x, m.ba_proj, name="gdn_ba", norm_w=L.input_norm, eps=eps)], 1)
                     o = ops.gdn(proj, m, self.hk, self.hv, b, st.gdn[li], st,
                                 log=None if gdn_log is None else gdn_log[li], to_alt=gdn_to_alt)
+                self._tap(lp + "linear_attn.out_proj.weight", o, b.n_rows)
                 r = self._row_parallel(o, m.out_proj, x, "r", rows)
             else:
+                self._tap(lp + "self_attn.q_proj.weight", x, b.n_rows, L.input_norm)
                 qkv = ops.linear(x, m.qkv_proj, name="attn_qkv", norm_w=L.input_norm, eps=eps)
                 q = ops.attn_prep(qkv, m, self.hq, self.hkv, b, st.kv[li], st)
                 ctx = ops.paged_attention(q, qkv, self.hq, self.hkv, b, st.kv[li], st, b.max_visible_launch)
+                self._tap(lp + "self_attn.o_proj.weight", ctx, b.n_rows)
                 r = self._row_parallel(ctx, m.o_proj, x, "r", rows)
+            self._tap(lp + "mlp.gate_proj.weight", r, b.n_rows, L.post_norm)
             act = ops.linear(r, L.gate_up, name="mlp_act", norm_w=L.post_norm, eps=eps, swiglu=True)
+            self._tap(lp + "mlp.down_proj.weight", act, b.n_rows)
             # ping-pong the residual stream so a layer never writes the buffer it still reads
             xname = "x_a" if (li & 1) == 0 else "x_b"
             x = self._row_parallel(act, L.down, r, xname, rows)
@@ -96,6 +113,7 @@ class Qwen35Runner:
         tokens = logits = hidden = None
         if n_out > 0:
             hidden = ops.gather_rows(x, b.out_rows, n_out, "out_hidden", st.status)
+            self._tap(_P + "lm_head.weight", hidden, n_out, w.final_norm)
             logits = ops.linear(hidden, w.lm_head, name="logits", norm_w=w.final_norm, eps=eps, out_f32=True)
             if sample:
                 tokens = ops.sample(logits, b, n_out, mask=mask, mask_active=mask_active, status=st.status)

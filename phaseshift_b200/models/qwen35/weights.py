@@ -271,70 +271,190 @@ def _rows(t: torch.Tensor, heads: range, dim: int) -> torch.Tensor:
     return t[heads.start * dim: heads.stop * dim]
 
 
-def build_engine_weights(cfg: Qwen35Config, get: Callable[[str], torch.Tensor], preset: str = "bf16",
-                         device="cpu", tp_rank: int = 0, tp_size: int = 1,
-                         importance: Optional[Callable[[str], Optional[torch.Tensor]]] = None,
+class DenseSource:
+    """Weights given as full-precision HF tensors; projections are quantised here according to the preset."""
+
+    def __init__(self, get: Callable[[str], torch.Tensor], preset: str, device,
+                 importance: Optional[Callable[[str], Optional[torch.Tensor]]] = None):
+        self.get, self.preset, self.device, self.importance = get, preset, device, importance
+
+    def tensor(self, name: str) -> torch.Tensor:
+        return self.get(name)
+
+    def linear(self, parts, role: str, layer: int, interleave: bool = False) -> QuantizedTensor:
+        """parts: [(hf_name, row_range | None, k_range | None)] concatenated along rows."""
+        ws = []
+        for (name, rr, kr) in parts:
+            w = self.get(name)
+            if w.dim() > 2:
+                w = w.reshape(w.shape[0], -1)
+            if rr is not None:
+                w = w[rr.start:rr.stop]
+            if kr is not None:
+                w = w[:, kr.start:kr.stop]
+            ws.append(w)
+        if interleave:
+            w = torch.stack(ws, 1).reshape(len(ws) * ws[0].shape[0], ws[0].shape[1])
+        else:
+            w = torch.cat(ws, 0) if len(ws) > 1 else ws[0]
+        fmt = format_for(self.preset, role, layer)
+        imp = self.importance(parts[0][0]) if self.importance is not None else None
+        if imp is not None and parts[0][2] is not None:
+            imp = imp[parts[0][2].start:parts[0][2].stop]
+        return quantize(w.to(self.device), fmt, imp)
+
+
+class QuantizedSource:
+    """Weights read from a quantised model directory: canonical payloads are sliced and concatenated as
+    stored (never re-quantised).  K ranges must fall on block boundaries (reference rule:
+    docs/developer/tensor_partition.md:60-127)."""
+
+    def __init__(self, collection, manifest, device):
+        self.col, self.man, self.device = collection, manifest, device
+        self.entries = manifest.by_name()
+
+    def tensor(self, name: str) -> torch.Tensor:
+        name = self.man.aliases.get(name, name)
+        e = self.entries[name]
+        if e.encoding != "bf16":
+            raise ValueError(f"{name} is stored as {e.encoding}, expected a plain bf16 tensor")
+        return self.col.tensor(e.data)
+
+    def _payload(self, name: str):
+        name = self.man.aliases.get(name, name)
+        e = self.entries[name]
+        if e.encoding == "bf16":
+            return e, self.col.tensor(e.data).reshape(e.logical_shape[0], -1), None
+        return e, self.col.tensor(e.codes), self.col.tensor(e.metadata1)
+
+    def linear(self, parts, role: str, layer: int, interleave: bool = False) -> QuantizedTensor:
+        codes, scales, fmt, tscale, k_log = [], [], None, None, None
+        for (name, rr, kr) in parts:
+            e, c, sc = self._payload(name)
+            if fmt is None:
+                fmt, tscale = e.encoding, (e.metadata2 if e.metadata2 is not None else 1.0)
+            elif e.encoding != fmt or abs((e.metadata2 or 1.0) - tscale) > 1e-12 * max(1.0, abs(tscale)):
+                raise ValueError(f"tensors fused into one projection must share encoding and tensor scale ({name})")
+            k = e.logical_shape[1]
+            if rr is not None:
+                c = c[rr.start:rr.stop]
+                sc = None if sc is None else sc[rr.start:rr.stop]
+            if kr is not None:
+                blk = {"bf16": 1, "nvfp4": 32, "mxfp8": 32}[fmt]
+                if kr.start % blk or kr.stop % blk:
+                    raise ValueError(f"K range {kr} of {name} is not aligned to {blk}")
+                if fmt == "nvfp4":
+                    c, sc = c[:, kr.start // 2:kr.stop // 2], sc[:, kr.start // 16:kr.stop // 16]
+                elif fmt == "mxfp8":
+                    c, sc = c[:, kr.start:kr.stop], sc[:, kr.start // 32:kr.stop // 32]
+                else:
+                    c = c[:, kr.start:kr.stop]
+                k = kr.stop - kr.start
+            k_log = k
+            codes.append(c)
+            scales.append(sc)
+        if interleave:
+            cat = lambda xs: torch.stack(xs, 1).reshape(len(xs) * xs[0].shape[0], xs[0].shape[1])
+        else:
+            cat = lambda xs: torch.cat(xs, 0) if len(xs) > 1 else xs[0]
+        c = cat(codes).contiguous().to(self.device)
+        sc = None if scales[0] is None else cat(scales).contiguous().to(self.device)
+        n = c.shape[0]
+        kp = {"bf16": c.shape[1], "nvfp4": c.shape[1] * 2, "mxfp8": c.shape[1]}[fmt]
+        return QuantizedTensor(fmt, (n, k_log), kp, c, sc, float(tscale))
+
+
+def build_engine_weights(cfg: Qwen35Config, get, preset: str = "bf16", device="cpu", tp_rank: int = 0,
+                         tp_size: int = 1, importance: Optional[Callable[[str], Optional[torch.Tensor]]] = None,
                          keep_canonical: bool = True) -> EngineWeights:
-    """``get(name)`` returns the full HF tensor; slicing, fusing and quantisation happen here, one layer
-    at a time so a 27B model never needs more than one layer of BF16 weights resident."""
+    """Build the engine's fused, (optionally) quantised and tiled weights for one tensor-parallel rank.
+
+    ``get`` is either a callable ``name -> full HF tensor`` (weights are quantised here per ``preset``) or
+    a source object (``DenseSource`` / ``QuantizedSource``).  Work proceeds one layer at a time so a 27B
+    model never needs more than one layer of BF16 weights resident."""
+    src = get if hasattr(get, "linear") else DenseSource(get, preset, device, importance)
     geo = TpGeometry.make(cfg, tp_rank, tp_size)
     Dk, Dv, D = cfg.linear_key_head_dim, cfg.linear_value_head_dim, cfg.head_dim
     qk = cfg.gdn_qk_dim
+    on_cuda = torch.device(device).type == "cuda"
 
-    def lin(w: torch.Tensor, role: str, layer: int, name: str = "") -> LinearW:
-        fmt = format_for(preset, role, layer)
-        imp = importance(name) if (importance is not None and name) else None
-        lw = LinearW(quantize(w.to(device), fmt, imp))
-        if torch.device(device).type == "cuda" and role != "embed":
+    def lin(parts, role: str, layer: int, interleave: bool = False) -> LinearW:
+        lw = LinearW(src.linear(parts, role, layer, interleave))
+        if on_cuda and role != "embed":
             lw.make_tiled(keep_canonical or role == "gdn_small")   # the GDN kernel reads b/a rows row-major
         return lw
 
     def dev(t: torch.Tensor, dtype=torch.bfloat16) -> torch.Tensor:
         return t.to(device=device, dtype=dtype).contiguous()
 
+    def hr(heads: range, dim: int, base: int = 0) -> range:
+        return range(base + heads.start * dim, base + heads.stop * dim)
+
     layers = []
     for l, lt in enumerate(cfg.layer_types):
         lp = f"{P}layers.{l}."
         if lt == 0:
             a = lp + "linear_attn."
-            qkv = get(a + "in_proj_qkv.weight")
-            wq, wk, wv = qkv[:qk], qkv[qk:2 * qk], qkv[2 * qk:]
-            seg = [_rows(wq, geo.gdn_k_heads, Dk), _rows(wk, geo.gdn_k_heads, Dk), _rows(wv, geo.gdn_v_heads, Dv),
-                   _rows(get(a + "in_proj_z.weight"), geo.gdn_v_heads, Dv)]
-            in_proj = lin(torch.cat(seg, 0), "gdn_qkvz", l, a + "in_proj_qkv.weight")
-            ba = torch.cat([_rows(get(a + "in_proj_b.weight"), geo.gdn_v_heads, 1),
-                            _rows(get(a + "in_proj_a.weight"), geo.gdn_v_heads, 1)], 0)
-            cw = get(a + "conv1d.weight").reshape(cfg.gdn_conv_dim, 4)
-            cw = torch.cat([_rows(cw[:qk], geo.gdn_k_heads, Dk), _rows(cw[qk:2 * qk], geo.gdn_k_heads, Dk),
-                            _rows(cw[2 * qk:], geo.gdn_v_heads, Dv)], 0)
-            out_w = get(a + "out_proj.weight")[:, geo.gdn_v_heads.start * Dv: geo.gdn_v_heads.stop * Dv]
-            mixer = GdnW(in_proj, lin(ba, "gdn_small", l), dev(cw),
-                         dev(_rows(get(a + "A_log"), geo.gdn_v_heads, 1), torch.float32),
-                         dev(_rows(get(a + "dt_bias"), geo.gdn_v_heads, 1), torch.float32),
-                         dev(get(a + "norm.weight")), lin(out_w, "gdn_out", l, a + "out_proj.weight"))
+            kh, vh = geo.gdn_k_heads, geo.gdn_v_heads
+            in_proj = lin([(a + "in_proj_qkv.weight", hr(kh, Dk), None), (a + "in_proj_qkv.weight", hr(kh, Dk, qk), None),
+                           (a + "in_proj_qkv.weight", hr(vh, Dv, 2 * qk), None), (a + "in_proj_z.weight", hr(vh, Dv), None)],
+                          "gdn_qkvz", l)
+            ba = lin([(a + "in_proj_b.weight", hr(vh, 1), None), (a + "in_proj_a.weight", hr(vh, 1), None)], "gdn_small", l)
+            cw = src.tensor(a + "conv1d.weight").reshape(cfg.gdn_conv_dim, 4)
+            cw = torch.cat([_rows(cw[:qk], kh, Dk), _rows(cw[qk:2 * qk], kh, Dk), _rows(cw[2 * qk:], vh, Dv)], 0)
+            out_proj = lin([(a + "out_proj.weight", None, hr(vh, Dv))], "gdn_out", l)
+            mixer = GdnW(in_proj, ba, dev(cw), dev(_rows(src.tensor(a + "A_log"), vh, 1), torch.float32),
+                         dev(_rows(src.tensor(a + "dt_bias"), vh, 1), torch.float32), dev(src.tensor(a + "norm.weight")),
+                         out_proj)
         else:
             a = lp + "self_attn."
-            wq = _rows(get(a + "q_proj.weight"), geo.q_heads, 2 * D)
-            wk = _rows(get(a + "k_proj.weight"), geo.kv_heads, D)
-            wv = _rows(get(a + "v_proj.weight"), geo.kv_heads, D)
-            o_w = get(a + "o_proj.weight")[:, geo.q_heads.start * D: geo.q_heads.stop * D]
-            mixer = AttnW(lin(torch.cat([wq, wk, wv], 0), "attn_qkv", l, a + "q_proj.weight"),
-                          dev(get(a + "q_norm.weight")), dev(get(a + "k_norm.weight")),
-                          lin(o_w, "attn_o", l, a + "o_proj.weight"))
-        g = get(lp + "mlp.gate_proj.weight")[geo.inter.start: geo.inter.stop]
-        u = get(lp + "mlp.up_proj.weight")[geo.inter.start: geo.inter.stop]
-        gu = torch.stack([g, u], 1).reshape(2 * g.shape[0], g.shape[1])
-        down = get(lp + "mlp.down_proj.weight")[:, geo.inter.start: geo.inter.stop]
-        layers.append(LayerW(lt, dev(get(lp + "input_layernorm.weight")), mixer,
-                             dev(get(lp + "post_attention_layernorm.weight")),
-                             lin(gu, "ffn_gate_up", l, lp + "mlp.gate_proj.weight"),
-                             lin(down, "ffn_down", l, lp + "mlp.down_proj.weight")))
-    embed_w = get(P + "embed_tokens.weight")
-    embed = lin(embed_w, "embed", 0)
+            qkv = lin([(a + "q_proj.weight", hr(geo.q_heads, 2 * D), None), (a + "k_proj.weight", hr(geo.kv_heads, D), None),
+                       (a + "v_proj.weight", hr(geo.kv_heads, D), None)], "attn_qkv", l)
+            o_proj = lin([(a + "o_proj.weight", None, hr(geo.q_heads, D))], "attn_o", l)
+            mixer = AttnW(qkv, dev(src.tensor(a + "q_norm.weight")), dev(src.tensor(a + "k_norm.weight")), o_proj)
+        gu = lin([(lp + "mlp.gate_proj.weight", geo.inter, None), (lp + "mlp.up_proj.weight", geo.inter, None)],
+                 "ffn_gate_up", l, interleave=True)
+        down = lin([(lp + "mlp.down_proj.weight", None, geo.inter)], "ffn_down", l)
+        layers.append(LayerW(lt, dev(src.tensor(lp + "input_layernorm.weight")), mixer,
+                             dev(src.tensor(lp + "post_attention_layernorm.weight")), gu, down))
+    embed = lin([(P + "embed_tokens.weight", None, None)], "embed", 0)
     if cfg.tie_word_embeddings:
         lm_head = LinearW(embed.q)
-        if torch.device(device).type == "cuda":
+        if on_cuda:
             lm_head.make_tiled(True)
     else:
-        lm_head = lin(get(P + "lm_head.weight"), "lm_head", 0, P + "lm_head.weight")
-    return EngineWeights(cfg, embed, layers, dev(get(P + "norm.weight")), lm_head, tp_rank, tp_size, preset)
+        lm_head = lin([(P + "lm_head.weight", None, None)], "lm_head", 0)
+    return EngineWeights(cfg, embed, layers, dev(src.tensor(P + "norm.weight")), lm_head, tp_rank, tp_size, preset)
+
+
+# Tensors that are fused into one projection and must therefore share an NVFP4 per-tensor scale.
+def scale_groups(cfg: Qwen35Config) -> List[List[str]]:
+    groups = []
+    for l, lt in enumerate(cfg.layer_types):
+        lp = f"{P}layers.{l}."
+        groups.append([lp + "mlp.gate_proj.weight", lp + "mlp.up_proj.weight"])
+        if lt == 0:
+            groups.append([lp + "linear_attn.in_proj_qkv.weight", lp + "linear_attn.in_proj_z.weight"])
+        else:
+            a = lp + "self_attn."
+            groups.append([a + "q_proj.weight", a + "k_proj.weight", a + "v_proj.weight"])
+    return groups
+
+
+def load_engine_weights(model_dir, device="cpu", preset: Optional[str] = None, tp_rank: int = 0, tp_size: int = 1,
+                        keep_canonical: bool = True, verify_weights: bool = False) -> EngineWeights:
+    """Load a model directory: quantised (manifest present, auto-detected) or plain BF16 (quantised on the
+    fly when ``preset`` asks for it)."""
+    from ...io.model_dir import ShardCollection, is_quantized_dir
+    from ...quant.manifest import Manifest
+    cfg = Qwen35Config.from_dir(model_dir)
+    col = ShardCollection(model_dir)
+    if is_quantized_dir(model_dir):
+        man = Manifest.load(model_dir)
+        if verify_weights:
+            from ...quant.offline import verify_crc
+            verify_crc(col, man)
+        src = QuantizedSource(col, man, device)
+        return build_engine_weights(cfg, src, man.preset, device, tp_rank, tp_size, keep_canonical=keep_canonical)
+    return build_engine_weights(cfg, lambda n: col.tensor(n), preset or "bf16", device, tp_rank, tp_size,
+                                keep_canonical=keep_canonical)

@@ -1,0 +1,330 @@
+"""Offline quantiser core: quantize / verify / kld / imatrix / ppl.
+
+Counterpart of the reference's ``phaseshift_quantizer_core`` (src/phaseshift/quantization/offline/
+quantizer.cpp:98-989, kld.cpp, imatrix_collect.cpp, ppl.cpp).  ``quantize_model`` streams one HF tensor
+at a time: classify the name into a role, pick the encoding from the preset, quantise rows on the CPU
+reference quantiser (C++) or on the GPU, write structure-of-arrays tensors into size-bounded shards,
+record per-tensor CRC32 in the manifest, copy tokenizer / config assets and (unless disabled) verify the
+result.  ``evaluate_kld`` runs the BF16 model and the quantised bundle teacher-forced over token windows
+and reports the distribution of KL(p_bf16 || p_quant); ``collect_imatrix`` accumulates per-input-channel
+activation energy at every projection input; ``evaluate_ppl`` reports teacher-forced perplexity.
+"""
+from __future__ import annotations
+
+import hashlib
+import json
+import shutil
+from pathlib import Path
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..core.native import runtime
+from ..io.model_dir import ShardCollection, ShardWriter, is_quantized_dir
+from ..models.qwen35.config import Qwen35Config
+from ..models.qwen35.weights import format_for, scale_groups
+from . import formats
+from .manifest import CODES, META1, Manifest, TensorEntry, classify_qwen35, layer_of
+
+ASSETS = ("config.json", "generation_config.json", "tokenizer.json", "tokenizer_config.json", "vocab.json",
+          "merges.txt", "special_tokens_map.json", "chat_template.jinja", "added_tokens.json")
+
+
+def model_fingerprint(model_dir) -> str:
+    """sha256 over config + tensor names/shapes/CRC of the first and last KiB of every tensor (cheap, stable)."""
+    h = hashlib.sha256()
+    h.update((Path(model_dir) / "config.json").read_bytes())
+    col = ShardCollection(model_dir)
+    for n in sorted(col.names()):
+        dt, shape, nbytes = col.spec(n)
+        h.update(f"{n}:{dt}:{shape}:{nbytes}".encode())
+    col.close()
+    return h.hexdigest()
+
+
+def read_tokens(path) -> List[int]:
+    p = Path(path)
+    if p.suffix == ".npy":
+        return np.load(p).astype(np.int64).reshape(-1).tolist()
+    if p.suffix == ".bin":
+        return np.fromfile(p, dtype=np.int32).astype(np.int64).tolist()
+    return [int(t) for t in p.read_text().replace(",", " ").split()]
+
+
+# ------------------------------------------------------------------------------------------------ imatrix file
+def save_imatrix(path, sums: Dict[str, torch.Tensor], counts: Dict[str, int], meta: Optional[dict] = None) -> None:
+    from safetensors.torch import save_file
+    md = {"format": "phaseshift-imatrix", "counts": json.dumps(counts)}
+    md.update({k: str(v) for k, v in (meta or {}).items()})
+    save_file({k: v.float().contiguous().cpu() for k, v in sums.items()}, str(path), metadata=md)
+
+
+def load_imatrix(path):
+    rt = runtime()
+    r = rt.SafetensorsReader(str(path))
+    md = r.metadata()
+    if md.get("format") != "phaseshift-imatrix":
+        raise ValueError("not an imatrix file")
+    counts = json.loads(md["counts"])
+    out = {}
+    for n in r.names():
+        out[n] = torch.from_numpy(np.array(r.data(n)).view(np.float32).copy()) / max(1, counts.get(n, 1))
+    return out
+
+
+# ------------------------------------------------------------------------------------------------ quantize
+def imatrix_key(name: str) -> str:
+    """Projections that read the same activations share one importance vector (collected under the first)."""
+    for a, b in (("k_proj", "q_proj"), ("v_proj", "q_proj"), ("up_proj", "gate_proj"), ("in_proj_z", "in_proj_qkv")):
+        name = name.replace(a + ".weight", b + ".weight")
+    return name
+
+
+def _quantize_tensor(w: torch.Tensor, fmt: str, backend: str, tensor_scale: Optional[float], importance, search: int):
+    if fmt == "bf16":
+        return formats.quantize(w, "bf16")
+    if backend == "cuda":
+        wd = w.to("cuda").float()
+        imp = None if importance is None else importance.to("cuda")
+        q = formats.quantize_nvfp4(wd, imp, search, tensor_scale) if fmt == "nvfp4" else formats.quantize_mxfp8(wd, imp, min(search, 1))
+        return q.to("cpu")
+    rt = runtime()
+    wf = w.float().contiguous()
+    n, k = wf.shape
+    kp = formats.align_up(k, formats.K_ALIGN)
+    imp_ptr = 0
+    if importance is not None:
+        importance = importance.float().contiguous()
+        imp_ptr = importance.data_ptr()
+    if fmt == "nvfp4":
+        ts = tensor_scale if tensor_scale is not None else (float(wf.abs().max()) / (6.0 * 448.0) or 1.0)
+        codes = torch.zeros(n, kp // 2, dtype=torch.uint8)
+        scales = torch.zeros(n, kp // 16, dtype=torch.uint8)
+        rt.quantize_rows_nvfp4(wf.data_ptr(), n, k, kp, ts, search, imp_ptr, codes.data_ptr(), scales.data_ptr())
+        return formats.QuantizedTensor("nvfp4", (n, k), kp, codes, scales, ts)
+    codes = torch.zeros(n, kp, dtype=torch.uint8)
+    scales = torch.zeros(n, kp // 32, dtype=torch.uint8)
+    rt.quantize_rows_mxfp8(wf.data_ptr(), n, k, kp, min(search, 1), imp_ptr, codes.data_ptr(), scales.data_ptr())
+    return formats.QuantizedTensor("mxfp8", (n, k), kp, codes, scales, 1.0)
+
+
+def quantize_model(input_dir, output_dir, preset: str = "nvfp4", backend: str = "cpu", imatrix: Optional[str] = None,
+                   imatrix_policy: str = "strict", max_shard_size: int = 4 << 30, overwrite: bool = False,
+                   verify: bool = True, search: int = 2, log=print) -> Manifest:
+    inp, out = Path(input_dir), Path(output_dir)
+    if is_quantized_dir(inp):
+        raise ValueError("input is already a quantised directory")
+    if out.exists() and any(out.iterdir()):
+        if not overwrite:
+            raise FileExistsError(f"{out} is not empty (use --overwrite)")
+        shutil.rmtree(out)
+    out.mkdir(parents=True, exist_ok=True)
+    if backend == "cuda" and not torch.cuda.is_available():
+        raise RuntimeError("--backend cuda requested but no CUDA device is available")
+    cfg = Qwen35Config.from_dir(inp)
+    col = ShardCollection(inp)
+    imat = load_imatrix(imatrix) if imatrix else None
+    names = [n for n in col.names() if n.startswith("model.language_model.") or n.startswith("lm_head")]
+    group_of = {}
+    for g in scale_groups(cfg):
+        for n in g:
+            group_of[n] = g
+    man = Manifest(preset=preset, source_fingerprint=model_fingerprint(inp),
+                   imatrix={"file": str(imatrix), "policy": imatrix_policy} if imatrix else None)
+    plan = []
+    for n in names:
+        dt, shape, _ = col.spec(n)
+        role = classify_qwen35(n)
+        is_matrix = len(shape) == 2 and role not in ("norm", "other")
+        fmt = format_for(preset, role, layer_of(n)) if is_matrix else "bf16"
+        if imat is not None and is_matrix and fmt != "bf16" and imatrix_key(n) not in imat and role not in ("embed",):
+            if imatrix_policy == "strict":
+                raise ValueError(f"imatrix has no entry for {n} (policy strict)")
+        plan.append((n, role, fmt, shape))
+    writer = ShardWriter(out, max_shard_size)
+    for (n, role, fmt, shape) in plan:
+        if fmt == "bf16":
+            writer.add(n, torch.bfloat16 if len(shape) else torch.bfloat16, shape)
+        else:
+            kp = formats.align_up(shape[1], formats.K_ALIGN)
+            writer.add(n + CODES, torch.uint8, [shape[0], kp // 2 if fmt == "nvfp4" else kp])
+            writer.add(n + META1, torch.uint8, [shape[0], kp // (16 if fmt == "nvfp4" else 32)])
+    writer.begin()
+    tscale_cache: Dict[str, float] = {}
+    for (n, role, fmt, shape) in plan:
+        w = col.tensor(n)
+        if fmt == "bf16":
+            crc = writer.write(n, w.to(torch.bfloat16))
+            man.tensors.append(TensorEntry(n, role, "bf16", "row_major_k_contiguous", list(shape),
+                                           shape[-1] if shape else 1, data=n, crc32={n: crc}))
+            continue
+        ts = None
+        if fmt == "nvfp4":
+            grp = group_of.get(n, [n])
+            key = grp[0]
+            if key not in tscale_cache:
+                amax = max(float(col.tensor(m).float().abs().max()) for m in grp)
+                tscale_cache[key] = amax / (6.0 * 448.0) if amax > 0 else 1.0
+            ts = tscale_cache[key]
+        q = _quantize_tensor(w, fmt, backend, ts, None if imat is None else imat.get(imatrix_key(n)), search)
+        c1 = writer.write(n + CODES, q.codes)
+        c2 = writer.write(n + META1, q.scales)
+        man.tensors.append(TensorEntry(n, role, fmt, "row_major_k_contiguous", list(shape), q.k_padded,
+                                       codes=n + CODES, metadata1=n + META1,
+                                       metadata2=q.tensor_scale if fmt == "nvfp4" else None,
+                                       crc32={n + CODES: c1, n + META1: c2}))
+        log(f"quantized {n} {tuple(shape)} -> {fmt}")
+    writer.finish()
+    if cfg.tie_word_embeddings:
+        man.aliases["model.language_model.lm_head.weight"] = "model.language_model.embed_tokens.weight"
+    man.save(out)
+    for a in ASSETS:
+        if (inp / a).exists():
+            shutil.copy2(inp / a, out / a)
+    col.close()
+    if verify:
+        problems = validate_model_dir(out)
+        if problems:
+            raise RuntimeError("self-verification failed: " + "; ".join(problems[:5]))
+    return man
+
+
+def verify_crc(col: ShardCollection, man: Manifest) -> None:
+    for t in man.tensors:
+        for stored, crc in t.crc32.items():
+            if col.crc32(stored) != crc:
+                raise ValueError(f"CRC mismatch in {stored}")
+
+
+def validate_model_dir(model_dir) -> List[str]:
+    """Returns a list of problems (empty = valid)."""
+    problems: List[str] = []
+    d = Path(model_dir)
+    try:
+        man = Manifest.load(d)
+        cfg = Qwen35Config.from_dir(d)
+        col = ShardCollection(d)
+    except Exception as e:
+        return [f"cannot open: {e}"]
+    from ..models.qwen35.weights import hf_tensor_shapes
+    have = man.by_name()
+    for n, shape in hf_tensor_shapes(cfg).items():
+        n2 = man.aliases.get(n, n)
+        if n2 not in have:
+            problems.append(f"missing tensor {n}")
+            continue
+        e = have[n2]
+        if list(e.logical_shape) != list(shape):
+            problems.append(f"{n}: logical shape {e.logical_shape} != {list(shape)}")
+        for stored in ([e.data] if e.encoding == "bf16" else [e.codes, e.metadata1]):
+            if not col.has(stored):
+                problems.append(f"{n}: stored tensor {stored} missing")
+                continue
+            if col.crc32(stored) != e.crc32.get(stored):
+                problems.append(f"{n}: CRC mismatch in {stored}")
+        if e.encoding != "bf16":
+            kp = formats.align_up(e.logical_shape[1], formats.K_ALIGN)
+            if e.k_padded != kp:
+                problems.append(f"{n}: k_padded {e.k_padded} != {kp}")
+            _, cs, _ = col.spec(e.codes)
+            want = [e.logical_shape[0], kp // 2 if e.encoding == "nvfp4" else kp]
+            if list(cs) != want:
+                problems.append(f"{n}: codes shape {cs} != {want}")
+    col.close()
+    return problems
+
+
+# ------------------------------------------------------------------------------------------------ evaluation
+def _engine_for(model_dir, device, max_seq_len: int, preset: Optional[str] = None):
+    from ..models.qwen35.weights import load_engine_weights
+    from ..runtime.engine import Engine
+    from ..runtime.state import StateConfig
+    ew = load_engine_weights(model_dir, device, preset)
+    return Engine(ew, device, StateConfig(max_slots=1, max_seq_len=max_seq_len, page_tokens=16), use_graphs=False)
+
+
+def _window_logits(eng, ids: Sequence[int], chunk: int = 512) -> torch.Tensor:
+    """Teacher-forced logits [len(ids), vocab] (fp32, on CPU) for one window starting at position 0."""
+    from ..runtime.batch import SeqRows
+    s = eng.open_sequence()
+    outs = []
+    try:
+        for c0 in range(0, len(ids), chunk):
+            part = list(ids[c0:c0 + chunk])
+            _, out = eng.step([SeqRows(s.slot, s.position, part, tuple(range(len(part))))], [s], sample=False)
+            outs.append(out.logits[:len(part)].float().cpu())
+    finally:
+        eng.close_sequence(s)
+    return torch.cat(outs, 0)
+
+
+def kl_divergence(base_logits: torch.Tensor, test_logits: torch.Tensor) -> torch.Tensor:
+    """Per-position KL(p_base || p_test) in nats, computed in fp64."""
+    lp = torch.log_softmax(base_logits.double(), -1)
+    lq = torch.log_softmax(test_logits.double(), -1)
+    return (lp.exp() * (lp - lq)).sum(-1)
+
+
+def kld_report(kl: torch.Tensor, top1_agree: float) -> dict:
+    q = lambda p: float(torch.quantile(kl, p))
+    return {"positions": int(kl.numel()), "mean": float(kl.mean()), "p50": q(0.5), "p90": q(0.9), "p99": q(0.99),
+            "p99_9": q(0.999), "max": float(kl.max()), "top1_agreement": top1_agree}
+
+
+def evaluate_kld(input_dir, bundle_dir, tokens: Sequence[int], window: int = 512, stride: int = 512,
+                 max_eval_tokens: int = 0, device="cpu", self_check: bool = False) -> dict:
+    base = _engine_for(input_dir, device, window + 1)
+    test = base if self_check else _engine_for(bundle_dir, device, window + 1)
+    kls, agree, total = [], 0, 0
+    n = len(tokens) if max_eval_tokens <= 0 else min(len(tokens), max_eval_tokens)
+    for w0 in range(0, max(1, n - 1), stride):
+        ids = tokens[w0:w0 + window]
+        if len(ids) < 2:
+            break
+        lb = _window_logits(base, ids)
+        lt = lb if self_check else _window_logits(test, ids)
+        kls.append(kl_divergence(lb, lt))
+        agree += int((lb.argmax(-1) == lt.argmax(-1)).sum())
+        total += lb.shape[0]
+    kl = torch.cat(kls)
+    rep = kld_report(kl, agree / max(1, total))
+    rep.update(window=window, stride=stride, baseline=str(input_dir), bundle=str(bundle_dir))
+    return rep
+
+
+def evaluate_ppl(model_dir, tokens: Sequence[int], max_tokens: int = 2048, device="cpu") -> dict:
+    ids = list(tokens[:max_tokens])
+    eng = _engine_for(model_dir, device, len(ids) + 1)
+    lg = _window_logits(eng, ids)
+    lp = torch.log_softmax(lg[:-1].double(), -1)
+    nll = -lp[torch.arange(len(ids) - 1), torch.tensor(ids[1:])]
+    return {"tokens": len(ids) - 1, "nll": float(nll.mean()), "ppl": float(nll.mean().exp())}
+
+
+def collect_imatrix(model_dir, tokens: Sequence[int], output, window: int = 512, stride: int = 512,
+                    max_calibration_tokens: int = 0, device="cpu") -> dict:
+    """Accumulate sum(x^2) per input channel for every projection input (7 sites per layer + lm_head, the
+    tags the reference places in its lowering, src/phaseshift/models/qwen35/model/lower_to_primitives.cpp:
+    717-719,819-821,899-901,928-930,940-942,979-980)."""
+    eng = _engine_for(model_dir, device, window + 1)
+    sums: Dict[str, torch.Tensor] = {}
+    counts: Dict[str, int] = {}
+
+    def collector(tag: str, x: torch.Tensor) -> None:
+        v = x.float().pow(2).sum(0).cpu()
+        if tag in sums:
+            sums[tag] += v
+            counts[tag] += x.shape[0]
+        else:
+            sums[tag] = v
+            counts[tag] = x.shape[0]
+    eng.runner.imatrix_collector = collector
+    n = len(tokens) if max_calibration_tokens <= 0 else min(len(tokens), max_calibration_tokens)
+    for w0 in range(0, max(1, n - 1), stride):
+        ids = tokens[w0:w0 + window]
+        if len(ids) < 2:
+            break
+        _window_logits(eng, ids)
+    save_imatrix(output, sums, counts, {"model": str(model_dir), "tokens": n})
+    return {"sites": len(sums), "tokens": n, "output": str(output)}

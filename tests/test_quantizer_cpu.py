@@ -1,0 +1,81 @@
+"""Offline quantiser round trip on a tiny model (CPU): quantize -> verify -> load -> kld / ppl / imatrix."""
+import json
+
+import pytest
+import torch
+
+from phaseshift_b200.io.model_dir import ShardCollection, save_hf_model
+from phaseshift_b200.models.qwen35.config import tiny_config
+from phaseshift_b200.models.qwen35.weights import build_engine_weights, load_engine_weights, random_hf_weights
+from phaseshift_b200.quant import offline
+from phaseshift_b200.quant.manifest import Manifest
+
+
+@pytest.fixture(scope="module")
+def model_dirs(tmp_path_factory):
+    d = tmp_path_factory.mktemp("m")
+    cfg = tiny_config()
+    hf = random_hf_weights(cfg, seed=0)
+    src = d / "bf16"
+    save_hf_model(src, cfg, hf, max_shard_size=1 << 20)      # force several shards
+    return cfg, hf, src, d
+
+
+def test_sharded_hf_dir_roundtrip(model_dirs):
+    cfg, hf, src, _ = model_dirs
+    assert (src / "model.safetensors.index.json").exists()
+    col = ShardCollection(src)
+    for n, t in hf.items():
+        assert torch.equal(col.tensor(n), t)
+    ew = load_engine_weights(src, "cpu")
+    assert ew.layers[0].mixer.in_proj.N == cfg.gdn_conv_dim + cfg.gdn_v_dim
+
+
+def test_quantize_verify_load_and_eval(model_dirs):
+    cfg, hf, src, d = model_dirs
+    out = d / "nvfp4"
+    man = offline.quantize_model(src, out, preset="nvfp4", backend="cpu", max_shard_size=1 << 20, log=lambda *_: None)
+    assert offline.validate_model_dir(out) == []
+    m2 = Manifest.load(out)
+    enc = {t.name: t.encoding for t in m2.tensors}
+    assert enc["model.language_model.embed_tokens.weight"] == "mxfp8"
+    assert enc["model.language_model.layers.0.mlp.down_proj.weight"] == "mxfp8"      # layer % 4 == 0
+    assert enc["model.language_model.layers.1.mlp.down_proj.weight"] == "nvfp4"
+    assert enc["model.language_model.layers.0.linear_attn.in_proj_a.weight"] == "bf16"
+    assert enc["model.language_model.layers.3.self_attn.q_proj.weight"] == "nvfp4"
+    # q/k/v share one NVFP4 tensor scale so they can be fused into one projection without requantising
+    byn = m2.by_name()
+    a = "model.language_model.layers.3.self_attn."
+    assert byn[a + "q_proj.weight"].metadata2 == byn[a + "k_proj.weight"].metadata2 == byn[a + "v_proj.weight"].metadata2
+    # quantised directory loads into the engine and agrees with on-the-fly quantisation of the same weights
+    ew_dir = load_engine_weights(out, "cpu")
+    ew_fly = build_engine_weights(cfg, lambda n: hf[n], "nvfp4", "cpu")
+    for ld, lf in zip(ew_dir.layers, ew_fly.layers):
+        rel = (ld.gate_up.dense() - lf.gate_up.dense()).norm() / lf.gate_up.dense().norm()
+        assert rel < 0.05
+    toks = torch.randint(0, cfg.vocab_size, (80,), generator=torch.Generator().manual_seed(3)).tolist()
+    rep = offline.evaluate_kld(src, out, toks, window=32, stride=32)
+    assert rep["positions"] > 60 and 0 <= rep["mean"] < 0.05 and rep["max"] >= rep["p99"] >= rep["p50"] >= 0
+    selfrep = offline.evaluate_kld(src, out, toks, window=32, stride=32, self_check=True)
+    assert selfrep["max"] < 1e-9 and selfrep["top1_agreement"] == 1.0
+    ppl = offline.evaluate_ppl(out, toks, max_tokens=48)
+    assert ppl["ppl"] > 1.0
+    # corrupt one byte -> verify must notice
+    victim = next(out.glob("model-00001*.safetensors"))
+    b = bytearray(victim.read_bytes()); b[-5] ^= 0xFF; victim.write_bytes(bytes(b))
+    assert any("CRC" in p for p in offline.validate_model_dir(out))
+
+
+def test_imatrix_collect_and_weighted_quantize(model_dirs):
+    cfg, hf, src, d = model_dirs
+    toks = torch.randint(0, cfg.vocab_size, (70,), generator=torch.Generator().manual_seed(4)).tolist()
+    im = d / "im.safetensors"
+    rep = offline.collect_imatrix(src, toks, im, window=32, stride=32)
+    assert rep["sites"] == 4 * cfg.num_hidden_layers + 1      # 4 projection inputs per layer + lm_head
+    loaded = offline.load_imatrix(im)
+    k = "model.language_model.layers.0.mlp.gate_proj.weight"
+    assert loaded[k].shape == (cfg.hidden_size,) and float(loaded[k].min()) >= 0
+    out = d / "nvfp4_im"
+    offline.quantize_model(src, out, preset="nvfp4", backend="cpu", imatrix=str(im), imatrix_policy="best-effort",
+                           log=lambda *_: None)
+    assert offline.validate_model_dir(out) == [] and Manifest.load(out).imatrix["file"] == str(im)
