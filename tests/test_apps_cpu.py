@@ -1,0 +1,112 @@
+"""Entry points on CPU: compute single-shot / serve-stdio contract, quantizer CLI, argument validation."""
+import io
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from phaseshift_b200.apps import compute, quantizer
+from phaseshift_b200.io.model_dir import save_hf_model
+from phaseshift_b200.models.qwen35.config import tiny_config
+from phaseshift_b200.models.qwen35.reference import reference_greedy
+from phaseshift_b200.models.qwen35.weights import random_hf_weights
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def model_dir(tmp_path_factory):
+    d = tmp_path_factory.mktemp("app") / "tiny"
+    cfg = tiny_config(eos_token_ids=[4095])
+    hf = random_hf_weights(cfg, seed=0)
+    save_hf_model(d, cfg, hf)
+    return cfg, hf, d
+
+
+def test_invalid_flags_exit_2_before_load():
+    assert compute.main(["--random-model", "tiny", "--decode-backend", "gpu-mcu"]) == 2
+    assert compute.main(["--random-model", "tiny", "--kv-cache-dtype", "psq4"]) == 2
+    assert compute.main(["--max-new-tokens", "4"]) == 2
+    assert compute.main(["--random-model", "tiny", "--dflash2-ngram-tail", "2"]) == 2
+    with pytest.raises(SystemExit):
+        compute.main(["--help"])
+
+
+def test_single_shot_contract(model_dir, tmp_path, capsys):
+    cfg, hf, d = model_dir
+    ids = torch.randint(0, 4000, (12,), generator=torch.Generator().manual_seed(2)).tolist()
+    f = tmp_path / "p.ids"
+    f.write_text(" ".join(map(str, ids)))
+    assert compute.main(["--model-dir", str(d), "--input-ids-file", str(f), "--max-new-tokens", "6", "--device", "cpu"]) == 0
+    out = dict(l.split("=", 1) for l in capsys.readouterr().out.strip().splitlines())
+    assert out["PROMPT_TOKENS"] == "12" and out["GENERATED_TOKENS"] == "6" and out["KV_CACHE_DTYPE"] == "bf16"
+    assert [int(t) for t in out["GENERATED_IDS"].split(",")] == reference_greedy(cfg, hf, ids, 6)
+    lg = tmp_path / "l.bin"
+    assert compute.main(["--model-dir", str(d), "--input-ids-file", str(f), "--max-new-tokens", "3", "--device", "cpu",
+                         "--dump-logits", str(lg)]) == 0
+    out2 = dict(l.split("=", 1) for l in capsys.readouterr().out.strip().splitlines())
+    assert out2["LOGITS_VOCAB"] == "4096" and out2["LOGITS_TOTAL_ROWS"] == "3" and lg.stat().st_size == 3 * 4096 * 4
+    assert out2["GENERATED_IDS"].split(",") == out["GENERATED_IDS"].split(",")[:3]
+
+
+@pytest.mark.timeout(180)
+def test_serve_stdio_protocol(model_dir):
+    cfg, hf, d = model_dir
+    p = subprocess.Popen([sys.executable, "-m", "phaseshift_b200.apps.compute", "--model-dir", str(d), "--device", "cpu",
+                          "--serve-stdio", "--max-concurrent-requests", "2", "--max-seq-len", "128"],
+                         stdin=subprocess.PIPE, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, cwd=ROOT,
+                         env=dict(os.environ, PYTHONPATH=ROOT))
+    try:
+        assert "PHASESHIFT_SERVE_READY" in p.stderr.readline()
+        ids = list(range(5, 25))
+
+        def send(o):
+            p.stdin.write(json.dumps(o) + "\n"); p.stdin.flush()
+        send({"op": "ping"})
+        assert json.loads(p.stdout.readline()) == {"event": "pong"}
+        send({"op": "generate", "request_id": 7, "input_ids": ids, "max_new_tokens": 5})
+        send({"op": "generate", "request_id": 8, "input_ids": ids[:9], "max_new_tokens": 100})
+        toks, done = {7: [], 8: []}, {}
+        while 7 not in done:
+            e = json.loads(p.stdout.readline())
+            if e["event"] == "token":
+                toks[e["request_id"]].append(e["token_id"])
+            elif e["event"] == "done":
+                done[e["request_id"]] = e
+        assert toks[7] == done[7]["generated_ids"] == reference_greedy(cfg, hf, ids, 5)
+        assert done[7]["finish_reason"] == "length" and done[7]["prompt_tokens"] == 20
+        send({"op": "cancel", "request_id": 8})
+        while 8 not in done:
+            e = json.loads(p.stdout.readline())
+            if e["event"] == "done":
+                done[e["request_id"]] = e
+        assert done[8]["finish_reason"] == "cancelled"
+        send({"op": "bogus", "request_id": 9})
+        assert json.loads(p.stdout.readline())["event"] == "error"
+        send({"op": "shutdown"})
+        assert json.loads(p.stdout.readline()) == {"event": "shutdown"}
+        assert p.wait(timeout=30) == 0
+    finally:
+        if p.poll() is None:
+            p.kill()
+
+
+def test_quantizer_cli(model_dir, tmp_path, capsys):
+    cfg, hf, d = model_dir
+    out = tmp_path / "q"
+    assert quantizer.main(["quantize", "--input", str(d), "--output", str(out), "--preset", "nvfp4"]) == 0
+    assert quantizer.main(["quantize", "--input", str(d), "--output", str(out)]) == 2          # not empty, no --overwrite
+    assert quantizer.main(["verify", str(out)]) == 0
+    tk = tmp_path / "t.txt"
+    tk.write_text(" ".join(str(i % 4000) for i in range(3, 70)))
+    capsys.readouterr()
+    assert quantizer.main(["kld", "--input", str(d), "--bundle", str(out), "--tokens", str(tk), "--window", "32",
+                           "--stride", "32", "--device", "cpu"]) == 0
+    rep = dict(l.split("=", 1) for l in capsys.readouterr().out.strip().splitlines())
+    assert float(rep["KLD_MEAN"]) >= 0 and float(rep["KLD_MAX"]) >= float(rep["KLD_P50"])
+    assert quantizer.main(["ppl", "--model-dir", str(out), "--tokens", str(tk), "--max-tokens", "40", "--device", "cpu"]) == 0
+    # quantised directory runs through compute with the exact-match contract against itself
+    assert compute.main(["--model-dir", str(out), "--max-new-tokens", "4", "--device", "cpu", "--verify-weights", "1"]) == 0
