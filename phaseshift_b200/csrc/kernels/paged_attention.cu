@@ -10,7 +10,10 @@
 // One CTA = (split, kv head, row) and serves all G = Hq/Hkv query heads that share the K/V tile.
 //
 // K/V pools: [num_pages, Hkv, page_tokens, D]; FP8 pools carry one f32 scale per (page, head, token).
+#include <stdio.h>
+
 #include "ps_common.cuh"
+#include "ps_noalloc.h"
 
 namespace ps {
 
@@ -270,4 +273,57 @@ PS_API int ps_paged_attention(const void* q, const void* k_pool, const void* v_p
     m.ld_gate = ld_gate; m.gate_head_stride = gate_head_stride; m.gate_offset = gate_offset;
     m.out = (__nv_bfloat16*)out;
     return launch_pdl(paged_attn_merge_kernel, dim3(Hq, rows), dim3(D), 0, stream, m);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free variant: identical kernels, partial results in static device storage (ps_noalloc.h).
+namespace ps {
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+static void* g_noalloc_ptr[64] = {nullptr};           // device address of the array, per device ordinal
+static thread_local char g_noalloc_err[256] = "";
+}  // namespace ps
+
+PS_API const char* ps_noalloc_last_error(void) { return ps::g_noalloc_err; }
+
+PS_API int ps_paged_attention_noalloc(const void* q, const void* k_pool, const void* v_pool, const void* k_scale,
+                                      const void* v_scale, const void* block_table, int max_blocks, int page_tokens,
+                                      int num_pages, const void* row_slot, const void* row_pos, int rows, int Hq, int Hkv,
+                                      int D, float sm_scale, int kv_fp8, int split_tokens, int max_splits,
+                                      int max_visible, const void* gate, int ld_gate, int gate_head_stride,
+                                      int gate_offset, void* out, void* status, cudaStream_t stream) {
+    using namespace ps;
+    g_noalloc_err[0] = 0;
+    if (rows <= 0 || Hq <= 0 || max_splits <= 0 || D <= 0) return (int)cudaErrorInvalidValue;
+    const size_t acc_floats = (size_t)rows * Hq * max_splits * D;
+    const size_t ml_floats = (size_t)rows * Hq * max_splits * 2;
+    const size_t need = (acc_floats + ml_floats) * sizeof(float);
+    if (need > (size_t)kNoAllocScratchBytes) {
+        snprintf(g_noalloc_err, sizeof(g_noalloc_err),
+                 "ps_paged_attention_noalloc: rows*Hq*max_splits*(D+2)*4 = %zu bytes exceeds the built-in scratch of %d bytes",
+                 need, (int)kNoAllocScratchBytes);
+        return PS_NOALLOC_TOO_LARGE;
+    }
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) {
+        snprintf(g_noalloc_err, sizeof(g_noalloc_err), "ps_paged_attention_noalloc: cannot identify the current device");
+        return PS_NOALLOC_SETUP_FAILED;
+    }
+    if (g_noalloc_ptr[dev] == nullptr) {
+        // One-time set-up for this device: the array's name is only a host-side stand-in, the kernels
+        // need its device address.
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            snprintf(g_noalloc_err, sizeof(g_noalloc_err), "ps_paged_attention_noalloc: cudaGetSymbolAddress failed: %s",
+                     cudaGetErrorString(e));
+            return PS_NOALLOC_SETUP_FAILED;
+        }
+        g_noalloc_ptr[dev] = p;
+    }
+    float* part_acc = reinterpret_cast<float*>(g_noalloc_ptr[dev]);
+    float* part_ml = part_acc + acc_floats;
+    return ps_paged_attention(q, k_pool, v_pool, k_scale, v_scale, block_table, max_blocks, page_tokens, num_pages,
+                              row_slot, row_pos, rows, Hq, Hkv, D, sm_scale, kv_fp8, split_tokens, max_splits, max_visible,
+                              part_acc, part_ml, gate, ld_gate, gate_head_stride, gate_offset, out, status, stream);
 }
