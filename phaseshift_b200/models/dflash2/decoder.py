@@ -1,0 +1,155 @@
+"""DFlash2 speculative decoding round state machine.
+
+One round (reference: src/phaseshift/models/qwen35/runtime/dflash2_spec_decoder.cpp:416-650,
+docs/developer/dflash2.md:746-807,942-962):
+
+1. ``K = min(num_drafts, remaining - 1, room - 1)``; K == 0 falls back to a plain decode step.
+2. The drafter proposes K tokens from the pending (anchor) token and its context ring.
+3. The target verifies rows ``[anchor, d1..dK]`` in ONE forward in Exact numeric mode (every row is
+   computed with the arithmetic of a single-row decode), sampling one token per row; GDN layers keep
+   their old recurrent state and log (k, delta, decay) per row instead.
+4. ``spec_greedy_accept``: longest prefix where draft == target sample; the next token is the target's
+   sample at the first mismatch (correction) or after the last draft (bonus).
+5. Commit ``accepted + 1`` rows: replay the GDN log prefix onto the old state, advance the position
+   (conv history and KV pages beyond it are simply overwritten later), trim surplus KV pages, append the
+   committed rows' hidden taps to the drafter's ring.
+
+With temperature 0 the emitted stream equals target-only greedy decoding token for token; with
+temperature > 0 drafts are compared against the target's own samples (sample-and-compare), each row using
+``sample_index = tokens generated so far + row``.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ...core.native import runtime
+from ...runtime.batch import SeqRows
+from .model import DFlash2Config, DFlash2Drafter
+
+
+def embed_rows(table, ids: torch.Tensor) -> torch.Tensor:
+    """Rows of the target's embedding table (bf16 or MXFP8 canonical payload) as fp32."""
+    q = table.q
+    if q.fmt == "bf16":
+        return q.codes[ids].float()
+    if q.fmt == "mxfp8":
+        c = q.codes[ids].view(torch.float8_e4m3fn).float()
+        s = torch.exp2(q.scales[ids].float() - 127.0)
+        return (c.reshape(len(ids), -1, 32) * s[..., None]).reshape(len(ids), -1)[:, :q.shape[1]]
+    raise ValueError("unsupported embedding format " + q.fmt)
+
+
+class DFlash2SpecDecoder:
+    def __init__(self, engine, drafter: DFlash2Drafter, num_drafts: int = 7, ngram_tail: int = 0, ngram_n: int = 0):
+        if engine.sc.spec_rows < num_drafts + 1 + ngram_tail:
+            raise ValueError("engine state was not sized for this many speculative rows (StateConfig.spec_rows)")
+        if engine.sc.conv_ring < 3 + num_drafts + 1 + ngram_tail:
+            raise ValueError("conv_ring must be >= 3 + speculative rows so history survives a rollback")
+        self.eng, self.drafter, self.k = engine, drafter, num_drafts
+        self.ngram_tail, self.ngram_n = ngram_tail, ngram_n
+        self.rt = runtime()
+        self.taps = list(drafter.cfg.target_layer_ids)
+        cfg = engine.cfg
+        rows = 16 if num_drafts + 1 + ngram_tail > 8 else 8
+        st = engine.state
+        dev = engine.device
+        Dk, Dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
+        self.logs: Dict[int, tuple] = {}
+        for li, g in enumerate(st.gdn):
+            if g is not None:
+                self.logs[li] = (torch.zeros(rows, st.hv, Dk, device=dev), torch.zeros(rows, st.hv, Dv, device=dev),
+                                 torch.zeros(rows, st.hv, device=dev))
+        self.stats = {"rounds": 0, "accepted": 0, "proposed": 0, "emitted": 0, "plain_steps": 0}
+
+    @staticmethod
+    def from_dir(engine, drafter_dir, num_drafts: int = 7, ngram_tail: int = 0, ngram_n: int = 0):
+        dt = torch.float32 if engine.device.type == "cpu" else torch.bfloat16
+        return DFlash2SpecDecoder(engine, DFlash2Drafter.from_dir(drafter_dir, engine.device, dt), num_drafts, ngram_tail,
+                                  ngram_n)
+
+    # ------------------------------------------------------------------ target bridges
+    def _embed(self, ids: torch.Tensor) -> torch.Tensor:
+        return embed_rows(self.eng.runner.w.embed, ids)
+
+    def _lm_head(self, h: torch.Tensor) -> torch.Tensor:
+        ops = self.eng.ops
+        x = h.to(ops.act_dtype).contiguous()
+        return ops.linear(x, self.eng.runner.w.lm_head, name="dflash_logits", out_f32=True).float()
+
+    def _append_taps(self, out, n_rows: int, pos_start: int) -> None:
+        self.drafter.append_context([out.taps[l][:n_rows] for l in self.taps], pos_start)
+
+    # ------------------------------------------------------------------ phases
+    def prefill(self, s, prompt: Sequence[int], chunk: int, samp: dict) -> int:
+        tok = None
+        for c0 in range(0, len(prompt), chunk):
+            ids = list(prompt[c0:c0 + chunk])
+            last = c0 + chunk >= len(prompt)
+            pos0 = s.position
+            toks, out = self.eng.step([SeqRows(s.slot, pos0, ids, (len(ids) - 1,) if last else (), sample_index=0, **samp)],
+                                      [s], tap_layers=self.taps)
+            self._append_taps(out, len(ids), pos0)
+            if toks:
+                tok = toks[0]
+        return tok
+
+    def round(self, s, anchor: int, generated: List[int], remaining: int, samp: dict) -> List[int]:
+        """Advance by one speculative round; returns the tokens emitted (1 .. K+1)."""
+        eng = self.eng
+        room = eng.sc.max_seq_len - s.position
+        k = max(0, min(self.k, remaining - 1, room - 1))
+        pos0 = s.position
+        if k == 0:
+            toks, out = eng.step([SeqRows(s.slot, pos0, [anchor], (0,), sample_index=len(generated), **samp)], [s],
+                                 tap_layers=self.taps)
+            self._append_taps(out, 1, pos0)
+            self.stats["plain_steps"] += 1
+            return [toks[0]]
+        drafts = self.drafter.propose(anchor, k, self._embed, self._lm_head, pos0)
+        if self.ngram_tail and self.ngram_n:
+            drafts = drafts + self.rt.ngram_tail(generated + [anchor] + drafts, self.ngram_n,
+                                                 min(self.ngram_tail, max(0, remaining - 1 - len(drafts))))
+        rows = [anchor] + drafts
+        n = len(rows)
+        toks, out = eng.step([SeqRows(s.slot, pos0, rows, tuple(range(n)), sample_index=len(generated), **samp)], [s],
+                             commit=False, tap_layers=self.taps, gdn_log=self.logs, gdn_to_alt=True, exact=True)
+        accepted, nxt, full = self.rt.spec_greedy_accept(drafts, toks)
+        keep = accepted + 1                                  # anchor + accepted drafts are now part of the sequence
+        st = eng.state
+        desc = torch.tensor([[0, keep, s.slot, pos0]], dtype=torch.int32, device=eng.device)
+        for li, g in enumerate(st.gdn):
+            if g is not None:
+                eng.ops.gdn_replay(g, st.hv, desc, 1, self.logs[li])
+        s.position = pos0 + keep
+        eng.trim_pages(s)
+        self._append_taps(out, keep, pos0)
+        self.stats["rounds"] += 1
+        self.stats["accepted"] += accepted
+        self.stats["proposed"] += len(drafts)
+        return drafts[:accepted] + [nxt]
+
+    # ------------------------------------------------------------------ one request
+    def generate(self, prompt: Sequence[int], max_new_tokens: int, stop_tokens: Sequence[int] = (), prefill_chunk: int = 2048,
+                 temperature: float = 0.0, top_p: float = 1.0, top_k: int = 0, seed: int = 0) -> Tuple[List[int], dict]:
+        samp = dict(temperature=temperature, top_p=top_p, top_k=top_k, seed=seed)
+        self.drafter.reset()
+        s = self.eng.open_sequence()
+        out: List[int] = []
+        try:
+            tok = self.prefill(s, prompt, prefill_chunk, samp)
+            out.append(tok)
+            while len(out) < max_new_tokens and out[-1] not in stop_tokens:
+                emitted = self.round(s, out[-1], out[:-1], max_new_tokens - len(out), samp)
+                for t in emitted:
+                    out.append(t)
+                    if t in stop_tokens or len(out) >= max_new_tokens:
+                        break
+        finally:
+            self.eng.close_sequence(s)
+        self.stats["emitted"] = len(out)
+        r = max(1, self.stats["rounds"])
+        stats = dict(self.stats, tokens_per_round=round((self.stats["accepted"] + self.stats["rounds"]) / r, 3),
+                     mean_accepted=round(self.stats["accepted"] / r, 3))
+        return out, stats

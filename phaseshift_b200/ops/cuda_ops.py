@@ -49,6 +49,7 @@ class CudaOps:
         self.max_splits = attn_max_splits or -(-(max_seq_len + 1) // self.split_tokens)
         self.launches = 0
         self.use_tc_gemm = True
+        self.exact_rows = False     # verify steps: keep every projection on the batch-invariant small-M kernel
         self.wscratch = None
         self.status = torch.zeros(1, dtype=torch.int32, device=device)   # kernels' own bounded-wait status word
 
@@ -90,7 +91,7 @@ class CudaOps:
         assert out.shape[0] == M and out.shape[1] == n_out and out.stride(1) == 1
         if tp_combine is not None and M > SMALL_M_MAX:
             raise ValueError("the fused tensor-parallel combine handles at most 8 rows")
-        if M > SMALL_M_MAX and self.use_tc_gemm:
+        if M > SMALL_M_MAX and self.use_tc_gemm and not self.exact_rows:
             return self.linear_large(x, W, name=name, norm_w=norm_w, eps=eps, residual=residual, swiglu=swiglu,
                                      out_f32=out_f32, out=out)
         pro = PRO_RMSNORM if norm_w is not None else PRO_NONE

@@ -30,6 +30,7 @@ class RefOps:
         half = cfg.rotary_dim // 2
         self.inv_freq = cfg.rope_theta ** (-torch.arange(half, dtype=torch.float64) * 2.0 / cfg.rotary_dim)
         self.launches = 0
+        self.exact_rows = False
 
     def _dense(self, W: LinearW) -> torch.Tensor:
         return W.dense().to(self.device)

@@ -161,8 +161,12 @@ class Engine:
 
     def step(self, rows: Sequence[SeqRows], seq_objs: Sequence[Sequence_], *, commit: bool = True,
              tap_layers: Sequence[int] = (), gdn_log=None, gdn_to_alt: bool = False, mask=None,
-             mask_active=None, want_logits: bool = False, sample: bool = True):
-        """Run one step.  Returns (tokens list[int] per output row, StepOutput)."""
+             mask_active=None, want_logits: bool = False, sample: bool = True, exact: bool = False):
+        """Run one step.  Returns (tokens list[int] per output row, StepOutput).
+
+        ``exact``: compute every row with single-row-decode arithmetic (the reference's VerifyNumericMode::Exact,
+        include/phaseshift/runtime/execution/execution_types.h:6-27): projections stay on the batch-invariant
+        small-M kernel instead of the tensor-core GEMM, so speculative verification reproduces plain decoding."""
         n_rows = sum(len(r.token_ids) for r in rows)
         n_out = sum(len(r.output_rows) for r in rows)
         bucket = resolve_row_bucket(n_rows)
@@ -182,16 +186,20 @@ class Engine:
                     del s.pages[-a:]
             raise
         b.fill(rows)
-        plain = not tap_layers and gdn_log is None and not gdn_to_alt and mask is None and sample
+        plain = not tap_layers and gdn_log is None and not gdn_to_alt and mask is None and sample and not exact
         use_graph = self.use_graphs and bucket <= GRAPH_MAX_ROWS and plain
         b.graph_static = use_graph
         b.upload()
         if use_graph:
             out = self._run_graph(bucket, b, n_out)
         else:
-            out = self.runner.forward(b, bucket if self.backend == "cuda" else n_rows, n_out, tap_layers=tap_layers,
-                                      gdn_log=gdn_log, gdn_to_alt=gdn_to_alt, mask=mask, mask_active=mask_active,
-                                      sample=sample)
+            self.ops.exact_rows = exact
+            try:
+                out = self.runner.forward(b, bucket if self.backend == "cuda" else n_rows, n_out, tap_layers=tap_layers,
+                                          gdn_log=gdn_log, gdn_to_alt=gdn_to_alt, mask=mask, mask_active=mask_active,
+                                          sample=sample)
+            finally:
+                self.ops.exact_rows = False
         toks: List[int] = []
         if self.device.type == "cuda":
             if out.tokens is not None and n_out:
@@ -201,6 +209,8 @@ class Engine:
             status = int(self.h_status[0])
             if out.tokens is not None:
                 toks = self.h_tokens[:n_out].tolist()
+            if status == 0 and hasattr(self.ops, "status"):
+                status = int(self.ops.status[0])
         else:
             status = int(self.state.status[0])
             if out.tokens is not None:
@@ -208,6 +218,8 @@ class Engine:
         self.steps += 1
         if status != 0:
             self.state.status.zero_()
+            if hasattr(self.ops, "status"):
+                self.ops.status.zero_()
             for s in seq_objs:
                 s.poisoned = True
             raise SequenceError(f"device reported status {status}; sequences poisoned")

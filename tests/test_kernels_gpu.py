@@ -337,3 +337,28 @@ def test_large_m_linear_fused_epilogues(fmt):
     y = cu.linear(x, W, name="b", norm_w=nw, eps=1e-6, swiglu=True)
     assert _rel_err(y, ref.linear(x, W, name="b", norm_w=nw, eps=1e-6, swiglu=True)) < 2e-2
     assert int(cu.status[0]) == 0
+
+
+def test_dflash2_exact_verify_on_gpu():
+    """On the GPU the verify forward (8 rows, Exact mode) must reproduce single-row decoding bit for bit, so a
+    perfect drafter is fully accepted and any drafter leaves the greedy stream unchanged."""
+    from phaseshift_b200.models.dflash2.decoder import DFlash2SpecDecoder
+    from phaseshift_b200.models.dflash2.model import DFlash2Drafter, random_weights, tiny_drafter_config
+    from phaseshift_b200.runtime.engine import Engine
+    cfg = tiny_config()
+    hf = random_hf_weights(cfg, seed=0)
+    prompt = torch.randint(0, cfg.vocab_size, (21,), generator=torch.Generator().manual_seed(8)).tolist()
+    for preset in ("bf16", "nvfp4"):
+        ew = build_engine_weights(cfg, lambda n: hf[n], preset, "cuda")
+        plain = Engine(ew, "cuda", StateConfig(max_slots=1, max_seq_len=96)).generate(prompt, 24, prefill_chunk=8)
+        eng = Engine(ew, "cuda", StateConfig(max_slots=1, max_seq_len=96, conv_ring=16, spec_rows=8))
+        dcfg = tiny_drafter_config(cfg)
+        dec = DFlash2SpecDecoder(eng, DFlash2Drafter(dcfg, random_weights(dcfg, 1), "cuda"), num_drafts=5)
+        out, stats = dec.generate(prompt, 24, prefill_chunk=8)
+        assert out == plain, preset
+        full = prompt + plain
+        dec2 = DFlash2SpecDecoder(Engine(ew, "cuda", StateConfig(max_slots=1, max_seq_len=96, conv_ring=16, spec_rows=8)),
+                                  DFlash2Drafter(dcfg, random_weights(dcfg, 1), "cuda"), num_drafts=5)
+        dec2.drafter.propose = lambda a, k, e, l, pos, allowed=None: full[pos + 1: pos + 1 + k]
+        out2, stats2 = dec2.generate(prompt, 24, prefill_chunk=8)
+        assert out2 == plain and stats2["accepted"] == stats2["proposed"], (preset, stats2)
