@@ -1,0 +1,331 @@
+"""phaseshift-server: OpenAI-compatible HTTP server in one process.
+
+The reference chains LocalAI (Go) -> gRPC backend (Python) -> ``phaseshift-compute --serve-stdio``
+(src/apps/server/phaseshift_server.py, backend/phaseshift_backend.py, backend/compute_client.py); the
+three hops exist only because of its Go front end.  Here FastAPI talks to the serving loop directly: a
+single engine thread owns the GPU and steps the continuous batcher, HTTP handlers exchange messages with
+it through queues.  Preserved surface (docs/user/server.md:79-330): ``/v1/chat/completions`` (stream and
+non-stream, tools, strict tools, ``response_format``), ``/v1/responses``, ``/v1/models``, opt-in reasoning,
+HTTP 400 for bad schemas / tool contracts / unknown ``reasoning_effort`` before generation starts,
+``finish_reason="cancelled"`` when the client disconnects, fail-closed structured output.
+"""
+from __future__ import annotations
+
+import argparse
+import asyncio
+import json
+import queue
+import sys
+import threading
+import time
+import uuid
+from typing import Dict, List, Optional
+
+from ..serving import chat
+
+try:        # module-level names so FastAPI can resolve the handlers' (string) annotations
+    from fastapi import FastAPI, Request
+    from fastapi.responses import JSONResponse, StreamingResponse
+except Exception:  # pragma: no cover - the server app needs fastapi; everything else imports without it
+    FastAPI = Request = JSONResponse = StreamingResponse = None
+
+
+def build_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="phaseshift-server")
+    ap.add_argument("--model-dir"); ap.add_argument("--random-model", choices=["tiny", "4b", "27b"])
+    ap.add_argument("--preset", default=None); ap.add_argument("--host", default="127.0.0.1")
+    ap.add_argument("--port", type=int, default=8000); ap.add_argument("--max-seq-len", type=int, default=32768)
+    ap.add_argument("--arena-gib", type=float, default=16); ap.add_argument("--device", default=None)
+    ap.add_argument("--kv-cache-dtype", default="bf16", choices=["bf16", "fp8_e4m3"])
+    ap.add_argument("--page-tokens", type=int, default=16); ap.add_argument("--max-concurrent-requests", type=int, default=4)
+    ap.add_argument("--kv-cache-capacity-tokens", type=int, default=0)
+    ap.add_argument("--prefix-cache-capacity-tokens", type=int, default=16384)
+    ap.add_argument("--prefix-cache-max-entries", type=int, default=8)
+    ap.add_argument("--default-max-output-tokens", type=int, default=4096)
+    ap.add_argument("--dflash2-model-dir"); ap.add_argument("--dflash2-drafts", type=int, default=7)
+    ap.add_argument("--model-name", default="phaseshift"); ap.add_argument("--verify-weights", type=int, default=0)
+    ap.add_argument("--startup-timeout", type=int, default=120)
+    return ap
+
+
+class EngineThread(threading.Thread):
+    """Owns the serving loop.  Commands in: ("submit", ticket, kwargs) / ("cancel", ticket).  Each ticket has
+    an out-queue receiving ("token", id) / ("done", info) / ("error", message)."""
+
+    def __init__(self, serving):
+        super().__init__(daemon=True)
+        self.srv = serving
+        self.cmd: "queue.Queue" = queue.Queue()
+        self.out: Dict[int, "queue.Queue"] = {}
+        self.rid_of: Dict[int, int] = {}
+        self.ticket_of: Dict[int, int] = {}
+        self._next = 1
+        self._lock = threading.Lock()
+        self.running = True
+        self.ready = threading.Event()
+
+    def new_ticket(self) -> int:
+        with self._lock:
+            t = self._next
+            self._next += 1
+            self.out[t] = queue.Queue()
+            return t
+
+    def run(self):
+        self.ready.set()
+        while self.running:
+            try:
+                while True:
+                    c = self.cmd.get(block=self.srv.idle(), timeout=0.05 if self.srv.idle() else None)
+                    self._handle(c)
+            except queue.Empty:
+                pass
+            if self.srv.idle():
+                continue
+            for e in self.srv.step():
+                t = self.ticket_of.get(e.request_id)
+                if t is None:
+                    continue
+                if e.kind == "token":
+                    self.out[t].put(("token", e.token_id))
+                else:
+                    self.out[t].put((e.kind, e.info))
+                    self.srv.batcher.retire(e.request_id)
+                    self.ticket_of.pop(e.request_id, None)
+                    self.rid_of.pop(t, None)
+
+    def _handle(self, c):
+        if c[0] == "submit":
+            _, t, kw = c
+            try:
+                rid = self.srv.submit(**kw)
+                self.rid_of[t] = rid
+                self.ticket_of[rid] = t
+            except Exception as e:
+                self.out[t].put(("error", {"message": str(e), "bad_request": True}))
+        elif c[0] == "cancel":
+            rid = self.rid_of.pop(c[1], None)
+            if rid is not None and self.srv.cancel(rid):
+                r = self.srv.request(rid)
+                self.out[c[1]].put(("done", {"generated_ids": r["generated"], "finish_reason": "cancelled",
+                                             "prompt_tokens": r["prompt_tokens"], "restored_tokens": r["restored_tokens"],
+                                             "prefill_tokens": r["prefill_tokens"], "cache_checkpoint_tokens": 0}))
+                self.ticket_of.pop(rid, None)
+        elif c[0] == "stop":
+            self.running = False
+
+
+def create_app(serving, tokenizer, model_name: str, default_max_output_tokens: int, stop_ids: List[int], max_seq_len: int):
+    if FastAPI is None:
+        raise RuntimeError("fastapi is required for phaseshift-server")
+    app = FastAPI(title="phaseshift-b200")
+    eng = EngineThread(serving)
+    eng.start()
+    app.state.engine_thread = eng
+
+    def bad(msg: str, code: int = 400):
+        return JSONResponse({"error": {"message": msg, "type": "invalid_request_error"}}, status_code=code)
+
+    def prepare(body: dict):
+        msgs = body.get("messages")
+        if not isinstance(msgs, list):
+            raise chat.RequestError("messages must be a list")
+        effort = body.get("reasoning_effort")
+        if effort not in (None, "none", "low", "medium", "high"):
+            raise chat.RequestError(f"unknown reasoning_effort {effort!r}")
+        reasoning = effort in ("low", "medium", "high")
+        tools, mode, forced = chat.validate_tools(body.get("tools"), body.get("tool_choice"))
+        cons = chat.response_format_constraint(body.get("response_format"))
+        if mode in ("required", "named"):
+            if cons:
+                raise chat.RequestError("response_format cannot be combined with a required tool call")
+            cons = {"structural_tag": chat.structural_tag_for_tools(tools, forced, True)}
+        elif mode == "auto" and tools and any(t["function"].get("strict") for t in tools):
+            cons = cons or {"structural_tag": chat.structural_tag_for_tools(tools, None, False)}
+        if cons and serving.constraints is None:
+            raise chat.RequestError("structured output was requested but this server has no grammar engine configured")
+        if "json_schema" in cons:      # the serving loop takes grammar / structural_tag; wrap the schema as a tag-less format
+            cons = {"structural_tag": json.dumps({"type": "structural_tag",
+                                                  "format": {"type": "json_schema", "json_schema": json.loads(cons["json_schema"])}})}
+        rp = chat.render_prompt(tokenizer, msgs, tools if mode != "none" else None, reasoning)
+        max_new = int(body.get("max_completion_tokens") or body.get("max_tokens") or default_max_output_tokens)
+        if len(rp.ids) + 1 > max_seq_len:
+            raise chat.RequestError(f"prompt of {len(rp.ids)} tokens exceeds the context window of {max_seq_len}")
+        max_new = max(1, min(max_new, max_seq_len - len(rp.ids)))
+        kw = dict(prompt=rp.ids, max_new_tokens=max_new, temperature=float(body.get("temperature") or 0.0),
+                  top_p=float(body.get("top_p") or 1.0), top_k=int(body.get("top_k") or 0), seed=int(body.get("seed") or 0),
+                  stop_tokens=stop_ids, checkpoint_position=rp.checkpoint_position, grammar=cons.get("grammar"),
+                  structural_tag=cons.get("structural_tag"))
+        return kw, reasoning, mode
+
+    def finish_reason(info, has_calls: bool) -> str:
+        if has_calls:
+            return "tool_calls"
+        return {"stop": "stop", "length": "length", "cancelled": "cancelled", "error": "error"}.get(info.get("finish_reason"), "stop")
+
+    @app.get("/health")
+    def health():
+        return {"status": "ok"}
+
+    @app.get("/v1/models")
+    def models():
+        return {"object": "list", "data": [{"id": model_name, "object": "model", "owned_by": "phaseshift-b200"}]}
+
+    async def wait_item(q: "queue.Queue", request: Request, ticket: int):
+        while True:
+            try:
+                return q.get_nowait()
+            except queue.Empty:
+                if await request.is_disconnected():
+                    eng.cmd.put(("cancel", ticket))
+                await asyncio.sleep(0.002)
+
+    @app.post("/v1/chat/completions")
+    async def chat_completions(request: Request):
+        try:
+            body = await request.json()
+            kw, reasoning, mode = prepare(body)
+        except chat.RequestError as e:
+            return bad(str(e))
+        except Exception as e:
+            return bad(f"malformed request: {e}")
+        t = eng.new_ticket()
+        eng.cmd.put(("submit", t, kw))
+        q = eng.out[t]
+        cid, created = "chatcmpl-" + uuid.uuid4().hex[:24], int(time.time())
+        if body.get("stream"):
+            async def gen():
+                ids: List[int] = []
+                sent = 0
+                yield "data: " + json.dumps({"id": cid, "object": "chat.completion.chunk", "created": created, "model": model_name,
+                                             "choices": [{"index": 0, "delta": {"role": "assistant"}, "finish_reason": None}]}) + "\n\n"
+                while True:
+                    kind, val = await wait_item(q, request, t)
+                    if kind == "token":
+                        ids.append(val)
+                        text = tokenizer.decode([i for i in ids if i not in stop_ids], skip_special_tokens=True)
+                        if text.endswith("�"):
+                            continue                     # incomplete UTF-8 sequence: wait for more bytes
+                        delta, sent = text[sent:], len(text)
+                        if delta:
+                            yield "data: " + json.dumps({"id": cid, "object": "chat.completion.chunk", "created": created,
+                                                         "model": model_name, "choices": [{"index": 0, "delta": {"content": delta},
+                                                                                           "finish_reason": None}]}) + "\n\n"
+                    else:
+                        if kind == "error":
+                            yield "data: " + json.dumps({"error": {"message": val.get("message", "error")}}) + "\n\n"
+                        else:
+                            text = tokenizer.decode([i for i in val["generated_ids"] if i not in stop_ids], skip_special_tokens=True)
+                            _, calls = chat.parse_tool_calls(text)
+                            yield "data: " + json.dumps({"id": cid, "object": "chat.completion.chunk", "created": created,
+                                                         "model": model_name,
+                                                         "choices": [{"index": 0, "delta": ({"tool_calls": calls} if calls else {}),
+                                                                      "finish_reason": finish_reason(val, bool(calls))}]}) + "\n\n"
+                        yield "data: [DONE]\n\n"
+                        eng.out.pop(t, None)
+                        return
+            return StreamingResponse(gen(), media_type="text/event-stream")
+        while True:
+            kind, val = await wait_item(q, request, t)
+            if kind == "token":
+                continue
+            eng.out.pop(t, None)
+            if kind == "error":
+                return bad(val.get("message", "error"), 400 if val.get("bad_request") else 500)
+            text = tokenizer.decode([i for i in val["generated_ids"] if i not in stop_ids], skip_special_tokens=True)
+            reasoning_text, answer = chat.split_reasoning(text, reasoning) if reasoning else ("", text)
+            answer, calls = chat.parse_tool_calls(answer) if mode != "none" else (answer, [])
+            msg = {"role": "assistant", "content": answer or None if calls else answer}
+            if calls:
+                msg["tool_calls"] = calls
+            if reasoning_text:
+                msg["reasoning_content"] = reasoning_text
+            return {"id": cid, "object": "chat.completion", "created": created, "model": model_name,
+                    "choices": [{"index": 0, "message": msg, "finish_reason": finish_reason(val, bool(calls))}],
+                    "usage": {"prompt_tokens": val["prompt_tokens"], "completion_tokens": len(val["generated_ids"]),
+                              "total_tokens": val["prompt_tokens"] + len(val["generated_ids"]),
+                              "prompt_tokens_details": {"cached_tokens": val.get("restored_tokens", 0)}}}
+
+    @app.post("/v1/responses")
+    async def responses(request: Request):
+        try:
+            body = await request.json()
+            inp = body.get("input")
+            msgs = [{"role": "user", "content": inp}] if isinstance(inp, str) else list(inp or [])
+            if body.get("instructions"):
+                msgs = [{"role": "system", "content": body["instructions"]}] + msgs
+            kw, reasoning, mode = prepare({"messages": msgs, "max_tokens": body.get("max_output_tokens"),
+                                           "temperature": body.get("temperature"), "top_p": body.get("top_p"),
+                                           "tools": body.get("tools"), "tool_choice": body.get("tool_choice")})
+        except chat.RequestError as e:
+            return bad(str(e))
+        except Exception as e:
+            return bad(f"malformed request: {e}")
+        t = eng.new_ticket()
+        eng.cmd.put(("submit", t, kw))
+        while True:
+            kind, val = await wait_item(eng.out[t], request, t)
+            if kind == "token":
+                continue
+            eng.out.pop(t, None)
+            if kind == "error":
+                return bad(val.get("message", "error"), 400 if val.get("bad_request") else 500)
+            text = tokenizer.decode([i for i in val["generated_ids"] if i not in stop_ids], skip_special_tokens=True)
+            return {"id": "resp_" + uuid.uuid4().hex[:24], "object": "response", "created_at": int(time.time()), "model": model_name,
+                    "status": "completed" if val["finish_reason"] in ("stop", "length") else val["finish_reason"],
+                    "output": [{"type": "message", "role": "assistant", "content": [{"type": "output_text", "text": text}]}],
+                    "usage": {"input_tokens": val["prompt_tokens"], "output_tokens": len(val["generated_ids"])}}
+
+    return app
+
+
+def load_tokenizer(model_dir: Optional[str], vocab_size: int):
+    if model_dir:
+        import os
+        if any(os.path.exists(os.path.join(model_dir, f)) for f in ("tokenizer.json", "tokenizer_config.json")):
+            from transformers import AutoTokenizer
+            return AutoTokenizer.from_pretrained(model_dir)
+    return chat.ByteTokenizer(vocab_size)
+
+
+def build_runtime(a):
+    from .compute import ComputeRuntime
+    ns = argparse.Namespace(model_dir=a.model_dir, random_model=a.random_model, preset=a.preset, device=a.device,
+                            max_seq_len=a.max_seq_len, page_tokens=a.page_tokens,
+                            max_concurrent_requests=a.max_concurrent_requests,
+                            kv_cache_capacity_tokens=a.kv_cache_capacity_tokens or (a.max_concurrent_requests + 1) * (a.max_seq_len + 1),
+                            kv_cache_dtype=a.kv_cache_dtype, prefix_cache_capacity_tokens=a.prefix_cache_capacity_tokens,
+                            prefix_cache_max_entries=a.prefix_cache_max_entries, constraint_tokenizer_info=None,
+                            verify_weights=a.verify_weights, dflash2_model_dir=None, dflash2_drafts=a.dflash2_drafts,
+                            dflash2_ngram_tail=0, dflash2_ngram_n=0, max_scheduled_tokens=2048)
+    rt = ComputeRuntime(ns)
+    tok = load_tokenizer(a.model_dir, rt.cfg.vocab_size)
+    try:
+        from ..runtime.constraints import TokenConstraintCompiler
+        if isinstance(tok, chat.ByteTokenizer):
+            comp = TokenConstraintCompiler(tok.vocab_strings()[:rt.cfg.vocab_size], rt.cfg.vocab_size, [tok.eos_token_id], vocab_type="raw")
+        else:
+            comp = TokenConstraintCompiler.from_tokenizer(tok, rt.cfg.vocab_size, rt.cfg.eos_token_ids)
+        rt.serving.constraints = comp
+    except Exception as e:      # fail closed: structured requests will be rejected with 400
+        print(f"[server] grammar engine unavailable: {e}", file=sys.stderr)
+    stop = list(rt.cfg.eos_token_ids) or [getattr(tok, "eos_token_id", 2)]
+    return rt, tok, stop
+
+
+def main(argv=None) -> int:
+    a = build_parser().parse_args(argv)
+    if not a.model_dir and not a.random_model:
+        print("phaseshift-server: --model-dir is required", file=sys.stderr)
+        return 2
+    import uvicorn
+    rt, tok, stop = build_runtime(a)
+    app = create_app(rt.serving, tok, a.model_name, a.default_max_output_tokens, stop, a.max_seq_len)
+    print(f"phaseshift-server: model={a.model_name} ctx={a.max_seq_len} concurrency={a.max_concurrent_requests} "
+          f"prefix_cache={a.prefix_cache_capacity_tokens}x{a.prefix_cache_max_entries} http://{a.host}:{a.port}", file=sys.stderr)
+    uvicorn.run(app, host=a.host, port=a.port, log_level="warning")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
