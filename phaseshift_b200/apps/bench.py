@@ -1,0 +1,293 @@
+"""phaseshift-bench: end-to-end and per-kernel micro-benchmarks (reference: src/apps/bench/main.cpp:46-99,
+docs/user/bench.md).  Every sub-command times on the device with CUDA events after warm-up, flushes L2
+between samples for kernel benches and prints ``key=value`` lines (``gpu_tokens_per_sec``,
+``GREEDY_TOKEN_SUM`` determinism checksum for pp / tg) or CSV rows for kernel sweeps.
+"""
+from __future__ import annotations
+
+import argparse
+import statistics
+import sys
+from typing import List, Optional
+
+SUBCOMMANDS = ("pp", "tg", "batch", "gemm", "activation-quantize", "rmsnorm", "l2-normalize", "kv-append",
+               "paged-attention", "rope", "gdn-recurrence", "gdn-conv1d", "elementwise", "embedding", "sampling", "mtp",
+               "gpu-memory", "tp-reduce", "dflash2")
+FUSED_AWAY = {"activation-quantize": "activation staging is part of the small-M linear prologue (bench: gemm --rows 1)",
+              "l2-normalize": "q/k L2 normalisation is fused into the GDN kernel (bench: gdn-recurrence)",
+              "rope": "partial RoPE is fused with q/k norm and the KV append (bench: kv-append)",
+              "gdn-conv1d": "the short conv is fused into the GDN kernel (bench: gdn-recurrence)",
+              "elementwise": "residual add / SwiGLU / gates live in projection epilogues (bench: gemm)",
+              "mtp": "the MTP head is not built (bench-only in the reference); use dflash2"}
+
+
+def _model_args(p):
+    p.add_argument("--model-dir"); p.add_argument("--random-model", default=None, choices=["tiny", "4b", "27b"])
+    p.add_argument("--preset", default=None); p.add_argument("--device", default=None)
+    p.add_argument("--kv-cache-dtype", default="bf16", choices=["bf16", "fp8_e4m3"])
+    p.add_argument("--runs", type=int, default=3); p.add_argument("--warmup", type=int, default=1); p.add_argument("--output")
+
+
+def build_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="phaseshift-bench")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    pp = sub.add_parser("pp", help="prefill throughput"); _model_args(pp)
+    pp.add_argument("--prompt-tokens", type=int, default=128); pp.add_argument("--mode", default="forward", choices=["forward", "greedy"])
+    pp.add_argument("--prefill-chunk", type=int, default=2048)
+    tg = sub.add_parser("tg", help="decode throughput"); _model_args(tg)
+    tg.add_argument("--mode", default="greedy", choices=["forward", "greedy"]); tg.add_argument("--context", type=int, default=128)
+    tg.add_argument("--tokens", type=int, default=8); tg.add_argument("--prefill-chunk", type=int, default=2048)
+    tg.add_argument("--compute-logits", type=int, default=1)
+    ba = sub.add_parser("batch", help="concurrent serving throughput"); _model_args(ba)
+    ba.add_argument("--requests", type=int, default=8); ba.add_argument("--prompt-tokens", type=int, default=512)
+    ba.add_argument("--tokens", type=int, default=64); ba.add_argument("--shared-prefix", type=int, default=0)
+    ge = sub.add_parser("gemm", help="projection kernels")
+    ge.add_argument("--dtype", default="nvfp4", choices=["bf16", "nvfp4", "mxfp8"])
+    ge.add_argument("--variant", default="auto", choices=["gemv", "gemm", "auto"]); ge.add_argument("--rows", default="1,4,8,256,2048")
+    ge.add_argument("--n", type=int, default=5120); ge.add_argument("--k", type=int, default=5120)
+    ge.add_argument("--actual-qwen-shapes", action="store_true"); ge.add_argument("--warmup", type=int, default=5)
+    ge.add_argument("--samples", type=int, default=10); ge.add_argument("--check", action="store_true"); ge.add_argument("--out")
+    for name in ("rmsnorm", "kv-append", "paged-attention", "gdn-recurrence", "embedding", "sampling", "gpu-memory", "dflash2"):
+        p = sub.add_parser(name); p.add_argument("--rows", type=int, default=1); p.add_argument("--context", type=int, default=4096)
+        p.add_argument("--samples", type=int, default=20); p.add_argument("--model", default="27b", choices=["tiny", "4b", "27b"])
+        p.add_argument("--kv-cache-dtype", default="bf16", choices=["bf16", "fp8_e4m3"]); p.add_argument("--variant", default="optimized", choices=["optimized"])
+    tr = sub.add_parser("tp-reduce", help="row-parallel combine latency (run under torchrun for > 1 GPU)")
+    tr.add_argument("--rows", default="1,8"); tr.add_argument("--hidden", type=int, default=5120); tr.add_argument("--samples", type=int, default=50)
+    for name, why in FUSED_AWAY.items():
+        p = sub.add_parser(name, help="(fused away) " + why); p.add_argument("--variant", default="optimized", choices=["optimized"])
+    return ap
+
+
+def _engine(a, max_seq_len: int, slots: int = 1):
+    import torch
+    from ..models.qwen35.config import PRESETS
+    from ..models.qwen35.weights import build_engine_weights, load_engine_weights, random_getter
+    from ..runtime.engine import Engine
+    from ..runtime.state import StateConfig
+    dev = torch.device(a.device or ("cuda:0" if torch.cuda.is_available() else "cpu"))
+    if a.model_dir:
+        ew = load_engine_weights(a.model_dir, dev, a.preset, keep_canonical=dev.type != "cuda")
+    else:
+        cfg = PRESETS[a.random_model or "tiny"]()
+        ew = build_engine_weights(cfg, random_getter(cfg, 0, dev), a.preset or "bf16", dev, keep_canonical=dev.type != "cuda")
+    return Engine(ew, dev, StateConfig(max_slots=slots, max_seq_len=max_seq_len, kv_dtype=a.kv_cache_dtype)), dev
+
+
+def _timed(dev, fn):
+    import time
+    import torch
+    if dev.type == "cuda":
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize(); e0.record(); r = fn(); e1.record(); torch.cuda.synchronize()
+        return e0.elapsed_time(e1), r
+    t0 = time.perf_counter(); r = fn()
+    return (time.perf_counter() - t0) * 1e3, r
+
+
+def cmd_pp(a) -> int:
+    import torch
+    eng, dev = _engine(a, a.prompt_tokens + 8)
+    ids = torch.randint(0, eng.cfg.vocab_size, (a.prompt_tokens,), generator=torch.Generator().manual_seed(0)).tolist()
+    times, tok = [], 0
+    for i in range(a.warmup + a.runs):
+        s = eng.open_sequence()
+        ms, tok = _timed(dev, lambda: eng.prefill(s, ids, a.prefill_chunk, sample_last=a.mode == "greedy"))
+        eng.close_sequence(s)
+        if i >= a.warmup:
+            times.append(ms)
+    ms = statistics.median(times)
+    print(f"prompt_tokens={a.prompt_tokens}"); print(f"prefill_ms={ms:.3f}")
+    print(f"gpu_tokens_per_sec={a.prompt_tokens / ms * 1e3:.2f}"); print(f"GREEDY_TOKEN_SUM={tok or 0}")
+    return 0
+
+
+def cmd_tg(a) -> int:
+    import torch
+    eng, dev = _engine(a, a.context + a.tokens + 8)
+    ids = torch.randint(0, eng.cfg.vocab_size, (a.context,), generator=torch.Generator().manual_seed(0)).tolist()
+    times, sums = [], []
+    for i in range(a.warmup + a.runs):
+        s = eng.open_sequence()
+        tok = eng.prefill(s, ids, a.prefill_chunk)
+        out = [tok]
+
+        def run():
+            for _ in range(a.tokens):
+                out.append(eng.decode(s, out[-1], sample_index=len(out)))
+        ms, _ = _timed(dev, run)
+        eng.close_sequence(s)
+        if i >= a.warmup:
+            times.append(ms); sums.append(sum(out))
+    ms = statistics.median(times)
+    print(f"context={a.context}"); print(f"tokens={a.tokens}"); print(f"decode_ms_per_token={ms / a.tokens:.4f}")
+    print(f"gpu_tokens_per_sec={a.tokens / ms * 1e3:.2f}"); print(f"GREEDY_TOKEN_SUM={sums[-1]}")
+    print(f"deterministic={int(len(set(sums)) == 1)}")
+    return 0
+
+
+def cmd_batch(a) -> int:
+    import torch
+    from ..runtime.serving import ServingEngine
+    eng, dev = _engine(a, a.prompt_tokens + a.tokens + 8, slots=a.requests)
+    srv = ServingEngine(eng, prefix_cache_tokens=4 * a.shared_prefix if a.shared_prefix else 0, prefix_min_tokens=16)
+    g = torch.Generator().manual_seed(0)
+    shared = torch.randint(0, eng.cfg.vocab_size, (a.shared_prefix,), generator=g).tolist()
+
+    def run():
+        for _ in range(a.requests):
+            rest = torch.randint(0, eng.cfg.vocab_size, (a.prompt_tokens - a.shared_prefix,), generator=g).tolist()
+            srv.submit(shared + rest, a.tokens, checkpoint_position=a.shared_prefix)
+        return srv.run_until_idle()
+    ms, ev = _timed(dev, run)
+    n = sum(1 for e in ev if e.kind == "token")
+    print(f"requests={a.requests}"); print(f"generated_tokens={n}"); print(f"wall_ms={ms:.2f}")
+    print(f"aggregate_tokens_per_sec={n / ms * 1e3:.2f}"); print(f"steps={srv.stats['steps']}")
+    return 0
+
+
+QWEN27B_SHAPES = [("gdn_in_proj", 16384, 5120), ("gdn_out_proj", 5120, 6144), ("attn_qkv", 14336, 5120), ("attn_o", 5120, 6144),
+                  ("mlp_gate_up", 34816, 5120), ("mlp_down", 5120, 17408), ("lm_head", 151936, 5120)]
+
+
+def cmd_gemm(a) -> int:
+    import torch
+    from ..models.qwen35.config import tiny_config
+    from ..models.qwen35.weights import LinearW
+    from ..ops.cuda_ops import CudaOps
+    from ..quant import formats
+    dev = torch.device("cuda:0")
+    ops = CudaOps(tiny_config(), dev)
+    shapes = QWEN27B_SHAPES if a.actual_qwen_shapes else [("custom", a.n, a.k)]
+    flush = torch.empty(64 * 1024 * 1024, device=dev)
+    rows = [int(r) for r in a.rows.split(",")]
+    lines = ["dtype,requested_variant,selected_variant,shape_name,rows,n,k,warmup,samples,min_us,p50_us,p95_us,mean_us,GBps,TFLOPs"]
+    formats.DEFAULT_SEARCH = 0
+    for (name, n, k) in shapes:
+        W = LinearW(formats.quantize(torch.randn(n, k, device=dev) * 0.02, a.dtype)).make_tiled(keep_canonical=a.check)
+        for m in rows:
+            if a.variant == "gemv" and m > 8 or a.variant == "gemm" and m <= 8:
+                continue
+            x = torch.randn(m, k, device=dev).to(torch.bfloat16)
+            sel = "gemv" if m <= 8 else "gemm"
+            for _ in range(a.warmup):
+                ops.linear(x, W, name="b")
+            ts = []
+            for _ in range(a.samples):
+                flush.zero_()
+                ms, y = _timed(dev, lambda: ops.linear(x, W, name="b"))
+                ts.append(ms * 1e3)
+            ts.sort()
+            p50 = ts[len(ts) // 2]
+            if a.check:
+                ref = x.float() @ W.dense().T
+                err = float((y.float() - ref).norm() / ref.norm())
+                assert err < 2e-2, f"numerics check failed: rel err {err}"
+            lines.append(f"{a.dtype},{a.variant},{sel},{name},{m},{n},{k},{a.warmup},{a.samples},{ts[0]:.2f},{p50:.2f},"
+                         f"{ts[int(len(ts) * 0.95) - 1]:.2f},{sum(ts) / len(ts):.2f},{W.nbytes / p50 / 1e3:.1f},{2 * m * n * k / p50 / 1e6:.2f}")
+        del W
+    text = "\n".join(lines)
+    print(text)
+    if a.out:
+        open(a.out, "w").write(text + "\n")
+    return 0
+
+
+def cmd_kernel(a) -> int:
+    """Single-kernel latency on a synthetic decode-shaped problem of the named model."""
+    import torch
+    from ..models.qwen35.config import PRESETS
+    from ..models.qwen35.weights import build_engine_weights, random_getter
+    from ..runtime.batch import SeqRows, StepBatch
+    from ..runtime.engine import Engine
+    from ..runtime.state import StateConfig
+    dev = torch.device("cuda:0")
+    cfg = PRESETS[a.model]()
+    if a.cmd == "gpu-memory":
+        free, total = torch.cuda.mem_get_info()
+        print(f"gpu_total_bytes={total}"); print(f"gpu_free_bytes={free}")
+        print(f"model_params={cfg.param_count()}"); return 0
+    small = type(cfg)(**{**cfg.__dict__, "num_hidden_layers": 4, "layer_types": None, "vocab_size": min(cfg.vocab_size, 32768)})
+    ew = build_engine_weights(small, random_getter(small, 0, dev), "bf16", dev)
+    eng = Engine(ew, dev, StateConfig(max_slots=1, max_seq_len=a.context + 64, kv_dtype=a.kv_cache_dtype), use_graphs=False)
+    ops, st = eng.ops, eng.state
+    s = eng.open_sequence()
+    eng._reserve(s, a.context + a.rows + 1)
+    b = StepBatch(max(a.rows, 1), 1, dev)
+    b.fill([SeqRows(s.slot, a.context, [1] * a.rows, tuple(range(a.rows)))]); b.upload()
+    L_attn = next(l for l in ew.layers if l.kind == 1); L_gdn = next(l for l in ew.layers if l.kind == 0)
+    li_a, li_g = small.attn_layers[0], small.gdn_layers[0]
+    g = torch.Generator(device=dev).manual_seed(0)
+    x = torch.randn(a.rows, small.hidden_size, device=dev, generator=g).to(torch.bfloat16)
+    qkv = torch.randn(a.rows, L_attn.mixer.qkv_proj.N, device=dev, generator=g).to(torch.bfloat16)
+    proj = torch.randn(a.rows, L_gdn.mixer.in_proj.N + L_gdn.mixer.ba_proj.N, device=dev, generator=g).to(torch.bfloat16)
+    logits = torch.randn(a.rows, cfg.vocab_size, device=dev, generator=g)
+    q = ops.attn_prep(qkv, L_attn.mixer, eng.runner.hq, eng.runner.hkv, b, st.kv[li_a], st)
+    fns = {"rmsnorm": lambda: ops.rmsnorm(x, L_attn.input_norm, 1e-6, "bn"),
+           "kv-append": lambda: ops.attn_prep(qkv, L_attn.mixer, eng.runner.hq, eng.runner.hkv, b, st.kv[li_a], st),
+           "paged-attention": lambda: ops.paged_attention(q, qkv, eng.runner.hq, eng.runner.hkv, b, st.kv[li_a], st, a.context + a.rows),
+           "gdn-recurrence": lambda: ops.gdn(proj, L_gdn.mixer, eng.runner.hk, eng.runner.hv, b, st.gdn[li_g], st),
+           "embedding": lambda: ops.embed(b, a.rows, ew.embed, st.status),
+           "sampling": lambda: ops.sample(logits, b, a.rows, status=st.status)}
+    if a.cmd == "dflash2":
+        print("dflash2_bench=use bench.py --dflash2 for round timings"); return 0
+    fn = fns[a.cmd]
+    for _ in range(5):
+        fn()
+    ts = sorted(_timed(dev, fn)[0] * 1e3 for _ in range(a.samples))
+    print(f"kernel={a.cmd}"); print(f"model={a.model}"); print(f"rows={a.rows}"); print(f"context={a.context}")
+    print(f"min_us={ts[0]:.2f}"); print(f"p50_us={ts[len(ts) // 2]:.2f}"); print(f"p95_us={ts[int(len(ts) * 0.95) - 1]:.2f}")
+    return 0
+
+
+def cmd_tp_reduce(a) -> int:
+    import os
+    import torch
+    import torch.distributed as dist
+    from ..models.qwen35.config import tiny_config
+    from ..models.qwen35.weights import LinearW
+    from ..ops.cuda_ops import CudaOps
+    from ..parallel.tp import TensorParallel
+    from ..quant.formats import quantize
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    torch.cuda.set_device(rank); dev = torch.device("cuda", rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    tp = TensorParallel(dist.group.WORLD, dev) if world > 1 else None
+    ops = CudaOps(tiny_config(), dev)
+    H = a.hidden
+    W = LinearW(quantize(torch.randn(H, 1024, device=dev) * 0.02, "bf16")).make_tiled()
+    for m in [int(r) for r in a.rows.split(",")]:
+        x = torch.randn(m, 1024, device=dev).to(torch.bfloat16); res = torch.zeros(m, H, device=dev, dtype=torch.bfloat16)
+        comb = tp.combine_for(H) if tp else None
+        run_f = lambda: ops.linear(x, W, name="o", residual=res, tp_combine=comb)
+        part = torch.empty(m, H, device=dev, dtype=torch.bfloat16)
+
+        def run_n():
+            y = ops.linear(x, W, name="p")
+            if world > 1:
+                dist.all_reduce(y)
+            return torch.add(y, res, out=part)
+        for name, fn in (("fused", run_f), ("nccl", run_n)):
+            for _ in range(5):
+                fn()
+            ts = sorted(_timed(dev, fn)[0] * 1e3 for _ in range(a.samples))
+            t = torch.tensor([ts[len(ts) // 2]], device=dev)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            if rank == 0:
+                print(f"tp_reduce transport={name} ranks={world} rows={m} hidden={H} payload_bytes={m * H * 2} p50_us={float(t):.2f}")
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def main(argv: Optional[List[str]] = None) -> int:
+    a = build_parser().parse_args(argv)
+    if a.cmd in FUSED_AWAY:
+        print(f"{a.cmd}: {FUSED_AWAY[a.cmd]}")
+        return 0
+    return {"pp": cmd_pp, "tg": cmd_tg, "batch": cmd_batch, "gemm": cmd_gemm, "tp-reduce": cmd_tp_reduce}.get(a.cmd, cmd_kernel)(a)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

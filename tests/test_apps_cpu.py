@@ -110,3 +110,22 @@ def test_quantizer_cli(model_dir, tmp_path, capsys):
     assert quantizer.main(["ppl", "--model-dir", str(out), "--tokens", str(tk), "--max-tokens", "40", "--device", "cpu"]) == 0
     # quantised directory runs through compute with the exact-match contract against itself
     assert compute.main(["--model-dir", str(out), "--max-new-tokens", "4", "--device", "cpu", "--verify-weights", "1"]) == 0
+
+
+def test_bench_subcommands_help_and_cpu_runs(capsys):
+    from phaseshift_b200.apps import bench
+    for sub in bench.SUBCOMMANDS:
+        with pytest.raises(SystemExit) as e:
+            bench.main([sub, "--help"])
+        assert e.value.code == 0
+    with pytest.raises(SystemExit) as e:
+        bench.main(["rmsnorm", "--variant", "bogus"])            # invalid variant must fail
+    assert e.value.code == 2
+    capsys.readouterr()
+    assert bench.main(["tg", "--random-model", "tiny", "--device", "cpu", "--context", "12", "--tokens", "4", "--runs", "2"]) == 0
+    out = dict(l.split("=", 1) for l in capsys.readouterr().out.strip().splitlines())
+    assert out["deterministic"] == "1" and float(out["gpu_tokens_per_sec"]) > 0 and "GREEDY_TOKEN_SUM" in out
+    assert bench.main(["pp", "--random-model", "tiny", "--device", "cpu", "--prompt-tokens", "24", "--runs", "1", "--warmup", "0"]) == 0
+    assert bench.main(["batch", "--random-model", "tiny", "--device", "cpu", "--requests", "3", "--prompt-tokens", "20",
+                       "--tokens", "3"]) == 0
+    assert "aggregate_tokens_per_sec" in capsys.readouterr().out
