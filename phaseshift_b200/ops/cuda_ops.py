@@ -31,6 +31,7 @@ SMALL_M_MAX = 8
 class CudaOps:
     act_dtype = torch.bfloat16
     name = "cuda"
+    GDN_CHUNKED_MIN_ROWS = 16      # steps with more rows than this use the chunked GDN kernels
 
     def __init__(self, cfg: Qwen35Config, device, attn_split_tokens: int = 128, attn_max_splits: int = 0,
                  max_seq_len: int = 4096):
@@ -174,6 +175,19 @@ class CudaOps:
         rows = proj.shape[0]
         Dk, Dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
         out = self.buf("gdn_o", rows, hv * Dv)
+        if rows > self.GDN_CHUNKED_MIN_ROWS and log is None and not to_alt and not self.exact_rows and xn is None:
+            # prefill-sized step: chunked form (fp32 products, one forward substitution per 64 rows)
+            f32 = torch.float32
+            q = self.buf("gdn_q", rows, hv * Dk, f32); k = self.buf("gdn_k", rows, hv * Dk, f32)
+            v = self.buf("gdn_v", rows, hv * Dv, f32); o = self.buf("gdn_of", rows, hv * Dv, f32)
+            beta = self.buf("gdn_beta", rows, hv, f32); g = self.buf("gdn_g", rows, hv, f32)
+            _lib.call("ps_gdn_chunked", ptr(proj), c_int(proj.stride(0)), c_int(rows), c_int(hk), c_int(hv), c_int(Dk),
+                      c_int(Dv), ptr(gw.conv_w), ptr(gw.A_log), ptr(gw.dt_bias), ptr(gw.norm_w),
+                      c_float(cfg.rms_norm_eps), ptr(gs.conv), c_int(st.sc.conv_ring), ptr(gs.rec), ptr(b.seq_desc),
+                      c_int(b.max_seqs if b.graph_static else b.n_seqs), ptr(b.row_slot), ptr(b.row_pos), ptr(q), ptr(k),
+                      ptr(v), ptr(beta), ptr(g), ptr(o), ptr(out))
+            self.launches += 4
+            return out
         state_out = gs.rec_alt if to_alt else gs.rec
         lk = ld = ldd = None
         if log is not None:

@@ -179,6 +179,48 @@ def test_gdn_rows_and_decode(geom):
     assert _rel_err(st_c.gdn[li].rec[1], st_r.gdn[li].rec[1]) < 1e-3
 
 
+def test_gdn_chunked_matches_reference_and_row_kernel():
+    """Prefill-sized steps take the chunked kernels: two sequences, several chunks with a ragged tail, a
+    non-zero incoming state and a second step that continues from the stored state and conv history."""
+    cfg = Qwen35Config(vocab_size=1024, hidden_size=512, intermediate_size=512, num_hidden_layers=4,
+                       linear_num_key_heads=2, linear_num_value_heads=6)
+    cu, ref = _ops(cfg)
+    sc = StateConfig(max_slots=3, max_seq_len=512, page_tokens=16, conv_ring=8, spec_rows=8)
+    st_c = ModelState(cfg, sc, _dev(), torch.bfloat16)
+    st_w = ModelState(cfg, sc, _dev(), torch.bfloat16)
+    st_r = ModelState(cfg, sc, _dev(), torch.float32)
+    hf = random_hf_weights(cfg, seed=4, device="cuda")
+    ew = build_engine_weights(cfg, lambda n: hf[n], "bf16", "cuda")
+    li = cfg.gdn_layers[0]
+    gw = ew.layers[li].mixer
+    Hk, Hv = cfg.linear_num_key_heads, cfg.linear_num_value_heads
+    width = gw.in_proj.N + gw.ba_proj.N
+    g = torch.Generator(device="cuda").manual_seed(11)
+    init = torch.randn(st_c.gdn[li].rec.shape, device="cuda", generator=g) * 0.1
+    for st in (st_c, st_w, st_r):
+        st.gdn[li].rec.copy_(init)
+    pos = {2: 0, 0: 0}
+    for (n2, n0) in ((150, 70), (64, 129)):
+        proj = (torch.randn(n2 + n0, width, device="cuda", generator=g) * 0.7).to(torch.bfloat16)
+        b = StepBatch(512, 2, _dev())
+        b.fill([SeqRows(2, pos[2], [0] * n2, ()), SeqRows(0, pos[0], [0] * n0, ())]); b.upload()
+        pos[2] += n2; pos[0] += n0
+        o_c = cu.gdn(proj, gw, Hk, Hv, b, st_c.gdn[li], st_c)
+        cu.GDN_CHUNKED_MIN_ROWS = 1 << 30            # row-sequential kernel on the same inputs
+        try:
+            o_w = cu.gdn(proj, gw, Hk, Hv, b, st_w.gdn[li], st_w).clone()
+        finally:
+            del cu.GDN_CHUNKED_MIN_ROWS
+        o_r = ref.gdn(proj.float(), gw, Hk, Hv, b, st_r.gdn[li], st_r)
+        torch.cuda.synchronize()
+        assert _rel_err(o_c, o_r) < 2e-2
+        assert _rel_err(o_c.float(), o_w.float()) < 1e-2
+        for slot in (0, 2):
+            assert _rel_err(st_c.gdn[li].rec[slot], st_r.gdn[li].rec[slot]) < 1e-3
+        assert torch.equal(st_c.gdn[li].conv, st_w.gdn[li].conv)
+    assert torch.equal(st_c.gdn[li].rec[1], init[1])      # untouched slot
+
+
 def test_gdn_multirow_bit_equals_single_rows_and_replay():
     """Verify-rows launch == sequential decodes bit for bit; log replay of an accepted prefix rebuilds
     exactly the state sequential decoding reaches."""
