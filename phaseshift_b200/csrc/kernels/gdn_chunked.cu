@@ -1,31 +1,41 @@
-// Gated DeltaNet, chunked (prefill) form: three launches per layer.
+// Gated DeltaNet, chunked (prefill) form: four launches per layer.
 //
-//   1. gdn_prepare : fully parallel over (row, value head): causal depthwise conv (kernel 4) + SiLU on the
-//      head's q/k/v channels, L2 normalisation (q also scaled by Dk^-0.5), beta = sigmoid(b),
-//      g = -exp(A_log) * softplus(a + dt_bias); writes per-head fp32 q, k, v, beta, g and the conv history.
-//   2. gdn_chunk_scan : one CTA per (sequence, value head, 32-column slice of Dv); walks the sequence in
-//      chunks of 64 rows.  With G_t the running sum of g inside the chunk and D_t = exp(G_t), the exact
-//      recurrence  S <- d_t S ; delta_t = beta_t (v_t - S^T k_t) ; S <- S + k_t delta_t^T ; o_t = S^T q_t
-//      is equivalent, per chunk with incoming state S0, to
-//          (I + A) Delta = B,   A_ts = beta_t (D_t/D_s) (k_t.k_s) for s < t,   B_t = beta_t (v_t - D_t S0^T k_t)
-//          o_t = D_t S0^T q_t + sum_{s<=t} (D_t/D_s) (q_t.k_s) delta_s
-//          S_C = D_C S0 + sum_s (D_C/D_s) k_s delta_s^T
-//      so the chunk costs a few small matrix products plus ONE forward substitution in which every thread
-//      owns a column and runs the 64-step recurrence out of registers (no barriers inside).  All decay
-//      ratios have s <= t and g <= 0, so every exponential is <= 1.  State and all arithmetic are fp32.
-//   3. gdn_post : RMSNorm over the head's Dv outputs (direct weight) * SiLU(z) -> bf16.
+// With G_t the running sum of the log decays g inside a 64-row chunk, D_t = exp(G_t) and S0 the state
+// entering the chunk, the exact recurrence
+//     S <- d_t S ;  delta_t = beta_t (v_t - S^T k_t) ;  S <- S + k_t delta_t^T ;  o_t = S^T q_t
+// is equivalent to
+//     (I + A) Delta = B,  A_ts = beta_t (D_t/D_s)(k_t.k_s) for s < t,  B_t = beta_t (v_t - D_t S0^T k_t)
+//     o_t = D_t S0^T q_t + sum_{s<=t} (D_t/D_s)(q_t.k_s) delta_s ,   S_C = D_C S0 + sum_s (D_C/D_s) k_s delta_s^T
+// and, with T = (I + A)^-1 (unit lower triangular, independent of the state),
+//     Delta = U - W S0 ,   U = T diag(beta) V ,   W = T diag(beta D) K .
+// Everything that does not depend on S0 is computed for all chunks at once:
 //
+//   1. gdn_chunk_prep : one CTA per (chunk, value head): causal depthwise conv (kernel 4) + SiLU with the
+//      taps sliding through registers, L2 normalisation (q also scaled by Dk^-0.5), beta = sigmoid(b),
+//      g = -exp(A_log) softplus(a + dt_bias); then A, T by forward substitution on the identity (one
+//      thread per column, out of registers), W, U, and the decayed operands Qd = D q, Kd = (D_C/D_s) k,
+//      QKd_ts = (D_t/D_s)(q_t.k_s), written to scratch.
+//   2. gdn_history : stores the raw inputs of each sequence's last rows in the conv ring (a separate
+//      launch so no CTA reads history that another CTA of the same step is overwriting).
+//   3. gdn_chunk_scan : one CTA per (sequence, value head, 32-column slice of Dv) walks the chunks:
+//      Delta = U - W S0 ;  O = Qd S0 + QKd Delta ;  S = D_C S0 + Kd^T Delta.  Three small products per
+//      chunk, no serial solve on the critical path.
+//   4. gdn_post : RMSNorm over the head's Dv outputs (direct weight) * SiLU(z) -> bf16.
+//
+// All decay ratios have s <= t and g <= 0, so every exponential is <= 1.  State and arithmetic are fp32.
 // The reference's chunked kernel (src/phaseshift/models/qwen35/kernels/optimized/gdn/recurrence.hip:
 // 128-519) uses chunk 32, bf16 WMMA products (hi+lo split in "exact" mode) and a 32-step serial forward
-// substitution per column; here the products stay in fp32 on the CUDA cores, which at 2 M MAC per chunk
-// and slice is ~20x faster than the row-sequential kernel and well below the projections' time.
-// Decode and speculative verification keep using the row-sequential kernel (gdn_recurrent.cu), whose
-// per-row arithmetic is independent of the batch.
+// substitution per column inside the sequential walk.  Decode and speculative verification keep using
+// the row-sequential kernel (gdn_recurrent.cu), whose per-row arithmetic is independent of the batch.
 #include "ps_common.cuh"
 
 namespace ps {
 
 struct GdnSeqDesc2 { int row_start; int n_rows; int slot; int pos_start; };
+
+constexpr int kChunk = 64;
+constexpr int kSlice = 64;     // Dv columns per scan CTA
+constexpr int kTP = 68;        // pitch of T rows (floats), multiple of 4 for 16-byte broadcast loads
 
 struct GdnPrepArgs {
     const __nv_bfloat16* proj; int ld_proj;      // [rows, ld]: [q | k | v | z | b | a]
@@ -33,60 +43,222 @@ struct GdnPrepArgs {
     const __nv_bfloat16* conv_w; const float* A_log; const float* dt_bias;
     __nv_bfloat16* conv_state; int ring;
     const int* row_slot; const int* row_pos;
-    float* q; float* k; float* v; float* beta; float* g;             // [rows, Hv, Dk|Dv], [rows, Hv]
+    const GdnSeqDesc2* seqs; int n_seqs;
+    float* scratch;                              // per (chunk, head): W, Qd, Kd [64,Dk]; U [64,Dv]; QKd [64,64]
+    float* dc;                                   // per (chunk, head): D_C
 };
 
-// grid = (Hv, rows), block = 128 threads
-__global__ void __launch_bounds__(128) gdn_prepare_kernel(const GdnPrepArgs a) {
-    __shared__ float s_q[128], s_k[128], s_red[96];
-    const int h = blockIdx.x, row = blockIdx.y, t = threadIdx.x;
-    const int slot = a.row_slot[row];
-    if (slot < 0) return;
-    const int pos = a.row_pos[row];
-    // a tap comes from this step when the row j places up belongs to the same sequence, else from history
-    bool in_step[3];
+__host__ __device__ inline size_t chunk_scratch_floats(int Dk, int Dv) { return (size_t)kChunk * (3 * Dk + Dv + kChunk); }
+
+// Locate global chunk `gc` (chunks are numbered sequence by sequence): returns false when out of range.
+__device__ __forceinline__ bool find_chunk(const GdnSeqDesc2* seqs, int n_seqs, int gc, GdnSeqDesc2& sd, int& chunk) {
+    int base = 0;
+    for (int s = 0; s < n_seqs; ++s) {
+        const GdnSeqDesc2 d = seqs[s];
+        const int nc = d.n_rows > 0 && d.slot >= 0 ? (d.n_rows + kChunk - 1) / kChunk : 0;
+        if (gc < base + nc) { sd = d; chunk = gc - base; return true; }
+        base += nc;
+    }
+    return false;
+}
+
+// Rows 16 RB .. 16 RB + 15 of  out = T x  for one column: T is lower triangular, so the sum stops at
+// column 16 (RB + 1); T rows are read as 16-byte broadcasts.
+template <int RB>
+__device__ __forceinline__ void wu_rows(const float* sT, const float (&x)[kChunk], float* dst, int dp) {
 #pragma unroll
-    for (int j = 1; j <= 3; ++j) in_step[j - 1] = row - j >= 0 && a.row_slot[row - j] == slot && a.row_pos[row - j] == pos - j;
-    const int Dk = a.Dk, Dv = a.Dv, CH = 2 * Dk + Dv;
-    const int hk = h / (a.Hv / a.Hk);
-    const int q_off = hk * Dk, k_off = a.Hk * Dk + hk * Dk, v_off = 2 * a.Hk * Dk + h * Dv;
-    const int b_off = 2 * a.Hk * Dk + 2 * a.Hv * Dv + h, a_off = b_off + a.Hv;
-    const __nv_bfloat16* pr = a.proj + (size_t)row * a.ld_proj;
-    __nv_bfloat16* hist = a.conv_state + ((size_t)slot * a.Hv + h) * a.ring * CH;
-    float qq = 0.f, kk = 0.f;
-    for (int c = t; c < CH; c += 128) {
-        const int gc = c < Dk ? q_off + c : (c < 2 * Dk ? k_off + (c - Dk) : v_off + (c - 2 * Dk));
-        const uint2 wraw = *reinterpret_cast<const uint2*>(a.conv_w + (size_t)gc * 4);
-        const float2 w01 = bf16x2_bits_to_f32x2(wraw.x), w23 = bf16x2_bits_to_f32x2(wraw.y);
-        float taps[3];
+    for (int rr = 0; rr < 16; ++rr) {
+        const int r = RB * 16 + rr;
+        float s4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int j = 1; j <= 3; ++j) {
-            float v = 0.f;
-            if (pos - j >= 0) {
-                if (in_step[j - 1]) v = bf16_to_f32(a.proj[(size_t)(row - j) * a.ld_proj + gc]);
-                else v = bf16_to_f32(hist[(size_t)((pos - j) % a.ring) * CH + c]);
-            }
-            taps[j - 1] = v;
+        for (int s = 0; s < (RB + 1) * 16; s += 4) {
+            const float4 tv = *reinterpret_cast<const float4*>(sT + r * kTP + s);
+            s4[0] = fmaf(tv.x, x[s], s4[0]);
+            s4[1] = fmaf(tv.y, x[s + 1], s4[1]);
+            s4[2] = fmaf(tv.z, x[s + 2], s4[2]);
+            s4[3] = fmaf(tv.w, x[s + 3], s4[3]);
         }
-        float y = w01.x * taps[2];
-        y = fmaf(w01.y, taps[1], y);
-        y = fmaf(w23.x, taps[0], y);
-        y = fmaf(w23.y, bf16_to_f32(pr[gc]), y);
-        y = silu_f(y);
-        if (c < Dk) { s_q[c] = y; qq += y * y; }
-        else if (c < 2 * Dk) { s_k[c - Dk] = y; kk += y * y; }
-        else { a.v[((size_t)row * a.Hv + h) * Dv + (c - 2 * Dk)] = y; }
+        dst[(size_t)r * dp] = (s4[0] + s4[1]) + (s4[2] + s4[3]);
     }
-    float r2[2] = {qq, kk};
-    block_sum_n<2>(r2, s_red);
-    const float qn = rsqrtf(r2[0] + 1e-6f) * rsqrtf((float)Dk), kn = rsqrtf(r2[1] + 1e-6f);
-    for (int i = t; i < Dk; i += 128) {
-        a.q[((size_t)row * a.Hv + h) * Dk + i] = s_q[i] * qn;
-        a.k[((size_t)row * a.Hv + h) * Dk + i] = s_k[i] * kn;
+}
+
+__device__ __forceinline__ float dot4(const float4& a, const float4& b, float acc) {
+    acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc); acc = fmaf(a.z, b.z, acc); return fmaf(a.w, b.w, acc);
+}
+
+// grid = (max chunks, Hv), block = 256 threads
+template <int DK, int DV>
+__global__ void __launch_bounds__(256) gdn_chunk_prep_kernel(const GdnPrepArgs a) {
+    constexpr int CH = 2 * DK + DV, PK = DK + 4, PV = DV + 4, RAWR = kChunk + 3;
+    extern __shared__ __align__(16) float sm[];
+    float* sQ = sm;                        // [64][DK+4]
+    float* sK = sQ + kChunk * PK;          // [64][DK+4]
+    float* sV = sK + kChunk * PK;          // [64][DV+4]
+    float* sG = sV + kChunk * PV;          // [64]
+    float* sBeta = sG + kChunk;            // [64]
+    float* sU = sBeta + kChunk;            // union: raw bf16 input tile [67][CH], later A [64][65] and T [64][68]
+    __nv_bfloat16* sRaw = reinterpret_cast<__nv_bfloat16*>(sU);
+    float* sA = sU;
+    float* sT = sA + kChunk * 65;          // 64 * 65 floats keep the T rows 16-byte aligned
+
+    GdnSeqDesc2 sd; int chunk;
+    if (!find_chunk(a.seqs, a.n_seqs, blockIdx.x, sd, chunk)) return;
+    const int h = blockIdx.y, t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    const int r0 = chunk * kChunk, C = min(kChunk, sd.n_rows - r0);
+    const size_t row0 = (size_t)sd.row_start + r0;
+    const int pos0 = sd.pos_start + r0;
+    const int hk = h / (a.Hv / a.Hk);
+    const int q_off = hk * DK, k_off = a.Hk * DK + hk * DK, v_off = 2 * a.Hk * DK + h * DV;
+    const int b_off = 2 * a.Hk * DK + 2 * a.Hv * DV + h, a_off = b_off + a.Hv;
+    const __nv_bfloat16* hist = a.conv_state + ((size_t)sd.slot * a.Hv + h) * a.ring * CH;
+    float* scr = a.scratch + ((size_t)blockIdx.x * a.Hv + h) * chunk_scratch_floats(DK, DV);
+    float* gW = scr; float* gQd = gW + kChunk * DK; float* gKd = gQd + kChunk * DK;
+    float* gU = gKd + kChunk * DK; float* gQK = gU + kChunk * DV;
+
+    // ---- stage the raw inputs of rows -3 .. 63 (this head's q | k | v channels) with wide loads
+    {
+        const bool vec = (a.ld_proj % 8) == 0;
+        constexpr int PPR = CH / 8;
+        for (int p = t; p < RAWR * PPR; p += 256) {
+            const int rr = p / PPR - 3, c = (p % PPR) * 8;
+            const int gc = c < DK ? q_off + c : (c < 2 * DK ? k_off + (c - DK) : v_off + (c - 2 * DK));
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (rr < C && pos0 + rr >= 0) {
+                if (r0 + rr >= 0) {
+                    const __nv_bfloat16* src = a.proj + (size_t)((long long)row0 + rr) * a.ld_proj + gc;
+                    if (vec) v = __ldg(reinterpret_cast<const uint4*>(src));
+                    else {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) w[j] = (uint32_t)__bfloat16_as_ushort(src[2 * j]) | ((uint32_t)__bfloat16_as_ushort(src[2 * j + 1]) << 16);
+                        v = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                } else {
+                    v = *reinterpret_cast<const uint4*>(hist + (size_t)((pos0 + rr) % a.ring) * CH + c);
+                }
+            }
+            *reinterpret_cast<uint4*>(sRaw + (rr + 3) * CH + c) = v;
+        }
     }
-    if (t == 0) {
-        a.beta[(size_t)row * a.Hv + h] = sigmoid_f(bf16_to_f32(pr[b_off]));
-        a.g[(size_t)row * a.Hv + h] = -__expf(a.A_log[h]) * softplus_f(bf16_to_f32(pr[a_off]) + a.dt_bias[h]);
+    // ---- beta and the running log decay (last warp, two 32-wide halves)
+    if (warp == 7) {
+        float g0 = 0.f, g1 = 0.f, b0 = 0.f, b1 = 0.f;
+        const float Aexp = -__expf(a.A_log[h]), dtb = a.dt_bias[h];
+        if (lane < C) {
+            const __nv_bfloat16* pr = a.proj + (row0 + lane) * a.ld_proj;
+            b0 = sigmoid_f(bf16_to_f32(pr[b_off])); g0 = Aexp * softplus_f(bf16_to_f32(pr[a_off]) + dtb);
+        }
+        if (lane + 32 < C) {
+            const __nv_bfloat16* pr = a.proj + (row0 + lane + 32) * a.ld_proj;
+            b1 = sigmoid_f(bf16_to_f32(pr[b_off])); g1 = Aexp * softplus_f(bf16_to_f32(pr[a_off]) + dtb);
+        }
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float n0 = __shfl_up_sync(0xffffffffu, g0, o), n1 = __shfl_up_sync(0xffffffffu, g1, o);
+            if (lane >= o) { g0 += n0; g1 += n1; }
+        }
+        const float tot0 = __shfl_sync(0xffffffffu, g0, 31);
+        sG[lane] = g0; sG[lane + 32] = g1 + tot0;
+        sBeta[lane] = b0; sBeta[lane + 32] = b1;
+    }
+    __syncthreads();
+    // ---- conv + SiLU: a thread owns a channel pair and slides its taps through registers
+    for (int cp = t; cp < CH / 2; cp += 256) {
+        const int c = 2 * cp;
+        const int gc = c < DK ? q_off + c : (c < 2 * DK ? k_off + (c - DK) : v_off + (c - 2 * DK));
+        const uint4 wraw = *reinterpret_cast<const uint4*>(a.conv_w + (size_t)gc * 4);     // two channels x four taps
+        const float2 wa01 = bf16x2_bits_to_f32x2(wraw.x), wa23 = bf16x2_bits_to_f32x2(wraw.y);
+        const float2 wb01 = bf16x2_bits_to_f32x2(wraw.z), wb23 = bf16x2_bits_to_f32x2(wraw.w);
+        const uint32_t* col = reinterpret_cast<const uint32_t*>(sRaw + c);
+        float2 x3 = bf16x2_bits_to_f32x2(col[0 * (CH / 2)]), x2 = bf16x2_bits_to_f32x2(col[1 * (CH / 2)]);
+        float2 x1 = bf16x2_bits_to_f32x2(col[2 * (CH / 2)]);
+        float* dst = c < DK ? sQ + c : (c < 2 * DK ? sK + (c - DK) : sV + (c - 2 * DK));
+        const int pitch = c < 2 * DK ? PK : PV;
+#pragma unroll 8
+        for (int r = 0; r < kChunk; ++r) {
+            const float2 x0 = bf16x2_bits_to_f32x2(col[(r + 3) * (CH / 2)]);
+            float ya = wa01.x * x3.x; ya = fmaf(wa01.y, x2.x, ya); ya = fmaf(wa23.x, x1.x, ya); ya = fmaf(wa23.y, x0.x, ya);
+            float yb = wb01.x * x3.y; yb = fmaf(wb01.y, x2.y, yb); yb = fmaf(wb23.x, x1.y, yb); yb = fmaf(wb23.y, x0.y, yb);
+            x3 = x2; x2 = x1; x1 = x0;
+            *reinterpret_cast<float2*>(dst + r * pitch) = make_float2(silu_f(ya), silu_f(yb));
+        }
+    }
+    __syncthreads();
+    // ---- L2 norms: warp w owns rows 8w .. 8w+7
+    for (int r = warp * 8; r < warp * 8 + 8; ++r) {
+        float qq = 0.f, kk = 0.f;
+        for (int d = lane; d < DK; d += 32) { const float qv = sQ[r * PK + d], kv = sK[r * PK + d]; qq += qv * qv; kk += kv * kv; }
+        qq = warp_sum(qq); kk = warp_sum(kk);
+        const float qn = rsqrtf(qq + 1e-6f) * rsqrtf((float)DK), kn = rsqrtf(kk + 1e-6f);
+        for (int d = lane; d < DK; d += 32) { sQ[r * PK + d] *= qn; sK[r * PK + d] *= kn; }
+    }
+    __syncthreads();
+    // ---- A (strictly lower) and QKd (lower incl. diagonal): rows (t/16) + 16 i, columns (t%16) + 16 j,
+    //      operands read four dims at a time
+    {
+        const int tr = t / 16, tc = t % 16;
+        float kk[4][4] = {}, qk[4][4] = {};
+        for (int d = 0; d < DK; d += 4) {
+            float4 kr[4], qr[4], kc[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                kr[i] = *reinterpret_cast<const float4*>(sK + (tr + 16 * i) * PK + d);
+                qr[i] = *reinterpret_cast<const float4*>(sQ + (tr + 16 * i) * PK + d);
+                kc[i] = *reinterpret_cast<const float4*>(sK + (tc + 16 * i) * PK + d);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) { kk[i][j] = dot4(kr[i], kc[j], kk[i][j]); qk[i][j] = dot4(qr[i], kc[j], qk[i][j]); }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int tt = tr + 16 * i, ss = tc + 16 * j;
+                const float dec = ss <= tt ? __expf(sG[tt] - sG[ss]) : 0.f;
+                sA[tt * 65 + ss] = ss < tt ? sBeta[tt] * dec * kk[i][j] : 0.f;
+                gQK[tt * kChunk + ss] = dec * qk[i][j];
+            }
+    }
+    __syncthreads();
+    // ---- T = (I + A)^-1: thread j < 64 solves column j by forward substitution out of registers
+    if (t < kChunk) {
+        float x[kChunk];
+#pragma unroll
+        for (int i = 0; i < kChunk; ++i) {
+            float s4[4] = {i == t ? 1.f : 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int j = 0; j < i; ++j) s4[j & 3] = fmaf(-sA[i * 65 + j], x[j], s4[j & 3]);
+            x[i] = (s4[0] + s4[1]) + (s4[2] + s4[3]);
+        }
+#pragma unroll
+        for (int i = 0; i < kChunk; ++i) sT[i * kTP + t] = x[i];
+    } else {
+        // meanwhile the other warps write the decayed operands
+        const float GC = sG[kChunk - 1];
+        for (int i = t - kChunk; i < kChunk * DK / 4; i += 256 - kChunk) {
+            const int r = (i * 4) / DK, d = (i * 4) % DK;
+            const float eq = __expf(sG[r]), ek = __expf(GC - sG[r]);
+            const float4 q = *reinterpret_cast<const float4*>(sQ + r * PK + d), k = *reinterpret_cast<const float4*>(sK + r * PK + d);
+            reinterpret_cast<float4*>(gQd)[i] = make_float4(eq * q.x, eq * q.y, eq * q.z, eq * q.w);
+            reinterpret_cast<float4*>(gKd)[i] = make_float4(ek * k.x, ek * k.y, ek * k.z, ek * k.w);
+        }
+        if (t == kChunk) a.dc[(size_t)blockIdx.x * a.Hv + h] = __expf(GC);
+    }
+    __syncthreads();
+    // ---- W = T diag(beta D) K and U = T diag(beta) V: a thread owns one column, 64 inputs in registers
+    if (t < DK + DV) {
+        const bool isW = t < DK;
+        const int col = isW ? t : t - DK;
+        const float* src = isW ? sK + col : sV + col;
+        const int pitch = isW ? PK : PV;
+        float x[kChunk];
+#pragma unroll
+        for (int s = 0; s < kChunk; ++s) x[s] = src[s * pitch] * sBeta[s] * (isW ? __expf(sG[s]) : 1.f);
+        float* dst = isW ? gW + col : gU + col;
+        const int dp = isW ? DK : DV;
+        wu_rows<0>(sT, x, dst, dp); wu_rows<1>(sT, x, dst, dp); wu_rows<2>(sT, x, dst, dp); wu_rows<3>(sT, x, dst, dp);
     }
 }
 
@@ -112,165 +284,137 @@ __global__ void gdn_history_kernel(const GdnPrepArgs a, int rows) {
     }
 }
 
-constexpr int kChunk = 64;
-constexpr int kSlice = 32;     // Dv columns per CTA
-
 struct GdnScanArgs {
-    const float* q; const float* k; const float* v; const float* beta; const float* g;
-    int Hv, Dv;
+    const float* scratch; const float* dc;
+    int Hv, Dv, n_seqs;
     float* state;                 // [slots, Hv, Dk, Dv] fp32, updated in place
     const GdnSeqDesc2* seqs;
     float* o;                     // [rows, Hv, Dv] fp32
 };
 
-// grid = (Dv / 32, Hv, n_seqs), block = 256 threads.  DK = 128 or 64.
-template <int DK>
+__device__ __forceinline__ void fma8(float (&acc)[8], float w, const float4& s0, const float4& s1) {
+    acc[0] = fmaf(w, s0.x, acc[0]); acc[1] = fmaf(w, s0.y, acc[1]); acc[2] = fmaf(w, s0.z, acc[2]); acc[3] = fmaf(w, s0.w, acc[3]);
+    acc[4] = fmaf(w, s1.x, acc[4]); acc[5] = fmaf(w, s1.y, acc[5]); acc[6] = fmaf(w, s1.z, acc[6]); acc[7] = fmaf(w, s1.w, acc[7]);
+}
+
+// grid = (Dv / kSlice, Hv, n_seqs), block = 256 threads.  Register tiles: 2 rows x 8 columns for the
+// products with S0, 4 rows x 8 columns for the state update; all shared-memory operands are read as
+// 16-byte vectors so the loops are bound by the FMA pipe, not by shared-memory bandwidth.
+template <int DK, int DV>
 __global__ void __launch_bounds__(256) gdn_chunk_scan_kernel(const GdnScanArgs a) {
+    constexpr int PK = DK + 4, PS = kSlice + 4;
     extern __shared__ __align__(16) float sm[];
-    float* sK = sm;                          // [64][DK+1]
-    float* sQ = sK + kChunk * (DK + 1);      // [64][DK+1]
-    float* sKK = sQ + kChunk * (DK + 1);     // [64][65]  A_ts (s < t) then reused
-    float* sQK = sKK + kChunk * 65;          // [64][65]  masked decay * q.k
-    float* sS = sQK + kChunk * 65;           // [DK][33]  state slice
-    float* sB = sS + DK * 33;                // [64][33]  B then Delta
-    float* sG = sB + kChunk * 33;            // [64] cumulative log decay
-    float* sBeta = sG + kChunk;              // [64]
+    float* sW = sm;                          // [64][DK+4]
+    float* sQd = sW + kChunk * PK;           // [64][DK+4]
+    float* sKd = sQd + kChunk * PK;          // [64][DK+4]
+    float* sS = sKd + kChunk * PK;           // [DK][kSlice+4]  state slice
+    float* sD = sS + DK * PS;                // [64][kSlice+4]  U slice, then Delta
+    float* sQK = sD + kChunk * PS;           // [64][65]
 
-    const int slice = blockIdx.x, h = blockIdx.y;
+    const int slice = blockIdx.x, h = blockIdx.y, t = threadIdx.x, Hv = a.Hv, c0 = slice * kSlice;
     const GdnSeqDesc2 sd = a.seqs[blockIdx.z];
-    if (sd.n_rows <= 0) return;
-    const int t = threadIdx.x, Hv = a.Hv, Dv = a.Dv, c0 = slice * kSlice;
-    float* Sg = a.state + ((size_t)sd.slot * Hv + h) * DK * Dv;
-    for (int i = t; i < DK * kSlice; i += 256) sS[(i / kSlice) * 33 + (i % kSlice)] = Sg[(size_t)(i / kSlice) * Dv + c0 + (i % kSlice)];
+    if (sd.n_rows <= 0 || sd.slot < 0) return;
+    int gc = 0;
+    for (int s = 0; s < (int)blockIdx.z; ++s) {
+        const GdnSeqDesc2 d = a.seqs[s];
+        if (d.n_rows > 0 && d.slot >= 0) gc += (d.n_rows + kChunk - 1) / kChunk;
+    }
+    float* Sg = a.state + ((size_t)sd.slot * Hv + h) * DK * DV;
+    for (int i = t; i < DK * kSlice / 4; i += 256) {
+        const int d = (i * 4) / kSlice, c = (i * 4) % kSlice;
+        *reinterpret_cast<float4*>(sS + d * PS + c) = *reinterpret_cast<const float4*>(Sg + (size_t)d * DV + c0 + c);
+    }
+    const int r2 = t / 8, cb = (t % 8) * 8;          // rows 2 r2, 2 r2 + 1 ; columns cb .. cb + 7
 
-    for (int r0 = 0; r0 < sd.n_rows; r0 += kChunk) {
+    for (int r0 = 0; r0 < sd.n_rows; r0 += kChunk, ++gc) {
         const int C = min(kChunk, sd.n_rows - r0);
         const size_t rowbase = (size_t)(sd.row_start + r0);
+        const float* scr = a.scratch + ((size_t)gc * Hv + h) * chunk_scratch_floats(DK, DV);
+        const float* gW = scr; const float* gQd = gW + kChunk * DK; const float* gKd = gQd + kChunk * DK;
+        const float* gU = gKd + kChunk * DK; const float* gQK = gU + kChunk * DV;
         __syncthreads();
-        // ---- load q, k (rows beyond C are zero), beta, running log decay
-        for (int i = t; i < kChunk * DK; i += 256) {
-            const int r = i / DK, d = i % DK;
-            float kv = 0.f, qv = 0.f;
-            if (r < C) {
-                kv = a.k[((rowbase + r) * Hv + h) * DK + d];
-                qv = a.q[((rowbase + r) * Hv + h) * DK + d];
-            }
-            sK[r * (DK + 1) + d] = kv; sQ[r * (DK + 1) + d] = qv;
+        for (int i = t; i < kChunk * DK / 4; i += 256) {
+            const int r = (i * 4) / DK, d = (i * 4) % DK;
+            *reinterpret_cast<float4*>(sW + r * PK + d) = __ldg(reinterpret_cast<const float4*>(gW) + i);
+            *reinterpret_cast<float4*>(sQd + r * PK + d) = __ldg(reinterpret_cast<const float4*>(gQd) + i);
+            *reinterpret_cast<float4*>(sKd + r * PK + d) = __ldg(reinterpret_cast<const float4*>(gKd) + i);
         }
-        if (t < 32) {        // inclusive scan of g over the chunk by one warp (two 32-wide halves)
-            float g0 = t < C ? a.g[(rowbase + t) * Hv + h] : 0.f;
-            float g1 = t + 32 < C ? a.g[(rowbase + t + 32) * Hv + h] : 0.f;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const float n0 = __shfl_up_sync(0xffffffffu, g0, o), n1 = __shfl_up_sync(0xffffffffu, g1, o);
-                if (t >= o) { g0 += n0; g1 += n1; }
-            }
-            const float tot0 = __shfl_sync(0xffffffffu, g0, 31);
-            sG[t] = g0; sG[t + 32] = g1 + tot0;
-            sBeta[t] = t < C ? a.beta[(rowbase + t) * Hv + h] : 0.f;
-            sBeta[t + 32] = t + 32 < C ? a.beta[(rowbase + t + 32) * Hv + h] : 0.f;
+        for (int i = t; i < kChunk * kChunk; i += 256) sQK[(i / kChunk) * 65 + (i % kChunk)] = __ldg(gQK + i);
+        for (int i = t; i < kChunk * kSlice / 4; i += 256) {
+            const int r = (i * 4) / kSlice, c = (i * 4) % kSlice;
+            *reinterpret_cast<float4*>(sD + r * PS + c) = __ldg(reinterpret_cast<const float4*>(gU + (size_t)r * DV + c0 + c));
         }
+        const float DC = a.dc[(size_t)gc * Hv + h];
         __syncthreads();
-        // ---- KK (strictly lower, scaled into A) and QK (lower incl. diagonal, decay-masked): 64x64 each.
-        //      Thread -> rows (t/16) + 16 i, columns (t%16) + 16 j: conflict-free with the odd row stride.
+        // ---- Delta = U - W S0 and R = Qd S0
+        float R0[8], R1[8];
         {
-            const int tr = t / 16, tc = t % 16;
-            float kk[4][4] = {}, qk[4][4] = {};
-            for (int d = 0; d < DK; ++d) {
-                float kr[4], qr[4], kc[4];
+            float P0[8], P1[8];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    kr[i] = sK[(tr + 16 * i) * (DK + 1) + d]; qr[i] = sQ[(tr + 16 * i) * (DK + 1) + d];
-                    kc[i] = sK[(tc + 16 * i) * (DK + 1) + d];
+            for (int j = 0; j < 8; ++j) { P0[j] = P1[j] = R0[j] = R1[j] = 0.f; }
+            const float* w0p = sW + (2 * r2) * PK; const float* q0p = sQd + (2 * r2) * PK;
+#pragma unroll 2
+            for (int d = 0; d < DK; d += 4) {
+                const float4 w0 = *reinterpret_cast<const float4*>(w0p + d), w1 = *reinterpret_cast<const float4*>(w0p + PK + d);
+                const float4 q0 = *reinterpret_cast<const float4*>(q0p + d), q1 = *reinterpret_cast<const float4*>(q0p + PK + d);
+                const float wv0[4] = {w0.x, w0.y, w0.z, w0.w}, wv1[4] = {w1.x, w1.y, w1.z, w1.w};
+                const float qv0[4] = {q0.x, q0.y, q0.z, q0.w}, qv1[4] = {q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+                for (int dd = 0; dd < 4; ++dd) {
+                    const float4 s0 = *reinterpret_cast<const float4*>(sS + (d + dd) * PS + cb);
+                    const float4 s1 = *reinterpret_cast<const float4*>(sS + (d + dd) * PS + cb + 4);
+                    fma8(P0, wv0[dd], s0, s1); fma8(P1, wv1[dd], s0, s1);
+                    fma8(R0, qv0[dd], s0, s1); fma8(R1, qv1[dd], s0, s1);
                 }
+            }
+            float* d0 = sD + (2 * r2) * PS + cb;
 #pragma unroll
-                for (int i = 0; i < 4; ++i)
+            for (int j = 0; j < 8; ++j) { d0[j] -= P0[j]; d0[PS + j] -= P1[j]; }
+        }
+        __syncthreads();
+        // ---- O = R + QKd Delta (row 2 r2 sees s <= 2 r2, row 2 r2 + 1 one more)
+        {
+            const float* qk0 = sQK + (2 * r2) * 65;
+            for (int s = 0; s <= 2 * r2 + 1; ++s) {
+                const float4 s0 = *reinterpret_cast<const float4*>(sD + s * PS + cb), s1 = *reinterpret_cast<const float4*>(sD + s * PS + cb + 4);
+                fma8(R0, qk0[s], s0, s1);            // QKd is zero above the diagonal
+                fma8(R1, qk0[65 + s], s0, s1);
+            }
+            if (2 * r2 < C) {
+                float* op = a.o + ((rowbase + 2 * r2) * Hv + h) * DV + c0 + cb;
+                *reinterpret_cast<float4*>(op) = make_float4(R0[0], R0[1], R0[2], R0[3]);
+                *reinterpret_cast<float4*>(op + 4) = make_float4(R0[4], R0[5], R0[6], R0[7]);
+            }
+            if (2 * r2 + 1 < C) {
+                float* op = a.o + ((rowbase + 2 * r2 + 1) * Hv + h) * DV + c0 + cb;
+                *reinterpret_cast<float4*>(op) = make_float4(R1[0], R1[1], R1[2], R1[3]);
+                *reinterpret_cast<float4*>(op + 4) = make_float4(R1[4], R1[5], R1[6], R1[7]);
+            }
+        }
+        // ---- S = D_C S0 + Kd^T Delta : thread -> state rows 4 d4 .. 4 d4 + 3, columns cb .. cb + 7
+        for (int d4 = t / 8; d4 * 4 < DK; d4 += 32) {
+            float acc[4][8];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) { kk[i][j] = fmaf(kr[i], kc[j], kk[i][j]); qk[i][j] = fmaf(qr[i], kc[j], qk[i][j]); }
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[i][j] = DC * sS[(4 * d4 + i) * PS + cb + j];
+#pragma unroll 2
+            for (int s = 0; s < kChunk; ++s) {
+                const float4 kv = *reinterpret_cast<const float4*>(sKd + s * PK + 4 * d4);
+                const float4 s0 = *reinterpret_cast<const float4*>(sD + s * PS + cb), s1 = *reinterpret_cast<const float4*>(sD + s * PS + cb + 4);
+                fma8(acc[0], kv.x, s0, s1); fma8(acc[1], kv.y, s0, s1); fma8(acc[2], kv.z, s0, s1); fma8(acc[3], kv.w, s0, s1);
             }
 #pragma unroll
             for (int i = 0; i < 4; ++i)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int tt = tr + 16 * i, ss = tc + 16 * j;
-                    const float dec = ss <= tt ? __expf(sG[tt] - sG[ss]) : 0.f;
-                    sKK[tt * 65 + ss] = ss < tt ? sBeta[tt] * dec * kk[i][j] : 0.f;
-                    sQK[tt * 65 + ss] = dec * qk[i][j];
-                }
-        }
-        // ---- P = K S0, R = Q S0 for this slice: thread -> (row r = t/4, 8 columns)
-        float Rreg[8];
-        {
-            const int r = t / 4, cb = (t % 4) * 8;
-            float P[8] = {};
-#pragma unroll
-            for (int j = 0; j < 8; ++j) Rreg[j] = 0.f;
-            for (int d = 0; d < DK; ++d) {
-                const float kv = sK[r * (DK + 1) + d], qv = sQ[r * (DK + 1) + d];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) { const float s = sS[d * 33 + cb + j]; P[j] = fmaf(kv, s, P[j]); Rreg[j] = fmaf(qv, s, Rreg[j]); }
-            }
-            const float Dt = __expf(sG[r]), bt = sBeta[r];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                float vv = 0.f;
-                if (r < C) vv = a.v[((rowbase + r) * Hv + h) * Dv + c0 + cb + j];
-                sB[r * 33 + cb + j] = bt * (vv - Dt * P[j]);
-                Rreg[j] *= Dt;
-            }
-        }
-        __syncthreads();
-        // ---- forward substitution (I + A) Delta = B: threads 0..31 own one column each, 64 steps from registers
-        if (t < kSlice) {
-            float x[kChunk];
-#pragma unroll
-            for (int i = 0; i < kChunk; ++i) {
-                float s4[4] = {sB[i * 33 + t], 0.f, 0.f, 0.f};      // four partial sums shorten the dependency chain
-#pragma unroll
-                for (int j = 0; j < i; ++j) s4[j & 3] = fmaf(-sKK[i * 65 + j], x[j], s4[j & 3]);
-                x[i] = (s4[0] + s4[1]) + (s4[2] + s4[3]);
-            }
-#pragma unroll
-            for (int i = 0; i < kChunk; ++i) sB[i * 33 + t] = x[i];
-        }
-        __syncthreads();
-        // ---- o_t = D_t R_t + sum_{s<=t} QKdec[t][s] delta_s ; same (row, 8 columns) mapping
-        {
-            const int r = t / 4, cb = (t % 4) * 8;
-            float o[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) o[j] = Rreg[j];
-            for (int s = 0; s <= r; ++s) {
-                const float w = sQK[r * 65 + s];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) o[j] = fmaf(w, sB[s * 33 + cb + j], o[j]);
-            }
-            if (r < C) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) a.o[((rowbase + r) * Hv + h) * Dv + c0 + cb + j] = o[j];
-            }
-        }
-        // ---- S = D_C S0 + sum_s (D_C / D_s) k_s delta_s^T : thread -> (d = t % DK .., columns)
-        {
-            const float GC = sG[C - 1];
-            const float DC = __expf(GC);
-            for (int i = t; i < DK * 4; i += 256) {
-                const int d = i / 4, cb = (i % 4) * 8;
-                float acc[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) acc[j] = DC * sS[d * 33 + cb + j];
-                for (int s = 0; s < C; ++s) {
-                    const float w = __expf(GC - sG[s]) * sK[s * (DK + 1) + d];
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) acc[j] = fmaf(w, sB[s * 33 + cb + j], acc[j]);
-                }
-#pragma unroll
-                for (int j = 0; j < 8; ++j) sS[d * 33 + cb + j] = acc[j];
-            }
+                for (int j = 0; j < 8; ++j) sS[(4 * d4 + i) * PS + cb + j] = acc[i][j];
         }
     }
     __syncthreads();
-    for (int i = t; i < DK * kSlice; i += 256) Sg[(size_t)(i / kSlice) * Dv + c0 + (i % kSlice)] = sS[(i / kSlice) * 33 + (i % kSlice)];
+    for (int i = t; i < DK * kSlice / 4; i += 256) {
+        const int d = (i * 4) / kSlice, c = (i * 4) % kSlice;
+        *reinterpret_cast<float4*>(Sg + (size_t)d * DV + c0 + c) = *reinterpret_cast<const float4*>(sS + d * PS + c);
+    }
 }
 
 // grid = (Hv, rows), block = Dv threads
@@ -288,39 +432,55 @@ __global__ void gdn_post_kernel(const float* o, const __nv_bfloat16* proj, int l
 
 }  // namespace ps
 
-// Chunked GDN mixer for prefill-sized steps.  Scratch: q,k [rows,Hv,Dk] f32; v,o [rows,Hv,Dv] f32; beta,g [rows,Hv] f32.
+// Floats of scratch needed for a step of `rows` rows in `n_seqs` sequences (upper bound on the chunks).
+PS_API long long ps_gdn_chunked_scratch_floats(int rows, int n_seqs, int Hv, int Dk, int Dv) {
+    const long long chunks = (rows + ps::kChunk - 1) / ps::kChunk + n_seqs;
+    return chunks * Hv * (long long)ps::chunk_scratch_floats(Dk, Dv);
+}
+
+namespace ps {
+template <int DK, int DV>
+static int launch_chunked(const GdnPrepArgs& p, const GdnScanArgs& s, int max_chunks, cudaStream_t stream) {
+    const size_t raw_b = (size_t)(kChunk + 3) * (2 * DK + DV) * 2, at_b = sizeof(float) * (kChunk * 65 + kChunk * kTP);
+    const size_t smem_a = sizeof(float) * (2 * kChunk * (DK + 4) + kChunk * (DV + 4) + 2 * kChunk) + (raw_b > at_b ? raw_b : at_b);
+    const size_t smem_b = sizeof(float) * (3 * kChunk * (DK + 4) + DK * (kSlice + 4) + kChunk * (kSlice + 4) + kChunk * 65);
+    static bool set = false;
+    if (!set) {
+        cudaFuncSetAttribute(gdn_chunk_prep_kernel<DK, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a);
+        cudaFuncSetAttribute(gdn_chunk_scan_kernel<DK, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_b);
+        set = true;
+    }
+    gdn_chunk_prep_kernel<DK, DV><<<dim3(max_chunks, p.Hv), 256, smem_a, stream>>>(p);
+    int err = PS_LAUNCH_CHECK();
+    if (err) return err;
+    gdn_chunk_scan_kernel<DK, DV><<<dim3(DV / kSlice, p.Hv, p.n_seqs), 256, smem_b, stream>>>(s);
+    return PS_LAUNCH_CHECK();
+}
+}  // namespace ps
+
+// Chunked GDN mixer for prefill-sized steps.  `scratch` holds ps_gdn_chunked_scratch_floats() floats,
+// `dc` one float per (chunk, head), `o` [rows, Hv, Dv] floats.
 PS_API int ps_gdn_chunked(const void* proj, int ld_proj, int rows, int Hk, int Hv, int Dk, int Dv, const void* conv_w,
                           const void* A_log, const void* dt_bias, const void* norm_w, float eps, void* conv_state, int ring,
                           void* state, const void* seqs, int n_seqs, const void* row_slot, const void* row_pos,
-                          void* q, void* k, void* v, void* beta, void* g, void* o, void* out,
-                          cudaStream_t stream) {
+                          void* scratch, void* dc, void* o, void* out, cudaStream_t stream) {
     using namespace ps;
-    if (rows <= 0 || n_seqs <= 0 || (Dk != 128 && Dk != 64) || Dv % kSlice || Dv > 128 || Dk > 128 || ring < 4)
-        return (int)cudaErrorInvalidValue;
+    if (rows <= 0 || n_seqs <= 0 || Hk <= 0 || (Hv % Hk) || ring < 4) return (int)cudaErrorInvalidValue;
     GdnPrepArgs p;
     p.proj = (const __nv_bfloat16*)proj; p.ld_proj = ld_proj; p.Hk = Hk; p.Hv = Hv; p.Dk = Dk; p.Dv = Dv;
     p.conv_w = (const __nv_bfloat16*)conv_w; p.A_log = (const float*)A_log; p.dt_bias = (const float*)dt_bias;
     p.conv_state = (__nv_bfloat16*)conv_state; p.ring = ring; p.row_slot = (const int*)row_slot; p.row_pos = (const int*)row_pos;
-    p.q = (float*)q; p.k = (float*)k; p.v = (float*)v; p.beta = (float*)beta; p.g = (float*)g;
-    gdn_prepare_kernel<<<dim3(Hv, rows), 128, 0, stream>>>(p);
-    int err = PS_LAUNCH_CHECK();
+    p.seqs = (const GdnSeqDesc2*)seqs; p.n_seqs = n_seqs; p.scratch = (float*)scratch; p.dc = (float*)dc;
+    GdnScanArgs s;
+    s.scratch = p.scratch; s.dc = p.dc; s.Hv = Hv; s.Dv = Dv; s.n_seqs = n_seqs; s.state = (float*)state; s.seqs = p.seqs;
+    s.o = (float*)o;
+    const int max_chunks = (rows + kChunk - 1) / kChunk + n_seqs;
+    int err;
+    if (Dk == 128 && Dv == 128) err = launch_chunked<128, 128>(p, s, max_chunks, stream);
+    else if (Dk == 64 && Dv == 64) err = launch_chunked<64, 64>(p, s, max_chunks, stream);
+    else return (int)cudaErrorInvalidValue;
     if (err) return err;
     gdn_history_kernel<<<dim3(Hv, rows), 128, 0, stream>>>(p, rows);
-    if ((err = PS_LAUNCH_CHECK())) return err;
-    GdnScanArgs s;
-    s.q = p.q; s.k = p.k; s.v = p.v; s.beta = p.beta; s.g = p.g; s.Hv = Hv; s.Dv = Dv; s.state = (float*)state;
-    s.seqs = (const GdnSeqDesc2*)seqs; s.o = (float*)o;
-    const size_t smem = sizeof(float) * (2 * kChunk * (Dk + 1) + 2 * kChunk * 65 + Dk * 33 + kChunk * 33 + 2 * kChunk);
-    dim3 grid(Dv / kSlice, Hv, n_seqs);
-    if (Dk == 128) {
-        static bool set = false;
-        if (!set) { cudaFuncSetAttribute(gdn_chunk_scan_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); set = true; }
-        gdn_chunk_scan_kernel<128><<<grid, 256, smem, stream>>>(s);
-    } else {
-        static bool set = false;
-        if (!set) { cudaFuncSetAttribute(gdn_chunk_scan_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); set = true; }
-        gdn_chunk_scan_kernel<64><<<grid, 256, smem, stream>>>(s);
-    }
     if ((err = PS_LAUNCH_CHECK())) return err;
     gdn_post_kernel<<<dim3(Hv, rows), Dv, 0, stream>>>((const float*)o, (const __nv_bfloat16*)proj, ld_proj,
                                                        2 * Hk * Dk + Hv * Dv, (const __nv_bfloat16*)norm_w, eps, Hv, Dv,

@@ -32,6 +32,7 @@ class CudaOps:
     act_dtype = torch.bfloat16
     name = "cuda"
     GDN_CHUNKED_MIN_ROWS = 16      # steps with more rows than this use the chunked GDN kernels
+    ATTN_PREFILL_MIN_ROWS = 16     # ... and the tiled tensor-core attention kernel
 
     def __init__(self, cfg: Qwen35Config, device, attn_split_tokens: int = 128, attn_max_splits: int = 0,
                  max_seq_len: int = 4096):
@@ -156,6 +157,15 @@ class CudaOps:
         cfg = self.cfg
         rows, D = q.shape[0], cfg.head_dim
         out = self.buf("attn_ctx", rows, hq * D)
+        if rows > self.ATTN_PREFILL_MIN_ROWS and not self.exact_rows and not b.graph_static and D in (64, 128, 256):
+            # prefill-sized step: 64-row query tiles on the tensor cores
+            _lib.call("ps_attn_prefill", ptr(q), ptr(kv.k), ptr(kv.v), ptr(kv.k_scale), ptr(kv.v_scale),
+                      ptr(st.block_table), c_int(st.max_blocks), c_int(st.sc.page_tokens), c_int(st.num_pages),
+                      ptr(b.seq_desc), c_int(b.n_seqs), c_int(rows), c_int(hq), c_int(hkv), c_int(D), c_float(D ** -0.5),
+                      c_int(1 if st.kv_fp8 else 0), ptr(qkv), c_int(qkv.stride(0)), c_int(2 * D), c_int(D), ptr(out),
+                      ptr(st.status))
+            self.launches += 1
+            return out
         pacc = self.buf("attn_part_acc", rows, hq * self.max_splits * D, torch.float32)
         pml = self.buf("attn_part_ml", rows, hq * self.max_splits * 2, torch.float32)
         _lib.call("ps_paged_attention", ptr(q), ptr(kv.k), ptr(kv.v), ptr(kv.k_scale), ptr(kv.v_scale),
@@ -176,16 +186,17 @@ class CudaOps:
         Dk, Dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
         out = self.buf("gdn_o", rows, hv * Dv)
         if rows > self.GDN_CHUNKED_MIN_ROWS and log is None and not to_alt and not self.exact_rows and xn is None:
-            # prefill-sized step: chunked form (fp32 products, one forward substitution per 64 rows)
+            # prefill-sized step: chunked form (state-independent part for all chunks at once, then a lean scan)
             f32 = torch.float32
-            q = self.buf("gdn_q", rows, hv * Dk, f32); k = self.buf("gdn_k", rows, hv * Dk, f32)
-            v = self.buf("gdn_v", rows, hv * Dv, f32); o = self.buf("gdn_of", rows, hv * Dv, f32)
-            beta = self.buf("gdn_beta", rows, hv, f32); g = self.buf("gdn_g", rows, hv, f32)
+            n_seqs = b.max_seqs if b.graph_static else b.n_seqs
+            chunks = (rows + 63) // 64 + n_seqs
+            scr = self.buf("gdn_scratch", 1, chunks * hv * 64 * (3 * Dk + Dv + 64), f32)
+            dc = self.buf("gdn_dc", 1, chunks * hv, f32)
+            o = self.buf("gdn_of", rows, hv * Dv, f32)
             _lib.call("ps_gdn_chunked", ptr(proj), c_int(proj.stride(0)), c_int(rows), c_int(hk), c_int(hv), c_int(Dk),
                       c_int(Dv), ptr(gw.conv_w), ptr(gw.A_log), ptr(gw.dt_bias), ptr(gw.norm_w),
                       c_float(cfg.rms_norm_eps), ptr(gs.conv), c_int(st.sc.conv_ring), ptr(gs.rec), ptr(b.seq_desc),
-                      c_int(b.max_seqs if b.graph_static else b.n_seqs), ptr(b.row_slot), ptr(b.row_pos), ptr(q), ptr(k),
-                      ptr(v), ptr(beta), ptr(g), ptr(o), ptr(out))
+                      c_int(n_seqs), ptr(b.row_slot), ptr(b.row_pos), ptr(scr), ptr(dc), ptr(o), ptr(out))
             self.launches += 4
             return out
         state_out = gs.rec_alt if to_alt else gs.rec

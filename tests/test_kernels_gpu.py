@@ -142,6 +142,49 @@ def test_attention_prefill_then_decode(kv_dtype, geom):
     assert int(st_c.status[0]) == 0
 
 
+@pytest.mark.parametrize("kv_dtype", ["bf16", "fp8_e4m3"])
+def test_attention_prefill_chunks_two_sequences(kv_dtype):
+    """Tiled prefill attention: a second chunk that starts at an unaligned position next to a fresh sequence,
+    with gate, against the fp32 reference."""
+    cfg = Qwen35Config(vocab_size=1024, hidden_size=512, intermediate_size=512, num_hidden_layers=4,
+                       num_attention_heads=12, num_key_value_heads=2, head_dim=256)
+    cu, ref = _ops(cfg, 512)
+    sc = StateConfig(max_slots=2, max_seq_len=512, page_tokens=16, kv_dtype=kv_dtype, kv_capacity_tokens=2048)
+    st_c = ModelState(cfg, sc, _dev(), torch.bfloat16)
+    st_r = ModelState(cfg, sc, _dev(), torch.float32)
+    nb = st_c.max_blocks
+    for st in (st_c, st_r):
+        perm = torch.randperm(st.num_pages - 1, generator=torch.Generator().manual_seed(5))[:2 * nb] + 1
+        st.block_table[0, :nb] = perm[:nb].int().to(_dev())
+        st.block_table[1, :nb] = perm[nb:2 * nb].int().to(_dev())
+    li = cfg.attn_layers[0]
+    hf = random_hf_weights(cfg, seed=3, device="cuda")
+    ew = build_engine_weights(cfg, lambda n: hf[n], "bf16", "cuda")
+    aw = ew.layers[li].mixer
+    Hq, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    g = torch.Generator(device="cuda").manual_seed(9)
+    width = 2 * Hq * D + 2 * Hkv * D
+    tol = 2e-2 if kv_dtype == "bf16" else 6e-2
+    for seqs in ([SeqRows(0, 0, [0] * 100, ())], [SeqRows(0, 100, [0] * 77, ()), SeqRows(1, 0, [0] * 130, ())]):
+        n = sum(len(s.token_ids) for s in seqs)
+        qkv = torch.randn(n, width, device="cuda", generator=g).to(torch.bfloat16)
+        b = StepBatch(512, 2, _dev())
+        b.fill(seqs); b.upload()
+        q_c = cu.attn_prep(qkv, aw, Hq, Hkv, b, st_c.kv[li], st_c)
+        q_r = ref.attn_prep(qkv.float(), aw, Hq, Hkv, b, st_r.kv[li], st_r)
+        o_c = cu.paged_attention(q_c, qkv, Hq, Hkv, b, st_c.kv[li], st_c, b.max_visible)
+        o_r = ref.paged_attention(q_r, qkv.float(), Hq, Hkv, b, st_r.kv[li], st_r, b.max_visible)
+        cu.ATTN_PREFILL_MIN_ROWS = 1 << 30           # split-KV kernel on the same inputs
+        try:
+            o_s = cu.paged_attention(q_c, qkv, Hq, Hkv, b, st_c.kv[li], st_c, b.max_visible).clone()
+        finally:
+            del cu.ATTN_PREFILL_MIN_ROWS
+        torch.cuda.synchronize()
+        assert _rel_err(o_c[:n], o_r[:n]) < tol
+        assert _rel_err(o_c[:n].float(), o_s[:n].float()) < 1.5e-2
+    assert int(st_c.status[0]) == 0
+
+
 @pytest.mark.parametrize("geom", ["tiny", "big"])
 def test_gdn_rows_and_decode(geom):
     if geom == "tiny":
