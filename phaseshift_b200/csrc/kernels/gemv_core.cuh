@@ -104,6 +104,19 @@ template <int WF> __device__ __forceinline__ float stage_target_absmax() {
     return WF == W_NVFP4 ? 512.f : (WF == W_MXFP8 ? 8.f : 0.f);
 }
 
+// Position of activation k inside the staged row.  A lane's kChunk activations of one k-step are
+// several 16-byte groups; group q of lane l sits at 16-byte slot q * 32 + l of the step, so that the
+// warp's q-th vector load touches 32 consecutive 16-byte slots (no shared-memory bank conflicts)
+// instead of slots kChunk * sizeof(XS) bytes apart.
+template <int WF> __device__ __forceinline__ int xpos(int k) {
+    using XS = typename WTraits<WF>::XS;
+    constexpr int EPG = 16 / (int)sizeof(XS);                       // elements per 16-byte group
+    constexpr int GPL = WTraits<WF>::kChunk / EPG;                  // groups per lane
+    constexpr int SK = 32 * WTraits<WF>::kChunk;                    // elements per k-step
+    const int r = k % SK, g = r / EPG;
+    return (k - r) + ((g % GPL) * 32 + g / GPL) * EPG + (r % EPG);
+}
+
 // Row statistics + staging of prologue(x) into shared memory (XS type), zero-padded to kpad.
 // Pass 1 reads x from global once, parks the raw bf16 bits in the staging buffer and accumulates the
 // sum of squares (RMSNorm) and max |x (1+w)| (fp16 range scaling; the sigmoid gate only shrinks |x|);
@@ -133,8 +146,9 @@ __device__ __forceinline__ void stage_rows(const LinearSmallArgs& a, typename WT
                 }
                 amax = fmaxf(amax, fmaxf(fabsf(xv.x), fabsf(xv.y)));
             }
-            if constexpr (sizeof(XS) == 4) xrow[k] = __uint_as_float(bits);            // raw bits parked in word k
-            else *reinterpret_cast<uint32_t*>(xrow + k) = bits;
+            const int kp = xpos<WF>(k);
+            if constexpr (sizeof(XS) == 4) xrow[kp] = __uint_as_float(bits);           // raw bits parked in place
+            else *reinterpret_cast<uint32_t*>(xrow + kp) = bits;
         }
         if (norm || target > 0.f) block_sum_max(ss, amax, red);
         const float ir = norm ? rsqrtf(ss / (float)a.K + a.eps) : 1.f;
@@ -148,9 +162,10 @@ __device__ __forceinline__ void stage_rows(const LinearSmallArgs& a, typename WT
         }
         if (threadIdx.x == 0) xscale_inv[m] = 1.f / s;
         for (int k = threadIdx.x * 2; k < kpad; k += THREADS * 2) {
+            const int kp = xpos<WF>(k);
             uint32_t bits;
-            if constexpr (sizeof(XS) == 4) bits = __float_as_uint(xrow[k]);
-            else bits = *reinterpret_cast<const uint32_t*>(xrow + k);
+            if constexpr (sizeof(XS) == 4) bits = __float_as_uint(xrow[kp]);
+            else bits = *reinterpret_cast<const uint32_t*>(xrow + kp);
             float2 xv = bf16x2_bits_to_f32x2(bits);
             float v0 = xv.x, v1 = xv.y;
             if (live && k < a.K) {
@@ -169,8 +184,8 @@ __device__ __forceinline__ void stage_rows(const LinearSmallArgs& a, typename WT
                     *reinterpret_cast<uint32_t*>(a.xn_out + (size_t)m * a.K + k) = f32x2_to_bf16x2_bits(v0, v1);
             }
             v0 *= s; v1 *= s;
-            if constexpr (sizeof(XS) == 4) *reinterpret_cast<float2*>(xrow + k) = make_float2(v0, v1);
-            else *reinterpret_cast<__half2*>(xrow + k) = __floats2half2_rn(v0, v1);
+            if constexpr (sizeof(XS) == 4) *reinterpret_cast<float2*>(xrow + kp) = make_float2(v0, v1);
+            else *reinterpret_cast<__half2*>(xrow + kp) = __floats2half2_rn(v0, v1);
         }
     }
 }
@@ -199,14 +214,14 @@ __device__ __forceinline__ float half2_hsum_f32(__half2 p) { return __half2float
 
 // One lane's share of one weight row inside a block: kChunk weights against one batch row's staged
 // activations (`xm` = this lane's activations for that k range, as 32-bit words, shared by the rows
-// of the quad).  Identical code serves the register-ring and the TMA-ring kernels.
+// of the quad; `xs` passed to load_x points at the lane's first 16-byte group of the step, see xpos).  Identical code serves the register-ring and the TMA-ring kernels.
 template <int WF> struct RowDot;
 
 template <> struct RowDot<W_BF16> {
     static constexpr int kXWords = 8;       // 8 fp32 activations
     __device__ static __forceinline__ void load_x(const float* xs, uint32_t (&xm)[kXWords]) {
         const uint4 a = *reinterpret_cast<const uint4*>(xs);
-        const uint4 b = *reinterpret_cast<const uint4*>(xs + 4);
+        const uint4 b = *(reinterpret_cast<const uint4*>(xs) + 32);
         xm[0] = a.x; xm[1] = a.y; xm[2] = a.z; xm[3] = a.w; xm[4] = b.x; xm[5] = b.y; xm[6] = b.z; xm[7] = b.w;
     }
     __device__ static __forceinline__ float dot(uint4 w, uint32_t /*scale_bits*/, const uint32_t (&xm)[kXWords], float acc) {
@@ -228,7 +243,7 @@ template <> struct RowDot<W_NVFP4> {
         const uint4* xp = reinterpret_cast<const uint4*>(xs);
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-            const uint4 v = xp[q];
+            const uint4 v = xp[q * 32];
             xm[q * 4] = v.x; xm[q * 4 + 1] = v.y; xm[q * 4 + 2] = v.z; xm[q * 4 + 3] = v.w;
         }
     }
@@ -264,7 +279,7 @@ template <> struct RowDot<W_MXFP8> {
     static constexpr int kXWords = 8;       // 16 fp16 activations
     __device__ static __forceinline__ void load_x(const __half* xs, uint32_t (&xm)[kXWords]) {
         const uint4* xp = reinterpret_cast<const uint4*>(xs);
-        const uint4 a = xp[0], b = xp[1];
+        const uint4 a = xp[0], b = xp[32];
         xm[0] = a.x; xm[1] = a.y; xm[2] = a.z; xm[3] = a.w; xm[4] = b.x; xm[5] = b.y; xm[6] = b.z; xm[7] = b.w;
     }
     __device__ static __forceinline__ float dot(uint4 w, uint32_t scale_bits, const uint32_t (&xm)[kXWords], float acc) {

@@ -107,7 +107,7 @@ __global__ void __launch_bounds__(kStThreads, 1) linear_stream_kernel(const Line
             // warp-uniform outcome: either every lane saw the copy land or the whole warp gives up
             if (!__all_sync(0xffffffffu, tc::mbar_wait(&s_bar[warp][slot], (uint32_t)(consumed / n_slots) & 1u))) { timed_out = true; break; }
             const unsigned char* blk = my_ring + (size_t)slot * kSlot;
-            const int k = (st * 32 + lane) * CH;
+            const int k = st * 32 * CH + lane * (16 / (int)sizeof(XS));      // lane's first 16-byte group of the step
             uint4 w[R]; uint32_t sb[R];
 #pragma unroll
             for (int r = 0; r < R; ++r) {
