@@ -209,23 +209,33 @@ struct AttnMergeArgs {
     __nv_bfloat16* out;   // [rows, Hq*D]
 };
 
-// grid = (Hq, rows), block = D threads.  Splits are merged in ascending order (fixed order => exact).
+// grid = (Hq, rows), block = D threads.  The split weights exp(m_s - max m) are computed once, in
+// parallel (thread s owns split s), then every thread adds its output dimension over the splits in
+// ascending order, so the result depends only on the row's position, never on the batch.
+constexpr int kAttnMaxSplits = 1024;
 __global__ void paged_attn_merge_kernel(const AttnMergeArgs a) {
+    __shared__ float s_w[kAttnMaxSplits];
+    __shared__ float s_red[64];
     cudaTriggerProgrammaticLaunchCompletion();
     cudaGridDependencySynchronize();
     const int h = blockIdx.x, row = blockIdx.y, d = threadIdx.x;
     const int visible = a.row_pos[row] + 1;
-    const int n = (visible + a.split_tokens - 1) / a.split_tokens;
+    const int n = (visible + a.split_tokens - 1) / a.split_tokens;      // 0 for a padding row
     const float* ml = a.part_ml + ((size_t)row * a.Hq + h) * a.max_splits * 2;
     const float* pa = a.part_acc + ((size_t)row * a.Hq + h) * a.max_splits * a.D;
     float m = -3.0e38f;
-    for (int s = 0; s < n; ++s) m = fmaxf(m, ml[2 * s]);
-    float l = 0.f, o = 0.f;
-    for (int s = 0; s < n; ++s) {
+    for (int s = d; s < n; s += blockDim.x) m = fmaxf(m, ml[2 * s]);
+    m = block_max(m, s_red);
+    float l = 0.f;
+    for (int s = d; s < n; s += blockDim.x) {
         const float w = __expf(ml[2 * s] - m);
+        s_w[s] = w;
         l = fmaf(w, ml[2 * s + 1], l);
-        o = fmaf(w, pa[(size_t)s * a.D + d], o);
     }
+    l = block_sum(l, s_red + 32);      // its barriers also publish s_w
+    float o = 0.f;
+#pragma unroll 4
+    for (int s = 0; s < n; ++s) o = fmaf(s_w[s], pa[(size_t)s * a.D + d], o);
     float v = l > 0.f ? o / l : 0.f;
     if (a.gate != nullptr) {
         v = bf16_to_f32(f32_to_bf16(v));
@@ -256,7 +266,7 @@ PS_API int ps_paged_attention(const void* q, const void* k_pool, const void* v_p
     a.part_acc = (float*)part_acc; a.part_ml = (float*)part_ml; a.status = (uint32_t*)status;
     int n_splits = (max_visible + split_tokens - 1) / split_tokens;
     if (n_splits < 1) n_splits = 1;
-    if (n_splits > max_splits) return (int)cudaErrorInvalidValue;
+    if (n_splits > max_splits || max_splits > kAttnMaxSplits) return (int)cudaErrorInvalidValue;
     const size_t smem = (size_t)kAttnTile * (D + 8) * 2 + (size_t)kAttnTile * D * 2 +
                         sizeof(float) * (kAttnMaxG * D + kAttnMaxG * kAttnTile + kAttnMaxG + 2 * kAttnTile);
     static bool attr_set = false;

@@ -71,10 +71,32 @@ __global__ void __launch_bounds__(kSampThreads) sample_kernel(const SampleArgs a
     // pass 1: constrained argmax (also the softmax max); non-finite logits fail closed
     Best b{-INFINITY, 0xffffffffu};
     bool bad = false;
-    for (uint32_t i = threadIdx.x; i < (uint32_t)a.vocab; i += kSampThreads) {
-        const float v = lg[i];
-        if (!(fabsf(v) <= 3.0e38f)) bad = true;
-        if (allowed(m, i) && ranks_before(v, i, b.v, b.i)) { b.v = v; b.i = i; }
+    if ((a.ld & 3) == 0 && (reinterpret_cast<uintptr_t>(a.logits) & 15) == 0) {
+        // 16-byte loads, several in flight per thread: the sweep is latency-bound otherwise
+        const uint32_t n4 = (uint32_t)a.vocab >> 2;
+        const float4* lg4 = reinterpret_cast<const float4*>(lg);
+#pragma unroll 4
+        for (uint32_t j = threadIdx.x; j < n4; j += kSampThreads) {
+            const float4 q = lg4[j];
+            const float vv[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const uint32_t i = 4 * j + e;
+                if (!(fabsf(vv[e]) <= 3.0e38f)) bad = true;
+                if (allowed(m, i) && ranks_before(vv[e], i, b.v, b.i)) { b.v = vv[e]; b.i = i; }
+            }
+        }
+        for (uint32_t i = 4 * n4 + threadIdx.x; i < (uint32_t)a.vocab; i += kSampThreads) {
+            const float v = lg[i];
+            if (!(fabsf(v) <= 3.0e38f)) bad = true;
+            if (allowed(m, i) && ranks_before(v, i, b.v, b.i)) { b.v = v; b.i = i; }
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < (uint32_t)a.vocab; i += kSampThreads) {
+            const float v = lg[i];
+            if (!(fabsf(v) <= 3.0e38f)) bad = true;
+            if (allowed(m, i) && ranks_before(v, i, b.v, b.i)) { b.v = v; b.i = i; }
+        }
     }
     const int any_bad = __syncthreads_or(bad ? 1 : 0);
     b = block_best(b, sh_best);

@@ -34,7 +34,7 @@ class CudaOps:
     GDN_CHUNKED_MIN_ROWS = 16      # steps with more rows than this use the chunked GDN kernels
     ATTN_PREFILL_MIN_ROWS = 16     # ... and the tiled tensor-core attention kernel
 
-    def __init__(self, cfg: Qwen35Config, device, attn_split_tokens: int = 128, attn_max_splits: int = 0,
+    def __init__(self, cfg: Qwen35Config, device, attn_split_tokens: int = 64, attn_max_splits: int = 0,
                  max_seq_len: int = 4096):
         if device.type != "cuda":
             raise ValueError("CudaOps needs a CUDA device")
@@ -46,7 +46,7 @@ class CudaOps:
         self.inv_freq = torch.from_numpy(inv).to(device)
         # split length is fixed per engine (never per batch) so attention results are batch-invariant
         self.split_tokens = attn_split_tokens
-        while -(-(max_seq_len + 1) // self.split_tokens) > 256:
+        while -(-(max_seq_len + 1) // self.split_tokens) > 512:
             self.split_tokens *= 2
         self.max_splits = attn_max_splits or -(-(max_seq_len + 1) // self.split_tokens)
         self.launches = 0
