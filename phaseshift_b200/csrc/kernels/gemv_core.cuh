@@ -124,8 +124,8 @@ template <int WF> __device__ __forceinline__ int xpos(int k) {
 // kernel's critical path.  With `xn_out` set, CTA 0 also stores the normalised row (bf16) to global
 // for a consumer that needs it again (the GDN kernel's in-kernel b/a projections).
 template <int WF, int MT, int THREADS>
-__device__ __forceinline__ void stage_rows(const LinearSmallArgs& a, typename WTraits<WF>::XS* xs, int kpad,
-                                           float* xscale_inv, float* red) {
+__device__ __forceinline__ void stage_rows_generic(const LinearSmallArgs& a, typename WTraits<WF>::XS* xs, int kpad,
+                                                float* xscale_inv, float* red) {
     using XS = typename WTraits<WF>::XS;
     const float target = stage_target_absmax<WF>();
     const bool norm = a.prologue == PRO_RMSNORM_ONEPLUS;
@@ -186,6 +186,110 @@ __device__ __forceinline__ void stage_rows(const LinearSmallArgs& a, typename WT
             v0 *= s; v1 *= s;
             if constexpr (sizeof(XS) == 4) *reinterpret_cast<float2*>(xrow + kp) = make_float2(v0, v1);
             else *reinterpret_cast<__half2*>(xrow + kp) = __floats2half2_rn(v0, v1);
+        }
+    }
+}
+
+// Fast path of stage_rows: every thread keeps its share of the row (up to kStageVec 16-byte vectors of
+// eight activations) in registers between the statistics pass and the final write, so the row costs a
+// single global round trip, no shared-memory parking and no second read of the norm weights.
+constexpr int kStageVec = 6;
+
+template <int WF, int MT, int THREADS>
+__device__ __forceinline__ void stage_rows(const LinearSmallArgs& a, typename WTraits<WF>::XS* xs, int kpad,
+                                           float* xscale_inv, float* red) {
+    using XS = typename WTraits<WF>::XS;
+    const int nvec = kpad >> 3;
+    const bool norm = a.prologue == PRO_RMSNORM_ONEPLUS, gated = a.prologue == PRO_SIGMOID_GATE;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(a.x) & 15) == 0) &&
+                         (!norm || (reinterpret_cast<uintptr_t>(a.norm_w) & 15) == 0) &&
+                         (!gated || ((reinterpret_cast<uintptr_t>(a.gate) & 15) == 0 && (a.ld_gate & 7) == 0)) &&
+                         (a.xn_out == nullptr || (reinterpret_cast<uintptr_t>(a.xn_out) & 15) == 0);
+    if (nvec > kStageVec * THREADS || !aligned) { stage_rows_generic<WF, MT, THREADS>(a, xs, kpad, xscale_inv, red); return; }
+    const float target = stage_target_absmax<WF>();
+    const int kvec = a.K >> 3;                      // K is a multiple of 32
+    uint4 wv[kStageVec];
+#pragma unroll
+    for (int j = 0; j < kStageVec; ++j) {
+        const int idx = threadIdx.x + j * THREADS;
+        wv[j] = (norm && idx < kvec) ? __ldg(reinterpret_cast<const uint4*>(a.norm_w) + idx) : make_uint4(0, 0, 0, 0);
+    }
+    for (int m = 0; m < MT; ++m) {
+        const bool live = m < a.M;
+        const uint4* xr = reinterpret_cast<const uint4*>(a.x + (size_t)m * a.ldx);
+        XS* xrow = xs + (size_t)m * kpad;
+        uint4 xv[kStageVec], gv[kStageVec];
+#pragma unroll
+        for (int j = 0; j < kStageVec; ++j) {
+            const int idx = threadIdx.x + j * THREADS;
+            const bool in = live && idx < kvec;
+            xv[j] = in ? xr[idx] : make_uint4(0, 0, 0, 0);
+            gv[j] = (gated && in) ? *(reinterpret_cast<const uint4*>(a.gate + (size_t)m * a.ld_gate) + idx) : make_uint4(0, 0, 0, 0);
+        }
+        float ss = 0.f, amax = 0.f;
+#pragma unroll
+        for (int j = 0; j < kStageVec; ++j) {
+            const uint32_t xw[4] = {xv[j].x, xv[j].y, xv[j].z, xv[j].w};
+            const uint32_t ww[4] = {wv[j].x, wv[j].y, wv[j].z, wv[j].w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float2 v = bf16x2_bits_to_f32x2(xw[e]);
+                ss += v.x * v.x + v.y * v.y;
+                if (norm) { const float2 w = bf16x2_bits_to_f32x2(ww[e]); v.x *= 1.f + w.x; v.y *= 1.f + w.y; }
+                amax = fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y)));
+            }
+        }
+        if (norm || target > 0.f) block_sum_max(ss, amax, red);
+        const float ir = norm ? rsqrtf(ss / (float)a.K + a.eps) : 1.f;
+        float s = 1.f;
+        if (target > 0.f) {
+            const float am = amax * ir;
+            if (am > 0.f && am < 3.0e38f) {
+                // target/am = f * 2^e with f in [0.5, 1): s = 2^(e-1), clamped
+                const int e = (int)((__float_as_uint(target / am) >> 23) & 0xffu) - 126;
+                s = __uint_as_float((uint32_t)(max(-60, min(60, e - 1)) + 127) << 23);
+            }
+        }
+        if (threadIdx.x == 0) xscale_inv[m] = 1.f / s;
+#pragma unroll
+        for (int j = 0; j < kStageVec; ++j) {
+            const int idx = threadIdx.x + j * THREADS;
+            const uint32_t xw[4] = {xv[j].x, xv[j].y, xv[j].z, xv[j].w};
+            const uint32_t ww[4] = {wv[j].x, wv[j].y, wv[j].z, wv[j].w};
+            const uint32_t gw[4] = {gv[j].x, gv[j].y, gv[j].z, gv[j].w};
+            float f[8]; uint32_t xn[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float2 v = bf16x2_bits_to_f32x2(xw[e]);
+                if (norm) {
+                    const float2 w = bf16x2_bits_to_f32x2(ww[e]);
+                    // rounded to bf16 like a standalone norm kernel would store it
+                    v.x = bf16_to_f32(f32_to_bf16(v.x * ir * (1.f + w.x)));
+                    v.y = bf16_to_f32(f32_to_bf16(v.y * ir * (1.f + w.y)));
+                } else if (gated) {
+                    const float2 g = bf16x2_bits_to_f32x2(gw[e]);
+                    v.x = bf16_to_f32(f32_to_bf16(v.x * sigmoid_f(g.x)));
+                    v.y = bf16_to_f32(f32_to_bf16(v.y * sigmoid_f(g.y)));
+                }
+                xn[e] = f32x2_to_bf16x2_bits(v.x, v.y);
+                f[2 * e] = v.x * s; f[2 * e + 1] = v.y * s;
+            }
+            if (a.xn_out != nullptr && blockIdx.x == 0 && live && idx < kvec)
+                *(reinterpret_cast<uint4*>(a.xn_out + (size_t)m * a.K) + idx) = make_uint4(xn[0], xn[1], xn[2], xn[3]);
+            const int k0 = idx << 3;
+            if (idx < nvec) {
+            if constexpr (sizeof(XS) == 4) {
+                *reinterpret_cast<float4*>(xrow + xpos<WF>(k0)) = make_float4(f[0], f[1], f[2], f[3]);
+                *reinterpret_cast<float4*>(xrow + xpos<WF>(k0 + 4)) = make_float4(f[4], f[5], f[6], f[7]);
+            } else {
+                uint4 h;
+                __half2 h0 = __floats2half2_rn(f[0], f[1]), h1 = __floats2half2_rn(f[2], f[3]);
+                __half2 h2 = __floats2half2_rn(f[4], f[5]), h3 = __floats2half2_rn(f[6], f[7]);
+                h.x = *reinterpret_cast<uint32_t*>(&h0); h.y = *reinterpret_cast<uint32_t*>(&h1);
+                h.z = *reinterpret_cast<uint32_t*>(&h2); h.w = *reinterpret_cast<uint32_t*>(&h3);
+                *reinterpret_cast<uint4*>(xrow + xpos<WF>(k0)) = h;
+            }
+            }
         }
     }
 }
