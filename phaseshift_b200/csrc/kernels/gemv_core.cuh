@@ -195,9 +195,23 @@ __device__ __forceinline__ void stage_rows_generic(const LinearSmallArgs& a, typ
 // single global round trip, no shared-memory parking and no second read of the norm weights.
 constexpr int kStageVec = 6;
 
+struct StageW { uint4 v[kStageVec]; };
+
+// The norm weights do not depend on the producer grid: load them before waiting for it.
+template <int THREADS>
+__device__ __forceinline__ void stage_load_norm_w(const LinearSmallArgs& a, StageW& w) {
+    const bool ok = a.prologue == PRO_RMSNORM_ONEPLUS && (reinterpret_cast<uintptr_t>(a.norm_w) & 15) == 0;
+    const int kvec = a.K >> 3;
+#pragma unroll
+    for (int j = 0; j < kStageVec; ++j) {
+        const int idx = threadIdx.x + j * THREADS;
+        w.v[j] = (ok && idx < kvec) ? __ldg(reinterpret_cast<const uint4*>(a.norm_w) + idx) : make_uint4(0, 0, 0, 0);
+    }
+}
+
 template <int WF, int MT, int THREADS>
 __device__ __forceinline__ void stage_rows(const LinearSmallArgs& a, typename WTraits<WF>::XS* xs, int kpad,
-                                           float* xscale_inv, float* red) {
+                                           float* xscale_inv, float* red, const StageW& sw) {
     using XS = typename WTraits<WF>::XS;
     const int nvec = kpad >> 3;
     const bool norm = a.prologue == PRO_RMSNORM_ONEPLUS, gated = a.prologue == PRO_SIGMOID_GATE;
@@ -208,12 +222,7 @@ __device__ __forceinline__ void stage_rows(const LinearSmallArgs& a, typename WT
     if (nvec > kStageVec * THREADS || !aligned) { stage_rows_generic<WF, MT, THREADS>(a, xs, kpad, xscale_inv, red); return; }
     const float target = stage_target_absmax<WF>();
     const int kvec = a.K >> 3;                      // K is a multiple of 32
-    uint4 wv[kStageVec];
-#pragma unroll
-    for (int j = 0; j < kStageVec; ++j) {
-        const int idx = threadIdx.x + j * THREADS;
-        wv[j] = (norm && idx < kvec) ? __ldg(reinterpret_cast<const uint4*>(a.norm_w) + idx) : make_uint4(0, 0, 0, 0);
-    }
+    const uint4 (&wv)[kStageVec] = sw.v;
     for (int m = 0; m < MT; ++m) {
         const bool live = m < a.M;
         const uint4* xr = reinterpret_cast<const uint4*>(a.x + (size_t)m * a.ldx);

@@ -51,6 +51,7 @@ __global__ void __launch_bounds__(kStThreads, 1) linear_stream_kernel(const Line
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_quads = (a.N + R - 1) / R;
     const int steps = gemv_steps<WF>(a.K);
+    constexpr int wave_first = kStWaveQuads;
     int quad_begin, quad_end;
     cta_range(n_quads, gridDim.x, blockIdx.x, quad_begin, quad_end);
 
@@ -75,8 +76,18 @@ __global__ void __launch_bounds__(kStThreads, 1) linear_stream_kernel(const Line
     }
 
     for (int i = threadIdx.x; i < kStWaveQuads * kStWarps * R * MT; i += kStThreads) partial[i] = 0.f;
+    StageW sw;
+    stage_load_norm_w<kStThreads>(a, sw);
     cudaGridDependencySynchronize();
-    stage_rows<WF, MT, kStThreads>(a, xs, kpad, s_xscale_inv, s_red);
+    // the first wave's residual rows are needed only in the epilogue: pull them towards the SM now
+    if (a.epilogue == EPI_RESIDUAL && a.residual != nullptr) {
+        const int wq0 = min(wave_first, quad_end - quad_begin);
+        for (int i = threadIdx.x; i < wq0 * MT; i += kStThreads) {
+            const int ql = i / MT, m = i % MT;
+            if (m < a.M) asm volatile("prefetch.global.L1 [%0];" ::"l"(a.residual + (size_t)m * a.ld_res + (size_t)(quad_begin + ql) * R));
+        }
+    }
+    stage_rows<WF, MT, kStThreads>(a, xs, kpad, s_xscale_inv, s_red, sw);
     __syncthreads();
 
     int consumed = 0;
