@@ -208,7 +208,7 @@ def cmd_kernel(a) -> int:
         print(f"model_params={cfg.param_count()}"); return 0
     small = type(cfg)(**{**cfg.__dict__, "num_hidden_layers": 4, "layer_types": None, "vocab_size": min(cfg.vocab_size, 32768)})
     ew = build_engine_weights(small, random_getter(small, 0, dev), "bf16", dev)
-    eng = Engine(ew, dev, StateConfig(max_slots=1, max_seq_len=a.context + 64, kv_dtype=a.kv_cache_dtype), use_graphs=False)
+    eng = Engine(ew, dev, StateConfig(max_slots=1, max_seq_len=a.context + a.rows + 64, kv_dtype=a.kv_cache_dtype), use_graphs=False)
     ops, st = eng.ops, eng.state
     s = eng.open_sequence()
     eng._reserve(s, a.context + a.rows + 1)

@@ -367,9 +367,13 @@ __global__ void __launch_bounds__(256) gdn_chunk_scan_kernel(const GdnScanArgs a
                     fma8(R0, qv0[dd], s0, s1); fma8(R1, qv1[dd], s0, s1);
                 }
             }
-            float* d0 = sD + (2 * r2) * PS + cb;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) { d0[j] -= P0[j]; d0[PS + j] -= P1[j]; }
+            float4* d0 = reinterpret_cast<float4*>(sD + (2 * r2) * PS + cb);
+            float4* d1 = reinterpret_cast<float4*>(sD + (2 * r2 + 1) * PS + cb);
+            float4 u;
+            u = d0[0]; d0[0] = make_float4(u.x - P0[0], u.y - P0[1], u.z - P0[2], u.w - P0[3]);
+            u = d0[1]; d0[1] = make_float4(u.x - P0[4], u.y - P0[5], u.z - P0[6], u.w - P0[7]);
+            u = d1[0]; d1[0] = make_float4(u.x - P1[0], u.y - P1[1], u.z - P1[2], u.w - P1[3]);
+            u = d1[1]; d1[1] = make_float4(u.x - P1[4], u.y - P1[5], u.z - P1[6], u.w - P1[7]);
         }
         __syncthreads();
         // ---- O = R + QKd Delta (row 2 r2 sees s <= 2 r2, row 2 r2 + 1 one more)
@@ -395,9 +399,12 @@ __global__ void __launch_bounds__(256) gdn_chunk_scan_kernel(const GdnScanArgs a
         for (int d4 = t / 8; d4 * 4 < DK; d4 += 32) {
             float acc[4][8];
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-#pragma unroll
-                for (int j = 0; j < 8; ++j) acc[i][j] = DC * sS[(4 * d4 + i) * PS + cb + j];
+            for (int i = 0; i < 4; ++i) {
+                const float4 a0 = *reinterpret_cast<const float4*>(sS + (4 * d4 + i) * PS + cb);
+                const float4 a1 = *reinterpret_cast<const float4*>(sS + (4 * d4 + i) * PS + cb + 4);
+                acc[i][0] = DC * a0.x; acc[i][1] = DC * a0.y; acc[i][2] = DC * a0.z; acc[i][3] = DC * a0.w;
+                acc[i][4] = DC * a1.x; acc[i][5] = DC * a1.y; acc[i][6] = DC * a1.z; acc[i][7] = DC * a1.w;
+            }
 #pragma unroll 2
             for (int s = 0; s < kChunk; ++s) {
                 const float4 kv = *reinterpret_cast<const float4*>(sKd + s * PK + 4 * d4);
@@ -405,9 +412,10 @@ __global__ void __launch_bounds__(256) gdn_chunk_scan_kernel(const GdnScanArgs a
                 fma8(acc[0], kv.x, s0, s1); fma8(acc[1], kv.y, s0, s1); fma8(acc[2], kv.z, s0, s1); fma8(acc[3], kv.w, s0, s1);
             }
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-#pragma unroll
-                for (int j = 0; j < 8; ++j) sS[(4 * d4 + i) * PS + cb + j] = acc[i][j];
+            for (int i = 0; i < 4; ++i) {
+                *reinterpret_cast<float4*>(sS + (4 * d4 + i) * PS + cb) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+                *reinterpret_cast<float4*>(sS + (4 * d4 + i) * PS + cb + 4) = make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
+            }
         }
     }
     __syncthreads();

@@ -49,7 +49,15 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __shared__ int s_abort;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile_m = blockIdx.y, tile_n = blockIdx.x;
+    // Rasterisation: the M tiles of a band of up to 16 vary fastest, so the CTAs that run together share
+    // a few weight tiles (each read from HBM once and then served by L2) and the whole activation band.
+    const int tiles_m = (g.M + kBM - 1) / kBM, tiles_n = (g.N + BN - 1) / BN;
+    const int band = tiles_m < 16 ? tiles_m : 16;
+    const int per_band = band * tiles_n;
+    const int first_m = ((int)blockIdx.x / per_band) * band;
+    const int gm = min(band, tiles_m - first_m);
+    const int in_band = (int)blockIdx.x - (first_m / band) * per_band;
+    const int tile_m = first_m + in_band % gm, tile_n = in_band / gm;
     const int k_iters = (g.K + kBK - 1) / kBK;
 
     if (threadIdx.x == 0) {
@@ -208,7 +216,7 @@ static int launch_gemm(const void* a, int lda, const void* w, int ldw, const Gem
         cudaFuncSetAttribute(gemm_bf16_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         attr_set = true;
     }
-    dim3 grid((g.N + BN - 1) / BN, (g.M + kBM - 1) / kBM);
+    dim3 grid(((g.N + BN - 1) / BN) * ((g.M + kBM - 1) / kBM));
     gemm_bf16_tc_kernel<BN><<<grid, kGemmThreads, smem, stream>>>(map_a, map_w, g);
     return PS_LAUNCH_CHECK();
 }
