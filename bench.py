@@ -36,6 +36,8 @@ def _parse():
     ap.add_argument("--kv-dtype", default="bf16", choices=["bf16", "fp8_e4m3"])
     ap.add_argument("--prefill-chunk", type=int, default=2048)
     ap.add_argument("--quant-search", type=int, default=1)
+    ap.add_argument("--dflash2", type=int, default=1, help="also time DFlash2 speculative rounds (1 GPU only)")
+    ap.add_argument("--dflash2-tokens", type=int, default=48)
     ap.add_argument("--watchdog", type=int, default=1500,
                     help="seconds after which a hung run dumps every thread's stack to stderr and exits")
     return ap.parse_args()
@@ -90,6 +92,49 @@ def reference_arm(args):
     return 0
 
 
+def dflash2_arm(eng, cfg, dev, prompt, args):
+    """DFlash2 speculative decoding through the public decoder API with a random-init drafter of the
+    published 27B drafter shape.  Two acceptance regimes bracket a trained drafter: `chance` (the random
+    drafter's own proposals: ~0 accepted, so a round costs draft + 8-row verify for one token) and `oracle`
+    (proposals replaced by the target's own greedy continuation: every draft accepted).  Both must emit
+    exactly the plain greedy stream."""
+    import torch
+    from phaseshift_b200.models.dflash2.decoder import DFlash2SpecDecoder
+    from phaseshift_b200.models.dflash2.model import DFlash2Config, DFlash2Drafter, random_weights, tiny_drafter_config
+    n = args.dflash2_tokens
+    dcfg = DFlash2Config(vocab_size=cfg.vocab_size) if args.model == "27b" else tiny_drafter_config(cfg)
+    with torch.no_grad():
+        plain = eng.generate(prompt, n, prefill_chunk=args.prefill_chunk)
+        w = {k: v.to(torch.bfloat16) for k, v in random_weights(dcfg, 1, dev).items()}
+        drafter = DFlash2Drafter(dcfg, w, dev)
+        dec = DFlash2SpecDecoder(eng, drafter, num_drafts=7)
+        out = {}
+        full = list(prompt) + list(plain)
+        native_propose = drafter.propose
+        for mode in ("chance", "oracle"):
+            if mode == "oracle":
+                def propose(anchor, k, embed, lm_head, pos, allowed=None, _p=native_propose):
+                    _p(anchor, k, embed, lm_head, pos)          # the drafter still runs, its output is replaced
+                    return full[pos + 1: pos + 1 + k]
+                drafter.propose = propose
+            drafter.reset()
+            dec.stats = {k: 0 for k in dec.stats}
+            samp = dict(temperature=0.0, top_p=1.0, top_k=0, seed=0)
+            s = eng.open_sequence()
+            toks = [dec.prefill(s, prompt, args.prefill_chunk, samp)]
+            torch.cuda.synchronize(); t0 = time.perf_counter()
+            while len(toks) < n:
+                toks.extend(dec.round(s, toks[-1], toks[:-1], n - len(toks), samp))
+            torch.cuda.synchronize(); dt = time.perf_counter() - t0
+            eng.close_sequence(s)
+            r = max(1, dec.stats["rounds"])
+            out[mode] = {"tok_s": round((len(toks) - 1) / dt, 2), "round_ms": round(dt * 1e3 / r, 3), "rounds": r,
+                         "tokens_per_round": round((len(toks) - 1) / r, 3), "exact_match": toks[:n] == list(plain)[:n]}
+        out["num_drafts"] = 7
+        out["drafter"] = "random-init, %d layers, hidden %d (bf16, torch ops)" % (dcfg.num_hidden_layers, dcfg.hidden_size)
+    return out
+
+
 def main():
     args = _parse()
     if args.impl == "reference":
@@ -138,7 +183,8 @@ def main():
     build_s = time.time() - t0
     K, W = args.steps, args.warmup
     max_seq = args.context + 2 * (K + W) + 64
-    eng = Engine(ew, dev, StateConfig(max_slots=1, max_seq_len=max_seq, page_tokens=16, kv_dtype=args.kv_dtype), tp=tp)
+    eng = Engine(ew, dev, StateConfig(max_slots=1, max_seq_len=max_seq, page_tokens=16, kv_dtype=args.kv_dtype,
+                                      conv_ring=16, spec_rows=8), tp=tp)
     g = torch.Generator().manual_seed(1234)
     prompt = torch.randint(0, cfg.vocab_size, (args.context,), generator=g).tolist()
 
@@ -199,11 +245,25 @@ def main():
         checksum = int(gout.tokens[0])
         eng.close_sequence(s)
 
+        # ---------------- time to first token through the public API (warm): prefill + first sampled token on the host
+        ttft = []
+        for _ in range(3):
+            s2 = eng.open_sequence()
+            barrier(); t_a = time.perf_counter()
+            eng.prefill(s2, prompt, args.prefill_chunk)
+            torch.cuda.synchronize(); ttft.append((time.perf_counter() - t_a) * 1e3)
+            eng.close_sequence(s2)
+        ttft_ms = statistics.median(ttft)
+
+        dflash = None
+        if args.dflash2 and world == 1:
+            dflash = dflash2_arm(eng, cfg, dev, prompt, args)
+
     # max over ranks of the per-step time
-    t = torch.tensor([dev_ms, e2e_ms, prefill_ms], device=dev, dtype=torch.float64)
+    t = torch.tensor([dev_ms, e2e_ms, prefill_ms, ttft_ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    dev_ms, e2e_ms, prefill_ms = (float(x) for x in t.tolist())
+    dev_ms, e2e_ms, prefill_ms, ttft_ms = (float(x) for x in t.tolist())
     launches_per_step = eng.launches_per_graph.get(graph_key, 0)
     rd_bytes = ew.decode_read_bytes()
     peaks = {}
@@ -227,7 +287,10 @@ def main():
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8},
         "gpu_launches": launches_per_step * K,
         "launches_per_step": launches_per_step,
-        "prefill": {"tokens": args.context, "ms": round(prefill_ms, 2), "tok_s": round(args.context / prefill_ms * 1e3, 1)},
+        "prefill": {"tokens": args.context, "first_call_ms": round(prefill_ms, 2), "ms": round(ttft_ms, 2),
+                    "tok_s": round(args.context / ttft_ms * 1e3, 1)},
+        "ttft_p50_ms": round(ttft_ms, 2),
+        "dflash2": dflash,
         "weights_gb_per_step": round(rd_bytes / 1e9, 3),
         "hbm_roofline_frac_of_measured": round(rd_bytes / (dev_ms * 1e-3) / (hbm * 1e9), 4),
         "build_s": round(build_s, 1), "token_checksum": checksum, "impl": "ours",
