@@ -1,0 +1,150 @@
+// Stand-alone all-reduce over NVLink peer memory for prefill-sized activations (more rows than the
+// fused combine in the projection epilogue handles): out = sum over ranks of partial [rows, n] (bf16)
+// + residual, written as bf16.  Two variants:
+//
+//   * peer one-shot : every rank waits (bounded) until the same CTA of every peer has started -- which, by
+//     stream order on the peer, means the peer's partial is complete in its symmetric buffer -- then
+//     reads all `size` partials with plain peer loads and adds them in rank order 0..size-1 in fp32, so
+//     every rank holds bit-identical sums.  One launch, one barrier, no second pass.
+//   * multimem two-shot : rank r reduces the 16-byte chunks with (chunk % size == r) through the
+//     NVSwitch (`multimem.ld_reduce`, fp32 accumulation) and broadcasts them with `multimem.st` into
+//     every rank's result buffer; after a second barrier each rank adds the residual from its local
+//     copy.  Every element is reduced exactly once, so ranks agree bit for bit, and each GPU moves only
+//     1/size of the data through its links twice.
+//
+// Inputs are double-buffered by the parity of a per-CTA collective counter: a rank can be at most one
+// collective ahead of its slowest peer, so a buffer is rewritten only after every peer has finished
+// reading it.  Every wait is bounded by a clock budget and reports PS_DEV_WAIT_TIMEOUT through the status
+// word instead of hanging.  The reference's transport does leader-reduce + broadcast with a host
+// rendezvous per collective (src/phaseshift/runtime/tp/hip_peer_tp_transport.hip:314-369).
+#include "ps_common.cuh"
+
+namespace ps {
+
+constexpr int kArMaxRanks = 8;
+constexpr long long kArWaitCycles = 2000000000LL;     // ~1 s
+
+struct ArArgs {
+    int size, rank;
+    const __nv_bfloat16* in[kArMaxRanks];   // every rank's partial for this parity (peer pointers), dense [rows, n]
+    __nv_bfloat16* mc_in;                   // multicast address of the same buffer (multimem variant), else null
+    __nv_bfloat16* mc_res;                  // multicast address of the result buffer (multimem variant)
+    const __nv_bfloat16* res_local;         // local address of the result buffer (multimem variant)
+    uint32_t* flags[kArMaxRanks];           // rank r's flags: [2][grid][size]
+    uint32_t* counter;                      // local [grid]
+    const __nv_bfloat16* residual; int ld_res;
+    __nv_bfloat16* out; int ldo;
+    int rows, n;
+    uint32_t* status;
+};
+
+// Signal every peer and wait for every peer at (phase, this CTA).  Returns false on timeout.
+__device__ __forceinline__ bool ar_barrier(const ArArgs& a, int phase, uint32_t val, bool* s_fail) {
+    __syncthreads();
+    if (threadIdx.x < a.size) {
+        __threadfence_system();
+        const size_t base = ((size_t)phase * gridDim.x + blockIdx.x) * a.size;
+        uint32_t* f = a.flags[threadIdx.x] + base + a.rank;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(val) : "memory");
+        const uint32_t* mine = a.flags[a.rank] + base + threadIdx.x;
+        const long long t0 = clock64();
+        uint32_t seen;
+        do {
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+            if ((int32_t)(seen - val) >= 0) break;
+            if (clock64() - t0 > kArWaitCycles) { *s_fail = true; break; }
+        } while (true);
+    }
+    __syncthreads();
+    return !*s_fail;
+}
+
+__device__ __forceinline__ void acc_bf16x8(float (&acc)[8], const uint4& v) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = bf16x2_bits_to_f32x2(w[i]); acc[2 * i] += f.x; acc[2 * i + 1] += f.y; }
+}
+
+__device__ __forceinline__ void finish_chunk(const ArArgs& a, long long chunk, float (&acc)[8]) {
+    const int per_row = a.n >> 3;
+    const int row = (int)(chunk / per_row), col = (int)(chunk % per_row) << 3;
+    if (a.residual != nullptr) {
+        // the sum is rounded to bf16 before the residual add, like projection-then-add
+        const uint4 r = *reinterpret_cast<const uint4*>(a.residual + (size_t)row * a.ld_res + col);
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = bf16x2_bits_to_f32x2(w[i]);
+            acc[2 * i] = bf16_to_f32(f32_to_bf16(acc[2 * i])) + f.x;
+            acc[2 * i + 1] = bf16_to_f32(f32_to_bf16(acc[2 * i + 1])) + f.y;
+        }
+    }
+    *reinterpret_cast<uint4*>(a.out + (size_t)row * a.ldo + col) =
+        make_uint4(f32x2_to_bf16x2_bits(acc[0], acc[1]), f32x2_to_bf16x2_bits(acc[2], acc[3]),
+                   f32x2_to_bf16x2_bits(acc[4], acc[5]), f32x2_to_bf16x2_bits(acc[6], acc[7]));
+}
+
+__global__ void __launch_bounds__(256) allreduce_peer_kernel(const ArArgs a) {
+    __shared__ bool s_fail;
+    __shared__ uint32_t s_val;
+    if (threadIdx.x == 0) { s_fail = false; s_val = a.counter[blockIdx.x] + 1u; }
+    __syncthreads();
+    const uint32_t val = s_val;
+    if (!ar_barrier(a, 0, val, &s_fail)) { if (threadIdx.x == 0) set_status(a.status, PS_DEV_WAIT_TIMEOUT); return; }
+    if (threadIdx.x == 0) a.counter[blockIdx.x] = val;
+    const long long chunks = (long long)a.rows * (a.n >> 3);
+    for (long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x; c < chunks; c += (long long)gridDim.x * blockDim.x) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int r = 0; r < a.size; ++r) acc_bf16x8(acc, __ldcv(reinterpret_cast<const uint4*>(a.in[r]) + c));
+        finish_chunk(a, c, acc);
+    }
+}
+
+__global__ void __launch_bounds__(256) allreduce_multimem_kernel(const ArArgs a) {
+    __shared__ bool s_fail;
+    __shared__ uint32_t s_val;
+    if (threadIdx.x == 0) { s_fail = false; s_val = a.counter[blockIdx.x] + 1u; }
+    __syncthreads();
+    const uint32_t val = s_val;
+    if (!ar_barrier(a, 0, val, &s_fail)) { if (threadIdx.x == 0) set_status(a.status, PS_DEV_WAIT_TIMEOUT); return; }
+    const long long chunks = (long long)a.rows * (a.n >> 3);
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    // shot 1: reduce my share through the switch and broadcast it into every rank's result buffer
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i * a.size + a.rank < chunks; i += stride) {
+        const long long c = i * a.size + a.rank;
+        uint32_t x, y, z, w;
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(x), "=r"(y), "=r"(z), "=r"(w) : "l"(reinterpret_cast<const uint4*>(a.mc_in) + c) : "memory");
+        asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};"
+                     ::"l"(reinterpret_cast<uint4*>(a.mc_res) + c), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+    }
+    if (!ar_barrier(a, 1, val, &s_fail)) { if (threadIdx.x == 0) set_status(a.status, PS_DEV_WAIT_TIMEOUT); return; }
+    if (threadIdx.x == 0) a.counter[blockIdx.x] = val;
+    // shot 2: the CTA with the same index on rank (c % size) produced chunk c; read the local copy
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i * a.size < chunks; i += stride) {
+        for (int r = 0; r < a.size; ++r) {
+            const long long c = i * a.size + r;
+            if (c >= chunks) break;
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            acc_bf16x8(acc, __ldcv(reinterpret_cast<const uint4*>(a.res_local) + c));
+            finish_chunk(a, c, acc);
+        }
+    }
+}
+
+}  // namespace ps
+
+// `args` points to a host copy of ps::ArArgs.  n must be a multiple of 8; all buffers 16-byte aligned.
+// `grid` must be the same on every rank (flags are indexed by CTA).
+PS_API int ps_allreduce(const void* args, int use_multimem, int grid, cudaStream_t stream) {
+    using namespace ps;
+    const ArArgs& a = *reinterpret_cast<const ArArgs*>(args);
+    if (a.size < 1 || a.size > kArMaxRanks || a.rows <= 0 || (a.n & 7) || grid < 1) return (int)cudaErrorInvalidValue;
+    if (use_multimem) {
+        if (a.mc_in == nullptr || a.mc_res == nullptr || a.res_local == nullptr) return (int)cudaErrorInvalidValue;
+        allreduce_multimem_kernel<<<grid, 256, 0, stream>>>(a);
+    } else {
+        allreduce_peer_kernel<<<grid, 256, 0, stream>>>(a);
+    }
+    return PS_LAUNCH_CHECK();
+}

@@ -12,8 +12,11 @@ Two transports implement the combine:
 * ``fused`` (decode / verify, rows <= 8): the projection kernel itself pushes its fp32 partials into
   every peer's receive buffer over NVLink, signals per-CTA flags and adds the partials in rank order
   (``TpCombine`` in csrc/kernels/gemv_core.cuh).  No separate collective launch exists.
-* ``nccl`` (baseline, and prefill-sized activations): ``all_reduce`` on the partial projection, then a
-  residual-add kernel.  Also the path used on CPU (gloo) by the host-logic tests.
+* prefill-sized activations (rows > 8) under the fused transport: the stand-alone peer-memory
+  all-reduce kernel (csrc/kernels/allreduce.cu; peer one-shot by default, ``PS_TP_MULTIMEM=1`` selects
+  the NVSwitch ``multimem`` two-shot) with the residual add fused.
+* ``nccl`` (baseline): ``all_reduce`` on the partial projection, then a residual-add kernel.  Also the
+  path used on CPU (gloo) by the host-logic tests.
 
 Transport selection mirrors ``create_tp_transport`` + ``verify()`` in the reference
 (src/phaseshift/runtime/tp/tp_transports.cpp:81-110, hip_peer_tp_transport.hip:200-312): the fused
@@ -41,6 +44,18 @@ class TpCombineStruct(ctypes.Structure):
                 ("counter", ctypes.c_void_p), ("max_rows", ctypes.c_int), ("n_pad", ctypes.c_int)]
 
 
+class ArStruct(ctypes.Structure):
+    """Host twin of ps::ArArgs (csrc/kernels/allreduce.cu)."""
+    _fields_ = [("size", ctypes.c_int), ("rank", ctypes.c_int),
+                ("inp", ctypes.c_void_p * MAX_RANKS), ("mc_in", ctypes.c_void_p), ("mc_res", ctypes.c_void_p),
+                ("res_local", ctypes.c_void_p), ("flags", ctypes.c_void_p * MAX_RANKS), ("counter", ctypes.c_void_p),
+                ("residual", ctypes.c_void_p), ("ld_res", ctypes.c_int), ("out", ctypes.c_void_p), ("ldo", ctypes.c_int),
+                ("rows", ctypes.c_int), ("n", ctypes.c_int), ("status", ctypes.c_void_p)]
+
+
+AR_GRID = 128
+
+
 class TensorParallel:
     def __init__(self, group, device, transport: str = "auto"):
         self.group = group
@@ -50,7 +65,9 @@ class TensorParallel:
         self.transport = "nccl"
         self.combines: Dict[int, TpCombineStruct] = {}
         self._keep = []
-        self.stats = {"fused": 0, "nccl": 0}
+        self.stats = {"fused": 0, "nccl": 0, "peer_allreduce": 0}
+        self._ar = None                      # stand-alone all-reduce state (symmetric buffers), built on first use
+        self.use_multimem = os.environ.get("PS_TP_MULTIMEM", "0") == "1"
         want = os.environ.get("PS_TP_TRANSPORT", transport)
         if self.size > 1 and self.device.type == "cuda" and want in ("auto", "fused"):
             try:
@@ -68,7 +85,57 @@ class TensorParallel:
         t.zero_()
         hdl = sm.rendezvous(t, self.group.group_name)
         self._keep.append((t, hdl))
+        self._last_hdl = hdl
         return t, [int(p) for p in hdl.buffer_ptrs]
+
+    # ------------------------------------------------------------------ stand-alone all-reduce (rows > 8)
+    def _ar_state(self, nbytes: int):
+        """Symmetric input (two parities) / result buffers and flags for the all-reduce kernel; grown
+        collectively (every rank sees the same sequence of sizes)."""
+        st = self._ar
+        if st is not None and st["cap"] >= nbytes:
+            return st
+        cap = max(nbytes, 1 << 20)
+        cap = 1 << (cap - 1).bit_length()
+        inp, in_ptrs = self._symm_alloc(2 * cap)
+        mc_in = int(getattr(self._last_hdl, "multicast_ptr", 0) or 0)
+        res, res_ptrs = self._symm_alloc(cap)
+        mc_res = int(getattr(self._last_hdl, "multicast_ptr", 0) or 0)
+        _, flag_ptrs = self._symm_alloc(2 * AR_GRID * self.size * 4)
+        counter = torch.zeros(AR_GRID, dtype=torch.int32, device=self.device)
+        status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        torch.cuda.synchronize()
+        dist.barrier(self.group)
+        self._ar = dict(cap=cap, inp=inp, in_ptrs=in_ptrs, mc_in=mc_in, res=res, res_ptrs=res_ptrs, mc_res=mc_res,
+                        flag_ptrs=flag_ptrs, counter=counter, status=status, parity=0)
+        return self._ar
+
+    def peer_all_reduce(self, partial: torch.Tensor, residual: Optional[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
+        """out = sum over ranks of `partial` (+ residual) with this package's peer-memory kernel."""
+        from ..ops import _lib
+        rows, n = partial.shape
+        nbytes = rows * n * 2
+        st = self._ar_state(nbytes)
+        par = st["parity"]
+        st["inp"][par * st["cap"]: par * st["cap"] + nbytes].view(torch.bfloat16).copy_(partial.reshape(-1))
+        a = ArStruct()
+        a.size, a.rank, a.rows, a.n = self.size, self.rank, rows, n
+        for r in range(self.size):
+            a.inp[r] = st["in_ptrs"][r] + par * st["cap"]
+            a.flags[r] = st["flag_ptrs"][r]
+        multimem = self.use_multimem and st["mc_in"] != 0 and st["mc_res"] != 0
+        a.mc_in = (st["mc_in"] + par * st["cap"]) if multimem else None
+        a.mc_res = st["mc_res"] if multimem else None
+        a.res_local = st["res"].data_ptr()
+        a.counter = st["counter"].data_ptr()
+        a.residual = residual.data_ptr() if residual is not None else None
+        a.ld_res = residual.stride(0) if residual is not None else 0
+        a.out, a.ldo = out.data_ptr(), out.stride(0)
+        a.status = st["status"].data_ptr()
+        _lib.call("ps_allreduce", ctypes.byref(a), ctypes.c_int(1 if multimem else 0), ctypes.c_int(AR_GRID))
+        st["parity"] ^= 1
+        self.stats["peer_allreduce"] += 1
+        return out
 
     def combine_for(self, n: int) -> Optional[TpCombineStruct]:
         """Fused-combine descriptor for projections with `n` output features (allocated on first use;
@@ -97,11 +164,30 @@ class TensorParallel:
     # ------------------------------------------------------------------ baseline combine
     def all_reduce_residual(self, partial: torch.Tensor, residual: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         """out = sum_over_ranks(partial) + residual with the library collective (baseline / large rows)."""
+        if (self.transport == "fused" and self.size > 1 and partial.dtype == torch.bfloat16 and partial.is_contiguous()
+                and partial.shape[1] % 8 == 0 and out.dtype == torch.bfloat16):
+            return self.peer_all_reduce(partial, residual, out)
         self.stats["nccl"] += 1
         if self.size > 1:
             dist.all_reduce(partial, group=self.group)
         torch.add(partial, residual, out=out)
         return out
+
+    # ------------------------------------------------------------------ liveness
+    def start_monitor(self, store=None, interval_s: float = 0.2, timeout_s: float = 2.0):
+        """Start the host-side heartbeat (parallel/health.py); `assert_alive()` is then cheap to call between
+        steps and raises RankLostError before a launch that would wait for a dead peer."""
+        from .health import PeerMonitor
+        if store is None:
+            from torch.distributed.distributed_c10d import _get_default_store
+            store = _get_default_store()
+        self.monitor = PeerMonitor(store, self.rank, self.size, interval_s, timeout_s).start()
+        return self.monitor
+
+    def assert_alive(self) -> None:
+        m = getattr(self, "monitor", None)
+        if m is not None:
+            m.assert_alive()
 
     def disable_fused(self, why: str) -> None:
         if self.transport == "fused":

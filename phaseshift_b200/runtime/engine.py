@@ -84,6 +84,7 @@ class Engine:
         self.sc = state_cfg
         self.state = ModelState(self.cfg, state_cfg, self.device, self.ops.act_dtype, geo)
         self.runner = Qwen35Runner(weights, self.state, self.ops, tp)
+        self.tp = tp
         self.alloc = PageAllocator(self.state.num_pages, state_cfg.max_slots)
         self.seqs: Dict[int, Sequence_] = {}
         self.batches: Dict[int, StepBatch] = {}
@@ -167,6 +168,8 @@ class Engine:
         ``exact``: compute every row with single-row-decode arithmetic (the reference's VerifyNumericMode::Exact,
         include/phaseshift/runtime/execution/execution_types.h:6-27): projections stay on the batch-invariant
         small-M kernel instead of the tensor-core GEMM, so speculative verification reproduces plain decoding."""
+        if self.tp is not None:
+            self.tp.assert_alive()           # host-side heartbeat: never launch towards a peer that is gone
         n_rows = sum(len(r.token_ids) for r in rows)
         n_out = sum(len(r.output_rows) for r in rows)
         bucket = resolve_row_bucket(n_rows)

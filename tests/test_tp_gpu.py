@@ -39,6 +39,11 @@ def test_tp2_fused_matches_nccl_and_ranks_agree(preset, tmp_path):
     assert fused[0]["tokens"] == fused[1]["tokens"], "ranks must produce identical tokens"
     assert all(r["transport"] == "fused" and r["stats"]["fused"] > 0 and r["status"] == 0 for r in fused)
     assert fused[0]["graphs"] > 0, "the fused combine must be graph-capturable"
+    assert all(r["stats"]["peer_allreduce"] > 0 for r in fused), "prefill chunks must use the peer all-reduce kernel"
+    for r in fused:
+        for variant, ar in r["allreduce"].items():
+            assert ar["status"] == 0 and ar["rank_disagreement"] == 0.0, (variant, ar)
+            assert ar["max_err"] < 0.06, (variant, ar)
     assert all(r["transport"] == "nccl" for r in nccl) and nccl[0]["tokens"] == nccl[1]["tokens"]
     # same partial sums, different summation order and rounding (fp32 partials vs a bf16 all-reduce): the
     # tiny random model has nearly flat logits, so only the leading tokens are comparable

@@ -27,8 +27,29 @@ def main():
     eng = Engine(ew, dev, StateConfig(max_slots=1, max_seq_len=96), tp=tp)
     out = eng.generate(list(range(3, 27)), n_new, prefill_chunk=8)
     torch.cuda.synchronize()
+    # stand-alone peer-memory all-reduce (both variants) against the library collective
+    ar = {}
+    if tp.transport == "fused":
+        g = torch.Generator(device=dev).manual_seed(100 + rank)
+        for variant in ("peer", "multimem"):
+            tp.use_multimem = variant == "multimem"
+            errs = []
+            for rows in (9, 300, 300):
+                part = (torch.randn(rows, 512, device=dev, generator=g) * 0.5).to(torch.bfloat16)
+                resid = torch.randn(rows, 512, device=dev, generator=torch.Generator(device=dev).manual_seed(7)).to(torch.bfloat16)
+                got = torch.empty_like(part)
+                tp.peer_all_reduce(part, resid, got)
+                ref = part.float()
+                dist.all_reduce(ref)
+                ref = ref.to(torch.bfloat16).float() + resid.float()
+                errs.append(float((got.float() - ref).abs().max()))
+                gl = [torch.empty_like(got) for _ in range(world)]
+                dist.all_gather(gl, got)
+                errs.append(float(max((x.float() - got.float()).abs().max() for x in gl)))     # ranks agree bit for bit
+            ar[variant] = {"max_err": max(errs[0::2]), "rank_disagreement": max(errs[1::2]),
+                           "status": int(tp._ar["status"][0]), "multicast": bool(tp._ar["mc_in"])}
     res = {"rank": rank, "tokens": out, "transport": tp.transport, "stats": tp.stats,
-           "status": int(eng.ops.status[0]), "graphs": len(eng.graphs)}
+           "status": int(eng.ops.status[0]), "graphs": len(eng.graphs), "allreduce": ar}
     gathered = [None] * world
     dist.all_gather_object(gathered, res)
     if rank == 0:
