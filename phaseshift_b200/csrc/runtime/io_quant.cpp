@@ -330,7 +330,10 @@ void quantize_row_mxfp8(const float* w, int k, int k_padded, int search, const f
     for (int b0 = 0; b0 < k_padded; b0 += 32) {
         float amax = 0.f;
         for (int i = 0; i < 32; ++i) { blk[i] = (b0 + i < k) ? w[b0 + i] : 0.f; amax = std::max(amax, std::fabs(blk[i])); }
-        const float e0 = std::ceil(std::log2((amax > 0 ? amax : 1.0f) / 448.0f));
+        // ceil(log2(amax / 448)) in exact integer arithmetic (the device quantiser computes the same)
+        int fe;
+        const float fm = std::frexp((amax > 0 ? amax : 1.0f) / 448.0f, &fe);
+        const float e0 = (float)(fm == 0.5f ? fe - 1 : fe);
         double best_err = 0; int best_e = 0; uint8_t best_c[32];
         bool have = false;
         for (int step = -search; step <= search; ++step) {

@@ -91,6 +91,40 @@ def _pad_k(w: torch.Tensor) -> torch.Tensor:
     return out
 
 
+USE_CUDA_KERNELS = True     # CUDA tensors go through the dedicated quantiser kernels (bit-equal to the C++ ones)
+
+
+def _kernel_quantize(wf: torch.Tensor, fmt: str, k: int, kp: int, importance, search: int, tensor_scale: float):
+    """Row quantiser kernels (csrc/kernels/quant_kernels.cu).  `wf` is fp32 [N, kp] on a CUDA device."""
+    import ctypes
+    from ..ops import _lib
+    n = wf.shape[0]
+    dev = wf.device
+    nv = fmt == "nvfp4"
+    codes = torch.empty(n, kp // 2 if nv else kp, dtype=torch.uint8, device=dev)
+    scales = torch.empty(n, kp // (16 if nv else 32), dtype=torch.uint8, device=dev)
+    imp = None
+    if importance is not None:
+        imp = importance.float().reshape(-1).to(dev).contiguous()
+    with torch.cuda.device(dev):
+        _lib.call("ps_quantize_rows", ctypes.c_int(1 if nv else 0), ctypes.c_void_p(wf.data_ptr()), ctypes.c_longlong(wf.stride(0)),
+                  ctypes.c_int(n), ctypes.c_int(k), ctypes.c_int(kp), ctypes.c_float(tensor_scale), ctypes.c_int(search),
+                  ctypes.c_void_p(imp.data_ptr() if imp is not None else None), ctypes.c_void_p(codes.data_ptr()),
+                  ctypes.c_void_p(scales.data_ptr()))
+    return codes, scales
+
+
+def _kernels_ok(w: torch.Tensor) -> bool:
+    if not (USE_CUDA_KERNELS and w.is_cuda):
+        return False
+    try:
+        from ..ops import _lib
+        _lib.lib()
+        return True
+    except Exception:
+        return False
+
+
 def quantize_nvfp4(w: torch.Tensor, importance: Optional[torch.Tensor] = None, search: int = 2,
                    tensor_scale: Optional[float] = None) -> QuantizedTensor:
     """w [N, K] float -> NVFP4.  ``search`` = number of e4m3 scale steps tried on each side."""
@@ -100,6 +134,10 @@ def quantize_nvfp4(w: torch.Tensor, importance: Optional[torch.Tensor] = None, s
     amax_t = float(wf.abs().max())
     if tensor_scale is None:
         tensor_scale = amax_t / (6.0 * 448.0) if amax_t > 0 else 1.0
+    if _kernels_ok(wf):
+        ts = float(torch.tensor(tensor_scale, dtype=torch.float32))
+        codes, scales = _kernel_quantize(wf.contiguous(), "nvfp4", k, kp, importance, search, ts)
+        return QuantizedTensor("nvfp4", (n, k), kp, codes, scales, float(tensor_scale))
     blk = wf.reshape(n, kp // 16, 16)
     imp = None
     if importance is not None:
@@ -150,12 +188,17 @@ def quantize_mxfp8(w: torch.Tensor, importance: Optional[torch.Tensor] = None, s
     n, k = w.shape
     wf = _pad_k(w.float())
     kp = wf.shape[1]
+    if _kernels_ok(wf):
+        codes, scales = _kernel_quantize(wf.contiguous(), "mxfp8", k, kp, importance, search, 1.0)
+        return QuantizedTensor("mxfp8", (n, k), kp, codes, scales, 1.0)
     blk = wf.reshape(n, kp // 32, 32)
     imp = None
     if importance is not None:
         imp = _pad_k(importance.float().reshape(1, -1)).reshape(1, kp // 32, 32)
     amax = blk.abs().amax(-1)
-    e0 = torch.ceil(torch.log2(torch.where(amax > 0, amax, torch.ones_like(amax)) / 448.0))
+    # ceil(log2(amax / 448)) in exact integer arithmetic (same as the C++ and CUDA quantisers)
+    fm, fe = torch.frexp(torch.where(amax > 0, amax, torch.ones_like(amax)) / 448.0)
+    e0 = torch.where(fm == 0.5, fe - 1, fe).to(wf.dtype)
     best_err = best_e = best_c = None
     for step in range(-search, search + 1):
         e = (e0 + step).clamp(-126, 127)
