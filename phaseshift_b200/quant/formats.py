@@ -10,6 +10,16 @@ shape rules as the reference's canonical SoA payload, docs/developer/psq_canonic
 * ``mxfp8``: codes = E4M3 bytes [N, Kp]; metadata1 = UE8M0 exponent per 32 weights [N, Kp/32].
   w ~= e4m3(code) * 2^(e-127).  8.25 bpw.
 
+Two further formats are understood as *interchange* formats (checkpoints produced elsewhere), the
+counterparts of the reference's FP8-block128 and MXFP4 kernels (src/phaseshift/models/qwen35/kernels/
+optimized/linear/fp8_block128.hip, mxfp4.hip).  They have no kernels of their own: `to_kernel_format`
+re-expresses them in a format the sm_100a kernels consume.
+
+* ``mxfp4``: E2M1 nibbles as in ``nvfp4``; metadata1 = UE8M0 exponent per 32 weights.  4.25 bpw.  Runs as
+  NVFP4 without any loss: every MXFP4 block scale 2^e is representable as e4m3(2^(e-t)) * 2^t.
+* ``fp8_block128``: E4M3 bytes [N, Kp]; metadata1 = fp32 scale per 128 x 128 block [ceil(N/128), Kp/128].
+  Runs as MXFP8 after one re-quantisation (its scales are not powers of two).
+
 Block scales are chosen by a small search around the max-abs scale that minimises the block's
 squared error, the counterpart of the reference's 65-candidate PSQ scale search
 (src/phaseshift/quantization/psq/psq.cpp:39-74); an optional per-input-channel importance vector
@@ -26,7 +36,8 @@ import torch
 E2M1_VALUES = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
 _E2M1_BOUNDS = (0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0)
 FORMATS = ("bf16", "nvfp4", "mxfp8")
-BLOCK = {"bf16": 16, "nvfp4": 16, "mxfp8": 32}
+INTERCHANGE_FORMATS = ("mxfp4", "fp8_block128")
+BLOCK = {"bf16": 16, "nvfp4": 16, "mxfp8": 32, "mxfp4": 32, "fp8_block128": 128}
 K_ALIGN = 32
 DEFAULT_SEARCH = 2      # scale-search half-width used by quantize() (0 = plain max-abs scales)
 
@@ -235,7 +246,75 @@ def quantize(w: torch.Tensor, fmt: str, importance: Optional[torch.Tensor] = Non
     if fmt == "bf16":
         n, k = w.shape
         return QuantizedTensor("bf16", (n, k), k, w.to(torch.bfloat16).contiguous(), None, 1.0)
+    if fmt == "mxfp4":
+        return quantize_mxfp4(w)
+    if fmt == "fp8_block128":
+        return quantize_fp8_block128(w)
     raise ValueError(f"unknown weight format {fmt!r}")
+
+
+def quantize_mxfp4(w: torch.Tensor) -> QuantizedTensor:
+    """OCP MXFP4: E2M1 codes with one power-of-two scale per 32 weights (scale = 2^(floor(log2(amax)) - 2))."""
+    n, k = w.shape
+    wf = _pad_k(w.float())
+    kp = wf.shape[1]
+    blk = wf.reshape(n, kp // 32, 32)
+    amax = blk.abs().amax(-1)
+    _, fe = torch.frexp(torch.where(amax > 0, amax, torch.ones_like(amax)))     # amax = f * 2^fe, f in [0.5, 1)
+    e = (fe - 1 - 2).clamp(-127, 127)                                           # emax of E2M1 is 2
+    r = blk / torch.exp2(e.float())[..., None]
+    idx = _e2m1_index(r.abs())
+    q = idx.to(torch.uint8) | ((r < 0).to(torch.uint8) << 3)
+    q = torch.where(idx == 0, torch.zeros_like(q), q).reshape(n, kp)
+    codes = (q[:, 0::2] | (q[:, 1::2] << 4)).contiguous()
+    return QuantizedTensor("mxfp4", (n, k), kp, codes, (e + 127).to(torch.uint8).contiguous(), 1.0)
+
+
+def dequantize_mxfp4(q: QuantizedTensor) -> torch.Tensor:
+    n, k = q.shape
+    c = q.codes
+    nib = torch.stack([c & 0xF, c >> 4], -1).reshape(n, q.k_padded)
+    v = _e2m1_value(nib & 7) * torch.where((nib & 8) != 0, -1.0, 1.0)
+    s = torch.exp2(q.scales.float() - 127.0)
+    return (v.reshape(n, q.k_padded // 32, 32) * s[..., None]).reshape(n, q.k_padded)[:, :k].contiguous()
+
+
+def quantize_fp8_block128(w: torch.Tensor) -> QuantizedTensor:
+    """E4M3 codes with one fp32 scale (amax / 448) per 128 x 128 block; `scales` is a float32 tensor."""
+    n, k = w.shape
+    kp = align_up(k, 128)
+    npad = align_up(n, 128)
+    wf = w.new_zeros(npad, kp, dtype=torch.float32)
+    wf[:n, :k] = w.float()
+    blk = wf.reshape(npad // 128, 128, kp // 128, 128)
+    amax = blk.abs().amax(dim=(1, 3))
+    s = torch.where(amax > 0, amax / 448.0, torch.ones_like(amax))
+    codes = _to_e4m3_bytes(blk / s[:, None, :, None]).reshape(npad, kp)[:n].contiguous()
+    return QuantizedTensor("fp8_block128", (n, k), kp, codes, s.contiguous(), 1.0)
+
+
+def dequantize_fp8_block128(q: QuantizedTensor) -> torch.Tensor:
+    n, k = q.shape
+    s = q.scales.float().repeat_interleave(128, 0)[:n].repeat_interleave(128, 1)[:, :q.k_padded]
+    return (_from_e4m3_bytes(q.codes) * s)[:, :k].contiguous()
+
+
+def to_kernel_format(q: QuantizedTensor) -> QuantizedTensor:
+    """Re-express an interchange-format tensor in a format the kernels execute (identity otherwise)."""
+    if q.fmt == "mxfp4":
+        # lossless: codes unchanged, scale 2^e per 32 -> the same UE4M3 byte for both 16-blocks, with a
+        # power-of-two tensor scale chosen so every block exponent fits UE4M3's normal range [2^-6, 2^8]
+        e = q.scales.to(torch.int32) - 127
+        live = q.codes.reshape(q.shape[0], -1, 16).ne(0).any(-1)                # all-zero blocks may take any scale
+        t = int(e[live].max()) - 8 if bool(live.any()) else 0
+        rel = (e - t).clamp(min=-6)
+        if bool((rel[live] < -6).any()):
+            return quantize_nvfp4(dequantize_mxfp4(q), search=DEFAULT_SEARCH)   # range too wide: re-quantise
+        sb = ((rel + 7) << 3).to(torch.uint8)                                   # e4m3 byte of 2^rel (mantissa 0)
+        return QuantizedTensor("nvfp4", q.shape, q.k_padded, q.codes, sb.repeat_interleave(2, 1).contiguous(), float(2.0 ** t))
+    if q.fmt == "fp8_block128":
+        return quantize_mxfp8(dequantize_fp8_block128(q), search=min(DEFAULT_SEARCH, 1))
+    return q
 
 
 def dequantize(q: QuantizedTensor) -> torch.Tensor:
@@ -243,8 +322,12 @@ def dequantize(q: QuantizedTensor) -> torch.Tensor:
         return dequantize_nvfp4(q)
     if q.fmt == "mxfp8":
         return dequantize_mxfp8(q)
+    if q.fmt == "mxfp4":
+        return dequantize_mxfp4(q)
+    if q.fmt == "fp8_block128":
+        return dequantize_fp8_block128(q)
     return q.codes.float()[:, :q.shape[1]]
 
 
 def bits_per_weight(fmt: str) -> float:
-    return {"bf16": 16.0, "nvfp4": 4.5, "mxfp8": 8.25}[fmt]
+    return {"bf16": 16.0, "nvfp4": 4.5, "mxfp8": 8.25, "mxfp4": 4.25, "fp8_block128": 8.002}[fmt]

@@ -79,3 +79,27 @@ def test_imatrix_collect_and_weighted_quantize(model_dirs):
     offline.quantize_model(src, out, preset="nvfp4", backend="cpu", imatrix=str(im), imatrix_policy="best-effort",
                            log=lambda *_: None)
     assert offline.validate_model_dir(out) == [] and Manifest.load(out).imatrix["file"] == str(im)
+
+
+def test_interchange_formats_roundtrip_and_kernel_conversion():
+    """MXFP4 and FP8-block128 (interchange formats): quantise/dequantise, and re-expression in the formats the
+    kernels execute -- lossless for MXFP4 -> NVFP4, one e4m3 re-rounding for FP8-block128 -> MXFP8."""
+    import torch
+    from phaseshift_b200.quant import formats as F
+    g = torch.Generator().manual_seed(0)
+    w = torch.randn(40, 200, generator=g) * 0.05
+    w[3, :64] = 0
+    w[7] *= 30
+    q4 = F.quantize(w, "mxfp4")
+    d4 = F.dequantize(q4)
+    assert q4.codes.shape == (40, 112) and q4.scales.shape == (40, 7)
+    assert float((d4 - w).norm() / w.norm()) < 0.13
+    k4 = F.to_kernel_format(q4)
+    assert k4.fmt == "nvfp4" and torch.equal(F.dequantize(k4), d4)
+    q8 = F.quantize(w, "fp8_block128")
+    d8 = F.dequantize(q8)
+    assert q8.scales.dtype == torch.float32 and q8.scales.shape == (1, 2)
+    assert float((d8 - w).norm() / w.norm()) < 0.04
+    k8 = F.to_kernel_format(q8)
+    assert k8.fmt == "mxfp8" and float((F.dequantize(k8) - d8).norm() / d8.norm()) < 0.04
+    assert F.to_kernel_format(F.quantize(w, "nvfp4")).fmt == "nvfp4"
