@@ -152,7 +152,7 @@ def quantize_nvfp4(w: torch.Tensor, importance: Optional[torch.Tensor] = None, s
     blk = wf.reshape(n, kp // 16, 16)
     imp = None
     if importance is not None:
-        imp = _pad_k(importance.float().reshape(1, -1)).reshape(1, kp // 16, 16)
+        imp = _pad_k(importance.float().reshape(1, -1)).reshape(1, kp // 16, 16).to(wf.device)
     base = blk.abs().amax(-1) / 6.0 / tensor_scale                      # ideal block scale in e4m3 units
     base_b = _to_e4m3_bytes(base).to(torch.int16)
     best_err = None
@@ -205,7 +205,7 @@ def quantize_mxfp8(w: torch.Tensor, importance: Optional[torch.Tensor] = None, s
     blk = wf.reshape(n, kp // 32, 32)
     imp = None
     if importance is not None:
-        imp = _pad_k(importance.float().reshape(1, -1)).reshape(1, kp // 32, 32)
+        imp = _pad_k(importance.float().reshape(1, -1)).reshape(1, kp // 32, 32).to(wf.device)
     amax = blk.abs().amax(-1)
     # ceil(log2(amax / 448)) in exact integer arithmetic (same as the C++ and CUDA quantisers)
     fm, fe = torch.frexp(torch.where(amax > 0, amax, torch.ones_like(amax)) / 448.0)
