@@ -234,6 +234,17 @@ class CudaOps:
         self.launches += 1
         return out.view(-1)[:n]
 
+    def topk(self, logits: torch.Tensor, k: int, mask: Optional[torch.Tensor] = None):
+        """Exact top-k (k <= 128) per row of fp32 logits, sorted descending, ties to the lower id.
+        Returns (ids int32 [rows, k], values fp32 [rows, k]); `mask` is an optional allowed-token bitmask."""
+        rows, vocab = logits.shape
+        ids = self.buf("topk_ids", rows, k, torch.int32)
+        vals = self.buf("topk_vals", rows, k, torch.float32)
+        _lib.call("ps_topk", ptr(logits), c_ll(logits.stride(0)), c_int(vocab), c_int(rows), c_int(k), ptr(mask),
+                  c_int(mask.shape[1] if mask is not None else 0), ptr(ids), ptr(vals))
+        self.launches += 1
+        return ids, vals
+
     def rmsnorm(self, x: torch.Tensor, w: torch.Tensor, eps: float, name: str, one_plus: bool = True,
                 add: Optional[torch.Tensor] = None, sum_out: Optional[torch.Tensor] = None) -> torch.Tensor:
         rows, H = x.shape

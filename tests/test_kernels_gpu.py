@@ -447,3 +447,41 @@ def test_dflash2_exact_verify_on_gpu():
         dec2.drafter.propose = lambda a, k, e, l, pos, allowed=None: full[pos + 1: pos + 1 + k]
         out2, stats2 = dec2.generate(prompt, 24, prefill_chunk=8)
         assert out2 == plain and stats2["accepted"] == stats2["proposed"], (preset, stats2)
+
+
+def test_radix_topk_matches_sort_and_breaks_ties_by_id():
+    cfg = tiny_config()
+    cu, _ = _ops(cfg)
+    g = torch.Generator(device="cuda").manual_seed(21)
+    logits = torch.randn(5, 151936, device="cuda", generator=g) * 4
+    logits[1, 777] = float("inf")
+    logits[2, :] = logits[2, :].round()                     # heavy ties, also at the threshold
+    logits[3, 100:200] = 50.0                               # 100 equal maxima: ids 100..131 must win for k = 32
+    for k in (1, 16, 32, 128):
+        ids, vals = cu.topk(logits, k)
+        torch.cuda.synchronize()
+        order = torch.sort(logits.double() * 1e6 - torch.arange(logits.shape[1], device="cuda").double() * 1e-3, dim=1,
+                           descending=True).indices[:, :k] if False else None
+        for r in range(5):
+            row = logits[r]
+            ref_v = torch.sort(row, descending=True).values[:k]
+            assert torch.equal(vals[r], ref_v), (k, r)
+            assert torch.equal(row[ids[r].long()], ref_v)                    # ids point at those values
+            # ties: among equal values the ids ascend, and no lower id with the same value was skipped
+            v, i = vals[r].tolist(), ids[r].tolist()
+            assert all(not (v[j] == v[j + 1] and i[j] > i[j + 1]) for j in range(k - 1))
+            thr = v[-1]
+            eq_ids = (row == thr).nonzero().flatten().tolist()
+            taken = [x for x, vv in zip(i, v) if vv == thr]
+            assert taken == eq_ids[:len(taken)]
+    # constrained: only the allowed tokens compete; fewer allowed than k pads with -1
+    mask = torch.zeros(5, (151936 + 31) // 32, dtype=torch.int32, device="cuda")
+    allowed = [5, 64, 1000, 150000]
+    for a in allowed:
+        mask[:, a // 32] |= (1 << (a % 32))
+    ids, vals = cu.topk(logits, 8, mask=mask)
+    torch.cuda.synchronize()
+    for r in range(5):
+        got = [x for x in ids[r].tolist() if x >= 0]
+        assert sorted(got) == allowed and ids[r, 4:].tolist() == [-1] * 4
+        assert got == sorted(allowed, key=lambda a: (-float(logits[r, a]), a))
