@@ -253,17 +253,48 @@ def _window_logits(eng, ids: Sequence[int], chunk: int = 512) -> torch.Tensor:
         for c0 in range(0, len(ids), chunk):
             part = list(ids[c0:c0 + chunk])
             _, out = eng.step([SeqRows(s.slot, s.position, part, tuple(range(len(part))))], [s], sample=False)
-            outs.append(out.logits[:len(part)].float().cpu())
+            outs.append(out.logits[:len(part)].float().clone())
     finally:
         eng.close_sequence(s)
     return torch.cat(outs, 0)
 
 
+def _vp(t: torch.Tensor):
+    import ctypes
+    return ctypes.c_void_p(t.data_ptr())
+
+
 def kl_divergence(base_logits: torch.Tensor, test_logits: torch.Tensor) -> torch.Tensor:
-    """Per-position KL(p_base || p_test) in nats, computed in fp64."""
+    """Per-position KL(p_base || p_test) in nats: the reduction kernel on CUDA tensors
+    (csrc/kernels/quant_kernels.cu), fp64 torch math otherwise."""
+    if base_logits.is_cuda and base_logits.dtype == torch.float32 and test_logits.dtype == torch.float32:
+        import ctypes
+        from ..ops import _lib
+        b, t = base_logits.contiguous(), test_logits.contiguous()
+        rows, vocab = b.shape
+        kl = torch.empty(rows, dtype=torch.float32, device=b.device)
+        agree = torch.empty(rows, dtype=torch.int32, device=b.device)
+        with torch.cuda.device(b.device):
+            _lib.call("ps_kld_rows", _vp(b), _vp(t), ctypes.c_int(rows), ctypes.c_int(vocab), ctypes.c_longlong(vocab), _vp(kl), _vp(agree))
+        return kl.double().cpu()
     lp = torch.log_softmax(base_logits.double(), -1)
     lq = torch.log_softmax(test_logits.double(), -1)
-    return (lp.exp() * (lp - lq)).sum(-1)
+    return (lp.exp() * (lp - lq)).sum(-1).cpu()
+
+
+def nll_rows(logits: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+    """-log softmax(logits)[target] per row (kernel on CUDA fp32 logits, fp64 torch math otherwise)."""
+    if logits.is_cuda and logits.dtype == torch.float32:
+        import ctypes
+        from ..ops import _lib
+        lg = logits.contiguous()
+        tg = targets.to(lg.device, torch.int32).contiguous()
+        out = torch.empty(lg.shape[0], dtype=torch.float32, device=lg.device)
+        with torch.cuda.device(lg.device):
+            _lib.call("ps_nll_rows", _vp(lg), _vp(tg), ctypes.c_int(lg.shape[0]), ctypes.c_int(lg.shape[1]), ctypes.c_longlong(lg.shape[1]), _vp(out))
+        return out.double().cpu()
+    lp = torch.log_softmax(logits.double(), -1)
+    return (-lp[torch.arange(logits.shape[0]), targets.long().to(lp.device)]).cpu()
 
 
 def kld_report(kl: torch.Tensor, top1_agree: float) -> dict:
@@ -297,8 +328,7 @@ def evaluate_ppl(model_dir, tokens: Sequence[int], max_tokens: int = 2048, devic
     ids = list(tokens[:max_tokens])
     eng = _engine_for(model_dir, device, len(ids) + 1)
     lg = _window_logits(eng, ids)
-    lp = torch.log_softmax(lg[:-1].double(), -1)
-    nll = -lp[torch.arange(len(ids) - 1), torch.tensor(ids[1:])]
+    nll = nll_rows(lg[:-1], torch.tensor(ids[1:]))
     return {"tokens": len(ids) - 1, "nll": float(nll.mean()), "ppl": float(nll.mean().exp())}
 
 
@@ -312,6 +342,17 @@ def collect_imatrix(model_dir, tokens: Sequence[int], output, window: int = 512,
     counts: Dict[str, int] = {}
 
     def collector(tag: str, x: torch.Tensor) -> None:
+        if x.is_cuda and x.dtype == torch.bfloat16 and x.stride(1) == 1:
+            import ctypes
+            from ..ops import _lib
+            if tag not in sums:
+                sums[tag] = torch.zeros(x.shape[1], dtype=torch.float32, device=x.device)
+                counts[tag] = 0
+            with torch.cuda.device(x.device):
+                _lib.call("ps_imatrix_accumulate", _vp(x), ctypes.c_longlong(x.stride(0)), ctypes.c_int(x.shape[0]),
+                          ctypes.c_int(x.shape[1]), _vp(sums[tag]))
+            counts[tag] += x.shape[0]
+            return
         v = x.float().pow(2).sum(0).cpu()
         if tag in sums:
             sums[tag] += v
