@@ -26,6 +26,7 @@ def _model_args(p):
     p.add_argument("--preset", default=None); p.add_argument("--device", default=None)
     p.add_argument("--kv-cache-dtype", default="bf16", choices=["bf16", "fp8_e4m3"])
     p.add_argument("--runs", type=int, default=3); p.add_argument("--warmup", type=int, default=1); p.add_argument("--output")
+    p.add_argument("--batch-shadow", type=int, default=0, help="keep resident bf16 weights for batched steps (2 B/weight)")
 
 
 def build_parser() -> argparse.ArgumentParser:
@@ -70,7 +71,8 @@ def _engine(a, max_seq_len: int, slots: int = 1):
     else:
         cfg = PRESETS[a.random_model or "tiny"]()
         ew = build_engine_weights(cfg, random_getter(cfg, 0, dev), a.preset or "bf16", dev, keep_canonical=dev.type != "cuda")
-    return Engine(ew, dev, StateConfig(max_slots=slots, max_seq_len=max_seq_len, kv_dtype=a.kv_cache_dtype)), dev
+    return Engine(ew, dev, StateConfig(max_slots=slots, max_seq_len=max_seq_len, kv_dtype=a.kv_cache_dtype),
+                  batch_shadow=bool(getattr(a, "batch_shadow", 0))), dev
 
 
 def _timed(dev, fn):

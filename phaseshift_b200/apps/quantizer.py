@@ -13,7 +13,7 @@ def build_parser() -> argparse.ArgumentParser:
     sub = ap.add_subparsers(dest="cmd", required=True)
     q = sub.add_parser("quantize", help="BF16 model directory -> self-contained quantised directory")
     q.add_argument("--input", required=True); q.add_argument("--output", required=True)
-    q.add_argument("--preset", default="nvfp4", choices=["nvfp4", "mxfp8", "bf16"])
+    q.add_argument("--preset", default="nvfp4", choices=["nvfp4", "mxfp8", "bf16", "mxfp4"])
     q.add_argument("--backend", default="cpu", choices=["cpu", "cuda"])
     q.add_argument("--scope", default="text-only", choices=["text-only"])
     q.add_argument("--imatrix"); q.add_argument("--imatrix-policy", default="strict", choices=["strict", "best-effort"])

@@ -23,7 +23,7 @@ namespace ps {
 
 enum GemmEpilogue : int { GEPI_STORE = 0, GEPI_RESIDUAL = 1, GEPI_SWIGLU = 2 };
 
-constexpr int kBM = 128, kBK = 64, kGemmStages = 4;
+constexpr int kBM = 128, kBK = 64;
 constexpr int kGemmThreads = 192;
 
 struct GemmArgs {
@@ -32,10 +32,14 @@ struct GemmArgs {
     const __nv_bfloat16* residual; int ld_res;
     void* out; int ldo; int out_f32;
     uint32_t* status;
+    int a_box_rows;      // rows fetched per A tile (a multiple of 8, <= 128); the rest of the tile stays zero
 };
 
-template <int BN>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+// BN x kGemmStages x CTAs per SM: <256, 4, 1> / <128, 4, 1> for prefill-sized M; <32, 5, 2> for M <= 128 (batched decode
+// on resident bf16 weights), where the problem is a weight stream: narrow N tiles give every SM a slice even
+// when N is 5120, and two co-resident CTAs per SM keep ~40 KB of weights in flight without wave quantisation.
+template <int BN, int kGemmStages, int kMinBlocks>
+__global__ void __launch_bounds__(kGemmThreads, kMinBlocks)
 gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const GemmArgs g) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -59,6 +63,12 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int in_band = (int)blockIdx.x - (first_m / band) * per_band;
     const int tile_m = first_m + in_band % gm, tile_n = in_band / gm;
     const int k_iters = (g.K + kBK - 1) / kBK;
+    const int a_bytes = g.a_box_rows * kBK * 2;            // bytes one TMA load of A delivers
+    if (g.a_box_rows < kBM) {
+        // few-row problems fetch only the rows that exist; the remaining rows of every A stage are zeroed once
+        for (int i = threadIdx.x; i < kGemmStages * kABytes / 16; i += kGemmThreads) reinterpret_cast<uint4*>(sA)[i] = make_uint4(0, 0, 0, 0);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // make the zeros visible to the tensor core's async reads
+    }
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kGemmStages; ++s) { tc::mbar_init(&full_bar[s], 1); tc::mbar_init(&empty_bar[s], 1); }
@@ -84,7 +94,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const int s = it % kGemmStages;
                 const uint32_t ph = (uint32_t)(it / kGemmStages) & 1u;
                 if (it >= kGemmStages && !tc::mbar_wait(&empty_bar[s], ph ^ 1u)) { atomicExch(&s_abort, 1); break; }
-                tc::mbar_expect_tx(&full_bar[s], kABytes + kBBytes);
+                tc::mbar_expect_tx(&full_bar[s], a_bytes + kBBytes);
                 tc::tma_load_2d(sA + s * kABytes, &map_a, it * kBK, tile_m * kBM, &full_bar[s]);
                 tc::tma_load_2d(sB + s * kBBytes, &map_w, it * kBK, tile_n * BN, &full_bar[s]);
             }
@@ -203,21 +213,22 @@ static int make_map_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64
     return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
-template <int BN>
+template <int BN, int kGemmStages, int kMinBlocks>
 static int launch_gemm(const void* a, int lda, const void* w, int ldw, const GemmArgs& g, cudaStream_t stream) {
     CUtensorMap map_a, map_w;
-    int err = make_map_2d(&map_a, a, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)lda, kBM);
+    int err = make_map_2d(&map_a, a, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)lda, (uint32_t)g.a_box_rows);
     if (err) return err;
     err = make_map_2d(&map_w, w, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)ldw, BN);
     if (err) return err;
     const size_t smem = (size_t)kGemmStages * (kBM * kBK * 2 + BN * kBK * 2) + 1024;
     static bool attr_set = false;
     if (!attr_set) {
-        cudaFuncSetAttribute(gemm_bf16_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(gemm_bf16_tc_kernel<BN, kGemmStages, kMinBlocks>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(gemm_bf16_tc_kernel<BN, kGemmStages, kMinBlocks>, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
         attr_set = true;
     }
     dim3 grid(((g.N + BN - 1) / BN) * ((g.M + kBM - 1) / kBM));
-    gemm_bf16_tc_kernel<BN><<<grid, kGemmThreads, smem, stream>>>(map_a, map_w, g);
+    gemm_bf16_tc_kernel<BN, kGemmStages, kMinBlocks><<<grid, kGemmThreads, smem, stream>>>(map_a, map_w, g);
     return PS_LAUNCH_CHECK();
 }
 
@@ -235,6 +246,8 @@ PS_API int ps_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, int M
     GemmArgs g;
     g.M = M; g.N = N; g.K = K; g.epilogue = epilogue; g.residual = (const __nv_bfloat16*)residual; g.ld_res = ld_res;
     g.out = out; g.ldo = ldo; g.out_f32 = out_f32; g.status = (uint32_t*)status;
-    if (N >= 256) return launch_gemm<256>(a, lda, w, ldw, g, stream);
-    return launch_gemm<128>(a, lda, w, ldw, g, stream);
+    g.a_box_rows = M >= kBM ? kBM : ((M + 7) / 8) * 8;
+    if (M <= kBM && N >= 512) return launch_gemm<32, 5, 2>(a, lda, w, ldw, g, stream);
+    if (N >= 256) return launch_gemm<256, 4, 1>(a, lda, w, ldw, g, stream);
+    return launch_gemm<128, 4, 1>(a, lda, w, ldw, g, stream);
 }

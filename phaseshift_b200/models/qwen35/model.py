@@ -76,7 +76,8 @@ class Qwen35Runner:
                 n_main = m.in_proj.N
                 if hasattr(ops, "buf"):
                     proj = ops.buf("gdn_proj", rows, n_main + m.ba_proj.N)
-                    if rows <= FUSED_BA_MAX_ROWS:
+                    batched = rows >= 2 and m.in_proj.shadow is not None and not ops.exact_rows
+                    if rows <= FUSED_BA_MAX_ROWS and not batched:
                         # decode / verify: the GDN kernel projects beta/decay inputs itself from the
                         # normalised row that in_proj leaves behind -> one launch fewer per layer
                         xn = ops.buf("gdn_xn", rows, x.shape[1])

@@ -22,7 +22,7 @@ from typing import Callable, Dict, List, Optional
 
 import torch
 
-from ...quant.formats import QuantizedTensor, dequantize, quantize
+from ...quant.formats import QuantizedTensor, dequantize, quantize, to_kernel_format
 from .config import Qwen35Config
 
 P = "model.language_model."
@@ -107,6 +107,7 @@ class LinearW:
     _kpad: int = 0
     _fmt: str = ""
     _tscale: float = 1.0
+    shadow: Optional[torch.Tensor] = None      # optional resident bf16 expansion [N, k_padded] for batched steps
 
     def __post_init__(self):
         self._shape, self._kpad, self._fmt, self._tscale = self.q.shape, self.q.k_padded, self.q.fmt, self.q.tensor_scale
@@ -117,6 +118,22 @@ class LinearW:
             self.tiled = tile_weight(self.q)
         if not keep_canonical:
             self.q = None
+        return self
+
+    def make_shadow(self) -> "LinearW":
+        """Keep a resident bf16 expansion of the weights (2 B/weight) so that steps with several rows run the
+        tensor-core GEMM straight from it instead of re-expanding or streaming the block codes once per row."""
+        if self.shadow is None:
+            import ctypes
+            from ...ops import _lib
+            from ...ops.cuda_ops import WFMT
+            if self.tiled is None:
+                self.make_tiled()
+            self.shadow = torch.empty(self.N, self._kpad, dtype=torch.bfloat16, device=self.tiled.device)
+            with torch.cuda.device(self.tiled.device):
+                _lib.call("ps_dequant_tiled", ctypes.c_int(WFMT[self._fmt]), ctypes.c_void_p(self.tiled.data_ptr()), ctypes.c_int(self.N),
+                          ctypes.c_int(self._kpad), ctypes.c_float(self._tscale), ctypes.c_void_p(self.shadow.data_ptr()),
+                          ctypes.c_int(self._kpad))
         return self
 
     @property
@@ -209,6 +226,23 @@ class EngineWeights:
                 n += m.qkv_proj.nbytes + m.o_proj.nbytes
         return n
 
+    def linears(self) -> List[LinearW]:
+        """Every projection a step multiplies by (the embedding table is a gather, not a projection)."""
+        out = [self.lm_head]
+        for l in self.layers:
+            m = l.mixer
+            out += [l.gate_up, l.down] + ([m.in_proj, m.ba_proj, m.out_proj] if l.kind == 0 else [m.qkv_proj, m.o_proj])
+        return out
+
+    def make_shadows(self) -> int:
+        """Resident bf16 expansions for batched steps (see LinearW.make_shadow); returns the bytes added."""
+        n = 0
+        for w in self.linears():
+            if w.fmt != "bf16" or True:
+                w.make_shadow()
+                n += w.shadow.numel() * 2
+        return n
+
     def decode_read_bytes(self) -> int:
         """Weight bytes one decode step must stream from HBM (everything except the embedding table)."""
         return self.weight_bytes() - self.embed.nbytes
@@ -229,6 +263,12 @@ def format_for(preset: str, role: str, layer: int) -> str:
         if role in ("ffn_down", "gdn_qkvz", "gdn_out"):
             return "mxfp8" if layer % 4 == 0 else "nvfp4"
         return "nvfp4"
+    if preset in ("mxfp4", "fp8_block128"):
+        # interchange presets: big projections in the named format (re-expressed for the kernels at load),
+        # vocabulary matrices in MXFP8, the small GDN projections in BF16
+        if role in ("embed", "lm_head"):
+            return "mxfp8"
+        return "bf16" if role == "gdn_small" else preset
     raise ValueError(f"unknown preset {preset!r}")
 
 
@@ -301,7 +341,7 @@ class DenseSource:
         imp = self.importance(parts[0][0]) if self.importance is not None else None
         if imp is not None and parts[0][2] is not None:
             imp = imp[parts[0][2].start:parts[0][2].stop]
-        return quantize(w.to(self.device), fmt, imp)
+        return to_kernel_format(quantize(w.to(self.device), fmt, imp))
 
 
 class QuantizedSource:
@@ -340,13 +380,15 @@ class QuantizedSource:
                 c = c[rr.start:rr.stop]
                 sc = None if sc is None else sc[rr.start:rr.stop]
             if kr is not None:
-                blk = {"bf16": 1, "nvfp4": 32, "mxfp8": 32}[fmt]
+                blk = {"bf16": 1, "nvfp4": 32, "mxfp8": 32, "mxfp4": 32}[fmt]
                 if kr.start % blk or kr.stop % blk:
                     raise ValueError(f"K range {kr} of {name} is not aligned to {blk}")
                 if fmt == "nvfp4":
                     c, sc = c[:, kr.start // 2:kr.stop // 2], sc[:, kr.start // 16:kr.stop // 16]
                 elif fmt == "mxfp8":
                     c, sc = c[:, kr.start:kr.stop], sc[:, kr.start // 32:kr.stop // 32]
+                elif fmt == "mxfp4":
+                    c, sc = c[:, kr.start // 2:kr.stop // 2], sc[:, kr.start // 32:kr.stop // 32]
                 else:
                     c = c[:, kr.start:kr.stop]
                 k = kr.stop - kr.start
@@ -360,8 +402,10 @@ class QuantizedSource:
         c = cat(codes).contiguous().to(self.device)
         sc = None if scales[0] is None else cat(scales).contiguous().to(self.device)
         n = c.shape[0]
-        kp = {"bf16": c.shape[1], "nvfp4": c.shape[1] * 2, "mxfp8": c.shape[1]}[fmt]
-        return QuantizedTensor(fmt, (n, k_log), kp, c, sc, float(tscale))
+        if fmt not in ("bf16", "nvfp4", "mxfp8", "mxfp4"):
+            raise ValueError(f"{parts[0][0]}: encoding {fmt!r} cannot be loaded from a model directory")
+        kp = {"bf16": c.shape[1], "nvfp4": c.shape[1] * 2, "mxfp8": c.shape[1], "mxfp4": c.shape[1] * 2}[fmt]
+        return to_kernel_format(QuantizedTensor(fmt, (n, k_log), kp, c, sc, float(tscale)))
 
 
 def build_engine_weights(cfg: Qwen35Config, get, preset: str = "bf16", device="cpu", tp_rank: int = 0,

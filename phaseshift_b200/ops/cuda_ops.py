@@ -93,7 +93,10 @@ class CudaOps:
         assert out.shape[0] == M and out.shape[1] == n_out and out.stride(1) == 1
         if tp_combine is not None and M > SMALL_M_MAX:
             raise ValueError("the fused tensor-parallel combine handles at most 8 rows")
-        if M > SMALL_M_MAX and self.use_tc_gemm and not self.exact_rows:
+        # tensor-core GEMM: prefill-sized steps, and batched steps (>= 2 rows) when a resident bf16 expansion of
+        # the weights exists (Fast mode only: Exact verification stays on the batch-invariant streaming kernel)
+        batched = M >= 2 and W.shadow is not None and tp_combine is None and xn_out is None
+        if (M > SMALL_M_MAX or batched) and self.use_tc_gemm and not self.exact_rows:
             return self.linear_large(x, W, name=name, norm_w=norm_w, eps=eps, residual=residual, swiglu=swiglu,
                                      out_f32=out_f32, out=out)
         pro = PRO_RMSNORM if norm_w is not None else PRO_NONE
@@ -126,17 +129,36 @@ class CudaOps:
         if W.tiled is None:
             W.make_tiled()
         kp = W.k_padded
-        need = W.N * kp
-        if self.wscratch is None or self.wscratch.numel() < need:
-            self.wscratch = torch.empty(need, dtype=torch.bfloat16, device=self.device)
-        wd = self.wscratch[:need].view(W.N, kp)
-        _lib.call("ps_dequant_tiled", c_int(WFMT[W.fmt]), ptr(W.tiled), c_int(W.N), c_int(kp),
-                  c_float(W.tensor_scale), ptr(wd), c_int(kp))
+        if W.shadow is not None:
+            wd = W.shadow
+        else:
+            need = W.N * kp
+            if self.wscratch is None or self.wscratch.numel() < need:
+                self.wscratch = torch.empty(need, dtype=torch.bfloat16, device=self.device)
+            wd = self.wscratch[:need].view(W.N, kp)
+            _lib.call("ps_dequant_tiled", c_int(WFMT[W.fmt]), ptr(W.tiled), c_int(W.N), c_int(kp),
+                      c_float(W.tensor_scale), ptr(wd), c_int(kp))
+            self.launches += 1
         epi = EPI_SWIGLU if swiglu else (EPI_RESIDUAL if residual is not None else EPI_STORE)
+        if W.shadow is not None and M <= 64 and W.N % 2 == 0:
+            # batched decode: swap-AB split-K weight-streaming GEMM (gemm_smallm.cu)
+            L = _lib.lib()
+            L.ps_gemm_smallm_splits.restype = ctypes.c_int
+            splits = L.ps_gemm_smallm_splits(c_int(W.N), c_int(kp))
+            need = splits * M * W.N
+            part = self.ws.get(("smallm_partial", 0))
+            if part is None or part.numel() < need:
+                part = torch.empty(max(need, 1 << 22), dtype=torch.float32, device=self.device)
+                self.ws[("smallm_partial", 0)] = part
+            _lib.call("ps_gemm_smallm", ptr(a), c_int(a.stride(0)), ptr(wd), c_int(kp), c_int(M), c_int(W.N), c_int(kp), c_int(epi),
+                      ptr(residual), c_int(residual.stride(0) if residual is not None else 0), ptr(out), c_int(out.stride(0)),
+                      c_int(1 if out_f32 else 0), ptr(part), ptr(self.status))
+            self.launches += 2
+            return out
         _lib.call("ps_gemm_bf16_tc", ptr(a), c_int(a.stride(0)), ptr(wd), c_int(kp), c_int(M), c_int(W.N), c_int(kp),
                   c_int(epi), ptr(residual), c_int(residual.stride(0) if residual is not None else 0), ptr(out),
                   c_int(out.stride(0)), c_int(1 if out_f32 else 0), ptr(self.status))
-        self.launches += 2
+        self.launches += 1
         return out
 
     def attn_prep(self, qkv: torch.Tensor, aw: AttnW, hq: int, hkv: int, b: StepBatch, kv: KVLayer,

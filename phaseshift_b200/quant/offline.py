@@ -84,6 +84,10 @@ def imatrix_key(name: str) -> str:
 def _quantize_tensor(w: torch.Tensor, fmt: str, backend: str, tensor_scale: Optional[float], importance, search: int):
     if fmt == "bf16":
         return formats.quantize(w, "bf16")
+    if fmt == "mxfp4":
+        return formats.quantize_mxfp4(w.to("cuda") if backend == "cuda" else w).to("cpu")
+    if fmt not in ("nvfp4", "mxfp8"):
+        raise ValueError(f"the quantizer cannot write {fmt!r} bundles")
     if backend == "cuda":
         wd = w.to("cuda").float()
         imp = None if importance is None else importance.to("cuda")
@@ -148,7 +152,7 @@ def quantize_model(input_dir, output_dir, preset: str = "nvfp4", backend: str = 
             writer.add(n, torch.bfloat16 if len(shape) else torch.bfloat16, shape)
         else:
             kp = formats.align_up(shape[1], formats.K_ALIGN)
-            writer.add(n + CODES, torch.uint8, [shape[0], kp // 2 if fmt == "nvfp4" else kp])
+            writer.add(n + CODES, torch.uint8, [shape[0], kp // 2 if fmt in ("nvfp4", "mxfp4") else kp])
             writer.add(n + META1, torch.uint8, [shape[0], kp // (16 if fmt == "nvfp4" else 32)])
     writer.begin()
     tscale_cache: Dict[str, float] = {}
@@ -228,7 +232,7 @@ def validate_model_dir(model_dir) -> List[str]:
             if e.k_padded != kp:
                 problems.append(f"{n}: k_padded {e.k_padded} != {kp}")
             _, cs, _ = col.spec(e.codes)
-            want = [e.logical_shape[0], kp // 2 if e.encoding == "nvfp4" else kp]
+            want = [e.logical_shape[0], kp // 2 if e.encoding in ("nvfp4", "mxfp4") else kp]
             if list(cs) != want:
                 problems.append(f"{n}: codes shape {cs} != {want}")
     col.close()

@@ -68,7 +68,11 @@ class PageAllocator:
 
 class Engine:
     def __init__(self, weights: EngineWeights, device, state_cfg: StateConfig, backend: str = "auto", tp=None,
-                 use_graphs: bool = True):
+                 use_graphs: bool = True, batch_shadow: bool = False):
+        """``batch_shadow``: keep a resident bf16 expansion of every projection (2 bytes per weight on top of the
+        block-quantised copy) so steps with two or more rows run the tensor-core GEMM on it: a batched decode step
+        then costs about one pass over the bf16 weights whatever the number of rows, instead of one pass over the
+        block codes per row.  Single-row decode and Exact verification keep streaming the quantised weights."""
         self.cfg: Qwen35Config = weights.cfg
         self.device = torch.device(device)
         if backend == "auto":
@@ -85,6 +89,7 @@ class Engine:
         self.state = ModelState(self.cfg, state_cfg, self.device, self.ops.act_dtype, geo)
         self.runner = Qwen35Runner(weights, self.state, self.ops, tp)
         self.tp = tp
+        self.shadow_bytes = weights.make_shadows() if (batch_shadow and backend == "cuda") else 0
         self.alloc = PageAllocator(self.state.num_pages, state_cfg.max_slots)
         self.seqs: Dict[int, Sequence_] = {}
         self.batches: Dict[int, StepBatch] = {}

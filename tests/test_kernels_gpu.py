@@ -485,3 +485,50 @@ def test_radix_topk_matches_sort_and_breaks_ties_by_id():
         got = [x for x in ids[r].tolist() if x >= 0]
         assert sorted(got) == allowed and ids[r, 4:].tolist() == [-1] * 4
         assert got == sorted(allowed, key=lambda a: (-float(logits[r, a]), a))
+
+
+def test_batched_steps_on_resident_bf16_weights_match_streaming():
+    """With batch_shadow the 2..8-row steps run the tensor-core GEMM on resident bf16 weights; results must agree
+    with the streaming path within bf16 rounding, and single-row decode must be unaffected (bit-identical)."""
+    from phaseshift_b200.runtime.engine import Engine
+    cfg = tiny_config()
+    hf = random_hf_weights(cfg, seed=0)
+    prompt = torch.randint(0, cfg.vocab_size, (19,), generator=torch.Generator().manual_seed(3)).tolist()
+    for preset in ("nvfp4", "bf16"):
+        outs = []
+        for shadow in (False, True):
+            ew = build_engine_weights(cfg, lambda n: hf[n], preset, "cuda")
+            eng = Engine(ew, "cuda", StateConfig(max_slots=4, max_seq_len=96), batch_shadow=shadow)
+            assert (eng.shadow_bytes > 0) == shadow
+            single = eng.generate(prompt, 6, prefill_chunk=64)
+            seqs = [eng.open_sequence() for _ in range(3)]
+            for i, s in enumerate(seqs):
+                eng.prefill(s, prompt[i:], 64)
+            rows = [SeqRows(s.slot, s.position, [5 + i], (0,)) for i, s in enumerate(seqs)]
+            _, out = eng.step(rows, seqs, want_logits=True, commit=False)
+            outs.append((single, out.logits[:3].float().clone()))
+            for s in seqs:
+                eng.close_sequence(s)
+        assert outs[0][0] == outs[1][0], "single-row decode must not depend on the shadow copy"
+        assert _rel_err(outs[1][1], outs[0][1]) < 3e-2, preset
+
+
+@pytest.mark.parametrize("shape", [(3, 5120, 5120), (8, 1024, 17408), (64, 34816, 512), (128, 600, 256)])
+def test_tcgen05_gemm_small_m_weight_streaming(shape):
+    M, N, K = shape
+    cfg = tiny_config()
+    cu, _ = _ops(cfg)
+    g = torch.Generator(device="cuda").manual_seed(M + N)
+    a = (torch.randn(M, K, device="cuda", generator=g)).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    res = torch.randn(M, N, device="cuda", generator=g).to(torch.bfloat16)
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    import ctypes
+    from phaseshift_b200.ops import _lib
+    vp = lambda t: ctypes.c_void_p(t.data_ptr())
+    _lib.call("ps_gemm_bf16_tc", vp(a), ctypes.c_int(K), vp(w), ctypes.c_int(K), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
+              ctypes.c_int(1), vp(res), ctypes.c_int(N), vp(out), ctypes.c_int(N), ctypes.c_int(0), vp(cu.status))
+    torch.cuda.synchronize()
+    ref = (a.float() @ w.float().T).to(torch.bfloat16).float() + res.float()
+    assert _rel_err(out.float(), ref) < 4e-3
+    assert int(cu.status[0]) == 0

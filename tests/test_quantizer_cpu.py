@@ -103,3 +103,34 @@ def test_interchange_formats_roundtrip_and_kernel_conversion():
     k8 = F.to_kernel_format(q8)
     assert k8.fmt == "mxfp8" and float((F.dequantize(k8) - d8).norm() / d8.norm()) < 0.04
     assert F.to_kernel_format(F.quantize(w, "nvfp4")).fmt == "nvfp4"
+
+
+def test_mxfp4_bundle_loads_and_runs_as_nvfp4(tmp_path):
+    """An OCP-MXFP4 model directory written by the quantizer loads through the NVFP4 path without re-quantisation
+    loss: the engine built from the bundle and the engine built from the dequantised MXFP4 weights emit the same
+    tokens; the in-memory interchange presets build too."""
+    import torch
+    from phaseshift_b200.io.model_dir import save_hf_model
+    from phaseshift_b200.models.qwen35.config import tiny_config
+    from phaseshift_b200.models.qwen35.weights import build_engine_weights, load_engine_weights, random_hf_weights
+    from phaseshift_b200.quant import offline
+    from phaseshift_b200.runtime.engine import Engine
+    from phaseshift_b200.runtime.state import StateConfig
+    cfg = tiny_config()
+    hf = random_hf_weights(cfg, seed=2)
+    src = tmp_path / "bf16"
+    save_hf_model(src, cfg, hf)
+    out = tmp_path / "mxfp4"
+    man = offline.quantize_model(src, out, "mxfp4", "cpu")
+    assert any(t.encoding == "mxfp4" for t in man.tensors)
+    assert offline.validate_model_dir(out) == []
+    ew = load_engine_weights(out, "cpu")
+    assert ew.layers[0].gate_up.fmt == "nvfp4"
+    prompt = list(range(5, 25))
+    toks = Engine(ew, "cpu", StateConfig(max_slots=1, max_seq_len=64)).generate(prompt, 8, prefill_chunk=16)
+    ew2 = build_engine_weights(cfg, lambda n: hf[n], "mxfp4", "cpu")
+    toks2 = Engine(ew2, "cpu", StateConfig(max_slots=1, max_seq_len=64)).generate(prompt, 8, prefill_chunk=16)
+    assert toks == toks2
+    ew3 = build_engine_weights(cfg, lambda n: hf[n], "fp8_block128", "cpu")
+    assert ew3.layers[0].gate_up.fmt == "mxfp8"
+    assert len(Engine(ew3, "cpu", StateConfig(max_slots=1, max_seq_len=64)).generate(prompt, 4, prefill_chunk=16)) == 4
