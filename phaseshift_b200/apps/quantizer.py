@@ -26,6 +26,7 @@ def build_parser() -> argparse.ArgumentParser:
     k.add_argument("--report"); k.add_argument("--window", type=int, default=512); k.add_argument("--stride", type=int, default=512)
     k.add_argument("--max-eval-tokens", type=int, default=0); k.add_argument("--self", dest="self_check", action="store_true")
     k.add_argument("--device", default=None)
+    k.add_argument("--baseline-cache", default=None, help="directory that keeps the baseline model's logits between runs")
     i = sub.add_parser("imatrix", help="collect per-channel activation importance")
     i.add_argument("--input", help="unused alias of --model-dir"); i.add_argument("--model-dir", required=True)
     i.add_argument("--tokens", required=True); i.add_argument("--output", required=True)
@@ -60,11 +61,13 @@ def main(argv: Optional[List[str]] = None) -> int:
             return 0 if not problems else 1
         elif a.cmd == "kld":
             rep = offline.evaluate_kld(a.input, a.bundle, offline.read_tokens(a.tokens), a.window, a.stride,
-                                       a.max_eval_tokens, _device(a.device), a.self_check)
+                                       a.max_eval_tokens, _device(a.device), a.self_check, a.baseline_cache)
             if a.report:
                 open(a.report, "w").write(json.dumps(rep, indent=1))
             for k in ("positions", "mean", "p50", "p90", "p99", "p99_9", "max", "top1_agreement"):
                 print(f"KLD_{k.upper()}={rep[k]}")
+            if a.baseline_cache:
+                print(f"KLD_BASELINE_CACHE_HITS={rep['baseline_cache_hits']}"); print(f"KLD_BASELINE_CACHE_MISSES={rep['baseline_cache_misses']}")
         elif a.cmd == "imatrix":
             rep = offline.collect_imatrix(a.model_dir, offline.read_tokens(a.tokens), a.output, a.window, a.stride,
                                           a.max_calibration_tokens, _device(a.device))

@@ -11,6 +11,8 @@ activation energy at every projection input; ``evaluate_ppl`` reports teacher-fo
 """
 from __future__ import annotations
 
+import os
+
 import hashlib
 import json
 import shutil
@@ -307,24 +309,80 @@ def kld_report(kl: torch.Tensor, top1_agree: float) -> dict:
             "p99_9": q(0.999), "max": float(kl.max()), "top1_agreement": top1_agree}
 
 
+class BaselineLogitCache:
+    """On-disk cache of the baseline model's logits, one file per evaluation window, keyed by the source model's
+    fingerprint, the window's token ids and its position: repeated `kld` runs against different bundles of the same
+    source (the usual sweep over presets) run the BF16 baseline only once.  Logits are stored as bf16-rounded fp16
+    pairs would lose range, so they are kept in fp32; a 512-token window of a 152 k vocabulary is ~300 MB, hence
+    the cache is opt-in (`--baseline-cache DIR`) and bounded by `max_bytes` (oldest files are evicted)."""
+
+    def __init__(self, directory, fingerprint: str, max_bytes: int = 64 << 30):
+        self.dir = Path(directory)
+        self.dir.mkdir(parents=True, exist_ok=True)
+        self.fp, self.max_bytes = fingerprint, max_bytes
+        self.hits = self.misses = 0
+
+    def _path(self, w0: int, ids: Sequence[int]) -> Path:
+        import hashlib
+        h = hashlib.sha256()
+        h.update(self.fp.encode()); h.update(str(w0).encode()); h.update(torch.tensor(list(ids), dtype=torch.int32).numpy().tobytes())
+        return self.dir / (h.hexdigest()[:32] + ".pt")
+
+    def get(self, w0: int, ids: Sequence[int]) -> Optional[torch.Tensor]:
+        p = self._path(w0, ids)
+        if p.exists():
+            try:
+                t = torch.load(p, map_location="cpu")
+                if t.shape[0] == len(ids):
+                    self.hits += 1
+                    os.utime(p)
+                    return t
+            except Exception:
+                p.unlink(missing_ok=True)
+        self.misses += 1
+        return None
+
+    def put(self, w0: int, ids: Sequence[int], logits: torch.Tensor) -> None:
+        p = self._path(w0, ids)
+        tmp = p.with_suffix(".tmp")
+        torch.save(logits.float().cpu(), tmp)
+        os.replace(tmp, p)
+        files = sorted(self.dir.glob("*.pt"), key=lambda f: f.stat().st_mtime)
+        total = sum(f.stat().st_size for f in files)
+        while total > self.max_bytes and len(files) > 1:
+            f = files.pop(0)
+            total -= f.stat().st_size
+            f.unlink(missing_ok=True)
+
+
 def evaluate_kld(input_dir, bundle_dir, tokens: Sequence[int], window: int = 512, stride: int = 512,
-                 max_eval_tokens: int = 0, device="cpu", self_check: bool = False) -> dict:
-    base = _engine_for(input_dir, device, window + 1)
-    test = base if self_check else _engine_for(bundle_dir, device, window + 1)
+                 max_eval_tokens: int = 0, device="cpu", self_check: bool = False, baseline_cache=None) -> dict:
+    cache = BaselineLogitCache(baseline_cache, model_fingerprint(input_dir)) if baseline_cache else None
+    base = None                                   # built lazily: a fully cached run never loads the baseline model
+    test = None if self_check else _engine_for(bundle_dir, device, window + 1)
     kls, agree, total = [], 0, 0
     n = len(tokens) if max_eval_tokens <= 0 else min(len(tokens), max_eval_tokens)
     for w0 in range(0, max(1, n - 1), stride):
         ids = tokens[w0:w0 + window]
         if len(ids) < 2:
             break
-        lb = _window_logits(base, ids)
+        lb = cache.get(w0, ids) if cache is not None else None
+        if lb is None:
+            if base is None:
+                base = _engine_for(input_dir, device, window + 1)
+            lb = _window_logits(base, ids)
+            if cache is not None:
+                cache.put(w0, ids, lb)
         lt = lb if self_check else _window_logits(test, ids)
+        lb = lb.to(lt.device)
         kls.append(kl_divergence(lb, lt))
         agree += int((lb.argmax(-1) == lt.argmax(-1)).sum())
         total += lb.shape[0]
     kl = torch.cat(kls)
     rep = kld_report(kl, agree / max(1, total))
     rep.update(window=window, stride=stride, baseline=str(input_dir), bundle=str(bundle_dir))
+    if cache is not None:
+        rep.update(baseline_cache_hits=cache.hits, baseline_cache_misses=cache.misses)
     return rep
 
 

@@ -57,6 +57,13 @@ def test_quantize_verify_load_and_eval(model_dirs):
     rep = offline.evaluate_kld(src, out, toks, window=32, stride=32)
     assert rep["positions"] > 60 and 0 <= rep["mean"] < 0.05 and rep["max"] >= rep["p99"] >= rep["p50"] >= 0
     selfrep = offline.evaluate_kld(src, out, toks, window=32, stride=32, self_check=True)
+    # baseline-logit cache: the second run reads every window from disk and reports the same numbers
+    cdir = d / "kld_cache"
+    r1 = offline.evaluate_kld(src, out, toks, window=32, stride=32, baseline_cache=cdir)
+    r2 = offline.evaluate_kld(src, out, toks, window=32, stride=32, baseline_cache=cdir)
+    assert r1["baseline_cache_misses"] > 0 and r1["baseline_cache_hits"] == 0
+    assert r2["baseline_cache_misses"] == 0 and r2["baseline_cache_hits"] == r1["baseline_cache_misses"]
+    assert abs(r1["mean"] - rep["mean"]) < 1e-12 and abs(r2["mean"] - rep["mean"]) < 1e-9
     assert selfrep["max"] < 1e-9 and selfrep["top1_agreement"] == 1.0
     ppl = offline.evaluate_ppl(out, toks, max_tokens=48)
     assert ppl["ppl"] > 1.0
