@@ -106,7 +106,7 @@ def dflash2_arm(eng, cfg, dev, prompt, args):
     with torch.no_grad():
         plain = eng.generate(prompt, n, prefill_chunk=args.prefill_chunk)
         w = {k: v.to(torch.bfloat16) for k, v in random_weights(dcfg, 1, dev).items()}
-        drafter = DFlash2Drafter(dcfg, w, dev)
+        drafter = DFlash2Drafter(dcfg, w, dev, torch.bfloat16)
         dec = DFlash2SpecDecoder(eng, drafter, num_drafts=7)
         out = {}
         full = list(prompt) + list(plain)

@@ -50,6 +50,8 @@ class DFlash2SpecDecoder:
         self.eng, self.drafter, self.k = engine, drafter, num_drafts
         self.ngram_tail, self.ngram_n = ngram_tail, ngram_n
         self.rt = runtime()
+        if hasattr(engine.ops, "topk"):
+            drafter.topk_fn = engine.ops.topk              # exact radix top-k kernel for the candidate sets
         self.taps = list(drafter.cfg.target_layer_ids)
         cfg = engine.cfg
         rows = 16 if num_drafts + 1 + ngram_tail > 8 else 8

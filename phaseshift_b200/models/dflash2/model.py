@@ -277,18 +277,25 @@ class DFlash2Drafter:
         return self.select(h, logits, anchor)
 
     def select(self, h: torch.Tensor, logits: torch.Tensor, anchor: int) -> List[int]:
-        """Exact top-k (logit desc, id asc) then the sequential candidate selector chain."""
+        """Exact top-k (logit desc, id asc) then the sequential candidate selector chain.  The chain runs on the
+        device without reading intermediate winners back: one host synchronisation per proposal."""
         c = self.cfg
         kk = min(c.selector_top_k, logits.shape[-1])
-        # stable tie rule: higher logit first, lower id first among equals
-        order = torch.argsort(logits, dim=-1, descending=True, stable=True)[:, :kk]
-        top_l = torch.gather(logits, 1, order)
+        topk = getattr(self, "topk_fn", None)
+        if topk is not None and logits.is_cuda and logits.dtype == torch.float32 and kk <= 128:
+            order, top_l = topk(logits.contiguous(), kk)          # radix top-k kernel: same tie rule
+            order, top_l = order.long(), top_l.clone()
+        else:
+            # stable tie rule: higher logit first, lower id first among equals
+            order = torch.argsort(logits, dim=-1, descending=True, stable=True)[:, :kk]
+            top_l = torch.gather(logits, 1, order)
         hproj = (h @ self.w["selector.hidden_projection.weight"].T).float()     # [K, rank]
         pred, succ = self.w["selector.pred_codebook"].float(), self.w["selector.succ_codebook"].float()
-        out, prev = [], anchor
+        prev = torch.tensor(anchor, device=logits.device)
+        picks = []
         for r in range(h.shape[0]):
             score = top_l[r] + (pred[prev] * hproj[r]) @ succ[order[r]].T
-            j = int(torch.argmax(score))                   # first maximal index = best-ranked candidate on ties
-            prev = int(order[r, j])
-            out.append(prev)
-        return out
+            j = torch.argmax(score)                        # first maximal index = best-ranked candidate on ties
+            prev = order[r, j]
+            picks.append(prev)
+        return torch.stack(picks).tolist() if picks else []
