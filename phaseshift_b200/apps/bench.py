@@ -278,6 +278,25 @@ def cmd_tp_reduce(a) -> int:
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
             if rank == 0:
                 print(f"tp_reduce transport={name} ranks={world} rows={m} hidden={H} payload_bytes={m * H * 2} p50_us={float(t):.2f}")
+    # stand-alone all-reduce kernels against the library collective on prefill-sized payloads
+    if tp is not None and tp.transport == "fused":
+        for m in (256, 2048):
+            part = (torch.randn(m, H, device=dev) * 0.1).to(torch.bfloat16)
+            res = torch.zeros(m, H, device=dev, dtype=torch.bfloat16); out = torch.empty_like(part)
+            cases = [("peer", lambda: (setattr(tp, "use_multimem", False), tp.peer_all_reduce(part, res, out))),
+                     ("multimem", lambda: (setattr(tp, "use_multimem", True), tp.peer_all_reduce(part, res, out))),
+                     ("nccl", lambda: (dist.all_reduce(part.clone()), None))]
+            for name, fn in cases:
+                for _ in range(5):
+                    fn()
+                ts = sorted(_timed(dev, fn)[0] * 1e3 for _ in range(a.samples))
+                t = torch.tensor([ts[len(ts) // 2]], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                if rank == 0:
+                    nbytes = m * H * 2
+                    print(f"tp_allreduce kernel={name} ranks={world} rows={m} hidden={H} payload_bytes={nbytes} p50_us={float(t):.2f} "
+                          f"bus_GBps={2 * (world - 1) / world * nbytes / float(t) / 1e3:.1f}")
+        tp.use_multimem = False
     if world > 1:
         dist.destroy_process_group()
     return 0
