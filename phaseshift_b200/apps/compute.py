@@ -100,8 +100,9 @@ class ComputeRuntime:
         sc = StateConfig(max_slots=a.max_concurrent_requests, max_seq_len=a.max_seq_len, page_tokens=a.page_tokens,
                          kv_capacity_tokens=a.kv_cache_capacity_tokens, kv_dtype=a.kv_cache_dtype,
                          conv_ring=32 if spec else 4, spec_rows=a.dflash2_drafts + 1 if spec else 0)
-        shadow = a.batch_shadow == "on"
-        if a.batch_shadow == "auto" and a.max_concurrent_requests > 1 and self.device.type == "cuda":
+        mode = getattr(a, "batch_shadow", "off")
+        shadow = mode == "on"
+        if mode == "auto" and a.max_concurrent_requests > 1 and self.device.type == "cuda":
             import torch
             free, _ = torch.cuda.mem_get_info(self.device)
             need = sum(w.N * w.k_padded * 2 for w in ew.linears())

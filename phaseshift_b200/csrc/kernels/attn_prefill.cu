@@ -242,12 +242,188 @@ __global__ void __launch_bounds__(kPfThreads) attn_prefill_kernel(const AttnPref
     }
 }
 
+// ---- bf16 pools: the same tile loop with K/V tiles copied asynchronously (cp.async, 16 bytes per request):
+// the K tile of step t+1 is in flight while step t does its softmax and P V, the V tile of step t+1 while
+// step t+1 computes Q K^T, so the tensor cores no longer wait for a full global -> shared round trip per tile.
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    const int n = valid ? 16 : 0;                 // src-size 0: the 16 destination bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <int D>
+__device__ __forceinline__ void issue_tile(const AttnPrefillArgs& a, const void* pool, __nv_bfloat16* dst, int slot, int kvh, int t0,
+                                           int end, bool& bad) {
+    constexpr int P = D + 8, PPR = D / 8;
+    if (t0 < end) {
+        for (int p = threadIdx.x; p < kPfTok * PPR; p += kPfThreads) {
+            const int t = p / PPR, c = p % PPR, tok = t0 + t;
+            const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(pool);
+            bool ok = tok < end;
+            if (ok) {
+                const int page = a.block_table[(size_t)slot * a.max_blocks + tok / a.page_tokens];
+                if (page < 0 || page >= a.num_pages) { bad = true; ok = false; }
+                else src += (((size_t)page * a.Hkv + kvh) * a.page_tokens + tok % a.page_tokens) * D + c * 8;
+            }
+            cp_async16(dst + t * P + c * 8, src, ok);
+        }
+    }
+    cp_async_commit();                              // always commit so the group count stays uniform
+}
+
+template <int D>
+__global__ void __launch_bounds__(kPfThreads) attn_prefill_async_kernel(const AttnPrefillArgs a) {
+    constexpr int P = D + 8;
+    extern __shared__ __align__(16) unsigned char smem[];
+    __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem);
+    __nv_bfloat16* sK = sQ + kPfRows * P;
+    __nv_bfloat16* sV = sK + kPfTok * P;
+
+    const int* sd = a.seqs + 4 * blockIdx.z;
+    const int row_start = sd[0], n_rows = sd[1], slot = sd[2], pos_start = sd[3];
+    const int tile = (int)gridDim.x - 1 - (int)blockIdx.x;
+    const int r_begin = tile * kPfRows;
+    if (r_begin >= n_rows || slot < 0) return;
+    const int nq = min(kPfRows, n_rows - r_begin);
+    const int h = blockIdx.y, G = a.Hq / a.Hkv, kvh = h / G;
+    const int pos_q0 = pos_start + r_begin;
+    const int kv_end = pos_q0 + nq;
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    bool bad = false;
+
+    issue_tile<D>(a, a.k_pool, sK, slot, kvh, 0, kv_end, bad);
+    issue_tile<D>(a, a.v_pool, sV, slot, kvh, 0, kv_end, bad);
+    for (int p = t; p < kPfRows * (D / 8); p += kPfThreads) {
+        const int r = p / (D / 8), c = p % (D / 8);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < nq) v = __ldg(reinterpret_cast<const uint4*>(a.q + ((size_t)(row_start + r_begin + r) * a.Hq + h) * D) + c);
+        *reinterpret_cast<uint4*>(sQ + r * P + c * 8) = v;
+    }
+
+    float o[D / 8][4];
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+    float m_run[2] = {-1.0e30f, -1.0e30f}, l_run[2] = {0.f, 0.f};
+    const int rpos0 = pos_q0 + warp * 16 + (lane >> 2);
+
+    for (int t0 = 0; t0 < kv_end; t0 += kPfTok) {
+        const bool live = t0 <= pos_q0 + warp * 16 + 15;       // some row of this warp sees this tile
+        cp_async_wait<1>();                                     // K(t) has landed (V(t) may still be in flight)
+        __syncthreads();
+        float s[kPfTok / 8][4];
+#pragma unroll
+        for (int j = 0; j < kPfTok / 8; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
+        if (live) {
+#pragma unroll 4
+            for (int kk = 0; kk < D / 16; ++kk) {
+                uint32_t af[4];
+                ldsm_x4(af, sQ + (warp * 16 + (lane & 15)) * P + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+                for (int n2 = 0; n2 < kPfTok / 16; ++n2) {
+                    uint32_t bf[4];
+                    ldsm_x4(bf, sK + (n2 * 16 + (lane & 7) + (lane >> 4) * 8) * P + kk * 16 + ((lane >> 3) & 1) * 8);
+                    mma_bf16_16816(s[2 * n2], af, bf[0], bf[1]);
+                    mma_bf16_16816(s[2 * n2 + 1], af, bf[2], bf[3]);
+                }
+            }
+        }
+        __syncthreads();                                        // every warp is done with the K tile
+        issue_tile<D>(a, a.k_pool, sK, slot, kvh, t0 + kPfTok, kv_end, bad);
+        uint32_t pf[kPfTok / 16][4];
+        float alpha[2] = {1.f, 1.f};
+        if (live) {
+            float mx[2] = {-1.0e30f, -1.0e30f};
+#pragma unroll
+            for (int j = 0; j < kPfTok / 8; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int tok = t0 + 8 * j + (lane & 3) * 2 + (e & 1);
+                    float v = s[j][e] * a.scale_log2;
+                    if (tok > rpos0 + (e >> 1) * 8) v = -1.0e30f;
+                    s[j][e] = v;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+                const float m_new = fmaxf(m_run[r], mx[r]);
+                alpha[r] = exp2f(m_run[r] - m_new);
+                m_run[r] = m_new;
+                l_run[r] *= alpha[r];
+            }
+#pragma unroll
+            for (int j = 0; j < kPfTok / 8; ++j) {
+                float p[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    p[e] = s[j][e] > -0.5e30f ? exp2f(s[j][e] - m_run[e >> 1]) : 0.f;
+                    l_run[e >> 1] += p[e];
+                }
+                pf[j >> 1][(j & 1) * 2 + 0] = f32x2_to_bf16x2_bits(p[0], p[1]);
+                pf[j >> 1][(j & 1) * 2 + 1] = f32x2_to_bf16x2_bits(p[2], p[3]);
+            }
+#pragma unroll
+            for (int j = 0; j < D / 8; ++j) { o[j][0] *= alpha[0]; o[j][1] *= alpha[0]; o[j][2] *= alpha[1]; o[j][3] *= alpha[1]; }
+        }
+        cp_async_wait<1>();                                     // V(t) has landed (K(t+1) may still be in flight)
+        __syncthreads();
+        if (live) {
+#pragma unroll
+            for (int kk = 0; kk < kPfTok / 16; ++kk) {
+#pragma unroll
+                for (int n2 = 0; n2 < D / 16; ++n2) {
+                    uint32_t bf[4];
+                    ldsm_x4_t(bf, sV + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * P + n2 * 16 + (lane >> 4) * 8);
+                    mma_bf16_16816(o[2 * n2], pf[kk], bf[0], bf[1]);
+                    mma_bf16_16816(o[2 * n2 + 1], pf[kk], bf[2], bf[3]);
+                }
+            }
+        }
+        __syncthreads();                                        // every warp is done with the V tile
+        issue_tile<D>(a, a.v_pool, sV, slot, kvh, t0 + kPfTok, kv_end, bad);
+    }
+    cp_async_wait<0>();
+    if (bad) set_status(a.status, PS_DEV_BAD_INDEX);
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int lr = warp * 16 + (lane >> 2) + r * 8;
+        if (lr >= nq) continue;
+        const size_t row = (size_t)(row_start + r_begin + lr);
+        const float inv = l_run[r] > 0.f ? 1.f / l_run[r] : 0.f;
+#pragma unroll
+        for (int j = 0; j < D / 8; ++j) {
+            const int d = 8 * j + (lane & 3) * 2;
+            float v0 = bf16_to_f32(f32_to_bf16(o[j][2 * r] * inv)), v1 = bf16_to_f32(f32_to_bf16(o[j][2 * r + 1] * inv));
+            if (a.gate != nullptr) {
+                const float2 gv = bf16x2_bits_to_f32x2(*reinterpret_cast<const uint32_t*>(
+                    a.gate + row * a.ld_gate + (size_t)h * a.gate_head_stride + a.gate_offset + d));
+                v0 *= sigmoid_f(gv.x); v1 *= sigmoid_f(gv.y);
+            }
+            *reinterpret_cast<uint32_t*>(a.out + (row * a.Hq + h) * D + d) = f32x2_to_bf16x2_bits(v0, v1);
+        }
+    }
+}
+
 template <int D>
 static int launch_prefill(const AttnPrefillArgs& a, int max_q_tiles, int n_seqs, cudaStream_t stream) {
     const size_t smem = (size_t)(kPfRows + 2 * kPfTok) * (D + 8) * 2 + 2 * kPfTok * sizeof(float);
     static bool set = false;
-    if (!set) { cudaFuncSetAttribute(attn_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); set = true; }
-    attn_prefill_kernel<D><<<dim3(max_q_tiles, a.Hq, n_seqs), kPfThreads, smem, stream>>>(a);
+    if (!set) {
+        cudaFuncSetAttribute(attn_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(attn_prefill_async_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        set = true;
+    }
+    if (a.kv_fp8) attn_prefill_kernel<D><<<dim3(max_q_tiles, a.Hq, n_seqs), kPfThreads, smem, stream>>>(a);
+    else attn_prefill_async_kernel<D><<<dim3(max_q_tiles, a.Hq, n_seqs), kPfThreads, smem, stream>>>(a);
     return PS_LAUNCH_CHECK();
 }
 

@@ -47,8 +47,8 @@ __global__ void __launch_bounds__(256) gdn_rows_kernel(const GdnArgs a) {
     constexpr int RG = 256 / CG;        // row groups
     constexpr int R = DK / RG;          // rows per thread
     constexpr int CH = 2 * DK + DV;     // conv channels owned by this head
-    __shared__ float s_q[DK], s_k[DK], s_v[DV], s_red[32], s_red4[160];
-    __shared__ float s_part[RG][DV];
+    __shared__ float s_q[DK], s_k[DK], s_v[DV], s_red[32], s_red4[192];
+    __shared__ float s_part[RG][DV], s_partq[RG][DV];
     __shared__ float s_vec[DV];
 
     const int h = blockIdx.x;
@@ -108,9 +108,9 @@ __global__ void __launch_bounds__(256) gdn_rows_kernel(const GdnArgs a) {
             const int gc = c < DK ? q_off + c : (c < 2 * DK ? k_off + (c - DK) : v_off + (c - 2 * DK));
             hist[(size_t)(pos % a.ring) * CH + c] = pr[gc];
         }
-        // ---- L2 norms and (optionally) the beta / decay input projections: one fused block reduction
-        float red4[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int i = t; i < DK; i += 256) { red4[0] += s_q[i] * s_q[i]; red4[1] += s_k[i] * s_k[i]; }
+        // ---- L2 norms, k.q and (optionally) the beta / decay input projections: one fused block reduction
+        float red5[5] = {0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int i = t; i < DK; i += 256) { red5[0] += s_q[i] * s_q[i]; red5[1] += s_k[i] * s_k[i]; red5[4] += s_q[i] * s_k[i]; }
         if (a.ba_w != nullptr) {
             const __nv_bfloat16* xr = a.xn + (size_t)row * a.ba_k;
             const __nv_bfloat16* wb = a.ba_w + (size_t)h * a.ba_k;
@@ -119,72 +119,69 @@ __global__ void __launch_bounds__(256) gdn_rows_kernel(const GdnArgs a) {
                 const float2 xv = bf16x2_bits_to_f32x2(*reinterpret_cast<const uint32_t*>(xr + i));
                 const float2 bv = bf16x2_bits_to_f32x2(__ldg(reinterpret_cast<const uint32_t*>(wb + i)));
                 const float2 av = bf16x2_bits_to_f32x2(__ldg(reinterpret_cast<const uint32_t*>(wa + i)));
-                red4[2] = fmaf(xv.x, bv.x, red4[2]); red4[2] = fmaf(xv.y, bv.y, red4[2]);
-                red4[3] = fmaf(xv.x, av.x, red4[3]); red4[3] = fmaf(xv.y, av.y, red4[3]);
+                red5[2] = fmaf(xv.x, bv.x, red5[2]); red5[2] = fmaf(xv.y, bv.y, red5[2]);
+                red5[3] = fmaf(xv.x, av.x, red5[3]); red5[3] = fmaf(xv.y, av.y, red5[3]);
             }
         }
-        block_sum_n<4>(red4, s_red4);
-        const float qn = rsqrtf(red4[0] + 1e-6f) * rsqrtf((float)DK);
-        const float kn = rsqrtf(red4[1] + 1e-6f);
+        block_sum_n<5>(red5, s_red4);
+        const float qn = rsqrtf(red5[0] + 1e-6f) * rsqrtf((float)DK);
+        const float kn = rsqrtf(red5[1] + 1e-6f);
+        const float kq = red5[4] * qn * kn;                       // k . q of the normalised vectors
         float b_in, a_in;
         if (a.ba_w != nullptr) {
-            b_in = bf16_to_f32(f32_to_bf16(red4[2])); a_in = bf16_to_f32(f32_to_bf16(red4[3]));
+            b_in = bf16_to_f32(f32_to_bf16(red5[2])); a_in = bf16_to_f32(f32_to_bf16(red5[3]));
         } else {
             b_in = bf16_to_f32(pr[b_off]); a_in = bf16_to_f32(pr[a_off]);
         }
         const float beta = sigmoid_f(b_in);
         const float gate = neg_expA * softplus_f(a_in + dtb);
         const float d = __expf(gate);
-        // ---- kv = (d S)^T k
+        // ---- one pass over the state: S <- d S, partial sums of S^T k and S^T q (both of the decayed old state)
         float kreg[R], qreg[R];
 #pragma unroll
         for (int r = 0; r < R; ++r) { kreg[r] = s_k[rg + RG * r] * kn; qreg[r] = s_q[rg + RG * r] * qn; }
-        float p[4] = {0.f, 0.f, 0.f, 0.f};
+        float p[4] = {0.f, 0.f, 0.f, 0.f}, pq[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int r = 0; r < R; ++r) {
 #pragma unroll
-            for (int c = 0; c < 4; ++c) { S[r][c] *= d; p[c] = fmaf(S[r][c], kreg[r], p[c]); }
+            for (int c = 0; c < 4; ++c) { S[r][c] *= d; p[c] = fmaf(S[r][c], kreg[r], p[c]); pq[c] = fmaf(S[r][c], qreg[r], pq[c]); }
         }
         *reinterpret_cast<float4*>(&s_part[rg][cg * 4]) = make_float4(p[0], p[1], p[2], p[3]);
+        *reinterpret_cast<float4*>(&s_partq[rg][cg * 4]) = make_float4(pq[0], pq[1], pq[2], pq[3]);
         __syncthreads();
+        // delta = beta (v - S^T k);  o = S_new^T q = S^T q + (k.q) delta   with S_new = S + k delta^T
+        float ov = 0.f;
         if (t < DV) {
-            float kv = 0.f;
+            float kv = 0.f, qv = 0.f;
 #pragma unroll
-            for (int g = 0; g < RG; ++g) kv += s_part[g][t];
+            for (int g = 0; g < RG; ++g) { kv += s_part[g][t]; qv += s_partq[g][t]; }
             const float delta = (s_v[t] - kv) * beta;
             s_vec[t] = delta;
+            ov = fmaf(kq, delta, qv);
             if (a.log_delta) a.log_delta[((size_t)row * a.Hv + h) * DV + t] = delta;
         }
         if (a.log_k) {
             for (int i = t; i < DK; i += 256) a.log_k[((size_t)row * a.Hv + h) * DK + i] = s_k[i] * kn;
             if (t == 0) a.log_d[(size_t)row * a.Hv + h] = d;
         }
-        __syncthreads();
-        // ---- S += k (x) delta ; o = S^T q
-        const float4 dl = *reinterpret_cast<const float4*>(&s_vec[cg * 4]);
-        const float dlr[4] = {dl.x, dl.y, dl.z, dl.w};
-        float o[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-#pragma unroll
-            for (int c = 0; c < 4; ++c) { S[r][c] = fmaf(kreg[r], dlr[c], S[r][c]); o[c] = fmaf(S[r][c], qreg[r], o[c]); }
-        }
-        __syncthreads();   // s_part reads above are done
-        *reinterpret_cast<float4*>(&s_part[rg][cg * 4]) = make_float4(o[0], o[1], o[2], o[3]);
-        __syncthreads();
-        float ov = 0.f;
-        if (t < DV) {
-#pragma unroll
-            for (int g = 0; g < RG; ++g) ov += s_part[g][t];
-        }
-        const float ss = block_sum(t < DV ? ov * ov : 0.f, s_red);
+        const float ss = block_sum(t < DV ? ov * ov : 0.f, s_red);      // its barriers also publish s_vec
         if (t < DV) {
             const float inv = rsqrtf(ss / (float)DV + a.eps);
             const float y = ov * inv * bf16_to_f32(a.norm_w[t]);
             const float z = bf16_to_f32(pr[z_off + t]);
             a.out[(size_t)row * (a.Hv * DV) + h * DV + t] = f32_to_bf16(y * silu_f(z));
         }
-        __syncthreads();
+        // ---- S += k (x) delta (registers only)
+        {
+            const float4 dl = *reinterpret_cast<const float4*>(&s_vec[cg * 4]);
+            const float dlr[4] = {dl.x, dl.y, dl.z, dl.w};
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) S[r][c] = fmaf(kreg[r], dlr[c], S[r][c]);
+            }
+        }
+        __syncthreads();      // s_q / s_k / s_v / s_part / s_vec are rewritten by the next row
     }
     {
         float* sp = a.state_out + ((size_t)sd.slot * a.Hv + h) * DK * DV;
