@@ -44,6 +44,7 @@ struct GdnPrepArgs {
     __nv_bfloat16* conv_state; int ring;
     const int* row_slot; const int* row_pos;
     const GdnSeqDesc2* seqs; int n_seqs;
+    int min_rows;                                // sequences with at most this many rows are left to the row kernel
     float* scratch;                              // per (chunk, head): W, Qd, Kd [64,Dk]; U [64,Dv]; QKd [64,64]
     float* dc;                                   // per (chunk, head): D_C
 };
@@ -51,11 +52,11 @@ struct GdnPrepArgs {
 __host__ __device__ inline size_t chunk_scratch_floats(int Dk, int Dv) { return (size_t)kChunk * (3 * Dk + Dv + kChunk); }
 
 // Locate global chunk `gc` (chunks are numbered sequence by sequence): returns false when out of range.
-__device__ __forceinline__ bool find_chunk(const GdnSeqDesc2* seqs, int n_seqs, int gc, GdnSeqDesc2& sd, int& chunk) {
+__device__ __forceinline__ bool find_chunk(const GdnSeqDesc2* seqs, int n_seqs, int min_rows, int gc, GdnSeqDesc2& sd, int& chunk) {
     int base = 0;
     for (int s = 0; s < n_seqs; ++s) {
         const GdnSeqDesc2 d = seqs[s];
-        const int nc = d.n_rows > 0 && d.slot >= 0 ? (d.n_rows + kChunk - 1) / kChunk : 0;
+        const int nc = d.n_rows > min_rows && d.slot >= 0 ? (d.n_rows + kChunk - 1) / kChunk : 0;
         if (gc < base + nc) { sd = d; chunk = gc - base; return true; }
         base += nc;
     }
@@ -102,7 +103,7 @@ __global__ void __launch_bounds__(256) gdn_chunk_prep_kernel(const GdnPrepArgs a
     float* sT = sA + kChunk * 65;          // 64 * 65 floats keep the T rows 16-byte aligned
 
     GdnSeqDesc2 sd; int chunk;
-    if (!find_chunk(a.seqs, a.n_seqs, blockIdx.x, sd, chunk)) return;
+    if (!find_chunk(a.seqs, a.n_seqs, a.min_rows, blockIdx.x, sd, chunk)) return;
     const int h = blockIdx.y, t = threadIdx.x, warp = t >> 5, lane = t & 31;
     const int r0 = chunk * kChunk, C = min(kChunk, sd.n_rows - r0);
     const size_t row0 = (size_t)sd.row_start + r0;
@@ -262,12 +263,21 @@ __global__ void __launch_bounds__(256) gdn_chunk_prep_kernel(const GdnPrepArgs a
     }
 }
 
+// True when `row` belongs to a sequence this launch handles (more than min_rows rows in the step).
+__device__ __forceinline__ bool row_is_chunked(const GdnSeqDesc2* seqs, int n_seqs, int min_rows, int row) {
+    for (int s = 0; s < n_seqs; ++s) {
+        const GdnSeqDesc2 d = seqs[s];
+        if (row >= d.row_start && row < d.row_start + d.n_rows) return d.n_rows > min_rows && d.slot >= 0;
+    }
+    return false;
+}
+
 // History for later steps: the raw inputs of each sequence's last `ring` rows.  Separate launch so the
 // prepare CTAs of a step never race with history reads of earlier rows of the same step.
 __global__ void gdn_history_kernel(const GdnPrepArgs a, int rows) {
     const int h = blockIdx.x, row = blockIdx.y, t = threadIdx.x;
     const int slot = a.row_slot[row];
-    if (slot < 0) return;
+    if (slot < 0 || !row_is_chunked(a.seqs, a.n_seqs, a.min_rows, row)) return;
     // only the last `ring` rows of a sequence in this step matter (later rows overwrite earlier slots)
     const int pos = a.row_pos[row];
     bool last = true;
@@ -286,7 +296,7 @@ __global__ void gdn_history_kernel(const GdnPrepArgs a, int rows) {
 
 struct GdnScanArgs {
     const float* scratch; const float* dc;
-    int Hv, Dv, n_seqs;
+    int Hv, Dv, n_seqs, min_rows;
     float* state;                 // [slots, Hv, Dk, Dv] fp32, updated in place
     const GdnSeqDesc2* seqs;
     float* o;                     // [rows, Hv, Dv] fp32
@@ -313,11 +323,11 @@ __global__ void __launch_bounds__(256) gdn_chunk_scan_kernel(const GdnScanArgs a
 
     const int slice = blockIdx.x, h = blockIdx.y, t = threadIdx.x, Hv = a.Hv, c0 = slice * kSlice;
     const GdnSeqDesc2 sd = a.seqs[blockIdx.z];
-    if (sd.n_rows <= 0 || sd.slot < 0) return;
+    if (sd.n_rows <= a.min_rows || sd.slot < 0) return;
     int gc = 0;
     for (int s = 0; s < (int)blockIdx.z; ++s) {
         const GdnSeqDesc2 d = a.seqs[s];
-        if (d.n_rows > 0 && d.slot >= 0) gc += (d.n_rows + kChunk - 1) / kChunk;
+        if (d.n_rows > a.min_rows && d.slot >= 0) gc += (d.n_rows + kChunk - 1) / kChunk;
     }
     float* Sg = a.state + ((size_t)sd.slot * Hv + h) * DK * DV;
     for (int i = t; i < DK * kSlice / 4; i += 256) {
@@ -427,10 +437,11 @@ __global__ void __launch_bounds__(256) gdn_chunk_scan_kernel(const GdnScanArgs a
 
 // grid = (Hv, rows), block = Dv threads
 __global__ void gdn_post_kernel(const float* o, const __nv_bfloat16* proj, int ld_proj, int z_off, const __nv_bfloat16* norm_w,
-                                float eps, int Hv, int Dv, const int* row_slot, __nv_bfloat16* out) {
+                                float eps, int Hv, int Dv, const int* row_slot, __nv_bfloat16* out, const GdnSeqDesc2* seqs,
+                                int n_seqs, int min_rows) {
     __shared__ float red[32];
     const int h = blockIdx.x, row = blockIdx.y, t = threadIdx.x;
-    if (row_slot[row] < 0) return;
+    if (row_slot[row] < 0 || !row_is_chunked(seqs, n_seqs, min_rows, row)) return;
     const float v = o[((size_t)row * Hv + h) * Dv + t];
     const float ss = block_sum(v * v, red);
     const float y = v * rsqrtf(ss / (float)Dv + eps) * bf16_to_f32(norm_w[t]);
@@ -471,16 +482,16 @@ static int launch_chunked(const GdnPrepArgs& p, const GdnScanArgs& s, int max_ch
 PS_API int ps_gdn_chunked(const void* proj, int ld_proj, int rows, int Hk, int Hv, int Dk, int Dv, const void* conv_w,
                           const void* A_log, const void* dt_bias, const void* norm_w, float eps, void* conv_state, int ring,
                           void* state, const void* seqs, int n_seqs, const void* row_slot, const void* row_pos,
-                          void* scratch, void* dc, void* o, void* out, cudaStream_t stream) {
+                          int min_rows, void* scratch, void* dc, void* o, void* out, cudaStream_t stream) {
     using namespace ps;
     if (rows <= 0 || n_seqs <= 0 || Hk <= 0 || (Hv % Hk) || ring < 4) return (int)cudaErrorInvalidValue;
     GdnPrepArgs p;
     p.proj = (const __nv_bfloat16*)proj; p.ld_proj = ld_proj; p.Hk = Hk; p.Hv = Hv; p.Dk = Dk; p.Dv = Dv;
     p.conv_w = (const __nv_bfloat16*)conv_w; p.A_log = (const float*)A_log; p.dt_bias = (const float*)dt_bias;
     p.conv_state = (__nv_bfloat16*)conv_state; p.ring = ring; p.row_slot = (const int*)row_slot; p.row_pos = (const int*)row_pos;
-    p.seqs = (const GdnSeqDesc2*)seqs; p.n_seqs = n_seqs; p.scratch = (float*)scratch; p.dc = (float*)dc;
+    p.seqs = (const GdnSeqDesc2*)seqs; p.n_seqs = n_seqs; p.min_rows = min_rows; p.scratch = (float*)scratch; p.dc = (float*)dc;
     GdnScanArgs s;
-    s.scratch = p.scratch; s.dc = p.dc; s.Hv = Hv; s.Dv = Dv; s.n_seqs = n_seqs; s.state = (float*)state; s.seqs = p.seqs;
+    s.scratch = p.scratch; s.dc = p.dc; s.Hv = Hv; s.Dv = Dv; s.n_seqs = n_seqs; s.min_rows = min_rows; s.state = (float*)state; s.seqs = p.seqs;
     s.o = (float*)o;
     const int max_chunks = (rows + kChunk - 1) / kChunk + n_seqs;
     int err;
@@ -492,6 +503,6 @@ PS_API int ps_gdn_chunked(const void* proj, int ld_proj, int rows, int Hk, int H
     if ((err = PS_LAUNCH_CHECK())) return err;
     gdn_post_kernel<<<dim3(Hv, rows), Dv, 0, stream>>>((const float*)o, (const __nv_bfloat16*)proj, ld_proj,
                                                        2 * Hk * Dk + Hv * Dv, (const __nv_bfloat16*)norm_w, eps, Hv, Dv,
-                                                       (const int*)row_slot, (__nv_bfloat16*)out);
+                                                       (const int*)row_slot, (__nv_bfloat16*)out, p.seqs, n_seqs, min_rows);
     return PS_LAUNCH_CHECK();
 }

@@ -39,6 +39,7 @@ struct GdnArgs {
     // optional in-kernel beta/decay projections: b = xn . ba_w[h], a = xn . ba_w[Hv + h] (bf16 weights);
     // when null the kernel reads b and a from `proj`
     const __nv_bfloat16* ba_w; const __nv_bfloat16* xn; int ba_k;
+    int max_rows;                               // sequences with more rows in this step belong to the chunked kernels
 };
 
 template <int DK, int DV>
@@ -53,7 +54,7 @@ __global__ void __launch_bounds__(256) gdn_rows_kernel(const GdnArgs a) {
 
     const int h = blockIdx.x;
     const GdnSeqDesc sd = a.seqs[blockIdx.y];
-    if (sd.n_rows <= 0) return;
+    if (sd.n_rows <= 0 || sd.n_rows > a.max_rows) return;
     const int hk = h / (a.Hv / a.Hk);
     const int t = threadIdx.x, cg = t % CG, rg = t / CG;
     const int q_off = hk * DK, k_off = a.Hk * DK + hk * DK, v_off = 2 * a.Hk * DK + h * DV;
@@ -235,7 +236,7 @@ __global__ void __launch_bounds__(256) gdn_replay_kernel(const GdnReplayArgs a) 
 PS_API int ps_gdn_rows(const void* proj, int ld_proj, int Hk, int Hv, int Dk, int Dv, const void* conv_w,
                        const void* A_log, const void* dt_bias, const void* norm_w, float eps, void* conv_state,
                        int ring, const void* state_in, void* state_out, const void* seqs, int n_seqs, void* out,
-                       void* log_k, void* log_delta, void* log_d, const void* ba_w, const void* xn, int ba_k,
+                       void* log_k, void* log_delta, void* log_d, const void* ba_w, const void* xn, int ba_k, int max_rows,
                        cudaStream_t stream) {
     using namespace ps;
     if (n_seqs <= 0 || Hk <= 0 || (Hv % Hk) || ring < 4) return (int)cudaErrorInvalidValue;
@@ -246,6 +247,7 @@ PS_API int ps_gdn_rows(const void* proj, int ld_proj, int Hk, int Hv, int Dk, in
     a.state_in = (const float*)state_in; a.state_out = (float*)state_out; a.seqs = (const GdnSeqDesc*)seqs;
     a.out = (__nv_bfloat16*)out; a.log_k = (float*)log_k; a.log_delta = (float*)log_delta; a.log_d = (float*)log_d;
     a.ba_w = (const __nv_bfloat16*)ba_w; a.xn = (const __nv_bfloat16*)xn; a.ba_k = ba_k;
+    a.max_rows = max_rows > 0 ? max_rows : 0x7fffffff;
     if (ba_w != nullptr && (ba_k & 1)) return (int)cudaErrorInvalidValue;
     dim3 grid(Hv, n_seqs);
     if (Dk == 128 && Dv == 128) return launch_pdl(gdn_rows_kernel<128, 128>, grid, dim3(256), 0, stream, a);

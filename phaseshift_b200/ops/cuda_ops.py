@@ -179,7 +179,11 @@ class CudaOps:
         cfg = self.cfg
         rows, D = q.shape[0], cfg.head_dim
         out = self.buf("attn_ctx", rows, hq * D)
-        if rows > self.ATTN_PREFILL_MIN_ROWS and not self.exact_rows and not b.graph_static and D in (64, 128, 256):
+        # the tiled kernel pays off when some sequence brings a long run of rows (a prefill chunk); steps made of
+        # many sequences with a row or two each (batched decode) keep the per-row split-KV kernel
+        tiled = (not self.exact_rows and not b.graph_static and D in (64, 128, 256)
+                 and any(len(sq.token_ids) > self.ATTN_PREFILL_MIN_ROWS for sq in b.seqs))
+        if tiled:
             # prefill-sized step: 64-row query tiles on the tensor cores
             _lib.call("ps_attn_prefill", ptr(q), ptr(kv.k), ptr(kv.v), ptr(kv.k_scale), ptr(kv.v_scale),
                       ptr(st.block_table), c_int(st.max_blocks), c_int(st.sc.page_tokens), c_int(st.num_pages),
@@ -207,30 +211,41 @@ class CudaOps:
         rows = proj.shape[0]
         Dk, Dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
         out = self.buf("gdn_o", rows, hv * Dv)
-        if rows > self.GDN_CHUNKED_MIN_ROWS and log is None and not to_alt and not self.exact_rows and xn is None:
-            # prefill-sized step: chunked form (state-independent part for all chunks at once, then a lean scan)
+        state_out = gs.rec_alt if to_alt else gs.rec
+        n_seqs = b.max_seqs if b.graph_static else b.n_seqs
+        # Sequences with many rows in this step (prefill chunks) take the chunked kernels, sequences with few rows
+        # (decode / verify rows of other requests in the same step) the row-sequential kernel; both can be present.
+        T = self.GDN_CHUNKED_MIN_ROWS
+        plain = log is None and not to_alt and not self.exact_rows and not b.graph_static
+        seq_rows = [len(sq.token_ids) for sq in b.seqs] if plain else []
+        any_long = any(n > T for n in seq_rows)
+        any_short = (not any_long) or any(n <= T for n in seq_rows)
+        if any_long:
             f32 = torch.float32
-            n_seqs = b.max_seqs if b.graph_static else b.n_seqs
-            chunks = (rows + 63) // 64 + n_seqs
+            long_rows = sum(n for n in seq_rows if n > T)
+            chunks = sum((n + 63) // 64 for n in seq_rows if n > T)
             scr = self.buf("gdn_scratch", 1, chunks * hv * 64 * (3 * Dk + Dv + 64), f32)
             dc = self.buf("gdn_dc", 1, chunks * hv, f32)
             o = self.buf("gdn_of", rows, hv * Dv, f32)
+            if xn is not None:
+                raise ValueError("the chunked GDN path reads the b/a projections from `proj`")
             _lib.call("ps_gdn_chunked", ptr(proj), c_int(proj.stride(0)), c_int(rows), c_int(hk), c_int(hv), c_int(Dk),
                       c_int(Dv), ptr(gw.conv_w), ptr(gw.A_log), ptr(gw.dt_bias), ptr(gw.norm_w),
                       c_float(cfg.rms_norm_eps), ptr(gs.conv), c_int(st.sc.conv_ring), ptr(gs.rec), ptr(b.seq_desc),
-                      c_int(n_seqs), ptr(b.row_slot), ptr(b.row_pos), ptr(scr), ptr(dc), ptr(o), ptr(out))
+                      c_int(n_seqs), ptr(b.row_slot), ptr(b.row_pos), c_int(T), ptr(scr), ptr(dc), ptr(o), ptr(out))
             self.launches += 4
-            return out
-        state_out = gs.rec_alt if to_alt else gs.rec
-        lk = ld = ldd = None
-        if log is not None:
-            lk, ld, ldd = log
-        _lib.call("ps_gdn_rows", ptr(proj), c_int(proj.stride(0)), c_int(hk), c_int(hv), c_int(Dk), c_int(Dv),
-                  ptr(gw.conv_w), ptr(gw.A_log), ptr(gw.dt_bias), ptr(gw.norm_w), c_float(cfg.rms_norm_eps),
-                  ptr(gs.conv), c_int(st.sc.conv_ring), ptr(gs.rec), ptr(state_out), ptr(b.seq_desc),
-                  c_int(b.max_seqs if b.graph_static else b.n_seqs), ptr(out), ptr(lk), ptr(ld), ptr(ldd),
-                  ptr(gw.ba_proj.q.codes if xn is not None else None), ptr(xn), c_int(gw.ba_proj.K))
-        self.launches += 1
+            del long_rows
+        if any_short:
+            lk = ld = ldd = None
+            if log is not None:
+                lk, ld, ldd = log
+            _lib.call("ps_gdn_rows", ptr(proj), c_int(proj.stride(0)), c_int(hk), c_int(hv), c_int(Dk), c_int(Dv),
+                      ptr(gw.conv_w), ptr(gw.A_log), ptr(gw.dt_bias), ptr(gw.norm_w), c_float(cfg.rms_norm_eps),
+                      ptr(gs.conv), c_int(st.sc.conv_ring), ptr(gs.rec), ptr(state_out), ptr(b.seq_desc),
+                      c_int(n_seqs), ptr(out), ptr(lk), ptr(ld), ptr(ldd),
+                      ptr(gw.ba_proj.q.codes if xn is not None else None), ptr(xn), c_int(gw.ba_proj.K),
+                      c_int(T if any_long else 0))
+            self.launches += 1
         return out
 
     def gdn_replay(self, gs: GdnLayerState, hv: int, seq_desc: torch.Tensor, n_seqs: int, log) -> None:

@@ -532,3 +532,49 @@ def test_tcgen05_gemm_small_m_weight_streaming(shape):
     ref = (a.float() @ w.float().T).to(torch.bfloat16).float() + res.float()
     assert _rel_err(out.float(), ref) < 4e-3
     assert int(cu.status[0]) == 0
+
+
+def test_gdn_and_attention_mixed_step_long_and_short_sequences():
+    """Continuous batching: one step carries a prefill chunk of one request and single decode rows of others.  The
+    long sequence goes through the chunked / tiled kernels, the short ones through the row kernels, in one call."""
+    cfg = Qwen35Config(vocab_size=1024, hidden_size=512, intermediate_size=512, num_hidden_layers=4,
+                       linear_num_key_heads=2, linear_num_value_heads=6, num_attention_heads=12, num_key_value_heads=2,
+                       head_dim=256)
+    cu, ref = _ops(cfg, 512)
+    sc = StateConfig(max_slots=4, max_seq_len=512, page_tokens=16, conv_ring=8, spec_rows=8, kv_capacity_tokens=4096)
+    st_c = ModelState(cfg, sc, _dev(), torch.bfloat16)
+    st_r = ModelState(cfg, sc, _dev(), torch.float32)
+    nb = st_c.max_blocks
+    for st in (st_c, st_r):
+        perm = torch.randperm(st.num_pages - 1, generator=torch.Generator().manual_seed(5))[:4 * nb] + 1
+        for s in range(4):
+            st.block_table[s, :nb] = perm[s * nb:(s + 1) * nb].int().to(_dev())
+    hf = random_hf_weights(cfg, seed=4, device="cuda")
+    ew = build_engine_weights(cfg, lambda n: hf[n], "bf16", "cuda")
+    lg, la = cfg.gdn_layers[0], cfg.attn_layers[0]
+    gw, aw = ew.layers[lg].mixer, ew.layers[la].mixer
+    Hk, Hv = cfg.linear_num_key_heads, cfg.linear_num_value_heads
+    Hq, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    g = torch.Generator(device="cuda").manual_seed(13)
+    gwidth, awidth = gw.in_proj.N + gw.ba_proj.N, 2 * Hq * D + 2 * Hkv * D
+    # step 1: give the three "decode" sequences some history; step 2: mixed step
+    steps = [[SeqRows(1, 0, [0] * 20, ()), SeqRows(2, 0, [0] * 33, ()), SeqRows(3, 0, [0] * 5, ())],
+             [SeqRows(0, 0, [0] * 100, ()), SeqRows(1, 20, [0], ()), SeqRows(2, 33, [0, 0], ()), SeqRows(3, 5, [0], ())]]
+    for seqs in steps:
+        n = sum(len(s.token_ids) for s in seqs)
+        b = StepBatch(256, 4, _dev())
+        b.fill(seqs); b.upload()
+        proj = (torch.randn(n, gwidth, device="cuda", generator=g) * 0.7).to(torch.bfloat16)
+        o_c = cu.gdn(proj, gw, Hk, Hv, b, st_c.gdn[lg], st_c)
+        o_r = ref.gdn(proj.float(), gw, Hk, Hv, b, st_r.gdn[lg], st_r)
+        qkv = torch.randn(n, awidth, device="cuda", generator=g).to(torch.bfloat16)
+        q_c = cu.attn_prep(qkv, aw, Hq, Hkv, b, st_c.kv[la], st_c)
+        q_r = ref.attn_prep(qkv.float(), aw, Hq, Hkv, b, st_r.kv[la], st_r)
+        a_c = cu.paged_attention(q_c, qkv, Hq, Hkv, b, st_c.kv[la], st_c, b.max_visible)
+        a_r = ref.paged_attention(q_r, qkv.float(), Hq, Hkv, b, st_r.kv[la], st_r, b.max_visible)
+        torch.cuda.synchronize()
+        assert _rel_err(o_c[:n], o_r[:n]) < 2e-2
+        assert _rel_err(a_c[:n], a_r[:n]) < 2e-2
+        for slot in range(4):
+            assert _rel_err(st_c.gdn[lg].rec[slot], st_r.gdn[lg].rec[slot]) < 1e-3 or float(st_r.gdn[lg].rec[slot].abs().max()) == 0
+    assert int(st_c.status[0]) == 0
