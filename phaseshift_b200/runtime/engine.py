@@ -24,6 +24,7 @@ from .batch import SeqRows, StepBatch, resolve_row_bucket
 from .state import ModelState, StateConfig
 
 GRAPH_MAX_ROWS = 8
+GRAPH_MAX_DECODE_ROWS = 64      # pure decode batches (one row per sequence) are also replayed from graphs
 
 
 class SequenceError(RuntimeError):
@@ -195,7 +196,8 @@ class Engine:
             raise
         b.fill(rows)
         plain = not tap_layers and gdn_log is None and not gdn_to_alt and mask is None and sample and not exact
-        use_graph = self.use_graphs and bucket <= GRAPH_MAX_ROWS and plain
+        decode_batch = bucket <= GRAPH_MAX_DECODE_ROWS and all(len(r.token_ids) == 1 for r in rows)
+        use_graph = self.use_graphs and plain and (bucket <= GRAPH_MAX_ROWS or decode_batch)
         b.graph_static = use_graph
         b.upload()
         if use_graph:
@@ -283,7 +285,8 @@ class Engine:
         b = self._batch(bucket)
         b.fill(rows)
         plain = not tap_layers and gdn_log is None and not gdn_to_alt and mask is None and sample
-        use_graph = self.use_graphs and bucket <= GRAPH_MAX_ROWS and plain
+        decode_batch = bucket <= GRAPH_MAX_DECODE_ROWS and all(len(r.token_ids) == 1 for r in rows)
+        use_graph = self.use_graphs and plain and (bucket <= GRAPH_MAX_ROWS or decode_batch)
         b.graph_static = use_graph
         b.upload()
         if use_graph:

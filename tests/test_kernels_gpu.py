@@ -578,3 +578,26 @@ def test_gdn_and_attention_mixed_step_long_and_short_sequences():
         for slot in range(4):
             assert _rel_err(st_c.gdn[lg].rec[slot], st_r.gdn[lg].rec[slot]) < 1e-3 or float(st_r.gdn[lg].rec[slot].abs().max()) == 0
     assert int(st_c.status[0]) == 0
+
+
+def test_decode_batches_beyond_eight_rows_replay_from_graphs():
+    """Pure decode batches (one row per sequence) up to 64 rows are captured per bucket; replays must produce the
+    tokens of the eager path."""
+    from phaseshift_b200.runtime.engine import Engine
+    cfg = tiny_config()
+    hf = random_hf_weights(cfg, seed=0)
+    ew = build_engine_weights(cfg, lambda n: hf[n], "nvfp4", "cuda")
+    outs = []
+    for graphs in (True, False):
+        eng = Engine(ew, "cuda", StateConfig(max_slots=12, max_seq_len=64), use_graphs=graphs)
+        seqs = [eng.open_sequence() for _ in range(12)]
+        toks = [eng.prefill(s, list(range(3 + i, 12 + i)), 64) for i, s in enumerate(seqs)]
+        hist = []
+        for _ in range(4):
+            rows = [SeqRows(s.slot, s.position, [t], (0,)) for s, t in zip(seqs, toks)]
+            toks, _ = eng.step(rows, seqs)
+            hist.append(list(toks))
+        outs.append(hist)
+        if graphs:
+            assert any(k // 4096 == 16 for k in eng.graphs), "the 12-row decode batch must have been captured (bucket 16)"
+    assert outs[0] == outs[1]
