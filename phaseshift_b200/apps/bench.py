@@ -44,7 +44,7 @@ def build_parser() -> argparse.ArgumentParser:
     ba.add_argument("--tokens", type=int, default=64); ba.add_argument("--shared-prefix", type=int, default=0)
     ge = sub.add_parser("gemm", help="projection kernels")
     ge.add_argument("--dtype", default="nvfp4", choices=["bf16", "nvfp4", "mxfp8"])
-    ge.add_argument("--variant", default="auto", choices=["gemv", "gemm", "auto"]); ge.add_argument("--rows", default="1,4,8,256,2048")
+    ge.add_argument("--variant", default="auto", choices=["gemv", "gemm", "batched", "auto"]); ge.add_argument("--rows", default="1,4,8,256,2048")
     ge.add_argument("--n", type=int, default=5120); ge.add_argument("--k", type=int, default=5120)
     ge.add_argument("--actual-qwen-shapes", action="store_true"); ge.add_argument("--warmup", type=int, default=5)
     ge.add_argument("--samples", type=int, default=10); ge.add_argument("--check", action="store_true"); ge.add_argument("--out")
@@ -166,11 +166,13 @@ def cmd_gemm(a) -> int:
     formats.DEFAULT_SEARCH = 0
     for (name, n, k) in shapes:
         W = LinearW(formats.quantize(torch.randn(n, k, device=dev) * 0.02, a.dtype)).make_tiled(keep_canonical=a.check)
+        if a.variant == "batched":
+            W.make_shadow()                 # resident bf16 expansion: rows 2..64 run the swap-AB split-K tcgen05 GEMM
         for m in rows:
-            if a.variant == "gemv" and m > 8 or a.variant == "gemm" and m <= 8:
+            if a.variant == "gemv" and m > 8 or a.variant == "gemm" and m <= 8 or a.variant == "batched" and not (2 <= m <= 64):
                 continue
             x = torch.randn(m, k, device=dev).to(torch.bfloat16)
-            sel = "gemv" if m <= 8 else "gemm"
+            sel = "batched" if a.variant == "batched" else ("gemv" if m <= 8 else "gemm")
             for _ in range(a.warmup):
                 ops.linear(x, W, name="b")
             ts = []
