@@ -271,7 +271,8 @@ def cmd_tp_reduce(a) -> int:
             if world > 1:
                 dist.all_reduce(y)
             return torch.add(y, res, out=part)
-        for name, fn in (("fused", run_f), ("nccl", run_n)):
+        run_p = lambda: ops.linear(x, W, name="o", residual=res)          # the projection alone (no combine)
+        for name, fn in (("none", run_p), ("fused", run_f), ("nccl", run_n)):
             for _ in range(5):
                 fn()
             ts = sorted(_timed(dev, fn)[0] * 1e3 for _ in range(a.samples))

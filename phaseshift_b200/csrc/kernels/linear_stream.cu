@@ -195,7 +195,8 @@ __global__ void __launch_bounds__(kStThreads, 1) linear_stream_kernel(const Line
             __syncthreads();
             // 2. publish: one system-scope release per peer, then 3. wait for the same CTA of every peer
             if (threadIdx.x < tp.size) {
-                __threadfence_system();
+                // the barrier above ordered the CTA's peer stores before this thread; the system-scope release
+                // on the flag is cumulative over them, so no separate fence is needed
                 uint32_t* f = tp.flags[threadIdx.x] + (size_t)blockIdx.x * tp.size + tp.rank;
                 asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(val) : "memory");
                 const uint32_t* mine = tp.flags[tp.rank] + (size_t)blockIdx.x * tp.size + threadIdx.x;
