@@ -435,6 +435,165 @@ __global__ void __launch_bounds__(256) gdn_chunk_scan_kernel(const GdnScanArgs a
     }
 }
 
+// ---- tensor-core scan: the same three products on mma.sync m16n8k8 (TF32 operands, fp32 accumulation).
+// The recurrent state lives in registers as accumulator fragments (warp w owns state rows 16w .. 16w+15, all
+// 64 columns of the slice) and is never rounded; only the operand COPIES in shared memory are rounded to TF32
+// (round-to-nearest, once, when they are stored).  Shared-memory pitches are chosen so that every fragment
+// load is conflict-free: rows indexed by the fragment's group id use a pitch = 4 (mod 32), rows indexed by
+// the k index a pitch = 8 (mod 32).
+__device__ __forceinline__ float to_tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
+__device__ __forceinline__ void mma_tf32(float (&c)[4], const float (&a)[4], float b0, float b1) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(__float_as_uint(a[0])), "r"(__float_as_uint(a[1])), "r"(__float_as_uint(a[2])), "r"(__float_as_uint(a[3])),
+                   "r"(__float_as_uint(b0)), "r"(__float_as_uint(b1)));
+}
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(256) gdn_chunk_scan_tc_kernel(const GdnScanArgs a) {
+    constexpr int PA = DK + 4, PT = DK + 8, PS = kSlice + 8, PQ = kChunk + 4, NT = kSlice / 8;
+    extern __shared__ __align__(16) float sm[];
+    float* sW = sm;                          // [64][PA]   A operand, rows by group id
+    float* sQd = sW + kChunk * PA;           // [64][PA]
+    float* sKd = sQd + kChunk * PA;          // [64][PT]   read transposed (rows by k index)
+    float* sS = sKd + kChunk * PT;           // [DK][PS]   B operand (TF32 copy of the state slice)
+    float* sD = sS + DK * PS;                // [64][PS]   U slice, then Delta (B operand)
+    float* sQK = sD + kChunk * PS;           // [64][PQ]   A operand
+
+    const int slice = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, Hv = a.Hv, c0 = slice * kSlice;
+    const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const GdnSeqDesc2 sd = a.seqs[blockIdx.z];
+    if (sd.n_rows <= a.min_rows || sd.slot < 0) return;
+    int gc = 0;
+    for (int s = 0; s < (int)blockIdx.z; ++s) {
+        const GdnSeqDesc2 d = a.seqs[s];
+        if (d.n_rows > a.min_rows && d.slot >= 0) gc += (d.n_rows + kChunk - 1) / kChunk;
+    }
+    float* Sg = a.state + ((size_t)sd.slot * Hv + h) * DK * DV;
+    const bool own = warp < DK / 16;                    // this warp keeps state rows 16 warp .. 16 warp + 15
+    const int mt = warp & 3, ch = warp >> 2;            // (a), (c): rows 16 mt .., columns 32 ch .. 32 ch + 31
+    float S[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) { S[nt][0] = S[nt][1] = S[nt][2] = S[nt][3] = 0.f; }
+    if (own) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            const float2 lo = *reinterpret_cast<const float2*>(Sg + (size_t)(16 * warp + g) * DV + c0 + 8 * nt + 2 * t);
+            const float2 hi = *reinterpret_cast<const float2*>(Sg + (size_t)(16 * warp + g + 8) * DV + c0 + 8 * nt + 2 * t);
+            S[nt][0] = lo.x; S[nt][1] = lo.y; S[nt][2] = hi.x; S[nt][3] = hi.y;
+            *reinterpret_cast<float2*>(sS + (16 * warp + g) * PS + 8 * nt + 2 * t) = make_float2(to_tf32(lo.x), to_tf32(lo.y));
+            *reinterpret_cast<float2*>(sS + (16 * warp + g + 8) * PS + 8 * nt + 2 * t) = make_float2(to_tf32(hi.x), to_tf32(hi.y));
+        }
+    }
+
+    for (int r0 = 0; r0 < sd.n_rows; r0 += kChunk, ++gc) {
+        const int C = min(kChunk, sd.n_rows - r0);
+        const size_t rowbase = (size_t)(sd.row_start + r0);
+        const float* scr = a.scratch + ((size_t)gc * Hv + h) * chunk_scratch_floats(DK, DV);
+        const float* gW = scr; const float* gQd = gW + kChunk * DK; const float* gKd = gQd + kChunk * DK;
+        const float* gU = gKd + kChunk * DK; const float* gQK = gU + kChunk * DV;
+        __syncthreads();                                 // previous chunk's readers of the tiles are done
+        for (int i = tid; i < kChunk * DK / 4; i += 256) {
+            const int r = (i * 4) / DK, d = (i * 4) % DK;
+            const float4 w = __ldg(reinterpret_cast<const float4*>(gW) + i), q = __ldg(reinterpret_cast<const float4*>(gQd) + i);
+            const float4 k = __ldg(reinterpret_cast<const float4*>(gKd) + i);
+            *reinterpret_cast<float4*>(sW + r * PA + d) = make_float4(to_tf32(w.x), to_tf32(w.y), to_tf32(w.z), to_tf32(w.w));
+            *reinterpret_cast<float4*>(sQd + r * PA + d) = make_float4(to_tf32(q.x), to_tf32(q.y), to_tf32(q.z), to_tf32(q.w));
+            *reinterpret_cast<float4*>(sKd + r * PT + d) = make_float4(to_tf32(k.x), to_tf32(k.y), to_tf32(k.z), to_tf32(k.w));
+        }
+        for (int i = tid; i < kChunk * kChunk / 4; i += 256) {
+            const int r = (i * 4) / kChunk, c = (i * 4) % kChunk;
+            const float4 v = __ldg(reinterpret_cast<const float4*>(gQK) + i);
+            *reinterpret_cast<float4*>(sQK + r * PQ + c) = make_float4(to_tf32(v.x), to_tf32(v.y), to_tf32(v.z), to_tf32(v.w));
+        }
+        for (int i = tid; i < kChunk * kSlice / 4; i += 256) {
+            const int r = (i * 4) / kSlice, c = (i * 4) % kSlice;
+            *reinterpret_cast<float4*>(sD + r * PS + c) = __ldg(reinterpret_cast<const float4*>(gU + (size_t)r * DV + c0 + c));
+        }
+        const float DC = a.dc[(size_t)gc * Hv + h];
+        __syncthreads();
+        // ---- (a) P = W S0, R = Qd S0 : rows 16 mt .., columns 32 ch + 8 nt ..
+        float P[4][4], R[4][4];
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) { P[nt][0] = P[nt][1] = P[nt][2] = P[nt][3] = 0.f; R[nt][0] = R[nt][1] = R[nt][2] = R[nt][3] = 0.f; }
+        {
+            const float* wr = sW + (16 * mt + g) * PA + t;
+            const float* qr = sQd + (16 * mt + g) * PA + t;
+#pragma unroll 4
+            for (int ks = 0; ks < DK / 8; ++ks) {
+                const float aw[4] = {wr[8 * ks], wr[8 * PA + 8 * ks], wr[8 * ks + 4], wr[8 * PA + 8 * ks + 4]};
+                const float aq[4] = {qr[8 * ks], qr[8 * PA + 8 * ks], qr[8 * ks + 4], qr[8 * PA + 8 * ks + 4]};
+                const float* sb = sS + (8 * ks + t) * PS + 32 * ch + g;
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt) {
+                    const float b0 = sb[8 * nt], b1 = sb[4 * PS + 8 * nt];
+                    mma_tf32(P[nt], aw, b0, b1);
+                    mma_tf32(R[nt], aq, b0, b1);
+                }
+            }
+        }
+        // Delta = U - P, written (TF32) over U in place: every lane owns its accumulator positions
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            float* d0 = sD + (16 * mt + g) * PS + 32 * ch + 8 * nt + 2 * t;
+            float* d1 = d0 + 8 * PS;
+            const float2 u0 = *reinterpret_cast<const float2*>(d0), u1 = *reinterpret_cast<const float2*>(d1);
+            *reinterpret_cast<float2*>(d0) = make_float2(to_tf32(u0.x - P[nt][0]), to_tf32(u0.y - P[nt][1]));
+            *reinterpret_cast<float2*>(d1) = make_float2(to_tf32(u1.x - P[nt][2]), to_tf32(u1.y - P[nt][3]));
+        }
+        __syncthreads();
+        // ---- (c) O = R + QKd Delta (QKd is zero above the diagonal: k-steps beyond this row tile are skipped)
+        {
+            const float* ar = sQK + (16 * mt + g) * PQ + t;
+            for (int ks = 0; ks < 2 * mt + 2; ++ks) {
+                const float aq[4] = {ar[8 * ks], ar[8 * PQ + 8 * ks], ar[8 * ks + 4], ar[8 * PQ + 8 * ks + 4]};
+                const float* sb = sD + (8 * ks + t) * PS + 32 * ch + g;
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt) mma_tf32(R[nt], aq, sb[8 * nt], sb[4 * PS + 8 * nt]);
+            }
+            const int row_lo = 16 * mt + g, row_hi = row_lo + 8;
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) {
+                const int col = c0 + 32 * ch + 8 * nt + 2 * t;
+                if (row_lo < C) *reinterpret_cast<float2*>(a.o + ((rowbase + row_lo) * Hv + h) * DV + col) = make_float2(R[nt][0], R[nt][1]);
+                if (row_hi < C) *reinterpret_cast<float2*>(a.o + ((rowbase + row_hi) * Hv + h) * DV + col) = make_float2(R[nt][2], R[nt][3]);
+            }
+        }
+        // ---- (d) S = D_C S0 + Kd^T Delta : state rows 16 warp .., all columns; A[m = d][k = s] = Kd[s][d]
+        if (own) {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) { S[nt][0] *= DC; S[nt][1] *= DC; S[nt][2] *= DC; S[nt][3] *= DC; }
+            const float* kr = sKd + t * PT + 16 * warp + g;
+#pragma unroll 2
+            for (int ks = 0; ks < kChunk / 8; ++ks) {
+                const float ak[4] = {kr[(8 * ks) * PT], kr[(8 * ks) * PT + 8], kr[(8 * ks + 4) * PT], kr[(8 * ks + 4) * PT + 8]};
+                const float* sb = sD + (8 * ks + t) * PS + g;
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) mma_tf32(S[nt], ak, sb[8 * nt], sb[4 * PS + 8 * nt]);
+            }
+        }
+        __syncthreads();                                 // (a) readers of sS and (c)/(d) readers of sD are done
+        if (own) {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                *reinterpret_cast<float2*>(sS + (16 * warp + g) * PS + 8 * nt + 2 * t) = make_float2(to_tf32(S[nt][0]), to_tf32(S[nt][1]));
+                *reinterpret_cast<float2*>(sS + (16 * warp + g + 8) * PS + 8 * nt + 2 * t) = make_float2(to_tf32(S[nt][2]), to_tf32(S[nt][3]));
+            }
+        }
+    }
+    if (own) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            *reinterpret_cast<float2*>(Sg + (size_t)(16 * warp + g) * DV + c0 + 8 * nt + 2 * t) = make_float2(S[nt][0], S[nt][1]);
+            *reinterpret_cast<float2*>(Sg + (size_t)(16 * warp + g + 8) * DV + c0 + 8 * nt + 2 * t) = make_float2(S[nt][2], S[nt][3]);
+        }
+    }
+}
+
 // grid = (Hv, rows), block = Dv threads
 __global__ void gdn_post_kernel(const float* o, const __nv_bfloat16* proj, int ld_proj, int z_off, const __nv_bfloat16* norm_w,
                                 float eps, int Hv, int Dv, const int* row_slot, __nv_bfloat16* out, const GdnSeqDesc2* seqs,
@@ -463,16 +622,23 @@ static int launch_chunked(const GdnPrepArgs& p, const GdnScanArgs& s, int max_ch
     const size_t raw_b = (size_t)(kChunk + 3) * (2 * DK + DV) * 2, at_b = sizeof(float) * (kChunk * 65 + kChunk * kTP);
     const size_t smem_a = sizeof(float) * (2 * kChunk * (DK + 4) + kChunk * (DV + 4) + 2 * kChunk) + (raw_b > at_b ? raw_b : at_b);
     const size_t smem_b = sizeof(float) * (3 * kChunk * (DK + 4) + DK * (kSlice + 4) + kChunk * (kSlice + 4) + kChunk * 65);
+    const size_t smem_t = sizeof(float) * (2 * kChunk * (DK + 4) + kChunk * (DK + 8) + DK * (kSlice + 8) + kChunk * (kSlice + 8) +
+                                           kChunk * (kChunk + 4));
     static bool set = false;
+    static int use_tc = 1;
     if (!set) {
         cudaFuncSetAttribute(gdn_chunk_prep_kernel<DK, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a);
         cudaFuncSetAttribute(gdn_chunk_scan_kernel<DK, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_b);
+        cudaFuncSetAttribute(gdn_chunk_scan_tc_kernel<DK, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_t);
+        const char* e = getenv("PS_GDN_SCAN");            // "fp32": the CUDA-core scan (all-fp32 products)
+        use_tc = (e == nullptr || e[0] != 'f') ? 1 : 0;
         set = true;
     }
     gdn_chunk_prep_kernel<DK, DV><<<dim3(max_chunks, p.Hv), 256, smem_a, stream>>>(p);
     int err = PS_LAUNCH_CHECK();
     if (err) return err;
-    gdn_chunk_scan_kernel<DK, DV><<<dim3(DV / kSlice, p.Hv, p.n_seqs), 256, smem_b, stream>>>(s);
+    if (use_tc) gdn_chunk_scan_tc_kernel<DK, DV><<<dim3(DV / kSlice, p.Hv, p.n_seqs), 256, smem_t, stream>>>(s);
+    else gdn_chunk_scan_kernel<DK, DV><<<dim3(DV / kSlice, p.Hv, p.n_seqs), 256, smem_b, stream>>>(s);
     return PS_LAUNCH_CHECK();
 }
 }  // namespace ps
