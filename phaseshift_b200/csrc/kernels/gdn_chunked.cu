@@ -83,6 +83,19 @@ __device__ __forceinline__ void wu_rows(const float* sT, const float (&x)[kChunk
     }
 }
 
+// TF32 tensor-core helpers (operands rounded to nearest TF32, fp32 accumulation)
+__device__ __forceinline__ float to_tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
+__device__ __forceinline__ void mma_tf32(float (&c)[4], const float (&a)[4], float b0, float b1) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(__float_as_uint(a[0])), "r"(__float_as_uint(a[1])), "r"(__float_as_uint(a[2])), "r"(__float_as_uint(a[3])),
+                   "r"(__float_as_uint(b0)), "r"(__float_as_uint(b1)));
+}
+
 __device__ __forceinline__ float dot4(const float4& a, const float4& b, float acc) {
     acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc); acc = fmaf(a.z, b.z, acc); return fmaf(a.w, b.w, acc);
 }
@@ -194,32 +207,37 @@ __global__ void __launch_bounds__(256) gdn_chunk_prep_kernel(const GdnPrepArgs a
         for (int d = lane; d < DK; d += 32) { sQ[r * PK + d] *= qn; sK[r * PK + d] *= kn; }
     }
     __syncthreads();
-    // ---- A (strictly lower) and QKd (lower incl. diagonal): rows (t/16) + 16 i, columns (t%16) + 16 j,
-    //      operands read four dims at a time
+    // ---- A (strictly lower) and QKd (lower incl. diagonal) on the tensor cores: warp -> rows 16 mt .., columns
+    //      32 ch .. 32 ch + 31; K K^T and Q K^T share the B fragments (B[k = d][n = s] = K[s][d])
     {
-        const int tr = t / 16, tc = t % 16;
-        float kk[4][4] = {}, qk[4][4] = {};
-        for (int d = 0; d < DK; d += 4) {
-            float4 kr[4], qr[4], kc[4];
+        const int g = lane >> 2, tq = lane & 3, mt = warp & 3, ch = warp >> 2;
+        float kk[4][4], qk[4][4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                kr[i] = *reinterpret_cast<const float4*>(sK + (tr + 16 * i) * PK + d);
-                qr[i] = *reinterpret_cast<const float4*>(sQ + (tr + 16 * i) * PK + d);
-                kc[i] = *reinterpret_cast<const float4*>(sK + (tc + 16 * i) * PK + d);
+        for (int nt = 0; nt < 4; ++nt) { kk[nt][0] = kk[nt][1] = kk[nt][2] = kk[nt][3] = 0.f; qk[nt][0] = qk[nt][1] = qk[nt][2] = qk[nt][3] = 0.f; }
+        if (ch * 32 <= 16 * mt + 15) {                      // tiles entirely above the diagonal stay zero
+            const float* kr = sK + (16 * mt + g) * PK + tq;
+            const float* qr = sQ + (16 * mt + g) * PK + tq;
+#pragma unroll 4
+            for (int ks = 0; ks < DK / 8; ++ks) {
+                const float ak[4] = {to_tf32(kr[8 * ks]), to_tf32(kr[8 * PK + 8 * ks]), to_tf32(kr[8 * ks + 4]), to_tf32(kr[8 * PK + 8 * ks + 4])};
+                const float aq[4] = {to_tf32(qr[8 * ks]), to_tf32(qr[8 * PK + 8 * ks]), to_tf32(qr[8 * ks + 4]), to_tf32(qr[8 * PK + 8 * ks + 4])};
+                const float* kb = sK + (32 * ch + g) * PK + 8 * ks + tq;
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt) {
+                    const float b0 = to_tf32(kb[8 * nt * PK]), b1 = to_tf32(kb[8 * nt * PK + 4]);
+                    mma_tf32(kk[nt], ak, b0, b1);
+                    mma_tf32(qk[nt], aq, b0, b1);
+                }
             }
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-#pragma unroll
-                for (int j = 0; j < 4; ++j) { kk[i][j] = dot4(kr[i], kc[j], kk[i][j]); qk[i][j] = dot4(qr[i], kc[j], qk[i][j]); }
         }
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
+        for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int tt = tr + 16 * i, ss = tc + 16 * j;
+            for (int e = 0; e < 4; ++e) {
+                const int tt = 16 * mt + g + (e >> 1) * 8, ss = 32 * ch + 8 * nt + 2 * tq + (e & 1);
                 const float dec = ss <= tt ? __expf(sG[tt] - sG[ss]) : 0.f;
-                sA[tt * 65 + ss] = ss < tt ? sBeta[tt] * dec * kk[i][j] : 0.f;
-                gQK[tt * kChunk + ss] = dec * qk[i][j];
+                sA[tt * 65 + ss] = ss < tt ? sBeta[tt] * dec * kk[nt][e] : 0.f;
+                gQK[tt * kChunk + ss] = dec * qk[nt][e];
             }
     }
     __syncthreads();
@@ -248,20 +266,40 @@ __global__ void __launch_bounds__(256) gdn_chunk_prep_kernel(const GdnPrepArgs a
         if (t == kChunk) a.dc[(size_t)blockIdx.x * a.Hv + h] = __expf(GC);
     }
     __syncthreads();
-    // ---- W = T diag(beta D) K and U = T diag(beta) V: a thread owns one column, 64 inputs in registers
-    if (t < DK + DV) {
-        const bool isW = t < DK;
-        const int col = isW ? t : t - DK;
-        const float* src = isW ? sK + col : sV + col;
+    // ---- W = T diag(beta D) K (warps 0-3) and U = T diag(beta) V (warps 4-7) on the tensor cores: warp -> rows
+    //      16 mt .., all columns of its matrix; T is lower triangular, so k-steps beyond the row tile are skipped
+    {
+        const int g = lane >> 2, tq = lane & 3, mt = warp & 3;
+        const bool isW = warp < 4;
+        constexpr int NTW = (DK > DV ? DK : DV) / 8;
+        const int ntiles = (isW ? DK : DV) / 8;
+        const float* src = isW ? sK : sV;
         const int pitch = isW ? PK : PV;
-        float x[kChunk];
+        float acc[NTW][4];
 #pragma unroll
-        for (int s = 0; s < kChunk; ++s) x[s] = src[s * pitch] * sBeta[s] * (isW ? __expf(sG[s]) : 1.f);
-        float* dst = isW ? gW + col : gU + col;
+        for (int nt = 0; nt < NTW; ++nt) { acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f; }
+        const float* tr = sT + (16 * mt + g) * kTP + tq;
+        for (int ks = 0; ks < 2 * mt + 2; ++ks) {
+            const float at[4] = {to_tf32(tr[8 * ks]), to_tf32(tr[8 * kTP + 8 * ks]), to_tf32(tr[8 * ks + 4]), to_tf32(tr[8 * kTP + 8 * ks + 4])};
+            const int s0 = 8 * ks + tq, s1 = s0 + 4;
+            const float f0 = sBeta[s0] * (isW ? __expf(sG[s0]) : 1.f), f1 = sBeta[s1] * (isW ? __expf(sG[s1]) : 1.f);
+            const float* b0p = src + s0 * pitch + g;
+            const float* b1p = src + s1 * pitch + g;
+#pragma unroll
+            for (int nt = 0; nt < NTW; ++nt)
+                if (nt < ntiles) mma_tf32(acc[nt], at, to_tf32(b0p[8 * nt] * f0), to_tf32(b1p[8 * nt] * f1));
+        }
+        float* dst = isW ? gW : gU;
         const int dp = isW ? DK : DV;
-        wu_rows<0>(sT, x, dst, dp); wu_rows<1>(sT, x, dst, dp); wu_rows<2>(sT, x, dst, dp); wu_rows<3>(sT, x, dst, dp);
+#pragma unroll
+        for (int nt = 0; nt < NTW; ++nt)
+            if (nt < ntiles) {
+                *reinterpret_cast<float2*>(dst + (size_t)(16 * mt + g) * dp + 8 * nt + 2 * tq) = make_float2(acc[nt][0], acc[nt][1]);
+                *reinterpret_cast<float2*>(dst + (size_t)(16 * mt + g + 8) * dp + 8 * nt + 2 * tq) = make_float2(acc[nt][2], acc[nt][3]);
+            }
     }
 }
+
 
 // True when `row` belongs to a sequence this launch handles (more than min_rows rows in the step).
 __device__ __forceinline__ bool row_is_chunked(const GdnSeqDesc2* seqs, int n_seqs, int min_rows, int row) {
@@ -441,18 +479,6 @@ __global__ void __launch_bounds__(256) gdn_chunk_scan_kernel(const GdnScanArgs a
 // (round-to-nearest, once, when they are stored).  Shared-memory pitches are chosen so that every fragment
 // load is conflict-free: rows indexed by the fragment's group id use a pitch = 4 (mod 32), rows indexed by
 // the k index a pitch = 8 (mod 32).
-__device__ __forceinline__ float to_tf32(float x) {
-    uint32_t r;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-    return __uint_as_float(r);
-}
-__device__ __forceinline__ void mma_tf32(float (&c)[4], const float (&a)[4], float b0, float b1) {
-    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(__float_as_uint(a[0])), "r"(__float_as_uint(a[1])), "r"(__float_as_uint(a[2])), "r"(__float_as_uint(a[3])),
-                   "r"(__float_as_uint(b0)), "r"(__float_as_uint(b1)));
-}
-
 template <int DK, int DV>
 __global__ void __launch_bounds__(256) gdn_chunk_scan_tc_kernel(const GdnScanArgs a) {
     constexpr int PA = DK + 4, PT = DK + 8, PS = kSlice + 8, PQ = kChunk + 4, NT = kSlice / 8;
