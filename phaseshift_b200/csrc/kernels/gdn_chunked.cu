@@ -12,17 +12,19 @@
 //
 //   1. gdn_chunk_prep : one CTA per (chunk, value head): causal depthwise conv (kernel 4) + SiLU with the
 //      taps sliding through registers, L2 normalisation (q also scaled by Dk^-0.5), beta = sigmoid(b),
-//      g = -exp(A_log) softplus(a + dt_bias); then A, T by forward substitution on the identity (one
-//      thread per column, out of registers), W, U, and the decayed operands Qd = D q, Kd = (D_C/D_s) k,
-//      QKd_ts = (D_t/D_s)(q_t.k_s), written to scratch.
+//      g = -exp(A_log) softplus(a + dt_bias); then A and QKd from K K^T and Q K^T on the tensor cores, T by
+//      forward substitution on the identity (one thread per column, out of registers), W and U as
+//      tensor-core products with T, and the decayed operands Qd = D q, Kd = (D_C/D_s) k, written to scratch.
 //   2. gdn_history : stores the raw inputs of each sequence's last rows in the conv ring (a separate
 //      launch so no CTA reads history that another CTA of the same step is overwriting).
-//   3. gdn_chunk_scan : one CTA per (sequence, value head, 32-column slice of Dv) walks the chunks:
-//      Delta = U - W S0 ;  O = Qd S0 + QKd Delta ;  S = D_C S0 + Kd^T Delta.  Three small products per
-//      chunk, no serial solve on the critical path.
+//   3. gdn_chunk_scan_tc : one CTA per (sequence, value head, 64-column slice of Dv) walks the chunks:
+//      Delta = U - W S0 ;  O = Qd S0 + QKd Delta ;  S = D_C S0 + Kd^T Delta.  Three small tensor-core
+//      products per chunk, no serial solve on the critical path; the state stays in accumulator registers.
+//      (gdn_chunk_scan is the same walk with fp32 CUDA-core products, selected by PS_GDN_SCAN=fp32.)
 //   4. gdn_post : RMSNorm over the head's Dv outputs (direct weight) * SiLU(z) -> bf16.
 //
-// All decay ratios have s <= t and g <= 0, so every exponential is <= 1.  State and arithmetic are fp32.
+// All decay ratios have s <= t and g <= 0, so every exponential is <= 1.  The state and every accumulation
+// are fp32; the tensor-core products take TF32 operands (mma.sync m16n8k8, round-to-nearest copies).
 // The reference's chunked kernel (src/phaseshift/models/qwen35/kernels/optimized/gdn/recurrence.hip:
 // 128-519) uses chunk 32, bf16 WMMA products (hi+lo split in "exact" mode) and a 32-step serial forward
 // substitution per column inside the sequential walk.  Decode and speculative verification keep using
@@ -63,26 +65,6 @@ __device__ __forceinline__ bool find_chunk(const GdnSeqDesc2* seqs, int n_seqs, 
     return false;
 }
 
-// Rows 16 RB .. 16 RB + 15 of  out = T x  for one column: T is lower triangular, so the sum stops at
-// column 16 (RB + 1); T rows are read as 16-byte broadcasts.
-template <int RB>
-__device__ __forceinline__ void wu_rows(const float* sT, const float (&x)[kChunk], float* dst, int dp) {
-#pragma unroll
-    for (int rr = 0; rr < 16; ++rr) {
-        const int r = RB * 16 + rr;
-        float s4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int s = 0; s < (RB + 1) * 16; s += 4) {
-            const float4 tv = *reinterpret_cast<const float4*>(sT + r * kTP + s);
-            s4[0] = fmaf(tv.x, x[s], s4[0]);
-            s4[1] = fmaf(tv.y, x[s + 1], s4[1]);
-            s4[2] = fmaf(tv.z, x[s + 2], s4[2]);
-            s4[3] = fmaf(tv.w, x[s + 3], s4[3]);
-        }
-        dst[(size_t)r * dp] = (s4[0] + s4[1]) + (s4[2] + s4[3]);
-    }
-}
-
 // TF32 tensor-core helpers (operands rounded to nearest TF32, fp32 accumulation)
 __device__ __forceinline__ float to_tf32(float x) {
     uint32_t r;
@@ -94,10 +76,6 @@ __device__ __forceinline__ void mma_tf32(float (&c)[4], const float (&a)[4], flo
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(__float_as_uint(a[0])), "r"(__float_as_uint(a[1])), "r"(__float_as_uint(a[2])), "r"(__float_as_uint(a[3])),
                    "r"(__float_as_uint(b0)), "r"(__float_as_uint(b1)));
-}
-
-__device__ __forceinline__ float dot4(const float4& a, const float4& b, float acc) {
-    acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc); acc = fmaf(a.z, b.z, acc); return fmaf(a.w, b.w, acc);
 }
 
 // grid = (max chunks, Hv), block = 256 threads
