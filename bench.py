@@ -44,21 +44,82 @@ def _parse():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons while the timed regions run.
+
+    Reads NVML in a background thread every 10 ms (read-only queries; the handle is found by the CUDA device's
+    UUID so CUDA_VISIBLE_DEVICES does not matter); only samples taken between `begin()` and `stop()` count.
+    Falls back to an `nvidia-smi -lms` child process when NVML cannot be loaded."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index: int):
+        import threading
         self.p = None
+        self.nv = None
+        self.samples = []          # (sm_mhz, reasons bitmask, power W)
+        self.max_mhz = None
+        self.active = False
+        self.done = False
         try:
-            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                       "-lms", "100", "-i", str(gpu_index)], stdout=subprocess.PIPE,
-                                      stderr=subprocess.DEVNULL, text=True)
+            import pynvml as nv
+            import torch
+            nv.nvmlInit()
+            try:
+                uuid = str(torch.cuda.get_device_properties(gpu_index).uuid)
+                self.h = nv.nvmlDeviceGetHandleByUUID(("GPU-" + uuid).encode())
+            except Exception:
+                self.h = nv.nvmlDeviceGetHandleByIndex(gpu_index)
+            self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(self.h, nv.NVML_CLOCK_SM))
+            self.nv = nv
+            self.th = threading.Thread(target=self._run, daemon=True)
+            self.th.start()
         except Exception:
-            self.p = None
+            self.nv = None
+            try:
+                self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                           "-lms", "100", "-i", str(gpu_index)], stdout=subprocess.PIPE,
+                                          stderr=subprocess.DEVNULL, text=True)
+            except Exception:
+                self.p = None
+
+    def _run(self):
+        nv = self.nv
+        while not self.done:
+            if self.active:
+                try:
+                    mhz = float(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                    rs = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.h))
+                    pw = nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0
+                    self.samples.append((mhz, rs, pw))
+                except Exception:
+                    pass
+            time.sleep(0.01)
+
+    def begin(self):
+        self.active = True
 
     def stop(self) -> dict:
+        if self.nv is not None:
+            self.active = False
+            self.done = True
+            self.th.join(timeout=2)
+            nv = self.nv
+            names = (("hw_slowdown", nv.nvmlClocksEventReasonHwSlowdown),
+                     ("hw_thermal_slowdown", nv.nvmlClocksEventReasonHwThermalSlowdown),
+                     ("sw_thermal_slowdown", nv.nvmlClocksEventReasonSwThermalSlowdown),
+                     ("sw_power_cap", nv.nvmlClocksEventReasonSwPowerCap),
+                     ("hw_power_brake", nv.nvmlClocksEventReasonHwPowerBrakeSlowdown),
+                     ("applications_clocks", nv.nvmlClocksEventReasonApplicationsClocksSetting))
+            seen = 0
+            for _, rs, _ in self.samples:
+                seen |= rs
+            sm = [x[0] for x in self.samples]
+            pw = [x[2] for x in self.samples]
+            return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": self.max_mhz,
+                    "reasons": sorted(n for n, bit in names if seen & bit),
+                    "power_w": round(statistics.median(pw), 1) if pw else None,
+                    "samples": len(sm), "source": "nvml"}
         if self.p is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.p.terminate()
@@ -80,7 +141,7 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "source": "nvidia-smi"}
 
 
 def reference_arm(args):
@@ -202,13 +263,14 @@ def main():
         prefill_ms = ev0.elapsed_time(ev1)
 
         # ---------------- end-to-end arm: public API, per-step H2D of inputs + D2H of the sampled token
+        sampler = ClockSampler(local_rank)
         for _ in range(W):
             tok = eng.decode(s, tok)
         b1 = eng.batches[1]
         h2d = b1.h2d_bytes()
         launches0 = eng.ops.launches
         barrier()
-        sampler = ClockSampler(local_rank)
+        sampler.begin()
         t_e2e0 = time.perf_counter()
         for _ in range(K):
             tok = eng.decode(s, tok)
