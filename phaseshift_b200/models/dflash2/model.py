@@ -171,10 +171,27 @@ class DFlash2Drafter:
 
     @staticmethod
     def from_dir(d, device, dtype=torch.float32) -> "DFlash2Drafter":
-        from ...io.model_dir import ShardCollection
+        """Loads a BF16 drafter directory, or a bundle written by the offline quantizer's DFlash2 adapter
+        (block-quantised backbone projections are expanded once at load: the drafter's products run in
+        ``dtype``)."""
+        from ...io.model_dir import ShardCollection, is_quantized_dir
         cfg = DFlash2Config.from_dir(d)
         col = ShardCollection(d)
-        w = {n: col.tensor(n).clone() for n in tensor_shapes(cfg)}
+        if not is_quantized_dir(d):
+            w = {n: col.tensor(n).clone() for n in tensor_shapes(cfg)}
+            return DFlash2Drafter(cfg, w, device, dtype)
+        from ...quant import formats
+        from ...quant.manifest import Manifest
+        entries = Manifest.load(d).by_name()
+        w = {}
+        for n, shape in tensor_shapes(cfg).items():
+            e = entries[n]
+            if e.encoding == "bf16":
+                w[n] = col.tensor(e.data).clone().reshape(shape)
+            else:
+                q = formats.QuantizedTensor(e.encoding, tuple(e.logical_shape), e.k_padded, col.tensor(e.codes),
+                                            col.tensor(e.metadata1), e.metadata2 if e.metadata2 is not None else 1.0)
+                w[n] = formats.dequantize(q).reshape(shape)
         return DFlash2Drafter(cfg, w, device, dtype)
 
     def save(self, d) -> None:

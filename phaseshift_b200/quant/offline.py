@@ -83,6 +83,25 @@ def imatrix_key(name: str) -> str:
     return name
 
 
+def is_drafter_dir(model_dir) -> bool:
+    """True for a DFlash2 drafter directory (config.json names the DFlash2DraftModel architecture)."""
+    try:
+        raw = json.loads((Path(model_dir) / "config.json").read_text())
+    except Exception:
+        return False
+    return (raw.get("architectures") or [""])[0] == "DFlash2DraftModel"
+
+
+def classify_drafter(name: str) -> str:
+    """Role of a DFlash2 drafter tensor.  The backbone projections (q/k/v/o, gate/up/down and the tap
+    projection ``fc``) are the drafter's weight traffic and follow the preset's 4-bit role (reference:
+    src/phaseshift/quantization/fpx/profile.cpp:96-128, "DFlash backbone linears"); norms, the dynamic-conv
+    kernels and the selector tables stay BF16."""
+    if name == "fc.weight" or (name.startswith("layers.") and name.endswith("_proj.weight")):
+        return "dflash_backbone"
+    return "other"
+
+
 def _quantize_tensor(w: torch.Tensor, fmt: str, backend: str, tensor_scale: Optional[float], importance, search: int):
     if fmt == "bf16":
         return formats.quantize(w, "bf16")
@@ -128,20 +147,29 @@ def quantize_model(input_dir, output_dir, preset: str = "nvfp4", backend: str = 
     out.mkdir(parents=True, exist_ok=True)
     if backend == "cuda" and not torch.cuda.is_available():
         raise RuntimeError("--backend cuda requested but no CUDA device is available")
-    cfg = Qwen35Config.from_dir(inp)
+    drafter = is_drafter_dir(inp)
     col = ShardCollection(inp)
     imat = load_imatrix(imatrix) if imatrix else None
-    names = [n for n in col.names() if n.startswith("model.language_model.") or n.startswith("lm_head")]
     group_of = {}
-    for g in scale_groups(cfg):
-        for n in g:
-            group_of[n] = g
+    if drafter:
+        # DFlash2 adapter: same bundle format, drafter tensor names and roles
+        from ..models.dflash2.model import DFlash2Config, tensor_shapes
+        cfg = DFlash2Config.from_dir(inp)
+        names = [n for n in tensor_shapes(cfg) if col.has(n)]
+        classify = classify_drafter
+    else:
+        cfg = Qwen35Config.from_dir(inp)
+        names = [n for n in col.names() if n.startswith("model.language_model.") or n.startswith("lm_head")]
+        classify = classify_qwen35
+        for g in scale_groups(cfg):
+            for n in g:
+                group_of[n] = g
     man = Manifest(preset=preset, source_fingerprint=model_fingerprint(inp),
                    imatrix={"file": str(imatrix), "policy": imatrix_policy} if imatrix else None)
     plan = []
     for n in names:
         dt, shape, _ = col.spec(n)
-        role = classify_qwen35(n)
+        role = classify(n)
         is_matrix = len(shape) == 2 and role not in ("norm", "other")
         fmt = format_for(preset, role, layer_of(n)) if is_matrix else "bf16"
         if imat is not None and is_matrix and fmt != "bf16" and imatrix_key(n) not in imat and role not in ("embed",):
@@ -182,7 +210,7 @@ def quantize_model(input_dir, output_dir, preset: str = "nvfp4", backend: str = 
                                        crc32={n + CODES: c1, n + META1: c2}))
         log(f"quantized {n} {tuple(shape)} -> {fmt}")
     writer.finish()
-    if cfg.tie_word_embeddings:
+    if not drafter and cfg.tie_word_embeddings:
         man.aliases["model.language_model.lm_head.weight"] = "model.language_model.embed_tokens.weight"
     man.save(out)
     for a in ASSETS:
@@ -209,13 +237,17 @@ def validate_model_dir(model_dir) -> List[str]:
     d = Path(model_dir)
     try:
         man = Manifest.load(d)
-        cfg = Qwen35Config.from_dir(d)
+        if is_drafter_dir(d):
+            from ..models.dflash2.model import DFlash2Config, tensor_shapes
+            expected = tensor_shapes(DFlash2Config.from_dir(d))
+        else:
+            from ..models.qwen35.weights import hf_tensor_shapes
+            expected = hf_tensor_shapes(Qwen35Config.from_dir(d))
         col = ShardCollection(d)
     except Exception as e:
         return [f"cannot open: {e}"]
-    from ..models.qwen35.weights import hf_tensor_shapes
     have = man.by_name()
-    for n, shape in hf_tensor_shapes(cfg).items():
+    for n, shape in expected.items():
         n2 = man.aliases.get(n, n)
         if n2 not in have:
             problems.append(f"missing tensor {n}")

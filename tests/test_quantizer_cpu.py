@@ -141,3 +141,37 @@ def test_mxfp4_bundle_loads_and_runs_as_nvfp4(tmp_path):
     ew3 = build_engine_weights(cfg, lambda n: hf[n], "fp8_block128", "cpu")
     assert ew3.layers[0].gate_up.fmt == "mxfp8"
     assert len(Engine(ew3, "cpu", StateConfig(max_slots=1, max_seq_len=64)).generate(prompt, 4, prefill_chunk=16)) == 4
+
+
+def test_dflash2_adapter_quantizes_and_loads_a_drafter(tmp_path):
+    """The quantizer's DFlash2 adapter: backbone projections of a drafter directory become NVFP4, norms /
+    dynamic-conv kernels / selector tables stay BF16, the bundle verifies (and notices corruption), and the
+    drafter loaded from it carries the dequantised weights."""
+    import torch
+    from phaseshift_b200.models.dflash2.model import DFlash2Drafter, random_weights, tiny_drafter_config
+    from phaseshift_b200.models.qwen35.config import tiny_config
+    from phaseshift_b200.quant import formats as F, offline
+    from phaseshift_b200.quant.manifest import Manifest
+    dc = tiny_drafter_config(tiny_config())
+    w = random_weights(dc, seed=5)
+    src = tmp_path / "drafter_bf16"
+    DFlash2Drafter(dc, w, "cpu").save(src)
+    assert offline.is_drafter_dir(src)
+    out = tmp_path / "drafter_nvfp4"
+    man = offline.quantize_model(src, out, "nvfp4", "cpu", log=lambda *_: None)
+    enc = {t.name: t.encoding for t in man.tensors}
+    assert enc["layers.0.self_attn.q_proj.weight"] == "nvfp4" and enc["layers.1.mlp.down_proj.weight"] == "nvfp4"
+    assert enc["fc.weight"] == "nvfp4"
+    assert enc["layers.0.attn_conv.kernel_projection.weight"] == "bf16" and enc["selector.pred_codebook"] == "bf16"
+    assert enc["norm.weight"] == "bf16" and enc["layers.0.attn_conv.base_kernel"] == "bf16"
+    assert offline.validate_model_dir(out) == []
+    d2 = DFlash2Drafter.from_dir(out, "cpu")
+    n = "layers.0.mlp.gate_proj.weight"
+    ref = w[n].to(torch.bfloat16).float()
+    assert torch.equal(d2.w[n], F.dequantize(F.quantize(ref, "nvfp4")).reshape(ref.shape))
+    assert float((d2.w[n] - ref).norm() / ref.norm()) < 0.12
+    assert torch.equal(d2.w["norm.weight"], w["norm.weight"].to(torch.bfloat16).float())
+    assert Manifest.load(out).preset == "nvfp4"
+    victim = next(out.glob("model*.safetensors"))
+    b = bytearray(victim.read_bytes()); b[-3] ^= 0xFF; victim.write_bytes(bytes(b))
+    assert any("CRC" in p for p in offline.validate_model_dir(out))
