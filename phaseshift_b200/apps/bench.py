@@ -17,8 +17,7 @@ FUSED_AWAY = {"activation-quantize": "activation staging is part of the small-M 
               "l2-normalize": "q/k L2 normalisation is fused into the GDN kernel (bench: gdn-recurrence)",
               "rope": "partial RoPE is fused with q/k norm and the KV append (bench: kv-append)",
               "gdn-conv1d": "the short conv is fused into the GDN kernel (bench: gdn-recurrence)",
-              "elementwise": "residual add / SwiGLU / gates live in projection epilogues (bench: gemm)",
-              "mtp": "the MTP head is not built (bench-only in the reference); use dflash2"}
+              "elementwise": "residual add / SwiGLU / gates live in projection epilogues (bench: gemm)"}
 
 
 def _model_args(p):
@@ -42,6 +41,13 @@ def build_parser() -> argparse.ArgumentParser:
     ba = sub.add_parser("batch", help="concurrent serving throughput"); _model_args(ba)
     ba.add_argument("--requests", type=int, default=8); ba.add_argument("--prompt-tokens", type=int, default=512)
     ba.add_argument("--tokens", type=int, default=64); ba.add_argument("--shared-prefix", type=int, default=0)
+    mt = sub.add_parser("mtp", help="speculative decoding with the built-in MTP head (random-init head unless the "
+                                    "model directory carries mtp.* tensors)"); _model_args(mt)
+    mt.add_argument("--context", type=int, default=128); mt.add_argument("--tokens", type=int, default=32)
+    mt.add_argument("--draft-k", type=int, default=4); mt.add_argument("--mtp-chain", default="pre", choices=["pre", "post"])
+    mt.add_argument("--verify-mode", default="exact", choices=["exact", "fast"])
+    mt.add_argument("--replay-check", action="store_true", help="compare the emitted tokens with plain greedy decoding")
+    mt.add_argument("--prefill-chunk", type=int, default=2048)
     ge = sub.add_parser("gemm", help="projection kernels")
     ge.add_argument("--dtype", default="nvfp4", choices=["bf16", "nvfp4", "mxfp8"])
     ge.add_argument("--variant", default="auto", choices=["gemv", "gemm", "batched", "auto"]); ge.add_argument("--rows", default="1,4,8,256,2048")
@@ -59,7 +65,7 @@ def build_parser() -> argparse.ArgumentParser:
     return ap
 
 
-def _engine(a, max_seq_len: int, slots: int = 1):
+def _engine(a, max_seq_len: int, slots: int = 1, spec_rows: int = 0):
     import torch
     from ..models.qwen35.config import PRESETS
     from ..models.qwen35.weights import build_engine_weights, load_engine_weights, random_getter
@@ -71,7 +77,8 @@ def _engine(a, max_seq_len: int, slots: int = 1):
     else:
         cfg = PRESETS[a.random_model or "tiny"]()
         ew = build_engine_weights(cfg, random_getter(cfg, 0, dev), a.preset or "bf16", dev, keep_canonical=dev.type != "cuda")
-    return Engine(ew, dev, StateConfig(max_slots=slots, max_seq_len=max_seq_len, kv_dtype=a.kv_cache_dtype),
+    extra = dict(conv_ring=max(16, 3 + spec_rows), spec_rows=spec_rows) if spec_rows else {}
+    return Engine(ew, dev, StateConfig(max_slots=slots, max_seq_len=max_seq_len, kv_dtype=a.kv_cache_dtype, **extra),
                   batch_shadow=bool(getattr(a, "batch_shadow", 0))), dev
 
 
@@ -124,6 +131,50 @@ def cmd_tg(a) -> int:
     print(f"context={a.context}"); print(f"tokens={a.tokens}"); print(f"decode_ms_per_token={ms / a.tokens:.4f}")
     print(f"gpu_tokens_per_sec={a.tokens / ms * 1e3:.2f}"); print(f"GREEDY_TOKEN_SUM={sums[-1]}")
     print(f"deterministic={int(len(set(sums)) == 1)}")
+    return 0
+
+
+def cmd_mtp(a) -> int:
+    """Speculative decoding with the MTP head (reference bench: src/apps/bench/main.cpp `mtp`, --spec / --verify-mode /
+    --replay-check).  Prints acceptance statistics and the decode rate; the head is random-init unless the model
+    directory has mtp.* tensors, so the acceptance of a random head is the chance level."""
+    import torch
+    from ..models.dflash2.decoder import DFlash2SpecDecoder
+    from ..models.qwen35.mtp import MTPDrafter, random_mtp_weights
+    if not 1 <= a.draft_k <= 7:
+        print("error: --draft-k must be in 1..7", file=sys.stderr)
+        return 2
+    eng, dev = _engine(a, a.context + a.tokens + 16, spec_rows=8)
+    dt = torch.float32 if dev.type == "cpu" else torch.bfloat16
+    head = None
+    if a.model_dir:
+        try:
+            head = MTPDrafter.from_dir(a.model_dir, eng.cfg, dev, dt, a.mtp_chain)
+        except ValueError:
+            head = None
+    source = "model-dir" if head is not None else "random-init"
+    if head is None:
+        head = MTPDrafter(eng.cfg, random_mtp_weights(eng.cfg, 0, dev), dev, dt, a.mtp_chain)
+    dec = DFlash2SpecDecoder(eng, head, num_drafts=a.draft_k)
+    dec.verify_exact = a.verify_mode == "exact"
+    ids = torch.randint(0, eng.cfg.vocab_size, (a.context,), generator=torch.Generator().manual_seed(0)).tolist()
+    times, out, stats = [], [], {}
+    for i in range(a.warmup + a.runs):
+        for k in dec.stats:
+            dec.stats[k] = 0
+        ms, (out, stats) = _timed(dev, lambda: dec.generate(ids, a.tokens, prefill_chunk=a.prefill_chunk))
+        if i >= a.warmup:
+            times.append(ms)
+    ms = statistics.median(times)
+    print(f"context={a.context}"); print(f"tokens={len(out)}"); print(f"draft_k={a.draft_k}"); print(f"mtp_head={source}")
+    print(f"verify_mode={a.verify_mode}"); print(f"rounds={stats['rounds']}"); print(f"accepted={stats['accepted']}")
+    print(f"proposed={stats['proposed']}"); print(f"tokens_per_round={stats['tokens_per_round']}")
+    print(f"request_ms={ms:.3f}"); print(f"gpu_tokens_per_sec={len(out) / ms * 1e3:.2f}   # prefill included")
+    print(f"GREEDY_TOKEN_SUM={sum(out)}")
+    if a.replay_check:
+        plain = eng.generate(ids, a.tokens, prefill_chunk=a.prefill_chunk)
+        print(f"replay_match={int(plain == out)}")
+        return 0 if plain == out or a.verify_mode == "fast" else 1
     return 0
 
 
@@ -310,7 +361,8 @@ def main(argv: Optional[List[str]] = None) -> int:
     if a.cmd in FUSED_AWAY:
         print(f"{a.cmd}: {FUSED_AWAY[a.cmd]}")
         return 0
-    return {"pp": cmd_pp, "tg": cmd_tg, "batch": cmd_batch, "gemm": cmd_gemm, "tp-reduce": cmd_tp_reduce}.get(a.cmd, cmd_kernel)(a)
+    return {"pp": cmd_pp, "tg": cmd_tg, "batch": cmd_batch, "gemm": cmd_gemm, "tp-reduce": cmd_tp_reduce,
+            "mtp": cmd_mtp}.get(a.cmd, cmd_kernel)(a)
 
 
 if __name__ == "__main__":

@@ -42,7 +42,9 @@ def embed_rows(table, ids: torch.Tensor) -> torch.Tensor:
 
 
 class DFlash2SpecDecoder:
-    def __init__(self, engine, drafter: DFlash2Drafter, num_drafts: int = 7, ngram_tail: int = 0, ngram_n: int = 0):
+    def __init__(self, engine, drafter, num_drafts: int = 7, ngram_tail: int = 0, ngram_n: int = 0):
+        """``drafter``: a ``DFlash2Drafter`` or any object with the same interface (``cfg.target_layer_ids``,
+        ``reset``, ``append_context``, ``propose``), e.g. the built-in MTP head (models/qwen35/mtp.py)."""
         if engine.sc.spec_rows < num_drafts + 1 + ngram_tail:
             raise ValueError("engine state was not sized for this many speculative rows (StateConfig.spec_rows)")
         if engine.sc.conv_ring < 3 + num_drafts + 1 + ngram_tail:
@@ -50,8 +52,11 @@ class DFlash2SpecDecoder:
         self.eng, self.drafter, self.k = engine, drafter, num_drafts
         self.ngram_tail, self.ngram_n = ngram_tail, ngram_n
         self.rt = runtime()
+        self.verify_exact = True       # Exact numeric mode: every verified row uses single-row-decode arithmetic
         if hasattr(engine.ops, "topk"):
             drafter.topk_fn = engine.ops.topk              # exact radix top-k kernel for the candidate sets
+        if hasattr(drafter, "bind"):
+            drafter.bind(self._embed, self._lm_head)
         self.taps = list(drafter.cfg.target_layer_ids)
         cfg = engine.cfg
         rows = 16 if num_drafts + 1 + ngram_tail > 8 else 8
@@ -80,8 +85,12 @@ class DFlash2SpecDecoder:
         x = h.to(ops.act_dtype).contiguous()
         return ops.linear(x, self.eng.runner.w.lm_head, name="dflash_logits", out_f32=True).float()
 
-    def _append_taps(self, out, n_rows: int, pos_start: int) -> None:
-        self.drafter.append_context([out.taps[l][:n_rows] for l in self.taps], pos_start)
+    def _append_taps(self, out, n_rows: int, pos_start: int, tokens: Sequence[int]) -> None:
+        taps = [out.taps[l][:n_rows] for l in self.taps]
+        if getattr(self.drafter, "wants_tokens", False):       # e.g. the MTP head pairs hidden j with token j + 1
+            self.drafter.append_context(taps, pos_start, tokens=list(tokens[:n_rows]))
+        else:
+            self.drafter.append_context(taps, pos_start)
 
     # ------------------------------------------------------------------ phases
     def prefill(self, s, prompt: Sequence[int], chunk: int, samp: dict) -> int:
@@ -92,7 +101,7 @@ class DFlash2SpecDecoder:
             pos0 = s.position
             toks, out = self.eng.step([SeqRows(s.slot, pos0, ids, (len(ids) - 1,) if last else (), sample_index=0, **samp)],
                                       [s], tap_layers=self.taps)
-            self._append_taps(out, len(ids), pos0)
+            self._append_taps(out, len(ids), pos0, ids)
             if toks:
                 tok = toks[0]
         return tok
@@ -106,7 +115,7 @@ class DFlash2SpecDecoder:
         if k == 0:
             toks, out = eng.step([SeqRows(s.slot, pos0, [anchor], (0,), sample_index=len(generated), **samp)], [s],
                                  tap_layers=self.taps)
-            self._append_taps(out, 1, pos0)
+            self._append_taps(out, 1, pos0, [anchor])
             self.stats["plain_steps"] += 1
             return [toks[0]]
         drafts = self.drafter.propose(anchor, k, self._embed, self._lm_head, pos0)
@@ -116,7 +125,7 @@ class DFlash2SpecDecoder:
         rows = [anchor] + drafts
         n = len(rows)
         toks, out = eng.step([SeqRows(s.slot, pos0, rows, tuple(range(n)), sample_index=len(generated), **samp)], [s],
-                             commit=False, tap_layers=self.taps, gdn_log=self.logs, gdn_to_alt=True, exact=True)
+                             commit=False, tap_layers=self.taps, gdn_log=self.logs, gdn_to_alt=True, exact=self.verify_exact)
         accepted, nxt, full = self.rt.spec_greedy_accept(drafts, toks)
         keep = accepted + 1                                  # anchor + accepted drafts are now part of the sequence
         st = eng.state
@@ -126,7 +135,7 @@ class DFlash2SpecDecoder:
                 eng.ops.gdn_replay(g, st.hv, desc, 1, self.logs[li])
         s.position = pos0 + keep
         eng.trim_pages(s)
-        self._append_taps(out, keep, pos0)
+        self._append_taps(out, keep, pos0, rows)
         self.stats["rounds"] += 1
         self.stats["accepted"] += accepted
         self.stats["proposed"] += len(drafts)

@@ -129,3 +129,8 @@ def test_bench_subcommands_help_and_cpu_runs(capsys):
     assert bench.main(["batch", "--random-model", "tiny", "--device", "cpu", "--requests", "3", "--prompt-tokens", "20",
                        "--tokens", "3"]) == 0
     assert "aggregate_tokens_per_sec" in capsys.readouterr().out
+    # MTP speculative decoding with a random head: exact verification reproduces plain greedy decoding
+    assert bench.main(["mtp", "--random-model", "tiny", "--device", "cpu", "--context", "20", "--tokens", "10", "--draft-k", "3",
+                       "--runs", "1", "--warmup", "0", "--replay-check"]) == 0
+    out = dict(l.split("=", 1) for l in capsys.readouterr().out.strip().splitlines())
+    assert out["replay_match"] == "1" and int(out["proposed"]) >= int(out["accepted"]) and out["mtp_head"] == "random-init"
