@@ -49,6 +49,8 @@ struct GdnPrepArgs {
     int min_rows;                                // sequences with at most this many rows are left to the row kernel
     float* scratch;                              // per (chunk, head): W, Qd, Kd [64,Dk]; U [64,Dv]; QKd [64,64]
     float* dc;                                   // per (chunk, head): D_C
+    int round_tf32;                              // 1: W, Qd, Kd, QKd are stored rounded to TF32 (the tensor-core scan copies them
+                                                 // into shared memory asynchronously and cannot round on the way)
 };
 
 __host__ __device__ inline size_t chunk_scratch_floats(int Dk, int Dv) { return (size_t)kChunk * (3 * Dk + Dv + kChunk); }
@@ -215,7 +217,7 @@ __global__ void __launch_bounds__(256) gdn_chunk_prep_kernel(const GdnPrepArgs a
                 const int tt = 16 * mt + g + (e >> 1) * 8, ss = 32 * ch + 8 * nt + 2 * tq + (e & 1);
                 const float dec = ss <= tt ? __expf(sG[tt] - sG[ss]) : 0.f;
                 sA[tt * 65 + ss] = ss < tt ? sBeta[tt] * dec * kk[nt][e] : 0.f;
-                gQK[tt * kChunk + ss] = dec * qk[nt][e];
+                gQK[tt * kChunk + ss] = a.round_tf32 ? to_tf32(dec * qk[nt][e]) : dec * qk[nt][e];
             }
     }
     __syncthreads();
@@ -238,8 +240,13 @@ __global__ void __launch_bounds__(256) gdn_chunk_prep_kernel(const GdnPrepArgs a
             const int r = (i * 4) / DK, d = (i * 4) % DK;
             const float eq = __expf(sG[r]), ek = __expf(GC - sG[r]);
             const float4 q = *reinterpret_cast<const float4*>(sQ + r * PK + d), k = *reinterpret_cast<const float4*>(sK + r * PK + d);
-            reinterpret_cast<float4*>(gQd)[i] = make_float4(eq * q.x, eq * q.y, eq * q.z, eq * q.w);
-            reinterpret_cast<float4*>(gKd)[i] = make_float4(ek * k.x, ek * k.y, ek * k.z, ek * k.w);
+            float4 qd = make_float4(eq * q.x, eq * q.y, eq * q.z, eq * q.w), kd = make_float4(ek * k.x, ek * k.y, ek * k.z, ek * k.w);
+            if (a.round_tf32) {
+                qd = make_float4(to_tf32(qd.x), to_tf32(qd.y), to_tf32(qd.z), to_tf32(qd.w));
+                kd = make_float4(to_tf32(kd.x), to_tf32(kd.y), to_tf32(kd.z), to_tf32(kd.w));
+            }
+            reinterpret_cast<float4*>(gQd)[i] = qd;
+            reinterpret_cast<float4*>(gKd)[i] = kd;
         }
         if (t == kChunk) a.dc[(size_t)blockIdx.x * a.Hv + h] = __expf(GC);
     }
@@ -269,6 +276,10 @@ __global__ void __launch_bounds__(256) gdn_chunk_prep_kernel(const GdnPrepArgs a
         }
         float* dst = isW ? gW : gU;
         const int dp = isW ? DK : DV;
+        if (isW && a.round_tf32) {
+#pragma unroll
+            for (int nt = 0; nt < NTW; ++nt) { acc[nt][0] = to_tf32(acc[nt][0]); acc[nt][1] = to_tf32(acc[nt][1]); acc[nt][2] = to_tf32(acc[nt][2]); acc[nt][3] = to_tf32(acc[nt][3]); }
+        }
 #pragma unroll
         for (int nt = 0; nt < NTW; ++nt)
             if (nt < ntiles) {
@@ -494,32 +505,51 @@ __global__ void __launch_bounds__(256) gdn_chunk_scan_tc_kernel(const GdnScanArg
         }
     }
 
+    // Tile traffic is asynchronous (cp.async, 16 bytes per copy; the preparation kernel already rounded W, Qd, Kd and
+    // QKd to TF32).  Per chunk the copy groups are committed in the order [U] [QKd] [Kd] and, once product (a) has
+    // released its operands, [W, Qd of the next chunk]; each product waits only for the groups it reads, so Kd and QKd
+    // arrive under product (a) and the next chunk's W / Qd under products (c) and (d).
+    auto cp16 = [](float* dst, const float* src) {
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+    };
+    auto commit = []() { asm volatile("cp.async.commit_group;" ::: "memory"); };
+    auto issue_wq = [&](int chunk_id) {
+        const float* scr = a.scratch + ((size_t)chunk_id * Hv + h) * chunk_scratch_floats(DK, DV);
+        const float* gW = scr; const float* gQd = gW + kChunk * DK;
+        for (int i = tid; i < kChunk * DK / 4; i += 256) {
+            const int r = (i * 4) / DK, d = (i * 4) % DK;
+            cp16(sW + r * PA + d, gW + 4 * i);
+            cp16(sQd + r * PA + d, gQd + 4 * i);
+        }
+    };
+    issue_wq(gc);
+    commit();
+
     for (int r0 = 0; r0 < sd.n_rows; r0 += kChunk, ++gc) {
         const int C = min(kChunk, sd.n_rows - r0);
         const size_t rowbase = (size_t)(sd.row_start + r0);
         const float* scr = a.scratch + ((size_t)gc * Hv + h) * chunk_scratch_floats(DK, DV);
-        const float* gW = scr; const float* gQd = gW + kChunk * DK; const float* gKd = gQd + kChunk * DK;
+        const float* gKd = scr + 2 * kChunk * DK;
         const float* gU = gKd + kChunk * DK; const float* gQK = gU + kChunk * DV;
-        __syncthreads();                                 // previous chunk's readers of the tiles are done
-        for (int i = tid; i < kChunk * DK / 4; i += 256) {
-            const int r = (i * 4) / DK, d = (i * 4) % DK;
-            const float4 w = __ldg(reinterpret_cast<const float4*>(gW) + i), q = __ldg(reinterpret_cast<const float4*>(gQd) + i);
-            const float4 k = __ldg(reinterpret_cast<const float4*>(gKd) + i);
-            *reinterpret_cast<float4*>(sW + r * PA + d) = make_float4(to_tf32(w.x), to_tf32(w.y), to_tf32(w.z), to_tf32(w.w));
-            *reinterpret_cast<float4*>(sQd + r * PA + d) = make_float4(to_tf32(q.x), to_tf32(q.y), to_tf32(q.z), to_tf32(q.w));
-            *reinterpret_cast<float4*>(sKd + r * PT + d) = make_float4(to_tf32(k.x), to_tf32(k.y), to_tf32(k.z), to_tf32(k.w));
-        }
-        for (int i = tid; i < kChunk * kChunk / 4; i += 256) {
-            const int r = (i * 4) / kChunk, c = (i * 4) % kChunk;
-            const float4 v = __ldg(reinterpret_cast<const float4*>(gQK) + i);
-            *reinterpret_cast<float4*>(sQK + r * PQ + c) = make_float4(to_tf32(v.x), to_tf32(v.y), to_tf32(v.z), to_tf32(v.w));
-        }
+        // the barrier that closed the previous chunk's product (d) released sD, sQK and sKd
         for (int i = tid; i < kChunk * kSlice / 4; i += 256) {
             const int r = (i * 4) / kSlice, c = (i * 4) % kSlice;
-            *reinterpret_cast<float4*>(sD + r * PS + c) = __ldg(reinterpret_cast<const float4*>(gU + (size_t)r * DV + c0 + c));
+            cp16(sD + r * PS + c, gU + (size_t)r * DV + c0 + c);
         }
+        commit();
+        for (int i = tid; i < kChunk * kChunk / 4; i += 256) {
+            const int r = (i * 4) / kChunk, c = (i * 4) % kChunk;
+            cp16(sQK + r * PQ + c, gQK + 4 * i);
+        }
+        commit();
+        for (int i = tid; i < kChunk * DK / 4; i += 256) {
+            const int r = (i * 4) / DK, d = (i * 4) % DK;
+            cp16(sKd + r * PT + d, gKd + 4 * i);
+        }
+        commit();
         const float DC = a.dc[(size_t)gc * Hv + h];
-        __syncthreads();
+        asm volatile("cp.async.wait_group 2;" ::: "memory");      // [W, Qd] and [U] have landed (this thread's copies)
+        __syncthreads();                                          // ... everyone's; also orders the sS stores before (a)
         // ---- (a) P = W S0, R = Qd S0 : rows 16 mt .., columns 32 ch + 8 nt ..
         float P[4][4], R[4][4];
 #pragma unroll
@@ -549,7 +579,10 @@ __global__ void __launch_bounds__(256) gdn_chunk_scan_tc_kernel(const GdnScanArg
             *reinterpret_cast<float2*>(d0) = make_float2(to_tf32(u0.x - P[nt][0]), to_tf32(u0.y - P[nt][1]));
             *reinterpret_cast<float2*>(d1) = make_float2(to_tf32(u1.x - P[nt][2]), to_tf32(u1.y - P[nt][3]));
         }
-        __syncthreads();
+        asm volatile("cp.async.wait_group 1;" ::: "memory");      // [QKd] has landed; [Kd] may still be in flight
+        __syncthreads();                                          // Delta and QKd visible; (a) is done with sW / sQd
+        if (r0 + kChunk < sd.n_rows) issue_wq(gc + 1);
+        commit();                                                 // (an empty group on the last chunk keeps the counts uniform)
         // ---- (c) O = R + QKd Delta (QKd is zero above the diagonal: k-steps beyond this row tile are skipped)
         {
             const float* ar = sQK + (16 * mt + g) * PQ + t;
@@ -567,6 +600,8 @@ __global__ void __launch_bounds__(256) gdn_chunk_scan_tc_kernel(const GdnScanArg
                 if (row_hi < C) *reinterpret_cast<float2*>(a.o + ((rowbase + row_hi) * Hv + h) * DV + col) = make_float2(R[nt][2], R[nt][3]);
             }
         }
+        asm volatile("cp.async.wait_group 1;" ::: "memory");      // [Kd] has landed; the next chunk's [W, Qd] may be in flight
+        __syncthreads();
         // ---- (d) S = D_C S0 + Kd^T Delta : state rows 16 warp .., all columns; A[m = d][k = s] = Kd[s][d]
         if (own) {
 #pragma unroll
@@ -589,6 +624,7 @@ __global__ void __launch_bounds__(256) gdn_chunk_scan_tc_kernel(const GdnScanArg
             }
         }
     }
+    asm volatile("cp.async.wait_all;" ::: "memory");
     if (own) {
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
@@ -638,7 +674,9 @@ static int launch_chunked(const GdnPrepArgs& p, const GdnScanArgs& s, int max_ch
         use_tc = (e == nullptr || e[0] != 'f') ? 1 : 0;
         set = true;
     }
-    gdn_chunk_prep_kernel<DK, DV><<<dim3(max_chunks, p.Hv), 256, smem_a, stream>>>(p);
+    GdnPrepArgs pp = p;
+    pp.round_tf32 = use_tc;
+    gdn_chunk_prep_kernel<DK, DV><<<dim3(max_chunks, p.Hv), 256, smem_a, stream>>>(pp);
     int err = PS_LAUNCH_CHECK();
     if (err) return err;
     if (use_tc) gdn_chunk_scan_tc_kernel<DK, DV><<<dim3(DV / kSlice, p.Hv, p.n_seqs), 256, smem_t, stream>>>(s);

@@ -168,6 +168,9 @@ class DFlash2Drafter:
         self.v_ring = torch.zeros_like(self.k_ring)
         self.ring_pos = torch.full((W,), -1, dtype=torch.long, device=self.device)   # absolute position held by a slot
         self.context_len = 0
+        self.use_graph = True          # CUDA devices: proposals replay a captured graph (see _propose_captured)
+        self._graphs: Dict[int, tuple] = {}
+        self.graph_error: Optional[str] = None
 
     @staticmethod
     def from_dir(d, device, dtype=torch.float32) -> "DFlash2Drafter":
@@ -245,12 +248,18 @@ class DFlash2Drafter:
         self.ring_pos[slots] = pos
         self.context_len = pos_start + n
 
-    def backbone(self, x: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
+    def backbone(self, x: torch.Tensor, pos: torch.Tensor, static: bool = False) -> torch.Tensor:
+        """``static``: attend over every ring slot and mask the empty ones instead of compacting the live slots, so
+        that all shapes are fixed and the call can be captured in a CUDA graph (same mathematics)."""
         c = self.cfg
         T = x.shape[0]
         G = c.num_attention_heads // c.num_key_value_heads
-        valid = self.ring_pos >= 0
-        ctx_pos = self.ring_pos[valid]
+        if static:
+            live = None
+            ctx_pos = self.ring_pos
+        else:
+            live = torch.nonzero(self.ring_pos >= 0).squeeze(1)   # one host synchronisation per call, none per layer
+            ctx_pos = self.ring_pos.index_select(0, live)
         for l in range(c.num_hidden_layers):
             p = f"layers.{l}."
             n = _rms(x, self.w[p + "input_layernorm.weight"], c.rms_norm_eps)
@@ -260,13 +269,13 @@ class DFlash2Drafter:
             vn = (a @ self.w[p + "self_attn.v_proj.weight"].T).reshape(T, c.num_key_value_heads, c.head_dim)
             q = _rope(_rms(q, self.w[p + "self_attn.q_norm.weight"], c.rms_norm_eps), pos, c.rope_theta)
             kn = _rope(_rms(kn, self.w[p + "self_attn.k_norm.weight"], c.rms_norm_eps), pos, c.rope_theta)
-            kc = self.k_ring[l][valid].reshape(-1, c.num_key_value_heads, c.head_dim)
-            vc = self.v_ring[l][valid].reshape(-1, c.num_key_value_heads, c.head_dim)
+            kc = (self.k_ring[l] if static else self.k_ring[l].index_select(0, live)).reshape(-1, c.num_key_value_heads, c.head_dim)
+            vc = (self.v_ring[l] if static else self.v_ring[l].index_select(0, live)).reshape(-1, c.num_key_value_heads, c.head_dim)
             K = torch.cat([kc, kn], 0).repeat_interleave(G, 1)
             V = torch.cat([vc, vn], 0).repeat_interleave(G, 1)
             kpos = torch.cat([ctx_pos, pos], 0)
             s = torch.einsum("thd,shd->hts", q.float(), K.float()) * (c.head_dim ** -0.5)
-            ok = (pos[:, None] - kpos[None, :]).abs() < c.sliding_window        # non-causal window
+            ok = ((pos[:, None] - kpos[None, :]).abs() < c.sliding_window) & (kpos >= 0)[None, :]   # non-causal window
             s = s.masked_fill(~ok[None], float("-inf"))
             att = torch.einsum("hts,shd->thd", torch.softmax(s, -1), V.float()).to(x.dtype)
             o = att.reshape(T, -1) @ self.w[p + "self_attn.o_proj.weight"].T
@@ -284,6 +293,14 @@ class DFlash2Drafter:
     def propose(self, anchor: int, k: int, embed, lm_head_logits, pos_start: int, allowed=None) -> List[int]:
         """``embed(ids)`` -> [n, H] target embeddings, ``lm_head_logits(h)`` -> [n, vocab] fp32 target-head logits."""
         c = self.cfg
+        # one graph, for the draft count the decoder normally asks for; the shorter proposals at the end of a request
+        # run eagerly (a capture costs more than the handful of calls it would serve)
+        if self.device.type == "cuda" and allowed is None and self.use_graph and k >= 1 and (not self._graphs or k in self._graphs):
+            try:
+                return self._propose_captured(anchor, k, embed, lm_head_logits, pos_start)
+            except RuntimeError as e:                  # capture refused (e.g. an op that synchronises): stay eager
+                self.use_graph, self.graph_error = False, str(e)
+                torch.cuda.synchronize(self.device)
         ids = torch.tensor([anchor] + [c.mask_token_id] * k, device=self.device)
         x = embed(ids).to(self.dtype)
         pos = torch.arange(pos_start, pos_start + k + 1, device=self.device)
@@ -293,7 +310,47 @@ class DFlash2Drafter:
             logits = logits.masked_fill(~allowed, float("-inf"))
         return self.select(h, logits, anchor)
 
+    def _propose_captured(self, anchor: int, k: int, embed, lm_head_logits, pos_start: int) -> List[int]:
+        """The whole proposal (embedding, backbone over the full ring, target head, top-k, selector chain) as one CUDA
+        graph per draft count: a proposal is a few hundred small launches, so eager dispatch costs more than the math.
+        Inputs live in fixed tensors (token ids, positions); the K/V ring and its position table are updated in place
+        between replays by ``append_context``."""
+        st = self._graphs.get(k)
+        if st is None:
+            c = self.cfg
+            ids = torch.full((k + 1,), c.mask_token_id, dtype=torch.long, device=self.device)
+            base = torch.arange(k + 1, device=self.device)
+            pos = torch.zeros(k + 1, dtype=torch.long, device=self.device)
+
+            def run():
+                x = embed(ids).to(self.dtype)
+                h = self.backbone(x, pos, static=True)[1:]
+                return self.select_device(h, lm_head_logits(h).float(), ids[0])
+            ids[0] = anchor
+            torch.add(base, pos_start, out=pos)
+            cur = torch.cuda.current_stream(self.device)
+            side = torch.cuda.Stream(self.device)
+            side.wait_stream(cur)
+            with torch.cuda.stream(side):                 # warm-up off the capture: workspaces get allocated here
+                for _ in range(2):
+                    run()
+            cur.wait_stream(side)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                out = run()
+            st = (graph, ids, base, pos, out)
+            self._graphs[k] = st
+        graph, ids, base, pos, out = st
+        ids[0] = anchor
+        torch.add(base, pos_start, out=pos)
+        graph.replay()
+        return out.tolist()
+
     def select(self, h: torch.Tensor, logits: torch.Tensor, anchor: int) -> List[int]:
+        picks = self.select_device(h, logits, torch.tensor(anchor, device=logits.device))
+        return picks.tolist() if picks is not None else []
+
+    def select_device(self, h: torch.Tensor, logits: torch.Tensor, prev: torch.Tensor):
         """Exact top-k (logit desc, id asc) then the sequential candidate selector chain.  The chain runs on the
         device without reading intermediate winners back: one host synchronisation per proposal."""
         c = self.cfg
@@ -307,12 +364,15 @@ class DFlash2Drafter:
             order = torch.argsort(logits, dim=-1, descending=True, stable=True)[:, :kk]
             top_l = torch.gather(logits, 1, order)
         hproj = (h @ self.w["selector.hidden_projection.weight"].T).float()     # [K, rank]
-        pred, succ = self.w["selector.pred_codebook"].float(), self.w["selector.succ_codebook"].float()
-        prev = torch.tensor(anchor, device=logits.device)
+        pred, succ = self.w["selector.pred_codebook"], self.w["selector.succ_codebook"]
+        # Every index below is a one-element tensor used through index_select: indexing with a zero-dimensional
+        # tensor would read it back to the host (a synchronisation per step, and illegal during graph capture).
+        prev = prev.reshape(1)
         picks = []
         for r in range(h.shape[0]):
-            score = top_l[r] + (pred[prev] * hproj[r]) @ succ[order[r]].T
-            j = torch.argmax(score)                        # first maximal index = best-ranked candidate on ties
-            prev = order[r, j]
+            cand = order[r]
+            score = top_l[r] + (pred.index_select(0, prev)[0].float() * hproj[r]) @ succ.index_select(0, cand).float().T
+            j = torch.argmax(score).reshape(1)             # first maximal index = best-ranked candidate on ties
+            prev = cand.index_select(0, j)
             picks.append(prev)
-        return torch.stack(picks).tolist() if picks else []
+        return torch.cat(picks) if picks else None

@@ -449,6 +449,41 @@ def test_dflash2_exact_verify_on_gpu():
         assert out2 == plain and stats2["accepted"] == stats2["proposed"], (preset, stats2)
 
 
+def test_dflash2_captured_proposal_matches_eager():
+    """The drafter's proposal replayed from its CUDA graph (attention over the whole ring with empty slots masked)
+    against the eager path (live slots compacted): same backbone output, and replays follow the ring and the anchor."""
+    from phaseshift_b200.models.dflash2.decoder import DFlash2SpecDecoder
+    from phaseshift_b200.models.dflash2.model import DFlash2Drafter, random_weights, tiny_drafter_config
+    from phaseshift_b200.runtime.engine import Engine
+    cfg = tiny_config()
+    hf = random_hf_weights(cfg, seed=0)
+    ew = build_engine_weights(cfg, lambda n: hf[n], "bf16", "cuda")
+    eng = Engine(ew, "cuda", StateConfig(max_slots=1, max_seq_len=96, conv_ring=16, spec_rows=8))
+    dcfg = tiny_drafter_config(cfg)
+    dr = DFlash2Drafter(dcfg, random_weights(dcfg, 1), "cuda")
+    dec = DFlash2SpecDecoder(eng, dr, num_drafts=5)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    taps = [torch.randn(30, cfg.hidden_size, device="cuda", generator=g) for _ in dcfg.target_layer_ids]
+    dr.append_context(taps, 0)
+    x = torch.randn(6, cfg.hidden_size, device="cuda", generator=g)
+    pos = torch.arange(30, 36, device="cuda")
+    assert _rel_err(dr.backbone(x, pos, static=True), dr.backbone(x, pos)) < 1e-4
+    dr.use_graph = False
+    eager = dr.propose(7, 5, dec._embed, dec._lm_head, 30)
+    dr.use_graph = True
+    first = dr.propose(7, 5, dec._embed, dec._lm_head, 30)             # captures
+    again = dr.propose(7, 5, dec._embed, dec._lm_head, 30)             # replays
+    assert len(first) == 5 and first == again
+    assert dr.graph_error is None and 5 in dr._graphs                  # the graph path really ran
+    assert sum(a == b for a, b in zip(first, eager)) >= 4               # same mathematics (ties aside)
+    dr.append_context([t[:4] for t in taps], 30)                       # the ring moved: replays must see it
+    dr.use_graph = False
+    eager2 = dr.propose(9, 5, dec._embed, dec._lm_head, 34)
+    dr.use_graph = True
+    assert sum(a == b for a, b in zip(dr.propose(9, 5, dec._embed, dec._lm_head, 34), eager2)) >= 4
+    assert int(eng.ops.status[0]) == 0
+
+
 def test_radix_topk_matches_sort_and_breaks_ties_by_id():
     cfg = tiny_config()
     cu, _ = _ops(cfg)
