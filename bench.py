@@ -152,7 +152,7 @@ def reference_arm(args):
     non-clang toolchains); it has no Python package, so it cannot be installed or run on a B200."""
     print(json.dumps({"impl": "reference", "unavailable":
                       "reference is a HIP C++20 runtime that builds only for AMD gfx1201 (cmake/options.cmake:109-115); "
-                      "pip install of /root/reference fails: no setup.py/pyproject.toml, no CUDA path"}))
+                      "pip install of the reference tree fails: no setup.py/pyproject.toml, no CUDA path"}))
     return 0
 
 
