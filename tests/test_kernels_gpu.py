@@ -449,6 +449,24 @@ def test_dflash2_exact_verify_on_gpu():
         assert out2 == plain and stats2["accepted"] == stats2["proposed"], (preset, stats2)
 
 
+def test_mtp_head_speculative_decoding_on_gpu():
+    """The MTP head as drafter on the CUDA engine: Exact verification keeps the greedy stream for both chaining modes."""
+    from phaseshift_b200.models.dflash2.decoder import DFlash2SpecDecoder
+    from phaseshift_b200.models.qwen35.mtp import MTPDrafter, random_mtp_weights
+    from phaseshift_b200.runtime.engine import Engine
+    cfg = tiny_config()
+    hf = random_hf_weights(cfg, seed=0)
+    prompt = torch.randint(0, cfg.vocab_size, (19,), generator=torch.Generator().manual_seed(9)).tolist()
+    ew = build_engine_weights(cfg, lambda n: hf[n], "nvfp4", "cuda")
+    plain = Engine(ew, "cuda", StateConfig(max_slots=1, max_seq_len=96)).generate(prompt, 20, prefill_chunk=8)
+    for chain in ("pre", "post"):
+        eng = Engine(ew, "cuda", StateConfig(max_slots=1, max_seq_len=96, conv_ring=16, spec_rows=8))
+        head = MTPDrafter(cfg, random_mtp_weights(cfg, 3, "cuda"), "cuda", torch.bfloat16, chain=chain)
+        out, stats = DFlash2SpecDecoder(eng, head, num_drafts=3).generate(prompt, 20, prefill_chunk=8)
+        assert out == plain, chain
+        assert stats["rounds"] > 0 and int(eng.ops.status[0]) == 0
+
+
 def test_dflash2_captured_proposal_matches_eager():
     """The drafter's proposal replayed from its CUDA graph (attention over the whole ring with empty slots masked)
     against the eager path (live slots compacted): same backbone output, and replays follow the ring and the anchor."""
