@@ -41,6 +41,9 @@ def _parse():
     ap.add_argument("--resident-bf16", type=int, default=0,
                     help="1: keep a bf16 expansion of every projection resident (2 B/weight more) so prefill and "
                          "multi-row steps skip the expansion pass; single-row decode still streams the block codes")
+    ap.add_argument("--layout", default="both", choices=["both", "tc", "stream"],
+                    help="kernel-side weight layouts kept resident: tensor-core operands, streaming tiles, or both "
+                         "(single-row decode streams, everything else runs on the tensor cores)")
     ap.add_argument("--watchdog", type=int, default=1500,
                     help="seconds after which a hung run dumps every thread's stack to stderr and exits")
     return ap.parse_args()
@@ -244,7 +247,7 @@ def main():
     formats.DEFAULT_SEARCH = args.quant_search
     with torch.no_grad():
         ew = build_engine_weights(cfg, random_getter(cfg, seed=0, device=dev), args.preset, dev,
-                                  tp_rank=rank, tp_size=world, keep_canonical=False)
+                                  tp_rank=rank, tp_size=world, keep_canonical=False, layout=args.layout)
     torch.cuda.synchronize()
     build_s = time.time() - t0
     K, W = args.steps, args.warmup
@@ -288,7 +291,7 @@ def main():
         # ---------------- device-timed arm: K graph replays, token fed back on the device
         pos0 = s.position
         eng._reserve(s, pos0 + K + max(W, 3) + 1)
-        graph_key = 1 * 4096 + 1
+        graph_key = (1 * 4096 + 1) * 2 + 1            # bucket 1, one output row, identity output gather
         graph = eng.graphs[graph_key]
         gout = eng.graph_out[graph_key]
         b1.fill([SeqRows(s.slot, pos0, [tok], (0,))]); b1.graph_static = True; b1.upload()

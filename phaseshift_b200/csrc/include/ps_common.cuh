@@ -23,6 +23,11 @@ enum PsDeviceStatus : uint32_t {
     PS_DEV_NONFINITE = 4,
 };
 
+// Budget, in GPU clock cycles, of every bounded device-side wait (mbarrier, peer flag, stream-K flag).
+// One definition for the whole library (elementwise.cu); ps_set_wait_budget() changes it, launchers pass
+// the current value to their kernels.  The default is about one second at B200 clocks.
+extern long long g_ps_wait_budget_cycles;
+
 // Launch helpers return the CUDA error code as int (0 = cudaSuccess).
 #define PS_LAUNCH_CHECK() (int)cudaGetLastError()
 

@@ -22,7 +22,6 @@
 namespace ps {
 
 constexpr int kArMaxRanks = 8;
-constexpr long long kArWaitCycles = 2000000000LL;     // ~1 s
 
 struct ArArgs {
     int size, rank;
@@ -39,7 +38,7 @@ struct ArArgs {
 };
 
 // Signal every peer and wait for every peer at (phase, this CTA).  Returns false on timeout.
-__device__ __forceinline__ bool ar_barrier(const ArArgs& a, int phase, uint32_t val, bool* s_fail) {
+__device__ __forceinline__ bool ar_barrier(const ArArgs& a, int phase, uint32_t val, bool* s_fail, long long budget) {
     __syncthreads();
     if (threadIdx.x < a.size) {
         __threadfence_system();
@@ -52,7 +51,7 @@ __device__ __forceinline__ bool ar_barrier(const ArArgs& a, int phase, uint32_t 
         do {
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
             if ((int32_t)(seen - val) >= 0) break;
-            if (clock64() - t0 > kArWaitCycles) { *s_fail = true; break; }
+            if (clock64() - t0 > budget) { *s_fail = true; break; }
         } while (true);
     }
     __syncthreads();
@@ -84,13 +83,13 @@ __device__ __forceinline__ void finish_chunk(const ArArgs& a, long long chunk, f
                    f32x2_to_bf16x2_bits(acc[4], acc[5]), f32x2_to_bf16x2_bits(acc[6], acc[7]));
 }
 
-__global__ void __launch_bounds__(256) allreduce_peer_kernel(const ArArgs a) {
+__global__ void __launch_bounds__(256) allreduce_peer_kernel(const ArArgs a, const long long budget) {
     __shared__ bool s_fail;
     __shared__ uint32_t s_val;
     if (threadIdx.x == 0) { s_fail = false; s_val = a.counter[blockIdx.x] + 1u; }
     __syncthreads();
     const uint32_t val = s_val;
-    if (!ar_barrier(a, 0, val, &s_fail)) { if (threadIdx.x == 0) set_status(a.status, PS_DEV_WAIT_TIMEOUT); return; }
+    if (!ar_barrier(a, 0, val, &s_fail, budget)) { if (threadIdx.x == 0) set_status(a.status, PS_DEV_WAIT_TIMEOUT); return; }
     if (threadIdx.x == 0) a.counter[blockIdx.x] = val;
     const long long chunks = (long long)a.rows * (a.n >> 3);
     for (long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x; c < chunks; c += (long long)gridDim.x * blockDim.x) {
@@ -100,13 +99,13 @@ __global__ void __launch_bounds__(256) allreduce_peer_kernel(const ArArgs a) {
     }
 }
 
-__global__ void __launch_bounds__(256) allreduce_multimem_kernel(const ArArgs a) {
+__global__ void __launch_bounds__(256) allreduce_multimem_kernel(const ArArgs a, const long long budget) {
     __shared__ bool s_fail;
     __shared__ uint32_t s_val;
     if (threadIdx.x == 0) { s_fail = false; s_val = a.counter[blockIdx.x] + 1u; }
     __syncthreads();
     const uint32_t val = s_val;
-    if (!ar_barrier(a, 0, val, &s_fail)) { if (threadIdx.x == 0) set_status(a.status, PS_DEV_WAIT_TIMEOUT); return; }
+    if (!ar_barrier(a, 0, val, &s_fail, budget)) { if (threadIdx.x == 0) set_status(a.status, PS_DEV_WAIT_TIMEOUT); return; }
     const long long chunks = (long long)a.rows * (a.n >> 3);
     const long long stride = (long long)gridDim.x * blockDim.x;
     // shot 1: reduce my share through the switch and broadcast it into every rank's result buffer
@@ -118,7 +117,7 @@ __global__ void __launch_bounds__(256) allreduce_multimem_kernel(const ArArgs a)
         asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};"
                      ::"l"(reinterpret_cast<uint4*>(a.mc_res) + c), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
     }
-    if (!ar_barrier(a, 1, val, &s_fail)) { if (threadIdx.x == 0) set_status(a.status, PS_DEV_WAIT_TIMEOUT); return; }
+    if (!ar_barrier(a, 1, val, &s_fail, budget)) { if (threadIdx.x == 0) set_status(a.status, PS_DEV_WAIT_TIMEOUT); return; }
     if (threadIdx.x == 0) a.counter[blockIdx.x] = val;
     // shot 2: the CTA with the same index on rank (c % size) produced chunk c; read the local copy
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i * a.size < chunks; i += stride) {
@@ -142,9 +141,9 @@ PS_API int ps_allreduce(const void* args, int use_multimem, int grid, cudaStream
     if (a.size < 1 || a.size > kArMaxRanks || a.rows <= 0 || (a.n & 7) || grid < 1) return (int)cudaErrorInvalidValue;
     if (use_multimem) {
         if (a.mc_in == nullptr || a.mc_res == nullptr || a.res_local == nullptr) return (int)cudaErrorInvalidValue;
-        allreduce_multimem_kernel<<<grid, 256, 0, stream>>>(a);
+        allreduce_multimem_kernel<<<grid, 256, 0, stream>>>(a, g_ps_wait_budget_cycles);
     } else {
-        allreduce_peer_kernel<<<grid, 256, 0, stream>>>(a);
+        allreduce_peer_kernel<<<grid, 256, 0, stream>>>(a, g_ps_wait_budget_cycles);
     }
     return PS_LAUNCH_CHECK();
 }

@@ -8,28 +8,51 @@
 namespace ps {
 
 // out[r, :] = table[ids[r], :]; an id outside [0, vocab) writes zeros and flags the status word.
+// `ssq` (optional): ssq[r * ssq_ld] receives the row's sum of squares, which lets the first projection's fused
+// RMSNorm skip its own sweep over the row (see gemm_bs.cu).
 __global__ void embedding_kernel(const int* ids, const __nv_bfloat16* table, int vocab, int H,
-                                 __nv_bfloat16* out, int ldo, uint32_t* status) {
+                                 __nv_bfloat16* out, int ldo, uint32_t* status, float* ssq, int ssq_ld) {
+    __shared__ float red[32];
     const int r = blockIdx.x;
     const int id = ids[r];
     const bool ok = id >= 0 && id < vocab;
     if (!ok && threadIdx.x == 0) set_status(status, PS_DEV_BAD_INDEX);
     const uint4* src = reinterpret_cast<const uint4*>(table + (size_t)(ok ? id : 0) * H);
     uint4* dst = reinterpret_cast<uint4*>(out + (size_t)r * ldo);
-    for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = ok ? __ldg(src + i) : make_uint4(0, 0, 0, 0);
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H / 8; i += blockDim.x) {
+        const uint4 v = ok ? __ldg(src + i) : make_uint4(0, 0, 0, 0);
+        dst[i] = v;
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { const float2 a = bf16x2_bits_to_f32x2(w[e]); ss += a.x * a.x + a.y * a.y; }
+    }
+    if (ssq != nullptr) {
+        ss = block_sum(ss, red);
+        if (threadIdx.x == 0) ssq[(size_t)r * ssq_ld] = ss;
+    }
 }
 
 // MXFP8 table (E4M3 codes + UE8M0 scale per 32): dequantising gather.
 __global__ void embedding_mxfp8_kernel(const int* ids, const uint8_t* codes, const uint8_t* scales, int vocab,
-                                       int H, __nv_bfloat16* out, int ldo, uint32_t* status) {
+                                       int H, __nv_bfloat16* out, int ldo, uint32_t* status, float* ssq, int ssq_ld) {
+    __shared__ float red[32];
     const int r = blockIdx.x;
     const int id = ids[r];
     const bool ok = id >= 0 && id < vocab;
     if (!ok && threadIdx.x == 0) set_status(status, PS_DEV_BAD_INDEX);
+    float ss = 0.f;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         float v = 0.f;
         if (ok) v = e4m3_to_f32(codes[(size_t)id * H + i]) * __uint_as_float((uint32_t)scales[(size_t)id * (H / 32) + i / 32] << 23);
-        out[(size_t)r * ldo + i] = f32_to_bf16(v);
+        const __nv_bfloat16 o = f32_to_bf16(v);
+        out[(size_t)r * ldo + i] = o;
+        const float of = bf16_to_f32(o);
+        ss += of * of;
+    }
+    if (ssq != nullptr) {
+        ss = block_sum(ss, red);
+        if (threadIdx.x == 0) ssq[(size_t)r * ssq_ld] = ss;
     }
 }
 
@@ -91,19 +114,19 @@ __global__ void gather_rows_kernel(const uint8_t* src, size_t src_pitch, const i
 }  // namespace ps
 
 PS_API int ps_embedding(const void* ids, const void* table, int rows, int vocab, int H, void* out, int ldo,
-                        void* status, cudaStream_t stream) {
+                        void* status, void* ssq, int ssq_ld, cudaStream_t stream) {
     if (rows <= 0 || (H % 8)) return (int)cudaErrorInvalidValue;
     ps::embedding_kernel<<<rows, 256, 0, stream>>>((const int*)ids, (const __nv_bfloat16*)table, vocab, H,
-                                                   (__nv_bfloat16*)out, ldo, (uint32_t*)status);
+                                                   (__nv_bfloat16*)out, ldo, (uint32_t*)status, (float*)ssq, ssq_ld);
     return PS_LAUNCH_CHECK();
 }
 
 PS_API int ps_embedding_mxfp8(const void* ids, const void* codes, const void* scales, int rows, int vocab, int H,
-                              void* out, int ldo, void* status, cudaStream_t stream) {
+                              void* out, int ldo, void* status, void* ssq, int ssq_ld, cudaStream_t stream) {
     if (rows <= 0 || (H % 32)) return (int)cudaErrorInvalidValue;
     ps::embedding_mxfp8_kernel<<<rows, 256, 0, stream>>>((const int*)ids, (const uint8_t*)codes,
                                                          (const uint8_t*)scales, vocab, H, (__nv_bfloat16*)out, ldo,
-                                                         (uint32_t*)status);
+                                                         (uint32_t*)status, (float*)ssq, ssq_ld);
     return PS_LAUNCH_CHECK();
 }
 
@@ -144,4 +167,16 @@ PS_API int ps_gather_rows(const void* src, long long src_pitch, const void* rows
                                                   (uint8_t*)dst, (size_t)dst_pitch, row_bytes, n_src_rows,
                                                   (uint32_t*)status);
     return PS_LAUNCH_CHECK();
+}
+
+// ---- library-wide budget of bounded device-side waits (declared in ps_common.cuh)
+long long g_ps_wait_budget_cycles = 2000000000ll;
+
+// Set the budget (GPU clock cycles) that launchers hand to kernels with bounded waits.  Values below 1000
+// are clamped.  Returns the previous value.  Tests use a small budget to make a wait run out on purpose;
+// deployments with slow peers may raise it.
+PS_API long long ps_set_wait_budget(long long cycles) {
+    const long long prev = g_ps_wait_budget_cycles;
+    g_ps_wait_budget_cycles = cycles < 1000 ? 1000 : cycles;
+    return prev;
 }

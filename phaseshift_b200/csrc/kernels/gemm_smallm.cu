@@ -26,6 +26,7 @@ struct SmallMArgs {
     int splits;
     float* partial;         // [splits, M, N] fp32
     uint32_t* status;
+    long long budget;       // clock-cycle budget of every mbarrier wait
 };
 
 template <int STAGES>
@@ -75,7 +76,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             for (int it = 0; it < k_iters; ++it) {
                 const int s = it % STAGES;
                 const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
-                if (it >= STAGES && !tc::mbar_wait(&empty_bar[s], ph ^ 1u)) { atomicExch(&s_abort, 1); break; }
+                if (it >= STAGES && !tc::mbar_wait(&empty_bar[s], ph ^ 1u, g.budget)) { atomicExch(&s_abort, 1); break; }
                 tc::mbar_expect_tx(&full_bar[s], kWBytes + x_bytes);
                 tc::tma_load_2d(sW + s * kWBytes, &map_w, (it0 + it) * kSmBK, tile_n * kSmBM, &full_bar[s]);
                 tc::tma_load_2d(sX + s * kXStride, &map_x, (it0 + it) * kSmBK, 0, &full_bar[s]);
@@ -88,7 +89,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             for (int it = 0; it < k_iters && ok; ++it) {
                 const int s = it % STAGES;
                 const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
-                if (!tc::mbar_wait(&full_bar[s], ph)) { atomicExch(&s_abort, 1); ok = false; break; }
+                if (!tc::mbar_wait(&full_bar[s], ph, g.budget)) { atomicExch(&s_abort, 1); ok = false; break; }
                 tc::fence_after_sync();
                 const uint32_t w_addr = tc::smem_u32(sW + s * kWBytes), x_addr = tc::smem_u32(sX + s * kXStride);
 #pragma unroll
@@ -102,7 +103,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     } else {
         // epilogue warps 2..5 -> TMEM lane quadrant (warp % 4); lane = weight row, column = batch row
         const int quad = warp & 3;
-        const bool done = k_iters > 0 ? tc::mbar_wait(&acc_bar, 0) : true;
+        const bool done = k_iters > 0 ? tc::mbar_wait(&acc_bar, 0, g.budget) : true;
         tc::fence_after_sync();
         const int n = tile_n * kSmBM + quad * 32 + lane;
         if (done && s_abort == 0) {
@@ -223,7 +224,7 @@ PS_API int ps_gemm_smallm(const void* a, int lda, const void* w, int ldw, int M,
     g.splits = ps_gemm_smallm_splits(N, K);
     const int iters = (K + kSmBK - 1) / kSmBK;
     g.iters_per_split = (iters + g.splits - 1) / g.splits;
-    g.partial = (float*)partial; g.status = (uint32_t*)status;
+    g.partial = (float*)partial; g.status = (uint32_t*)status; g.budget = g_ps_wait_budget_cycles;
     CUtensorMap map_w, map_x;
     int err = sm_map_2d(&map_w, w, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, kSmBM);
     if (err) return err;

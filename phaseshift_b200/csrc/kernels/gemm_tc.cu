@@ -32,6 +32,7 @@ struct GemmArgs {
     const __nv_bfloat16* residual; int ld_res;
     void* out; int ldo; int out_f32;
     uint32_t* status;
+    long long budget;    // clock-cycle budget of every mbarrier wait
     int a_box_rows;      // rows fetched per A tile (a multiple of 8, <= 128); the rest of the tile stays zero
 };
 
@@ -93,7 +94,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             for (int it = 0; it < k_iters; ++it) {
                 const int s = it % kGemmStages;
                 const uint32_t ph = (uint32_t)(it / kGemmStages) & 1u;
-                if (it >= kGemmStages && !tc::mbar_wait(&empty_bar[s], ph ^ 1u)) { atomicExch(&s_abort, 1); break; }
+                if (it >= kGemmStages && !tc::mbar_wait(&empty_bar[s], ph ^ 1u, g.budget)) { atomicExch(&s_abort, 1); break; }
                 tc::mbar_expect_tx(&full_bar[s], a_bytes + kBBytes);
                 tc::tma_load_2d(sA + s * kABytes, &map_a, it * kBK, tile_m * kBM, &full_bar[s]);
                 tc::tma_load_2d(sB + s * kBBytes, &map_w, it * kBK, tile_n * BN, &full_bar[s]);
@@ -107,7 +108,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             for (int it = 0; it < k_iters && ok; ++it) {
                 const int s = it % kGemmStages;
                 const uint32_t ph = (uint32_t)(it / kGemmStages) & 1u;
-                if (!tc::mbar_wait(&full_bar[s], ph)) { atomicExch(&s_abort, 1); ok = false; break; }
+                if (!tc::mbar_wait(&full_bar[s], ph, g.budget)) { atomicExch(&s_abort, 1); ok = false; break; }
                 tc::fence_after_sync();
                 const uint32_t a_addr = tc::smem_u32(sA + s * kABytes), b_addr = tc::smem_u32(sB + s * kBBytes);
 #pragma unroll
@@ -124,7 +125,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else {
         // ------------------------------------------------ epilogue: warps 2..5 -> TMEM lane quadrant (warp % 4)
         const int quad = warp & 3;
-        const bool done = tc::mbar_wait(&acc_bar, 0);
+        const bool done = tc::mbar_wait(&acc_bar, 0, g.budget);
         tc::fence_after_sync();
         const int row = tile_m * kBM + quad * 32 + lane;
         if (done && s_abort == 0) {
@@ -246,6 +247,7 @@ PS_API int ps_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, int M
     GemmArgs g;
     g.M = M; g.N = N; g.K = K; g.epilogue = epilogue; g.residual = (const __nv_bfloat16*)residual; g.ld_res = ld_res;
     g.out = out; g.ldo = ldo; g.out_f32 = out_f32; g.status = (uint32_t*)status;
+    g.budget = g_ps_wait_budget_cycles;
     g.a_box_rows = M >= kBM ? kBM : ((M + 7) / 8) * 8;
     if (M <= kBM && N >= 512) return launch_gemm<32, 5, 2>(a, lda, w, ldw, g, stream);
     if (N >= 256) return launch_gemm<256, 4, 1>(a, lda, w, ldw, g, stream);

@@ -29,7 +29,7 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint3
 
 template <int WF, int MT>
 __global__ void __launch_bounds__(kStThreads, 1) linear_stream_kernel(const LinearSmallArgs a, uint32_t* status,
-                                                                       const int n_slots) {
+                                                                       const int n_slots, const long long budget) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     using XS = typename WTraits<WF>::XS;
     using RD = RowDot<WF>;
@@ -116,7 +116,7 @@ __global__ void __launch_bounds__(kStThreads, 1) linear_stream_kernel(const Line
         for (int u = u0; u < u_end; ++u) {
             const int slot = consumed % n_slots;
             // warp-uniform outcome: either every lane saw the copy land or the whole warp gives up
-            if (!__all_sync(0xffffffffu, tc::mbar_wait(&s_bar[warp][slot], (uint32_t)(consumed / n_slots) & 1u))) { timed_out = true; break; }
+            if (!__all_sync(0xffffffffu, tc::mbar_wait(&s_bar[warp][slot], (uint32_t)(consumed / n_slots) & 1u, budget))) { timed_out = true; break; }
             const unsigned char* blk = my_ring + (size_t)slot * kSlot;
             const int k = st * 32 * CH + lane * (16 / (int)sizeof(XS));      // lane's first 16-byte group of the step
             uint4 w[R]; uint32_t sb[R];
@@ -205,7 +205,7 @@ __global__ void __launch_bounds__(kStThreads, 1) linear_stream_kernel(const Line
                 do {
                     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
                     if ((int32_t)(seen - val) >= 0) break;
-                    if (clock64() - t0 > tc::kWaitBudgetCycles) { timed_out = true; break; }
+                    if (clock64() - t0 > budget) { timed_out = true; break; }
                 } while (true);
             }
             __syncthreads();
@@ -230,7 +230,7 @@ __global__ void __launch_bounds__(kStThreads, 1) linear_stream_kernel(const Line
         // A copy never completed.  Report it and give copies still in flight a bounded chance to land
         // before the CTA (and its shared memory) goes away.
         set_status(status, PS_DEV_WAIT_TIMEOUT);
-        for (int c = consumed; c < issued; ++c) tc::mbar_wait(&s_bar[warp][c % n_slots], (uint32_t)(c / n_slots) & 1u);
+        for (int c = consumed; c < issued; ++c) tc::mbar_wait(&s_bar[warp][c % n_slots], (uint32_t)(c / n_slots) & 1u, budget);
     }
 }
 
@@ -259,7 +259,7 @@ static int launch_stream(const LinearSmallArgs& a, uint32_t* status, cudaStream_
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = g_st_pdl ? 1 : 0;
-    return (int)cudaLaunchKernelEx(&cfg, linear_stream_kernel<WF, MT>, a, status, slots);
+    return (int)cudaLaunchKernelEx(&cfg, linear_stream_kernel<WF, MT>, a, status, slots, g_ps_wait_budget_cycles);
 }
 
 template <int WF>

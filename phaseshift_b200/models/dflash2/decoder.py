@@ -53,6 +53,9 @@ class DFlash2SpecDecoder:
         self.ngram_tail, self.ngram_n = ngram_tail, ngram_n
         self.rt = runtime()
         self.verify_exact = True       # Exact numeric mode: every verified row uses single-row-decode arithmetic
+        # verification rows and plain single-row steps must run the same projection arithmetic
+        if hasattr(engine, "set_uniform_arithmetic"):
+            engine.set_uniform_arithmetic(True)
         if hasattr(engine.ops, "topk"):
             drafter.topk_fn = engine.ops.topk              # exact radix top-k kernel for the candidate sets
         if hasattr(drafter, "bind"):
@@ -113,7 +116,7 @@ class DFlash2SpecDecoder:
         k = max(0, min(self.k, remaining - 1, room - 1))
         pos0 = s.position
         if k == 0:
-            toks, out = eng.step([SeqRows(s.slot, pos0, [anchor], (0,), sample_index=len(generated), **samp)], [s],
+            toks, out = eng.step([SeqRows(s.slot, pos0, [anchor], (0,), sample_index=len(generated) + 1, **samp)], [s],
                                  tap_layers=self.taps)
             self._append_taps(out, 1, pos0, [anchor])
             self.stats["plain_steps"] += 1
@@ -124,7 +127,7 @@ class DFlash2SpecDecoder:
                                                  min(self.ngram_tail, max(0, remaining - 1 - len(drafts))))
         rows = [anchor] + drafts
         n = len(rows)
-        toks, out = eng.step([SeqRows(s.slot, pos0, rows, tuple(range(n)), sample_index=len(generated), **samp)], [s],
+        toks, out = eng.step([SeqRows(s.slot, pos0, rows, tuple(range(n)), sample_index=len(generated) + 1, **samp)], [s],
                              commit=False, tap_layers=self.taps, gdn_log=self.logs, gdn_to_alt=True, exact=self.verify_exact)
         accepted, nxt, full = self.rt.spec_greedy_accept(drafts, toks)
         keep = accepted + 1                                  # anchor + accepted drafts are now part of the sequence

@@ -37,35 +37,62 @@ class Qwen35Runner:
         self.hk, self.hv = len(geo.gdn_k_heads), len(geo.gdn_v_heads)
         # optional callable(tag, activations[rows, K]): importance-matrix collection at projection inputs
         self.imatrix_collector = None
+        # optional callable(tag, values[rows, K]): what the tensor-core projections quantise at each input site,
+        # i.e. x (1 + norm weight) before the row factor 1/rms (activation-scale calibration)
+        self.act_collector = None
+        self.use_ssq = hasattr(ops, "ssq_buf")
 
     def _tap(self, tag: str, x: torch.Tensor, n_rows: int, norm_w=None) -> None:
+        if self.act_collector is not None:
+            v = x[:n_rows].float()
+            self.act_collector(tag, v * (1.0 + norm_w.float()) if norm_w is not None else v)
         if self.imatrix_collector is None:
             return
         if norm_w is not None:
             x = self.ops.rmsnorm(x, norm_w, self.cfg.rms_norm_eps, "imatrix_norm")
         self.imatrix_collector(tag, x[:n_rows])
 
-    def _row_parallel(self, inp: torch.Tensor, W, residual: torch.Tensor, name: str, rows: int) -> torch.Tensor:
+    def _first_proj(self, li: int):
+        """The first projection of layer `li` (the lm_head after the last layer): what runs after layer li-1's down."""
+        if li >= len(self.w.layers):
+            return self.w.lm_head
+        L = self.w.layers[li]
+        return L.mixer.in_proj if L.kind == 0 else L.mixer.qkv_proj
+
+    def _row_parallel(self, inp: torch.Tensor, W, residual: torch.Tensor, name: str, rows: int, nxt=None):
         """Row-parallel projection + residual.  Single rank: residual fused in the projection epilogue.
-        Tensor parallel, <= 8 rows: the projection kernel also performs the cross-rank sum (fused
-        one-shot all-reduce over NVLink); otherwise the partial goes through the library all-reduce."""
+        Tensor parallel, few rows: the projection kernel also performs the cross-rank sum (fused one-shot
+        all-reduce over NVLink); otherwise the partial goes through the all-reduce kernel / library.
+        Returns (output, ssq): ssq = (tensor, n) partial sums of squares of the output rows when the kernel left
+        them for the next fused RMSNorm, else None."""
         ops, tp = self.ops, self.tp
+        ssq_out, ssq = None, None
+        if self.use_ssq and rows <= 32 and getattr(W, "sf_atoms", None) is not None:
+            ssq_out = ops.ssq_buf(name, rows)
+            ssq = (ssq_out, -(-W.N // 128))
+        kw = {"prefetch": nxt} if self.use_ssq else {}
         if tp is None or tp.size <= 1:
-            return ops.linear(inp, W, name=name, residual=residual)
-        comb = tp.combine_for(W.N) if (rows <= 8 and hasattr(ops, "buf")) else None
+            return ops.linear(inp, W, name=name, residual=residual, ssq_out=ssq_out, **kw), ssq
+        comb = tp.combine_for(W.N) if (rows <= tp.max_fused_rows(W) and hasattr(ops, "buf")) else None
         if comb is not None:
             tp.stats["fused"] += 1
-            return ops.linear(inp, W, name=name, residual=residual, tp_combine=comb)
+            return ops.linear(inp, W, name=name, residual=residual, tp_combine=comb, ssq_out=ssq_out, **kw), ssq
         part = ops.linear(inp, W, name="tp_partial")
         out = ops.buf(name, rows, W.N) if hasattr(ops, "buf") else torch.empty_like(part)
-        return tp.all_reduce_residual(part, residual, out)
+        return tp.all_reduce_residual(part, residual, out), None
 
     def forward(self, b: StepBatch, rows: int, n_out: int, *, tap_layers: Sequence[int] = (),
                 gdn_log: Optional[Dict[int, tuple]] = None, gdn_to_alt: bool = False,
                 mask=None, mask_active=None, sample: bool = True) -> StepOutput:
         cfg, ops, st, w = self.cfg, self.ops, self.state, self.w
         eps = cfg.rms_norm_eps
-        x = ops.embed(b, rows, w.embed, st.status)
+        x_ssq = None
+        if self.use_ssq and rows <= 32:
+            e_ssq = ops.ssq_buf("embed", rows)
+            x = ops.embed(b, rows, w.embed, st.status, ssq_out=e_ssq)
+            x_ssq = (e_ssq, 1)
+        else:
+            x = ops.embed(b, rows, w.embed, st.status)
         taps = {}
         from .weights import P as _P
         for li, L in enumerate(w.layers):
@@ -82,10 +109,11 @@ class Qwen35Runner:
                         # normalised row that in_proj leaves behind -> one launch fewer per layer
                         xn = ops.buf("gdn_xn", rows, x.shape[1])
                         ops.linear(x, m.in_proj, name="gdn_in", norm_w=L.input_norm, eps=eps, out=proj[:, :n_main],
-                                   xn_out=xn)
+                                   xn_out=xn, ssq_in=x_ssq, prefetch=m.out_proj)
                     else:
                         xn = None
-                        ops.linear(x, m.in_proj, name="gdn_in", norm_w=L.input_norm, eps=eps, out=proj[:, :n_main])
+                        ops.linear(x, m.in_proj, name="gdn_in", norm_w=L.input_norm, eps=eps, out=proj[:, :n_main],
+                                   ssq_in=x_ssq, prefetch=m.out_proj)
                         ops.linear(x, m.ba_proj, name="gdn_ba", norm_w=L.input_norm, eps=eps, out=proj[:, n_main:])
                     o = ops.gdn(proj, m, self.hk, self.hv, b, st.gdn[li], st,
                                 log=None if gdn_log is None else gdn_log[li], to_alt=gdn_to_alt, xn=xn)
@@ -95,27 +123,33 @@ class Qwen35Runner:
                     o = ops.gdn(proj, m, self.hk, self.hv, b, st.gdn[li], st,
                                 log=None if gdn_log is None else gdn_log[li], to_alt=gdn_to_alt)
                 self._tap(lp + "linear_attn.out_proj.weight", o, b.n_rows)
-                r = self._row_parallel(o, m.out_proj, x, "r", rows)
+                r, r_ssq = self._row_parallel(o, m.out_proj, x, "r", rows, L.gate_up)
             else:
                 self._tap(lp + "self_attn.q_proj.weight", x, b.n_rows, L.input_norm)
-                qkv = ops.linear(x, m.qkv_proj, name="attn_qkv", norm_w=L.input_norm, eps=eps)
+                qkv = ops.linear(x, m.qkv_proj, name="attn_qkv", norm_w=L.input_norm, eps=eps,
+                                 **({"ssq_in": x_ssq, "prefetch": m.o_proj} if self.use_ssq else {}))
                 q = ops.attn_prep(qkv, m, self.hq, self.hkv, b, st.kv[li], st)
                 ctx = ops.paged_attention(q, qkv, self.hq, self.hkv, b, st.kv[li], st, b.max_visible_launch)
                 self._tap(lp + "self_attn.o_proj.weight", ctx, b.n_rows)
-                r = self._row_parallel(ctx, m.o_proj, x, "r", rows)
+                r, r_ssq = self._row_parallel(ctx, m.o_proj, x, "r", rows, L.gate_up)
             self._tap(lp + "mlp.gate_proj.weight", r, b.n_rows, L.post_norm)
-            act = ops.linear(r, L.gate_up, name="mlp_act", norm_w=L.post_norm, eps=eps, swiglu=True)
+            act = ops.linear(r, L.gate_up, name="mlp_act", norm_w=L.post_norm, eps=eps, swiglu=True,
+                             **({"ssq_in": r_ssq, "prefetch": L.down} if self.use_ssq else {}))
             self._tap(lp + "mlp.down_proj.weight", act, b.n_rows)
             # ping-pong the residual stream so a layer never writes the buffer it still reads
             xname = "x_a" if (li & 1) == 0 else "x_b"
-            x = self._row_parallel(act, L.down, r, xname, rows)
+            x, x_ssq = self._row_parallel(act, L.down, r, xname, rows, self._first_proj(li + 1))
             if li in tap_layers:
                 taps[li] = x if not hasattr(ops, "buf") else ops.buf(f"tap{li}", rows, x.shape[1]).copy_(x)
         tokens = logits = hidden = None
         if n_out > 0:
-            hidden = ops.gather_rows(x, b.out_rows, n_out, "out_hidden", st.status)
+            if b.identity_out and self.use_ssq:
+                hidden, h_ssq = x[:n_out], x_ssq          # pure decode batch: no gather, and the row statistics carry over
+            else:
+                hidden, h_ssq = ops.gather_rows(x, b.out_rows, n_out, "out_hidden", st.status), None
             self._tap(_P + "lm_head.weight", hidden, n_out, w.final_norm)
-            logits = ops.linear(hidden, w.lm_head, name="logits", norm_w=w.final_norm, eps=eps, out_f32=True)
+            logits = ops.linear(hidden, w.lm_head, name="logits", norm_w=w.final_norm, eps=eps, out_f32=True,
+                                **({"ssq_in": h_ssq} if self.use_ssq else {}))
             if sample:
                 tokens = ops.sample(logits, b, n_out, mask=mask, mask_active=mask_active, status=st.status)
         return StepOutput(tokens, logits, hidden, taps)

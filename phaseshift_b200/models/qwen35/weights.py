@@ -108,9 +108,28 @@ class LinearW:
     _fmt: str = ""
     _tscale: float = 1.0
     shadow: Optional[torch.Tensor] = None      # optional resident bf16 expansion [N, k_padded] for batched steps
+    sf_atoms: Optional[torch.Tensor] = None    # block scales in the tensor-core layout (quant/act_quant.pack_sf_atoms)
+    codes: Optional[torch.Tensor] = None       # canonical code matrix kept for the tensor-core path (TMA reads it as is)
+    act_scale: float = 0.0                     # fixed NVFP4 activation scale of this projection's input site
 
     def __post_init__(self):
         self._shape, self._kpad, self._fmt, self._tscale = self.q.shape, self.q.k_padded, self.q.fmt, self.q.tensor_scale
+        if self.act_scale <= 0.0:
+            from ...quant.act_quant import DEFAULT_ACT_SCALE
+            self.act_scale = DEFAULT_ACT_SCALE
+
+    def make_umma(self, keep_canonical: bool = True) -> "LinearW":
+        """Prepare the block-scaled tensor-core operands: the code matrix stays canonical (row-major; the TMA
+        tile load swizzles it on the fly), the block scales are re-laid into 512-byte atoms once."""
+        if self._fmt not in ("nvfp4", "mxfp8"):
+            raise ValueError("only block-quantised projections have tensor-core operands")
+        if self.sf_atoms is None:
+            from ...quant.act_quant import pack_sf_atoms
+            self.codes = self.q.codes.contiguous()
+            self.sf_atoms = pack_sf_atoms(self.q.scales, self._fmt, self._kpad)
+        if not keep_canonical:
+            self.q = None
+        return self
 
     def make_tiled(self, keep_canonical: bool = True) -> "LinearW":
         from ...quant.tiling import tile_weight
@@ -159,14 +178,22 @@ class LinearW:
     @property
     def nbytes(self) -> int:
         if self.tiled is not None:
-            return self.tiled.numel()
+            return self.tiled.numel()          # also with both layouts resident: what a single-row step streams
+        if self.sf_atoms is not None:
+            # what a step streams: codes + one scale byte per block (atom padding is not read for real rows)
+            return self.codes.numel() * self.codes.element_size() + self.N * (self._kpad // (16 if self._fmt == "nvfp4" else 32))
         return self.q.nbytes
 
     def dense(self) -> torch.Tensor:
         """fp32 [N, K] (dequantised); cached, used by the CPU/reference ops."""
         if self._deq is None:
             q = self.q
-            if q is None:
+            if q is None and self.tiled is None and self.sf_atoms is not None:
+                from ...quant.act_quant import unpack_sf_atoms
+                nb = self._kpad // (16 if self._fmt == "nvfp4" else 32)
+                q = QuantizedTensor(self._fmt, self._shape, self._kpad, self.codes,
+                                    unpack_sf_atoms(self.sf_atoms, self._shape[0], nb), self._tscale)
+            elif q is None:
                 from ...quant.tiling import untile_weight
                 q = untile_weight(self.tiled, self._fmt, self._shape[0], self._kpad)
                 q.tensor_scale = self._tscale
@@ -214,6 +241,7 @@ class EngineWeights:
     tp_rank: int = 0
     tp_size: int = 1
     preset: str = "bf16"
+    layout: str = "canonical"
 
     def weight_bytes(self) -> int:
         n = self.embed.nbytes + self.lm_head.nbytes
@@ -410,12 +438,23 @@ class QuantizedSource:
 
 def build_engine_weights(cfg: Qwen35Config, get, preset: str = "bf16", device="cpu", tp_rank: int = 0,
                          tp_size: int = 1, importance: Optional[Callable[[str], Optional[torch.Tensor]]] = None,
-                         keep_canonical: bool = True) -> EngineWeights:
+                         keep_canonical: bool = True, layout: Optional[str] = None) -> EngineWeights:
     """Build the engine's fused, (optionally) quantised and tiled weights for one tensor-parallel rank.
 
     ``get`` is either a callable ``name -> full HF tensor`` (weights are quantised here per ``preset``) or
     a source object (``DenseSource`` / ``QuantizedSource``).  Work proceeds one layer at a time so a 27B
-    model never needs more than one layer of BF16 weights resident."""
+    model never needs more than one layer of BF16 weights resident.
+
+    ``layout`` picks the kernel-side form of block-quantised projections on a CUDA device: ``"tc"`` (default;
+    canonical codes + scale atoms for the block-scaled tensor-core kernel, activations quantised to the weights'
+    block format), ``"stream"`` (quad-tiled blocks for the CUDA-core streaming kernel, bf16 activations) or
+    ``"both"`` (either kernel can run: single-row decode streams, everything else uses the tensor cores; costs a
+    second copy of the block codes).
+    The ``PS_LINEAR_LAYOUT`` environment variable overrides the default."""
+    import os
+    layout = layout or os.environ.get("PS_LINEAR_LAYOUT", "tc")
+    if layout not in ("tc", "stream", "both"):
+        raise ValueError(f"unknown linear layout {layout!r}")
     src = get if hasattr(get, "linear") else DenseSource(get, preset, device, importance)
     geo = TpGeometry.make(cfg, tp_rank, tp_size)
     Dk, Dv, D = cfg.linear_key_head_dim, cfg.linear_value_head_dim, cfg.head_dim
@@ -425,7 +464,12 @@ def build_engine_weights(cfg: Qwen35Config, get, preset: str = "bf16", device="c
     def lin(parts, role: str, layer: int, interleave: bool = False) -> LinearW:
         lw = LinearW(src.linear(parts, role, layer, interleave))
         if on_cuda and role != "embed":
-            lw.make_tiled(keep_canonical or role == "gdn_small")   # the GDN kernel reads b/a rows row-major
+            if layout in ("tc", "both") and lw.fmt in ("nvfp4", "mxfp8"):
+                if layout == "both":
+                    lw.make_tiled(True)
+                lw.make_umma(keep_canonical)
+            else:
+                lw.make_tiled(keep_canonical or role == "gdn_small")   # the GDN kernel reads b/a rows row-major
         return lw
 
     def dev(t: torch.Tensor, dtype=torch.bfloat16) -> torch.Tensor:
@@ -465,10 +509,17 @@ def build_engine_weights(cfg: Qwen35Config, get, preset: str = "bf16", device="c
     if cfg.tie_word_embeddings:
         lm_head = LinearW(embed.q)
         if on_cuda:
-            lm_head.make_tiled(True)
+            if layout in ("tc", "both") and lm_head.fmt in ("nvfp4", "mxfp8"):
+                if layout == "both":
+                    lm_head.make_tiled(True)
+                lm_head.make_umma(True)
+            else:
+                lm_head.make_tiled(True)
     else:
         lm_head = lin([(P + "lm_head.weight", None, None)], "lm_head", 0)
-    return EngineWeights(cfg, embed, layers, dev(src.tensor(P + "norm.weight")), lm_head, tp_rank, tp_size, preset)
+    ew = EngineWeights(cfg, embed, layers, dev(src.tensor(P + "norm.weight")), lm_head, tp_rank, tp_size, preset)
+    ew.layout = layout if on_cuda else "canonical"
+    return ew
 
 
 # Tensors that are fused into one projection and must therefore share an NVFP4 per-tensor scale.
@@ -486,7 +537,8 @@ def scale_groups(cfg: Qwen35Config) -> List[List[str]]:
 
 
 def load_engine_weights(model_dir, device="cpu", preset: Optional[str] = None, tp_rank: int = 0, tp_size: int = 1,
-                        keep_canonical: bool = True, verify_weights: bool = False) -> EngineWeights:
+                        keep_canonical: bool = True, verify_weights: bool = False,
+                        layout: Optional[str] = None) -> EngineWeights:
     """Load a model directory: quantised (manifest present, auto-detected) or plain BF16 (quantised on the
     fly when ``preset`` asks for it)."""
     from ...io.model_dir import ShardCollection, is_quantized_dir
@@ -499,6 +551,7 @@ def load_engine_weights(model_dir, device="cpu", preset: Optional[str] = None, t
             from ...quant.offline import verify_crc
             verify_crc(col, man)
         src = QuantizedSource(col, man, device)
-        return build_engine_weights(cfg, src, man.preset, device, tp_rank, tp_size, keep_canonical=keep_canonical)
+        return build_engine_weights(cfg, src, man.preset, device, tp_rank, tp_size, keep_canonical=keep_canonical,
+                                    layout=layout)
     return build_engine_weights(cfg, lambda n: col.tensor(n), preset or "bf16", device, tp_rank, tp_size,
-                                keep_canonical=keep_canonical)
+                                keep_canonical=keep_canonical, layout=layout)

@@ -10,6 +10,7 @@ what lets a whole step be captured in a CUDA graph.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Dict, Optional, Tuple
 
 import numpy as np
@@ -54,6 +55,13 @@ class CudaOps:
         self.exact_rows = False     # verify steps: keep every projection on the batch-invariant small-M kernel
         self.wscratch = None
         self.status = torch.zeros(1, dtype=torch.int32, device=device)   # kernels' own bounded-wait status word
+        # block-scaled tensor-core projections: stream-K partials + flags (flags must read 0 between launches)
+        self.bs_ws: Optional[torch.Tensor] = None
+        self.bs_flags: Optional[torch.Tensor] = None
+        self.bs_grid_override = 0
+        self.force_tc = os.environ.get("PS_FORCE_TC", "0") == "1"   # single-row steps on the tensor-core kernel too
+        self.bs_prefetch = os.environ.get("PS_BS_PREFETCH", "1") != "0"
+        self._bs_plan_cache: Dict[tuple, bool] = {}
 
     # ------------------------------------------------------------------ workspace
     def buf(self, name: str, rows: int, cols: int, dtype=torch.bfloat16) -> torch.Tensor:
@@ -65,15 +73,21 @@ class CudaOps:
         return t
 
     # ------------------------------------------------------------------ ops
-    def embed(self, b: StepBatch, rows: int, table: LinearW, status) -> torch.Tensor:
+    SSQ_LD = 64          # partial sums of squares per row: one per 128-feature tile of the producing projection
+
+    def ssq_buf(self, name: str, rows: int) -> torch.Tensor:
+        return self.buf("ssq_" + name, rows, self.SSQ_LD, torch.float32)
+
+    def embed(self, b: StepBatch, rows: int, table: LinearW, status, ssq_out: Optional[torch.Tensor] = None) -> torch.Tensor:
         H = table.K
         out = self.buf("x_embed", rows, H)
+        ld = ssq_out.stride(0) if ssq_out is not None else 0
         if table.fmt == "bf16":
             _lib.call("ps_embedding", ptr(b.ids), ptr(table.q.codes), c_int(rows), c_int(table.N), c_int(H),
-                      ptr(out), c_int(H), ptr(status))
+                      ptr(out), c_int(H), ptr(status), ptr(ssq_out), c_int(ld))
         elif table.fmt == "mxfp8":
             _lib.call("ps_embedding_mxfp8", ptr(b.ids), ptr(table.q.codes), ptr(table.q.scales), c_int(rows),
-                      c_int(table.N), c_int(H), ptr(out), c_int(H), ptr(status))
+                      c_int(table.N), c_int(H), ptr(out), c_int(H), ptr(status), ptr(ssq_out), c_int(ld))
         else:
             raise ValueError("embedding table must be bf16 or mxfp8")
         self.launches += 1
@@ -82,21 +96,36 @@ class CudaOps:
     def linear(self, x: torch.Tensor, W: LinearW, *, name: str, norm_w: Optional[torch.Tensor] = None,
                eps: float = 0.0, residual: Optional[torch.Tensor] = None, swiglu: bool = False,
                out_f32: bool = False, out: Optional[torch.Tensor] = None,
-               xn_out: Optional[torch.Tensor] = None, tp_combine=None) -> torch.Tensor:
+               xn_out: Optional[torch.Tensor] = None, tp_combine=None, ssq_in=None,
+               ssq_out: Optional[torch.Tensor] = None, prefetch: Optional[LinearW] = None) -> torch.Tensor:
         """``tp_combine`` (a parallel.tp.TpCombineStruct): the projection is row-parallel and the kernel sums
-        the ranks' partial results over NVLink before the residual epilogue (rows <= 8 only)."""
+        the ranks' partial results over NVLink before the residual epilogue.
+        ``ssq_in`` = (tensor [rows, SSQ_LD] fp32, n): n partial sums of squares per row of ``x`` left by the kernel
+        that produced it, consumed by the fused RMSNorm; ``ssq_out``: receives the partial sums of the rows this
+        projection stores (block-scaled tensor-core path, <= 32 rows; ignored elsewhere).
+        ``prefetch``: the projection that will run next on the same rows; the tensor-core kernel warms L2 with the first
+        bytes of its weights while it drains."""
         M, K = x.shape
         assert K == W.K and x.dtype == torch.bfloat16 and x.stride(1) == 1, (x.shape, W.K, x.dtype)
         n_out = W.N // 2 if swiglu else W.N
         if out is None:
             out = self.buf(name, M, n_out, torch.float32 if out_f32 else torch.bfloat16)
         assert out.shape[0] == M and out.shape[1] == n_out and out.stride(1) == 1
+        if W.K % 32 and W.sf_atoms is None:
+            raise ValueError(f"K={W.K} must be a multiple of 32 for the streaming / bf16 tensor-core kernels")
+        sel = self.select_linear(W, M)
+        if sel == "tc":
+            # block-quantised codes straight into the tensor cores (any number of rows)
+            return self.linear_bs(x, W, name=name, norm_w=norm_w, eps=eps, residual=residual, swiglu=swiglu,
+                                  out_f32=out_f32, out=out, xn_out=xn_out, tp_combine=tp_combine, ssq_in=ssq_in,
+                                  ssq_out=ssq_out, prefetch=prefetch)
         if tp_combine is not None and M > SMALL_M_MAX:
             raise ValueError("the fused tensor-parallel combine handles at most 8 rows")
         # tensor-core GEMM: prefill-sized steps, and batched steps (>= 2 rows) when a resident bf16 expansion of
         # the weights exists (Fast mode only: Exact verification stays on the batch-invariant streaming kernel)
-        batched = M >= 2 and W.shadow is not None and tp_combine is None and xn_out is None
-        if (M > SMALL_M_MAX or batched) and self.use_tc_gemm and not self.exact_rows:
+        batched = (M >= 2 and W.shadow is not None and tp_combine is None and xn_out is None and self.use_tc_gemm
+                   and not self.exact_rows)
+        if sel == "gemm" or batched:
             return self.linear_large(x, W, name=name, norm_w=norm_w, eps=eps, residual=residual, swiglu=swiglu,
                                      out_f32=out_f32, out=out)
         pro = PRO_RMSNORM if norm_w is not None else PRO_NONE
@@ -158,6 +187,117 @@ class CudaOps:
         _lib.call("ps_gemm_bf16_tc", ptr(a), c_int(a.stride(0)), ptr(wd), c_int(kp), c_int(M), c_int(W.N), c_int(kp),
                   c_int(epi), ptr(residual), c_int(residual.stride(0) if residual is not None else 0), ptr(out),
                   c_int(out.stride(0)), c_int(1 if out_f32 else 0), ptr(self.status))
+        self.launches += 1
+        return out
+
+    # ------------------------------------------------------------------ kernel selection
+    def select_linear(self, W: LinearW, M: int) -> str:
+        """Which projection kernel serves `M` rows of `W` -- the job of the reference's linear selector
+        (src/phaseshift/models/qwen35/runtime/linear_selector.cpp:202-308), here a pure function of the weight's
+        resident layouts, the row count and two switches:
+
+        * ``"tc"``     block-scaled tcgen05 kernel (needs ``W.sf_atoms``): every multi-row step, and single-row steps
+                       when only that layout is resident or ``force_tc`` is set (speculative decoding: verification
+                       and plain steps must share one arithmetic);
+        * ``"stream"`` CUDA-core streaming kernel over ``W.tiled`` (bf16 activations): single rows, bf16 weights up to
+                       8 rows, and Exact verification of weights that have no tensor-core layout;
+        * ``"gemm"``   bf16 tcgen05 GEMM after a weight expansion: more than 8 rows of weights without ``sf_atoms``."""
+        if W.sf_atoms is not None:
+            if M > 1 or W.tiled is None or self.force_tc:
+                return "tc"
+            return "stream"
+        if M > SMALL_M_MAX and self.use_tc_gemm and not self.exact_rows:
+            return "gemm"
+        return "stream"
+
+    # ------------------------------------------------------------------ block-scaled tensor-core projection
+    BS_RESIDENT_MAX_ROWS = 32
+
+    def _bs_workspace(self):
+        if self.bs_ws is None:
+            L = _lib.lib()
+            L.ps_gemm_bs_workspace_bytes.restype = ctypes.c_longlong
+            L.ps_gemm_bs_flag_words.restype = ctypes.c_int
+            with torch.cuda.device(self.device):
+                nbytes, nflags = int(L.ps_gemm_bs_workspace_bytes()), int(L.ps_gemm_bs_flag_words())
+            self.bs_ws = torch.empty(nbytes // 4, dtype=torch.float32, device=self.device)
+            self.bs_flags = torch.zeros(nflags, dtype=torch.int32, device=self.device)
+        return self.bs_ws, self.bs_flags
+
+    def reset_after_error(self) -> None:
+        """A kernel gave up on a bounded wait: stream-K flags may be left raised; clear them."""
+        if self.bs_flags is not None:
+            self.bs_flags.zero_()
+        self.status.zero_()
+
+    def bs_resident_ok(self, W: LinearW, M: int) -> bool:
+        """Whether `M` rows of this projection fit the kernel's resident-activation path (pure host arithmetic)."""
+        if M > self.BS_RESIDENT_MAX_ROWS:
+            return False
+        key = (W.fmt, 16 if M <= 16 else 32, W.N, W.K)
+        ok = self._bs_plan_cache.get(key)
+        if ok is None:
+            out = (ctypes.c_int * 8)()
+            L = _lib.lib()
+            L.ps_gemm_bs_plan.restype = ctypes.c_int
+            with torch.cuda.device(self.device):
+                ok = bool(L.ps_gemm_bs_plan(c_int(WFMT[W.fmt]), c_int(M), c_int(W.N), c_int(W.K), c_int(1),
+                                            c_int(self.bs_grid_override), out))
+            self._bs_plan_cache[key] = ok
+        return ok
+
+    def act_quant(self, x: torch.Tensor, W: LinearW, norm_w, eps: float):
+        """Quantise `x` (after the optional fused RMSNorm) to the block format of `W` for the streamed path.
+        Returns (codes uint8 [M, panels * 128], scale atoms uint8, row scale fp32 [M] = 1/rms)."""
+        from ..quant.act_quant import ATOMS_PER_PANEL, PANEL_K
+        M, K = x.shape
+        P = -(-K // PANEL_K[W.fmt])
+        codes = self.buf(f"bs_xq{K}", M, P * 128, torch.uint8)
+        mblk = -(-M // 256) * 2
+        sf = self.buf(f"bs_xsf{K}_{W.fmt}", mblk, P * ATOMS_PER_PANEL[W.fmt] * 512, torch.uint8)
+        rs = self.buf("bs_xrs", M, 1, torch.float32)
+        _lib.call("ps_act_quant", c_int(WFMT[W.fmt]), ptr(x), c_int(x.stride(0)), c_int(M), c_int(K), ptr(norm_w),
+                  c_float(eps), c_float(W.act_scale), ptr(codes), ptr(sf), ptr(rs))
+        self.launches += 1
+        return codes, sf, rs
+
+    def linear_bs(self, x: torch.Tensor, W: LinearW, *, name: str, norm_w, eps, residual, swiglu, out_f32, out,
+                  xn_out=None, tp_combine=None, ssq_in=None, ssq_out=None, prefetch=None) -> torch.Tensor:
+        M, K = x.shape
+        if K % 8 or x.stride(0) % 8:
+            raise ValueError("block-scaled projections need K and the row pitch to be multiples of 8")
+        ws, flags = self._bs_workspace()
+        epi = EPI_SWIGLU if swiglu else (EPI_RESIDUAL if residual is not None else EPI_STORE)
+        resident = self.bs_resident_ok(W, M)
+        if tp_combine is not None and M > tp_combine.max_rows:
+            raise ValueError("the fused tensor-parallel combine is sized for %d rows" % tp_combine.max_rows)
+        codes = W.codes
+        if resident:
+            xq = sf = rs = None
+        else:
+            if xn_out is not None:
+                raise ValueError("xn_out is produced by the resident path only")
+            xq, sf, rs = self.act_quant(x, W, norm_w, eps)
+        ssq_t, ssq_n = ssq_in if (ssq_in is not None and resident and norm_w is not None) else (None, 0)
+        if M > 32 or swiglu:
+            ssq_out = None
+        nxt = prefetch if (prefetch is not None and prefetch.sf_atoms is not None and self.bs_prefetch) else None
+        err = _lib.lib().ps_gemm_bs
+        err.restype = ctypes.c_int
+        rc = err(c_int(WFMT[W.fmt]), ptr(codes), c_ll(codes.shape[1]), c_ll(codes.stride(0)), ptr(W.sf_atoms),
+                 c_float(W.tensor_scale), c_int(M), c_int(W.N), c_int(K), ptr(x if resident else None),
+                 c_int(x.stride(0)), ptr(norm_w if resident else None), c_float(eps), c_float(W.act_scale),
+                 ptr(xn_out), ptr(ssq_t), c_int(ssq_n), c_int(ssq_t.stride(0) if ssq_t is not None else 0),
+                 ptr(ssq_out), c_int(ssq_out.stride(0) if ssq_out is not None else 0), ptr(xq), ptr(sf), ptr(rs),
+                 c_int(epi), ptr(residual),
+                 c_int(residual.stride(0) if residual is not None else 0), ptr(out), c_int(out.stride(0)),
+                 c_int(1 if out_f32 else 0), ptr(ws), ptr(flags),
+                 ctypes.byref(tp_combine) if tp_combine is not None else ptr(None), ptr(self.status),
+                 c_int(self.bs_grid_override), c_int(WFMT[nxt.fmt] if nxt is not None else 0),
+                 ptr(nxt.codes if nxt is not None else None), c_ll(nxt.codes.shape[1] if nxt is not None else 0),
+                 c_ll(nxt.codes.stride(0) if nxt is not None else 0), ptr(nxt.sf_atoms if nxt is not None else None),
+                 c_int(nxt.N if nxt is not None else 0), c_int(nxt.K if nxt is not None else 0), _lib.stream())
+        _lib.check(rc, "ps_gemm_bs")
         self.launches += 1
         return out
 

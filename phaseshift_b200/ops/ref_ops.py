@@ -25,8 +25,12 @@ class RefOps:
     act_dtype = torch.float32
     name = "ref"
 
-    def __init__(self, cfg: Qwen35Config, device, **_):
+    def __init__(self, cfg: Qwen35Config, device, act_quant: bool = False, **_):
+        """``act_quant``: quantise the input of every block-quantised projection to the weights' block format
+        (quant/act_quant.py), the arithmetic of the CUDA tensor-core layout; off = bf16/fp32 activations, the
+        arithmetic of the streaming layout."""
         self.cfg, self.device = cfg, device
+        self.act_quant = act_quant
         half = cfg.rotary_dim // 2
         self.inv_freq = cfg.rope_theta ** (-torch.arange(half, dtype=torch.float64) * 2.0 / cfg.rotary_dim)
         self.launches = 0
@@ -35,15 +39,25 @@ class RefOps:
     def _dense(self, W: LinearW) -> torch.Tensor:
         return W.dense().to(self.device)
 
-    def embed(self, b: StepBatch, rows: int, table: LinearW, status) -> torch.Tensor:
+    def embed(self, b: StepBatch, rows: int, table: LinearW, status, ssq_out=None) -> torch.Tensor:
         return self._dense(table)[b.ids[:rows].long()]
 
     def linear(self, x, W: LinearW, *, name: str, norm_w=None, eps: float = 0.0, residual=None, swiglu=False,
-               out_f32=False, out=None):
+               out_f32=False, out=None, ssq_in=None, ssq_out=None, prefetch=None, **_):
         x = x.float()
-        if norm_w is not None:
-            x = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * (1.0 + norm_w.float())
-        y = x @ self._dense(W).T
+        if self.act_quant and W.fmt in ("nvfp4", "mxfp8"):
+            # the tensor-core layout's arithmetic: quantise x (1 + w), apply the row factor 1/rms after the product
+            from ..quant.act_quant import fake_quant
+            inv = torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) if norm_w is not None else None
+            if norm_w is not None:
+                x = x * (1.0 + norm_w.float())
+            y = fake_quant(x, W.fmt, W.act_scale) @ self._dense(W).T
+            if inv is not None:
+                y = y * inv
+        else:
+            if norm_w is not None:
+                x = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * (1.0 + norm_w.float())
+            y = x @ self._dense(W).T
         if swiglu:
             y = F.silu(y[:, 0::2]) * y[:, 1::2]
         if residual is not None:

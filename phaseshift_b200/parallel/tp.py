@@ -34,7 +34,7 @@ import torch
 import torch.distributed as dist
 
 MAX_RANKS = 8
-MAX_ROWS = 8
+MAX_ROWS = 32          # rows the fused combine's receive buffers are sized for
 GRID_MAX = 256
 
 
@@ -131,11 +131,19 @@ class TensorParallel:
         a.residual = residual.data_ptr() if residual is not None else None
         a.ld_res = residual.stride(0) if residual is not None else 0
         a.out, a.ldo = out.data_ptr(), out.stride(0)
-        a.status = st["status"].data_ptr()
+        # bounded-wait failures go to the engine's status word when one is attached (Engine sets `status_word`),
+        # so a timed-out all-reduce poisons the step like any other device failure
+        word = getattr(self, "status_word", None)
+        a.status = (word if word is not None else st["status"]).data_ptr()
         _lib.call("ps_allreduce", ctypes.byref(a), ctypes.c_int(1 if multimem else 0), ctypes.c_int(AR_GRID))
         st["parity"] ^= 1
         self.stats["peer_allreduce"] += 1
         return out
+
+    def max_fused_rows(self, W) -> int:
+        """Rows up to which a row-parallel projection over `W` combines inside its own kernel: 32 on the
+        block-scaled tensor-core path, 8 on the streaming kernel."""
+        return MAX_ROWS if getattr(W, "sf_atoms", None) is not None else 8
 
     def combine_for(self, n: int) -> Optional[TpCombineStruct]:
         """Fused-combine descriptor for projections with `n` output features (allocated on first use;

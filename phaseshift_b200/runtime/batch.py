@@ -59,6 +59,7 @@ class StepBatch:
         # graph_static: the step is replayed from a captured CUDA graph, so launch geometry must not
         # depend on this step's contents (attention covers max_context, GDN covers max_seqs descriptors)
         self.graph_static = False
+        self.identity_out = False
         self.max_context = 1
         o = 0
         self.ids = self.d_int[o:o + max_rows]; o += max_rows
@@ -98,6 +99,9 @@ class StepBatch:
             max_vis = max(max_vis, s.pos_start + n)
             r += n
         self.n_rows, self.n_seqs, self.n_out, self.max_visible = r, len(seqs), n_out, max_vis
+        # output row i is step row i for every i (a pure decode batch): the output gather is the identity
+        self.identity_out = n_out == r and bool(np.array_equal(a[3 * mr + 4 * ms:3 * mr + 4 * ms + n_out],
+                                                               np.arange(n_out, dtype=np.int32)))
         self.seqs = list(seqs)
 
     @property

@@ -69,7 +69,7 @@ class PageAllocator:
 
 class Engine:
     def __init__(self, weights: EngineWeights, device, state_cfg: StateConfig, backend: str = "auto", tp=None,
-                 use_graphs: bool = True, batch_shadow: bool = False):
+                 use_graphs: bool = True, batch_shadow: bool = False, calibrate: bool = True):
         """``batch_shadow``: keep a resident bf16 expansion of every projection (2 bytes per weight on top of the
         block-quantised copy) so steps with two or more rows run the tensor-core GEMM on it: a batched decode step
         then costs about one pass over the bf16 weights whatever the number of rows, instead of one pass over the
@@ -90,6 +90,8 @@ class Engine:
         self.state = ModelState(self.cfg, state_cfg, self.device, self.ops.act_dtype, geo)
         self.runner = Qwen35Runner(weights, self.state, self.ops, tp)
         self.tp = tp
+        if tp is not None and hasattr(self.ops, "status"):
+            tp.status_word = self.ops.status      # the transport's kernels report bounded-wait failures here
         self.shadow_bytes = weights.make_shadows() if (batch_shadow and backend == "cuda") else 0
         self.alloc = PageAllocator(self.state.num_pages, state_cfg.max_slots)
         self.seqs: Dict[int, Sequence_] = {}
@@ -102,8 +104,78 @@ class Engine:
             # the library all-reduce is not captured into CUDA graphs; only the in-kernel combine is
             self.use_graphs = False
         self.h_tokens = torch.zeros(2048, dtype=torch.int32, pin_memory=(self.device.type == "cuda"))
-        self.h_status = torch.zeros(1, dtype=torch.int32, pin_memory=(self.device.type == "cuda"))
+        self.h_status = torch.zeros(2, dtype=torch.int32, pin_memory=(self.device.type == "cuda"))
         self.steps = 0
+        self.act_scales_calibrated = False
+        if calibrate and backend == "cuda" and getattr(weights, "layout", "") in ("tc", "both"):
+            self.calibrate_act_scales()
+
+    def set_uniform_arithmetic(self, on: bool) -> None:
+        """Speculative decoding needs every step of a sequence -- single-row decode, multi-row verification, the
+        plain fallback rounds -- on one projection arithmetic, or verified tokens would not reproduce plain decoding
+        (the reference's Exact verify mode, include/phaseshift/runtime/execution/execution_types.h:6-27).  With both
+        weight layouts resident single-row steps normally stream with bf16 activations; this pins them to the
+        tensor-core kernel that multi-row steps use.  Captured graphs are dropped because they bake the choice in."""
+        if hasattr(self.ops, "force_tc") and self.ops.force_tc != on:
+            self.ops.force_tc = on
+            self.graphs.clear()
+            self.graph_out.clear()
+            self.launches_per_graph.clear()
+
+    # ------------------------------------------------------------------ activation scales (tensor-core layout)
+    def calibrate_act_scales(self, token_ids: Optional[Sequence[int]] = None, n_tokens: int = 64) -> Dict[str, float]:
+        """Fix the NVFP4 activation scale of every projection input site from one forward over `token_ids`
+        (default: `n_tokens` pseudo-random ids): the largest |x| seen at the site maps to a block scale of 32, which
+        leaves 14x of headroom before the UE4M3 block scale saturates and 11 binades below it at full precision.
+        The reference's activation quantiser scales each row by its own maximum
+        (src/phaseshift/models/qwen35/kernels/optimized/activation_quantize.hip:65-120); a fixed scale lets the
+        projection kernel quantise K-panels independently inside its prologue.  Every rank calibrates its own slice."""
+        from ..quant.act_quant import calibrate_act_scale
+        from ..models.qwen35.weights import P as _P
+        w = self.runner.w
+        sites: Dict[str, object] = {_P + "lm_head.weight": w.lm_head}
+        for li, L in enumerate(w.layers):
+            lp = f"{_P}layers.{li}."
+            m = L.mixer
+            if L.kind == 0:
+                sites[lp + "linear_attn.in_proj_qkv.weight"] = m.in_proj
+                sites[lp + "linear_attn.out_proj.weight"] = m.out_proj
+            else:
+                sites[lp + "self_attn.q_proj.weight"] = m.qkv_proj
+                sites[lp + "self_attn.o_proj.weight"] = m.o_proj
+            sites[lp + "mlp.gate_proj.weight"] = L.gate_up
+            sites[lp + "mlp.down_proj.weight"] = L.down
+        if token_ids is None:
+            g = torch.Generator().manual_seed(20240229)
+            n = max(1, min(n_tokens, self.sc.max_seq_len - 1))
+            token_ids = torch.randint(0, self.cfg.vocab_size, (n,), generator=g).tolist()
+        seen: Dict[str, torch.Tensor] = {}
+
+        def collect(tag: str, x: torch.Tensor) -> None:
+            a = x.detach().abs().amax().float()
+            seen[tag] = a if tag not in seen else torch.maximum(seen[tag], a)
+
+        prev = self.runner.act_collector
+        self.runner.act_collector = collect
+        graphs = self.use_graphs
+        self.use_graphs = False
+        s = self.open_sequence()
+        try:
+            with torch.no_grad():
+                r = SeqRows(s.slot, 0, list(token_ids), output_rows=(len(token_ids) - 1,))
+                self.step([r], [s])
+        finally:
+            self.close_sequence(s)
+            self.runner.act_collector = prev
+            self.use_graphs = graphs
+        out = {}
+        for tag, a in seen.items():
+            W = sites.get(tag)
+            if W is not None and W.fmt == "nvfp4":
+                W.act_scale = calibrate_act_scale(float(a))
+                out[tag] = W.act_scale
+        self.act_scales_calibrated = True
+        return out
 
     # ------------------------------------------------------------------ sequences
     def open_sequence(self) -> Sequence_:
@@ -194,42 +266,10 @@ class Engine:
                     self.alloc.release_pages(s.pages[-a:])
                     del s.pages[-a:]
             raise
-        b.fill(rows)
-        plain = not tap_layers and gdn_log is None and not gdn_to_alt and mask is None and sample and not exact
-        decode_batch = bucket <= GRAPH_MAX_DECODE_ROWS and all(len(r.token_ids) == 1 for r in rows)
-        use_graph = self.use_graphs and plain and (bucket <= GRAPH_MAX_ROWS or decode_batch)
-        b.graph_static = use_graph
-        b.upload()
-        if use_graph:
-            out = self._run_graph(bucket, b, n_out)
-        else:
-            self.ops.exact_rows = exact
-            try:
-                out = self.runner.forward(b, bucket if self.backend == "cuda" else n_rows, n_out, tap_layers=tap_layers,
-                                          gdn_log=gdn_log, gdn_to_alt=gdn_to_alt, mask=mask, mask_active=mask_active,
-                                          sample=sample)
-            finally:
-                self.ops.exact_rows = False
-        toks: List[int] = []
-        if self.device.type == "cuda":
-            if out.tokens is not None and n_out:
-                self.h_tokens[:n_out].copy_(out.tokens[:n_out], non_blocking=True)
-            self.h_status.copy_(self.state.status, non_blocking=True)
-            torch.cuda.current_stream().synchronize()
-            status = int(self.h_status[0])
-            if out.tokens is not None:
-                toks = self.h_tokens[:n_out].tolist()
-            if status == 0 and hasattr(self.ops, "status"):
-                status = int(self.ops.status[0])
-        else:
-            status = int(self.state.status[0])
-            if out.tokens is not None:
-                toks = out.tokens[:n_out].tolist()
-        self.steps += 1
+        toks, out, status = self._execute(rows, n_rows, n_out, bucket, b, tap_layers=tap_layers, gdn_log=gdn_log,
+                                          gdn_to_alt=gdn_to_alt, mask=mask, mask_active=mask_active, sample=sample,
+                                          exact=exact)
         if status != 0:
-            self.state.status.zero_()
-            if hasattr(self.ops, "status"):
-                self.ops.status.zero_()
             for s in seq_objs:
                 s.poisoned = True
             raise SequenceError(f"device reported status {status}; sequences poisoned")
@@ -239,7 +279,7 @@ class Engine:
         return toks, out
 
     def _run_graph(self, bucket: int, b: StepBatch, n_out: int) -> StepOutput:
-        key = bucket * 4096 + n_out
+        key = (bucket * 4096 + n_out) * 2 + (1 if b.identity_out else 0)
         g = self.graphs.get(key)
         if g is None:
             # warm up once outside capture (allocates workspaces, sets kernel attributes)
@@ -279,12 +319,25 @@ class Engine:
                  gdn_log=None, gdn_to_alt: bool = False, sample: bool = True):
         """Execute one step for sequences whose slots/pages are managed by the caller (the batcher).
         Returns (tokens, StepOutput, device_status)."""
+        if self.tp is not None:
+            self.tp.assert_alive()
         n_rows = sum(len(r.token_ids) for r in rows)
         n_out = sum(len(r.output_rows) for r in rows)
         bucket = resolve_row_bucket(n_rows)
         b = self._batch(bucket)
+        return self._execute(rows, n_rows, n_out, bucket, b, tap_layers=tap_layers, gdn_log=gdn_log,
+                             gdn_to_alt=gdn_to_alt, mask=mask, mask_active=mask_active, sample=sample, exact=False)
+
+    def _execute(self, rows, n_rows: int, n_out: int, bucket: int, b: StepBatch, *, tap_layers, gdn_log, gdn_to_alt,
+                 mask, mask_active, sample: bool, exact: bool):
+        """Fill and upload the batch descriptor, run the forward (graph replay for plain decode-sized steps, eager
+        otherwise), read back sampled ids and every device status word with one stream synchronisation.  Returns
+        (tokens, StepOutput, status); a non-zero status has already been cleared on the device (together with any
+        stream-K flags a kernel that gave up may have left raised) and it is the caller's job to poison sequences.
+        Status words: the state's own (bad page / slot indices), the op set's (bounded waits of the projection and
+        all-reduce kernels; the tensor-parallel transport writes into the same word)."""
         b.fill(rows)
-        plain = not tap_layers and gdn_log is None and not gdn_to_alt and mask is None and sample
+        plain = not tap_layers and gdn_log is None and not gdn_to_alt and mask is None and sample and not exact
         decode_batch = bucket <= GRAPH_MAX_DECODE_ROWS and all(len(r.token_ids) == 1 for r in rows)
         use_graph = self.use_graphs and plain and (bucket <= GRAPH_MAX_ROWS or decode_batch)
         b.graph_static = use_graph
@@ -292,29 +345,38 @@ class Engine:
         if use_graph:
             out = self._run_graph(bucket, b, n_out)
         else:
-            out = self.runner.forward(b, bucket if self.backend == "cuda" else n_rows, n_out, tap_layers=tap_layers,
-                                      gdn_log=gdn_log, gdn_to_alt=gdn_to_alt, mask=mask, mask_active=mask_active,
-                                      sample=sample)
+            self.ops.exact_rows = exact
+            try:
+                out = self.runner.forward(b, bucket if self.backend == "cuda" else n_rows, n_out, tap_layers=tap_layers,
+                                          gdn_log=gdn_log, gdn_to_alt=gdn_to_alt, mask=mask, mask_active=mask_active,
+                                          sample=sample)
+            finally:
+                self.ops.exact_rows = False
         toks: List[int] = []
+        ops_status = getattr(self.ops, "status", None)
         if self.device.type == "cuda":
             if out.tokens is not None and n_out:
                 self.h_tokens[:n_out].copy_(out.tokens[:n_out], non_blocking=True)
-            self.h_status.copy_(self.state.status, non_blocking=True)
+            self.h_status[0:1].copy_(self.state.status, non_blocking=True)
+            if ops_status is not None:
+                self.h_status[1:2].copy_(ops_status, non_blocking=True)
             torch.cuda.current_stream().synchronize()
-            status = int(self.h_status[0])
+            status = int(self.h_status[0]) or int(self.h_status[1])
             if out.tokens is not None:
                 toks = self.h_tokens[:n_out].tolist()
-            if status == 0 and hasattr(self.ops, "status"):
-                status = int(self.ops.status[0])
         else:
             status = int(self.state.status[0])
+            if status == 0 and ops_status is not None:
+                status = int(ops_status[0])
             if out.tokens is not None:
                 toks = out.tokens[:n_out].tolist()
         self.steps += 1
         if status != 0:
             self.state.status.zero_()
-            if hasattr(self.ops, "status"):
-                self.ops.status.zero_()
+            if ops_status is not None:
+                ops_status.zero_()
+            if hasattr(self.ops, "reset_after_error"):
+                self.ops.reset_after_error()
         return toks, out, status
 
     # ------------------------------------------------------------------ convenience: one request
