@@ -13,11 +13,10 @@ from typing import List, Optional
 SUBCOMMANDS = ("pp", "tg", "batch", "gemm", "activation-quantize", "rmsnorm", "l2-normalize", "kv-append",
                "paged-attention", "rope", "gdn-recurrence", "gdn-conv1d", "elementwise", "embedding", "sampling", "mtp",
                "gpu-memory", "tp-reduce", "dflash2")
-FUSED_AWAY = {"activation-quantize": "activation staging is part of the small-M linear prologue (bench: gemm --rows 1)",
-              "l2-normalize": "q/k L2 normalisation is fused into the GDN kernel (bench: gdn-recurrence)",
-              "rope": "partial RoPE is fused with q/k norm and the KV append (bench: kv-append)",
-              "gdn-conv1d": "the short conv is fused into the GDN kernel (bench: gdn-recurrence)",
-              "elementwise": "residual add / SwiGLU / gates live in projection epilogues (bench: gemm)"}
+# Reference sub-commands whose op has no stand-alone launch here: each times the kernel the op is fused into.
+FUSED_INTO = {"l2-normalize": "gdn-recurrence",      # q/k L2 normalisation happens inside the GDN mixer kernel
+              "gdn-conv1d": "gdn-recurrence",        # so does the short causal conv
+              "rope": "kv-append"}                   # partial RoPE is fused with q/k norm and the paged KV append
 
 
 def _model_args(p):
@@ -25,7 +24,6 @@ def _model_args(p):
     p.add_argument("--preset", default=None); p.add_argument("--device", default=None)
     p.add_argument("--kv-cache-dtype", default="bf16", choices=["bf16", "fp8_e4m3"])
     p.add_argument("--runs", type=int, default=3); p.add_argument("--warmup", type=int, default=1); p.add_argument("--output")
-    p.add_argument("--batch-shadow", type=int, default=0, help="keep resident bf16 weights for batched steps (2 B/weight)")
 
 
 def build_parser() -> argparse.ArgumentParser:
@@ -50,18 +48,17 @@ def build_parser() -> argparse.ArgumentParser:
     mt.add_argument("--prefill-chunk", type=int, default=2048)
     ge = sub.add_parser("gemm", help="projection kernels")
     ge.add_argument("--dtype", default="nvfp4", choices=["bf16", "nvfp4", "mxfp8"])
-    ge.add_argument("--variant", default="auto", choices=["gemv", "gemm", "batched", "auto"]); ge.add_argument("--rows", default="1,4,8,256,2048")
+    ge.add_argument("--variant", default="auto", choices=["gemv", "gemm", "tc", "auto"]); ge.add_argument("--rows", default="1,4,8,256,2048")
     ge.add_argument("--n", type=int, default=5120); ge.add_argument("--k", type=int, default=5120)
     ge.add_argument("--actual-qwen-shapes", action="store_true"); ge.add_argument("--warmup", type=int, default=5)
     ge.add_argument("--samples", type=int, default=10); ge.add_argument("--check", action="store_true"); ge.add_argument("--out")
-    for name in ("rmsnorm", "kv-append", "paged-attention", "gdn-recurrence", "embedding", "sampling", "gpu-memory", "dflash2"):
+    for name in ("rmsnorm", "kv-append", "paged-attention", "gdn-recurrence", "embedding", "sampling", "gpu-memory", "dflash2",
+                 "activation-quantize", "elementwise") + tuple(FUSED_INTO):
         p = sub.add_parser(name); p.add_argument("--rows", type=int, default=1); p.add_argument("--context", type=int, default=4096)
         p.add_argument("--samples", type=int, default=20); p.add_argument("--model", default="27b", choices=["tiny", "4b", "27b"])
         p.add_argument("--kv-cache-dtype", default="bf16", choices=["bf16", "fp8_e4m3"]); p.add_argument("--variant", default="optimized", choices=["optimized"])
     tr = sub.add_parser("tp-reduce", help="row-parallel combine latency (run under torchrun for > 1 GPU)")
     tr.add_argument("--rows", default="1,8"); tr.add_argument("--hidden", type=int, default=5120); tr.add_argument("--samples", type=int, default=50)
-    for name, why in FUSED_AWAY.items():
-        p = sub.add_parser(name, help="(fused away) " + why); p.add_argument("--variant", default="optimized", choices=["optimized"])
     return ap
 
 
@@ -78,8 +75,7 @@ def _engine(a, max_seq_len: int, slots: int = 1, spec_rows: int = 0):
         cfg = PRESETS[a.random_model or "tiny"]()
         ew = build_engine_weights(cfg, random_getter(cfg, 0, dev), a.preset or "bf16", dev, keep_canonical=dev.type != "cuda")
     extra = dict(conv_ring=max(16, 3 + spec_rows), spec_rows=spec_rows) if spec_rows else {}
-    return Engine(ew, dev, StateConfig(max_slots=slots, max_seq_len=max_seq_len, kv_dtype=a.kv_cache_dtype, **extra),
-                  batch_shadow=bool(getattr(a, "batch_shadow", 0))), dev
+    return Engine(ew, dev, StateConfig(max_slots=slots, max_seq_len=max_seq_len, kv_dtype=a.kv_cache_dtype, **extra)), dev
 
 
 def _timed(dev, fn):
@@ -216,14 +212,20 @@ def cmd_gemm(a) -> int:
     lines = ["dtype,requested_variant,selected_variant,shape_name,rows,n,k,warmup,samples,min_us,p50_us,p95_us,mean_us,GBps,TFLOPs"]
     formats.DEFAULT_SEARCH = 0
     for (name, n, k) in shapes:
-        W = LinearW(formats.quantize(torch.randn(n, k, device=dev) * 0.02, a.dtype)).make_tiled(keep_canonical=a.check)
-        if a.variant == "batched":
-            W.make_shadow()                 # resident bf16 expansion: rows 2..64 run the swap-AB split-K tcgen05 GEMM
+        # variants: gemv = streaming CUDA-core kernel (<= 8 rows), gemm = bf16 tcgen05 GEMM after a weight expansion,
+        # tc = block-scaled tcgen05 kernel on the quantised codes (any rows), auto = what the engine's selector picks
+        # with both layouts resident
+        W = LinearW(formats.quantize(torch.randn(n, k, device=dev) * 0.02, a.dtype))
+        block = a.dtype in ("nvfp4", "mxfp8")
+        if a.variant in ("gemv", "gemm", "auto") or not block:
+            W.make_tiled(True)
+        if a.variant in ("tc", "auto") and block:
+            W.make_umma(True)
         for m in rows:
-            if a.variant == "gemv" and m > 8 or a.variant == "gemm" and m <= 8 or a.variant == "batched" and not (2 <= m <= 64):
+            if a.variant == "gemv" and m > 8 or a.variant == "gemm" and m <= 8 or a.variant == "tc" and not block:
                 continue
             x = torch.randn(m, k, device=dev).to(torch.bfloat16)
-            sel = "batched" if a.variant == "batched" else ("gemv" if m <= 8 else "gemm")
+            sel = {"stream": "gemv"}.get(ops.select_linear(W, m), ops.select_linear(W, m))
             for _ in range(a.warmup):
                 ops.linear(x, W, name="b")
             ts = []
@@ -234,7 +236,9 @@ def cmd_gemm(a) -> int:
             ts.sort()
             p50 = ts[len(ts) // 2]
             if a.check:
-                ref = x.float() @ W.dense().T
+                from ..quant.act_quant import fake_quant
+                xr = fake_quant(x.float(), W.fmt, W.act_scale) if sel == "tc" else x.float()
+                ref = xr @ W.dense().T
                 err = float((y.float() - ref).norm() / ref.norm())
                 assert err < 2e-2, f"numerics check failed: rel err {err}"
             lines.append(f"{a.dtype},{a.variant},{sel},{name},{m},{n},{k},{a.warmup},{a.samples},{ts[0]:.2f},{p50:.2f},"
@@ -277,7 +281,26 @@ def cmd_kernel(a) -> int:
     proj = torch.randn(a.rows, L_gdn.mixer.in_proj.N + L_gdn.mixer.ba_proj.N, device=dev, generator=g).to(torch.bfloat16)
     logits = torch.randn(a.rows, cfg.vocab_size, device=dev, generator=g)
     q = ops.attn_prep(qkv, L_attn.mixer, eng.runner.hq, eng.runner.hkv, b, st.kv[li_a], st)
-    fns = {"rmsnorm": lambda: ops.rmsnorm(x, L_attn.input_norm, 1e-6, "bn"),
+    from ..models.qwen35.weights import LinearW
+    from ..ops import _lib
+    from ..ops._lib import c_int, ptr
+    from ..quant import formats
+    wq = LinearW(formats.quantize(torch.randn(256, small.hidden_size, device=dev) * 0.02, "nvfp4")).make_umma()
+    gu = torch.randn(a.rows, 2 * small.intermediate_size, device=dev, generator=g).to(torch.bfloat16)
+    gu_out = torch.empty(a.rows, small.intermediate_size, dtype=torch.bfloat16, device=dev)
+
+    def elementwise():          # the two stand-alone elementwise kernels that exist: residual add and interleaved SwiGLU
+        _lib.call("ps_add", ptr(x), c_int(x.stride(0)), ptr(x), c_int(x.stride(0)), ptr(x), c_int(x.stride(0)), c_int(a.rows),
+                  c_int(small.hidden_size))
+        _lib.call("ps_swiglu_interleaved", ptr(gu), c_int(gu.stride(0)), ptr(gu_out), c_int(gu_out.stride(0)), c_int(a.rows),
+                  c_int(small.intermediate_size))
+    fused_into = FUSED_INTO.get(a.cmd)
+    if fused_into:
+        print(f"fused_into={fused_into}")
+        a.cmd = fused_into
+    fns = {"activation-quantize": lambda: ops.act_quant(x, wq, L_attn.input_norm, 1e-6),
+           "elementwise": elementwise,
+           "rmsnorm": lambda: ops.rmsnorm(x, L_attn.input_norm, 1e-6, "bn"),
            "kv-append": lambda: ops.attn_prep(qkv, L_attn.mixer, eng.runner.hq, eng.runner.hkv, b, st.kv[li_a], st),
            "paged-attention": lambda: ops.paged_attention(q, qkv, eng.runner.hq, eng.runner.hkv, b, st.kv[li_a], st, a.context + a.rows),
            "gdn-recurrence": lambda: ops.gdn(proj, L_gdn.mixer, eng.runner.hk, eng.runner.hv, b, st.gdn[li_g], st),
@@ -358,9 +381,6 @@ def cmd_tp_reduce(a) -> int:
 
 def main(argv: Optional[List[str]] = None) -> int:
     a = build_parser().parse_args(argv)
-    if a.cmd in FUSED_AWAY:
-        print(f"{a.cmd}: {FUSED_AWAY[a.cmd]}")
-        return 0
     return {"pp": cmd_pp, "tg": cmd_tg, "batch": cmd_batch, "gemm": cmd_gemm, "tp-reduce": cmd_tp_reduce,
             "mtp": cmd_mtp}.get(a.cmd, cmd_kernel)(a)
 

@@ -28,9 +28,6 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--arena-gib", type=float, default=16)
     ap.add_argument("--page-tokens", type=int, default=16)
     ap.add_argument("--max-concurrent-requests", type=int, default=1)
-    ap.add_argument("--batch-shadow", default="auto", choices=["auto", "on", "off"],
-                    help="keep a resident bf16 expansion of the weights (2 B/weight) so batched steps run on the tensor cores; "
-                         "auto = on when more than one concurrent request is allowed and the expansion fits in free memory")
     ap.add_argument("--kv-cache-capacity-tokens", type=int, default=0)
     ap.add_argument("--prefix-cache-capacity-tokens", type=int, default=0)
     ap.add_argument("--prefix-cache-max-entries", type=int, default=16)
@@ -100,14 +97,7 @@ class ComputeRuntime:
         sc = StateConfig(max_slots=a.max_concurrent_requests, max_seq_len=a.max_seq_len, page_tokens=a.page_tokens,
                          kv_capacity_tokens=a.kv_cache_capacity_tokens, kv_dtype=a.kv_cache_dtype,
                          conv_ring=32 if spec else 4, spec_rows=a.dflash2_drafts + 1 if spec else 0)
-        mode = getattr(a, "batch_shadow", "off")
-        shadow = mode == "on"
-        if mode == "auto" and a.max_concurrent_requests > 1 and self.device.type == "cuda":
-            import torch
-            free, _ = torch.cuda.mem_get_info(self.device)
-            need = sum(w.N * w.k_padded * 2 for w in ew.linears())
-            shadow = need < 0.5 * free
-        self.engine = Engine(ew, self.device, sc, batch_shadow=shadow)
+        self.engine = Engine(ew, self.device, sc)
         compiler = None
         if a.constraint_tokenizer_info:
             from ..runtime.constraints import TokenConstraintCompiler

@@ -239,6 +239,7 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char* sBres = smem + (size_t)g.stages * kStage;                          // resident activation codes
+    __nv_bfloat16* sEpi = reinterpret_cast<__nv_bfloat16*>(sBres);                    // streamed path: 128 x 128 bf16 output staging
     uint32_t* sSfRes = reinterpret_cast<uint32_t*>(sBres + (size_t)g.res_slots * kBTile);   // [slot][APP][32 rows] scale words
     __shared__ __align__(8) uint64_t full_bar[kBsMaxStages], empty_bar[kBsMaxStages], acc_full[2], acc_empty[2], drain_bar;
     __shared__ uint32_t tmem_base_slot;
@@ -471,9 +472,12 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         tc::bulk_load(st + kOffSfb + j * kSfaBytes, g.sfx + ((size_t)(tm * NBLK + j) * P + p) * kSfaBytes, kSfaBytes, &full_bar[i]);
                 }
             }
+            long long prof_pwait = 0;
             for (int it = pre; u0 + it < u1; ++it) {
                 const int s = it % stages;
+                const long long tp0 = prof ? clock64() : 0;
                 if (!tc::mbar_wait_abortable(&empty_bar[s], (uint32_t)((it / stages) & 1) ^ 1u, g.budget, &s_abort)) break;
+                if (prof) prof_pwait += clock64() - tp0;
                 const int u = u0 + it, t = u / P, p = u - t * P, tn = t / g.tiles_m;
                 unsigned char* st = smem + (size_t)s * kStage;
                 tc::mbar_expect_tx(&full_bar[s], kStageTx);
@@ -489,6 +493,7 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 issued = it + 1;
             }
             s_issued = issued;
+            if (prof) g.prof[14] = prof_pwait;
             if (g.next_total > 0 && (int)blockIdx.x < g.next_grid) {
                 // everything this CTA needs is on its way: warm L2 with what the same CTA index reads first in the
                 // projection that follows, so that kernel's ring fill does not start from DRAM
@@ -600,10 +605,22 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             reinterpret_cast<__nv_bfloat16*>(g.out)[(size_t)m * g.ldo + n] = o;
             return bf16_to_f32(o);
         };
+        long long prof_ewait = 0, prof_ework = 0;
         while (S.next(t, p0, p1)) {
             const int buf = ACC_BUFS == 2 ? (seg & 1) : 0;
+            const long long te0 = prof ? clock64() : 0;
             if (!tc::mbar_wait_abortable(&acc_full[buf], (uint32_t)((seg / ACC_BUFS) & 1), g.budget, &s_abort)) ok = false;
+            const long long te1 = prof ? clock64() : 0;
+            prof_ewait += te1 - te0;
             ok = __all_sync(0xffffffffu, ok);           // warp-uniform: the shuffles below need every lane
+            if constexpr (!RES) {
+                // the streamed epilogue has named barriers inside its row-block loop: agree on `ok` across the four warps
+                if (!ok) s_abort = 1;
+                epi_bar_sync();
+                if (etid == 0) s_ssq[1] = s_abort == 0 ? 1.f : 0.f;
+                epi_bar_sync();
+                ok = s_ssq[1] != 0.f;
+            }
             tc::fence_after_sync();
             const uint32_t acc = tmem_base + (uint32_t)(buf * ACC_STRIDE) + lane_addr;
             const int tn = t / g.tiles_m, tm = t - tn * g.tiles_m;
@@ -648,6 +665,8 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             }
             if (finisher) {
                 const bool tp_on = g.tp.size > 1;
+                const bool staged = !RES && !g.out_f32 && !tp_on;       // bf16 output of many rows: staged through shared memory
+                bool released = false;
                 const bool want_ssq = g.ssq_out != nullptr && g.epilogue != EPI_SWIGLU;
                 uint32_t tp_val = 0; size_t tp_par = 0;
                 if (tp_on) {
@@ -689,13 +708,39 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                                 }
                             }
                         }
+                        // the row factors of the chunk sit one per lane and are broadcast with a shuffle
+                        const int m_base = tm * NB + c0;
+                        float rs_lane = g.out_scale;
+                        if constexpr (RES) rs_lane *= s_inv_rms[(c0 + lane) & 31];
+                        else if (g.row_scale != nullptr && m_base + lane < g.M) rs_lane *= g.row_scale[m_base + lane];
+                        if (staged) {
+                            // lean bodies, one per epilogue kind (no per-element mode branches): values go to the staging
+                            // block as rows of 128 (64 after SwiGLU) bf16; rows past M are staged too and never written out
+                            __nv_bfloat16* srow = sEpi + (c0 & 127) * (g.epilogue == EPI_SWIGLU ? 64 : 128);
+                            if (g.epilogue == EPI_SWIGLU) {
+#pragma unroll
+                                for (int j = 0; j < CH; ++j) {
+                                    const float yb = bf16_to_f32(f32_to_bf16(v[j] * __shfl_sync(0xffffffffu, rs_lane, j & 31)));
+                                    const float other = __shfl_xor_sync(0xffffffffu, yb, 1);
+                                    const float o = __fdividef(yb, 1.f + __expf(-yb)) * other;
+                                    if (!(lane & 1)) srow[j * 64 + (row_l >> 1)] = f32_to_bf16(o);
+                                }
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < CH; ++j)
+                                    srow[j * 128 + row_l] = f32_to_bf16(v[j] * __shfl_sync(0xffffffffu, rs_lane, j & 31));
+                            }
+                        } else {
+                        float resv[CH];
+                        const bool use_res = g.epilogue == EPI_RESIDUAL && !tp_on;
+#pragma unroll
+                        for (int j = 0; j < CH; ++j)
+                            resv[j] = (use_res && m_base + j < g.M && n < g.N) ? bf16_to_f32(g.residual[(size_t)(m_base + j) * g.ld_res + n]) : 0.f;
 #pragma unroll
                         for (int j = 0; j < CH; ++j) {
-                            const int m = tm * NB + c0 + j;
-                            if (m >= g.M) break;                    // uniform over the warp
-                            float rs = 1.f;
-                            if constexpr (RES) rs = s_inv_rms[c0 + j]; else if (g.row_scale != nullptr) rs = g.row_scale[m];
-                            const float y = v[j] * (g.out_scale * rs);
+                            const int m = m_base + j;
+                            const float y = v[j] * __shfl_sync(0xffffffffu, rs_lane, j & 31);
+                            if (m >= g.M) continue;                 // uniform over the warp
                             if (tp_on) {
                                 // tensor-parallel combine, step 1: push this rank's partial into every rank's receive buffer
                                 if (n < g.N) {
@@ -706,21 +751,87 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                                 const float yb = bf16_to_f32(f32_to_bf16(y));
                                 const float other = __shfl_xor_sync(0xffffffffu, yb, 1);
                                 if (!(lane & 1) && n + 1 < g.N) {
-                                    const float o = silu_f(yb) * other;
+                                    const float o = __fdividef(yb, 1.f + __expf(-yb)) * other;
                                     if (g.out_f32) reinterpret_cast<float*>(g.out)[(size_t)m * g.ldo + (n >> 1)] = o;
                                     else reinterpret_cast<__nv_bfloat16*>(g.out)[(size_t)m * g.ldo + (n >> 1)] = f32_to_bf16(o);
                                 }
                             } else {
-                                const float o = n < g.N ? store_plain(m, n, y) : 0.f;
+                                float o = 0.f;
+                                if (n < g.N) {
+                                    float yy = y;
+                                    if (use_res) yy = bf16_to_f32(f32_to_bf16(y)) + resv[j];
+                                    if (g.out_f32) { reinterpret_cast<float*>(g.out)[(size_t)m * g.ldo + n] = yy; o = yy; }
+                                    else {
+                                        const __nv_bfloat16 ob = f32_to_bf16(yy);
+                                        reinterpret_cast<__nv_bfloat16*>(g.out)[(size_t)m * g.ldo + n] = ob;
+                                        o = bf16_to_f32(ob);
+                                    }
+                                }
                                 if (want_ssq && c0 + j < 32) {
                                     const float sq = warp_sum(o * o);
                                     if (lane == 0) s_ssq[quad * 32 + c0 + j] = sq;
                                 }
                             }
                         }
+                        }
+                        if (staged && (((c0 + CH) & 127) == 0 || c0 + CH >= NB || tm * NB + c0 + CH >= g.M)) {
+                            // a block of up to 128 batch rows is staged: release the accumulator if it was the last one,
+                            // then write the rows out (and add the residual) in 16-byte pieces, full row segments per warp
+                            const int rb0 = tm * NB + ((c0 + CH - 1) & ~127);
+                            const bool last_block = c0 + CH >= NB || tm * NB + c0 + CH >= g.M;
+                            if (last_block && complete) {
+                                tc::fence_before_sync();
+                                __syncwarp();
+                                if (lane == 0) tc::mbar_arrive(&acc_empty[buf]);
+                                released = true;
+                            }
+                            epi_bar_sync();
+                            const int cols = g.epilogue == EPI_SWIGLU ? 64 : 128, cpr = cols >> 3;
+                            const int n_base = g.epilogue == EPI_SWIGLU ? (tn * kBsTileN) >> 1 : tn * kBsTileN;
+                            const int n_lim = g.epilogue == EPI_SWIGLU ? g.N >> 1 : g.N;
+                            const int rcnt = min(128, g.M - rb0);
+                            __nv_bfloat16* outp = reinterpret_cast<__nv_bfloat16*>(g.out);
+                            for (int i = etid; i < rcnt * cpr; i += 128) {
+                                const int rr = i / cpr, ch = i - rr * cpr;
+                                const int m = rb0 + rr, n0 = n_base + ch * 8;
+                                if (n0 >= n_lim) continue;
+                                const uint4 sv = *reinterpret_cast<const uint4*>(sEpi + rr * cols + ch * 8);
+                                uint32_t w[4] = {sv.x, sv.y, sv.z, sv.w};
+                                __nv_bfloat16* dst = outp + (size_t)m * g.ldo + n0;
+                                const bool full = n0 + 8 <= n_lim;
+                                if (g.epilogue == EPI_RESIDUAL) {
+                                    const __nv_bfloat16* rp = g.residual + (size_t)m * g.ld_res + n0;
+                                    if (full && (reinterpret_cast<uintptr_t>(rp) & 15) == 0) {
+                                        const uint4 rv = *reinterpret_cast<const uint4*>(rp);
+                                        const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+                                        for (int e = 0; e < 4; ++e) {
+                                            const float2 a2 = bf16x2_bits_to_f32x2(w[e]), r2 = bf16x2_bits_to_f32x2(rw[e]);
+                                            w[e] = f32x2_to_bf16x2_bits(a2.x + r2.x, a2.y + r2.y);
+                                        }
+                                    } else {
+#pragma unroll
+                                        for (int e = 0; e < 4; ++e) {
+                                            const float2 a2 = bf16x2_bits_to_f32x2(w[e]);
+                                            const float r0 = n0 + 2 * e < n_lim ? bf16_to_f32(rp[2 * e]) : 0.f;
+                                            const float r1 = n0 + 2 * e + 1 < n_lim ? bf16_to_f32(rp[2 * e + 1]) : 0.f;
+                                            w[e] = f32x2_to_bf16x2_bits(a2.x + r0, a2.y + r1);
+                                        }
+                                    }
+                                }
+                                if (full && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                                    *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+                                } else {
+#pragma unroll
+                                    for (int e = 0; e < 8; ++e)
+                                        if (n0 + e < n_lim) dst[e] = reinterpret_cast<const __nv_bfloat16*>(w)[e];
+                                }
+                            }
+                            epi_bar_sync();             // the staging block is free again
+                        }
                     }
                 }
-                if (complete) {
+                if (complete && !released) {
                     tc::fence_before_sync();
                     __syncwarp();
                     if (lane == 0) tc::mbar_arrive(&acc_empty[buf]);
@@ -771,8 +882,9 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 }
             }
             ++seg;
+            if (prof) prof_ework += clock64() - te1;
         }
-        if (prof && etid == 0) g.prof[9] = clock64();
+        if (prof && etid == 0) { g.prof[9] = clock64(); g.prof[11] = prof_ewait; g.prof[12] = prof_ework; g.prof[13] = seg; }
     }
     tc::fence_before_sync();
     __syncthreads();
@@ -925,6 +1037,7 @@ static bool bs_plan(int M, int N, int K, bool resident, int grid_override, BsPla
         res_bytes = (size_t)pl.res_slots * (pl.nb * 128 + T::kApp * 128);
         if (96 + pl.res_slots * T::kApp * 4 > 512) return false;      // resident scale columns in tensor memory
     }
+    if (!resident) res_bytes = 128 * 128 * 2;          // output staging block of the streamed path's epilogue
     const size_t avail = kBsSmemBudget - 1024;
     if (res_bytes + 3 * (size_t)stage > avail) return false;
     pl.stages = (int)((avail - res_bytes) / stage);

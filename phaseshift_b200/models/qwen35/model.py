@@ -103,7 +103,7 @@ class Qwen35Runner:
                 n_main = m.in_proj.N
                 if hasattr(ops, "buf"):
                     proj = ops.buf("gdn_proj", rows, n_main + m.ba_proj.N)
-                    batched = rows >= 2 and m.in_proj.shadow is not None and not ops.exact_rows
+                    batched = rows >= 2 and m.in_proj.rowmajor_bf16 is not None and not ops.exact_rows
                     if rows <= FUSED_BA_MAX_ROWS and not batched:
                         # decode / verify: the GDN kernel projects beta/decay inputs itself from the
                         # normalised row that in_proj leaves behind -> one launch fewer per layer

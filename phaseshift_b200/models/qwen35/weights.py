@@ -107,7 +107,6 @@ class LinearW:
     _kpad: int = 0
     _fmt: str = ""
     _tscale: float = 1.0
-    shadow: Optional[torch.Tensor] = None      # optional resident bf16 expansion [N, k_padded] for batched steps
     sf_atoms: Optional[torch.Tensor] = None    # block scales in the tensor-core layout (quant/act_quant.pack_sf_atoms)
     codes: Optional[torch.Tensor] = None       # canonical code matrix kept for the tensor-core path (TMA reads it as is)
     act_scale: float = 0.0                     # fixed NVFP4 activation scale of this projection's input site
@@ -139,21 +138,13 @@ class LinearW:
             self.q = None
         return self
 
-    def make_shadow(self) -> "LinearW":
-        """Keep a resident bf16 expansion of the weights (2 B/weight) so that steps with several rows run the
-        tensor-core GEMM straight from it instead of re-expanding or streaming the block codes once per row."""
-        if self.shadow is None:
-            import ctypes
-            from ...ops import _lib
-            from ...ops.cuda_ops import WFMT
-            if self.tiled is None:
-                self.make_tiled()
-            self.shadow = torch.empty(self.N, self._kpad, dtype=torch.bfloat16, device=self.tiled.device)
-            with torch.cuda.device(self.tiled.device):
-                _lib.call("ps_dequant_tiled", ctypes.c_int(WFMT[self._fmt]), ctypes.c_void_p(self.tiled.data_ptr()), ctypes.c_int(self.N),
-                          ctypes.c_int(self._kpad), ctypes.c_float(self._tscale), ctypes.c_void_p(self.shadow.data_ptr()),
-                          ctypes.c_int(self._kpad))
-        return self
+    @property
+    def rowmajor_bf16(self) -> Optional[torch.Tensor]:
+        """bf16 weights in plain row-major form [N, k_padded] (the canonical payload, when it is still resident):
+        what the bf16 tensor-core GEMMs read through TMA.  None for block-quantised weights."""
+        if self._fmt == "bf16" and self.q is not None and self.q.codes.is_cuda:
+            return self.q.codes
+        return None
 
     @property
     def N(self) -> int:
@@ -261,15 +252,6 @@ class EngineWeights:
             m = l.mixer
             out += [l.gate_up, l.down] + ([m.in_proj, m.ba_proj, m.out_proj] if l.kind == 0 else [m.qkv_proj, m.o_proj])
         return out
-
-    def make_shadows(self) -> int:
-        """Resident bf16 expansions for batched steps (see LinearW.make_shadow); returns the bytes added."""
-        n = 0
-        for w in self.linears():
-            if w.fmt != "bf16" or True:
-                w.make_shadow()
-                n += w.shadow.numel() * 2
-        return n
 
     def decode_read_bytes(self) -> int:
         """Weight bytes one decode step must stream from HBM (everything except the embedding table)."""
@@ -469,7 +451,8 @@ def build_engine_weights(cfg: Qwen35Config, get, preset: str = "bf16", device="c
                     lw.make_tiled(True)
                 lw.make_umma(keep_canonical)
             else:
-                lw.make_tiled(keep_canonical or role == "gdn_small")   # the GDN kernel reads b/a rows row-major
+                # the GDN kernel reads b/a rows row-major; bf16 matrices keep their row-major form for the tensor-core GEMMs
+                lw.make_tiled(keep_canonical or role == "gdn_small" or (lw.fmt == "bf16" and layout != "stream"))
         return lw
 
     def dev(t: torch.Tensor, dtype=torch.bfloat16) -> torch.Tensor:

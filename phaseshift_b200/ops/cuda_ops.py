@@ -121,9 +121,9 @@ class CudaOps:
                                   ssq_out=ssq_out, prefetch=prefetch)
         if tp_combine is not None and M > SMALL_M_MAX:
             raise ValueError("the fused tensor-parallel combine handles at most 8 rows")
-        # tensor-core GEMM: prefill-sized steps, and batched steps (>= 2 rows) when a resident bf16 expansion of
-        # the weights exists (Fast mode only: Exact verification stays on the batch-invariant streaming kernel)
-        batched = (M >= 2 and W.shadow is not None and tp_combine is None and xn_out is None and self.use_tc_gemm
+        # bf16 tensor-core GEMM: prefill-sized steps, and batched steps (>= 2 rows) of bf16 weights whose row-major form
+        # is resident (Fast mode only: Exact verification stays on the batch-invariant streaming kernel)
+        batched = (M >= 2 and W.rowmajor_bf16 is not None and tp_combine is None and xn_out is None and self.use_tc_gemm
                    and not self.exact_rows)
         if sel == "gemm" or batched:
             return self.linear_large(x, W, name=name, norm_w=norm_w, eps=eps, residual=residual, swiglu=swiglu,
@@ -158,8 +158,8 @@ class CudaOps:
         if W.tiled is None:
             W.make_tiled()
         kp = W.k_padded
-        if W.shadow is not None:
-            wd = W.shadow
+        if W.rowmajor_bf16 is not None:
+            wd = W.rowmajor_bf16
         else:
             need = W.N * kp
             if self.wscratch is None or self.wscratch.numel() < need:
@@ -169,7 +169,7 @@ class CudaOps:
                       c_float(W.tensor_scale), ptr(wd), c_int(kp))
             self.launches += 1
         epi = EPI_SWIGLU if swiglu else (EPI_RESIDUAL if residual is not None else EPI_STORE)
-        if W.shadow is not None and M <= 64 and W.N % 2 == 0:
+        if W.rowmajor_bf16 is not None and M <= 64 and W.N % 2 == 0:
             # batched decode: swap-AB split-K weight-streaming GEMM (gemm_smallm.cu)
             L = _lib.lib()
             L.ps_gemm_smallm_splits.restype = ctypes.c_int

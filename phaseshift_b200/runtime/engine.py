@@ -69,11 +69,9 @@ class PageAllocator:
 
 class Engine:
     def __init__(self, weights: EngineWeights, device, state_cfg: StateConfig, backend: str = "auto", tp=None,
-                 use_graphs: bool = True, batch_shadow: bool = False, calibrate: bool = True):
-        """``batch_shadow``: keep a resident bf16 expansion of every projection (2 bytes per weight on top of the
-        block-quantised copy) so steps with two or more rows run the tensor-core GEMM on it: a batched decode step
-        then costs about one pass over the bf16 weights whatever the number of rows, instead of one pass over the
-        block codes per row.  Single-row decode and Exact verification keep streaming the quantised weights."""
+                 use_graphs: bool = True, calibrate: bool = True):
+        """``calibrate``: fix the activation scales of the block-scaled tensor-core projections from one forward
+        (once per weight set; see calibrate_act_scales)."""
         self.cfg: Qwen35Config = weights.cfg
         self.device = torch.device(device)
         if backend == "auto":
@@ -92,7 +90,6 @@ class Engine:
         self.tp = tp
         if tp is not None and hasattr(self.ops, "status"):
             tp.status_word = self.ops.status      # the transport's kernels report bounded-wait failures here
-        self.shadow_bytes = weights.make_shadows() if (batch_shadow and backend == "cuda") else 0
         self.alloc = PageAllocator(self.state.num_pages, state_cfg.max_slots)
         self.seqs: Dict[int, Sequence_] = {}
         self.batches: Dict[int, StepBatch] = {}
@@ -107,8 +104,11 @@ class Engine:
         self.h_status = torch.zeros(2, dtype=torch.int32, pin_memory=(self.device.type == "cuda"))
         self.steps = 0
         self.act_scales_calibrated = False
-        if calibrate and backend == "cuda" and getattr(weights, "layout", "") in ("tc", "both"):
+        # once per weight set: a second engine over the same weights must run the same arithmetic as the first
+        if (calibrate and backend == "cuda" and getattr(weights, "layout", "") in ("tc", "both")
+                and not getattr(weights, "act_scales_calibrated", False)):
             self.calibrate_act_scales()
+            weights.act_scales_calibrated = True
 
     def set_uniform_arithmetic(self, on: bool) -> None:
         """Speculative decoding needs every step of a sequence -- single-row decode, multi-row verification, the

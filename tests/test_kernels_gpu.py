@@ -540,30 +540,31 @@ def test_radix_topk_matches_sort_and_breaks_ties_by_id():
         assert got == sorted(allowed, key=lambda a: (-float(logits[r, a]), a))
 
 
-def test_batched_steps_on_resident_bf16_weights_match_streaming():
-    """With batch_shadow the 2..8-row steps run the tensor-core GEMM on resident bf16 weights; results must agree
-    with the streaming path within bf16 rounding, and single-row decode must be unaffected (bit-identical)."""
+def test_batched_steps_agree_with_single_row_arithmetic():
+    """A 3-row decode batch (tensor-core kernels: block-scaled for nvfp4, swap-AB bf16 GEMM for bf16 weights) gives
+    logits close to what three single-row steps give, and engines over one weight set decode identically."""
     from phaseshift_b200.runtime.engine import Engine
     cfg = tiny_config()
     hf = random_hf_weights(cfg, seed=0)
     prompt = torch.randint(0, cfg.vocab_size, (19,), generator=torch.Generator().manual_seed(3)).tolist()
     for preset in ("nvfp4", "bf16"):
-        outs = []
-        for shadow in (False, True):
-            ew = build_engine_weights(cfg, lambda n: hf[n], preset, "cuda")
-            eng = Engine(ew, "cuda", StateConfig(max_slots=4, max_seq_len=96), batch_shadow=shadow)
-            assert (eng.shadow_bytes > 0) == shadow
-            single = eng.generate(prompt, 6, prefill_chunk=64)
-            seqs = [eng.open_sequence() for _ in range(3)]
-            for i, s in enumerate(seqs):
-                eng.prefill(s, prompt[i:], 64)
-            rows = [SeqRows(s.slot, s.position, [5 + i], (0,)) for i, s in enumerate(seqs)]
-            _, out = eng.step(rows, seqs, want_logits=True, commit=False)
-            outs.append((single, out.logits[:3].float().clone()))
-            for s in seqs:
-                eng.close_sequence(s)
-        assert outs[0][0] == outs[1][0], "single-row decode must not depend on the shadow copy"
-        assert _rel_err(outs[1][1], outs[0][1]) < 3e-2, preset
+        ew = build_engine_weights(cfg, lambda n: hf[n], preset, "cuda")
+        eng = Engine(ew, "cuda", StateConfig(max_slots=4, max_seq_len=96))
+        single = eng.generate(prompt, 6, prefill_chunk=64)
+        assert Engine(ew, "cuda", StateConfig(max_slots=4, max_seq_len=96)).generate(prompt, 6, prefill_chunk=64) == single
+        seqs = [eng.open_sequence() for _ in range(3)]
+        for i, s in enumerate(seqs):
+            eng.prefill(s, prompt[i:], 64)
+        rows = [SeqRows(s.slot, s.position, [5 + i], (0,)) for i, s in enumerate(seqs)]
+        _, out = eng.step(rows, seqs, want_logits=True, commit=False)
+        batch = out.logits[:3].float().clone()
+        one = []
+        for i, s in enumerate(seqs):
+            _, o1 = eng.step([rows[i]], [s], want_logits=True, commit=False)
+            one.append(o1.logits[0].float().clone())
+        for s in seqs:
+            eng.close_sequence(s)
+        assert _rel_err(batch, torch.stack(one)) < 3e-2, preset
 
 
 @pytest.mark.parametrize("shape", [(3, 5120, 5120), (8, 1024, 17408), (64, 34816, 512), (128, 600, 256)])
@@ -652,5 +653,5 @@ def test_decode_batches_beyond_eight_rows_replay_from_graphs():
             hist.append(list(toks))
         outs.append(hist)
         if graphs:
-            assert any(k // 4096 == 16 for k in eng.graphs), "the 12-row decode batch must have been captured (bucket 16)"
+            assert any((k // 2) // 4096 == 16 for k in eng.graphs), "the 12-row decode batch must have been captured (bucket 16)"
     assert outs[0] == outs[1]
