@@ -74,7 +74,19 @@ class DFlash2SpecDecoder:
         self.stats = {"rounds": 0, "accepted": 0, "proposed": 0, "emitted": 0, "plain_steps": 0}
 
     @staticmethod
-    def from_dir(engine, drafter_dir, num_drafts: int = 7, ngram_tail: int = 0, ngram_n: int = 0):
+    def from_dir(engine, drafter_dir, num_drafts: int = 7, ngram_tail: int = 0, ngram_n: int = 0, native: Optional[bool] = None,
+                 fmt: str = "nvfp4"):
+        """``native`` (default: whenever the engine runs the CUDA op set and the drafter's shape fits the kernels):
+        the drafter on the engine's own kernels (native.py) instead of torch tensor ops."""
+        if native is None:
+            native = engine.device.type == "cuda" and hasattr(engine.ops, "linear_bs")
+            if native:
+                c = DFlash2Config.from_dir(drafter_dir)
+                native = c.head_dim == 128 and c.num_attention_heads // c.num_key_value_heads <= 4
+        if native:
+            from .native import DFlash2NativeDrafter
+            return DFlash2SpecDecoder(engine, DFlash2NativeDrafter.from_dir(drafter_dir, engine, fmt), num_drafts, ngram_tail,
+                                      ngram_n)
         dt = torch.float32 if engine.device.type == "cpu" else torch.bfloat16
         return DFlash2SpecDecoder(engine, DFlash2Drafter.from_dir(drafter_dir, engine.device, dt), num_drafts, ngram_tail,
                                   ngram_n)
@@ -90,7 +102,10 @@ class DFlash2SpecDecoder:
 
     def _append_taps(self, out, n_rows: int, pos_start: int, tokens: Sequence[int]) -> None:
         taps = [out.taps[l][:n_rows] for l in self.taps]
-        if getattr(self.drafter, "wants_tokens", False):       # e.g. the MTP head pairs hidden j with token j + 1
+        if getattr(self.drafter, "native", False):              # reads the taps side by side, as the step wrote them
+            cat = out.taps_cat[:n_rows] if getattr(out, "taps_cat", None) is not None else None
+            self.drafter.append_context(taps, pos_start, cat=cat)
+        elif getattr(self.drafter, "wants_tokens", False):     # e.g. the MTP head pairs hidden j with token j + 1
             self.drafter.append_context(taps, pos_start, tokens=list(tokens[:n_rows]))
         else:
             self.drafter.append_context(taps, pos_start)
@@ -121,14 +136,27 @@ class DFlash2SpecDecoder:
             self._append_taps(out, 1, pos0, [anchor])
             self.stats["plain_steps"] += 1
             return [toks[0]]
-        drafts = self.drafter.propose(anchor, k, self._embed, self._lm_head, pos0)
-        if self.ngram_tail and self.ngram_n:
-            drafts = drafts + self.rt.ngram_tail(generated + [anchor] + drafts, self.ngram_n,
-                                                 min(self.ngram_tail, max(0, remaining - 1 - len(drafts))))
-        rows = [anchor] + drafts
-        n = len(rows)
-        toks, out = eng.step([SeqRows(s.slot, pos0, rows, tuple(range(n)), sample_index=len(generated) + 1, **samp)], [s],
-                             commit=False, tap_layers=self.taps, gdn_log=self.logs, gdn_to_alt=True, exact=self.verify_exact)
+        on_device = hasattr(self.drafter, "propose_device") and not (self.ngram_tail and self.ngram_n)
+        if on_device:
+            # the drafts never visit the host before verification: the verify step reads them from the device and
+            # brings them back together with its samples -- one host synchronisation per round
+            d_dev = self.drafter.propose_device(anchor, k, pos0)
+            toks, out = eng.step([SeqRows(s.slot, pos0, [anchor] + [0] * k, tuple(range(k + 1)),
+                                          sample_index=len(generated) + 1, **samp)], [s], commit=False, tap_layers=self.taps,
+                                 gdn_log=self.logs, gdn_to_alt=True, exact=self.verify_exact, device_ids=(1, d_dev),
+                                 read_back=d_dev)
+            drafts = list(out.read_back)
+            rows = [anchor] + drafts
+        else:
+            drafts = self.drafter.propose(anchor, k, self._embed, self._lm_head, pos0)
+            if self.ngram_tail and self.ngram_n:
+                drafts = drafts + self.rt.ngram_tail(generated + [anchor] + drafts, self.ngram_n,
+                                                     min(self.ngram_tail, max(0, remaining - 1 - len(drafts))))
+            rows = [anchor] + drafts
+            n = len(rows)
+            toks, out = eng.step([SeqRows(s.slot, pos0, rows, tuple(range(n)), sample_index=len(generated) + 1, **samp)], [s],
+                                 commit=False, tap_layers=self.taps, gdn_log=self.logs, gdn_to_alt=True,
+                                 exact=self.verify_exact)
         accepted, nxt, full = self.rt.spec_greedy_accept(drafts, toks)
         keep = accepted + 1                                  # anchor + accepted drafts are now part of the sequence
         st = eng.state

@@ -335,9 +335,8 @@ class DFlash2Drafter:
                 for _ in range(2):
                     run()
             cur.wait_stream(side)
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                out = run()
+            from ...utils.graphs import capture as capture_graph
+            graph, out = capture_graph(self.device, run)
             st = (graph, ids, base, pos, out)
             self._graphs[k] = st
         graph, ids, base, pos, out = st

@@ -22,10 +22,12 @@ FUSED_BA_MAX_ROWS = 8
 
 
 class StepOutput:
-    __slots__ = ("tokens", "logits", "hidden", "taps")
+    __slots__ = ("tokens", "logits", "hidden", "taps", "taps_cat", "read_back")
 
-    def __init__(self, tokens, logits, hidden, taps):
+    def __init__(self, tokens, logits, hidden, taps, taps_cat=None):
         self.tokens, self.logits, self.hidden, self.taps = tokens, logits, hidden, taps
+        self.taps_cat = taps_cat        # the tapped hidden states side by side, [rows, taps * H] (taps are views of it)
+        self.read_back = None
 
 
 class Qwen35Runner:
@@ -94,6 +96,11 @@ class Qwen35Runner:
         else:
             x = ops.embed(b, rows, w.embed, st.status)
         taps = {}
+        taps_cat = None
+        if tap_layers and hasattr(ops, "buf"):
+            # one buffer for all taps: a block drafter reads them side by side as its fc input
+            taps_cat = ops.buf("taps_cat", rows, len(tap_layers) * cfg.hidden_size)
+        tap_order = {li: j for j, li in enumerate(tap_layers)}
         from .weights import P as _P
         for li, L in enumerate(w.layers):
             m = L.mixer
@@ -140,7 +147,11 @@ class Qwen35Runner:
             xname = "x_a" if (li & 1) == 0 else "x_b"
             x, x_ssq = self._row_parallel(act, L.down, r, xname, rows, self._first_proj(li + 1))
             if li in tap_layers:
-                taps[li] = x if not hasattr(ops, "buf") else ops.buf(f"tap{li}", rows, x.shape[1]).copy_(x)
+                if taps_cat is None:
+                    taps[li] = x
+                else:
+                    H = x.shape[1]
+                    taps[li] = taps_cat[:, tap_order[li] * H:(tap_order[li] + 1) * H].copy_(x)
         tokens = logits = hidden = None
         if n_out > 0:
             if b.identity_out and self.use_ssq:
@@ -152,4 +163,4 @@ class Qwen35Runner:
                                 **({"ssq_in": h_ssq} if self.use_ssq else {}))
             if sample:
                 tokens = ops.sample(logits, b, n_out, mask=mask, mask_active=mask_active, status=st.status)
-        return StepOutput(tokens, logits, hidden, taps)
+        return StepOutput(tokens, logits, hidden, taps, taps_cat)

@@ -17,6 +17,8 @@ from typing import Dict, List, Optional, Sequence
 
 import torch
 
+from ..utils.graphs import capture as capture_graph
+
 from ..models.qwen35.config import Qwen35Config
 from ..models.qwen35.model import Qwen35Runner, StepOutput
 from ..models.qwen35.weights import EngineWeights, TpGeometry
@@ -25,6 +27,7 @@ from .state import ModelState, StateConfig
 
 GRAPH_MAX_ROWS = 8
 GRAPH_MAX_DECODE_ROWS = 64      # pure decode batches (one row per sequence) are also replayed from graphs
+GRAPH_MAX_VARIANT_ROWS = 16     # tapped / logged steps (speculative verification) replayed from graphs of their own
 
 
 class SequenceError(RuntimeError):
@@ -102,6 +105,9 @@ class Engine:
             self.use_graphs = False
         self.h_tokens = torch.zeros(2048, dtype=torch.int32, pin_memory=(self.device.type == "cuda"))
         self.h_status = torch.zeros(2, dtype=torch.int32, pin_memory=(self.device.type == "cuda"))
+        self.h_extra = torch.zeros(64, dtype=torch.int32, pin_memory=(self.device.type == "cuda"))
+        self.graph_variants = True      # verification / tapped steps replay captured graphs too
+        self.graph_refs: Dict[object, object] = {}
         self.steps = 0
         self.act_scales_calibrated = False
         # once per weight set: a second engine over the same weights must run the same arithmetic as the first
@@ -120,6 +126,7 @@ class Engine:
             self.ops.force_tc = on
             self.graphs.clear()
             self.graph_out.clear()
+            self.graph_refs.clear()
             self.launches_per_graph.clear()
 
     # ------------------------------------------------------------------ activation scales (tensor-core layout)
@@ -240,8 +247,14 @@ class Engine:
 
     def step(self, rows: Sequence[SeqRows], seq_objs: Sequence[Sequence_], *, commit: bool = True,
              tap_layers: Sequence[int] = (), gdn_log=None, gdn_to_alt: bool = False, mask=None,
-             mask_active=None, want_logits: bool = False, sample: bool = True, exact: bool = False):
+             mask_active=None, want_logits: bool = False, sample: bool = True, exact: bool = False,
+             device_ids=None, read_back: Optional[torch.Tensor] = None):
         """Run one step.  Returns (tokens list[int] per output row, StepOutput).
+
+        ``device_ids`` = (first row, int32 device tensor): token ids of those rows are taken from the device tensor
+        instead of ``rows`` (speculative drafts that were never read back); ``read_back``: a small int32 device tensor
+        copied to the host together with the sampled tokens (``StepOutput.read_back``), so that the step stays the
+        round's only host synchronisation.
 
         ``exact``: compute every row with single-row-decode arithmetic (the reference's VerifyNumericMode::Exact,
         include/phaseshift/runtime/execution/execution_types.h:6-27): projections stay on the batch-invariant
@@ -268,7 +281,7 @@ class Engine:
             raise
         toks, out, status = self._execute(rows, n_rows, n_out, bucket, b, tap_layers=tap_layers, gdn_log=gdn_log,
                                           gdn_to_alt=gdn_to_alt, mask=mask, mask_active=mask_active, sample=sample,
-                                          exact=exact)
+                                          exact=exact, device_ids=device_ids, read_back=read_back)
         if status != 0:
             for s in seq_objs:
                 s.poisoned = True
@@ -278,17 +291,29 @@ class Engine:
                 s.position = r.pos_start + len(r.token_ids)
         return toks, out
 
-    def _run_graph(self, bucket: int, b: StepBatch, n_out: int) -> StepOutput:
+    def _run_graph(self, bucket: int, b: StepBatch, n_out: int, variant=None) -> StepOutput:
+        """``variant`` = (tap layers, GDN log dict or None, to_alt, exact): steps that tap hidden states or log the
+        recurrent updates get graphs of their own (the tap and log tensors are fixed buffers, so the capture stays
+        valid; Exact mode only changes which kernels the host picks, which the capture bakes in)."""
         key = (bucket * 4096 + n_out) * 2 + (1 if b.identity_out else 0)
+        kw = {}
+        if variant is not None:
+            taps, log, to_alt, exact = variant
+            key = (key, tuple(taps), id(log) if log is not None else 0, to_alt, exact)
+            kw = dict(tap_layers=taps, gdn_log=log, gdn_to_alt=to_alt)
         g = self.graphs.get(key)
         if g is None:
-            # warm up once outside capture (allocates workspaces, sets kernel attributes)
-            self.runner.forward(b, bucket, n_out)
-            torch.cuda.current_stream().synchronize()
-            g = torch.cuda.CUDAGraph()
-            l0 = self.ops.launches
-            with torch.cuda.graph(g, stream=torch.cuda.Stream(self.device)):
-                out = self.runner.forward(b, bucket, n_out)
+            self.ops.exact_rows = bool(variant[3]) if variant is not None else False
+            try:
+                # warm up once outside capture (allocates workspaces, sets kernel attributes)
+                self.runner.forward(b, bucket, n_out, **kw)
+                torch.cuda.current_stream().synchronize()
+                l0 = self.ops.launches
+                g, out = capture_graph(self.device, lambda: self.runner.forward(b, bucket, n_out, **kw))
+            finally:
+                self.ops.exact_rows = False
+            if variant is not None:
+                self.graph_refs[key] = variant[1]          # keeps the log tensors (and the id in the key) alive
             self.launches_per_graph[key] = self.ops.launches - l0
             self.graphs[key] = g
             self.graph_out[key] = out
@@ -329,7 +354,7 @@ class Engine:
                              gdn_to_alt=gdn_to_alt, mask=mask, mask_active=mask_active, sample=sample, exact=False)
 
     def _execute(self, rows, n_rows: int, n_out: int, bucket: int, b: StepBatch, *, tap_layers, gdn_log, gdn_to_alt,
-                 mask, mask_active, sample: bool, exact: bool):
+                 mask, mask_active, sample: bool, exact: bool, device_ids=None, read_back=None):
         """Fill and upload the batch descriptor, run the forward (graph replay for plain decode-sized steps, eager
         otherwise), read back sampled ids and every device status word with one stream synchronisation.  Returns
         (tokens, StepOutput, status); a non-zero status has already been cleared on the device (together with any
@@ -340,10 +365,19 @@ class Engine:
         plain = not tap_layers and gdn_log is None and not gdn_to_alt and mask is None and sample and not exact
         decode_batch = bucket <= GRAPH_MAX_DECODE_ROWS and all(len(r.token_ids) == 1 for r in rows)
         use_graph = self.use_graphs and plain and (bucket <= GRAPH_MAX_ROWS or decode_batch)
+        # tapped / logged / Exact steps (speculative verification, tapped decode): graphs of their own
+        variant = None
+        if (self.use_graphs and self.graph_variants and not plain and mask is None and sample
+                and bucket <= GRAPH_MAX_VARIANT_ROWS):
+            variant = (tuple(tap_layers), gdn_log, bool(gdn_to_alt), bool(exact))
+            use_graph = True
         b.graph_static = use_graph
         b.upload()
+        if device_ids is not None:
+            r0, t = device_ids
+            b.ids[r0:r0 + t.numel()].copy_(t, non_blocking=True)
         if use_graph:
-            out = self._run_graph(bucket, b, n_out)
+            out = self._run_graph(bucket, b, n_out, variant)
         else:
             self.ops.exact_rows = exact
             try:
@@ -360,7 +394,11 @@ class Engine:
             self.h_status[0:1].copy_(self.state.status, non_blocking=True)
             if ops_status is not None:
                 self.h_status[1:2].copy_(ops_status, non_blocking=True)
+            if read_back is not None:
+                self.h_extra[:read_back.numel()].copy_(read_back, non_blocking=True)
             torch.cuda.current_stream().synchronize()
+            if read_back is not None:
+                out.read_back = self.h_extra[:read_back.numel()].tolist()
             status = int(self.h_status[0]) or int(self.h_status[1])
             if out.tokens is not None:
                 toks = self.h_tokens[:n_out].tolist()
@@ -370,6 +408,8 @@ class Engine:
                 status = int(ops_status[0])
             if out.tokens is not None:
                 toks = out.tokens[:n_out].tolist()
+            if read_back is not None:
+                out.read_back = read_back.tolist()
         self.steps += 1
         if status != 0:
             self.state.status.zero_()

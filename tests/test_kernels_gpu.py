@@ -70,6 +70,7 @@ def test_linear_small_rows_are_batch_invariant():
     """Row r of an M=8 launch is bit-identical to the same row in an M=1 launch (Exact verify property)."""
     cfg = tiny_config()
     cu, _ = _ops(cfg)
+    cu.exact_rows = True        # Exact mode: bf16 weights stay on the streaming kernel for every row count
     g = torch.Generator(device="cuda").manual_seed(9)
     for fmt in ("bf16", "nvfp4", "mxfp8"):
         w = torch.randn(640, 5120, device="cuda", generator=g) * 0.02
@@ -362,6 +363,7 @@ def test_stream_gemv_shapes_and_row_invariance(fmt):
     """Odd N / K tails, K larger than one staging pass allows for M=8, and row invariance across M."""
     cfg = tiny_config()
     cu, _ = _ops(cfg)
+    cu.exact_rows = True        # keep bf16 weights on the streaming kernel (Fast mode batches them on the tensor cores)
     g = torch.Generator(device="cuda").manual_seed(21)
     for (N, K) in [(1030, 5120), (510, 17408), (98, 2560), (7, 96)]:
         w = torch.randn(N, K, device="cuda", generator=g) * 0.02
@@ -549,18 +551,20 @@ def test_batched_steps_agree_with_single_row_arithmetic():
     prompt = torch.randint(0, cfg.vocab_size, (19,), generator=torch.Generator().manual_seed(3)).tolist()
     for preset in ("nvfp4", "bf16"):
         ew = build_engine_weights(cfg, lambda n: hf[n], preset, "cuda")
-        eng = Engine(ew, "cuda", StateConfig(max_slots=4, max_seq_len=96))
+        eng = Engine(ew, "cuda", StateConfig(max_slots=8, max_seq_len=96))
         single = eng.generate(prompt, 6, prefill_chunk=64)
         assert Engine(ew, "cuda", StateConfig(max_slots=4, max_seq_len=96)).generate(prompt, 6, prefill_chunk=64) == single
-        seqs = [eng.open_sequence() for _ in range(3)]
+        # a step advances the recurrent state even when the position is not committed: the batched step and the
+        # single-row steps get sequences of their own over the same prompts
+        seqs = [eng.open_sequence() for _ in range(6)]
         for i, s in enumerate(seqs):
-            eng.prefill(s, prompt[i:], 64)
-        rows = [SeqRows(s.slot, s.position, [5 + i], (0,)) for i, s in enumerate(seqs)]
-        _, out = eng.step(rows, seqs, want_logits=True, commit=False)
+            eng.prefill(s, prompt[i % 3:], 64)
+        rows = [SeqRows(s.slot, s.position, [5 + i % 3], (0,)) for i, s in enumerate(seqs)]
+        _, out = eng.step(rows[:3], seqs[:3], want_logits=True, commit=False)
         batch = out.logits[:3].float().clone()
         one = []
-        for i, s in enumerate(seqs):
-            _, o1 = eng.step([rows[i]], [s], want_logits=True, commit=False)
+        for i in range(3, 6):
+            _, o1 = eng.step([rows[i]], [seqs[i]], want_logits=True, commit=False)
             one.append(o1.logits[0].float().clone())
         for s in seqs:
             eng.close_sequence(s)
