@@ -5,7 +5,7 @@
 //   ps_dfl_rmsnorm        direct-weight RMSNorm, normalised value rounded to bf16 before the weight multiply
 //   ps_dfl_conv_apply     grouped dynamic causal conv (kernel 2, block-local): prepare / finish phase (+ residual)
 //   ps_dfl_headnorm_rope  per-head RMSNorm (same rounding) + full-width NeoX RoPE with bf16-rounded cos / sin
-//   ps_dfl_ring_attention non-causal sliding-window GQA attention over [ring context || block rows]
+//   ps_dfl_ring_attention non-causal sliding-window GQA attention over [ring context || block rows], split over keys
 //   ps_dfl_kv_ring_append per-layer k-norm + RoPE of the context keys, scatter of K / V into slot pos % window
 //   ps_dfl_feature_concat the tapped target hidden states side by side: [rows, taps * H]
 //   ps_dfl_noise_ids      block token ids and positions from a device control word: anchor, then K mask ids
@@ -138,94 +138,162 @@ __global__ void __launch_bounds__(128) dfl_kv_ring_append_kernel(const __nv_bflo
     if (l == 0 && h == 0 && lane == 0) ring_pos[slot] = pos;
 }
 
-// ---- ring GQA attention: one CTA per (block row t, kv head); warp w serves query head kvh * G + w (G <= 4).
-// Keys: ring slots with ring_pos >= 0, then the block's own rows; mask |pos_q - pos_k| < window; non-causal.
-constexpr int kDflKeys = 64, kDflPitch = 136;      // 64-key tiles, row pitch in bf16 (272 B: conflict-free column reads)
-__global__ void __launch_bounds__(128) dfl_ring_attention_kernel(const __nv_bfloat16* __restrict__ q, int ldq,
-                                                                 const __nv_bfloat16* __restrict__ kb, const __nv_bfloat16* __restrict__ vb, int ldkv,
-                                                                 const __nv_bfloat16* __restrict__ k_ring, const __nv_bfloat16* __restrict__ v_ring,
-                                                                 const int* __restrict__ ring_pos, const int* __restrict__ pos,
-                                                                 int T, int window, int q_heads, int kv_heads, float scale,
-                                                                 __nv_bfloat16* __restrict__ out, int ldo) {
+// ---- ring GQA attention, split over the keys.
+// Keys = the `window` ring slots followed by the block's own T rows; mask: slot filled and |pos_q - pos_k| < window;
+// non-causal.  Launch 1: one CTA per (64-key tile, kv head) scores ALL query rows of that kv head (T rows x G heads
+// <= 64) against its tile -- every K / V byte is read once -- and writes an unnormalised partial (o, max, sum) per
+// row.  Launch 2 merges the partials of a (row, head).  Register-blocked fp32 FMA: the whole op is ~0.3 GFLOP.
+constexpr int kDflKT = 64;            // keys per CTA
+constexpr int kDflQMax = 64;          // query rows (T * G) per kv head
+constexpr int kDflKPitch = 132;       // bf16 per Q / K row in shared memory: 8-byte aligned, conflict-free 8-byte column reads
+constexpr int kDflVPitch = 136;       // bf16 per V row: 16-byte aligned
+constexpr int kDflPPitch = 65;        // fp32 per probability row
+constexpr int kDflPartLd = 132;       // fp32 per partial row: 128 outputs, running max, running sum, 2 pad
+constexpr int kDflAttnSmem = (2 * kDflKT * kDflKPitch + kDflKT * kDflVPitch) * 2 + kDflQMax * kDflPPitch * 4 + 2 * 64 * 4;
+
+__device__ __forceinline__ void unpack4(const uint2 u, float (&f)[4]) {
+    const float2 a = bf16x2_bits_to_f32x2(u.x), b = bf16x2_bits_to_f32x2(u.y);
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+}
+
+template <int QR>      // query rows per thread: 2 serves up to 32 rows, 4 up to 64
+__global__ void __launch_bounds__(256) dfl_ring_attention_split_kernel(const __nv_bfloat16* __restrict__ q, int ldq,
+                                                                       const __nv_bfloat16* __restrict__ kb, const __nv_bfloat16* __restrict__ vb, int ldkv,
+                                                                       const __nv_bfloat16* __restrict__ k_ring, const __nv_bfloat16* __restrict__ v_ring,
+                                                                       const int* __restrict__ ring_pos, const int* __restrict__ pos,
+                                                                       int T, int window, int G, int kv_heads, float scale,
+                                                                       float* __restrict__ part) {
     constexpr int D = 128;
-    __shared__ __align__(16) __nv_bfloat16 sK[kDflKeys * kDflPitch], sV[kDflKeys * kDflPitch];
-    __shared__ float sQ[4][D];
-    __shared__ int sPos[kDflKeys];
-    const int t = blockIdx.x, kvh = blockIdx.y;
-    const int G = q_heads / kv_heads;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int kvf = kv_heads * D;
-    const int pq = pos[t];
-    if (warp < G)
-        for (int i = lane; i < D; i += 32) sQ[warp][i] = bf16_to_f32(q[(size_t)t * ldq + (kvh * G + warp) * D + i]) * scale;
-    float m_run = -3.0e38f, l_run = 0.f, o[4] = {0.f, 0.f, 0.f, 0.f};      // lane owns dims 4 lane .. 4 lane + 3
-    const int total = window + T;
-    for (int k0 = 0; k0 < total; k0 += kDflKeys) {
-        __syncthreads();
-        // stage a tile of keys / values (16 bytes per thread and row piece) and their positions
-        for (int i = threadIdx.x; i < kDflKeys * (D / 8); i += 128) {
-            const int r = i / (D / 8), c = i - r * (D / 8);
-            const int key = k0 + r;
-            uint4 kvv = make_uint4(0, 0, 0, 0), vvv = kvv;
-            if (key < window) {
-                kvv = *reinterpret_cast<const uint4*>(k_ring + (size_t)key * kvf + kvh * D + c * 8);
-                vvv = *reinterpret_cast<const uint4*>(v_ring + (size_t)key * kvf + kvh * D + c * 8);
-            } else if (key < total) {
-                kvv = *reinterpret_cast<const uint4*>(kb + (size_t)(key - window) * ldkv + kvh * D + c * 8);
-                vvv = *reinterpret_cast<const uint4*>(vb + (size_t)(key - window) * ldkv + kvh * D + c * 8);
-            }
-            *reinterpret_cast<uint4*>(sK + r * kDflPitch + c * 8) = kvv;
-            *reinterpret_cast<uint4*>(sV + r * kDflPitch + c * 8) = vvv;
-        }
-        if (threadIdx.x < kDflKeys) {
-            const int key = k0 + threadIdx.x;
-            sPos[threadIdx.x] = key < window ? ring_pos[key] : (key < total ? pos[key - window] : -1);
-        }
-        __syncthreads();
-        if (warp >= G) continue;
-        // scores of this warp's query head: lane handles keys lane and lane + 32 of the tile
-        float sc[2];
+    extern __shared__ __align__(16) unsigned char dfl_smem[];
+    __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(dfl_smem);
+    __nv_bfloat16* sK = sQ + kDflQMax * kDflKPitch;
+    __nv_bfloat16* sV = sK + kDflKT * kDflKPitch;
+    float* sP = reinterpret_cast<float*>(sV + kDflKT * kDflVPitch);
+    int* sPos = reinterpret_cast<int*>(sP + kDflQMax * kDflPPitch);
+    int* sQpos = sPos + 64;
+    const int split = blockIdx.x, kvh = blockIdx.y, tid = threadIdx.x;
+    const int kvf = kv_heads * D, Q = T * G, total = window + T, k0 = split * kDflKT;
+    // ---- stage Q (all rows of this kv head), the K / V tile and the positions
+    for (int i = tid; i < 16 * QR * (D / 4); i += 256) {
+        const int r = i / (D / 4), c = i - r * (D / 4);
+        uint2 v = make_uint2(0u, 0u);
+        if (r < Q) { const int t = r / G, g = r - t * G; v = *reinterpret_cast<const uint2*>(q + (size_t)t * ldq + (kvh * G + g) * D + c * 4); }
+        *reinterpret_cast<uint2*>(sQ + r * kDflKPitch + c * 4) = v;
+    }
+    for (int i = tid; i < kDflKT * (D / 4); i += 256) {
+        const int r = i / (D / 4), c = i - r * (D / 4), key = k0 + r;
+        uint2 v = make_uint2(0u, 0u);
+        if (key < window) v = *reinterpret_cast<const uint2*>(k_ring + (size_t)key * kvf + kvh * D + c * 4);
+        else if (key < total) v = *reinterpret_cast<const uint2*>(kb + (size_t)(key - window) * ldkv + kvh * D + c * 4);
+        *reinterpret_cast<uint2*>(sK + r * kDflKPitch + c * 4) = v;
+    }
+    for (int i = tid; i < kDflKT * (D / 8); i += 256) {
+        const int r = i / (D / 8), c = i - r * (D / 8), key = k0 + r;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (key < window) v = *reinterpret_cast<const uint4*>(v_ring + (size_t)key * kvf + kvh * D + c * 8);
+        else if (key < total) v = *reinterpret_cast<const uint4*>(vb + (size_t)(key - window) * ldkv + kvh * D + c * 8);
+        *reinterpret_cast<uint4*>(sV + r * kDflVPitch + c * 8) = v;
+    }
+    if (tid < kDflKT) {
+        const int key = k0 + tid;
+        sPos[tid] = key < window ? ring_pos[key] : (key < total ? pos[key - window] : -1);
+        sQpos[tid] = tid < Q ? pos[tid / G] : 0;
+    }
+    __syncthreads();
+    // ---- scores: thread (tq, tk) owns rows tq * QR + i and keys tk + 16 j
+    const int tq = tid >> 4, tk = tid & 15;
+    float acc[QR][4];
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            const int r = lane + 32 * u, kp = sPos[r];
+    for (int i = 0; i < QR; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+#pragma unroll 4
+    for (int c = 0; c < D / 4; ++c) {
+        float qf[QR][4], kf[4][4];
+#pragma unroll
+        for (int i = 0; i < QR; ++i) unpack4(*reinterpret_cast<const uint2*>(sQ + (tq * QR + i) * kDflKPitch + c * 4), qf[i]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) unpack4(*reinterpret_cast<const uint2*>(sK + (tk + 16 * j) * kDflKPitch + c * 4), kf[j]);
+#pragma unroll
+        for (int i = 0; i < QR; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                acc[i][j] += qf[i][0] * kf[j][0] + qf[i][1] * kf[j][1] + qf[i][2] * kf[j][2] + qf[i][3] * kf[j][3];
+    }
+    float* prt = part + ((size_t)split * kv_heads + kvh) * kDflQMax * kDflPartLd;
+#pragma unroll
+    for (int i = 0; i < QR; ++i) {
+        const int row = tq * QR + i, pq = sQpos[row];
+        float sc[4], mx = -3.0e38f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int kp = sPos[tk + 16 * j];
             const bool ok = kp >= 0 && abs(pq - kp) < window;
-            float acc = 0.f;
-            const __nv_bfloat16* kr = sK + r * kDflPitch;
-#pragma unroll 8
-            for (int d = 0; d < D; d += 2) {
-                const float2 kv2 = bf16x2_bits_to_f32x2(*reinterpret_cast<const uint32_t*>(kr + d));
-                acc += sQ[warp][d] * kv2.x + sQ[warp][d + 1] * kv2.y;
-            }
-            sc[u] = ok ? acc : -3.0e38f;
+            sc[j] = ok ? acc[i][j] * scale : -3.0e38f;
+            mx = fmaxf(mx, sc[j]);
         }
-        const float tmax = warp_max(fmaxf(sc[0], sc[1]));
-        if (tmax <= -3.0e38f) continue;                     // the whole tile is masked
-        const float m_new = fmaxf(m_run, tmax), corr = __expf(m_run - m_new);
-        float p[2];
 #pragma unroll
-        for (int u = 0; u < 2; ++u) p[u] = sc[u] > -3.0e38f ? __expf(sc[u] - m_new) : 0.f;
-        l_run = l_run * corr + warp_sum(p[0] + p[1]);
+        for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));     // the 16 lanes of one tq
+        float sum = 0.f;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) o[e] *= corr;
-        m_run = m_new;
+        for (int j = 0; j < 4; ++j) {
+            const float p = sc[j] > -3.0e38f ? __expf(sc[j] - mx) : 0.f;
+            sP[row * kDflPPitch + tk + 16 * j] = p;
+            sum += p;
+        }
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            for (int src = 0; src < 32; ++src) {
-                const float pk = __shfl_sync(0xffffffffu, p[u], src);
-                if (pk == 0.f) continue;
-                const __nv_bfloat16* vr = sV + (src + 32 * u) * kDflPitch + lane * 4;
-                const float2 v01 = bf16x2_bits_to_f32x2(*reinterpret_cast<const uint32_t*>(vr));
-                const float2 v23 = bf16x2_bits_to_f32x2(*reinterpret_cast<const uint32_t*>(vr + 2));
-                o[0] += pk * v01.x; o[1] += pk * v01.y; o[2] += pk * v23.x; o[3] += pk * v23.y;
-            }
+        for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if (tk == 0 && row < Q) { prt[(size_t)row * kDflPartLd + D] = mx; prt[(size_t)row * kDflPartLd + D + 1] = sum; }
+    }
+    __syncthreads();
+    // ---- partial outputs: thread (tq, tk) owns rows tq * QR + i and dims 8 tk .. 8 tk + 7
+    float o[QR][8];
+#pragma unroll
+    for (int i = 0; i < QR; ++i)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[i][e] = 0.f;
+#pragma unroll 4
+    for (int key = 0; key < kDflKT; ++key) {
+        const uint4 vv = *reinterpret_cast<const uint4*>(sV + key * kDflVPitch + tk * 8);
+        float vf[8];
+        { const float2 a = bf16x2_bits_to_f32x2(vv.x), b = bf16x2_bits_to_f32x2(vv.y), c2 = bf16x2_bits_to_f32x2(vv.z), d2 = bf16x2_bits_to_f32x2(vv.w);
+          vf[0] = a.x; vf[1] = a.y; vf[2] = b.x; vf[3] = b.y; vf[4] = c2.x; vf[5] = c2.y; vf[6] = d2.x; vf[7] = d2.y; }
+#pragma unroll
+        for (int i = 0; i < QR; ++i) {
+            const float p = sP[(tq * QR + i) * kDflPPitch + key];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[i][e] += p * vf[e];
         }
     }
-    if (warp < G) {
-        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-        __nv_bfloat16* od = out + (size_t)t * ldo + (kvh * G + warp) * D + lane * 4;
-        *reinterpret_cast<uint32_t*>(od) = f32x2_to_bf16x2_bits(o[0] * inv, o[1] * inv);
-        *reinterpret_cast<uint32_t*>(od + 2) = f32x2_to_bf16x2_bits(o[2] * inv, o[3] * inv);
+#pragma unroll
+    for (int i = 0; i < QR; ++i) {
+        const int row = tq * QR + i;
+        if (row >= Q) continue;
+        float4* dst = reinterpret_cast<float4*>(prt + (size_t)row * kDflPartLd + tk * 8);
+        dst[0] = make_float4(o[i][0], o[i][1], o[i][2], o[i][3]);
+        dst[1] = make_float4(o[i][4], o[i][5], o[i][6], o[i][7]);
     }
+}
+
+// merge the per-tile partials of one (block row, query head): grid T * q_heads, 128 threads (one per dim)
+__global__ void __launch_bounds__(128) dfl_ring_attention_merge_kernel(const float* __restrict__ part, int splits, int G, int kv_heads,
+                                                                       int q_heads, __nv_bfloat16* __restrict__ out, int ldo) {
+    constexpr int D = 128;
+    const int t = blockIdx.x / q_heads, h = blockIdx.x - t * q_heads;
+    const int kvh = h / G, row = t * G + (h - kvh * G), d = threadIdx.x;
+    const size_t stride = (size_t)kv_heads * kDflQMax * kDflPartLd;
+    const float* p0 = part + ((size_t)kvh * kDflQMax + row) * kDflPartLd;
+    float M = -3.0e38f;
+    for (int s2 = 0; s2 < splits; ++s2) M = fmaxf(M, p0[s2 * stride + D]);
+    float L = 0.f, acc = 0.f;
+    for (int s2 = 0; s2 < splits; ++s2) {
+        const float ms = p0[s2 * stride + D];
+        if (ms <= -3.0e38f) continue;
+        const float w = __expf(ms - M);
+        L += w * p0[s2 * stride + D + 1];
+        acc += w * p0[s2 * stride + d];
+    }
+    out[(size_t)t * ldo + h * D + d] = f32_to_bf16(L > 0.f ? acc / L : 0.f);
 }
 
 struct DflConcatArgs { const __nv_bfloat16* src[8]; int ld[8]; int n; };
@@ -318,14 +386,34 @@ PS_API int ps_dfl_kv_ring_append(const void* kv, int ld, int layers, int kv_head
     return PS_LAUNCH_CHECK();
 }
 
+// Rows of fp32 workspace (kDflPartLd = 132 floats each) the attention needs for T block rows over `window` slots.
+PS_API long long ps_dfl_ring_attention_workspace_floats(int T, int window, int kv_heads) {
+    const long long splits = (window + T + ps::kDflKT - 1) / ps::kDflKT;
+    return splits * kv_heads * ps::kDflQMax * ps::kDflPartLd;
+}
+
 PS_API int ps_dfl_ring_attention(const void* q, int ldq, const void* kb, const void* vb, int ldkv, const void* k_ring, const void* v_ring,
                                  const void* ring_pos, const void* pos, int T, int window, int q_heads, int kv_heads, int D, float scale,
-                                 void* out, int ldo, cudaStream_t stream) {
-    if (T <= 0 || D != 128 || q_heads % kv_heads || q_heads / kv_heads > 4 || (ldkv % 8) || (ldq % 2)) return (int)cudaErrorInvalidValue;
-    dim3 grid(T, kv_heads);
-    ps::dfl_ring_attention_kernel<<<grid, 128, 0, stream>>>((const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)kb, (const __nv_bfloat16*)vb, ldkv,
-                                                            (const __nv_bfloat16*)k_ring, (const __nv_bfloat16*)v_ring, (const int*)ring_pos,
-                                                            (const int*)pos, T, window, q_heads, kv_heads, scale, (__nv_bfloat16*)out, ldo);
+                                 void* out, int ldo, void* workspace, cudaStream_t stream) {
+    using namespace ps;
+    if (T <= 0 || D != 128 || q_heads % kv_heads || (ldkv % 8) || (ldq % 4) || workspace == nullptr) return (int)cudaErrorInvalidValue;
+    const int G = q_heads / kv_heads;
+    if (T * G > kDflQMax) return (int)cudaErrorInvalidValue;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(dfl_ring_attention_split_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDflAttnSmem);
+        cudaFuncSetAttribute(dfl_ring_attention_split_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDflAttnSmem);
+        attr_set = true;
+    }
+    const int splits = (window + T + kDflKT - 1) / kDflKT;
+    dim3 grid(splits, kv_heads);
+    if (T * G <= 32)
+        dfl_ring_attention_split_kernel<2><<<grid, 256, kDflAttnSmem, stream>>>((const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)kb, (const __nv_bfloat16*)vb, ldkv,
+            (const __nv_bfloat16*)k_ring, (const __nv_bfloat16*)v_ring, (const int*)ring_pos, (const int*)pos, T, window, G, kv_heads, scale, (float*)workspace);
+    else
+        dfl_ring_attention_split_kernel<4><<<grid, 256, kDflAttnSmem, stream>>>((const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)kb, (const __nv_bfloat16*)vb, ldkv,
+            (const __nv_bfloat16*)k_ring, (const __nv_bfloat16*)v_ring, (const int*)ring_pos, (const int*)pos, T, window, G, kv_heads, scale, (float*)workspace);
+    dfl_ring_attention_merge_kernel<<<T * q_heads, 128, 0, stream>>>((const float*)workspace, splits, G, kv_heads, q_heads, (__nv_bfloat16*)out, ldo);
     return PS_LAUNCH_CHECK();
 }
 

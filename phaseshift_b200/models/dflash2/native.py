@@ -41,7 +41,7 @@ class DFlash2NativeDrafter:
         if engine.device.type != "cuda" or not hasattr(engine.ops, "linear_bs"):
             raise ValueError("the native drafter needs an engine on the CUDA op set")
         c = cfg
-        if c.head_dim != 128 or c.num_attention_heads // c.num_key_value_heads > 4:
+        if c.head_dim != 128 or MAX_BLOCK_ROWS * (c.num_attention_heads // c.num_key_value_heads) > 64:
             raise ValueError("ring attention kernel: head_dim 128 and at most 4 query heads per KV head")
         self.cfg, self.eng, self.ops, self.device, self.fmt = cfg, engine, engine.ops, engine.device, fmt
         dev = self.device
@@ -60,8 +60,10 @@ class DFlash2NativeDrafter:
 
         self.fc = lin(weights["fc.weight"])
         self.fc_norm, self.final_norm = bf("fc_norm.weight"), bf("norm.weight")
-        # small, precision-sensitive projections stay bf16 (dynamic conv taps, selector projection)
-        self.hidden_projection = lin(weights["selector.hidden_projection.weight"], "bf16")
+        # small, precision-sensitive projections (dynamic conv taps, selector projection): 8-bit codes, still on the
+        # tensor-core kernel (one launch each)
+        small = "bf16" if fmt == "bf16" else "mxfp8"
+        self.hidden_projection = lin(weights["selector.hidden_projection.weight"], small)
         self.pred_cb, self.succ_cb = bf("selector.pred_codebook"), bf("selector.succ_codebook")
         self.layers = []
         kv_ctx, k_norms = [], []
@@ -74,8 +76,8 @@ class DFlash2NativeDrafter:
                 o=lin(weights[a + "o_proj.weight"]), q_norm=bf(a + "q_norm.weight"), k_norm=bf(a + "k_norm.weight"),
                 gate_up=lin(interleave(weights[p + "mlp.gate_proj.weight"], weights[p + "mlp.up_proj.weight"])),
                 down=lin(weights[p + "mlp.down_proj.weight"]),
-                attn_kproj=lin(weights[p + "attn_conv.kernel_projection.weight"], "bf16"),
-                mlp_kproj=lin(weights[p + "mlp_conv.kernel_projection.weight"], "bf16"),
+                attn_kproj=lin(weights[p + "attn_conv.kernel_projection.weight"], small),
+                mlp_kproj=lin(weights[p + "mlp_conv.kernel_projection.weight"], small),
                 attn_base=bf(p + "attn_conv.base_kernel"), mlp_base=bf(p + "mlp_conv.base_kernel"))
             self.layers.append(L)
             kv_ctx += [weights[a + "k_proj.weight"], weights[a + "v_proj.weight"]]
@@ -154,6 +156,12 @@ class DFlash2NativeDrafter:
         self.launches += 1
         return out
 
+    def _attn_workspace(self, T: int) -> torch.Tensor:
+        L = _lib.lib()
+        L.ps_dfl_ring_attention_workspace_floats.restype = ctypes.c_longlong
+        n = int(L.ps_dfl_ring_attention_workspace_floats(c_int(T), c_int(self.cfg.sliding_window), c_int(self.cfg.num_key_value_heads)))
+        return self.ops.buf("dfl_attn_part", n // 132, 132, torch.float32)
+
     # ------------------------------------------------------------------ context
     def target_feature(self, taps: Sequence[torch.Tensor], cat: Optional[torch.Tensor] = None) -> torch.Tensor:
         c = self.cfg
@@ -220,10 +228,12 @@ class DFlash2NativeDrafter:
                       ptr(L["k_norm"]), c_float(c.rms_norm_eps), ptr(self.pos), c_float(c.rope_theta), c_int(T), ptr(qkv),
                       c_int(qkv.stride(0)))
             att = ops.buf("dfl_att", T, qd)
+            part = self._attn_workspace(T)
             _lib.call("ps_dfl_ring_attention", ptr(qkv), c_int(qkv.stride(0)), ptr(qkv[:, qd:]), ptr(qkv[:, qd + kvd:]),
                       c_int(qkv.stride(0)), ptr(self.k_ring[l]), ptr(self.v_ring[l]), ptr(self.ring_pos), ptr(self.pos), c_int(T),
-                      c_int(c.sliding_window), c_int(hq), c_int(hkv), c_int(D), c_float(D ** -0.5), ptr(att), c_int(att.stride(0)))
-            self.launches += 2
+                      c_int(c.sliding_window), c_int(hq), c_int(hkv), c_int(D), c_float(D ** -0.5), ptr(att), c_int(att.stride(0)),
+                      ptr(part))
+            self.launches += 3
             o = self._linear(att, L["o"], "o")
             x = self._conv(o, dyn, L["attn_base"], 1, "x", residual=x, out=x)
             m = self._rms(x, L["post_norm"], "m")

@@ -417,9 +417,13 @@ class CudaOps:
         rows, vocab = logits.shape
         ids = self.buf("topk_ids", rows, k, torch.int32)
         vals = self.buf("topk_vals", rows, k, torch.float32)
+        L = _lib.lib()
+        L.ps_topk_workspace_bytes.restype = ctypes.c_longlong
+        need = int(L.ps_topk_workspace_bytes(c_int(vocab), c_int(rows), c_int(k)))
+        ws = self.buf("topk_ws", rows * k, need // (rows * k * 8), torch.int64)
         _lib.call("ps_topk", ptr(logits), c_ll(logits.stride(0)), c_int(vocab), c_int(rows), c_int(k), ptr(mask),
-                  c_int(mask.shape[1] if mask is not None else 0), ptr(ids), ptr(vals))
-        self.launches += 1
+                  c_int(mask.shape[1] if mask is not None else 0), ptr(ids), ptr(vals), ptr(ws), c_ll(need))
+        self.launches += 2
         return ids, vals
 
     def rmsnorm(self, x: torch.Tensor, w: torch.Tensor, eps: float, name: str, one_plus: bool = True,

@@ -94,11 +94,12 @@ def _attention_ref(q, kb, vb, k_ring, v_ring, ring_pos, pos, window, hq, hkv, D)
     return torch.einsum("hts,shd->thd", torch.softmax(s, -1), V).reshape(T, -1)
 
 
+@pytest.mark.parametrize("T", [1, 8, 16])
 @pytest.mark.parametrize("fill", [0, 17, 200])
-def test_ring_attention_matches_torch(fill):
+def test_ring_attention_matches_torch(fill, T):
     L = _lib()
     g = _gen(5 + fill)
-    T, hq, hkv, D, W = 8, 8, 2, 128, 128
+    hq, hkv, D, W = 8, 2, 128, 128
     qd, kvd = hq * D, hkv * D
     qkv = torch.randn(T, qd + 2 * kvd, device="cuda", generator=g).to(torch.bfloat16)
     k_ring = torch.randn(W, kvd, device="cuda", generator=g).to(torch.bfloat16)
@@ -108,9 +109,12 @@ def test_ring_attention_matches_torch(fill):
         ring_pos[p % W] = p
     pos = torch.arange(fill, fill + T, device="cuda", dtype=torch.int32)
     out = torch.empty(T, qd, device="cuda", dtype=torch.bfloat16)
+    L.lib().ps_dfl_ring_attention_workspace_floats.restype = ctypes.c_longlong
+    n_ws = int(L.lib().ps_dfl_ring_attention_workspace_floats(L.c_int(T), L.c_int(W), L.c_int(hkv)))
+    ws = torch.full((n_ws,), float("nan"), device="cuda")
     L.call("ps_dfl_ring_attention", L.ptr(qkv), L.c_int(qkv.stride(0)), L.ptr(qkv[:, qd:]), L.ptr(qkv[:, qd + kvd:]),
            L.c_int(qkv.stride(0)), L.ptr(k_ring), L.ptr(v_ring), L.ptr(ring_pos), L.ptr(pos), L.c_int(T), L.c_int(W), L.c_int(hq),
-           L.c_int(hkv), L.c_int(D), L.c_float(D ** -0.5), L.ptr(out), L.c_int(qd))
+           L.c_int(hkv), L.c_int(D), L.c_float(D ** -0.5), L.ptr(out), L.c_int(qd), L.ptr(ws))
     ref = _attention_ref(qkv[:, :qd], qkv[:, qd:qd + kvd], qkv[:, qd + kvd:], k_ring, v_ring, ring_pos, pos, W, hq, hkv, D)
     assert _rel_err(out, ref) < 6e-3
 
