@@ -3,6 +3,7 @@
 // ([anchor, MASK x K]) against a ring of up to `window` committed context rows per layer.
 //
 //   ps_dfl_rmsnorm        direct-weight RMSNorm, normalised value rounded to bf16 before the weight multiply
+//   ps_dfl_norm_proj4     fused RMSNorm + dynamic-kernel projection + conv prepare (or + selector projection)
 //   ps_dfl_conv_apply     grouped dynamic causal conv (kernel 2, block-local): prepare / finish phase (+ residual)
 //   ps_dfl_headnorm_rope  per-head RMSNorm (same rounding) + full-width NeoX RoPE with bf16-rounded cos / sin
 //   ps_dfl_ring_attention non-causal sliding-window GQA attention over [ring context || block rows], split over keys
@@ -73,6 +74,109 @@ __global__ void __launch_bounds__(256) dfl_conv_apply_kernel(const __nv_bfloat16
     *reinterpret_cast<uint32_t*>(out + (size_t)t * ldo + f) = f32x2_to_bf16x2_bits(ox, oy);
 }
 
+// ---- fused: direct RMSNorm -> tiny projection (4 C outputs per row) -> either the conv "prepare" phase or the
+// normalised rows.  One launch replaces norm + projection GEMM + elementwise conv for the two places a layer needs
+// them (before q/k/v and before the MLP) and norm + selector projection at the head.
+// CTA c of C owns projection outputs {c, c + C, c + 2C, c + 3C} (for the dynamic conv: the four taps
+// [phase][offset] of group c) and the feature slice [c H/C, (c+1) H/C) of the output rows.
+//   mode 0: y[t, f] = n[t, f]                                                          (proj stored as fp32)
+//   mode 1: y[t, f] = (base[0][0][f] + p[t][c]) n[t, f] + (base[0][1][f] + p[t][c + C]) n[t-1, f]   (proj stored as bf16)
+// with n = bf16(bf16(x rsqrt(mean x^2 + eps)) w) and the projection accumulated in fp32 over bf16 weights.
+constexpr int kDflFusedMaxRows = 16;
+__device__ __forceinline__ float dfl_norm_val(float x, float inv, float w) {
+    return bf16_to_f32(f32_to_bf16(bf16_to_f32(f32_to_bf16(x * inv)) * w));
+}
+// grid (C, T): CTA (c, t) serves row t (and needs the statistics of row t - 1 for the conv's second tap)
+__global__ void __launch_bounds__(256) dfl_norm_proj4_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ nw,
+                                                             float eps, const __nv_bfloat16* __restrict__ wp, int C, int T, int H, int mode,
+                                                             const __nv_bfloat16* __restrict__ base, void* __restrict__ proj_out, int ld_proj,
+                                                             __nv_bfloat16* __restrict__ y, int ldy) {
+    __shared__ float red[32 * 5];
+    const int c = blockIdx.x, t = blockIdx.y;
+    const bool has_prev = mode == 1 && t > 0;
+    const __nv_bfloat16* xr = x + (size_t)t * ldx;
+    const __nv_bfloat16* xp = x + (size_t)(has_prev ? t - 1 : t) * ldx;
+    // ---- row statistics of rows t and t - 1
+    float ss[2] = {0.f, 0.f};
+    for (int k = threadIdx.x * 8; k < H; k += 2048) {
+        const uint4 u = *reinterpret_cast<const uint4*>(xr + k);
+        const uint4 v = has_prev ? *reinterpret_cast<const uint4*>(xp + k) : u;
+        const uint32_t us[4] = {u.x, u.y, u.z, u.w}, vs[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 a = bf16x2_bits_to_f32x2(us[e]), b = bf16x2_bits_to_f32x2(vs[e]);
+            ss[0] += a.x * a.x + a.y * a.y;
+            ss[1] += b.x * b.x + b.y * b.y;
+        }
+    }
+    block_sum_n<2>(ss, red);
+    const float inv = rsqrtf(ss[0] / (float)H + eps), pinv = rsqrtf(ss[1] / (float)H + eps);
+    // ---- the four projection outputs of this CTA
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int k = threadIdx.x * 8; k < H; k += 2048) {
+        const uint4 u = *reinterpret_cast<const uint4*>(xr + k);
+        const uint4 wv = *reinterpret_cast<const uint4*>(nw + k);
+        uint4 pv[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) pv[j] = *reinterpret_cast<const uint4*>(wp + (size_t)(c + j * C) * H + k);
+        const uint32_t xs[4] = {u.x, u.y, u.z, u.w}, ws[4] = {wv.x, wv.y, wv.z, wv.w};
+        float n[8];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 xv = bf16x2_bits_to_f32x2(xs[e]), w2 = bf16x2_bits_to_f32x2(ws[e]);
+            n[2 * e] = dfl_norm_val(xv.x, inv, w2.x);
+            n[2 * e + 1] = dfl_norm_val(xv.y, inv, w2.y);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t ps4[4] = {pv[j].x, pv[j].y, pv[j].z, pv[j].w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 p2 = bf16x2_bits_to_f32x2(ps4[e]);
+                acc[j] += n[2 * e] * p2.x + n[2 * e + 1] * p2.y;
+            }
+        }
+    }
+    block_sum_n<4>(acc, red);
+    if (mode == 1) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[j] = bf16_to_f32(f32_to_bf16(acc[j]));       // what a bf16 projection output holds
+    }
+    if (threadIdx.x < 4) {
+        float v = acc[0];
+        if (threadIdx.x == 1) v = acc[1];
+        if (threadIdx.x == 2) v = acc[2];
+        if (threadIdx.x == 3) v = acc[3];
+        const size_t o = (size_t)t * ld_proj + c + threadIdx.x * C;
+        if (mode == 1) reinterpret_cast<__nv_bfloat16*>(proj_out)[o] = f32_to_bf16(v);
+        else reinterpret_cast<float*>(proj_out)[o] = v;
+    }
+    // ---- output row t of this CTA's feature slice
+    const int FS = H / C, f0 = c * FS;
+    for (int i = threadIdx.x; i < FS / 2; i += 256) {
+        const int f = f0 + i * 2;
+        const float2 w2 = bf16x2_bits_to_f32x2(*reinterpret_cast<const uint32_t*>(nw + f));
+        const float2 xv = bf16x2_bits_to_f32x2(*reinterpret_cast<const uint32_t*>(xr + f));
+        const float nx = dfl_norm_val(xv.x, inv, w2.x), ny = dfl_norm_val(xv.y, inv, w2.y);
+        if (mode == 0) {
+            *reinterpret_cast<uint32_t*>(y + (size_t)t * ldy + f) = f32x2_to_bf16x2_bits(nx, ny);
+            continue;
+        }
+        float px = 0.f, py = 0.f;
+        if (has_prev) {
+            const float2 pv2 = bf16x2_bits_to_f32x2(*reinterpret_cast<const uint32_t*>(xp + f));
+            px = dfl_norm_val(pv2.x, pinv, w2.x); py = dfl_norm_val(pv2.y, pinv, w2.y);
+        }
+        const float2 b0 = bf16x2_bits_to_f32x2(*reinterpret_cast<const uint32_t*>(base + f));
+        const float2 b1 = bf16x2_bits_to_f32x2(*reinterpret_cast<const uint32_t*>(base + H + f));
+        const float k0x = bf16_to_f32(f32_to_bf16(b0.x + acc[0])), k0y = bf16_to_f32(f32_to_bf16(b0.y + acc[0]));
+        const float k1x = bf16_to_f32(f32_to_bf16(b1.x + acc[1])), k1y = bf16_to_f32(f32_to_bf16(b1.y + acc[1]));
+        const float ox = bf16_to_f32(f32_to_bf16(k0x * nx)) + bf16_to_f32(f32_to_bf16(k1x * px));
+        const float oy = bf16_to_f32(f32_to_bf16(k0y * ny)) + bf16_to_f32(f32_to_bf16(k1y * py));
+        *reinterpret_cast<uint32_t*>(y + (size_t)t * ldy + f) = f32x2_to_bf16x2_bits(ox, oy);
+    }
+}
+
 // ---- per-head RMSNorm (direct weight) + NeoX RoPE over the whole head; one warp per (row, head), D <= 256
 __device__ __forceinline__ void headnorm_rope_row(const __nv_bfloat16* src, const __nv_bfloat16* w, float eps, int D,
                                                   float pos, float theta, bool do_norm, __nv_bfloat16* dst, int lane) {
@@ -124,9 +228,10 @@ __global__ void __launch_bounds__(128) dfl_kv_ring_append_kernel(const __nv_bflo
                                                                  int kv_heads, int D, const __nv_bfloat16* __restrict__ k_norm_w,
                                                                  float eps, int pos_start, int window, float theta, int n,
                                                                  __nv_bfloat16* __restrict__ k_ring, __nv_bfloat16* __restrict__ v_ring,
-                                                                 int* __restrict__ ring_pos) {
+                                                                 int* __restrict__ ring_pos, const int* __restrict__ ctl) {
     const int wid = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     const int kvf = kv_heads * D;
+    if (ctl != nullptr) { n = min(n, ctl[1]); pos_start = ctl[3]; }      // {-, rows to keep, -, first position} on the device
     if (wid >= n * layers * kv_heads) return;
     const int h = wid % kv_heads, l = (wid / kv_heads) % layers, r = wid / (kv_heads * layers);
     const int pos = pos_start + r, slot = pos % window;
@@ -314,27 +419,38 @@ __global__ void dfl_noise_ids_kernel(const int* __restrict__ ctl, int mask_id, i
 
 // ---- sequential candidate selector: one CTA walks the draft rows; for row r every candidate j of its top-kk list gets
 // score_j = logit_j + sum_i pred_cb[prev][i] * hproj[r][i] * succ_cb[cand_j][i]; the best-ranked maximal candidate wins and
-// becomes `prev` of the next row.
-__global__ void __launch_bounds__(128) dfl_select_kernel(const int* __restrict__ top_ids, const float* __restrict__ top_logits, int kk,
+// becomes `prev` of the next row.  The candidates of ALL rows are known up front, so their codebook rows are staged in
+// shared memory first; only pred_cb[prev] is a dependent load per row.
+__global__ void __launch_bounds__(256) dfl_select_kernel(const int* __restrict__ top_ids, const float* __restrict__ top_logits, int kk,
                                                          const float* __restrict__ hproj, int rank,
                                                          const __nv_bfloat16* __restrict__ pred_cb, const __nv_bfloat16* __restrict__ succ_cb,
                                                          const int* __restrict__ anchor, int anchor_value, int K, int vocab,
-                                                         int* __restrict__ out_tokens) {
+                                                         int* __restrict__ out_tokens, int staged) {
+    extern __shared__ __align__(16) unsigned char sel_smem[];
+    __nv_bfloat16* s_succ = reinterpret_cast<__nv_bfloat16*>(sel_smem);            // [K * kk][rank] when staged
     __shared__ float s_u[256];          // pred_cb[prev] * hproj[r]
     __shared__ float s_score[128];
     __shared__ int s_prev;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) s_prev = anchor != nullptr ? anchor[0] : anchor_value;
+    if (staged) {
+        for (int i = threadIdx.x; i < K * kk * rank; i += 256) {
+            const int cj = i / rank, cand = top_ids[cj];
+            s_succ[i] = (cand >= 0 && cand < vocab) ? succ_cb[(size_t)cand * rank + (i - cj * rank)] : f32_to_bf16(0.f);
+        }
+    }
     __syncthreads();
     for (int r = 0; r < K; ++r) {
         const int prev = min(max(s_prev, 0), vocab - 1);
-        for (int i = threadIdx.x; i < rank; i += 128) s_u[i] = bf16_to_f32(pred_cb[(size_t)prev * rank + i]) * hproj[(size_t)r * rank + i];
+        for (int i = threadIdx.x; i < rank; i += 256) s_u[i] = bf16_to_f32(pred_cb[(size_t)prev * rank + i]) * hproj[(size_t)r * rank + i];
         __syncthreads();
-        for (int j = warp; j < kk; j += 4) {
+        for (int j = warp; j < kk; j += 8) {
             const int cand = top_ids[r * kk + j];
             float acc = 0.f;
-            if (cand >= 0 && cand < vocab)
-                for (int i = lane; i < rank; i += 32) acc += s_u[i] * bf16_to_f32(succ_cb[(size_t)cand * rank + i]);
+            if (cand >= 0 && cand < vocab) {
+                const __nv_bfloat16* sr = staged ? s_succ + (size_t)(r * kk + j) * rank : succ_cb + (size_t)cand * rank;
+                for (int i = lane; i < rank; i += 32) acc += s_u[i] * bf16_to_f32(sr[i]);
+            }
             acc = warp_sum(acc);
             if (lane == 0) s_score[j] = cand >= 0 ? top_logits[r * kk + j] + acc : -3.0e38f;
         }
@@ -367,6 +483,19 @@ PS_API int ps_dfl_conv_apply(const void* in, int ld_in, const void* dyn, int ld_
     return PS_LAUNCH_CHECK();
 }
 
+// x [T, H] -> y [T, H] and proj [T, 4 C]; see dfl_norm_proj4_kernel.  wp: bf16 [4 C, H] row-major.
+// mode 1 (conv prepare): C = conv groups, base = base_kernel [2 phases][2 offsets][H], proj_out bf16.
+// mode 0 (norm + projection): proj_out fp32.
+PS_API int ps_dfl_norm_proj4(const void* x, int ldx, const void* norm_w, float eps, const void* wp, int C, int T, int H, int mode,
+                             const void* base, void* proj_out, int ld_proj, void* y, int ldy, cudaStream_t stream) {
+    if (T < 1 || T > ps::kDflFusedMaxRows || C < 1 || H % C || ((H / C) & 1) || (H % 8) || (ldx % 8) || ((uintptr_t)x % 16) ||
+        ((uintptr_t)wp % 16) || ((uintptr_t)norm_w % 16) || (mode == 1 && base == nullptr) || mode < 0 || mode > 1)
+        return (int)cudaErrorInvalidValue;
+    ps::dfl_norm_proj4_kernel<<<dim3(C, T), 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)norm_w, eps, (const __nv_bfloat16*)wp, C,
+                                                     T, H, mode, (const __nv_bfloat16*)base, proj_out, ld_proj, (__nv_bfloat16*)y, ldy);
+    return PS_LAUNCH_CHECK();
+}
+
 PS_API int ps_dfl_headnorm_rope(const void* x, int ldx, int heads, int D, const void* w, int heads_w, const void* w2, float eps,
                                 const void* pos, float theta, int rows, void* out, int ldo, cudaStream_t stream) {
     if (rows <= 0 || D > 256 || (D & 1) || (heads_w < heads && w2 == nullptr)) return (int)cudaErrorInvalidValue;
@@ -376,13 +505,17 @@ PS_API int ps_dfl_headnorm_rope(const void* x, int ldx, int heads, int D, const 
     return PS_LAUNCH_CHECK();
 }
 
+// ctl (optional, int32[4] on the device): rows beyond ctl[1] are skipped and ctl[3] replaces pos_start, so that a captured
+// graph can commit a number of rows that is only known on the device side of the launch.
 PS_API int ps_dfl_kv_ring_append(const void* kv, int ld, int layers, int kv_heads, int D, const void* k_norm_w, float eps, int pos_start,
-                                 int window, float theta, int n, void* k_ring, void* v_ring, void* ring_pos, cudaStream_t stream) {
+                                 int window, float theta, int n, void* k_ring, void* v_ring, void* ring_pos, const void* ctl,
+                                 cudaStream_t stream) {
     if (n <= 0 || D > 256 || (D & 1)) return (int)cudaErrorInvalidValue;
     const int warps = n * layers * kv_heads;
     ps::dfl_kv_ring_append_kernel<<<(warps + 3) / 4, 128, 0, stream>>>((const __nv_bfloat16*)kv, ld, layers, kv_heads, D,
                                                                         (const __nv_bfloat16*)k_norm_w, eps, pos_start, window, theta, n,
-                                                                        (__nv_bfloat16*)k_ring, (__nv_bfloat16*)v_ring, (int*)ring_pos);
+                                                                        (__nv_bfloat16*)k_ring, (__nv_bfloat16*)v_ring, (int*)ring_pos,
+                                                                        (const int*)ctl);
     return PS_LAUNCH_CHECK();
 }
 
@@ -437,8 +570,15 @@ PS_API int ps_dfl_select(const void* top_ids, const void* top_logits, int kk, co
                          const void* succ_cb, const void* anchor_dev, int anchor_value, int K, int vocab, void* out_tokens,
                          cudaStream_t stream) {
     if (K <= 0 || kk < 1 || kk > 128 || rank < 1 || rank > 256) return (int)cudaErrorInvalidValue;
-    ps::dfl_select_kernel<<<1, 128, 0, stream>>>((const int*)top_ids, (const float*)top_logits, kk, (const float*)hproj, rank,
-                                                 (const __nv_bfloat16*)pred_cb, (const __nv_bfloat16*)succ_cb, (const int*)anchor_dev,
-                                                 anchor_value, K, vocab, (int*)out_tokens);
+    const size_t stage_bytes = (size_t)K * kk * rank * 2;
+    const int staged = stage_bytes <= 96 * 1024 ? 1 : 0;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(ps::dfl_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        attr_set = true;
+    }
+    ps::dfl_select_kernel<<<1, 256, staged ? stage_bytes : 0, stream>>>((const int*)top_ids, (const float*)top_logits, kk, (const float*)hproj, rank,
+                                                                       (const __nv_bfloat16*)pred_cb, (const __nv_bfloat16*)succ_cb, (const int*)anchor_dev,
+                                                                       anchor_value, K, vocab, (int*)out_tokens, staged);
     return PS_LAUNCH_CHECK();
 }

@@ -1010,6 +1010,7 @@ static int bs_sm_count() {
     return g_bs_sms;
 }
 
+constexpr int kBsMinUnits = 4;
 struct BsPlan { int P, tiles_n, tiles_m, total, grid, stages, res_slots, res_full, nb; size_t smem; };
 
 template <int FMT>
@@ -1022,7 +1023,10 @@ static bool bs_plan(int M, int N, int K, bool resident, int grid_override, BsPla
     if ((long long)pl.tiles_n * pl.tiles_m > kBsMaxTiles) return false;
     pl.total = pl.tiles_n * pl.tiles_m * pl.P;
     const int sms = grid_override > 0 ? grid_override : bs_sm_count();
-    pl.grid = pl.total < sms ? pl.total : sms;
+    // small projections: at least kBsMinUnits panels per CTA, so that a tile is never cut into dozens of partials
+    // that its last contributor then has to sum
+    const int want = (pl.total + kBsMinUnits - 1) / kBsMinUnits;
+    pl.grid = want < sms ? want : sms;
     const int nblk = pl.nb > 128 ? 2 : 1;
     const int sfa = T::kApp * 512;
     int stage = resident ? (kBsATile + sfa) : (kBsATile + pl.nb * 128 + sfa + nblk * sfa);

@@ -41,11 +41,19 @@ __device__ __forceinline__ void topk_rounds(unsigned long long (&keys)[kTopkRegs
             const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
             best = other > best ? other : best;
         }
-        if (lane == 0) s_red[(it & 1) * WARPS + warp] = best;      // double-buffered: one barrier per round
+        if (lane == 0) s_red[warp] = best;
         __syncthreads();
-        unsigned long long w = 0;
+        if (warp == 0) {                                            // second level: one warp, one shared result
+            unsigned long long v = lane < WARPS ? s_red[lane] : 0ull;
 #pragma unroll
-        for (int i = 0; i < WARPS; ++i) { const unsigned long long v = s_red[(it & 1) * WARPS + i]; w = v > w ? v : w; }
+            for (int o = 16; o > 0; o >>= 1) {
+                const unsigned long long other = __shfl_xor_sync(0xffffffffu, v, o);
+                v = other > v ? other : v;
+            }
+            if (lane == 0) s_red[WARPS] = v;
+        }
+        __syncthreads();
+        const unsigned long long w = s_red[WARPS];
         if (w != 0) {
 #pragma unroll
             for (int e = 0; e < kTopkRegs; ++e) if (keys[e] == w) keys[e] = 0;
@@ -57,7 +65,7 @@ __device__ __forceinline__ void topk_rounds(unsigned long long (&keys)[kTopkRegs
 __global__ void __launch_bounds__(kTopkChunkThreads) topk_chunk_kernel(const float* __restrict__ logits, long long ld, int vocab, int k,
                                                                        int chunk, const uint32_t* __restrict__ mask, int mask_words,
                                                                        unsigned long long* __restrict__ ws) {
-    __shared__ unsigned long long s_red[2 * kTopkChunkThreads / 32];
+    __shared__ unsigned long long s_red[kTopkChunkThreads / 32 + 1];
     const int row = blockIdx.y, c = blockIdx.x;
     const float* lg = logits + (long long)row * ld;
     const uint32_t* m = mask != nullptr ? mask + (long long)row * mask_words : nullptr;
@@ -73,7 +81,7 @@ __global__ void __launch_bounds__(kTopkChunkThreads) topk_chunk_kernel(const flo
 
 __global__ void __launch_bounds__(kTopkMergeThreads) topk_merge_kernel(const unsigned long long* __restrict__ ws, int n_cand, int k,
                                                                        int* __restrict__ out_ids, float* __restrict__ out_vals) {
-    __shared__ unsigned long long s_red[2 * kTopkMergeThreads / 32];
+    __shared__ unsigned long long s_red[kTopkMergeThreads / 32 + 1];
     __shared__ unsigned long long s_out[kTopkMax];
     const int row = blockIdx.x;
     unsigned long long keys[kTopkRegs];

@@ -72,6 +72,9 @@ class DFlash2SpecDecoder:
                 self.logs[li] = (torch.zeros(rows, st.hv, Dk, device=dev), torch.zeros(rows, st.hv, Dv, device=dev),
                                  torch.zeros(rows, st.hv, device=dev))
         self.stats = {"rounds": 0, "accepted": 0, "proposed": 0, "emitted": 0, "plain_steps": 0}
+        self.commit_graphs = True          # device-draft rounds: the commit (log replay + ring append) is one graph replay
+        self._commit_graphs: Dict[tuple, object] = {}
+        self._commit_ctl = self._commit_host = None
 
     @staticmethod
     def from_dir(engine, drafter_dir, num_drafts: int = 7, ngram_tail: int = 0, ngram_n: int = 0, native: Optional[bool] = None,
@@ -109,6 +112,35 @@ class DFlash2SpecDecoder:
             self.drafter.append_context(taps, pos_start, tokens=list(tokens[:n_rows]))
         else:
             self.drafter.append_context(taps, pos_start)
+
+    def _commit_captured(self, out, n_rows: int, keep: int, slot: int, pos0: int) -> None:
+        """Commit `keep` of the verified rows -- replay of the recurrent-state log of every GDN layer and the append of
+        the kept rows' taps to the drafter's ring -- as ONE graph replay: the row count, slot and position travel in a
+        device control word, so the same graph serves every outcome of the acceptance test."""
+        eng, st = self.eng, self.eng.state
+        if self._commit_ctl is None:
+            self._commit_ctl = torch.zeros(1, 4, dtype=torch.int32, device=eng.device)
+            self._commit_host = torch.zeros(1, 4, dtype=torch.int32, pin_memory=True)
+        h = self._commit_host
+        h[0, 0], h[0, 1], h[0, 2], h[0, 3] = 0, keep, slot, pos0
+        self._commit_ctl.copy_(h, non_blocking=True)
+        cat = out.taps_cat[:n_rows]
+        key = (n_rows, cat.data_ptr())
+
+        def run():
+            for li, g in enumerate(st.gdn):
+                if g is not None:
+                    eng.ops.gdn_replay(g, st.hv, self._commit_ctl, 1, self.logs[li])
+            self.drafter.append_context([], 0, cat=cat, ctl=self._commit_ctl)
+        g = self._commit_graphs.get(key)
+        if g is None:
+            from ...utils.graphs import capture as capture_graph
+            run()                                           # this round's commit, eagerly (also the warm-up)
+            torch.cuda.current_stream().synchronize()
+            self._commit_graphs[key] = capture_graph(eng.device, run)[0]
+        else:
+            g.replay()
+        self.drafter.context_len = pos0 + keep
 
     # ------------------------------------------------------------------ phases
     def prefill(self, s, prompt: Sequence[int], chunk: int, samp: dict) -> int:
@@ -160,13 +192,16 @@ class DFlash2SpecDecoder:
         accepted, nxt, full = self.rt.spec_greedy_accept(drafts, toks)
         keep = accepted + 1                                  # anchor + accepted drafts are now part of the sequence
         st = eng.state
-        desc = torch.tensor([[0, keep, s.slot, pos0]], dtype=torch.int32, device=eng.device)
-        for li, g in enumerate(st.gdn):
-            if g is not None:
-                eng.ops.gdn_replay(g, st.hv, desc, 1, self.logs[li])
+        if on_device and getattr(out, "taps_cat", None) is not None and self.commit_graphs:
+            self._commit_captured(out, len(rows), keep, s.slot, pos0)
+        else:
+            desc = torch.tensor([[0, keep, s.slot, pos0]], dtype=torch.int32, device=eng.device)
+            for li, g in enumerate(st.gdn):
+                if g is not None:
+                    eng.ops.gdn_replay(g, st.hv, desc, 1, self.logs[li])
+            self._append_taps(out, keep, pos0, rows)
         s.position = pos0 + keep
         eng.trim_pages(s)
-        self._append_taps(out, keep, pos0, rows)
         self.stats["rounds"] += 1
         self.stats["accepted"] += accepted
         self.stats["proposed"] += len(drafts)

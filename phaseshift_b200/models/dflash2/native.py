@@ -60,10 +60,14 @@ class DFlash2NativeDrafter:
 
         self.fc = lin(weights["fc.weight"])
         self.fc_norm, self.final_norm = bf("fc_norm.weight"), bf("norm.weight")
-        # small, precision-sensitive projections (dynamic conv taps, selector projection): 8-bit codes, still on the
-        # tensor-core kernel (one launch each)
-        small = "bf16" if fmt == "bf16" else "mxfp8"
+        # tiny projections (dynamic conv taps: 4 * groups outputs; selector projection: rank outputs) stay bf16 and run
+        # inside the fused norm kernel (ps_dfl_norm_proj4) when their shape fits it, else as separate projections
+        self.fused_small = (c.selector_rank % 4 == 0 and c.hidden_size % (c.selector_rank // 4) == 0
+                            and (c.hidden_size // (c.selector_rank // 4)) % 2 == 0 and c.conv_group_size % 2 == 0
+                            and c.hidden_size % 8 == 0)
+        small = "bf16"
         self.hidden_projection = lin(weights["selector.hidden_projection.weight"], small)
+        self.hproj_w = bf("selector.hidden_projection.weight")
         self.pred_cb, self.succ_cb = bf("selector.pred_codebook"), bf("selector.succ_codebook")
         self.layers = []
         kv_ctx, k_norms = [], []
@@ -78,6 +82,7 @@ class DFlash2NativeDrafter:
                 down=lin(weights[p + "mlp.down_proj.weight"]),
                 attn_kproj=lin(weights[p + "attn_conv.kernel_projection.weight"], small),
                 mlp_kproj=lin(weights[p + "mlp_conv.kernel_projection.weight"], small),
+                attn_kproj_w=bf(p + "attn_conv.kernel_projection.weight"), mlp_kproj_w=bf(p + "mlp_conv.kernel_projection.weight"),
                 attn_base=bf(p + "attn_conv.base_kernel"), mlp_base=bf(p + "mlp_conv.base_kernel"))
             self.layers.append(L)
             kv_ctx += [weights[a + "k_proj.weight"], weights[a + "v_proj.weight"]]
@@ -156,6 +161,16 @@ class DFlash2NativeDrafter:
         self.launches += 1
         return out
 
+    def _norm_proj4(self, x: torch.Tensor, norm_w: torch.Tensor, wp: torch.Tensor, C: int, mode: int, base, name: str):
+        """Fused RMSNorm + 4C-output projection + (mode 1) conv prepare / (mode 0) normalised rows.  Returns (y, proj)."""
+        T, H = x.shape
+        y = self.ops.buf("dfl_" + name, T, H)
+        proj = self.ops.buf("dfl_" + name + "_p", T, 4 * C, torch.bfloat16 if mode == 1 else torch.float32)
+        _lib.call("ps_dfl_norm_proj4", ptr(x), c_int(x.stride(0)), ptr(norm_w), c_float(self.cfg.rms_norm_eps), ptr(wp), c_int(C), c_int(T),
+                  c_int(H), c_int(mode), ptr(base), ptr(proj), c_int(proj.stride(0)), ptr(y), c_int(y.stride(0)))
+        self.launches += 1
+        return y, proj
+
     def _attn_workspace(self, T: int) -> torch.Tensor:
         L = _lib.lib()
         L.ps_dfl_ring_attention_workspace_floats.restype = ctypes.c_longlong
@@ -165,8 +180,8 @@ class DFlash2NativeDrafter:
     # ------------------------------------------------------------------ context
     def target_feature(self, taps: Sequence[torch.Tensor], cat: Optional[torch.Tensor] = None) -> torch.Tensor:
         c = self.cfg
-        n = taps[0].shape[0]
         if cat is None:
+            n = taps[0].shape[0]
             cat = self.ops.buf("dfl_cat", n, len(taps) * self.H)
             srcs = (ctypes.c_void_p * len(taps))(*[t.data_ptr() for t in taps])
             lds = (ctypes.c_int * len(taps))(*[t.stride(0) for t in taps])
@@ -175,9 +190,13 @@ class DFlash2NativeDrafter:
         raw = self._linear(cat, self.fc, "fc")
         return self._rms(raw, self.fc_norm, "tf")
 
-    def append_context(self, taps: Sequence[torch.Tensor], pos_start: int, cat: Optional[torch.Tensor] = None) -> None:
+    def append_context(self, taps: Sequence[torch.Tensor], pos_start: int, cat: Optional[torch.Tensor] = None,
+                       ctl: Optional[torch.Tensor] = None) -> None:
         """Append committed target rows to every layer's ring.  ``taps``: the tapped hidden states, bf16 [n, H] each
-        (``cat``: the same rows already side by side, [n, taps * H], when the target step wrote them that way)."""
+        (``cat``: the same rows already side by side, [n, taps * H], when the target step wrote them that way).
+        ``ctl`` (int32[4] on the device: {-, rows to keep, -, first position}): only the first ctl[1] of the given rows
+        are appended, starting at position ctl[3]; the launch sequence then depends on nothing the host knows only
+        after a read-back, so it can sit in a captured graph (``pos_start`` is ignored; the caller tracks the length)."""
         c = self.cfg
         n = taps[0].shape[0] if cat is None else cat.shape[0]
         if n == 0:
@@ -195,9 +214,10 @@ class DFlash2NativeDrafter:
         kv = self._linear(tf, self.kv_ctx, "kv_ctx")
         _lib.call("ps_dfl_kv_ring_append", ptr(kv), c_int(kv.stride(0)), c_int(c.num_hidden_layers), c_int(c.num_key_value_heads),
                   c_int(c.head_dim), ptr(self.k_norms), c_float(c.rms_norm_eps), c_int(pos_start), c_int(c.sliding_window),
-                  c_float(c.rope_theta), c_int(n), ptr(self.k_ring), ptr(self.v_ring), ptr(self.ring_pos))
+                  c_float(c.rope_theta), c_int(n), ptr(self.k_ring), ptr(self.v_ring), ptr(self.ring_pos), ptr(ctl))
         self.launches += 1
-        self.context_len = pos_start + n
+        if ctl is None:
+            self.context_len = pos_start + n
         if collecting:
             self._finish_calibration("ctx")
 
@@ -219,9 +239,12 @@ class DFlash2NativeDrafter:
         qd, kvd, D = self.q_dim, self.kv_dim, c.head_dim
         hq, hkv = c.num_attention_heads, c.num_key_value_heads
         for l, L in enumerate(self.layers):
-            n = self._rms(x, L["in_norm"], "n")
-            dyn = self._linear(n, L["attn_kproj"], "dyn_a")
-            a = self._conv(n, dyn, L["attn_base"], 0, "a")
+            if self.fused_small:
+                a, dyn = self._norm_proj4(x, L["in_norm"], L["attn_kproj_w"], c.groups, 1, L["attn_base"], "a")
+            else:
+                n = self._rms(x, L["in_norm"], "n")
+                dyn = self._linear(n, L["attn_kproj"], "dyn_a")
+                a = self._conv(n, dyn, L["attn_base"], 0, "a")
             qkv = self._linear(a, L["qkv"], "qkv")
             # per-head norm + RoPE of the q and k heads in place (v untouched)
             _lib.call("ps_dfl_headnorm_rope", ptr(qkv), c_int(qkv.stride(0)), c_int(hq + hkv), c_int(D), ptr(L["q_norm"]), c_int(hq),
@@ -236,14 +259,21 @@ class DFlash2NativeDrafter:
             self.launches += 3
             o = self._linear(att, L["o"], "o")
             x = self._conv(o, dyn, L["attn_base"], 1, "x", residual=x, out=x)
-            m = self._rms(x, L["post_norm"], "m")
-            dyn2 = self._linear(m, L["mlp_kproj"], "dyn_m")
-            m2 = self._conv(m, dyn2, L["mlp_base"], 0, "m2")
+            if self.fused_small:
+                m2, dyn2 = self._norm_proj4(x, L["post_norm"], L["mlp_kproj_w"], c.groups, 1, L["mlp_base"], "m2")
+            else:
+                m = self._rms(x, L["post_norm"], "m")
+                dyn2 = self._linear(m, L["mlp_kproj"], "dyn_m")
+                m2 = self._conv(m, dyn2, L["mlp_base"], 0, "m2")
             act = self._linear(m2, L["gate_up"], "act", swiglu=True)
             d = self._linear(act, L["down"], "d")
             x = self._conv(d, dyn2, L["mlp_base"], 1, "x", residual=x, out=x)
-        h = self._rms(x, self.final_norm, "h")[1:T]                       # draft rows
-        hproj = self._linear(h, self.hidden_projection, "hproj", out_f32=True)
+        if self.fused_small:
+            hn, hp = self._norm_proj4(x, self.final_norm, self.hproj_w, c.selector_rank // 4, 0, None, "h")
+            h, hproj = hn[1:T], hp[1:T]                                   # draft rows
+        else:
+            h = self._rms(x, self.final_norm, "h")[1:T]
+            hproj = self._linear(h, self.hidden_projection, "hproj", out_f32=True)
         logits = ops.linear(h, eng.runner.w.lm_head, name="dfl_logits", out_f32=True)
         kk = min(c.selector_top_k, logits.shape[1])
         top_ids, top_vals = ops.topk(logits, kk)

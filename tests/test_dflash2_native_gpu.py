@@ -63,6 +63,34 @@ def test_conv_apply_matches_torch(phase):
         assert _rel_err(out, ref) < 6e-3
 
 
+@pytest.mark.parametrize("T,H,C", [(1, 256, 8), (8, 5120, 40), (16, 1024, 16)])
+def test_fused_norm_projection_conv_matches_torch(T, H, C):
+    """norm -> 4C-output projection -> conv prepare (mode 1) / normalised rows (mode 0) in one launch."""
+    from phaseshift_b200.models.dflash2.model import _rms
+    L = _lib()
+    g = _gen(20 + T)
+    x = (torch.randn(T, H, device="cuda", generator=g) * 2).to(torch.bfloat16)
+    nw = (1 + 0.1 * torch.randn(H, device="cuda", generator=g)).to(torch.bfloat16)
+    wp = (0.05 * torch.randn(4 * C, H, device="cuda", generator=g)).to(torch.bfloat16)
+    base = torch.randn(2, 2, H, device="cuda", generator=g).to(torch.bfloat16)
+    n = _rms(x, nw, 1e-6)
+    proj_ref = n.float() @ wp.float().T
+    for mode in (0, 1):
+        y = torch.empty_like(x)
+        proj = torch.empty(T, 4 * C, device="cuda", dtype=torch.bfloat16 if mode else torch.float32)
+        L.call("ps_dfl_norm_proj4", L.ptr(x), L.c_int(H), L.ptr(nw), L.c_float(1e-6), L.ptr(wp), L.c_int(C), L.c_int(T), L.c_int(H),
+               L.c_int(mode), L.ptr(base if mode else None), L.ptr(proj), L.c_int(4 * C), L.ptr(y), L.c_int(H))
+        assert _rel_err(proj, proj_ref) < (1e-2 if mode else 2e-3)
+        if mode == 0:
+            assert _rel_err(y, n) < 4e-3
+        else:
+            gs = H // C
+            d = proj.float().reshape(T, 2, 2, C)
+            k = base.float()[0][None] + d[:, 0].repeat_interleave(gs, -1)
+            prev = torch.cat([torch.zeros_like(n[:1]), n[:-1]], 0).float()
+            assert _rel_err(y, k[:, 0] * n.float() + k[:, 1] * prev) < 8e-3
+
+
 def test_headnorm_rope_matches_torch():
     from phaseshift_b200.models.dflash2.model import _rms, _rope
     L = _lib()
@@ -136,7 +164,7 @@ def test_kv_ring_append_matches_torch():
         m = min(W, n - c0)
         L.call("ps_dfl_kv_ring_append", L.ptr(kv[c0:]), L.c_int(kv.stride(0)), L.c_int(layers), L.c_int(hkv), L.c_int(D), L.ptr(kw),
                L.c_float(1e-6), L.c_int(pos0 + c0), L.c_int(W), L.c_float(1e7), L.c_int(m), L.ptr(k_ring), L.ptr(v_ring),
-               L.ptr(ring_pos))
+               L.ptr(ring_pos), L.ptr(None))
     pos = torch.arange(pos0, pos0 + n, device="cuda")
     for l in range(layers):
         k = kv[:, l * 2 * kvd:l * 2 * kvd + kvd].reshape(n, hkv, D)
@@ -147,6 +175,17 @@ def test_kv_ring_append_matches_torch():
             assert int(ring_pos[slot]) == pos0 + r
             assert _rel_err(k_ring[l, slot], kr[r]) < 8e-3
             assert torch.equal(v_ring[l, slot], v[r])
+    # device-side control: keep 3 of 8 offered rows, starting at position 200
+    before_k, before_pos = k_ring.clone(), ring_pos.clone()
+    ctl = torch.tensor([0, 3, 0, 200], dtype=torch.int32, device="cuda")
+    L.call("ps_dfl_kv_ring_append", L.ptr(kv), L.c_int(kv.stride(0)), L.c_int(layers), L.c_int(hkv), L.c_int(D), L.ptr(kw),
+           L.c_float(1e-6), L.c_int(0), L.c_int(W), L.c_float(1e7), L.c_int(8), L.ptr(k_ring), L.ptr(v_ring), L.ptr(ring_pos), L.ptr(ctl))
+    touched = {(200 + r) % W for r in range(3)}
+    for slot in range(W):
+        if slot in touched:
+            assert int(ring_pos[slot]) == 200 + [r for r in range(3) if (200 + r) % W == slot][0]
+        else:
+            assert int(ring_pos[slot]) == int(before_pos[slot]) and torch.equal(k_ring[:, slot], before_k[:, slot])
 
 
 def test_feature_concat_and_noise_ids():
@@ -266,11 +305,14 @@ def test_speculative_round_with_native_drafter_is_exact(preset, fmt):
     out, stats = dec.generate(prompt, 24, prefill_chunk=8)
     assert out == plain
     assert stats["rounds"] > 0 and any(isinstance(k, tuple) for k in eng.graphs)        # verification replayed a graph
+    assert dec._commit_graphs                                                           # ... and so did the commit
     # the same with graphs off (eager verification): same stream
     eng.graph_variants = False
     ndr.use_graph = False
+    dec.commit_graphs = False
     out2, _ = dec.generate(prompt, 24, prefill_chunk=8)
     assert out2 == plain
+    dec.commit_graphs = True
     # oracle drafts on the device
     eng.graph_variants = True
     full = prompt + plain
