@@ -38,14 +38,15 @@ struct ArArgs {
 };
 
 // Signal every peer and wait for every peer at (phase, this CTA).  Returns false on timeout.
-__device__ __forceinline__ bool ar_barrier(const ArArgs& a, int phase, uint32_t val, bool* s_fail, long long budget) {
+__device__ __forceinline__ bool peer_barrier(uint32_t* const* flags, int size, int rank, int phase, uint32_t val, bool* s_fail,
+                                             long long budget) {
     __syncthreads();
-    if (threadIdx.x < a.size) {
+    if (threadIdx.x < size) {
         __threadfence_system();
-        const size_t base = ((size_t)phase * gridDim.x + blockIdx.x) * a.size;
-        uint32_t* f = a.flags[threadIdx.x] + base + a.rank;
+        const size_t base = ((size_t)phase * gridDim.x + blockIdx.x) * size;
+        uint32_t* f = flags[threadIdx.x] + base + rank;
         asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(val) : "memory");
-        const uint32_t* mine = a.flags[a.rank] + base + threadIdx.x;
+        const uint32_t* mine = flags[rank] + base + threadIdx.x;
         const long long t0 = clock64();
         uint32_t seen;
         do {
@@ -56,6 +57,9 @@ __device__ __forceinline__ bool ar_barrier(const ArArgs& a, int phase, uint32_t 
     }
     __syncthreads();
     return !*s_fail;
+}
+__device__ __forceinline__ bool ar_barrier(const ArArgs& a, int phase, uint32_t val, bool* s_fail, long long budget) {
+    return peer_barrier(a.flags, a.size, a.rank, phase, val, s_fail, budget);
 }
 
 __device__ __forceinline__ void acc_bf16x8(float (&acc)[8], const uint4& v) {
@@ -131,7 +135,78 @@ __global__ void __launch_bounds__(256) allreduce_multimem_kernel(const ArArgs a,
     }
 }
 
+// ---- second half of the fused row-parallel projection for many rows: reduce + residual + all-gather.
+// The projection kernels of all ranks have pushed their bf16 partials of MY rows into my receive buffer
+// ([source rank][rpr][ld]; csrc/kernels/gemm_bs.cu, TpScatter).  Barrier A (the same CTA of every peer has started, so
+// by stream order its projection -- and with it its pushes -- is complete), then every rank adds the partials of the
+// rows it owns in rank order, rounds, adds the residual and stores the finished rows into EVERY rank's output buffer
+// (16-byte peer stores); barrier B (every peer's stores into my output are complete, and every peer is done reading
+// its receive buffer, so the next projection may push again).  Each row is reduced exactly once: ranks agree bit for bit.
+struct RgArgs {
+    int size, rank, rows, n, rpr;
+    const __nv_bfloat16* recv; int ld;         // local receive buffer
+    uint32_t* flags[kArMaxRanks];              // rank r's flags: [2][grid][size]
+    uint32_t* counter;                         // local [grid]
+    const __nv_bfloat16* residual; int ld_res; // local, all rows (null: none)
+    __nv_bfloat16* out[kArMaxRanks]; int ldo;  // every rank's output buffer (peer pointers)
+    uint32_t* status;
+};
+
+__global__ void __launch_bounds__(256) reduce_gather_kernel(const RgArgs a, const long long budget) {
+    __shared__ bool s_fail;
+    __shared__ uint32_t s_val;
+    if (threadIdx.x == 0) { s_fail = false; s_val = a.counter[blockIdx.x] + 1u; }
+    __syncthreads();
+    const uint32_t val = s_val;
+    if (!peer_barrier(a.flags, a.size, a.rank, 0, val, &s_fail, budget)) {
+        if (threadIdx.x == 0) set_status(a.status, PS_DEV_WAIT_TIMEOUT);
+        return;
+    }
+    const int m0 = a.rank * a.rpr, m1 = min(a.rows, m0 + a.rpr);
+    const int per_row = a.n >> 3;
+    const long long chunks = (long long)max(0, m1 - m0) * per_row;
+    for (long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x; c < chunks; c += (long long)gridDim.x * blockDim.x) {
+        const int lr = (int)(c / per_row), col = (int)(c % per_row) << 3;
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int r = 0; r < a.size; ++r)
+            acc_bf16x8(acc, __ldcv(reinterpret_cast<const uint4*>(a.recv + ((size_t)r * a.rpr + lr) * a.ld + col)));
+        const int row = m0 + lr;
+        if (a.residual != nullptr) {
+            const uint4 rv = *reinterpret_cast<const uint4*>(a.residual + (size_t)row * a.ld_res + col);
+            const uint32_t w[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = bf16x2_bits_to_f32x2(w[i]);
+                acc[2 * i] = bf16_to_f32(f32_to_bf16(acc[2 * i])) + f.x;
+                acc[2 * i + 1] = bf16_to_f32(f32_to_bf16(acc[2 * i + 1])) + f.y;
+            }
+        }
+        const uint4 o = make_uint4(f32x2_to_bf16x2_bits(acc[0], acc[1]), f32x2_to_bf16x2_bits(acc[2], acc[3]),
+                                   f32x2_to_bf16x2_bits(acc[4], acc[5]), f32x2_to_bf16x2_bits(acc[6], acc[7]));
+        for (int p = 0; p < a.size; ++p) {
+            const int pr = (a.rank + p) % a.size;          // start with myself, spread the peers over the links
+            *reinterpret_cast<uint4*>(a.out[pr] + (size_t)row * a.ldo + col) = o;
+        }
+    }
+    if (!peer_barrier(a.flags, a.size, a.rank, 1, val, &s_fail, budget)) {
+        if (threadIdx.x == 0) set_status(a.status, PS_DEV_WAIT_TIMEOUT);
+        return;
+    }
+    if (threadIdx.x == 0) a.counter[blockIdx.x] = val;
+}
+
 }  // namespace ps
+
+// `args` points to a host copy of ps::RgArgs.  n and the row pitches must be multiples of 8; `grid` the same on every rank.
+PS_API int ps_tp_reduce_gather(const void* args, int grid, cudaStream_t stream) {
+    using namespace ps;
+    const RgArgs& a = *reinterpret_cast<const RgArgs*>(args);
+    if (a.size < 1 || a.size > kArMaxRanks || a.rows <= 0 || (a.n & 7) || (a.ld & 7) || (a.ldo & 7) || (a.ld_res & 7) || grid < 1 ||
+        a.rpr < 1 || (long long)a.rpr * a.size < a.rows)
+        return (int)cudaErrorInvalidValue;
+    reduce_gather_kernel<<<grid, 256, 0, stream>>>(a, g_ps_wait_budget_cycles);
+    return PS_LAUNCH_CHECK();
+}
 
 // `args` points to a host copy of ps::ArArgs.  n must be a multiple of 8; all buffers 16-byte aligned.
 // `grid` must be the same on every rank (flags are indexed by CTA).

@@ -66,6 +66,15 @@ template <int FMT> struct BsT;
 template <> struct BsT<W_NVFP4> { static constexpr int kPanelK = 256, kApp = 4, kBlockK = 16, kBpp = 16; };
 template <> struct BsT<W_MXFP8> { static constexpr int kPanelK = 128, kApp = 1, kBlockK = 32, kBpp = 4; };
 
+// Reduce-scatter by push (tensor-parallel row-parallel projections with many rows): rows are dealt to the ranks in
+// contiguous blocks of `rpr`; the epilogue stores each bf16 row piece of this rank's partial product straight into the
+// owner's receive buffer over NVLink (plain 16-byte peer stores, overlapping the main loop of the tiles still to come).
+// The owner adds the `size` partials, the residual, and hands the rows to every rank (ps_tp_reduce_gather, allreduce.cu).
+struct TpScatter {
+    int size, rank, rpr, ld;              // size <= 1: disabled; ld = elements per row of the receive buffers
+    __nv_bfloat16* recv[kTpMaxRanks];     // rank r's receive buffer: [size (source)][rpr][ld] bf16
+};
+
 struct BsArgs {
     int M, N, K;
     int P, tiles_n, tiles_m, total_units;
@@ -94,6 +103,7 @@ struct BsArgs {
     int dbg;                       // timing experiments only (PS_BS_DBG): 1 skip weight-scale copies, 2 skip activation-scale
                                    // copies, 4 skip MMAs, 8 skip the activation prologue; results are then meaningless
     TpCombine tp;
+    TpScatter rs;                  // streamed path, tensor parallel: bf16 tiles go to the rank that owns their rows
 };
 
 // CTA that owns unit x under cta_range(total, grid, c, ...).
@@ -798,6 +808,11 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                                 const uint4 sv = *reinterpret_cast<const uint4*>(sEpi + rr * cols + ch * 8);
                                 uint32_t w[4] = {sv.x, sv.y, sv.z, sv.w};
                                 __nv_bfloat16* dst = outp + (size_t)m * g.ldo + n0;
+                                if (g.rs.size > 1) {
+                                    // tensor parallel: the piece goes to the rank that owns row m (peer store)
+                                    const int owner = m / g.rs.rpr;
+                                    dst = g.rs.recv[owner] + ((size_t)g.rs.rank * g.rs.rpr + (m - owner * g.rs.rpr)) * g.rs.ld + n0;
+                                }
                                 const bool full = n0 + 8 <= n_lim;
                                 if (g.epilogue == EPI_RESIDUAL) {
                                     const __nv_bfloat16* rp = g.residual + (size_t)m * g.ld_res + n0;
@@ -1127,7 +1142,7 @@ PS_API int ps_gemm_bs(int wfmt, const void* w_codes, long long w_row_bytes, long
                       const void* residual, int ld_res, void* out, int ldo, int out_f32, void* ws, void* flags,
                       const void* tp_combine, void* status, int grid_override, int next_fmt, const void* next_codes,
                       long long next_row_bytes, long long next_pitch, const void* next_sf, int next_N, int next_K,
-                      cudaStream_t stream) {
+                      const void* tp_scatter, cudaStream_t stream) {
     using namespace ps;
     if (M < 1 || N < 1 || K < 8 || (K % 8) || ((uintptr_t)w_codes % 16) || (w_pitch % 16) || ((uintptr_t)w_sf % 16))
         return (int)cudaErrorInvalidValue;
@@ -1160,6 +1175,14 @@ PS_API int ps_gemm_bs(int wfmt, const void* w_codes, long long w_row_bytes, long
             return (int)cudaErrorInvalidValue;
     } else {
         a.tp.size = 0;
+    }
+    a.rs.size = 0;
+    if (tp_scatter != nullptr) {
+        a.rs = *reinterpret_cast<const TpScatter*>(tp_scatter);
+        // only the streamed path's staged bf16 store knows how to scatter
+        if (a.rs.size > kTpMaxRanks || resident || epilogue != EPI_STORE || out_f32 || tp_combine != nullptr || (a.rs.ld % 8) ||
+            a.rs.rpr < 1 || (long long)a.rs.rpr * a.rs.size < M || N > a.rs.ld)
+            return (int)cudaErrorInvalidValue;
     }
     // the projection that runs next with the same number of rows: geometry of its first ring fill, for the L2 prefetch
     CUtensorMap map_next;

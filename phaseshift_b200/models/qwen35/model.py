@@ -79,6 +79,12 @@ class Qwen35Runner:
         if comb is not None:
             tp.stats["fused"] += 1
             return ops.linear(inp, W, name=name, residual=residual, tp_combine=comb, ssq_out=ssq_out, **kw), ssq
+        if (tp.transport == "fused" and hasattr(ops, "select_linear") and ops.select_linear(W, rows) == "tc"
+                and not ops.bs_resident_ok(W, rows) and W.N % 8 == 0 and getattr(tp, "use_scatter", True)):
+            # many rows: the projection's epilogue pushes its partial rows to their owner ranks while later tiles
+            # are still being multiplied; the owners reduce, add the residual and hand the rows to everybody
+            ops.linear(inp, W, name="tp_partial", tp_scatter=tp.scatter_for(rows, W.N))
+            return tp.reduce_gather(rows, W.N, residual, name), None
         part = ops.linear(inp, W, name="tp_partial")
         out = ops.buf(name, rows, W.N) if hasattr(ops, "buf") else torch.empty_like(part)
         return tp.all_reduce_residual(part, residual, out), None

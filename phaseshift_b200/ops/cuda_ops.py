@@ -97,14 +97,16 @@ class CudaOps:
                eps: float = 0.0, residual: Optional[torch.Tensor] = None, swiglu: bool = False,
                out_f32: bool = False, out: Optional[torch.Tensor] = None,
                xn_out: Optional[torch.Tensor] = None, tp_combine=None, ssq_in=None,
-               ssq_out: Optional[torch.Tensor] = None, prefetch: Optional[LinearW] = None) -> torch.Tensor:
+               ssq_out: Optional[torch.Tensor] = None, prefetch: Optional[LinearW] = None, tp_scatter=None) -> torch.Tensor:
         """``tp_combine`` (a parallel.tp.TpCombineStruct): the projection is row-parallel and the kernel sums
         the ranks' partial results over NVLink before the residual epilogue.
         ``ssq_in`` = (tensor [rows, SSQ_LD] fp32, n): n partial sums of squares per row of ``x`` left by the kernel
         that produced it, consumed by the fused RMSNorm; ``ssq_out``: receives the partial sums of the rows this
         projection stores (block-scaled tensor-core path, <= 32 rows; ignored elsewhere).
         ``prefetch``: the projection that will run next on the same rows; the tensor-core kernel warms L2 with the first
-        bytes of its weights while it drains."""
+        bytes of its weights while it drains.
+        ``tp_scatter`` (a parallel.tp.TpScatterStruct; tensor-core path with streamed activations only): instead of
+        storing to ``out`` the kernel pushes each bf16 output row to the receive buffer of the rank that owns it."""
         M, K = x.shape
         assert K == W.K and x.dtype == torch.bfloat16 and x.stride(1) == 1, (x.shape, W.K, x.dtype)
         n_out = W.N // 2 if swiglu else W.N
@@ -118,7 +120,9 @@ class CudaOps:
             # block-quantised codes straight into the tensor cores (any number of rows)
             return self.linear_bs(x, W, name=name, norm_w=norm_w, eps=eps, residual=residual, swiglu=swiglu,
                                   out_f32=out_f32, out=out, xn_out=xn_out, tp_combine=tp_combine, ssq_in=ssq_in,
-                                  ssq_out=ssq_out, prefetch=prefetch)
+                                  ssq_out=ssq_out, prefetch=prefetch, tp_scatter=tp_scatter)
+        if tp_scatter is not None:
+            raise ValueError("tp_scatter needs the block-scaled tensor-core path")
         if tp_combine is not None and M > SMALL_M_MAX:
             raise ValueError("the fused tensor-parallel combine handles at most 8 rows")
         # bf16 tensor-core GEMM: prefill-sized steps, and batched steps (>= 2 rows) of bf16 weights whose row-major form
@@ -262,7 +266,7 @@ class CudaOps:
         return codes, sf, rs
 
     def linear_bs(self, x: torch.Tensor, W: LinearW, *, name: str, norm_w, eps, residual, swiglu, out_f32, out,
-                  xn_out=None, tp_combine=None, ssq_in=None, ssq_out=None, prefetch=None) -> torch.Tensor:
+                  xn_out=None, tp_combine=None, ssq_in=None, ssq_out=None, prefetch=None, tp_scatter=None) -> torch.Tensor:
         M, K = x.shape
         if K % 8 or x.stride(0) % 8:
             raise ValueError("block-scaled projections need K and the row pitch to be multiples of 8")
@@ -296,7 +300,8 @@ class CudaOps:
                  c_int(self.bs_grid_override), c_int(WFMT[nxt.fmt] if nxt is not None else 0),
                  ptr(nxt.codes if nxt is not None else None), c_ll(nxt.codes.shape[1] if nxt is not None else 0),
                  c_ll(nxt.codes.stride(0) if nxt is not None else 0), ptr(nxt.sf_atoms if nxt is not None else None),
-                 c_int(nxt.N if nxt is not None else 0), c_int(nxt.K if nxt is not None else 0), _lib.stream())
+                 c_int(nxt.N if nxt is not None else 0), c_int(nxt.K if nxt is not None else 0),
+                 ctypes.byref(tp_scatter) if tp_scatter is not None else ptr(None), _lib.stream())
         _lib.check(rc, "ps_gemm_bs")
         self.launches += 1
         return out

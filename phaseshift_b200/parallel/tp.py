@@ -53,7 +53,23 @@ class ArStruct(ctypes.Structure):
                 ("rows", ctypes.c_int), ("n", ctypes.c_int), ("status", ctypes.c_void_p)]
 
 
+class TpScatterStruct(ctypes.Structure):
+    """Host twin of ps::TpScatter (csrc/kernels/gemm_bs.cu)."""
+    _fields_ = [("size", ctypes.c_int), ("rank", ctypes.c_int), ("rpr", ctypes.c_int), ("ld", ctypes.c_int),
+                ("recv", ctypes.c_void_p * MAX_RANKS)]
+
+
+class RgStruct(ctypes.Structure):
+    """Host twin of ps::RgArgs (csrc/kernels/allreduce.cu)."""
+    _fields_ = [("size", ctypes.c_int), ("rank", ctypes.c_int), ("rows", ctypes.c_int), ("n", ctypes.c_int), ("rpr", ctypes.c_int),
+                ("recv", ctypes.c_void_p), ("ld", ctypes.c_int),
+                ("flags", ctypes.c_void_p * MAX_RANKS), ("counter", ctypes.c_void_p),
+                ("residual", ctypes.c_void_p), ("ld_res", ctypes.c_int),
+                ("out", ctypes.c_void_p * MAX_RANKS), ("ldo", ctypes.c_int), ("status", ctypes.c_void_p)]
+
+
 AR_GRID = 128
+RG_GRID = 96
 
 
 class TensorParallel:
@@ -139,6 +155,68 @@ class TensorParallel:
         st["parity"] ^= 1
         self.stats["peer_allreduce"] += 1
         return out
+
+    # ------------------------------------------------------------------ fused projection -> reduce-scatter -> all-gather
+    def _rs_state(self, rows: int, n: int):
+        """Symmetric receive buffer ([source][rows per rank][n] bf16), barrier flags and the per-name output buffers of
+        the scatter path; grown collectively (every rank sees the same sequence of shapes)."""
+        st = getattr(self, "_rs", None)
+        need = (rows + self.size) * n * 2
+        if st is None or st["cap"] < need or st["n"] != n:
+            cap = 1 << (max(need, 1 << 20) - 1).bit_length()
+            recv, recv_ptrs = self._symm_alloc(cap)
+            _, flag_ptrs = self._symm_alloc(2 * RG_GRID * self.size * 4)
+            counter = torch.zeros(RG_GRID, dtype=torch.int32, device=self.device)
+            torch.cuda.synchronize()
+            dist.barrier(self.group)
+            st = dict(cap=cap, n=n, recv=recv, recv_ptrs=recv_ptrs, flag_ptrs=flag_ptrs, counter=counter, outs={})
+            self._rs = st
+        return st
+
+    def _rs_out(self, st, name: str, rows: int, n: int):
+        """Output buffer `name` in symmetric memory (peers store finished rows into it)."""
+        o = st["outs"].get(name)
+        if o is None or o[0].shape[0] < rows or o[0].shape[1] != n:
+            cap_rows = 1 << (max(rows, 64) - 1).bit_length()
+            t, ptrs = self._symm_alloc(cap_rows * n * 2)
+            torch.cuda.synchronize()
+            dist.barrier(self.group)
+            o = (t.view(torch.bfloat16).view(cap_rows, n), ptrs)
+            st["outs"][name] = o
+        return o
+
+    def scatter_for(self, rows: int, n: int) -> TpScatterStruct:
+        """Descriptor that makes the block-scaled projection kernel push its bf16 output rows to their owner ranks."""
+        st = self._rs_state(rows, n)
+        c = TpScatterStruct()
+        c.size, c.rank, c.rpr, c.ld = self.size, self.rank, -(-rows // self.size), n
+        for r in range(self.size):
+            c.recv[r] = st["recv_ptrs"][r]
+        return c
+
+    def reduce_gather(self, rows: int, n: int, residual: Optional[torch.Tensor], name: str) -> torch.Tensor:
+        """Second half of the scatter path: sum of the pushed partials of this rank's rows + residual, finished rows
+        stored to every rank.  Returns this rank's (complete) output [rows, n]."""
+        from ..ops import _lib
+        st = self._rs_state(rows, n)
+        out, out_ptrs = self._rs_out(st, name, rows, n)
+        a = RgStruct()
+        a.size, a.rank, a.rows, a.n, a.rpr = self.size, self.rank, rows, n, -(-rows // self.size)
+        a.recv, a.ld = st["recv"].data_ptr(), n
+        for r in range(self.size):
+            a.flags[r] = st["flag_ptrs"][r]
+            a.out[r] = out_ptrs[r]
+        a.counter = st["counter"].data_ptr()
+        a.residual = residual.data_ptr() if residual is not None else None
+        a.ld_res = residual.stride(0) if residual is not None else 0
+        a.ldo = n
+        word = getattr(self, "status_word", None)
+        if word is None:
+            word = st.setdefault("status", torch.zeros(1, dtype=torch.int32, device=self.device))
+        a.status = word.data_ptr()
+        _lib.call("ps_tp_reduce_gather", ctypes.byref(a), ctypes.c_int(RG_GRID))
+        self.stats["scatter"] = self.stats.get("scatter", 0) + 1
+        return out[:rows]
 
     def max_fused_rows(self, W) -> int:
         """Rows up to which a row-parallel projection over `W` combines inside its own kernel: 32 on the
