@@ -360,7 +360,8 @@ def cmd_tp_reduce(a) -> int:
         for m in (256, 2048):
             part = (torch.randn(m, H, device=dev) * 0.1).to(torch.bfloat16)
             res = torch.zeros(m, H, device=dev, dtype=torch.bfloat16); out = torch.empty_like(part)
-            cases = [("peer", lambda: (setattr(tp, "use_multimem", False), tp.peer_all_reduce(part, res, out))),
+            cases = [("two_shot", lambda: tp.reduce_gather(m, H, res, "bench_ar_out", partial=part)),
+                     ("peer", lambda: (setattr(tp, "use_multimem", False), tp.peer_all_reduce(part, res, out))),
                      ("multimem", lambda: (setattr(tp, "use_multimem", True), tp.peer_all_reduce(part, res, out))),
                      ("nccl", lambda: (dist.all_reduce(part.clone()), None))]
             for name, fn in cases:
@@ -371,9 +372,59 @@ def cmd_tp_reduce(a) -> int:
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
                 if rank == 0:
                     nbytes = m * H * 2
+                    wire = 2 * (world - 1) / world * nbytes          # what a bandwidth-optimal all-reduce sends per GPU
                     print(f"tp_allreduce kernel={name} ranks={world} rows={m} hidden={H} payload_bytes={nbytes} p50_us={float(t):.2f} "
-                          f"bus_GBps={2 * (world - 1) / world * nbytes / float(t) / 1e3:.1f}")
+                          f"bus_GBps={wire / float(t) / 1e3:.1f} frac_of_nvlink_770GBps={wire / 770e9 * 1e6 / float(t):.3f}")
         tp.use_multimem = False
+    # block-scaled tensor-core projection fused with its collective: a 27B down_proj (5120 x 17408 / ranks, NVFP4)
+    #  * rows <= 32 : partial sums combined inside the projection kernel
+    #  * more rows  : epilogue pushes rows to their owners (reduce-scatter), then reduce + residual + all-gather
+    # roofline target = max(FLOPs / measured bf16 GEMM peak, bytes each GPU must send / measured peer-copy bandwidth)
+    import json
+    from pathlib import Path
+    peaks = {"bf16_tflops": 1590.0}
+    for cand in (Path.cwd() / "MEASURED_PEAKS.json", Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"):
+        if cand.exists():
+            peaks.update(json.loads(cand.read_text()))
+            break
+    link_gbs = 770.0
+    Kfull, N = 17408, 5120
+    Wd = LinearW(quantize(torch.randn(N, Kfull // world, device=dev) * 0.02, "nvfp4")).make_umma()
+    for m in (1, 8, 32, 256, 2048):
+        x = (torch.randn(m, Kfull // world, device=dev)).to(torch.bfloat16)
+        res = torch.zeros(m, N, device=dev, dtype=torch.bfloat16)
+        cases = [("projection_only", lambda: ops.linear(x, Wd, name="tpb_o", residual=res))]
+        if tp is not None and tp.transport == "fused":
+            if m <= 32:
+                comb = tp.combine_for(N)
+                cases.append(("fused_combine", lambda: ops.linear(x, Wd, name="tpb_f", residual=res, tp_combine=comb)))
+            else:
+                def run_scatter():
+                    ops.linear(x, Wd, name="tpb_p", tp_scatter=tp.scatter_for(m, N))
+                    return tp.reduce_gather(m, N, res, "tpb_out")
+                cases.append(("fused_scatter_gather", run_scatter))
+            outn = torch.empty(m, N, device=dev, dtype=torch.bfloat16)
+
+            def run_nccl():
+                y = ops.linear(x, Wd, name="tpb_n")
+                dist.all_reduce(y)
+                return torch.add(y, res, out=outn)
+            cases.append(("nccl", run_nccl))
+        for name, fn in cases:
+            for _ in range(5):
+                fn()
+            rep = 10                                     # back-to-back calls: device time, not host launch gaps
+            ts = sorted(_timed(dev, lambda: [fn() for _ in range(rep)])[0] * 1e3 / rep for _ in range(max(5, a.samples // rep)))
+            t = torch.tensor([ts[len(ts) // 2]], device=dev)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            if rank == 0:
+                us = float(t)
+                flops = 2.0 * m * N * (Kfull // world)
+                wire = 0.0 if name == "projection_only" else 2.0 * (world - 1) / world * m * N * (4 if m <= 32 else 2)
+                target_us = max(flops / (peaks["bf16_tflops"] * 1e12), wire / (link_gbs * 1e9)) * 1e6
+                print(f"tp_fused path={name} ranks={world} rows={m} n={N} k_local={Kfull // world} p50_us={us:.2f} "
+                      f"wire_bytes_per_gpu={int(wire)} roofline_target_us={target_us:.2f} frac_of_roofline={target_us / us:.3f}")
     if world > 1:
         dist.destroy_process_group()
     return 0

@@ -137,14 +137,22 @@ __global__ void __launch_bounds__(256) allreduce_multimem_kernel(const ArArgs a,
 
 // ---- second half of the fused row-parallel projection for many rows: reduce + residual + all-gather.
 // The projection kernels of all ranks have pushed their bf16 partials of MY rows into my receive buffer
-// ([source rank][rpr][ld]; csrc/kernels/gemm_bs.cu, TpScatter).  Barrier A (the same CTA of every peer has started, so
+// ([source rank][rpr][ld]; csrc/kernels/gemm_bs.cu, TpScatter) -- or, for projection kernels that cannot push, left
+// their whole partial in symmetric memory, from where the owner pulls its rows (two-shot all-reduce).  Barrier A (the same CTA of every peer has started, so
 // by stream order its projection -- and with it its pushes -- is complete), then every rank adds the partials of the
 // rows it owns in rank order, rounds, adds the residual and stores the finished rows into EVERY rank's output buffer
 // (16-byte peer stores); barrier B (every peer's stores into my output are complete, and every peer is done reading
 // its receive buffer, so the next projection may push again).  Each row is reduced exactly once: ranks agree bit for bit.
 struct RgArgs {
     int size, rank, rows, n, rpr;
-    const __nv_bfloat16* recv; int ld;         // local receive buffer
+    // Where the partials of my rows are: source r's rows start at src[r], row (m - src_row0) of pitch ld.
+    //  push form: src[r] = my receive buffer + r * rpr * ld, src_row0 = my first row (local loads)
+    //  pull form: src[r] = rank r's partial [rows, ld] in symmetric memory, src_row0 = 0 (peer loads of my rows only)
+    const __nv_bfloat16* src[kArMaxRanks]; int src_row0, ld;
+    // optional first phase (projection kernels that cannot push themselves): my whole partial [rows, ld_partial] is
+    // dealt to the owners' receive buffers by this kernel (remote STORES only; nothing waits on a remote load)
+    const __nv_bfloat16* partial; int ld_partial;
+    __nv_bfloat16* recv[kArMaxRanks];          // rank r's receive buffer [source][rpr][ld]
     uint32_t* flags[kArMaxRanks];              // rank r's flags: [2][grid][size]
     uint32_t* counter;                         // local [grid]
     const __nv_bfloat16* residual; int ld_res; // local, all rows (null: none)
@@ -158,19 +166,38 @@ __global__ void __launch_bounds__(256) reduce_gather_kernel(const RgArgs a, cons
     if (threadIdx.x == 0) { s_fail = false; s_val = a.counter[blockIdx.x] + 1u; }
     __syncthreads();
     const uint32_t val = s_val;
+    const int per_row = a.n >> 3;
+    if (a.partial != nullptr) {
+        // CTA c pushes, for every owner, exactly the chunks that CTA c of that owner will reduce: barrier A below (same
+        // CTA index on every rank) then covers them
+        for (int p = 0; p < a.size; ++p) {
+            const int o = (a.rank + p) % a.size;
+            const int o0 = o * a.rpr, o1 = min(a.rows, o0 + a.rpr);
+            const long long n_o = (long long)max(0, o1 - o0) * per_row;
+            for (long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x; c < n_o; c += (long long)gridDim.x * blockDim.x) {
+                const int lr = (int)(c / per_row), col = (int)(c % per_row) << 3;
+                const uint4 v = *reinterpret_cast<const uint4*>(a.partial + (size_t)(o0 + lr) * a.ld_partial + col);
+                *reinterpret_cast<uint4*>(a.recv[o] + ((size_t)a.rank * a.rpr + lr) * a.ld + col) = v;
+            }
+        }
+    }
     if (!peer_barrier(a.flags, a.size, a.rank, 0, val, &s_fail, budget)) {
         if (threadIdx.x == 0) set_status(a.status, PS_DEV_WAIT_TIMEOUT);
         return;
     }
     const int m0 = a.rank * a.rpr, m1 = min(a.rows, m0 + a.rpr);
-    const int per_row = a.n >> 3;
     const long long chunks = (long long)max(0, m1 - m0) * per_row;
     for (long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x; c < chunks; c += (long long)gridDim.x * blockDim.x) {
         const int lr = (int)(c / per_row), col = (int)(c % per_row) << 3;
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int r = 0; r < a.size; ++r)
-            acc_bf16x8(acc, __ldcv(reinterpret_cast<const uint4*>(a.recv + ((size_t)r * a.rpr + lr) * a.ld + col)));
         const int row = m0 + lr;
+        uint4 pv[kArMaxRanks];
+#pragma unroll
+        for (int r = 0; r < kArMaxRanks; ++r)            // all loads in flight before the first add
+            if (r < a.size) pv[r] = __ldcv(reinterpret_cast<const uint4*>(a.src[r] + (size_t)(row - a.src_row0) * a.ld + col));
+#pragma unroll
+        for (int r = 0; r < kArMaxRanks; ++r)
+            if (r < a.size) acc_bf16x8(acc, pv[r]);
         if (a.residual != nullptr) {
             const uint4 rv = *reinterpret_cast<const uint4*>(a.residual + (size_t)row * a.ld_res + col);
             const uint32_t w[4] = {rv.x, rv.y, rv.z, rv.w};

@@ -85,6 +85,11 @@ class Qwen35Runner:
             # are still being multiplied; the owners reduce, add the residual and hand the rows to everybody
             ops.linear(inp, W, name="tp_partial", tp_scatter=tp.scatter_for(rows, W.N))
             return tp.reduce_gather(rows, W.N, residual, name), None
+        if (tp.transport == "fused" and hasattr(ops, "buf") and W.N % 8 == 0 and rows >= tp.size
+                and getattr(tp, "use_scatter", True)):
+            # projection kernels that cannot push: the collective kernel deals the partial to the owners itself
+            part = ops.linear(inp, W, name="tp_partial")
+            return tp.reduce_gather(rows, W.N, residual, name, partial=part), None
         part = ops.linear(inp, W, name="tp_partial")
         out = ops.buf(name, rows, W.N) if hasattr(ops, "buf") else torch.empty_like(part)
         return tp.all_reduce_residual(part, residual, out), None

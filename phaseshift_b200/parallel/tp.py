@@ -62,14 +62,15 @@ class TpScatterStruct(ctypes.Structure):
 class RgStruct(ctypes.Structure):
     """Host twin of ps::RgArgs (csrc/kernels/allreduce.cu)."""
     _fields_ = [("size", ctypes.c_int), ("rank", ctypes.c_int), ("rows", ctypes.c_int), ("n", ctypes.c_int), ("rpr", ctypes.c_int),
-                ("recv", ctypes.c_void_p), ("ld", ctypes.c_int),
+                ("src", ctypes.c_void_p * MAX_RANKS), ("src_row0", ctypes.c_int), ("ld", ctypes.c_int),
+                ("partial", ctypes.c_void_p), ("ld_partial", ctypes.c_int), ("recv", ctypes.c_void_p * MAX_RANKS),
                 ("flags", ctypes.c_void_p * MAX_RANKS), ("counter", ctypes.c_void_p),
                 ("residual", ctypes.c_void_p), ("ld_res", ctypes.c_int),
                 ("out", ctypes.c_void_p * MAX_RANKS), ("ldo", ctypes.c_int), ("status", ctypes.c_void_p)]
 
 
 AR_GRID = 128
-RG_GRID = 96
+RG_GRID = 296
 
 
 class TensorParallel:
@@ -194,15 +195,27 @@ class TensorParallel:
             c.recv[r] = st["recv_ptrs"][r]
         return c
 
-    def reduce_gather(self, rows: int, n: int, residual: Optional[torch.Tensor], name: str) -> torch.Tensor:
-        """Second half of the scatter path: sum of the pushed partials of this rank's rows + residual, finished rows
-        stored to every rank.  Returns this rank's (complete) output [rows, n]."""
+    def reduce_gather(self, rows: int, n: int, residual: Optional[torch.Tensor], name: str,
+                      partial: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Sum of the ranks' partials of this rank's rows + residual, finished rows stored to every rank.  Returns this
+        rank's (complete) output [rows, n].  The partials were pushed into the receive buffers by the projection kernel
+        (``scatter_for``), or -- ``partial`` given: this rank's whole partial product [rows, n] bf16, any local
+        memory -- are dealt to their owners by the same kernel first (a two-shot all-reduce with remote stores only)."""
         from ..ops import _lib
         st = self._rs_state(rows, n)
         out, out_ptrs = self._rs_out(st, name, rows, n)
         a = RgStruct()
         a.size, a.rank, a.rows, a.n, a.rpr = self.size, self.rank, rows, n, -(-rows // self.size)
-        a.recv, a.ld = st["recv"].data_ptr(), n
+        a.ld = n
+        a.src_row0 = a.rank * a.rpr
+        for r in range(self.size):
+            a.src[r] = st["recv"].data_ptr() + r * a.rpr * n * 2
+            a.recv[r] = st["recv_ptrs"][r]
+        if partial is not None:
+            assert partial.dtype == torch.bfloat16 and partial.stride(1) == 1 and partial.stride(0) % 8 == 0
+            a.partial, a.ld_partial = partial.data_ptr(), partial.stride(0)
+        else:
+            a.partial, a.ld_partial = None, 0
         for r in range(self.size):
             a.flags[r] = st["flag_ptrs"][r]
             a.out[r] = out_ptrs[r]
@@ -215,13 +228,15 @@ class TensorParallel:
             word = st.setdefault("status", torch.zeros(1, dtype=torch.int32, device=self.device))
         a.status = word.data_ptr()
         _lib.call("ps_tp_reduce_gather", ctypes.byref(a), ctypes.c_int(RG_GRID))
-        self.stats["scatter"] = self.stats.get("scatter", 0) + 1
+        key = "two_shot" if partial is not None else "scatter"
+        self.stats[key] = self.stats.get(key, 0) + 1
         return out[:rows]
 
     def max_fused_rows(self, W) -> int:
-        """Rows up to which a row-parallel projection over `W` combines inside its own kernel: 32 on the
-        block-scaled tensor-core path, 8 on the streaming kernel."""
-        return MAX_ROWS if getattr(W, "sf_atoms", None) is not None else 8
+        """Rows up to which a row-parallel projection over `W` combines inside its own kernel: 16 on the block-scaled
+        tensor-core path (its one-shot push of fp32 partials to every rank stops paying beyond that; the receive
+        buffers hold 32 rows), 8 on the streaming kernel."""
+        return 16 if getattr(W, "sf_atoms", None) is not None else 8
 
     def combine_for(self, n: int) -> Optional[TpCombineStruct]:
         """Fused-combine descriptor for projections with `n` output features (allocated on first use;
