@@ -296,7 +296,7 @@ def build_runtime(a):
                             kv_cache_capacity_tokens=a.kv_cache_capacity_tokens or (a.max_concurrent_requests + 1) * (a.max_seq_len + 1),
                             kv_cache_dtype=a.kv_cache_dtype, prefix_cache_capacity_tokens=a.prefix_cache_capacity_tokens,
                             prefix_cache_max_entries=a.prefix_cache_max_entries, constraint_tokenizer_info=None,
-                            verify_weights=a.verify_weights, dflash2_model_dir=None, dflash2_drafts=a.dflash2_drafts,
+                            verify_weights=a.verify_weights, dflash2_model_dir=a.dflash2_model_dir, dflash2_drafts=a.dflash2_drafts,
                             dflash2_ngram_tail=0, dflash2_ngram_n=0, max_scheduled_tokens=2048)
     rt = ComputeRuntime(ns)
     tok = load_tokenizer(a.model_dir, rt.cfg.vocab_size)

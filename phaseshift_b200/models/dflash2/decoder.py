@@ -143,32 +143,59 @@ class DFlash2SpecDecoder:
         self.drafter.context_len = pos0 + keep
 
     # ------------------------------------------------------------------ phases
-    def prefill(self, s, prompt: Sequence[int], chunk: int, samp: dict) -> int:
+    def _masks(self, matcher, drafts: Sequence[int]):
+        """Allowed-token bitmasks for verify rows [anchor, drafts...] under a grammar matcher: row i constrains the
+        token that follows drafts[:i] (reference: dflash2_spec_decoder.cpp:99, token_constraint.cpp:114).  Drafts the
+        grammar rejects, and everything after them, are dropped from the block.  Returns (kept drafts, mask, active)."""
+        words = (self.eng.cfg.vocab_size + 31) // 32
+        mask = torch.full((len(drafts) + 1, words), -1, dtype=torch.int32)
+        ok = matcher.fill_draft_masks(list(drafts), mask)
+        dev = self.eng.device
+        return list(drafts[:ok]), mask[:ok + 1].to(dev), torch.ones(ok + 1, dtype=torch.uint8).to(dev)
+
+    def prefill_chunk(self, s, ids: Sequence[int], last: bool, samp: dict, matcher=None) -> Optional[int]:
+        """One prefill chunk: runs the target on it, appends its tapped hidden states to the drafter's ring (the
+        reference appends per chunk too, dflash2_spec_decoder.cpp:416-520); the last chunk samples the first token."""
+        pos0 = s.position
+        kw = {}
+        if last and matcher is not None:
+            _, kw["mask"], kw["mask_active"] = self._masks(matcher, [])
+        toks, out = self.eng.step([SeqRows(s.slot, pos0, list(ids), (len(ids) - 1,) if last else (), sample_index=0, **samp)],
+                                  [s], tap_layers=self.taps, **kw)
+        self._append_taps(out, len(ids), pos0, ids)
+        if toks and matcher is not None:
+            matcher.accept(toks[0])
+        return toks[0] if toks else None
+
+    def prefill(self, s, prompt: Sequence[int], chunk: int, samp: dict, matcher=None) -> int:
         tok = None
         for c0 in range(0, len(prompt), chunk):
-            ids = list(prompt[c0:c0 + chunk])
-            last = c0 + chunk >= len(prompt)
-            pos0 = s.position
-            toks, out = self.eng.step([SeqRows(s.slot, pos0, ids, (len(ids) - 1,) if last else (), sample_index=0, **samp)],
-                                      [s], tap_layers=self.taps)
-            self._append_taps(out, len(ids), pos0, ids)
-            if toks:
-                tok = toks[0]
+            t = self.prefill_chunk(s, prompt[c0:c0 + chunk], c0 + chunk >= len(prompt), samp, matcher)
+            if t is not None:
+                tok = t
         return tok
 
-    def round(self, s, anchor: int, generated: List[int], remaining: int, samp: dict) -> List[int]:
-        """Advance by one speculative round; returns the tokens emitted (1 .. K+1)."""
+    def round(self, s, anchor: int, generated: List[int], remaining: int, samp: dict, matcher=None) -> List[int]:
+        """Advance by one speculative round; returns the tokens emitted (1 .. K+1).  ``matcher``: a grammar matcher
+        (runtime/constraints.py) that has accepted everything up to and including ``anchor``; every verify row is then
+        sampled under the mask of its own prefix, and the matcher is advanced over the emitted tokens."""
         eng = self.eng
         room = eng.sc.max_seq_len - s.position
         k = max(0, min(self.k, remaining - 1, room - 1))
         pos0 = s.position
         if k == 0:
+            kw = {}
+            if matcher is not None:
+                _, kw["mask"], kw["mask_active"] = self._masks(matcher, [])
             toks, out = eng.step([SeqRows(s.slot, pos0, [anchor], (0,), sample_index=len(generated) + 1, **samp)], [s],
-                                 tap_layers=self.taps)
+                                 tap_layers=self.taps, **kw)
             self._append_taps(out, 1, pos0, [anchor])
             self.stats["plain_steps"] += 1
+            if matcher is not None:
+                matcher.accept(toks[0])
             return [toks[0]]
-        on_device = hasattr(self.drafter, "propose_device") and not (self.ngram_tail and self.ngram_n)
+        on_device = (hasattr(self.drafter, "propose_device") and not (self.ngram_tail and self.ngram_n)
+                     and matcher is None)
         if on_device:
             # the drafts never visit the host before verification: the verify step reads them from the device and
             # brings them back together with its samples -- one host synchronisation per round
@@ -184,11 +211,14 @@ class DFlash2SpecDecoder:
             if self.ngram_tail and self.ngram_n:
                 drafts = drafts + self.rt.ngram_tail(generated + [anchor] + drafts, self.ngram_n,
                                                      min(self.ngram_tail, max(0, remaining - 1 - len(drafts))))
+            kw = {}
+            if matcher is not None:
+                drafts, kw["mask"], kw["mask_active"] = self._masks(matcher, drafts)
             rows = [anchor] + drafts
             n = len(rows)
             toks, out = eng.step([SeqRows(s.slot, pos0, rows, tuple(range(n)), sample_index=len(generated) + 1, **samp)], [s],
                                  commit=False, tap_layers=self.taps, gdn_log=self.logs, gdn_to_alt=True,
-                                 exact=self.verify_exact)
+                                 exact=self.verify_exact, **kw)
         accepted, nxt, full = self.rt.spec_greedy_accept(drafts, toks)
         keep = accepted + 1                                  # anchor + accepted drafts are now part of the sequence
         st = eng.state
@@ -205,7 +235,11 @@ class DFlash2SpecDecoder:
         self.stats["rounds"] += 1
         self.stats["accepted"] += accepted
         self.stats["proposed"] += len(drafts)
-        return drafts[:accepted] + [nxt]
+        emitted = drafts[:accepted] + [nxt]
+        if matcher is not None:
+            for t in emitted:
+                matcher.accept(t)
+        return emitted
 
     # ------------------------------------------------------------------ one request
     def generate(self, prompt: Sequence[int], max_new_tokens: int, stop_tokens: Sequence[int] = (), prefill_chunk: int = 2048,

@@ -48,6 +48,10 @@ class TokenConstraintState:
         for i, t in enumerate(drafts):
             if not self.accept(t):
                 break
+            if self.terminated():
+                # a draft that completes the grammar has no successor row to mask: leave it for the target to sample
+                self.rollback(1)
+                break
             ok += 1
             self.fill_next_mask(out[i + 1])
         if ok:

@@ -94,6 +94,45 @@ def test_serve_stdio_protocol(model_dir):
             p.kill()
 
 
+def test_serve_stdio_with_speculative_decoding(model_dir, tmp_path):
+    """--dflash2-model-dir under --serve-stdio: requests are served through speculative rounds and emit exactly the
+    plain greedy stream."""
+    from phaseshift_b200.models.dflash2.model import DFlash2Drafter, random_weights, tiny_drafter_config
+    cfg, hf, d = model_dir
+    dcfg = tiny_drafter_config(cfg)
+    ddir = tmp_path / "drafter"
+    DFlash2Drafter(dcfg, random_weights(dcfg, seed=1), "cpu").save(ddir)
+    p = subprocess.Popen([sys.executable, "-m", "phaseshift_b200.apps.compute", "--model-dir", str(d), "--device", "cpu",
+                          "--serve-stdio", "--max-seq-len", "128", "--dflash2-model-dir", str(ddir), "--dflash2-drafts", "4",
+                          "--max-scheduled-tokens", "8"],
+                         stdin=subprocess.PIPE, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, cwd=ROOT,
+                         env=dict(os.environ, PYTHONPATH=ROOT))
+    try:
+        assert "PHASESHIFT_SERVE_READY" in p.stderr.readline()
+        ids = list(range(5, 25))
+        for rid, n in ((1, 12), (2, 7)):
+            p.stdin.write(json.dumps({"op": "generate", "request_id": rid, "input_ids": ids[:20 - rid], "max_new_tokens": n}) + "\n")
+        p.stdin.flush()
+        toks, done = {1: [], 2: []}, {}
+        while len(done) < 2:
+            e = json.loads(p.stdout.readline())
+            if e["event"] == "token":
+                toks[e["request_id"]].append(e["token_id"])
+            elif e["event"] == "done":
+                done[e["request_id"]] = e
+            else:
+                raise AssertionError(e)
+        assert toks[1] == done[1]["generated_ids"] == reference_greedy(cfg, hf, ids[:19], 12)
+        assert toks[2] == done[2]["generated_ids"] == reference_greedy(cfg, hf, ids[:18], 7)
+        assert done[1]["prefill_tokens"] == 19
+        p.stdin.write(json.dumps({"op": "shutdown"}) + "\n"); p.stdin.flush()
+        assert json.loads(p.stdout.readline()) == {"event": "shutdown"}
+        assert p.wait(timeout=30) == 0
+    finally:
+        if p.poll() is None:
+            p.kill()
+
+
 def test_quantizer_cli(model_dir, tmp_path, capsys):
     cfg, hf, d = model_dir
     out = tmp_path / "q"

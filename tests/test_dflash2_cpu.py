@@ -79,3 +79,84 @@ def test_drafter_config_validation_and_save_load(tmp_path):
         DFlash2Config(is_causal=True)
     with pytest.raises(ValueError):
         DFlash2Config(target_layer_ids=[3, 3])
+
+
+def test_sampled_stream_with_always_accepting_drafter_equals_plain_sampling(setup):
+    """temperature > 0: verification compares drafts with the target's own samples, each row drawing with
+    sample_index = tokens generated so far + row, so an oracle drafter reproduces Engine.generate token for token."""
+    cfg, ew, prompt, _ = setup
+    samp = dict(temperature=0.9, top_p=0.95, top_k=40, seed=1234)
+    plain = Engine(ew, "cpu", StateConfig(max_slots=1, max_seq_len=96)).generate(prompt, 20, prefill_chunk=8, **samp)
+    assert len(set(plain)) > 4                                   # really sampled, not a constant stream
+    dec = _decoder(cfg, ew, k=5)
+    full = prompt + plain
+    dec.drafter.propose = lambda anchor, k, embed, lm_head, pos_start, allowed=None: full[pos_start + 1: pos_start + 1 + k]
+    out, stats = dec.generate(prompt, 20, prefill_chunk=8, **samp)
+    assert out == plain
+    assert stats["accepted"] == stats["proposed"]
+    # and with the random drafter (rejections, corrections): still the same stream
+    out2, _ = _decoder(cfg, ew, k=4).generate(prompt, 20, prefill_chunk=8, **samp)
+    assert out2 == plain
+
+
+def test_speculative_serving_loop_matches_plain_generation(setup):
+    """The serve path on speculative rounds: queued requests are served one after the other, chunked prefill feeds the
+    drafter's ring per chunk, events carry every token, and the streams equal plain greedy decoding."""
+    from phaseshift_b200.runtime.spec_serving import SpecServingEngine
+    cfg, ew, prompt, ref = setup
+    dec = _decoder(cfg, ew, k=4)
+    srv = SpecServingEngine(dec, prefill_chunk=8)
+    a = srv.submit(prompt, 24)
+    b = srv.submit(prompt[:9], 6)
+    c = srv.submit(prompt[3:], 50)
+    assert srv.cancel(c) and not srv.cancel(c)
+    ev = srv.run_until_idle()
+    assert [e.token_id for e in ev if e.kind == "token" and e.request_id == a] == ref
+    ref_b = Engine(ew, "cpu", StateConfig(max_slots=1, max_seq_len=96)).generate(prompt[:9], 6)
+    assert [e.token_id for e in ev if e.kind == "token" and e.request_id == b] == ref_b
+    done = {e.request_id: e.info for e in ev if e.kind == "done"}
+    assert done[a]["finish_reason"] == "length" and done[a]["generated_ids"] == ref and done[a]["prefill_tokens"] == len(prompt)
+    assert srv.idle() and srv.stats["rounds"] > 0 and not [e for e in ev if e.request_id == c]
+    # a stop token ends the request in the middle of a round
+    d = srv.submit(prompt, 24, stop_tokens=[ref[5]])
+    ev = srv.run_until_idle()
+    toks = [e.token_id for e in ev if e.kind == "token" and e.request_id == d]
+    assert toks == ref[:ref.index(ref[5]) + 1]
+    assert [e.info["finish_reason"] for e in ev if e.kind == "done"] == ["stop"]
+
+
+def test_constrained_speculative_decoding_stays_in_the_grammar():
+    """Grammar masks on every verify row: the emitted stream is a sentence of the grammar and equals what the plain
+    constrained serving loop emits, also when the drafter proposes tokens the grammar forbids."""
+    pytest.importorskip("xgrammar")
+    from phaseshift_b200.runtime.constraints import TokenConstraintCompiler
+    from phaseshift_b200.runtime.serving import ServingEngine
+    from phaseshift_b200.runtime.spec_serving import SpecServingEngine
+    cfg = tiny_config(vocab_size=256)
+    hf = random_hf_weights(cfg, seed=1)
+    ew = build_engine_weights(cfg, lambda n: hf[n], "bf16", "cpu")
+    base = [chr(ord("a") + i) for i in range(26)] + [str(i) for i in range(10)] + ["yes", "no", " ", "{", "}", '"', ":", ","]
+    vocab = base + [f"<t{i}>" for i in range(cfg.vocab_size - len(base))]
+    eos = cfg.vocab_size - 1
+    comp = TokenConstraintCompiler(vocab, cfg.vocab_size, stop_token_ids=[eos], vocab_type="raw")
+    grammar = 'root ::= ("yes" | "no") " " [0-9] [0-9] [a-f] [a-f] [a-f]'
+    plain = ServingEngine(Engine(ew, "cpu", StateConfig(max_slots=1, max_seq_len=64)), constraint_compiler=comp)
+    rid = plain.submit([1, 2, 3, 4], 16, stop_tokens=[eos], grammar=grammar)
+    want = [e.token_id for e in plain.run_until_idle() if e.kind == "token" and e.request_id == rid]
+    eng = Engine(ew, "cpu", StateConfig(max_slots=1, max_seq_len=64, conv_ring=16, spec_rows=8))
+    dcfg = tiny_drafter_config(cfg)
+    for mode in ("random", "oracle"):
+        dr = DFlash2Drafter(dcfg, random_weights(dcfg, seed=1), "cpu")
+        dec = DFlash2SpecDecoder(eng, dr, num_drafts=4)
+        if mode == "oracle":
+            full = [1, 2, 3, 4] + want
+            dr.propose = lambda anchor, k, embed, lm_head, pos_start, allowed=None: full[pos_start + 1: pos_start + 1 + k]
+        srv = SpecServingEngine(dec, constraint_compiler=comp)
+        rid = srv.submit([1, 2, 3, 4], 16, stop_tokens=[eos], grammar=grammar)
+        ev = srv.run_until_idle()
+        got = [e.token_id for e in ev if e.kind == "token" and e.request_id == rid]
+        assert got == want, (mode, got, want)
+        text = "".join(vocab[t] for t in got if t != eos)
+        assert text.split(" ")[0] in ("yes", "no") and len(text.split(" ")[1]) == 5
+        if mode == "oracle":
+            assert dec.stats["accepted"] > 0
