@@ -24,6 +24,7 @@ def _model_args(p):
     p.add_argument("--preset", default=None); p.add_argument("--device", default=None)
     p.add_argument("--kv-cache-dtype", default="bf16", choices=["bf16", "fp8_e4m3"])
     p.add_argument("--runs", type=int, default=3); p.add_argument("--warmup", type=int, default=1); p.add_argument("--output")
+    p.add_argument("--tp", type=int, default=1, choices=[1, 2, 4, 8], help="tensor-parallel ranks, one process per GPU")
 
 
 def build_parser() -> argparse.ArgumentParser:
@@ -69,13 +70,23 @@ def _engine(a, max_seq_len: int, slots: int = 1, spec_rows: int = 0):
     from ..runtime.engine import Engine
     from ..runtime.state import StateConfig
     dev = torch.device(a.device or ("cuda:0" if torch.cuda.is_available() else "cpu"))
+    tp, tp_kw = None, {}
+    if getattr(a, "tp", 1) > 1:
+        # every rank runs the same deterministic script (same requests, same scheduler decisions); rank 0 reports
+        import os
+        from ..parallel.launch import init_tensor_parallel, spawn_ranks
+        spawn_ranks(a.tp, "phaseshift_b200.apps.bench", sys.argv[1:])
+        tp, dev, _ = init_tensor_parallel(dev.type)
+        tp_kw = dict(tp_rank=tp.rank, tp_size=tp.size)
+        if tp.rank != 0:
+            sys.stdout = open(os.devnull, "w")
     if a.model_dir:
-        ew = load_engine_weights(a.model_dir, dev, a.preset, keep_canonical=dev.type != "cuda")
+        ew = load_engine_weights(a.model_dir, dev, a.preset, keep_canonical=dev.type != "cuda", **tp_kw)
     else:
         cfg = PRESETS[a.random_model or "tiny"]()
-        ew = build_engine_weights(cfg, random_getter(cfg, 0, dev), a.preset or "bf16", dev, keep_canonical=dev.type != "cuda")
+        ew = build_engine_weights(cfg, random_getter(cfg, 0, dev), a.preset or "bf16", dev, keep_canonical=dev.type != "cuda", **tp_kw)
     extra = dict(conv_ring=max(16, 3 + spec_rows), spec_rows=spec_rows) if spec_rows else {}
-    return Engine(ew, dev, StateConfig(max_slots=slots, max_seq_len=max_seq_len, kv_dtype=a.kv_cache_dtype, **extra)), dev
+    return Engine(ew, dev, StateConfig(max_slots=slots, max_seq_len=max_seq_len, kv_dtype=a.kv_cache_dtype, **extra), tp=tp), dev
 
 
 def _timed(dev, fn):

@@ -47,6 +47,9 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--dflash2-ngram-n", type=int, default=0)
     ap.add_argument("--dflash2-stats", type=int, default=0, choices=[0, 1])
     ap.add_argument("--serve-stdio", action="store_true")
+    ap.add_argument("--tp", type=int, default=1, choices=[1, 2, 4, 8],
+                    help="tensor-parallel ranks (one process per GPU; this process becomes rank 0 and starts the others)")
+    ap.add_argument("--perf-stats-output", help="write launch / timing / fallback counters of the run as JSON")
     ap.add_argument("--max-scheduled-tokens", type=int, default=2048)
     return ap
 
@@ -69,6 +72,8 @@ def validate_args(a) -> Optional[str]:
         return "--dflash2-drafts must be in [1, 15]"
     if a.dflash2_ngram_tail and not a.dflash2_model_dir:
         return "--dflash2-ngram-tail needs --dflash2-model-dir"
+    if getattr(a, "tp", 1) > 1 and a.dflash2_model_dir:
+        return "--tp with --dflash2-model-dir is not supported (the drafter is not tensor parallel)"
     return None
 
 
@@ -85,19 +90,26 @@ class ComputeRuntime:
         from ..runtime.state import StateConfig
         dev = a.device or ("cuda:0" if torch.cuda.is_available() else "cpu")
         self.device = torch.device(dev)
+        self.tp, self.host_group, self.rank = None, None, 0
+        tp_kw = {}
+        if getattr(a, "tp", 1) > 1:
+            from ..parallel.launch import init_tensor_parallel
+            self.tp, self.device, self.host_group = init_tensor_parallel(self.device.type)
+            self.rank = self.tp.rank
+            tp_kw = dict(tp_rank=self.tp.rank, tp_size=self.tp.size)
         if a.random_model:
             cfg = PRESETS[a.random_model]()
             ew = build_engine_weights(cfg, random_getter(cfg, 0, self.device), a.preset or "bf16", self.device,
-                                      keep_canonical=self.device.type != "cuda")
+                                      keep_canonical=self.device.type != "cuda", **tp_kw)
         else:
             ew = load_engine_weights(a.model_dir, self.device, a.preset, verify_weights=bool(a.verify_weights),
-                                     keep_canonical=self.device.type != "cuda")
+                                     keep_canonical=self.device.type != "cuda", **tp_kw)
         self.cfg = ew.cfg
         spec = bool(a.dflash2_model_dir)
         sc = StateConfig(max_slots=a.max_concurrent_requests, max_seq_len=a.max_seq_len, page_tokens=a.page_tokens,
                          kv_capacity_tokens=a.kv_cache_capacity_tokens, kv_dtype=a.kv_cache_dtype,
                          conv_ring=32 if spec else 4, spec_rows=a.dflash2_drafts + 1 if spec else 0)
-        self.engine = Engine(ew, self.device, sc)
+        self.engine = Engine(ew, self.device, sc, tp=self.tp)
         compiler = None
         if a.constraint_tokenizer_info:
             from ..runtime.constraints import TokenConstraintCompiler
@@ -254,15 +266,45 @@ def run_serve_stdio(a, rt: ComputeRuntime, fin=None, fout=None) -> int:
 
 
 def main(argv: Optional[List[str]] = None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
     a = build_parser().parse_args(argv)
     err = validate_args(a)
     if err:
         print(f"phaseshift-compute: {err}", file=sys.stderr)
         return 2
+    if a.tp > 1:
+        from ..parallel.launch import spawn_ranks
+        spawn_ranks(a.tp, "phaseshift_b200.apps.compute", argv)
     rt = ComputeRuntime(a)
-    if a.serve_stdio:
-        return run_serve_stdio(a, rt)
-    return run_single_shot(a, rt)
+    rc = 0
+    if a.tp > 1 and a.serve_stdio:
+        # rank 0 owns stdin / stdout; the other ranks replay its commands (runtime/tp_serving.py)
+        from ..runtime.tp_serving import TpServingLeader, follow
+        if rt.rank == 0:
+            rt.serving = TpServingLeader(rt.serving, rt.host_group)
+            try:
+                rc = run_serve_stdio(a, rt)
+            finally:
+                rt.serving.shutdown()
+        else:
+            follow(rt.serving, rt.host_group)
+    elif a.serve_stdio:
+        rc = run_serve_stdio(a, rt)
+    elif rt.rank == 0:
+        rc = run_single_shot(a, rt)
+    else:
+        rc = run_single_shot(a, rt, out=open(os.devnull, "w"))     # every rank runs the same request; rank 0 reports
+    if a.perf_stats_output and rt.rank == 0:
+        from ..utils.perf_stats import collect
+        with open(a.perf_stats_output, "w") as f:
+            json.dump(collect(rt.engine, rt.serving), f, indent=1)
+    if rt.tp is not None:
+        import torch.distributed as dist
+        m = getattr(rt.tp, "monitor", None)
+        if m is not None:
+            m.stop()
+        dist.destroy_process_group()
+    return rc
 
 
 if __name__ == "__main__":

@@ -45,6 +45,7 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--dflash2-model-dir"); ap.add_argument("--dflash2-drafts", type=int, default=7)
     ap.add_argument("--model-name", default="phaseshift"); ap.add_argument("--verify-weights", type=int, default=0)
     ap.add_argument("--startup-timeout", type=int, default=120)
+    ap.add_argument("--tp", type=int, default=1, choices=[1, 2, 4, 8], help="tensor-parallel ranks, one process per GPU")
     return ap
 
 
@@ -297,7 +298,7 @@ def build_runtime(a):
                             kv_cache_dtype=a.kv_cache_dtype, prefix_cache_capacity_tokens=a.prefix_cache_capacity_tokens,
                             prefix_cache_max_entries=a.prefix_cache_max_entries, constraint_tokenizer_info=None,
                             verify_weights=a.verify_weights, dflash2_model_dir=a.dflash2_model_dir, dflash2_drafts=a.dflash2_drafts,
-                            dflash2_ngram_tail=0, dflash2_ngram_n=0, max_scheduled_tokens=2048)
+                            dflash2_ngram_tail=0, dflash2_ngram_n=0, max_scheduled_tokens=2048, tp=getattr(a, "tp", 1))
     rt = ComputeRuntime(ns)
     tok = load_tokenizer(a.model_dir, rt.cfg.vocab_size)
     try:
@@ -319,7 +320,22 @@ def main(argv=None) -> int:
         print("phaseshift-server: --model-dir is required", file=sys.stderr)
         return 2
     import uvicorn
+    if a.tp > 1:
+        if a.dflash2_model_dir:
+            print("phaseshift-server: --tp with --dflash2-model-dir is not supported", file=sys.stderr)
+            return 2
+        from ..parallel.launch import spawn_ranks
+        spawn_ranks(a.tp, "phaseshift_b200.apps.server", list(sys.argv[1:] if argv is None else argv))
     rt, tok, stop = build_runtime(a)
+    if a.tp > 1:
+        # rank 0 serves HTTP; the other ranks replay its commands (runtime/tp_serving.py)
+        from ..runtime.tp_serving import TpServingLeader, follow
+        if rt.rank != 0:
+            follow(rt.serving, rt.host_group)
+            return 0
+        import atexit
+        rt.serving = TpServingLeader(rt.serving, rt.host_group)
+        atexit.register(rt.serving.shutdown)
     app = create_app(rt.serving, tok, a.model_name, a.default_max_output_tokens, stop, a.max_seq_len)
     print(f"phaseshift-server: model={a.model_name} ctx={a.max_seq_len} concurrency={a.max_concurrent_requests} "
           f"prefix_cache={a.prefix_cache_capacity_tokens}x{a.prefix_cache_max_entries} http://{a.host}:{a.port}", file=sys.stderr)

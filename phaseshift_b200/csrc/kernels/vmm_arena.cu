@@ -3,7 +3,7 @@
 // are unmapped/released from the tail when it shrinks, so tensors placed in the arena keep their
 // addresses for the life of the process (CUDA graphs and peer mappings stay valid) while HBM is only
 // spent on what is in use.  The reference's GpuArena reserves `--arena-gib` with one hipMalloc and bump
-// allocates inside it (include/phaseshift/core/gpu_arena.h); on a 180 GB part the reservation can be the
+// allocates inside it (include/phaseshift/core/memory/arena.h:14-62, src/phaseshift/core/memory/arena.hip:48-138); on a 180 GB part the reservation can be the
 // whole address budget while the commitment follows the KV cache.
 //
 // Host-only code; the driver entry points are resolved through the runtime, so the library needs no

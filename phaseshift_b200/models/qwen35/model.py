@@ -100,12 +100,13 @@ class Qwen35Runner:
         cfg, ops, st, w = self.cfg, self.ops, self.state, self.w
         eps = cfg.rms_norm_eps
         x_ssq = None
-        if self.use_ssq and rows <= 32:
-            e_ssq = ops.ssq_buf("embed", rows)
-            x = ops.embed(b, rows, w.embed, st.status, ssq_out=e_ssq)
-            x_ssq = (e_ssq, 1)
-        else:
-            x = ops.embed(b, rows, w.embed, st.status)
+        with ops.range("embed"):
+            if self.use_ssq and rows <= 32:
+                e_ssq = ops.ssq_buf("embed", rows)
+                x = ops.embed(b, rows, w.embed, st.status, ssq_out=e_ssq)
+                x_ssq = (e_ssq, 1)
+            else:
+                x = ops.embed(b, rows, w.embed, st.status)
         taps = {}
         taps_cat = None
         if tap_layers and hasattr(ops, "buf"):
@@ -119,6 +120,8 @@ class Qwen35Runner:
             if L.kind == 0:
                 self._tap(lp + "linear_attn.in_proj_qkv.weight", x, b.n_rows, L.input_norm)
                 n_main = m.in_proj.N
+                rng = ops.range("gdn.in_proj")
+                rng.__enter__()
                 if hasattr(ops, "buf"):
                     proj = ops.buf("gdn_proj", rows, n_main + m.ba_proj.N)
                     batched = rows >= 2 and m.in_proj.rowmajor_bf16 is not None and not ops.exact_rows
@@ -133,30 +136,41 @@ class Qwen35Runner:
                         ops.linear(x, m.in_proj, name="gdn_in", norm_w=L.input_norm, eps=eps, out=proj[:, :n_main],
                                    ssq_in=x_ssq, prefetch=m.out_proj)
                         ops.linear(x, m.ba_proj, name="gdn_ba", norm_w=L.input_norm, eps=eps, out=proj[:, n_main:])
-                    o = ops.gdn(proj, m, self.hk, self.hv, b, st.gdn[li], st,
-                                log=None if gdn_log is None else gdn_log[li], to_alt=gdn_to_alt, xn=xn)
+                    rng.__exit__(None, None, None)
+                    with ops.range("gdn.mixer"):
+                        o = ops.gdn(proj, m, self.hk, self.hv, b, st.gdn[li], st,
+                                    log=None if gdn_log is None else gdn_log[li], to_alt=gdn_to_alt, xn=xn)
                 else:
                     proj = torch.cat([ops.linear(x, m.in_proj, name="gdn_in", norm_w=L.input_norm, eps=eps),
                                       ops.linear(x, m.ba_proj, name="gdn_ba", norm_w=L.input_norm, eps=eps)], 1)
-                    o = ops.gdn(proj, m, self.hk, self.hv, b, st.gdn[li], st,
-                                log=None if gdn_log is None else gdn_log[li], to_alt=gdn_to_alt)
+                    rng.__exit__(None, None, None)
+                    with ops.range("gdn.mixer"):
+                        o = ops.gdn(proj, m, self.hk, self.hv, b, st.gdn[li], st,
+                                    log=None if gdn_log is None else gdn_log[li], to_alt=gdn_to_alt)
                 self._tap(lp + "linear_attn.out_proj.weight", o, b.n_rows)
-                r, r_ssq = self._row_parallel(o, m.out_proj, x, "r", rows, L.gate_up)
+                with ops.range("gdn.out_proj"):
+                    r, r_ssq = self._row_parallel(o, m.out_proj, x, "r", rows, L.gate_up)
             else:
                 self._tap(lp + "self_attn.q_proj.weight", x, b.n_rows, L.input_norm)
-                qkv = ops.linear(x, m.qkv_proj, name="attn_qkv", norm_w=L.input_norm, eps=eps,
-                                 **({"ssq_in": x_ssq, "prefetch": m.o_proj} if self.use_ssq else {}))
-                q = ops.attn_prep(qkv, m, self.hq, self.hkv, b, st.kv[li], st)
-                ctx = ops.paged_attention(q, qkv, self.hq, self.hkv, b, st.kv[li], st, b.max_visible_launch)
+                with ops.range("attn.qkv_proj"):
+                    qkv = ops.linear(x, m.qkv_proj, name="attn_qkv", norm_w=L.input_norm, eps=eps,
+                                     **({"ssq_in": x_ssq, "prefetch": m.o_proj} if self.use_ssq else {}))
+                with ops.range("attn.prep"):
+                    q = ops.attn_prep(qkv, m, self.hq, self.hkv, b, st.kv[li], st)
+                with ops.range("attn.core"):
+                    ctx = ops.paged_attention(q, qkv, self.hq, self.hkv, b, st.kv[li], st, b.max_visible_launch)
                 self._tap(lp + "self_attn.o_proj.weight", ctx, b.n_rows)
-                r, r_ssq = self._row_parallel(ctx, m.o_proj, x, "r", rows, L.gate_up)
+                with ops.range("attn.o_proj"):
+                    r, r_ssq = self._row_parallel(ctx, m.o_proj, x, "r", rows, L.gate_up)
             self._tap(lp + "mlp.gate_proj.weight", r, b.n_rows, L.post_norm)
-            act = ops.linear(r, L.gate_up, name="mlp_act", norm_w=L.post_norm, eps=eps, swiglu=True,
-                             **({"ssq_in": r_ssq, "prefetch": L.down} if self.use_ssq else {}))
+            with ops.range("mlp.gate_up"):
+                act = ops.linear(r, L.gate_up, name="mlp_act", norm_w=L.post_norm, eps=eps, swiglu=True,
+                                 **({"ssq_in": r_ssq, "prefetch": L.down} if self.use_ssq else {}))
             self._tap(lp + "mlp.down_proj.weight", act, b.n_rows)
             # ping-pong the residual stream so a layer never writes the buffer it still reads
             xname = "x_a" if (li & 1) == 0 else "x_b"
-            x, x_ssq = self._row_parallel(act, L.down, r, xname, rows, self._first_proj(li + 1))
+            with ops.range("mlp.down"):
+                x, x_ssq = self._row_parallel(act, L.down, r, xname, rows, self._first_proj(li + 1))
             if li in tap_layers:
                 if taps_cat is None:
                     taps[li] = x
@@ -170,8 +184,10 @@ class Qwen35Runner:
             else:
                 hidden, h_ssq = ops.gather_rows(x, b.out_rows, n_out, "out_hidden", st.status), None
             self._tap(_P + "lm_head.weight", hidden, n_out, w.final_norm)
-            logits = ops.linear(hidden, w.lm_head, name="logits", norm_w=w.final_norm, eps=eps, out_f32=True,
-                                **({"ssq_in": h_ssq} if self.use_ssq else {}))
+            with ops.range("head.lm_head"):
+                logits = ops.linear(hidden, w.lm_head, name="logits", norm_w=w.final_norm, eps=eps, out_f32=True,
+                                    **({"ssq_in": h_ssq} if self.use_ssq else {}))
             if sample:
-                tokens = ops.sample(logits, b, n_out, mask=mask, mask_active=mask_active, status=st.status)
+                with ops.range("head.sample"):
+                    tokens = ops.sample(logits, b, n_out, mask=mask, mask_active=mask_active, status=st.status)
         return StepOutput(tokens, logits, hidden, taps, taps_cat)

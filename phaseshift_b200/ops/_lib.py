@@ -7,6 +7,7 @@ run can never silently pass on PyTorch eager code.
 from __future__ import annotations
 
 import ctypes
+import os
 from pathlib import Path
 
 import torch
@@ -29,6 +30,11 @@ def lib() -> ctypes.CDLL:
             except Exception as e:  # pragma: no cover - build environment problem
                 raise KernelLibraryError(f"libps_kernels.so is not built and nvcc failed: {e}") from e
         _LIB = ctypes.CDLL(str(p))
+        ms = os.environ.get("PS_WAIT_BUDGET_MS")
+        if ms:
+            # budget of every bounded device-side wait (peer flags, mbarriers), in milliseconds at ~1.9 GHz
+            _LIB.ps_set_wait_budget.restype = ctypes.c_longlong
+            _LIB.ps_set_wait_budget(ctypes.c_longlong(int(float(ms) * 1.9e6)))
     return _LIB
 
 

@@ -16,6 +16,7 @@ from typing import Dict, Optional, Tuple
 import numpy as np
 import torch
 
+from .trace import OpTrace
 from ..models.qwen35.config import Qwen35Config
 from ..models.qwen35.weights import AttnW, GdnW, LinearW
 from ..runtime.batch import StepBatch
@@ -29,7 +30,7 @@ EPI_STORE, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2
 SMALL_M_MAX = 8
 
 
-class CudaOps:
+class CudaOps(OpTrace):
     act_dtype = torch.bfloat16
     name = "cuda"
     GDN_CHUNKED_MIN_ROWS = 16      # steps with more rows than this use the chunked GDN kernels
@@ -62,6 +63,8 @@ class CudaOps:
         self.force_tc = os.environ.get("PS_FORCE_TC", "0") == "1"   # single-row steps on the tensor-core kernel too
         self.bs_prefetch = os.environ.get("PS_BS_PREFETCH", "1") != "0"
         self._bs_plan_cache: Dict[tuple, bool] = {}
+        self.sel_counts: Dict[str, int] = {"tc_resident": 0, "tc_streamed": 0, "stream": 0, "gemm": 0}   # projection calls per kernel
+        self.fallbacks: Dict[str, int] = {}
 
     # ------------------------------------------------------------------ workspace
     def buf(self, name: str, rows: int, cols: int, dtype=torch.bfloat16) -> torch.Tensor:
@@ -129,6 +132,7 @@ class CudaOps:
         # is resident (Fast mode only: Exact verification stays on the batch-invariant streaming kernel)
         batched = (M >= 2 and W.rowmajor_bf16 is not None and tp_combine is None and xn_out is None and self.use_tc_gemm
                    and not self.exact_rows)
+        self.sel_counts["gemm" if (sel == "gemm" or batched) else "stream"] += 1
         if sel == "gemm" or batched:
             return self.linear_large(x, W, name=name, norm_w=norm_w, eps=eps, residual=residual, swiglu=swiglu,
                                      out_f32=out_f32, out=out)
@@ -273,6 +277,9 @@ class CudaOps:
         ws, flags = self._bs_workspace()
         epi = EPI_SWIGLU if swiglu else (EPI_RESIDUAL if residual is not None else EPI_STORE)
         resident = self.bs_resident_ok(W, M)
+        self.sel_counts["tc_resident" if resident else "tc_streamed"] += 1
+        if M <= self.BS_RESIDENT_MAX_ROWS and not resident:
+            self.fallbacks["tc_resident_to_streamed"] = self.fallbacks.get("tc_resident_to_streamed", 0) + 1
         if tp_combine is not None and M > tp_combine.max_rows:
             raise ValueError("the fused tensor-parallel combine is sized for %d rows" % tp_combine.max_rows)
         codes = W.codes

@@ -12,6 +12,8 @@ from __future__ import annotations
 from typing import Optional
 
 import torch
+
+from .trace import OpTrace
 import torch.nn.functional as F
 
 from ..models.qwen35.config import Qwen35Config
@@ -21,7 +23,7 @@ from ..runtime.state import GdnLayerState, KVLayer, ModelState
 from ..utils.sampling import sample_row_host
 
 
-class RefOps:
+class RefOps(OpTrace):
     act_dtype = torch.float32
     name = "ref"
 

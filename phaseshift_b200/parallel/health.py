@@ -8,9 +8,10 @@ counters of its peers.  A peer whose counter has not moved for ``timeout_s`` is 
 that can never complete.  The device side is bounded independently: every in-kernel wait on a peer flag
 gives up after about a second and reports ``PS_DEV_WAIT_TIMEOUT`` through the status word.
 
-The reference's coordinator detects a dead worker through its control pipe and aborts the barrier
-group (src/phaseshift/runtime/tp/tp_barrier_group.cpp:74-119, src/apps/compute/main.cpp:2179); here
-the ranks are SPMD peers, so liveness is a store-based heartbeat.
+The reference runs its ranks as threads of one process and aborts the shared barrier group when one of them
+fails (src/phaseshift/runtime/tp/tp_barrier_group.cpp:60-119,
+src/phaseshift/models/qwen35/runtime/tensor_parallel.cpp:396-515); here the ranks are SPMD processes, so
+liveness is a store-based heartbeat.
 """
 from __future__ import annotations
 

@@ -19,9 +19,9 @@ Two transports implement the combine:
   path used on CPU (gloo) by the host-logic tests.
 
 Transport selection mirrors ``create_tp_transport`` + ``verify()`` in the reference
-(src/phaseshift/runtime/tp/tp_transports.cpp:81-110, hip_peer_tp_transport.hip:200-312): the fused
-transport is used only after a self-test round against the NCCL sum passes on every rank; otherwise
-the engine falls back to NCCL loudly.
+(src/phaseshift/runtime/tp/tp_transports.cpp:81-110, hip_peer_tp_transport.hip:200-312): the engine runs
+``TensorParallel.verify`` at construction -- a self-test round against the NCCL sum on every rank -- and falls back
+to NCCL loudly if any rank fails it.
 """
 from __future__ import annotations
 
@@ -128,7 +128,11 @@ class TensorParallel:
         return self._ar
 
     def peer_all_reduce(self, partial: torch.Tensor, residual: Optional[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
-        """out = sum over ranks of `partial` (+ residual) with this package's peer-memory kernel."""
+        """out = sum over ranks of `partial` (+ residual) with the one-shot peer / multimem kernels (benchmarks and
+        tests; the engine's collectives are `combine_for`, `scatter_for` + `reduce_gather`).  The input double buffer
+        is selected by a parity kept on the HOST, so calls must not be captured into a CUDA graph."""
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("peer_all_reduce keeps its buffer parity on the host and cannot be graph-captured")
         from ..ops import _lib
         rows, n = partial.shape
         nbytes = rows * n * 2
@@ -265,9 +269,12 @@ class TensorParallel:
     # ------------------------------------------------------------------ baseline combine
     def all_reduce_residual(self, partial: torch.Tensor, residual: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         """out = sum_over_ranks(partial) + residual with the library collective (baseline / large rows)."""
-        if (self.transport == "fused" and self.size > 1 and partial.dtype == torch.bfloat16 and partial.is_contiguous()
-                and partial.shape[1] % 8 == 0 and out.dtype == torch.bfloat16):
-            return self.peer_all_reduce(partial, residual, out)
+        if (self.transport == "fused" and self.size > 1 and partial.dtype == torch.bfloat16 and partial.stride(1) == 1
+                and partial.shape[1] % 8 == 0 and partial.stride(0) % 8 == 0 and out.dtype == torch.bfloat16):
+            # two-shot kernel with device-side collective counters (safe inside captured graphs, unlike
+            # `peer_all_reduce`, whose input parity is tracked on the host)
+            out.copy_(self.reduce_gather(partial.shape[0], partial.shape[1], residual, "__ar_out__", partial=partial))
+            return out
         self.stats["nccl"] += 1
         if self.size > 1:
             dist.all_reduce(partial, group=self.group)
@@ -289,6 +296,64 @@ class TensorParallel:
         m = getattr(self, "monitor", None)
         if m is not None:
             m.assert_alive()
+
+    # ------------------------------------------------------------------ transport self-test
+    def verify(self, ops=None) -> bool:
+        """Self-test of the peer-memory transport against the library collective, run once by every rank at engine
+        construction (the reference's transport does the same before it is used,
+        src/phaseshift/runtime/tp/hip_peer_tp_transport.hip:200-312): the two-shot reduce/gather kernel on two payload
+        sizes and -- when an op set is given -- one projection with the in-kernel combine.  Any rank that sees a wrong
+        sum, a disagreement with its peers or a device wait that ran out makes EVERY rank fall back to the library
+        transport (the verdict is itself all-reduced).  Also performs, collectively and up front, the symmetric-memory
+        allocations the first real steps would otherwise do lazily."""
+        if self.transport != "fused" or self.size <= 1:
+            return True
+        dev = self.device
+        ok = True
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        saved = getattr(self, "status_word", None)
+        self.status_word = status
+        try:
+            g = torch.Generator(device=dev).manual_seed(4321 + self.rank)
+            shared = torch.Generator(device=dev).manual_seed(99)
+            for rows, n in ((3, 256), (200, 512)):
+                part = (torch.randn(rows, n, device=dev, generator=g) * 0.5).to(torch.bfloat16)
+                res = torch.randn(rows, n, device=dev, generator=shared).to(torch.bfloat16)
+                got = self.reduce_gather(rows, n, res, "__verify__", partial=part).clone()
+                ref = part.float()
+                dist.all_reduce(ref, group=self.group)
+                ref = ref.to(torch.bfloat16).float() + res.float()
+                ok = ok and bool(((got.float() - ref).abs().max() <= 0.06).item())
+                low = got.float().clone()
+                high = got.float().clone()
+                dist.all_reduce(low, op=dist.ReduceOp.MIN, group=self.group)
+                dist.all_reduce(high, op=dist.ReduceOp.MAX, group=self.group)
+                ok = ok and bool(torch.equal(low, high))              # every rank holds the same bits
+            if ops is not None and hasattr(ops, "linear_bs"):
+                from ..models.qwen35.weights import LinearW
+                from ..quant.formats import quantize, to_kernel_format
+                W = LinearW(to_kernel_format(quantize(torch.randn(256, 128, device=dev, generator=g) * 0.05, "bf16")))
+                x = torch.randn(2, 128, device=dev, generator=g).to(torch.bfloat16)
+                res = torch.randn(2, 256, device=dev, generator=shared).to(torch.bfloat16)
+                got = ops.linear(x, W, name="__verify_lin__", residual=res, tp_combine=self.combine_for(256)).float().clone()
+                ref = x.float() @ W.dense().to(dev).T
+                dist.all_reduce(ref, group=self.group)
+                ok = ok and bool(((got - (ref + res.float())).abs().max() <= 0.06).item())
+            torch.cuda.synchronize(dev)
+            ok = ok and int(status[0]) == 0
+            if ops is not None and getattr(ops, "status", None) is not None:
+                ok = ok and int(ops.status[0]) == 0
+        except Exception as e:      # pragma: no cover - a broken transport must not take the engine down
+            print(f"[tp] rank {self.rank}: transport self-test raised {e!r}", file=sys.stderr)
+            ok = False
+        finally:
+            self.status_word = saved
+        verdict = torch.tensor([1 if ok else 0], dtype=torch.int32, device=dev)
+        dist.all_reduce(verdict, op=dist.ReduceOp.MIN, group=self.group)
+        self.verified = bool(verdict.item())
+        if not self.verified:
+            self.disable_fused("transport self-test failed on at least one rank")
+        return self.verified
 
     def disable_fused(self, why: str) -> None:
         if self.transport == "fused":

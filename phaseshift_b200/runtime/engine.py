@@ -103,18 +103,46 @@ class Engine:
         if tp is not None and tp.size > 1 and tp.transport != "fused":
             # the library all-reduce is not captured into CUDA graphs; only the in-kernel combine is
             self.use_graphs = False
+        if tp is not None and tp.size > 1 and backend == "cuda":
+            # transport self-test + the collective allocations, before the first real step; a failed test drops
+            # every rank to the library transport (which is not graph-captured)
+            tp.status_word = self.ops.status
+            if not tp.verify(self.ops):
+                self.use_graphs = False
         self.h_tokens = torch.zeros(2048, dtype=torch.int32, pin_memory=(self.device.type == "cuda"))
         self.h_status = torch.zeros(2, dtype=torch.int32, pin_memory=(self.device.type == "cuda"))
         self.h_extra = torch.zeros(64, dtype=torch.int32, pin_memory=(self.device.type == "cuda"))
         self.graph_variants = True      # verification / tapped steps replay captured graphs too
         self.graph_refs: Dict[object, object] = {}
         self.steps = 0
+        self.status_errors = 0
         self.act_scales_calibrated = False
         # once per weight set: a second engine over the same weights must run the same arithmetic as the first
         if (calibrate and backend == "cuda" and getattr(weights, "layout", "") in ("tc", "both")
                 and not getattr(weights, "act_scales_calibrated", False)):
             self.calibrate_act_scales()
             weights.act_scales_calibrated = True
+        if tp is not None and tp.size > 1 and backend == "cuda":
+            self._tp_warmup()
+
+    def _tp_warmup(self) -> None:
+        """Tensor parallel: everything a first step would do lazily -- weight tiling, kernel attributes, symmetric
+        buffers of the combine / scatter paths -- happens here on every rank, followed by a barrier, so the ranks enter
+        their first real step together instead of skewed by seconds of one-off host work (device waits are bounded)."""
+        import torch.distributed as dist
+        graphs, self.use_graphs = self.use_graphs, False
+        s = self.open_sequence()
+        try:
+            n = max(1, min(40, self.sc.max_seq_len - 2))
+            self.step([SeqRows(s.slot, 0, [1] * n, (n - 1,))], [s])
+            self.step([SeqRows(s.slot, s.position, [1], (0,))], [s])
+        finally:
+            self.close_sequence(s)
+            self.use_graphs = graphs
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        dist.barrier(self.tp.group)
+        self.steps = 0
 
     def set_uniform_arithmetic(self, on: bool) -> None:
         """Speculative decoding needs every step of a sequence -- single-row decode, multi-row verification, the
@@ -412,12 +440,29 @@ class Engine:
                 out.read_back = read_back.tolist()
         self.steps += 1
         if status != 0:
+            self.status_errors += 1
             self.state.status.zero_()
             if ops_status is not None:
                 ops_status.zero_()
             if hasattr(self.ops, "reset_after_error"):
                 self.ops.reset_after_error()
         return toks, out, status
+
+    def profile_step(self, rows: Sequence[SeqRows], seq_objs: Sequence[Sequence_], **kw) -> Dict[str, dict]:
+        """Run one step eagerly with per-op-family device timing (ops/trace.py).  Returns name -> {calls, ms}; the
+        step itself behaves like ``step(..., commit=False)`` unless told otherwise."""
+        graphs, self.use_graphs = self.use_graphs, False
+        self.ops.collect_times()
+        self.ops.op_times = {}
+        self.ops.timing_enabled = True
+        try:
+            kw.setdefault("commit", False)
+            self.step(rows, seq_objs, **kw)
+        finally:
+            self.ops.timing_enabled = False
+            self.use_graphs = graphs
+        t = self.ops.collect_times()
+        return {k: {"calls": v[0], "ms": round(v[1], 4)} for k, v in sorted(t.items(), key=lambda kv: -kv[1][1])}
 
     # ------------------------------------------------------------------ convenience: one request
     def prefill(self, s: Sequence_, token_ids: Sequence[int], chunk: int = 2048, sample_last: bool = True,

@@ -133,6 +133,48 @@ def test_serve_stdio_with_speculative_decoding(model_dir, tmp_path):
             p.kill()
 
 
+def test_tensor_parallel_apps_on_cpu(model_dir, tmp_path):
+    """--tp 2 on the compute app (gloo ranks on CPU): the process becomes rank 0 and starts rank 1 itself; single shot
+    prints the single-rank stream, and under --serve-stdio rank 1 replays rank 0's commands step for step."""
+    cfg, hf, d = model_dir
+    ids = list(range(5, 25))
+    idf = tmp_path / "ids.txt"
+    idf.write_text(" ".join(map(str, ids)))
+    stats = tmp_path / "perf.json"
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    env.pop("RANK", None); env.pop("WORLD_SIZE", None)
+    r = subprocess.run([sys.executable, "-m", "phaseshift_b200.apps.compute", "--model-dir", str(d), "--device", "cpu", "--tp", "2",
+                        "--input-ids-file", str(idf), "--max-new-tokens", "6", "--max-seq-len", "64",
+                        "--perf-stats-output", str(stats)], capture_output=True, text=True, cwd=ROOT, env=env, timeout=240)
+    assert r.returncode == 0, r.stderr[-2000:]
+    want = reference_greedy(cfg, hf, ids, 6)
+    assert "GENERATED_IDS=" + ",".join(map(str, want)) in r.stdout
+    ps = json.loads(stats.read_text())
+    assert ps["tp"]["size"] == 2 and ps["steps"] > 0 and "serving" in ps
+    p = subprocess.Popen([sys.executable, "-m", "phaseshift_b200.apps.compute", "--model-dir", str(d), "--device", "cpu", "--tp", "2",
+                          "--serve-stdio", "--max-concurrent-requests", "2", "--max-seq-len", "64"],
+                         stdin=subprocess.PIPE, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, cwd=ROOT, env=env)
+    try:
+        assert "PHASESHIFT_SERVE_READY" in p.stderr.readline()
+        for rid, n in ((1, 6), (2, 4)):
+            p.stdin.write(json.dumps({"op": "generate", "request_id": rid, "input_ids": ids[:20 - rid], "max_new_tokens": n}) + "\n")
+        p.stdin.flush()
+        done = {}
+        while len(done) < 2:
+            e = json.loads(p.stdout.readline())
+            if e["event"] == "done":
+                done[e["request_id"]] = e
+            assert e["event"] != "error", e
+        assert done[1]["generated_ids"] == reference_greedy(cfg, hf, ids[:19], 6)
+        assert done[2]["generated_ids"] == reference_greedy(cfg, hf, ids[:18], 4)
+        p.stdin.write(json.dumps({"op": "shutdown"}) + "\n"); p.stdin.flush()
+        assert json.loads(p.stdout.readline()) == {"event": "shutdown"}
+        assert p.wait(timeout=60) == 0
+    finally:
+        if p.poll() is None:
+            p.kill()
+
+
 def test_quantizer_cli(model_dir, tmp_path, capsys):
     cfg, hf, d = model_dir
     out = tmp_path / "q"
