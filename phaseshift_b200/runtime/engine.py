@@ -125,6 +125,27 @@ class Engine:
         if tp is not None and tp.size > 1 and backend == "cuda":
             self._tp_warmup()
 
+    def _raise_if_peer_lost(self, e: BaseException) -> None:
+        """A library collective that failed under tensor parallelism (connection closed by a peer that exited, process
+        group timeout) means a rank is gone: surface it as RankLostError, naming the ranks once the heartbeat knows."""
+        if self.tp is None or self.tp.size <= 1:
+            return
+        msg = str(e)
+        if not any(k in msg for k in ("Connection closed", "Connection reset", "timed out", "Timed out", "timeout", "NCCL",
+                                      "gloo", "ProcessGroup", "Broken pipe")):
+            return
+        import time
+        from ..parallel.health import RankLostError
+        mon = getattr(self.tp, "monitor", None)
+        lost: List[int] = []
+        if mon is not None:
+            deadline = time.monotonic() + mon.timeout_s + 4 * mon.interval_s
+            while not lost and time.monotonic() < deadline:
+                lost = mon.lost()
+                if not lost:
+                    time.sleep(mon.interval_s)
+        raise RankLostError(lost) from e
+
     def _tp_warmup(self) -> None:
         """Tensor parallel: everything a first step would do lazily -- weight tiling, kernel attributes, symmetric
         buffers of the combine / scatter paths -- happens here on every rank, followed by a barrier, so the ranks enter
@@ -307,9 +328,13 @@ class Engine:
                     self.alloc.release_pages(s.pages[-a:])
                     del s.pages[-a:]
             raise
-        toks, out, status = self._execute(rows, n_rows, n_out, bucket, b, tap_layers=tap_layers, gdn_log=gdn_log,
-                                          gdn_to_alt=gdn_to_alt, mask=mask, mask_active=mask_active, sample=sample,
-                                          exact=exact, device_ids=device_ids, read_back=read_back)
+        try:
+            toks, out, status = self._execute(rows, n_rows, n_out, bucket, b, tap_layers=tap_layers, gdn_log=gdn_log,
+                                              gdn_to_alt=gdn_to_alt, mask=mask, mask_active=mask_active, sample=sample,
+                                              exact=exact, device_ids=device_ids, read_back=read_back)
+        except RuntimeError as e:
+            self._raise_if_peer_lost(e)
+            raise
         if status != 0:
             for s in seq_objs:
                 s.poisoned = True
@@ -378,8 +403,12 @@ class Engine:
         n_out = sum(len(r.output_rows) for r in rows)
         bucket = resolve_row_bucket(n_rows)
         b = self._batch(bucket)
-        return self._execute(rows, n_rows, n_out, bucket, b, tap_layers=tap_layers, gdn_log=gdn_log,
-                             gdn_to_alt=gdn_to_alt, mask=mask, mask_active=mask_active, sample=sample, exact=False)
+        try:
+            return self._execute(rows, n_rows, n_out, bucket, b, tap_layers=tap_layers, gdn_log=gdn_log,
+                                 gdn_to_alt=gdn_to_alt, mask=mask, mask_active=mask_active, sample=sample, exact=False)
+        except RuntimeError as e:
+            self._raise_if_peer_lost(e)
+            raise
 
     def _execute(self, rows, n_rows: int, n_out: int, bucket: int, b: StepBatch, *, tap_layers, gdn_log, gdn_to_alt,
                  mask, mask_active, sample: bool, exact: bool, device_ids=None, read_back=None):
