@@ -224,7 +224,8 @@ __global__ void __launch_bounds__(kStThreads, 1) linear_stream_kernel(const Line
                 quad_epilogue(a, n0, m, v);
             }
         }
-        if (__syncthreads_or(timed_out ? 1 : 0)) break;
+        // whichever thread's wait ran out, the whole CTA leaves and every warp's lane 0 reports and drains
+        if (__syncthreads_or(timed_out ? 1 : 0)) { timed_out = true; break; }
     }
     if (timed_out && lane == 0) {
         // A copy never completed.  Report it and give copies still in flight a bounded chance to land

@@ -147,6 +147,7 @@ def test_engine_poisons_the_step_and_serves_a_fresh_sequence(preset):
     assert int(eng.ops.status[0]) == 0 and int(eng.state.status[0]) == 0
     eng.close_sequence(s)
     eng.tp = eng.runner.tp = None                     # the job continues on this rank alone (its weights are a TP slice)
+    eng.graphs.clear(); eng.graph_out.clear()         # captured steps have the dead transport baked in
     s2 = eng.open_sequence()
     toks, _ = eng.step([SeqRows(s2.slot, 0, [5, 6, 7], (2,))], [s2])
     toks2, _ = eng.step([SeqRows(s2.slot, 3, [toks[0]], (0,))], [s2])
