@@ -63,16 +63,19 @@ def _run(cmd, verbose):
     return p.stdout + p.stderr
 
 
-def kernels_lib_path() -> Path:
-    return OUT / "libps_kernels.so"
+def kernels_lib_path(checked: bool = False) -> Path:
+    return OUT / ("libps_kernels_checked.so" if checked else "libps_kernels.so")
 
 
 def runtime_lib_path() -> Path:
     return OUT / ("ps_runtime" + sysconfig.get_config_var("EXT_SUFFIX"))
 
 
-def build_kernels(verbose: bool = False, force: bool = False, ptxas_info: bool = False) -> Path:
-    OBJ.mkdir(parents=True, exist_ok=True)
+def build_kernels(verbose: bool = False, force: bool = False, ptxas_info: bool = False, checked: bool = False) -> Path:
+    """``checked``: the -DPS_CHECKED variant (descriptor assertions that report through a status word), built beside
+    the normal library; ``PS_CHECKED=1`` in the environment makes the op set load it."""
+    obj_dir = OBJ / "checked" if checked else OBJ
+    obj_dir.mkdir(parents=True, exist_ok=True)
     headers = list((CSRC / "include").rglob("*.h")) + list((CSRC / "include").rglob("*.cuh")) + \
         list((CSRC / "kernels").glob("*.cuh"))
     srcs = sorted((CSRC / "kernels").glob("*.cu"))
@@ -80,10 +83,10 @@ def build_kernels(verbose: bool = False, force: bool = False, ptxas_info: bool =
     jobs = []
     objs = []
     for s in srcs:
-        o = OBJ / (s.stem + ".o")
+        o = obj_dir / (s.stem + ".o")
         objs.append(o)
         if force or _newer(s, o, headers):
-            cmd = [nvcc, *NVCC_FLAGS, "-c", str(s), "-o", str(o)]
+            cmd = [nvcc, *NVCC_FLAGS, *(["-DPS_CHECKED=1"] if checked else []), "-c", str(s), "-o", str(o)]
             if ptxas_info:
                 cmd[1:1] = ["-Xptxas", "-v"]
             jobs.append(cmd)
@@ -92,7 +95,7 @@ def build_kernels(verbose: bool = False, force: bool = False, ptxas_info: bool =
         with _cf.ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             for out in ex.map(lambda c: _run(c, verbose), jobs):
                 logs.append(out)
-    lib = kernels_lib_path()
+    lib = kernels_lib_path(checked)
     if jobs or not lib.exists():
         _run([nvcc, "-shared", "-o", str(lib), *map(str, objs), "-lcudart", "-lcuda",
               "-gencode", "arch=compute_100a,code=sm_100a"], verbose)
@@ -126,6 +129,7 @@ def build_runtime(verbose: bool = False, force: bool = False) -> Path:
 def build_all(verbose: bool = False, force: bool = False) -> None:
     build_runtime(verbose, force)
     build_kernels(verbose, force)
+    build_kernels(verbose, force, checked=True)
 
 
 if __name__ == "__main__":

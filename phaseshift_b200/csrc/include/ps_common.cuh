@@ -21,12 +21,43 @@ enum PsDeviceStatus : uint32_t {
     PS_DEV_WAIT_TIMEOUT = 2,   // a bounded spin-wait (peer flag, mbarrier) ran out of budget
     PS_DEV_SAMPLING_FAILED = 3,
     PS_DEV_NONFINITE = 4,
+    PS_DEV_CHECK_FAILED = 5,   // checked build only: a descriptor / row / slot assertion failed; the block returned
 };
 
 // Budget, in GPU clock cycles, of every bounded device-side wait (mbarrier, peer flag, stream-K flag).
 // One definition for the whole library (elementwise.cu); ps_set_wait_budget() changes it, launchers pass
 // the current value to their kernels.  The default is about one second at B200 clocks.
 extern long long g_ps_wait_budget_cycles;
+
+// Checked build (-DPS_CHECKED, a second library beside the normal one; the stand-in for a device sanitizer): kernels
+// validate the descriptors they are handed -- slots, row ranges -- against limits the host registers once per
+// translation unit, report PS_DEV_CHECK_FAILED through the registered status word and return instead of touching
+// memory.  PS_CHECK conditions must be uniform over the thread block (they guard an early return).
+#ifdef PS_CHECKED
+namespace ps {
+struct Limits { int max_slots, max_rows; uint32_t* status; };
+static __device__ Limits g_limits = {1 << 30, 1 << 30, nullptr};
+}
+#define PS_DEFINE_LIMITS_SETTER(tag)                                                                   \
+    PS_API int ps_set_limits_##tag(int max_slots, int max_rows, void* status) {                        \
+        ps::Limits l{max_slots, max_rows, (uint32_t*)status};                                          \
+        return (int)cudaMemcpyToSymbol(ps::g_limits, &l, sizeof(l));                                   \
+    }
+#define PS_CHECK(cond)                                                                                 \
+    do {                                                                                               \
+        if (!(cond)) {                                                                                 \
+            if (ps::g_limits.status != nullptr) atomicCAS(ps::g_limits.status, 0u, (uint32_t)PS_DEV_CHECK_FAILED); \
+            return;                                                                                    \
+        }                                                                                              \
+    } while (0)
+#define PS_SLOT_OK(s) ((s) >= 0 && (s) < ps::g_limits.max_slots)
+#define PS_ROWS_OK(r0, n) ((r0) >= 0 && (n) >= 0 && (r0) + (n) <= ps::g_limits.max_rows)
+#else
+#define PS_DEFINE_LIMITS_SETTER(tag)
+#define PS_CHECK(cond) ((void)0)
+#define PS_SLOT_OK(s) true
+#define PS_ROWS_OK(r0, n) true
+#endif
 
 // Launch helpers return the CUDA error code as int (0 = cudaSuccess).
 #define PS_LAUNCH_CHECK() (int)cudaGetLastError()

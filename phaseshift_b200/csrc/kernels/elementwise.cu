@@ -180,3 +180,12 @@ PS_API long long ps_set_wait_budget(long long cycles) {
     g_ps_wait_budget_cycles = cycles < 1000 ? 1000 : cycles;
     return prev;
 }
+
+// 1 when this library was compiled with -DPS_CHECKED (descriptor assertions on, see ps_common.cuh).
+PS_API int ps_checked_build() {
+#ifdef PS_CHECKED
+    return 1;
+#else
+    return 0;
+#endif
+}

@@ -351,6 +351,7 @@ __global__ void __launch_bounds__(256) gdn_chunk_scan_kernel(const GdnScanArgs a
     const int slice = blockIdx.x, h = blockIdx.y, t = threadIdx.x, Hv = a.Hv, c0 = slice * kSlice;
     const GdnSeqDesc2 sd = a.seqs[blockIdx.z];
     if (sd.n_rows <= a.min_rows || sd.slot < 0) return;
+    PS_CHECK(PS_SLOT_OK(sd.slot) && PS_ROWS_OK(sd.row_start, sd.n_rows));
     int gc = 0;
     for (int s = 0; s < (int)blockIdx.z; ++s) {
         const GdnSeqDesc2 d = a.seqs[s];
@@ -483,6 +484,7 @@ __global__ void __launch_bounds__(256) gdn_chunk_scan_tc_kernel(const GdnScanArg
     const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const GdnSeqDesc2 sd = a.seqs[blockIdx.z];
     if (sd.n_rows <= a.min_rows || sd.slot < 0) return;
+    PS_CHECK(PS_SLOT_OK(sd.slot) && PS_ROWS_OK(sd.row_start, sd.n_rows));
     int gc = 0;
     for (int s = 0; s < (int)blockIdx.z; ++s) {
         const GdnSeqDesc2 d = a.seqs[s];
@@ -649,6 +651,8 @@ __global__ void gdn_post_kernel(const float* o, const __nv_bfloat16* proj, int l
 }
 
 }  // namespace ps
+
+PS_DEFINE_LIMITS_SETTER(gdn_chunked)
 
 // Floats of scratch needed for a step of `rows` rows in `n_seqs` sequences (upper bound on the chunks).
 PS_API long long ps_gdn_chunked_scratch_floats(int rows, int n_seqs, int Hv, int Dk, int Dv) {

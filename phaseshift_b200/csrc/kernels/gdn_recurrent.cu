@@ -55,6 +55,7 @@ __global__ void __launch_bounds__(256) gdn_rows_kernel(const GdnArgs a) {
     const int h = blockIdx.x;
     const GdnSeqDesc sd = a.seqs[blockIdx.y];
     if (sd.n_rows <= 0 || sd.n_rows > a.max_rows) return;
+    PS_CHECK(PS_SLOT_OK(sd.slot) && PS_ROWS_OK(sd.row_start, sd.n_rows) && sd.pos_start >= 0);
     const int hk = h / (a.Hv / a.Hk);
     const int t = threadIdx.x, cg = t % CG, rg = t / CG;
     const int q_off = hk * DK, k_off = a.Hk * DK + hk * DK, v_off = 2 * a.Hk * DK + h * DV;
@@ -206,6 +207,7 @@ __global__ void __launch_bounds__(256) gdn_replay_kernel(const GdnReplayArgs a) 
     const int h = blockIdx.x;
     const GdnSeqDesc sd = a.seqs[blockIdx.y];
     if (sd.n_rows <= 0) return;
+    PS_CHECK(PS_SLOT_OK(sd.slot) && PS_ROWS_OK(sd.row_start, sd.n_rows));
     const int t = threadIdx.x, cg = t % CG, rg = t / CG;
     float* sp = a.state + ((size_t)sd.slot * a.Hv + h) * DK * DV;
     float S[R][4];
@@ -232,6 +234,8 @@ __global__ void __launch_bounds__(256) gdn_replay_kernel(const GdnReplayArgs a) 
 }
 
 }  // namespace ps
+
+PS_DEFINE_LIMITS_SETTER(gdn_recurrent)
 
 PS_API int ps_gdn_rows(const void* proj, int ld_proj, int Hk, int Hv, int Dk, int Dv, const void* conv_w,
                        const void* A_log, const void* dt_bias, const void* norm_w, float eps, void* conv_state,

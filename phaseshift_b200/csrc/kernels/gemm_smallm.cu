@@ -41,7 +41,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     constexpr int kXStride = 64 * kSmBK * 2;
     __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_bar;
     __shared__ uint32_t tmem_base_slot;
-    __shared__ int s_abort;
+    __shared__ int s_abort, s_issued, s_consumed;      // stages handed to TMA / waited for by the MMA thread
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile_n = blockIdx.x, split = blockIdx.y;
@@ -57,7 +57,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         for (int s = 0; s < STAGES; ++s) { tc::mbar_init(&full_bar[s], 1); tc::mbar_init(&empty_bar[s], 1); }
         tc::mbar_init(&acc_bar, 1);
         tc::fence_barrier_init();
-        s_abort = 0;
+        s_abort = 0; s_issued = 0; s_consumed = 0;
         tc::tma_prefetch_desc(&map_w);
         tc::tma_prefetch_desc(&map_x);
     }
@@ -80,6 +80,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 tc::mbar_expect_tx(&full_bar[s], kWBytes + x_bytes);
                 tc::tma_load_2d(sW + s * kWBytes, &map_w, (it0 + it) * kSmBK, tile_n * kSmBM, &full_bar[s]);
                 tc::tma_load_2d(sX + s * kXStride, &map_x, (it0 + it) * kSmBK, 0, &full_bar[s]);
+                s_issued = it + 1;
             }
         }
     } else if (warp == 1) {
@@ -90,6 +91,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 const int s = it % STAGES;
                 const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
                 if (!tc::mbar_wait(&full_bar[s], ph, g.budget)) { atomicExch(&s_abort, 1); ok = false; break; }
+                s_consumed = it + 1;
                 tc::fence_after_sync();
                 const uint32_t w_addr = tc::smem_u32(sW + s * kWBytes), x_addr = tc::smem_u32(sX + s * kXStride);
 #pragma unroll
@@ -127,7 +129,13 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     }
     tc::fence_before_sync();
     __syncthreads();
-    if (s_abort != 0 && threadIdx.x == 0) set_status(g.status, PS_DEV_WAIT_TIMEOUT);
+    if (s_abort != 0 && threadIdx.x == 0) {
+        set_status(g.status, PS_DEV_WAIT_TIMEOUT);
+        // copies still in flight get a bounded chance to land before the shared memory goes back to the next CTA
+        const long long b = g.budget < 4000000ll ? g.budget : 4000000ll;
+        for (int c = s_consumed; c < s_issued; ++c) tc::mbar_wait(&full_bar[c % STAGES], (uint32_t)((c / STAGES) & 1), b);
+    }
+    __syncthreads();
     if (warp == 1) {
         tc::fence_after_sync();
         tc::tmem_dealloc(tmem_acc, 64);

@@ -51,7 +51,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     unsigned char* sB = smem + kGemmStages * kABytes;
     __shared__ __align__(8) uint64_t full_bar[kGemmStages], empty_bar[kGemmStages], acc_bar;
     __shared__ uint32_t tmem_base_slot;
-    __shared__ int s_abort;
+    __shared__ int s_abort, s_issued, s_consumed;      // stages handed to TMA / waited for by the MMA thread
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // Rasterisation: the M tiles of a band of up to 16 vary fastest, so the CTAs that run together share
@@ -75,7 +75,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int s = 0; s < kGemmStages; ++s) { tc::mbar_init(&full_bar[s], 1); tc::mbar_init(&empty_bar[s], 1); }
         tc::mbar_init(&acc_bar, 1);
         tc::fence_barrier_init();
-        s_abort = 0;
+        s_abort = 0; s_issued = 0; s_consumed = 0;
         tc::tma_prefetch_desc(&map_a);
         tc::tma_prefetch_desc(&map_w);
     }
@@ -98,6 +98,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 tc::mbar_expect_tx(&full_bar[s], a_bytes + kBBytes);
                 tc::tma_load_2d(sA + s * kABytes, &map_a, it * kBK, tile_m * kBM, &full_bar[s]);
                 tc::tma_load_2d(sB + s * kBBytes, &map_w, it * kBK, tile_n * BN, &full_bar[s]);
+                s_issued = it + 1;
             }
         }
     } else if (warp == 1) {
@@ -109,6 +110,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const int s = it % kGemmStages;
                 const uint32_t ph = (uint32_t)(it / kGemmStages) & 1u;
                 if (!tc::mbar_wait(&full_bar[s], ph, g.budget)) { atomicExch(&s_abort, 1); ok = false; break; }
+                s_consumed = it + 1;
                 tc::fence_after_sync();
                 const uint32_t a_addr = tc::smem_u32(sA + s * kABytes), b_addr = tc::smem_u32(sB + s * kBBytes);
 #pragma unroll
@@ -176,7 +178,13 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
     tc::fence_before_sync();
     __syncthreads();
-    if (s_abort != 0 && threadIdx.x == 0) set_status(g.status, PS_DEV_WAIT_TIMEOUT);
+    if (s_abort != 0 && threadIdx.x == 0) {
+        set_status(g.status, PS_DEV_WAIT_TIMEOUT);
+        // copies still in flight get a bounded chance to land before the shared memory goes back to the next CTA
+        const long long b = g.budget < 4000000ll ? g.budget : 4000000ll;
+        for (int c = s_consumed; c < s_issued; ++c) tc::mbar_wait(&full_bar[c % kGemmStages], (uint32_t)((c / kGemmStages) & 1), b);
+    }
+    __syncthreads();
     if (warp == 1) {
         tc::fence_after_sync();
         tc::tmem_dealloc(tmem_acc, BN);

@@ -23,10 +23,11 @@ def lib() -> ctypes.CDLL:
     global _LIB
     if _LIB is None:
         from ..build import kernels_lib_path, build_kernels
-        p = kernels_lib_path()
+        checked = os.environ.get("PS_CHECKED", "0") == "1"
+        p = kernels_lib_path(checked)
         if not p.exists():
             try:
-                build_kernels()
+                build_kernels(checked=checked)
             except Exception as e:  # pragma: no cover - build environment problem
                 raise KernelLibraryError(f"libps_kernels.so is not built and nvcc failed: {e}") from e
         _LIB = ctypes.CDLL(str(p))
@@ -36,6 +37,23 @@ def lib() -> ctypes.CDLL:
             _LIB.ps_set_wait_budget.restype = ctypes.c_longlong
             _LIB.ps_set_wait_budget(ctypes.c_longlong(int(float(ms) * 1.9e6)))
     return _LIB
+
+
+def checked_build() -> bool:
+    """Whether the loaded kernel library is the checked variant (PS_CHECKED=1)."""
+    L = lib()
+    L.ps_checked_build.restype = ctypes.c_int
+    return bool(L.ps_checked_build())
+
+
+def set_limits(max_slots: int, max_rows: int, status) -> None:
+    """Checked build: register the descriptor limits and the status word with every kernel file that asserts on them."""
+    L = lib()
+    for tag in ("gdn_recurrent", "gdn_chunked"):
+        fn = getattr(L, "ps_set_limits_" + tag, None)
+        if fn is not None:
+            fn.restype = ctypes.c_int
+            check(fn(ctypes.c_int(max_slots), ctypes.c_int(max_rows), ptr(status)), "ps_set_limits_" + tag)
 
 
 def ptr(t) -> ctypes.c_void_p:

@@ -43,6 +43,8 @@ class CudaOps(OpTrace):
         _lib.lib()      # fail loudly when the native library is missing
         self.cfg, self.device = cfg, device
         self.ws: Dict[Tuple[str, int], torch.Tensor] = {}
+        self.checked = _lib.checked_build()          # PS_CHECKED=1: descriptor assertions in the kernels + workspace canaries
+        self._guarded: Dict[Tuple[str, int], torch.Tensor] = {}
         half = cfg.rotary_dim // 2
         inv = cfg.rope_theta ** (-np.arange(half, dtype=np.float64) * 2.0 / cfg.rotary_dim)
         self.inv_freq = torch.from_numpy(inv).to(device)
@@ -67,13 +69,33 @@ class CudaOps(OpTrace):
         self.fallbacks: Dict[str, int] = {}
 
     # ------------------------------------------------------------------ workspace
+    CANARY = 0xA5
+    CANARY_BYTES = 256
+
     def buf(self, name: str, rows: int, cols: int, dtype=torch.bfloat16) -> torch.Tensor:
         key = (name, rows)
         t = self.ws.get(key)
         if t is None or t.shape[1] != cols or t.dtype != dtype:
-            t = torch.empty(rows, cols, dtype=dtype, device=self.device)
+            if self.checked:
+                # checked build: every workspace sits between two guard regions that `check_canaries` inspects
+                n = rows * cols * torch.empty(0, dtype=dtype).element_size()
+                raw = torch.full((n + 2 * self.CANARY_BYTES,), self.CANARY, dtype=torch.uint8, device=self.device)
+                t = raw[self.CANARY_BYTES:self.CANARY_BYTES + n].view(dtype).view(rows, cols)
+                self._guarded[key] = raw
+            else:
+                t = torch.empty(rows, cols, dtype=dtype, device=self.device)
             self.ws[key] = t
         return t
+
+    def check_canaries(self):
+        """Checked build: names of the workspaces whose guard bytes were overwritten (an out-of-bounds write by some
+        kernel).  Synchronises; the engine calls it after every step when the checked library is loaded."""
+        bad = []
+        g = self.CANARY_BYTES
+        for key, raw in self._guarded.items():
+            if bool((raw[:g] != self.CANARY).any()) or bool((raw[-g:] != self.CANARY).any()):
+                bad.append(key[0])
+        return bad
 
     # ------------------------------------------------------------------ ops
     SSQ_LD = 64          # partial sums of squares per row: one per 128-feature tile of the producing projection

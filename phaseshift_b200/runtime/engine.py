@@ -89,6 +89,9 @@ class Engine:
             self.ops = RefOps(self.cfg, self.device)
         self.sc = state_cfg
         self.state = ModelState(self.cfg, state_cfg, self.device, self.ops.act_dtype, geo)
+        if getattr(self.ops, "checked", False):
+            from ..ops import _lib as _klib
+            _klib.set_limits(state_cfg.max_slots, 1 << 20, self.state.status)
         self.runner = Qwen35Runner(weights, self.state, self.ops, tp)
         self.tp = tp
         if tp is not None and hasattr(self.ops, "status"):
@@ -468,6 +471,10 @@ class Engine:
             if read_back is not None:
                 out.read_back = read_back.tolist()
         self.steps += 1
+        if getattr(self.ops, "checked", False):
+            bad = self.ops.check_canaries()
+            if bad:
+                raise RuntimeError("checked build: workspace guard bytes overwritten around " + ", ".join(sorted(set(bad))))
         if status != 0:
             self.status_errors += 1
             self.state.status.zero_()
