@@ -41,9 +41,25 @@ def _parse():
     ap.add_argument("--layout", default="both", choices=["both", "tc", "stream"],
                     help="kernel-side weight layouts kept resident: tensor-core operands, streaming tiles, or both "
                          "(single-row decode streams, everything else runs on the tensor cores)")
+    ap.add_argument("--config", type=int, default=0, choices=[0, 3, 4, 5],
+                    help="workload preset: 3 = prefill 4096 + 1024 decode steps; 4 = 8k-token prompt, 256 speculative "
+                         "tokens; 5 = the full serving load (256 requests)")
+    ap.add_argument("--serving-requests", type=int, default=24,
+                    help="continuous-batching block: concurrent requests with prompts U(512, 8192), outputs U(128, 1024), "
+                         "FP8 KV, half of them sharing a 1024-token prefix (0 = skip; the full load is 256)")
+    ap.add_argument("--serving-slots", type=int, default=12,
+                    help="sequence slots of the serving block (fewer than the requests, so that later admissions can hit "
+                         "the prefix cache the earlier ones filled)")
     ap.add_argument("--watchdog", type=int, default=1500,
                     help="seconds after which a hung run dumps every thread's stack to stderr and exits")
-    return ap.parse_args()
+    a = ap.parse_args()
+    if a.config == 3:
+        a.context, a.steps = 4096, 1024
+    elif a.config == 4:
+        a.context, a.dflash2_tokens = 8192, 256
+    elif a.config == 5:
+        a.serving_requests, a.serving_slots = 256, 64
+    return a
 
 
 class ClockSampler:
@@ -220,6 +236,72 @@ def dflash2_arm(eng, cfg, dev, prompt, args):
     return out
 
 
+def serving_block(ew, cfg, dev, tp, world, args):
+    """Continuous-batching serving through the public ServingEngine API: every request is submitted at t = 0, the
+    scheduler mixes prefill chunks and decode rows per step under the KV banker, half of the prompts start with one
+    shared 1024-token prefix (checkpointed by the first request that reaches it, restored by the later ones).  Under
+    tensor parallelism every rank runs the same deterministic scheduler.  Device time, max over ranks."""
+    import torch
+    import torch.distributed as dist
+    from phaseshift_b200.runtime.engine import Engine
+    from phaseshift_b200.runtime.serving import ServingEngine
+    from phaseshift_b200.runtime.state import StateConfig
+    n = args.serving_requests
+    g = torch.Generator().manual_seed(99)
+    small = args.model != "27b"
+    lo_p, hi_p, lo_o, hi_o, pre = (64, 256, 16, 64, 32) if small else (512, 8192, 128, 1024, 1024)
+    plen = torch.randint(lo_p, hi_p + 1, (n,), generator=g).tolist()
+    olen = torch.randint(lo_o, hi_o + 1, (n,), generator=g).tolist()
+    shared = torch.randint(0, cfg.vocab_size, (pre,), generator=g).tolist()
+    slots = max(1, min(n, args.serving_slots))
+    max_seq = hi_p + hi_o + 16
+    eng = Engine(ew, dev, StateConfig(max_slots=slots, max_seq_len=max_seq, page_tokens=16, kv_dtype="fp8_e4m3",
+                                      kv_capacity_tokens=slots * max_seq), tp=tp)
+    srv = ServingEngine(eng, max_step_tokens=2048, prefix_cache_tokens=8 * pre, prefix_cache_entries=4, prefix_min_tokens=min(64, pre))
+    for i in range(n):
+        body = torch.randint(0, cfg.vocab_size, (plen[i],), generator=g).tolist()
+        if i % 2 == 0:
+            srv.submit(shared + body[pre:], olen[i], checkpoint_position=pre)
+        else:
+            srv.submit(body, olen[i])
+    sampler = ClockSampler(dev.index or 0)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.begin()
+    ev0.record()
+    t0 = time.perf_counter()
+    first = {}
+    n_tok = 0
+    while not srv.idle():
+        for e in srv.step():
+            if e.kind == "token":
+                n_tok += 1
+                first.setdefault(e.request_id, (time.perf_counter() - t0) * 1e3)
+            elif e.kind in ("done", "error"):
+                srv.batcher.retire(e.request_id)
+    ev1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    t = torch.tensor([ev0.elapsed_time(ev1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t)
+    prompt_tokens = sum(plen)
+    return {"requests": n, "slots": slots, "prompt_len": f"U({lo_p},{hi_p})", "output_len": f"U({lo_o},{hi_o})",
+            "shared_prefix_tokens": pre, "shared_prefix_fraction": 0.5, "kv_cache": "fp8_e4m3", "weight_preset": args.preset,
+            "generated_tokens": n_tok, "prompt_tokens": prompt_tokens, "wall_ms": round(ms, 1),
+            "aggregate_tok_s": round(n_tok / ms * 1e3, 1), "aggregate_tok_s_per_gpu": round(n_tok / ms * 1e3 / world, 1),
+            "processed_tok_s": round((n_tok + srv.stats["prefill_tokens"]) / ms * 1e3, 1),
+            "p50_ttft_ms": round(statistics.median(first.values()), 1) if first else None,
+            "prefill_tokens_computed": srv.stats["prefill_tokens"],
+            "prefix_hit_tokens": srv.prefix.stats["restored_tokens"] if srv.prefix is not None else 0,
+            "steps": srv.stats["steps"], "failed_steps": srv.stats["failed_steps"],
+            "tp": dict(tp.stats, transport=tp.transport) if tp is not None else None, "clocks": clocks,
+            "timing": "CUDA events around the whole run, max over ranks; TTFT on the host clock of rank 0"}
+
+
 def main():
     args = _parse()
     if args.impl == "reference":
@@ -344,6 +426,9 @@ def main():
         dflash = None
         if args.dflash2 and world == 1:
             dflash = dflash2_arm(eng, cfg, dev, prompt, args)
+        serving = None
+        if args.serving_requests > 0:
+            serving = serving_block(ew, cfg, dev, tp, world, args)
 
     # max over ranks of the per-step time
     t = torch.tensor([dev_ms, e2e_ms, prefill_ms, ttft_ms], device=dev, dtype=torch.float64)
@@ -378,6 +463,7 @@ def main():
                     "tok_s": round(args.context / ttft_ms * 1e3, 1)},
         "ttft_p50_ms": round(ttft_ms, 2),
         "dflash2": dflash,
+        "serving": serving,
         "weights_gb_per_step": round(rd_bytes / 1e9, 3),
         "hbm_roofline_frac_of_measured": round(rd_bytes / (dev_ms * 1e-3) / (hbm * 1e9), 4),
         "build_s": round(build_s, 1), "token_checksum": checksum, "impl": "ours",

@@ -105,6 +105,8 @@ class ServingEngine:
                                 sample_index=sidx))
             if sample:
                 masked.append(rid)
+            if not is_decode:
+                self.stats["prefill_tokens"] += n
         mask = mask_active = None
         if self.matchers and any(rid in self.matchers for rid in masked):
             mask, mask_active = self._fill_masks(masked)
