@@ -237,6 +237,11 @@ __global__ void __launch_bounds__(256) gdn_replay_kernel(const GdnReplayArgs a) 
 
 PS_DEFINE_LIMITS_SETTER(gdn_recurrent)
 
+// Contract: the kernel may load the recurrent state of its slots BEFORE its stream predecessor has finished
+// (programmatic dependent launch): the predecessor must therefore not write `state_in` of those slots.  Inside the
+// engine that holds -- a projection kernel always sits between two GDN launches of one layer.  A caller that runs two
+// ps_gdn_rows back to back on one slot and state buffer must put another kernel (or an event) between them, or set
+// PS_PDL=0.
 PS_API int ps_gdn_rows(const void* proj, int ld_proj, int Hk, int Hv, int Dk, int Dv, const void* conv_w,
                        const void* A_log, const void* dt_bias, const void* norm_w, float eps, void* conv_state,
                        int ring, const void* state_in, void* state_out, const void* seqs, int n_seqs, void* out,

@@ -358,6 +358,27 @@ def test_e2e_tiny_model_matches_oracle_tokens():
         assert eng2.generate(prompt, 24, prefill_chunk=16) == out
 
 
+def test_e2e_bf16_tokens_equal_the_oracle_on_bf16_rounded_weights():
+    """bf16 weights, bf16 KV: the GPU engine's greedy stream equals, token for token, the fp32 oracle run on the same
+    bf16-rounded weights wherever the oracle's decision is not a numerical tie (top-2 margin above the bf16 activation
+    noise); at least 20 of the 24 steps must be that decisive, so the check cannot pass vacuously."""
+    from phaseshift_b200.models.qwen35.reference import reference_forward
+    from phaseshift_b200.runtime.engine import Engine
+    cfg = tiny_config()
+    hf = {k: v.to(torch.bfloat16).float() for k, v in random_hf_weights(cfg, seed=0).items()}
+    prompt = torch.randint(0, cfg.vocab_size, (32,), generator=torch.Generator().manual_seed(0)).tolist()
+    ew = build_engine_weights(cfg, lambda n: hf[n], "bf16", "cuda")
+    eng = Engine(ew, "cuda", StateConfig(max_slots=1, max_seq_len=128, page_tokens=16, kv_dtype="bf16"))
+    out = eng.generate(prompt, 24, prefill_chunk=16)
+    logits = reference_forward(cfg, hf, prompt + out[:-1])[len(prompt) - 1:]
+    top2 = logits.topk(2, -1)
+    decisive = (top2.values[:, 0] - top2.values[:, 1]) > 0.02
+    assert int(decisive.sum()) >= 20
+    want = top2.indices[:, 0]
+    got = torch.tensor(out)
+    assert torch.equal(got[decisive], want[decisive]), (got.tolist(), want.tolist())
+
+
 @pytest.mark.parametrize("fmt", ["bf16", "nvfp4", "mxfp8"])
 def test_stream_gemv_shapes_and_row_invariance(fmt):
     """Odd N / K tails, K larger than one staging pass allows for M=8, and row invariance across M."""
@@ -659,3 +680,39 @@ def test_decode_batches_beyond_eight_rows_replay_from_graphs():
         if graphs:
             assert any((k // 2) // 4096 == 16 for k in eng.graphs), "the 12-row decode batch must have been captured (bucket 16)"
     assert outs[0] == outs[1]
+
+
+@pytest.mark.parametrize("kvd", ["bf16", "fp8_e4m3"])
+def test_long_context_prefill_and_decode_paths_agree_at_32k(kvd):
+    """8 K-token prefill chunks up to a 32 K context, then decoding: the logits of the last position computed by the
+    prefill path (tiled attention over 32 K keys, chunked GDN) and by the decode path (split-KV attention with the
+    split length doubled to stay within 512 splits, row-sequential GDN) must agree -- two independent kernel families
+    over the same paged cache, block table and positions."""
+    from phaseshift_b200.runtime.engine import Engine
+    cfg = tiny_config()
+    hf = random_hf_weights(cfg, seed=0)
+    ew = build_engine_weights(cfg, lambda n: hf[n], "bf16", "cuda")
+    N = 32768
+    ids = torch.randint(0, cfg.vocab_size, (N,), generator=torch.Generator().manual_seed(2)).tolist()
+    sc = StateConfig(max_slots=2, max_seq_len=N + 16, page_tokens=16, kv_dtype=kvd)
+    eng = Engine(ew, "cuda", sc)
+    assert eng.ops.split_tokens * 512 >= N                      # the split length grew with the context
+    a, b = eng.open_sequence(), eng.open_sequence()
+    for c0 in range(0, N, 8192):
+        last = c0 + 8192 >= N
+        _, out_a = eng.step([SeqRows(a.slot, c0, ids[c0:c0 + 8192], (8191,) if last else ())], [a], want_logits=True)
+    for c0 in range(0, N - 1, 8192):
+        chunk = ids[c0:min(c0 + 8192, N - 1)]
+        eng.step([SeqRows(b.slot, c0, chunk, ())], [b])
+    _, out_b = eng.step([SeqRows(b.slot, N - 1, [ids[N - 1]], (0,))], [b], want_logits=True)
+    la, lb = out_a.logits[0].float(), out_b.logits[0].float()
+    assert torch.isfinite(la).all() and torch.isfinite(lb).all()
+    assert _rel_err(lb, la) < (3e-2 if kvd == "bf16" else 8e-2)
+    # and decoding simply continues from there
+    toks = []
+    t = int(la.argmax())
+    for i in range(4):
+        tk, _ = eng.step([SeqRows(a.slot, N + i, [t], (0,))], [a])
+        t = tk[0]
+        toks.append(t)
+    assert len(toks) == 4 and int(eng.ops.status[0]) == 0 and int(eng.state.status[0]) == 0

@@ -51,7 +51,7 @@ def test_noalloc_entry_matches_regular_entry_twice():
         torch.cuda.synchronize()
         assert int(status[0]) == 0
         assert torch.isfinite(got.float()).all()
-        assert torch.allclose(got.float(), ref.float(), atol=2e-2, rtol=2e-2)
+        assert torch.equal(got, ref)          # both entry points launch the same kernels: bit for bit
     # a problem larger than the built-in scratch is refused with a message, nothing is launched
     rc = lib.ps_paged_attention_noalloc(*_args(q, k, v, bt, slot, pos, rows, Hq, Hkv, D, split, 4096, vis, gate, got, status))
     assert rc == -2 and b"exceeds" in lib.ps_noalloc_last_error()
