@@ -262,6 +262,46 @@ def cmd_gemm(a) -> int:
     return 0
 
 
+def cmd_dflash2(a, cfg, dev) -> int:
+    """The drafter on its own: one proposal (captured graph, `--rows` = draft count, ring filled to `--context` rows),
+    the context append of one verified block, and the weights it streams.  The target is cut to 4 layers (the drafter
+    only borrows its embedding and lm_head); the drafter keeps the full shape of the named model's DFlash2 companion."""
+    import torch
+    from ..models.dflash2.model import DFlash2Config, random_weights, tiny_drafter_config
+    from ..models.dflash2.native import DFlash2NativeDrafter
+    from ..models.qwen35.weights import build_engine_weights, random_getter
+    from ..runtime.engine import Engine
+    from ..runtime.state import StateConfig
+    small = type(cfg)(**{**cfg.__dict__, "num_hidden_layers": 4, "layer_types": None})
+    ew = build_engine_weights(small, random_getter(small, 0, dev), "nvfp4", dev, layout="both")
+    eng = Engine(ew, dev, StateConfig(max_slots=1, max_seq_len=a.context + 64, conv_ring=16, spec_rows=16))
+    if a.model == "tiny":
+        dcfg = tiny_drafter_config(small, head_dim=128, num_attention_heads=4, num_key_value_heads=2)
+    else:
+        dcfg = DFlash2Config(vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size, intermediate_size=cfg.intermediate_size,
+                             target_layer_ids=[0, 1, 2, 3], num_target_layers=4)
+    dr = DFlash2NativeDrafter(dcfg, random_weights(dcfg, 1, dev), eng, "nvfp4")
+    k = max(1, min(15, a.rows if a.rows > 1 else 7))
+    n_ctx = min(a.context, dcfg.sliding_window)
+    g = torch.Generator(device=dev).manual_seed(0)
+    taps = [torch.randn(n_ctx, cfg.hidden_size, device=dev, generator=g).to(torch.bfloat16) for _ in dcfg.target_layer_ids]
+    dr.append_context(taps, 0)
+    for _ in range(3):
+        dr.propose_device(5, k, n_ctx)
+    rep = 20
+    ts = sorted(_timed(dev, lambda: [dr.propose_device(5, k, n_ctx) for _ in range(rep)])[0] * 1e3 / rep for _ in range(max(3, a.samples // 4)))
+    blk = [t[:k + 1] for t in taps]
+    for _ in range(2):
+        dr.append_context(blk, n_ctx)
+    ta = sorted(_timed(dev, lambda: [dr.append_context(blk, n_ctx) for _ in range(rep)])[0] * 1e3 / rep for _ in range(3))
+    wb = dr.weight_bytes() + eng.runner.w.lm_head.nbytes
+    print("kernel=dflash2"); print(f"model={a.model}"); print(f"drafts={k}"); print(f"context_rows={n_ctx}")
+    print(f"proposal_p50_us={ts[len(ts) // 2]:.1f}"); print(f"append_block_p50_us={ta[len(ta) // 2]:.1f}")
+    print(f"launches_per_proposal={dr.launches}"); print(f"weight_bytes_per_proposal={wb}")
+    print(f"hbm_GBps={wb / ts[len(ts) // 2] / 1e3:.0f}")
+    return 0
+
+
 def cmd_kernel(a) -> int:
     """Single-kernel latency on a synthetic decode-shaped problem of the named model."""
     import torch
@@ -276,6 +316,8 @@ def cmd_kernel(a) -> int:
         free, total = torch.cuda.mem_get_info()
         print(f"gpu_total_bytes={total}"); print(f"gpu_free_bytes={free}")
         print(f"model_params={cfg.param_count()}"); return 0
+    if a.cmd == "dflash2":
+        return cmd_dflash2(a, cfg, dev)
     small = type(cfg)(**{**cfg.__dict__, "num_hidden_layers": 4, "layer_types": None, "vocab_size": min(cfg.vocab_size, 32768)})
     ew = build_engine_weights(small, random_getter(small, 0, dev), "bf16", dev)
     eng = Engine(ew, dev, StateConfig(max_slots=1, max_seq_len=a.context + a.rows + 64, kv_dtype=a.kv_cache_dtype), use_graphs=False)
@@ -317,8 +359,6 @@ def cmd_kernel(a) -> int:
            "gdn-recurrence": lambda: ops.gdn(proj, L_gdn.mixer, eng.runner.hk, eng.runner.hv, b, st.gdn[li_g], st),
            "embedding": lambda: ops.embed(b, a.rows, ew.embed, st.status),
            "sampling": lambda: ops.sample(logits, b, a.rows, status=st.status)}
-    if a.cmd == "dflash2":
-        print("dflash2_bench=use bench.py --dflash2 for round timings"); return 0
     fn = fns[a.cmd]
     for _ in range(5):
         fn()

@@ -63,3 +63,80 @@ def distill(drafter: DFlash2Drafter, cfg, hf_weights, sequences: Sequence[List[i
     for p_ in params:
         p_.requires_grad_(False)
     return last
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Distillation against the serving engine itself (any size, on the GPU): the samples are what the ENGINE decodes
+# greedily and the hidden states it taps while doing so -- exactly what the drafter is fed at inference time.
+
+def engine_samples(engine, tap_layers: Sequence[int], n_seqs: int, prompt_len: int, gen_len: int, seed: int = 0,
+                   prefill_chunk: int = 2048):
+    """[(token ids, [tap tensor [len - 1, H] per tapped layer])]: greedy continuations of random prompts decoded by
+    ``engine`` with the tapped hidden states of every position that was fed to it."""
+    from ...runtime.batch import SeqRows
+    g = torch.Generator().manual_seed(seed)
+    out = []
+    taps_l = list(tap_layers)
+    for _ in range(n_seqs):
+        ids = torch.randint(0, engine.cfg.vocab_size, (prompt_len,), generator=g).tolist()
+        rows: List[List[torch.Tensor]] = [[] for _ in taps_l]
+        s = engine.open_sequence()
+        try:
+            tok = None
+            for c0 in range(0, prompt_len, prefill_chunk):
+                chunk = ids[c0:c0 + prefill_chunk]
+                last = c0 + prefill_chunk >= prompt_len
+                toks, o = engine.step([SeqRows(s.slot, c0, chunk, (len(chunk) - 1,) if last else ())], [s], tap_layers=taps_l)
+                for j, l in enumerate(taps_l):
+                    rows[j].append(o.taps[l][:len(chunk)].clone())
+                if toks:
+                    tok = toks[0]
+            for _ in range(gen_len):
+                ids.append(tok)
+                toks, o = engine.step([SeqRows(s.slot, s.position, [tok], (0,))], [s], tap_layers=taps_l)
+                for j, l in enumerate(taps_l):
+                    rows[j].append(o.taps[l][:1].clone())
+                tok = toks[0]
+            ids.append(tok)
+        finally:
+            engine.close_sequence(s)
+        out.append((ids, [torch.cat(r, 0) for r in rows]))
+    return out
+
+
+def distill_on_engine(drafter: DFlash2Drafter, engine, samples, k: int, steps: int = 200, lr: float = 1e-3, ctx: int = 256,
+                      log=None) -> float:
+    """Train the torch drafter (on the engine's device) to predict the K tokens that follow an anchor, from
+    ``[anchor, MASK x K]`` and the taps of up to ``ctx`` preceding positions, through the target's frozen embedding
+    and lm_head.  Returns the last loss.  The trained weights can then be handed to ``DFlash2NativeDrafter``."""
+    from .decoder import embed_rows
+    dcfg: DFlash2Config = drafter.cfg
+    dev = drafter.device
+    W = engine.runner.w
+    lm = W.lm_head.dense().to(device=dev, dtype=drafter.dtype)                # frozen target head [vocab, H]
+    params = [p.requires_grad_(True) for n, p in drafter.w.items() if "codebook" not in n]
+    opt = torch.optim.AdamW(params, lr=lr, weight_decay=0.0)
+    g = torch.Generator().manual_seed(1)
+    last = 0.0
+    for step in range(steps):
+        ids, taps = samples[int(torch.randint(0, len(samples), (1,), generator=g))]
+        p = int(torch.randint(min(8, len(ids) - k - 2), len(ids) - k - 1, (1,), generator=g))
+        c0 = max(0, p - ctx)
+        drafter.reset()
+        with torch.no_grad():
+            drafter.append_context([t[c0:p].to(drafter.dtype) for t in taps], c0)
+        block = torch.tensor([ids[p]] + [dcfg.mask_token_id] * k, device=dev)
+        x = embed_rows(W.embed, block).to(drafter.dtype)
+        h = drafter.backbone(x, torch.arange(p, p + k + 1, device=dev))[1:]
+        loss = F.cross_entropy((h @ lm.T).float(), torch.tensor(ids[p + 1:p + 1 + k], device=dev))
+        opt.zero_grad(set_to_none=True)
+        loss.backward()
+        torch.nn.utils.clip_grad_norm_(params, 1.0)
+        opt.step()
+        last = float(loss)
+        if log and step % 20 == 0:
+            log(f"distill step {step} loss {last:.3f}")
+    for p_ in params:
+        p_.requires_grad_(False)
+    drafter.reset()
+    return last
