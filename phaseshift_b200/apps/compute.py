@@ -25,7 +25,9 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--input-ids-file")
     ap.add_argument("--max-new-tokens", type=int, default=32)
     ap.add_argument("--max-seq-len", type=int, default=512)
-    ap.add_argument("--arena-gib", type=float, default=16)
+    ap.add_argument("--arena-gib", type=float, default=0,
+                    help="byte budget (GiB) of the device arenas holding the KV pages and the recurrent state; the engine "
+                         "refuses to start when the configuration needs more (0 = framework allocator, no budget)")
     ap.add_argument("--page-tokens", type=int, default=16)
     ap.add_argument("--max-concurrent-requests", type=int, default=1)
     ap.add_argument("--kv-cache-capacity-tokens", type=int, default=0)
@@ -109,7 +111,10 @@ class ComputeRuntime:
         sc = StateConfig(max_slots=a.max_concurrent_requests, max_seq_len=a.max_seq_len, page_tokens=a.page_tokens,
                          kv_capacity_tokens=a.kv_cache_capacity_tokens, kv_dtype=a.kv_cache_dtype,
                          conv_ring=32 if spec else 4, spec_rows=a.dflash2_drafts + 1 if spec else 0)
-        self.engine = Engine(ew, self.device, sc, tp=self.tp)
+        try:
+            self.engine = Engine(ew, self.device, sc, tp=self.tp, arena_gib=getattr(a, "arena_gib", 0) or 0)
+        except MemoryError as e:
+            raise SystemExit(f"phaseshift-compute: {e} (raise --arena-gib or lower --max-seq-len / --max-concurrent-requests)")
         compiler = None
         if a.constraint_tokenizer_info:
             from ..runtime.constraints import TokenConstraintCompiler

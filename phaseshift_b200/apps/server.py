@@ -35,7 +35,7 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--model-dir"); ap.add_argument("--random-model", choices=["tiny", "4b", "27b"])
     ap.add_argument("--preset", default=None); ap.add_argument("--host", default="127.0.0.1")
     ap.add_argument("--port", type=int, default=8000); ap.add_argument("--max-seq-len", type=int, default=32768)
-    ap.add_argument("--arena-gib", type=float, default=16); ap.add_argument("--device", default=None)
+    ap.add_argument("--arena-gib", type=float, default=0); ap.add_argument("--device", default=None)
     ap.add_argument("--kv-cache-dtype", default="bf16", choices=["bf16", "fp8_e4m3"])
     ap.add_argument("--page-tokens", type=int, default=16); ap.add_argument("--max-concurrent-requests", type=int, default=4)
     ap.add_argument("--kv-cache-capacity-tokens", type=int, default=0)
@@ -292,7 +292,7 @@ def load_tokenizer(model_dir: Optional[str], vocab_size: int):
 def build_runtime(a):
     from .compute import ComputeRuntime
     ns = argparse.Namespace(model_dir=a.model_dir, random_model=a.random_model, preset=a.preset, device=a.device,
-                            max_seq_len=a.max_seq_len, page_tokens=a.page_tokens,
+                            max_seq_len=a.max_seq_len, page_tokens=a.page_tokens, arena_gib=a.arena_gib,
                             max_concurrent_requests=a.max_concurrent_requests,
                             kv_cache_capacity_tokens=a.kv_cache_capacity_tokens or (a.max_concurrent_requests + 1) * (a.max_seq_len + 1),
                             kv_cache_dtype=a.kv_cache_dtype, prefix_cache_capacity_tokens=a.prefix_cache_capacity_tokens,

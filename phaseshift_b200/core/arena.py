@@ -4,7 +4,8 @@ CUDA graphs and peer mappings (KV pages, recurrent state, workspaces).
 `GpuArena` wraps the native VMM arena (csrc/kernels/vmm_arena.cu): a virtual range of ``reserve_bytes`` is
 reserved once, physical chunks are committed behind it on demand, and tensors are bump-allocated views
 into the range.  `ArenaSet` keeps the named arenas of one engine under a common budget, the role of the
-reference's ArenaSet / `--arena-gib` (include/phaseshift/core/gpu_arena.h).
+reference's ArenaSet / `--arena-gib` (include/phaseshift/core/memory/arena.h:14-120,
+src/phaseshift/core/memory/arena.hip:48-138).
 """
 from __future__ import annotations
 

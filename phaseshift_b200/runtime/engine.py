@@ -72,7 +72,7 @@ class PageAllocator:
 
 class Engine:
     def __init__(self, weights: EngineWeights, device, state_cfg: StateConfig, backend: str = "auto", tp=None,
-                 use_graphs: bool = True, calibrate: bool = True):
+                 use_graphs: bool = True, calibrate: bool = True, arena_gib: float = 0.0):
         """``calibrate``: fix the activation scales of the block-scaled tensor-core projections from one forward
         (once per weight set; see calibrate_act_scales)."""
         self.cfg: Qwen35Config = weights.cfg
@@ -88,7 +88,12 @@ class Engine:
             from ..ops.ref_ops import RefOps
             self.ops = RefOps(self.cfg, self.device)
         self.sc = state_cfg
-        self.state = ModelState(self.cfg, state_cfg, self.device, self.ops.act_dtype, geo)
+        self.arenas = None
+        if arena_gib and arena_gib > 0 and backend == "cuda":
+            # KV pages and recurrent state live in virtual-memory arenas under this byte budget (`--arena-gib`)
+            from ..core.arena import ArenaSet
+            self.arenas = ArenaSet(int(arena_gib * (1 << 30)), self.device.index or 0)
+        self.state = ModelState(self.cfg, state_cfg, self.device, self.ops.act_dtype, geo, arenas=self.arenas)
         if getattr(self.ops, "checked", False):
             from ..ops import _lib as _klib
             _klib.set_limits(state_cfg.max_slots, 1 << 20, self.state.status)

@@ -64,7 +64,10 @@ class ModelState:
     """All per-sequence device state of one rank."""
 
     def __init__(self, cfg: Qwen35Config, sc: StateConfig, device, act_dtype=torch.bfloat16,
-                 geo: Optional[TpGeometry] = None):
+                 geo: Optional[TpGeometry] = None, arenas=None):
+        """``arenas`` (a core.arena.ArenaSet, CUDA only): the KV pages and the recurrent / conv state are carved from
+        the named arenas "kv" and "state" (stable virtual addresses, physical memory committed for exactly what the
+        configuration needs, all under the set's byte budget) instead of the framework allocator."""
         if sc.kv_dtype not in KV_DTYPES:
             raise ValueError(f"kv dtype {sc.kv_dtype!r} not in {KV_DTYPES}")
         if sc.conv_ring < 4:
@@ -87,21 +90,35 @@ class ModelState:
         self.kv: List[Optional[KVLayer]] = []
         self.gdn: List[Optional[GdnLayerState]] = []
         Dk, Dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
+        self.arenas = arenas
+        esz = lambda dt: torch.empty(0, dtype=dt).element_size()
+        n_attn = sum(1 for lt in cfg.layer_types if lt == 1)
+        n_gdn = len(cfg.layer_types) - n_attn
+        kv_need = n_attn * (2 * self.num_pages * self.hkv * pt * D * esz(kvt) + (2 * self.num_pages * self.hkv * pt * 4 if fp8 else 0) + 1024)
+        st_need = n_gdn * (sc.max_slots * self.hv * (sc.conv_ring * (2 * Dk + Dv) * esz(act_dtype)
+                                                      + Dk * Dv * 4 * (2 if sc.spec_rows > 0 else 1)) + 1024)
+        kv_arena = arenas.get("kv", kv_need + (2 << 20)) if arenas is not None and n_attn else None
+        st_arena = arenas.get("state", st_need + (2 << 20)) if arenas is not None and n_gdn else None
+
+        def pool(arena, shape, dtype, fill=0):
+            if arena is None:
+                return torch.full(shape, fill, dtype=dtype, device=device) if fill else torch.zeros(shape, dtype=dtype, device=device)
+            t = arena.alloc(shape, dtype)
+            return t.fill_(fill) if fill else t.zero_()
         for lt in cfg.layer_types:
             if lt == 1:
-                k = torch.zeros(self.num_pages, self.hkv, pt, D, dtype=kvt, device=device)
-                v = torch.zeros_like(k)
+                k = pool(kv_arena, (self.num_pages, self.hkv, pt, D), kvt)
+                v = pool(kv_arena, (self.num_pages, self.hkv, pt, D), kvt)
                 ks = vs = None
                 if fp8:
-                    ks = torch.ones(self.num_pages, self.hkv, pt, dtype=torch.float32, device=device)
-                    vs = torch.ones_like(ks)
+                    ks = pool(kv_arena, (self.num_pages, self.hkv, pt), torch.float32, 1)
+                    vs = pool(kv_arena, (self.num_pages, self.hkv, pt), torch.float32, 1)
                 self.kv.append(KVLayer(k, v, ks, vs))
                 self.gdn.append(None)
             else:
-                conv = torch.zeros(sc.max_slots, self.hv, sc.conv_ring, 2 * Dk + Dv,
-                                   dtype=act_dtype, device=device)
-                rec = torch.zeros(sc.max_slots, self.hv, Dk, Dv, dtype=torch.float32, device=device)
-                alt = torch.zeros_like(rec) if sc.spec_rows > 0 else None
+                conv = pool(st_arena, (sc.max_slots, self.hv, sc.conv_ring, 2 * Dk + Dv), act_dtype)
+                rec = pool(st_arena, (sc.max_slots, self.hv, Dk, Dv), torch.float32)
+                alt = pool(st_arena, (sc.max_slots, self.hv, Dk, Dv), torch.float32) if sc.spec_rows > 0 else None
                 self.gdn.append(GdnLayerState(conv, rec, alt))
                 self.kv.append(None)
         self.block_table = torch.full((sc.max_slots, self.max_blocks), -1, dtype=torch.int32, device=device)

@@ -34,3 +34,30 @@ def test_arena_grows_keeps_addresses_and_is_usable_by_kernels():
     with pytest.raises(MemoryError):
         s.get("ws", 768 << 20)
     s.close()
+
+
+def test_engine_state_lives_in_the_arenas_and_the_budget_is_enforced():
+    """--arena-gib: KV pages and recurrent state are carved from the VMM arenas (same tokens as with the framework
+    allocator, committed bytes match the configuration), and a budget the configuration does not fit is refused."""
+    import pytest
+    from phaseshift_b200.models.qwen35.config import tiny_config
+    from phaseshift_b200.models.qwen35.weights import build_engine_weights, random_hf_weights
+    from phaseshift_b200.runtime.engine import Engine
+    from phaseshift_b200.runtime.state import StateConfig
+    cfg = tiny_config()
+    hf = random_hf_weights(cfg, seed=0)
+    ew = build_engine_weights(cfg, lambda n: hf[n], "nvfp4", "cuda")
+    prompt = list(range(11, 60))
+    sc = StateConfig(max_slots=4, max_seq_len=512, kv_dtype="fp8_e4m3")
+    plain = Engine(ew, "cuda", sc).generate(prompt, 16, prefill_chunk=32)
+    eng = Engine(ew, "cuda", sc, arena_gib=1.0)
+    assert eng.generate(prompt, 16, prefill_chunk=32) == plain
+    st = eng.state
+    assert set(eng.arenas.arenas) == {"kv", "state"}
+    kv = eng.arenas.arenas["kv"]
+    assert kv.base <= st.kv[3].k.data_ptr() < kv.base + kv.reserved
+    need = st.kv_bytes()
+    assert need <= kv.committed <= need + (64 << 20)           # exactly what the configuration needs, rounded to chunks
+    assert eng.arenas.committed() < (1 << 30)
+    with pytest.raises(MemoryError):
+        Engine(ew, "cuda", StateConfig(max_slots=64, max_seq_len=65536, kv_dtype="bf16"), arena_gib=0.05)
