@@ -124,7 +124,8 @@ class ComputeRuntime:
                                                vocab_type=info.get("vocab_type", "byte_level"))
         self.serving = ServingEngine(self.engine, max_step_tokens=a.max_scheduled_tokens,
                                      prefix_cache_tokens=a.prefix_cache_capacity_tokens,
-                                     prefix_cache_entries=a.prefix_cache_max_entries, constraint_compiler=compiler)
+                                     prefix_cache_entries=a.prefix_cache_max_entries, constraint_compiler=compiler,
+                                     terminal_checkpoints=a.prefix_cache_capacity_tokens > 0)
         self.spec = None
         if spec:
             from ..models.dflash2.decoder import DFlash2SpecDecoder
@@ -134,7 +135,9 @@ class ComputeRuntime:
             # served requests go through speculative rounds too (one request at a time, like the reference's
             # serve_step_dflash, src/apps/compute/main.hip:1077-1124); the plain loop stays available as `plain_serving`
             self.plain_serving = self.serving
-            self.serving = SpecServingEngine(self.spec, prefill_chunk=a.max_scheduled_tokens, constraint_compiler=compiler)
+            self.serving = SpecServingEngine(self.spec, prefill_chunk=a.max_scheduled_tokens, constraint_compiler=compiler,
+                                             prefix_cache_tokens=a.prefix_cache_capacity_tokens,
+                                             prefix_cache_entries=a.prefix_cache_max_entries)
 
 
 def run_single_shot(a, rt: ComputeRuntime, out=None) -> int:

@@ -213,6 +213,18 @@ class DFlash2Drafter:
         self.ring_pos.fill_(-1)
         self.context_len = 0
 
+    def snapshot(self):
+        """The context ring as of now (clones): what a prefix-cache entry keeps beside the target's state, so that a
+        restored prefix can be drafted from at once (reference: docs/developer/prefix_cache.md:27-47)."""
+        return (self.k_ring.clone(), self.v_ring.clone(), self.ring_pos.clone(), self.context_len)
+
+    def restore(self, snap) -> None:
+        k, v, p, n = snap
+        self.k_ring.copy_(k)
+        self.v_ring.copy_(v)
+        self.ring_pos.copy_(p)
+        self.context_len = n
+
     # ------------------------------------------------------------------ pieces
     def _conv(self, x, prefix: str, phase: int, dyn=None):
         """Grouped dynamic causal conv over the block rows (kernel 2, block-local, zero left padding).

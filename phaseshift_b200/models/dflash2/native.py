@@ -125,6 +125,18 @@ class DFlash2NativeDrafter:
         self.ring_pos.fill_(-1)
         self.context_len = 0
 
+    def snapshot(self):
+        """The context ring as of now (clones): what a prefix-cache entry keeps beside the target's state, so that a
+        restored prefix can be drafted from at once (reference: docs/developer/prefix_cache.md:27-47)."""
+        return (self.k_ring.clone(), self.v_ring.clone(), self.ring_pos.clone(), self.context_len)
+
+    def restore(self, snap) -> None:
+        k, v, p, n = snap
+        self.k_ring.copy_(k)
+        self.v_ring.copy_(v)
+        self.ring_pos.copy_(p)
+        self.context_len = n
+
     # ------------------------------------------------------------------ op wrappers
     def _linear(self, x: torch.Tensor, W: LinearW, name: str, **kw) -> torch.Tensor:
         if self._collect is not None:

@@ -34,7 +34,7 @@ class ServeEvent:
 class ServingEngine:
     def __init__(self, engine: Engine, max_step_tokens: int = 2048, max_step_requests: int = 0,
                  prefix_cache_tokens: int = 0, prefix_cache_entries: int = 16, prefix_min_tokens: int = 64,
-                 full_claim: bool = False, constraint_compiler=None):
+                 full_claim: bool = False, constraint_compiler=None, terminal_checkpoints: bool = False):
         rt = runtime()
         self.rt, self.engine = rt, engine
         cfg = rt.BatcherConfig()
@@ -50,7 +50,12 @@ class ServingEngine:
             if prefix_cache_tokens > 0 else None
         self.constraints = constraint_compiler
         self.matchers: Dict[int, object] = {}
-        self.stats = {"steps": 0, "tokens": 0, "prefill_tokens": 0, "failed_steps": 0}
+        # terminal checkpoints (reference: src/phaseshift/models/qwen35/runtime/prefix_cache.cpp:229,391): when a request
+        # finishes, everything it fed to the model (prompt + all generated tokens but the last) is cached, so the next
+        # turn of the same conversation restores it instead of prefilling it again
+        self.terminal_checkpoints = terminal_checkpoints and self.prefix is not None
+        self.stops: Dict[int, frozenset] = {}
+        self.stats = {"steps": 0, "tokens": 0, "prefill_tokens": 0, "failed_steps": 0, "terminal_checkpoints": 0}
 
     # ------------------------------------------------------------------ requests
     def submit(self, prompt: Sequence[int], max_new_tokens: int, temperature: float = 0.0, top_p: float = 1.0,
@@ -58,6 +63,7 @@ class ServingEngine:
                grammar: Optional[str] = None, structural_tag: Optional[str] = None) -> int:
         s = self.rt.Sampling(temperature, top_p, top_k, seed)
         rid = self.batcher.submit(list(prompt), max_new_tokens, s, list(stop_tokens), checkpoint_position)
+        self.stops[rid] = frozenset(int(t) for t in stop_tokens)
         if grammar is not None or structural_tag is not None:
             if self.constraints is None:
                 self.batcher.cancel(rid)
@@ -123,6 +129,8 @@ class ServingEngine:
             m = self.matchers.get(rid)
             if m is not None and tok >= 0 and not m.accept(tok):
                 sampled[masked.index(rid)] = -1
+        if self.terminal_checkpoints:
+            self._save_terminal(masked, sampled)
         for (kind, rid, tok) in b.commit(plan, list(sampled)):
             if kind == 0:
                 self.stats["tokens"] += 1
@@ -160,9 +168,23 @@ class ServingEngine:
                 "message": r["error"]}
 
     def _maybe_save_terminal(self, r: dict) -> None:
-        """Terminal checkpoints are written while the request still owns its pages, i.e. by `save_terminal`
-        from the event consumer; finished requests have already released them, so nothing to do here."""
-        return
+        self.stops.pop(r["id"], None)
+
+    def _save_terminal(self, rids: List[int], sampled) -> None:
+        """Before the step is committed (the requests still own their pages): snapshot every request this step's
+        token finishes.  The device state covers exactly the tokens fed so far = prompt + generated (the token
+        sampled now has not been fed), which is what a follow-up prompt will start with."""
+        b = self.batcher
+        for rid, tok in zip(rids, sampled):
+            r = b.request(rid)
+            if r is None or tok < 0:
+                continue
+            fed = list(r["prompt"]) + list(r["generated"])
+            if r["position"] + 0 < len(r["prompt"]):
+                continue                                   # still prefilling (cannot finish)
+            finishing = tok in self.stops.get(rid, ()) or len(r["generated"]) + 1 >= r["max_new_tokens"]
+            if finishing and self.prefix.save(fed, r["slot"], r["pages"]):
+                self.stats["terminal_checkpoints"] += 1
 
     def _fill_masks(self, rids: List[int]):
         vocab = self.engine.cfg.vocab_size

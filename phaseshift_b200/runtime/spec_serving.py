@@ -30,10 +30,18 @@ class _QueueFacade:
 
 
 class SpecServingEngine:
-    def __init__(self, decoder, prefill_chunk: int = 2048, constraint_compiler=None):
+    def __init__(self, decoder, prefill_chunk: int = 2048, constraint_compiler=None, prefix_cache_tokens: int = 0,
+                 prefix_cache_entries: int = 8, prefix_min_tokens: int = 64, terminal_checkpoints: bool = True):
+        """``prefix_cache_tokens`` > 0: prompt-boundary and terminal checkpoints as in plain serving; an entry also
+        keeps the drafter's context ring, so a restored prefix is drafted from at once."""
         self.dec, self.engine = decoder, decoder.eng
         self.prefill_chunk = prefill_chunk
         self.constraints = constraint_compiler
+        self.prefix = None
+        if prefix_cache_tokens > 0 and hasattr(decoder.drafter, "snapshot"):
+            from .prefix_cache import PrefixCache
+            self.prefix = PrefixCache(self.engine, prefix_cache_tokens, prefix_cache_entries, prefix_min_tokens)
+        self.terminal_checkpoints = terminal_checkpoints
         self.requests: Dict[int, dict] = {}
         self.queue: Deque[int] = deque()
         self.active: Optional[int] = None
@@ -61,7 +69,8 @@ class SpecServingEngine:
         self.requests[rid] = dict(id=rid, prompt=prompt, max_new_tokens=int(max_new_tokens), generated=[], state="queued",
                                   samp=dict(temperature=temperature, top_p=top_p, top_k=top_k, seed=seed),
                                   stop=set(int(t) for t in stop_tokens), matcher=matcher, prefilled=0, finish_reason="",
-                                  prompt_tokens=len(prompt), restored_tokens=0, prefill_tokens=0, error="")
+                                  prompt_tokens=len(prompt), restored_tokens=0, prefill_tokens=0, error="",
+                                  checkpoint_position=int(checkpoint_position), checkpoint_saved=False)
         self.queue.append(rid)
         return rid
 
@@ -98,18 +107,25 @@ class SpecServingEngine:
             r["state"] = "prefill"
             self.dec.drafter.reset()
             self.seq = self.engine.open_sequence()
+            self._restore_prefix(r)
         rid = self.active
         r = self.requests[rid]
         self.stats["steps"] += 1
         try:
             if r["state"] == "prefill":
                 c0 = r["prefilled"]
-                ids = r["prompt"][c0:c0 + self.prefill_chunk]
+                end = c0 + self.prefill_chunk
+                cp = r["checkpoint_position"]
+                if self.prefix is not None and c0 < cp < min(end, len(r["prompt"])):
+                    end = cp                                 # a chunk ends exactly at the checkpoint so it can be saved
+                ids = r["prompt"][c0:end]
                 last = c0 + len(ids) >= len(r["prompt"])
                 tok = self.dec.prefill_chunk(self.seq, ids, last, r["samp"], r["matcher"])
                 r["prefilled"] += len(ids)
                 r["prefill_tokens"] += len(ids)
                 self.stats["prefill_tokens"] += len(ids)
+                if self.prefix is not None and cp and r["prefilled"] == cp and not last:
+                    r["checkpoint_saved"] = self._save_prefix(r["prompt"][:cp])
                 if not last:
                     return ev
                 r["state"] = "decode"
@@ -140,12 +156,39 @@ class SpecServingEngine:
             r["finish_reason"] = "length"
         if r["finish_reason"]:
             r["state"] = "done"
+            if self.prefix is not None and self.terminal_checkpoints and r["finish_reason"] in ("stop", "length"):
+                fed = (r["prompt"] + r["generated"])[:self.seq.position]     # what the device state covers
+                self._save_prefix(fed)
             self._release()
             ev.append(ServeEvent("done", rid, info={"generated_ids": list(r["generated"]), "finish_reason": r["finish_reason"],
-                                                    "prompt_tokens": r["prompt_tokens"], "restored_tokens": 0,
-                                                    "prefill_tokens": r["prefill_tokens"], "cache_checkpoint_tokens": 0,
+                                                    "prompt_tokens": r["prompt_tokens"], "restored_tokens": r["restored_tokens"],
+                                                    "prefill_tokens": r["prefill_tokens"],
+                                                    "cache_checkpoint_tokens": r["checkpoint_position"] if r["checkpoint_saved"] else 0,
                                                     "message": ""}))
         return ev
+
+    # ------------------------------------------------------------------ prefix cache
+    def _save_prefix(self, tokens: Sequence[int]) -> bool:
+        s = self.seq
+        if s.position != len(tokens) or len(tokens) == 0:
+            return False
+        return self.prefix.save(list(tokens), s.slot, s.pages, extra=self.dec.drafter.snapshot())
+
+    def _restore_prefix(self, r: dict) -> None:
+        if self.prefix is None:
+            return
+        hit = self.prefix.lookup(r["prompt"])
+        if hit is None or hit.tokens >= len(r["prompt"]):
+            return
+        s = self.seq
+        self.engine._reserve(s, hit.tokens)
+        n_pages = -(-hit.tokens // self.engine.sc.page_tokens)
+        ring = self.prefix.restore(hit, s.slot, s.pages[:n_pages])
+        if ring is None:
+            return
+        self.dec.drafter.restore(ring)
+        s.position = hit.tokens
+        r["prefilled"] = r["restored_tokens"] = hit.tokens
 
     def run_until_idle(self, max_steps: int = 1_000_000) -> List[ServeEvent]:
         ev: List[ServeEvent] = []

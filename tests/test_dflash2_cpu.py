@@ -160,3 +160,29 @@ def test_constrained_speculative_decoding_stays_in_the_grammar():
         assert text.split(" ")[0] in ("yes", "no") and len(text.split(" ")[1]) == 5
         if mode == "oracle":
             assert dec.stats["accepted"] > 0
+
+
+def test_speculative_serving_restores_prefixes_with_the_drafter_ring(setup):
+    """Prefix cache under speculative serving: a prompt-boundary checkpoint and a terminal checkpoint both keep the
+    drafter's context ring; requests that hit them skip the prefill, draft from the restored ring, and still emit the
+    plain greedy stream."""
+    from phaseshift_b200.runtime.spec_serving import SpecServingEngine
+    cfg, ew, prompt, ref = setup
+    dec = _decoder(cfg, ew, k=4)
+    srv = SpecServingEngine(dec, prefill_chunk=8, prefix_cache_tokens=512, prefix_cache_entries=4, prefix_min_tokens=8)
+    a = srv.submit(prompt, 10, checkpoint_position=16)
+    ev = srv.run_until_idle()
+    done = {e.request_id: e.info for e in ev if e.kind == "done"}
+    assert done[a]["generated_ids"] == ref[:10] and done[a]["cache_checkpoint_tokens"] == 16
+    other = prompt[:16] + [7, 8, 9, 10, 11]
+    b = srv.submit(other, 6)
+    ev = srv.run_until_idle()
+    done = {e.request_id: e.info for e in ev if e.kind == "done"}
+    assert done[b]["restored_tokens"] == 16 and done[b]["prefill_tokens"] == len(other) - 16
+    assert done[b]["generated_ids"] == Engine(ew, "cpu", StateConfig(max_slots=1, max_seq_len=96)).generate(other, 6)
+    turn2 = prompt + ref[:10] + [3, 4, 5]                   # continues the first conversation: terminal checkpoint
+    c = srv.submit(turn2, 5)
+    ev = srv.run_until_idle()
+    done = {e.request_id: e.info for e in ev if e.kind == "done"}
+    assert done[c]["restored_tokens"] >= len(prompt) + 8
+    assert done[c]["generated_ids"] == Engine(ew, "cpu", StateConfig(max_slots=1, max_seq_len=96)).generate(turn2, 5)

@@ -73,3 +73,31 @@ def test_cancel_and_stop_token(tiny):
     assert srv.cancel(r2) and srv.request(r2)["finish_reason"] == "cancelled"
     toks, done = _collect(ev + srv.run_until_idle())
     assert toks[r1] == ref[:3] and done[r1].info["finish_reason"] == "stop"
+
+
+def test_terminal_checkpoint_serves_the_next_turn_and_pool_is_bounded(tiny):
+    """A finished request leaves a checkpoint of everything it fed to the model; the next turn of the conversation
+    (old prompt + old answer + new text) restores it and only prefills the new part.  The cache's storage is a pool
+    allocated once: saving more than fits evicts, never grows."""
+    cfg, hf, ew = tiny
+    eng = Engine(ew, "cpu", StateConfig(max_slots=2, max_seq_len=200, page_tokens=16))
+    srv = ServingEngine(eng, max_step_tokens=64, prefix_cache_tokens=256, prefix_cache_entries=3, prefix_min_tokens=16,
+                        terminal_checkpoints=True)
+    pool0 = srv.prefix.pool_bytes()
+    p1 = _prompt(cfg, 40, 21)
+    r1 = srv.submit(p1, 9)
+    toks, done = _collect(srv.run_until_idle())
+    a1 = toks[r1]
+    assert a1 == reference_greedy(cfg, hf, p1, 9) and srv.stats["terminal_checkpoints"] == 1
+    p2 = p1 + a1 + _prompt(cfg, 6, 22)                      # second turn
+    r2 = srv.submit(p2, 5)
+    toks, done = _collect(srv.run_until_idle())
+    assert done[r2].info["restored_tokens"] == len(p1) + len(a1) - 1          # the last token was sampled, never fed
+    assert done[r2].info["prefill_tokens"] == len(p2) - done[r2].info["restored_tokens"]
+    assert toks[r2] == reference_greedy(cfg, hf, p2, 5)
+    for seed in range(30, 36):                              # more conversations than the pool holds
+        srv.submit(_prompt(cfg, 50 + seed, seed), 3)
+    srv.run_until_idle()
+    s = srv.prefix.summary()
+    assert srv.prefix.pool_bytes() == pool0 and s["entries"] <= 3 and s["evictions"] > 0
+    assert s["pool_pages_free"] + sum(len(x.pages) for x in srv.prefix.snaps.values()) == srv.prefix.pool_pages
