@@ -44,30 +44,41 @@ class Sequence_:
 
 
 class PageAllocator:
-    """Free-list over KV pages (page 0 reserved) + per-slot generation counters for stale-handle
-    detection (reference: state/sequence_slot_pool.h:14-96, state/paged_kv_pool.h free-page list)."""
+    """Slots and KV pages of the engine's own (non-batcher) sequences: a thin adapter over the host runtime's
+    ``SlotPool`` / ``PagePool`` (csrc/runtime/runtime_core.cpp) -- the same free lists, generation counters and
+    stale-handle check the serving batcher uses; page 0 stays reserved
+    (reference: state/sequence_slot_pool.h:14-96, state/paged_kv_pool.h)."""
 
     def __init__(self, num_pages: int, max_slots: int):
-        self.free_pages = list(range(num_pages - 1, 0, -1))
-        self.free_slots = list(range(max_slots - 1, -1, -1))
+        from ..core.native import runtime
+        rt = runtime()
+        self.slots, self.pages = rt.SlotPool(max_slots), rt.PagePool(num_pages)
+        self.handles: Dict[int, object] = {}
         self.generation = [0] * max_slots
 
     def alloc_slot(self) -> Optional[int]:
-        return self.free_slots.pop() if self.free_slots else None
+        h = self.slots.acquire()
+        if h.slot < 0:
+            return None
+        self.handles[h.slot] = h
+        self.generation[h.slot] = h.generation
+        return h.slot
 
     def release_slot(self, slot: int) -> None:
+        self.slots.release(self.handles.pop(slot))      # raises on a stale handle
         self.generation[slot] += 1
-        self.free_slots.append(slot)
 
     def alloc_page(self) -> Optional[int]:
-        return self.free_pages.pop() if self.free_pages else None
+        p = self.pages.acquire()
+        return None if p < 0 else p
 
     def release_pages(self, pages: Sequence[int]) -> None:
-        self.free_pages.extend(pages)
+        for p in pages:
+            self.pages.release(int(p))
 
     @property
     def pages_free(self) -> int:
-        return len(self.free_pages)
+        return int(self.pages.free_count())
 
 
 class Engine:
@@ -120,6 +131,8 @@ class Engine:
         self.h_tokens = torch.zeros(2048, dtype=torch.int32, pin_memory=(self.device.type == "cuda"))
         self.h_status = torch.zeros(2, dtype=torch.int32, pin_memory=(self.device.type == "cuda"))
         self.h_extra = torch.zeros(64, dtype=torch.int32, pin_memory=(self.device.type == "cuda"))
+        self._h_pages = torch.zeros(64, max(64, self.state.max_blocks), dtype=torch.int32, pin_memory=(self.device.type == "cuda"))
+        self._h_pages_next = 0
         self.graph_variants = True      # verification / tapped steps replay captured graphs too
         self.graph_refs: Dict[object, object] = {}
         self.steps = 0
@@ -278,9 +291,21 @@ class Engine:
             s.pages.append(pg)
             added += 1
         if new_entries:
-            idx0 = new_entries[0][0]
-            vals = torch.tensor([p for _, p in new_entries], dtype=torch.int32)
-            self.state.block_table[s.slot, idx0:idx0 + len(vals)] = vals.to(self.device)
+            idx0, n = new_entries[0][0], len(new_entries)
+            if self.device.type == "cuda":
+                # pinned staging ring: no pageable (synchronous) host-to-device copy on the step path; a region is
+                # reused only after `_h_pages_slots` further reservations, by which time its copy has long been issued
+                # and consumed in stream order
+                if n > self._h_pages.shape[1]:
+                    self._h_pages = torch.zeros(self._h_pages.shape[0], n, dtype=torch.int32, pin_memory=True)
+                row = self._h_pages[self._h_pages_next % self._h_pages.shape[0]]
+                self._h_pages_next += 1
+                if self._h_pages_next % self._h_pages.shape[0] == 0:
+                    torch.cuda.current_stream().synchronize()      # once per ring cycle: every staged copy has landed
+                row[:n] = torch.as_tensor([p for _, p in new_entries], dtype=torch.int32)
+                self.state.block_table[s.slot, idx0:idx0 + n].copy_(row[:n], non_blocking=True)
+            else:
+                self.state.block_table[s.slot, idx0:idx0 + n] = torch.tensor([p for _, p in new_entries], dtype=torch.int32)
         return added
 
     def trim_pages(self, s: Sequence_) -> None:
