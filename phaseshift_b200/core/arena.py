@@ -105,7 +105,11 @@ class ArenaSet:
         if a is None:
             if sum(x.reserved for x in self.arenas.values()) + reserve_bytes > self.budget:
                 raise MemoryError(f"arena budget exceeded while reserving '{name}'")
-            a = GpuArena(reserve_bytes, self.device, name=name)
+            # physical memory is committed in chunks: small arenas get small chunks so that the commitment tracks the need
+            chunk = 2 << 20
+            while chunk < (256 << 20) and chunk * 16 < reserve_bytes:
+                chunk *= 2
+            a = GpuArena(reserve_bytes, self.device, chunk_bytes=chunk, name=name)
             self.arenas[name] = a
         return a
 
