@@ -113,6 +113,19 @@ __host__ __device__ inline int unit_owner(int total, int grid, int x) {
     return x < boundary ? x / (base + 1) : rem + (x - boundary) / base;
 }
 
+// Walks a CTA's unit range as groups of up to G consecutive K-panels of one tile: one pipeline stage each.  Producer and
+// consumers walk the same sequence (a segment of BsSegIter splits into the same groups).
+struct BsGroupIter {
+    int u, u_end, P, G;
+    __device__ __forceinline__ bool next(int& t, int& p, int& gn) {
+        if (u >= u_end) return false;
+        t = u / P; p = u - t * P;
+        gn = min(G, min(P - p, u_end - u));
+        u += gn;
+        return true;
+    }
+};
+
 // Walks a CTA's unit range as segments (tile, [p0, p1)).
 struct BsSegIter {
     int u, u_end, P;
@@ -214,9 +227,12 @@ __device__ __forceinline__ void load_act_block(const __nv_bfloat16* xr, const __
 // Byte offset of scale factor (row r, atom-local K-block j) inside a 512-byte atom.
 __host__ __device__ __forceinline__ int sf_atom_off(int r, int j) { return (r & 31) * 16 + ((r >> 5) & 3) * 4 + j; }
 
-// Threads per CTA: warp 0 producer, warp 1 MMA issuer, warps 2..5 epilogue; the resident variant adds six warps
-// that only help in the activation prologue (one (slot, block) pair per thread instead of two in a row).
-template <bool RES> constexpr int bs_threads() { return RES ? 384 : kBsThreads; }
+// Threads per CTA: warp 0 producer, warp 1 MMA issuer, warps 2..5 epilogue, warp 6 scale-copy issuer; the resident variant
+// adds five more warps that only help in the activation prologue (one (slot, block) pair per thread instead of two in a row).
+// Warp 6 issues the scale-factor copies (tcgen05.cp) one stage ahead of the MMA warp: the two instruction streams of a
+// stage (copies: ~55 cycles each, MMAs: ~86 each at N = 16) run in parallel instead of back to back in one thread.
+template <bool RES> constexpr int bs_threads() { return RES ? 384 : kBsThreads + 32; }
+template <bool RES> constexpr int bs_group() { return RES ? 2 : 1; }      // K-panels per pipeline stage
 
 template <int FMT, int NB, bool RES>
 __global__ void __launch_bounds__(bs_threads<RES>(), 1)
@@ -228,22 +244,30 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     constexpr int NBLK = NB > 128 ? 2 : 1;
     constexpr int kBTile = NB * 128;
     constexpr int kSfaBytes = APP * 512, kSfbBytes = NBLK * APP * 512;
-    constexpr int kStageRaw = RES ? (kBsATile + kSfaBytes) : (kBsATile + kBTile + kSfaBytes + kSfbBytes);
+    // Resident path: a pipeline stage holds G = 2 weight panels, so the MMA thread's per-stage costs (two barrier waits, the
+    // commit, loop control: ~600 of ~920 cycles per 16 KB panel, measured) are paid once per 32 KB.
+    constexpr int G = bs_group<RES>();
+    constexpr int kStageRaw = RES ? G * (kBsATile + kSfaBytes) : (kBsATile + kBTile + kSfaBytes + kSfbBytes);
     constexpr int kStage = (kStageRaw + 1023) / 1024 * 1024;
     constexpr int kOffB = kBsATile;
-    constexpr int kOffSfa = RES ? kBsATile : kBsATile + kBTile;
+    constexpr int kOffSfa = RES ? G * kBsATile : kBsATile + kBTile;
     constexpr int kOffSfb = kOffSfa + kSfaBytes;
-    constexpr uint32_t kStageTx = RES ? (kBsATile + kSfaBytes) : (kBsATile + kBTile + kSfaBytes + kSfbBytes);
+    constexpr uint32_t kPanelTx = RES ? (kBsATile + kSfaBytes) : (kBsATile + kBTile + kSfaBytes + kSfbBytes);   // bytes per panel of a stage
     constexpr int kResSfWords = APP * 32;           // resident path: 32-bit scale words per panel slot (4 K-blocks each)
     constexpr int ACC_BUFS = NB <= 128 ? 2 : 1;
     constexpr int ACC_STRIDE = NB < 32 ? 32 : NB;
     constexpr uint32_t SF_COL0 = ACC_BUFS * ACC_STRIDE;
-    constexpr uint32_t SFA_COLS = 4 * APP, SFB_COLS = RES ? 0 : 4 * APP * NBLK, SF_BUF_COLS = SFA_COLS + SFB_COLS;
+    constexpr uint32_t SFA_COLS = 4 * APP, SFB_COLS = RES ? 0 : 4 * APP * NBLK, SF_BUF_COLS = G * SFA_COLS + SFB_COLS;
     // resident activation scales: one 4-column granule per (slot, K-block group), like a tcgen05.cp would fill;
     // only the first column of a granule is written and read (batch rows < 32), but the MMA's scale address
     // stays 4-column aligned
-    constexpr uint32_t SFB_RES_COL0 = SF_COL0 + 2 * SF_BUF_COLS;
-    static_assert(SF_COL0 + 2 * SF_BUF_COLS <= 512, "tensor memory budget");
+    // Streamed path: warp 6 issues the scale-factor copies ahead of the MMA warp (12 copies per stage would otherwise sit in
+    // front of 4 MMAs in one instruction stream: +19 % at 2048 rows).  Resident path: 4 copies per stage, the hand-over between
+    // two threads costs more than it saves (measured), so the MMA thread issues them itself.
+    constexpr bool kSplitSf = !RES;
+    constexpr int kSfBufs = kSplitSf ? 4 : 2;        // scale-factor column sets in flight
+    constexpr uint32_t SFB_RES_COL0 = SF_COL0 + kSfBufs * SF_BUF_COLS;
+    static_assert(SF_COL0 + kSfBufs * SF_BUF_COLS <= 512, "tensor memory budget");
     constexpr int CH = NB == 16 ? 16 : 32;          // accumulator columns read per tcgen05.ld
 
     extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -252,6 +276,7 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     __nv_bfloat16* sEpi = reinterpret_cast<__nv_bfloat16*>(sBres);                    // streamed path: 128 x 128 bf16 output staging
     uint32_t* sSfRes = reinterpret_cast<uint32_t*>(sBres + (size_t)g.res_slots * kBTile);   // [slot][APP][32 rows] scale words
     __shared__ __align__(8) uint64_t full_bar[kBsMaxStages], empty_bar[kBsMaxStages], acc_full[2], acc_empty[2], drain_bar;
+    __shared__ __align__(8) uint64_t sf_ready[4], sf_free[4];      // scale-factor columns of a stage parity: copied / consumed
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile int s_abort;
     __shared__ int s_issued, s_consumed;
@@ -268,23 +293,30 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
     // ---- set-up: the barriers are initialised by two threads in parallel, then thread 0 at once fills the ring
     // with weights (they do not depend on the stream predecessor) while warps 1..5 go on to the prologue
-    const int pre = min(u1 - u0, stages);
+    // weights (and their scale atoms) of one group into stage slot `slot`
+    auto issue_weights = [&](int slot, int t, int p, int gn) {
+        const int tn = t / g.tiles_m;
+        unsigned char* st = smem + (size_t)slot * kStage;
+        tc::mbar_expect_tx(&full_bar[slot], (uint32_t)gn * kPanelTx);
+        for (int j = 0; j < gn; ++j) {
+            tc::tma_load_2d(st + j * kBsATile, &map_w, (p + j) * 128, tn * kBsTileN, &full_bar[slot]);
+            tc::bulk_load(st + kOffSfa + j * kSfaBytes, g.sfw + ((size_t)tn * P + p + j) * kSfaBytes, kSfaBytes, &full_bar[slot]);
+        }
+    };
+    BsGroupIter GI{u0, u1, P, G};               // thread 0's walk: ring fill here, the rest in the producer role
+    int pre = 0;                                // groups issued before the dependency sync (thread 0 only)
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; ++s) tc::mbar_init(&full_bar[s], 1);
         tc::fence_barrier_init();
         s_abort = 0; s_issued = 0; s_consumed = 0;
-        for (int i = 0; i < pre; ++i) {
-            const int u = u0 + i, t = u / P, p = u - t * P, tn = t / g.tiles_m;
-            unsigned char* st = smem + (size_t)i * kStage;
-            tc::mbar_expect_tx(&full_bar[i], kStageTx);
-            tc::tma_load_2d(st, &map_w, p * 128, tn * kBsTileN, &full_bar[i]);
-            tc::bulk_load(st + kOffSfa, g.sfw + ((size_t)tn * P + p) * kSfaBytes, kSfaBytes, &full_bar[i]);
-        }
+        int t, p, gn;
+        while (pre < stages && GI.next(t, p, gn)) { issue_weights(pre, t, p, gn); ++pre; }
         if (!RES) tc::tma_prefetch_desc(&map_x);
     } else if (threadIdx.x == 64) {
         for (int s = 0; s < stages; ++s) tc::mbar_init(&empty_bar[s], 1);
         for (int b = 0; b < 2; ++b) { tc::mbar_init(&acc_full[b], 1); tc::mbar_init(&acc_empty[b], 4); }
         tc::mbar_init(&drain_bar, 1);
+        for (int b = 0; b < 4; ++b) { tc::mbar_init(&sf_ready[b], 1); tc::mbar_init(&sf_free[b], 1); }
         tc::fence_barrier_init();
     }
     if (warp == 1) {
@@ -472,34 +504,30 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // ------------------------------------------------ TMA producer
         if (lane == 0) {
             int issued = pre;
+            // activation half of a (single-panel) stage of the streamed path
+            auto issue_acts = [&](int slot, int t, int p) {
+                const int tm = t % g.tiles_m;
+                unsigned char* st = smem + (size_t)slot * kStage;
+                tc::tma_load_2d(st + kOffB, &map_x, p * 128, tm * NB, &full_bar[slot]);
+#pragma unroll
+                for (int j = 0; j < NBLK; ++j)
+                    tc::bulk_load(st + kOffSfb + j * kSfaBytes, g.sfx + ((size_t)(tm * NBLK + j) * P + p) * kSfaBytes, kSfaBytes, &full_bar[slot]);
+            };
             if constexpr (!RES) {
                 for (int i = 0; i < pre; ++i) {     // activation halves of the stages filled before the dependency sync
-                    const int u = u0 + i, t = u / P, p = u - t * P, tm = t % g.tiles_m;
-                    unsigned char* st = smem + (size_t)i * kStage;
-                    tc::tma_load_2d(st + kOffB, &map_x, p * 128, tm * NB, &full_bar[i]);
-#pragma unroll
-                    for (int j = 0; j < NBLK; ++j)
-                        tc::bulk_load(st + kOffSfb + j * kSfaBytes, g.sfx + ((size_t)(tm * NBLK + j) * P + p) * kSfaBytes, kSfaBytes, &full_bar[i]);
+                    const int u = u0 + i, t = u / P;
+                    issue_acts(i, t, u - t * P);
                 }
             }
             long long prof_pwait = 0;
-            for (int it = pre; u0 + it < u1; ++it) {
+            int t, p, gn;
+            for (int it = pre; GI.next(t, p, gn); ++it) {
                 const int s = it % stages;
                 const long long tp0 = prof ? clock64() : 0;
                 if (!tc::mbar_wait_abortable(&empty_bar[s], (uint32_t)((it / stages) & 1) ^ 1u, g.budget, &s_abort)) break;
                 if (prof) prof_pwait += clock64() - tp0;
-                const int u = u0 + it, t = u / P, p = u - t * P, tn = t / g.tiles_m;
-                unsigned char* st = smem + (size_t)s * kStage;
-                tc::mbar_expect_tx(&full_bar[s], kStageTx);
-                tc::tma_load_2d(st, &map_w, p * 128, tn * kBsTileN, &full_bar[s]);
-                tc::bulk_load(st + kOffSfa, g.sfw + ((size_t)tn * P + p) * kSfaBytes, kSfaBytes, &full_bar[s]);
-                if constexpr (!RES) {
-                    const int tm = t % g.tiles_m;
-                    tc::tma_load_2d(st + kOffB, &map_x, p * 128, tm * NB, &full_bar[s]);
-#pragma unroll
-                    for (int j = 0; j < NBLK; ++j)
-                        tc::bulk_load(st + kOffSfb + j * kSfaBytes, g.sfx + ((size_t)(tm * NBLK + j) * P + p) * kSfaBytes, kSfaBytes, &full_bar[s]);
-                }
+                issue_weights(s, t, p, gn);
+                if constexpr (!RES) issue_acts(s, t, p);
                 issued = it + 1;
             }
             s_issued = issued;
@@ -509,7 +537,7 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 // projection that follows, so that kernel's ring fill does not start from DRAM
                 int n0, n1;
                 cta_range(g.next_total, g.next_grid, blockIdx.x, n0, n1);
-                const int cnt = min(n1 - n0, g.next_stages);
+                const int cnt = min(n1 - n0, g.next_stages * G);
                 for (int i = 0; i < cnt; ++i) {
                     const int u = n0 + i, t = u / g.next_P, p = u - t * g.next_P, tn = t / g.next_tiles_m;
                     tc::tma_prefetch_l2_2d(&map_next, p * 128, tn * kBsTileN);
@@ -520,11 +548,11 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     } else if (warp == 1) {
         // ------------------------------------------------ MMA issuer
         if (lane == 0) {
-            int it = 0, seg = 0, t, p0, p1, s = 0;
+            int it = 0, pi = 0, seg = 0, t, p0, p1, s = 0;      // it: stages consumed, pi: panels consumed
             uint32_t full_phase = 0;
             BsSegIter S{u0, u1, P};
             bool ok = true;
-            long long prof_wait = 0;
+            long long prof_wait = 0, prof_sf = 0, prof_mma = 0, prof_commit = 0;
             // descriptor low words (address >> 4) of stage 0; a stage adds kStage >> 4, a K-block 2 (32 bytes)
             const uint32_t a_lo0 = ((tc::smem_u32(smem) >> 4) & 0x3FFFu) | tc::kDescSw128LoFlags;
             const uint32_t sfa_lo0 = (tc::smem_u32(smem + kOffSfa) >> 4) & 0x3FFFu;
@@ -536,29 +564,97 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     tc::fence_after_sync();
                 }
                 const uint32_t acc = tmem_base + (uint32_t)(buf * ACC_STRIDE);
-                for (int p = p0; p < p1; ++p, ++it) {
+                for (int p = p0; p < p1; ++it) {
+                    const int gn = min(G, p1 - p);               // panels in this stage
                     const long long tw0 = prof ? clock64() : 0;
                     if (!tc::mbar_wait_abortable(&full_bar[s], full_phase, g.budget, &s_abort)) { ok = false; break; }
                     if (prof) prof_wait += clock64() - tw0;
                     tc::fence_after_sync();
                     const uint32_t st_lo = (uint32_t)s * (uint32_t)(kStage >> 4);
-                    const uint32_t sf_t = tmem_base + SF_COL0 + (uint32_t)(it & 1) * SF_BUF_COLS;
-                    const uint32_t a_lo = a_lo0 + st_lo;
-                    uint32_t b_lo, sfb_t;
-                    if constexpr (RES) {
-                        const int slot = g.res_full ? p : it;
-                        b_lo = bres_lo0 + (uint32_t)slot * (uint32_t)(kBTile >> 4);
-                        sfb_t = tmem_base + SFB_RES_COL0 + (uint32_t)slot * (4 * APP);
-                    } else {
-                        b_lo = a_lo + (uint32_t)(kOffB >> 4);
-                        sfb_t = sf_t + SFA_COLS;
+                    const uint32_t sf_t0 = tmem_base + SF_COL0 + (uint32_t)(it % kSfBufs) * SF_BUF_COLS;
+                    const long long ts0 = prof ? clock64() : 0;
+                    if constexpr (kSplitSf) {
+                        // the scale factors of this stage were copied to tensor memory by warp 6
+                        if (!tc::mbar_wait_abortable(&sf_ready[it % kSfBufs], (uint32_t)((it / kSfBufs) & 1), g.budget, &s_abort)) { ok = false; break; }
+                        tc::fence_after_sync();
+                    } else if (!(g.dbg & 1)) {
+                        for (int j = 0; j < gn; ++j)
+#pragma unroll
+                            for (int a = 0; a < APP; ++a)
+                                tc::tmem_cp_sf(sf_t0 + (uint32_t)j * SFA_COLS + 4 * a,
+                                               tc::desc_pack(sfa_lo0 + st_lo + (uint32_t)(j * (kSfaBytes >> 4) + a * 32), tc::kDescSfHi));
                     }
+                    const long long ts1 = prof ? clock64() : 0;
+                    prof_sf += ts1 - ts0;
+                    for (int j = 0; j < gn; ++j, ++pi) {
+                        const uint32_t sf_t = sf_t0 + (uint32_t)j * SFA_COLS;
+                        const uint32_t a_lo = a_lo0 + st_lo + (uint32_t)j * (uint32_t)(kBsATile >> 4);
+                        uint32_t b_lo, sfb_t;
+                        if constexpr (RES) {
+                            const int slot = g.res_full ? p + j : pi;
+                            b_lo = bres_lo0 + (uint32_t)slot * (uint32_t)(kBTile >> 4);
+                            sfb_t = tmem_base + SFB_RES_COL0 + (uint32_t)slot * (4 * APP);
+                        } else {
+                            b_lo = a_lo + (uint32_t)(kOffB >> 4);
+                            sfb_t = sf_t + SFA_COLS;
+                        }
+                        if (!(g.dbg & 4)) {
+#pragma unroll
+                            for (int kb = 0; kb < 4; ++kb) {
+                                const uint64_t adesc = tc::desc_pack(a_lo + 2 * kb, tc::kDescSw128Hi);
+                                const uint64_t bdesc = tc::desc_pack(b_lo + 2 * kb, tc::kDescSw128Hi);
+                                const uint32_t accum = (p + j > p0 || kb > 0) ? 1u : 0u;
+                                if constexpr (FMT == W_NVFP4) {
+                                    constexpr uint32_t idesc = tc::idesc_block_scaled(128, NB, tc::kFmtE2M1_mxf4, tc::kSfUE4M3, 0, 0);
+                                    tc::mma_nvfp4_ss(acc, adesc, bdesc, idesc, accum, sf_t + 4 * kb, sfb_t + 4 * NBLK * kb);
+                                } else {
+                                    const uint32_t idesc = tc::idesc_block_scaled(128, NB, tc::kFmtE4M3, tc::kSfUE8M0, (uint32_t)kb, (uint32_t)kb);
+                                    tc::mma_mxfp8_ss(acc, adesc, bdesc, idesc, accum, sf_t, sfb_t);
+                                }
+                            }
+                        }
+                    }
+                    p += gn;
+                    const long long ts2 = prof ? clock64() : 0;
+                    tc::mma_commit(&empty_bar[s]);
+                    if constexpr (kSplitSf) tc::mma_commit(&sf_free[it % kSfBufs]);
+                    if (prof) { prof_mma += ts2 - ts1; prof_commit += clock64() - ts2; }
+                    if (++s == stages) { s = 0; full_phase ^= 1u; }
+                }
+                if (ok) tc::mma_commit(&acc_full[buf]);
+                ++seg;
+            }
+            s_consumed = it;
+            if (prof) { g.prof[6] = prof_wait; g.prof[7] = clock64(); g.prof[8] = it; g.prof[16] = prof_sf; g.prof[17] = prof_mma; g.prof[18] = prof_commit; }
+            if (!ok || s_abort != 0) {
+                // give MMAs already issued a bounded chance to retire before the tensor memory is freed
+                tc::mma_commit(&drain_bar);
+                tc::mbar_wait(&drain_bar, 0, g.budget < 4000000ll ? g.budget : 4000000ll);
+            }
+        }
+    } else if (warp == 6) {
+        // ------------------------------------------------ scale-factor copies (tcgen05.cp), ahead of the MMAs (streamed path)
+        if (kSplitSf && lane == 0) {
+            int it = 0, t, p0, p1, s = 0;
+            uint32_t full_phase = 0;
+            BsSegIter S{u0, u1, P};
+            bool ok = true;
+            const uint32_t sfa_lo0 = (tc::smem_u32(smem + kOffSfa) >> 4) & 0x3FFFu;
+            while (ok && S.next(t, p0, p1)) {
+                for (int p = p0; p < p1; ++p, ++it) {
+                    // the columns of this parity are free once the MMAs of two stages ago have retired
+                    if (it >= kSfBufs && !tc::mbar_wait_abortable(&sf_free[it % kSfBufs], (uint32_t)((it / kSfBufs - 1) & 1), g.budget, &s_abort)) { ok = false; break; }
+                    if (!tc::mbar_wait_abortable(&full_bar[s], full_phase, g.budget, &s_abort)) { ok = false; break; }
+                    tc::fence_after_sync();
+                    const uint32_t st_lo = (uint32_t)s * (uint32_t)(kStage >> 4);
+                    const uint32_t sf_t = tmem_base + SF_COL0 + (uint32_t)(it % kSfBufs) * SF_BUF_COLS;
                     if (!(g.dbg & 1)) {
 #pragma unroll
                         for (int a = 0; a < APP; ++a)
                             tc::tmem_cp_sf(sf_t + 4 * a, tc::desc_pack(sfa_lo0 + st_lo + (uint32_t)(a * 32), tc::kDescSfHi));
                     }
                     if constexpr (!RES) {
+                        const uint32_t sfb_t = sf_t + SFA_COLS;
                         const uint32_t sfb_lo = sfa_lo0 + st_lo + (uint32_t)(kSfaBytes >> 4);
 #pragma unroll
                         for (int a = 0; a < APP; ++a)
@@ -566,33 +662,9 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                             for (int j = 0; j < NBLK; ++j)
                                 tc::tmem_cp_sf(sfb_t + 4 * (a * NBLK + j), tc::desc_pack(sfb_lo + (uint32_t)((j * APP + a) * 32), tc::kDescSfHi));
                     }
-                    if (!(g.dbg & 4)) {
-#pragma unroll
-                        for (int kb = 0; kb < 4; ++kb) {
-                            const uint64_t adesc = tc::desc_pack(a_lo + 2 * kb, tc::kDescSw128Hi);
-                            const uint64_t bdesc = tc::desc_pack(b_lo + 2 * kb, tc::kDescSw128Hi);
-                            const uint32_t accum = (p > p0 || kb > 0) ? 1u : 0u;
-                            if constexpr (FMT == W_NVFP4) {
-                                constexpr uint32_t idesc = tc::idesc_block_scaled(128, NB, tc::kFmtE2M1_mxf4, tc::kSfUE4M3, 0, 0);
-                                tc::mma_nvfp4_ss(acc, adesc, bdesc, idesc, accum, sf_t + 4 * kb, sfb_t + 4 * NBLK * kb);
-                            } else {
-                                const uint32_t idesc = tc::idesc_block_scaled(128, NB, tc::kFmtE4M3, tc::kSfUE8M0, (uint32_t)kb, (uint32_t)kb);
-                                tc::mma_mxfp8_ss(acc, adesc, bdesc, idesc, accum, sf_t, sfb_t);
-                            }
-                        }
-                    }
-                    tc::mma_commit(&empty_bar[s]);
+                    tc::mma_commit(&sf_ready[it % kSfBufs]);
                     if (++s == stages) { s = 0; full_phase ^= 1u; }
                 }
-                if (ok) tc::mma_commit(&acc_full[buf]);
-                ++seg;
-            }
-            s_consumed = it;
-            if (prof) { g.prof[6] = prof_wait; g.prof[7] = clock64(); g.prof[8] = it; }
-            if (!ok || s_abort != 0) {
-                // give MMAs already issued a bounded chance to retire before the tensor memory is freed
-                tc::mma_commit(&drain_bar);
-                tc::mbar_wait(&drain_bar, 0, g.budget < 4000000ll ? g.budget : 4000000ll);
             }
         }
     } else if (warp < 6) {
@@ -1044,7 +1116,8 @@ static bool bs_plan(int M, int N, int K, bool resident, int grid_override, BsPla
     pl.grid = want < sms ? want : sms;
     const int nblk = pl.nb > 128 ? 2 : 1;
     const int sfa = T::kApp * 512;
-    int stage = resident ? (kBsATile + sfa) : (kBsATile + pl.nb * 128 + sfa + nblk * sfa);
+    const int grp = resident ? bs_group<true>() : 1;
+    int stage = resident ? grp * (kBsATile + sfa) : (kBsATile + pl.nb * 128 + sfa + nblk * sfa);
     stage = (stage + 1023) / 1024 * 1024;
     size_t res_bytes = 0;
     pl.res_slots = 0; pl.res_full = 0;
@@ -1054,7 +1127,7 @@ static bool bs_plan(int M, int N, int K, bool resident, int grid_override, BsPla
         pl.res_full = base >= pl.P ? 1 : 0;
         pl.res_slots = pl.res_full ? pl.P : umax;
         res_bytes = (size_t)pl.res_slots * (pl.nb * 128 + T::kApp * 128);
-        if (96 + pl.res_slots * T::kApp * 4 > 512) return false;      // resident scale columns in tensor memory
+        if (64 + 2 * grp * T::kApp * 4 + pl.res_slots * T::kApp * 4 > 512) return false;   // accumulators + 2 scale sets + resident scale columns
     }
     if (!resident) res_bytes = 128 * 128 * 2;          // output staging block of the streamed path's epilogue
     const size_t avail = kBsSmemBudget - 1024;
@@ -1114,7 +1187,7 @@ PS_API int ps_gemm_bs_plan(int wfmt, int M, int N, int K, int resident, int grid
     return 1;
 }
 
-// Development aid: CTA 0 of later launches writes clock64() stamps of its phases into `buf` (16 x int64 on the
+// Development aid: CTA 0 of later launches writes clock64() stamps of its phases into `buf` (32 x int64 on the
 // device): [0] start, [1] set-up done, [2] stream predecessor done, [3] row statistics done, [4] quantisation done,
 // [5] prologue barrier, [6] cycles the MMA thread waited for data, [7] MMA thread done, [8] stages, [9] epilogue
 // done, [10] end.  Only the launch after `skip_launches` further ones is stamped (also inside a graph capture).
