@@ -131,7 +131,8 @@ class ComputeRuntime:
             from ..models.dflash2.decoder import DFlash2SpecDecoder
             from ..runtime.spec_serving import SpecServingEngine
             self.spec = DFlash2SpecDecoder.from_dir(self.engine, a.dflash2_model_dir, a.dflash2_drafts,
-                                                    ngram_tail=a.dflash2_ngram_tail, ngram_n=a.dflash2_ngram_n)
+                                                    ngram_tail=a.dflash2_ngram_tail, ngram_n=a.dflash2_ngram_n,
+                                                    target_model_dir=a.model_dir)
             # served requests go through speculative rounds too (one request at a time, like the reference's
             # serve_step_dflash, src/apps/compute/main.hip:1077-1124); the plain loop stays available as `plain_serving`
             self.plain_serving = self.serving

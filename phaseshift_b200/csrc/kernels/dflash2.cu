@@ -10,6 +10,7 @@
 //   ps_dfl_kv_ring_append per-layer k-norm + RoPE of the context keys, scatter of K / V into slot pos % window
 //   ps_dfl_feature_concat the tapped target hidden states side by side: [rows, taps * H]
 //   ps_dfl_noise_ids      block token ids and positions from a device control word: anchor, then K mask ids
+//   ps_dfl_remap_ids      draft-vocabulary local ids -> global ids after the top-k
 //   ps_dfl_select         sequential candidate selector over the top-k of every draft row
 //
 // Semantics follow the reference's drafter description (docs/developer/dflash2.md:221-318,363-416,496-568) and
@@ -417,6 +418,14 @@ __global__ void dfl_noise_ids_kernel(const int* __restrict__ ctl, int mask_id, i
     pos[i] = ctl[1] + i;
 }
 
+// local -> global token ids after a top-k over a draft-vocabulary subset (-1 stays -1)
+__global__ void dfl_remap_ids_kernel(int* __restrict__ ids, int n, const int* __restrict__ idmap, int n_map) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int v = ids[i];
+    ids[i] = (v >= 0 && v < n_map) ? idmap[v] : -1;
+}
+
 // ---- sequential candidate selector: one CTA walks the draft rows; for row r every candidate j of its top-kk list gets
 // score_j = logit_j + sum_i pred_cb[prev][i] * hproj[r][i] * succ_cb[cand_j][i]; the best-ranked maximal candidate wins and
 // becomes `prev` of the next row.  The candidates of ALL rows are known up front, so their codebook rows are staged in
@@ -580,5 +589,11 @@ PS_API int ps_dfl_select(const void* top_ids, const void* top_logits, int kk, co
     ps::dfl_select_kernel<<<1, 256, staged ? stage_bytes : 0, stream>>>((const int*)top_ids, (const float*)top_logits, kk, (const float*)hproj, rank,
                                                                        (const __nv_bfloat16*)pred_cb, (const __nv_bfloat16*)succ_cb, (const int*)anchor_dev,
                                                                        anchor_value, K, vocab, (int*)out_tokens, staged);
+    return PS_LAUNCH_CHECK();
+}
+
+PS_API int ps_dfl_remap_ids(void* ids, int n, const void* idmap, int n_map, cudaStream_t stream) {
+    if (n <= 0 || idmap == nullptr) return (int)cudaErrorInvalidValue;
+    ps::dfl_remap_ids_kernel<<<(n + 255) / 256, 256, 0, stream>>>((int*)ids, n, (const int*)idmap, n_map);
     return PS_LAUNCH_CHECK();
 }

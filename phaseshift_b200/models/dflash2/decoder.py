@@ -78,7 +78,7 @@ class DFlash2SpecDecoder:
 
     @staticmethod
     def from_dir(engine, drafter_dir, num_drafts: int = 7, ngram_tail: int = 0, ngram_n: int = 0, native: Optional[bool] = None,
-                 fmt: str = "nvfp4"):
+                 fmt: str = "nvfp4", target_model_dir=None):
         """``native`` (default: whenever the engine runs the CUDA op set and the drafter's shape fits the kernels):
         the drafter on the engine's own kernels (native.py) instead of torch tensor ops."""
         if native is None:
@@ -87,9 +87,14 @@ class DFlash2SpecDecoder:
                 c = DFlash2Config.from_dir(drafter_dir)
                 native = c.head_dim == 128 and c.num_attention_heads // c.num_key_value_heads <= 4
         if native:
+            from . import draft_vocab
             from .native import DFlash2NativeDrafter
-            return DFlash2SpecDecoder(engine, DFlash2NativeDrafter.from_dir(drafter_dir, engine, fmt), num_drafts, ngram_tail,
-                                      ngram_n)
+            dr = DFlash2NativeDrafter.from_dir(drafter_dir, engine, fmt)
+            # fixed draft vocabulary: only when the environment asks for it (off by default, like the reference)
+            dv = draft_vocab.resolve(target_model_dir, engine.cfg.vocab_size, engine.cfg.hidden_size, dr.cfg.selector_top_k)
+            if dv is not None:
+                dr.set_draft_vocab(dv.ids.tolist())
+            return DFlash2SpecDecoder(engine, dr, num_drafts, ngram_tail, ngram_n)
         dt = torch.float32 if engine.device.type == "cpu" else torch.bfloat16
         return DFlash2SpecDecoder(engine, DFlash2Drafter.from_dir(drafter_dir, engine.device, dt), num_drafts, ngram_tail,
                                   ngram_n)

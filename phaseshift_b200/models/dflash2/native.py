@@ -100,6 +100,8 @@ class DFlash2NativeDrafter:
         self.h_ctl = torch.zeros(2, dtype=torch.int32, pin_memory=True)
         self.tokens = torch.zeros(MAX_BLOCK_ROWS, dtype=torch.int32, device=dev)
         self.use_graph = True
+        self.sub_head: Optional[LinearW] = None       # draft-vocabulary head (rows of the target's lm_head) + id map
+        self.idmap: Optional[torch.Tensor] = None
         self._graphs: Dict[int, torch.cuda.CUDAGraph] = {}
         self._calibrated = {"ctx": fmt != "nvfp4", "blk": fmt != "nvfp4"}
         self._collect: Optional[Dict[int, float]] = None
@@ -116,6 +118,32 @@ class DFlash2NativeDrafter:
     @staticmethod
     def from_torch(drafter, engine, fmt: str = "nvfp4") -> "DFlash2NativeDrafter":
         return DFlash2NativeDrafter(drafter.cfg, drafter.w, engine, fmt)
+
+    def set_draft_vocab(self, ids) -> None:
+        """Restrict the drafter's head to the given target token ids (ascending; models/dflash2/draft_vocab.py): the
+        head pass streams only those rows of the target's lm_head, top-k runs on local ids and is mapped back to global
+        ids before the selector.  ``None`` restores the full vocabulary.  Captured proposals are dropped."""
+        self._graphs.clear()
+        if ids is None:
+            self.sub_head = self.idmap = None
+            return
+        from ...quant.act_quant import pack_sf_atoms, unpack_sf_atoms
+        from ...quant.formats import QuantizedTensor
+        head = self.eng.runner.w.lm_head
+        idx = torch.as_tensor([int(i) for i in ids], dtype=torch.long, device=self.device)
+        if head.fmt == "bf16":
+            q = QuantizedTensor("bf16", (idx.numel(), head.K), head.K, head.q.codes.index_select(0, idx).contiguous(), None, 1.0)
+            sub = LinearW(q)
+        else:
+            if head.sf_atoms is None:
+                raise ValueError("the draft-vocabulary head needs the target's lm_head in the tensor-core layout")
+            blk = 16 if head.fmt == "nvfp4" else 32
+            scales = unpack_sf_atoms(head.sf_atoms, head.N, head.k_padded // blk).index_select(0, idx).contiguous()
+            q = QuantizedTensor(head.fmt, (idx.numel(), head.K), head.k_padded, head.codes.index_select(0, idx).contiguous(),
+                                scales, head.tensor_scale)
+            sub = LinearW(q).make_umma(keep_canonical=True)
+            sub.act_scale = head.act_scale
+        self.sub_head, self.idmap = sub, idx.to(torch.int32).contiguous()
 
     def weight_bytes(self) -> int:
         n = sum(L[k].nbytes for L in self.layers for k in ("qkv", "o", "gate_up", "down", "attn_kproj", "mlp_kproj"))
@@ -286,9 +314,13 @@ class DFlash2NativeDrafter:
         else:
             h = self._rms(x, self.final_norm, "h")[1:T]
             hproj = self._linear(h, self.hidden_projection, "hproj", out_f32=True)
-        logits = ops.linear(h, eng.runner.w.lm_head, name="dfl_logits", out_f32=True)
+        head = self.sub_head if self.sub_head is not None else eng.runner.w.lm_head
+        logits = ops.linear(h, head, name="dfl_logits", out_f32=True)
         kk = min(c.selector_top_k, logits.shape[1])
         top_ids, top_vals = ops.topk(logits, kk)
+        if self.idmap is not None:
+            _lib.call("ps_dfl_remap_ids", ptr(top_ids), c_int(top_ids.numel()), ptr(self.idmap), c_int(self.idmap.numel()))
+            self.launches += 1
         _lib.call("ps_dfl_select", ptr(top_ids), ptr(top_vals), c_int(kk), ptr(hproj), c_int(c.selector_rank), ptr(self.pred_cb),
                   ptr(self.succ_cb), ptr(self.ids), c_int(0), c_int(k), c_int(c.vocab_size), ptr(self.tokens))
         self.launches += 1

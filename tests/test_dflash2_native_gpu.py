@@ -321,3 +321,30 @@ def test_speculative_round_with_native_drafter_is_exact(preset, fmt):
     out3, stats3 = dec.generate(prompt, 24, prefill_chunk=8)
     assert out3 == plain and stats3["accepted"] == stats3["proposed"], stats3
     assert int(eng.ops.status[0]) == 0
+
+
+@pytest.mark.parametrize("preset", ["nvfp4", "bf16"])
+def test_draft_vocabulary_head(preset):
+    """The drafter's head restricted to a subset of the target vocabulary: with the identity subset the proposals equal
+    the full head's; with a real subset every proposal lies inside it; speculative decoding stays exact either way."""
+    from phaseshift_b200.models.dflash2.decoder import DFlash2SpecDecoder
+    cfg, ew, eng, dcfg, tdr, ndr = _tiny_pair("nvfp4" if preset == "nvfp4" else "bf16", preset)
+    g = _gen(6)
+    taps = [torch.randn(20, cfg.hidden_size, device="cuda", generator=g).to(torch.bfloat16) for _ in dcfg.target_layer_ids]
+    ndr.append_context(taps, 0)
+    full = ndr.propose(9, 5, pos_start=20)
+    ndr.set_draft_vocab(list(range(cfg.vocab_size)))
+    assert ndr.propose(9, 5, pos_start=20) == full
+    subset = list(range(3, cfg.vocab_size, 7))
+    subset = subset[:len(subset) // 16 * 16]
+    ndr.set_draft_vocab(subset)
+    got = ndr.propose(9, 5, pos_start=20)
+    assert len(got) == 5 and all(t in set(subset) for t in got)
+    prompt = torch.randint(0, cfg.vocab_size, (21,), generator=torch.Generator().manual_seed(8)).tolist()
+    from phaseshift_b200.runtime.engine import Engine
+    ref_eng = Engine(ew, "cuda", StateConfig(max_slots=1, max_seq_len=128))
+    ref_eng.set_uniform_arithmetic(True)
+    out, _ = DFlash2SpecDecoder(eng, ndr, num_drafts=5).generate(prompt, 16, prefill_chunk=8)
+    assert out == ref_eng.generate(prompt, 16, prefill_chunk=8)
+    ndr.set_draft_vocab(None)
+    assert ndr.sub_head is None
