@@ -50,7 +50,7 @@ def test_closed_calls_and_cluster_multicast_loads_never_appear():
             if name in txt:
                 bad.append((str(p.relative_to(ROOT)), name))
         for m in re.finditer(r"cp\.async\.bulk[\w\.:]*", txt):
-            if "multicast::cluster" in m.group(0):
+            if ("multi" + "cast::cluster") in m.group(0):      # (spelled in two pieces: this file only tests for the qualifier)
                 bad.append((str(p.relative_to(ROOT)), m.group(0)))
     assert not bad, bad
 
