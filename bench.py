@@ -45,8 +45,9 @@ def _parse():
     ap.add_argument("--layout", default="both", choices=["both", "tc", "stream"],
                     help="kernel-side weight layouts kept resident: tensor-core operands, streaming tiles, or both "
                          "(single-row decode streams, everything else runs on the tensor cores)")
-    ap.add_argument("--config", type=int, default=0, choices=[0, 3, 4, 5],
-                    help="workload preset: 3 = prefill 4096 + 1024 decode steps; 4 = 8k-token prompt, 256 speculative "
+    ap.add_argument("--config", type=int, default=0, choices=[0, 2, 3, 4, 5],
+                    help="workload preset: 2 = the 4B-shaped model in bf16, prefill 2048 + 512 decode steps (pick the KV "
+                         "dtype with --kv-dtype); 3 = prefill 4096 + 1024 decode steps; 4 = 8k-token prompt, 256 speculative "
                          "tokens; 5 = the full serving load (256 requests)")
     ap.add_argument("--serving-requests", type=int, default=24,
                     help="continuous-batching block: concurrent requests with prompts U(512, 8192), outputs U(128, 1024), "
@@ -57,7 +58,9 @@ def _parse():
     ap.add_argument("--watchdog", type=int, default=1500,
                     help="seconds after which a hung run dumps every thread's stack to stderr and exits")
     a = ap.parse_args()
-    if a.config == 3:
+    if a.config == 2:
+        a.model, a.preset, a.context, a.steps, a.dflash2, a.serving_requests = "4b", "bf16", 2048, 512, 0, 0
+    elif a.config == 3:
         a.context, a.steps = 4096, 1024
     elif a.config == 4:
         a.context, a.dflash2_tokens = 8192, 256

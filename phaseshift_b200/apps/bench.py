@@ -12,7 +12,7 @@ from typing import List, Optional
 
 SUBCOMMANDS = ("pp", "tg", "batch", "gemm", "activation-quantize", "rmsnorm", "l2-normalize", "kv-append",
                "paged-attention", "rope", "gdn-recurrence", "gdn-conv1d", "elementwise", "embedding", "sampling", "mtp",
-               "gpu-memory", "tp-reduce", "dflash2")
+               "gpu-memory", "tp-reduce", "dflash2", "kld")
 # Reference sub-commands whose op has no stand-alone launch here: each times the kernel the op is fused into.
 FUSED_INTO = {"l2-normalize": "gdn-recurrence",      # q/k L2 normalisation happens inside the GDN mixer kernel
               "gdn-conv1d": "gdn-recurrence",        # so does the short causal conv
@@ -58,6 +58,9 @@ def build_parser() -> argparse.ArgumentParser:
         p = sub.add_parser(name); p.add_argument("--rows", type=int, default=1); p.add_argument("--context", type=int, default=4096)
         p.add_argument("--samples", type=int, default=20); p.add_argument("--model", default="27b", choices=["tiny", "4b", "27b"])
         p.add_argument("--kv-cache-dtype", default="bf16", choices=["bf16", "fp8_e4m3"]); p.add_argument("--variant", default="optimized", choices=["optimized"])
+    kl = sub.add_parser("kld", help="KL divergence of a quantised preset against the bf16 model of the same random weights"); _model_args(kl)
+    kl.add_argument("--tokens", type=int, default=512); kl.add_argument("--streams", type=int, default=2)
+    kl.add_argument("--layout", default="both", choices=["both", "tc", "stream"])
     tr = sub.add_parser("tp-reduce", help="row-parallel combine latency (run under torchrun for > 1 GPU)")
     tr.add_argument("--rows", default="1,8"); tr.add_argument("--hidden", type=int, default=5120); tr.add_argument("--samples", type=int, default=50)
     return ap
@@ -297,7 +300,7 @@ def cmd_dflash2(a, cfg, dev) -> int:
     wb = dr.weight_bytes() + eng.runner.w.lm_head.nbytes
     print("kernel=dflash2"); print(f"model={a.model}"); print(f"drafts={k}"); print(f"context_rows={n_ctx}")
     print(f"proposal_p50_us={ts[len(ts) // 2]:.1f}"); print(f"append_block_p50_us={ta[len(ta) // 2]:.1f}")
-    print(f"launches_per_proposal={dr.launches}"); print(f"weight_bytes_per_proposal={wb}")
+    print(f"launches_per_proposal={dr.graph_launches.get(k, 0)}"); print(f"weight_bytes_per_proposal={wb}")
     print(f"hbm_GBps={wb / ts[len(ts) // 2] / 1e3:.0f}")
     return 0
 
@@ -481,8 +484,57 @@ def cmd_tp_reduce(a) -> int:
     return 0
 
 
+def cmd_kld(a) -> int:
+    """Random-init model, random token streams: logits of every position from the bf16 engine and from the quantised
+    preset (same underlying weights, the engine's own kernels on both sides); KL(bf16 || preset), top-1 agreement."""
+    import torch
+    from ..models.qwen35.config import PRESETS
+    from ..models.qwen35.weights import build_engine_weights, random_getter
+    from ..runtime.batch import SeqRows
+    from ..runtime.engine import Engine
+    from ..runtime.state import StateConfig
+    dev = torch.device(a.device or "cuda:0")
+    cfg = PRESETS[a.random_model or "tiny"]()
+    preset = a.preset or "nvfp4"
+    n = a.tokens
+    g = torch.Generator().manual_seed(0)
+    streams = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for _ in range(a.streams)]
+
+    def logits_of(p, layout):
+        ew = build_engine_weights(cfg, random_getter(cfg, 0, dev), p, dev, keep_canonical=False, **({"layout": layout} if p != "bf16" else {}))
+        eng = Engine(ew, dev, StateConfig(max_slots=1, max_seq_len=n + 8, kv_dtype=a.kv_cache_dtype), use_graphs=False)
+        out = []
+        for ids in streams:
+            s = eng.open_sequence()
+            _, o = eng.step([SeqRows(s.slot, 0, ids, tuple(range(n)))], [s], want_logits=True)
+            out.append(torch.log_softmax(o.logits[:n].float(), -1).to(torch.bfloat16 if cfg.vocab_size > 65536 else torch.float32).cpu())
+            eng.close_sequence(s)
+        del eng, ew
+        torch.cuda.empty_cache()
+        return out
+    ref = logits_of("bf16", None)
+    got = logits_of(preset, a.layout)
+    kls, agree = [], 0
+    for r, q in zip(ref, got):
+        r, q = r.float(), q.float()
+        kls.append((r.exp() * (r - q)).sum(-1))
+        agree += int((r.argmax(-1) == q.argmax(-1)).sum())
+    kl = torch.cat(kls)
+    # two models whose logits are independent Gaussians of standard deviation s are about s^2 nats apart: the ceiling that
+    # a random-init model, which amplifies any perturbation layer after layer, approaches as it gets deeper
+    sd = float(torch.cat([r.float().std(-1) for r in ref]).mean())
+    qs = torch.quantile(kl, torch.tensor([0.5, 0.9, 0.99]))
+    print(f"model={a.random_model or 'tiny'}"); print(f"preset={preset}"); print(f"layout={a.layout}"); print(f"positions={kl.numel()}")
+    print(f"kld_mean={float(kl.mean()):.6f}"); print(f"kld_p50={float(qs[0]):.6f}"); print(f"kld_p90={float(qs[1]):.6f}")
+    print(f"kld_p99={float(qs[2]):.6f}"); print(f"kld_max={float(kl.max()):.6f}"); print(f"top1_agreement={agree / kl.numel():.4f}")
+    print(f"logit_std={sd:.4f}"); print(f"kld_over_decorrelated={float(kl.mean()) / max(sd * sd, 1e-12):.3f}")
+    return 0
+
+
 def main(argv: Optional[List[str]] = None) -> int:
     a = build_parser().parse_args(argv)
+    if a.cmd == "kld":
+        return cmd_kld(a)
     return {"pp": cmd_pp, "tg": cmd_tg, "batch": cmd_batch, "gemm": cmd_gemm, "tp-reduce": cmd_tp_reduce,
             "mtp": cmd_mtp}.get(a.cmd, cmd_kernel)(a)
 

@@ -106,6 +106,7 @@ class DFlash2NativeDrafter:
         self._calibrated = {"ctx": fmt != "nvfp4", "blk": fmt != "nvfp4"}
         self._collect: Optional[Dict[int, float]] = None
         self.launches = 0
+        self.graph_launches: Dict[int, int] = {}
 
     # ------------------------------------------------------------------ construction helpers
     @staticmethod
@@ -343,8 +344,10 @@ class DFlash2NativeDrafter:
         if g is None:
             self._block(k)                                # warm-up: workspaces, kernel attributes
             torch.cuda.current_stream().synchronize()
+            n0 = self.launches
             g, _ = capture_graph(self.device, lambda: self._block(k))
             self._graphs[k] = g
+            self.graph_launches[k] = self.launches - n0   # kernels in one proposal graph
         g.replay()
         return self.tokens[:k]
 

@@ -215,3 +215,11 @@ def test_bench_subcommands_help_and_cpu_runs(capsys):
                        "--runs", "1", "--warmup", "0", "--replay-check"]) == 0
     out = dict(l.split("=", 1) for l in capsys.readouterr().out.strip().splitlines())
     assert out["replay_match"] == "1" and int(out["proposed"]) >= int(out["accepted"]) and out["mtp_head"] == "random-init"
+    # quantised preset against the bf16 model of the same random weights: small divergence on a 4-layer model, and the
+    # 8-bit preset closer than the 4-bit one
+    kld = {}
+    for preset in ("nvfp4", "mxfp8"):
+        assert bench.main(["kld", "--random-model", "tiny", "--device", "cpu", "--tokens", "16", "--streams", "1", "--preset", preset]) == 0
+        kld[preset] = dict(l.split("=", 1) for l in capsys.readouterr().out.strip().splitlines())
+    assert 0 <= float(kld["mxfp8"]["kld_mean"]) < float(kld["nvfp4"]["kld_mean"]) < 0.05
+    assert float(kld["nvfp4"]["kld_over_decorrelated"]) < 0.3
