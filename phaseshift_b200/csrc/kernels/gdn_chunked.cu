@@ -80,20 +80,24 @@ __device__ __forceinline__ void mma_tf32(float (&c)[4], const float (&a)[4], flo
                    "r"(__float_as_uint(b0)), "r"(__float_as_uint(b1)));
 }
 
-// grid = (max chunks, Hv), block = 256 threads
+// grid = (max chunks, Hv), block = 256 threads, two CTAs per SM (shared memory: Q and K tiles, the raw q|k input tile
+// that A, T and the block-row temporaries later overwrite; V is convolved straight from global memory into Q's tile
+// once Q is dead).
 template <int DK, int DV>
-__global__ void __launch_bounds__(256) gdn_chunk_prep_kernel(const GdnPrepArgs a) {
-    constexpr int CH = 2 * DK + DV, PK = DK + 4, PV = DV + 4, RAWR = kChunk + 3;
+__global__ void __launch_bounds__(256, 2) gdn_chunk_prep_kernel(const GdnPrepArgs a) {
+    static_assert(DV <= DK && 256 % DK == 0 && 512 % DV == 0, "tile aliasing and the conv partition assume these");
+    constexpr int CH = 2 * DK + DV, CQK = 2 * DK, PK = DK + 4, PV = DV + 4, RAWR = kChunk + 3;
     extern __shared__ __align__(16) float sm[];
-    float* sQ = sm;                        // [64][DK+4]
+    float* sQ = sm;                        // [64][DK+4]; after the decayed operands are written: V [64][DV+4]
     float* sK = sQ + kChunk * PK;          // [64][DK+4]
-    float* sV = sK + kChunk * PK;          // [64][DV+4]
-    float* sG = sV + kChunk * PV;          // [64]
+    float* sV = sQ;
+    float* sG = sK + kChunk * PK;          // [64]
     float* sBeta = sG + kChunk;            // [64]
-    float* sU = sBeta + kChunk;            // union: raw bf16 input tile [67][CH], later A [64][65] and T [64][68]
+    float* sU = sBeta + kChunk;            // union: raw bf16 q|k tile [67][2 DK], later A [64][65], T [64][68], M [3][16][17]
     __nv_bfloat16* sRaw = reinterpret_cast<__nv_bfloat16*>(sU);
     float* sA = sU;
     float* sT = sA + kChunk * 65;          // 64 * 65 floats keep the T rows 16-byte aligned
+    float* sM = sT + kChunk * kTP;
 
     GdnSeqDesc2 sd; int chunk;
     if (!find_chunk(a.seqs, a.n_seqs, a.min_rows, blockIdx.x, sd, chunk)) return;
@@ -109,13 +113,13 @@ __global__ void __launch_bounds__(256) gdn_chunk_prep_kernel(const GdnPrepArgs a
     float* gW = scr; float* gQd = gW + kChunk * DK; float* gKd = gQd + kChunk * DK;
     float* gU = gKd + kChunk * DK; float* gQK = gU + kChunk * DV;
 
-    // ---- stage the raw inputs of rows -3 .. 63 (this head's q | k | v channels) with wide loads
+    // ---- stage the raw inputs of rows -3 .. 63 (this head's q | k channels) with wide loads
     {
         const bool vec = (a.ld_proj % 8) == 0;
-        constexpr int PPR = CH / 8;
+        constexpr int PPR = CQK / 8;
         for (int p = t; p < RAWR * PPR; p += 256) {
             const int rr = p / PPR - 3, c = (p % PPR) * 8;
-            const int gc = c < DK ? q_off + c : (c < 2 * DK ? k_off + (c - DK) : v_off + (c - 2 * DK));
+            const int gc = c < DK ? q_off + c : k_off + (c - DK);
             uint4 v = make_uint4(0, 0, 0, 0);
             if (rr < C && pos0 + rr >= 0) {
                 if (r0 + rr >= 0) {
@@ -131,7 +135,7 @@ __global__ void __launch_bounds__(256) gdn_chunk_prep_kernel(const GdnPrepArgs a
                     v = *reinterpret_cast<const uint4*>(hist + (size_t)((pos0 + rr) % a.ring) * CH + c);
                 }
             }
-            *reinterpret_cast<uint4*>(sRaw + (rr + 3) * CH + c) = v;
+            *reinterpret_cast<uint4*>(sRaw + (rr + 3) * CQK + c) = v;
         }
     }
     // ---- beta and the running log decay (last warp, two 32-wide halves)
@@ -156,25 +160,25 @@ __global__ void __launch_bounds__(256) gdn_chunk_prep_kernel(const GdnPrepArgs a
         sBeta[lane] = b0; sBeta[lane + 32] = b1;
     }
     __syncthreads();
-    // ---- conv + SiLU: a thread owns a channel pair and slides its taps through registers
-    for (int cp = t; cp < CH / 2; cp += 256) {
-        const int c = 2 * cp;
-        const int gc = c < DK ? q_off + c : (c < 2 * DK ? k_off + (c - DK) : v_off + (c - 2 * DK));
+    // ---- conv + SiLU of q and k: a thread owns a channel pair over a run of rows and slides its taps through registers
+    {
+        constexpr int PARTS = 256 / DK, RUN = kChunk / PARTS;           // DK channel pairs x PARTS row runs = 256 threads
+        const int c = 2 * (t % DK), rb = (t / DK) * RUN;
+        const int gc = c < DK ? q_off + c : k_off + (c - DK);
         const uint4 wraw = *reinterpret_cast<const uint4*>(a.conv_w + (size_t)gc * 4);     // two channels x four taps
         const float2 wa01 = bf16x2_bits_to_f32x2(wraw.x), wa23 = bf16x2_bits_to_f32x2(wraw.y);
         const float2 wb01 = bf16x2_bits_to_f32x2(wraw.z), wb23 = bf16x2_bits_to_f32x2(wraw.w);
-        const uint32_t* col = reinterpret_cast<const uint32_t*>(sRaw + c);
-        float2 x3 = bf16x2_bits_to_f32x2(col[0 * (CH / 2)]), x2 = bf16x2_bits_to_f32x2(col[1 * (CH / 2)]);
-        float2 x1 = bf16x2_bits_to_f32x2(col[2 * (CH / 2)]);
-        float* dst = c < DK ? sQ + c : (c < 2 * DK ? sK + (c - DK) : sV + (c - 2 * DK));
-        const int pitch = c < 2 * DK ? PK : PV;
+        const uint32_t* col = reinterpret_cast<const uint32_t*>(sRaw + c) + rb * (CQK / 2);
+        float2 x3 = bf16x2_bits_to_f32x2(col[0 * (CQK / 2)]), x2 = bf16x2_bits_to_f32x2(col[1 * (CQK / 2)]);
+        float2 x1 = bf16x2_bits_to_f32x2(col[2 * (CQK / 2)]);
+        float* dst = (c < DK ? sQ + c : sK + (c - DK)) + rb * PK;
 #pragma unroll 8
-        for (int r = 0; r < kChunk; ++r) {
-            const float2 x0 = bf16x2_bits_to_f32x2(col[(r + 3) * (CH / 2)]);
+        for (int r = 0; r < RUN; ++r) {
+            const float2 x0 = bf16x2_bits_to_f32x2(col[(r + 3) * (CQK / 2)]);
             float ya = wa01.x * x3.x; ya = fmaf(wa01.y, x2.x, ya); ya = fmaf(wa23.x, x1.x, ya); ya = fmaf(wa23.y, x0.x, ya);
             float yb = wb01.x * x3.y; yb = fmaf(wb01.y, x2.y, yb); yb = fmaf(wb23.x, x1.y, yb); yb = fmaf(wb23.y, x0.y, yb);
             x3 = x2; x2 = x1; x1 = x0;
-            *reinterpret_cast<float2*>(dst + r * pitch) = make_float2(silu_f(ya), silu_f(yb));
+            *reinterpret_cast<float2*>(dst + r * PK) = make_float2(silu_f(ya), silu_f(yb));
         }
     }
     __syncthreads();
@@ -221,20 +225,44 @@ __global__ void __launch_bounds__(256) gdn_chunk_prep_kernel(const GdnPrepArgs a
             }
     }
     __syncthreads();
-    // ---- T = (I + A)^-1: thread j < 64 solves column j by forward substitution out of registers
+    // ---- raw v inputs of this thread's conv run, requested now and used once Q's tile is free
+    constexpr int VPARTS = 512 / DV, VRUN = kChunk / VPARTS;             // DV / 2 channel pairs x VPARTS row runs = 256 threads
+    const int vc = 2 * (t % (DV / 2)), vrb = (t / (DV / 2)) * VRUN;
+    uint32_t vraw[VRUN + 3];
+    {
+        const bool even = (a.ld_proj & 1) == 0;
+#pragma unroll
+        for (int i = 0; i < VRUN + 3; ++i) {
+            const int rr = vrb + i - 3;
+            uint32_t v = 0;
+            if (rr < C && pos0 + rr >= 0) {
+                if (r0 + rr >= 0) {
+                    const __nv_bfloat16* src = a.proj + (size_t)((long long)row0 + rr) * a.ld_proj + v_off + vc;
+                    v = even ? __ldg(reinterpret_cast<const uint32_t*>(src))
+                             : ((uint32_t)__bfloat16_as_ushort(src[0]) | ((uint32_t)__bfloat16_as_ushort(src[1]) << 16));
+                } else {
+                    v = *reinterpret_cast<const uint32_t*>(hist + (size_t)((pos0 + rr) % a.ring) * CH + CQK + vc);
+                }
+            }
+            vraw[i] = v;
+        }
+    }
+    // ---- T = (I + A)^-1, diagonal 16x16 blocks: thread (block b, column j) solves by forward substitution out of
+    //      registers; meanwhile the other warps write the decayed operands
     if (t < kChunk) {
-        float x[kChunk];
+        const int b = t >> 4, j = t & 15;
+        const float* Ab = sA + (16 * b) * 65 + 16 * b;
+        float x[16];
 #pragma unroll
-        for (int i = 0; i < kChunk; ++i) {
-            float s4[4] = {i == t ? 1.f : 0.f, 0.f, 0.f, 0.f};
+        for (int i = 0; i < 16; ++i) {
+            float acc0 = i == j ? 1.f : 0.f, acc1 = 0.f;
 #pragma unroll
-            for (int j = 0; j < i; ++j) s4[j & 3] = fmaf(-sA[i * 65 + j], x[j], s4[j & 3]);
-            x[i] = (s4[0] + s4[1]) + (s4[2] + s4[3]);
+            for (int k = 0; k < i; ++k) { if (k & 1) acc1 = fmaf(-Ab[i * 65 + k], x[k], acc1); else acc0 = fmaf(-Ab[i * 65 + k], x[k], acc0); }
+            x[i] = acc0 + acc1;
         }
 #pragma unroll
-        for (int i = 0; i < kChunk; ++i) sT[i * kTP + t] = x[i];
+        for (int i = 0; i < 16; ++i) sT[(16 * b + i) * kTP + 16 * b + j] = x[i];
     } else {
-        // meanwhile the other warps write the decayed operands
         const float GC = sG[kChunk - 1];
         for (int i = t - kChunk; i < kChunk * DK / 4; i += 256 - kChunk) {
             const int r = (i * 4) / DK, d = (i * 4) % DK;
@@ -251,6 +279,46 @@ __global__ void __launch_bounds__(256) gdn_chunk_prep_kernel(const GdnPrepArgs a
         if (t == kChunk) a.dc[(size_t)blockIdx.x * a.Hv + h] = __expf(GC);
     }
     __syncthreads();
+    // ---- conv + SiLU of v into Q's tile (Q is dead: A, QKd and Qd are done)
+    {
+        const int gc = v_off + vc;
+        const uint4 wraw = *reinterpret_cast<const uint4*>(a.conv_w + (size_t)gc * 4);
+        const float2 wa01 = bf16x2_bits_to_f32x2(wraw.x), wa23 = bf16x2_bits_to_f32x2(wraw.y);
+        const float2 wb01 = bf16x2_bits_to_f32x2(wraw.z), wb23 = bf16x2_bits_to_f32x2(wraw.w);
+        float2 x3 = bf16x2_bits_to_f32x2(vraw[0]), x2 = bf16x2_bits_to_f32x2(vraw[1]), x1 = bf16x2_bits_to_f32x2(vraw[2]);
+        float* dst = sV + vrb * PV + vc;
+#pragma unroll
+        for (int r = 0; r < VRUN; ++r) {
+            const float2 x0 = bf16x2_bits_to_f32x2(vraw[r + 3]);
+            float ya = wa01.x * x3.x; ya = fmaf(wa01.y, x2.x, ya); ya = fmaf(wa23.x, x1.x, ya); ya = fmaf(wa23.y, x0.x, ya);
+            float yb = wb01.x * x3.y; yb = fmaf(wb01.y, x2.y, yb); yb = fmaf(wb23.x, x1.y, yb); yb = fmaf(wb23.y, x0.y, yb);
+            x3 = x2; x2 = x1; x1 = x0;
+            *reinterpret_cast<float2*>(dst + r * PV) = make_float2(silu_f(ya), silu_f(yb));
+        }
+    }
+    // ---- T, block rows 1 .. 3: T_ij = -T_ii (sum_{k = j .. i-1} A_ik T_kj) for all j < i at once
+    for (int bi = 1; bi < 4; ++bi) {
+        for (int e = t; e < bi * 256; e += 256) {
+            const int bj = e >> 8, r = (e >> 4) & 15, c = e & 15;
+            const float* Ar = sA + (16 * bi + r) * 65;
+            float acc0 = 0.f, acc1 = 0.f;
+            for (int k = 16 * bj; k < 16 * bi; k += 2) {
+                acc0 = fmaf(Ar[k], sT[k * kTP + 16 * bj + c], acc0);
+                acc1 = fmaf(Ar[k + 1], sT[(k + 1) * kTP + 16 * bj + c], acc1);
+            }
+            sM[(bj * 16 + r) * 17 + c] = acc0 + acc1;
+        }
+        __syncthreads();
+        for (int e = t; e < bi * 256; e += 256) {
+            const int bj = e >> 8, r = (e >> 4) & 15, c = e & 15;
+            const float* Tr = sT + (16 * bi + r) * kTP + 16 * bi;
+            float acc = 0.f;
+#pragma unroll
+            for (int k = 0; k < 16; ++k) acc = fmaf(Tr[k], sM[(bj * 16 + k) * 17 + c], acc);     // T_ii is zero above its diagonal
+            sT[(16 * bi + r) * kTP + 16 * bj + c] = -acc;
+        }
+        __syncthreads();
+    }
     // ---- W = T diag(beta D) K (warps 0-3) and U = T diag(beta) V (warps 4-7) on the tensor cores: warp -> rows
     //      16 mt .., all columns of its matrix; T is lower triangular, so k-steps beyond the row tile are skipped
     {
@@ -301,20 +369,17 @@ __device__ __forceinline__ bool row_is_chunked(const GdnSeqDesc2* seqs, int n_se
 
 // History for later steps: the raw inputs of each sequence's last `ring` rows.  Separate launch so the
 // prepare CTAs of a step never race with history reads of earlier rows of the same step.
-__global__ void gdn_history_kernel(const GdnPrepArgs a, int rows) {
-    const int h = blockIdx.x, row = blockIdx.y, t = threadIdx.x;
-    const int slot = a.row_slot[row];
-    if (slot < 0 || !row_is_chunked(a.seqs, a.n_seqs, a.min_rows, row)) return;
-    // only the last `ring` rows of a sequence in this step matter (later rows overwrite earlier slots)
-    const int pos = a.row_pos[row];
-    bool last = true;
-    if (row + a.ring < rows && a.row_slot[row + a.ring] == slot && a.row_pos[row + a.ring] == pos + a.ring) last = false;
-    if (!last) return;
+// grid = (Hv, ring, n_seqs): block (h, j, s) copies the j-th row from the end of sequence s.
+__global__ void gdn_history_kernel(const GdnPrepArgs a) {
+    const int h = blockIdx.x, j = blockIdx.y, t = threadIdx.x;
+    const GdnSeqDesc2 sd = a.seqs[blockIdx.z];
+    if (sd.slot < 0 || sd.n_rows <= a.min_rows || j >= sd.n_rows) return;
+    const int r = sd.n_rows - 1 - j, pos = sd.pos_start + r;
     const int Dk = a.Dk, Dv = a.Dv, CH = 2 * Dk + Dv;
     const int hk = h / (a.Hv / a.Hk);
     const int q_off = hk * Dk, k_off = a.Hk * Dk + hk * Dk, v_off = 2 * a.Hk * Dk + h * Dv;
-    const __nv_bfloat16* pr = a.proj + (size_t)row * a.ld_proj;
-    __nv_bfloat16* hist = a.conv_state + ((size_t)slot * a.Hv + h) * a.ring * CH;
+    const __nv_bfloat16* pr = a.proj + (size_t)(sd.row_start + r) * a.ld_proj;
+    __nv_bfloat16* hist = a.conv_state + ((size_t)sd.slot * a.Hv + h) * a.ring * CH;
     for (int c = t; c < CH; c += blockDim.x) {
         const int gc = c < Dk ? q_off + c : (c < 2 * Dk ? k_off + (c - Dk) : v_off + (c - 2 * Dk));
         hist[(size_t)(pos % a.ring) * CH + c] = pr[gc];
@@ -636,18 +701,38 @@ __global__ void __launch_bounds__(256) gdn_chunk_scan_tc_kernel(const GdnScanArg
     }
 }
 
-// grid = (Hv, rows), block = Dv threads
-__global__ void gdn_post_kernel(const float* o, const __nv_bfloat16* proj, int ld_proj, int z_off, const __nv_bfloat16* norm_w,
-                                float eps, int Hv, int Dv, const int* row_slot, __nv_bfloat16* out, const GdnSeqDesc2* seqs,
-                                int n_seqs, int min_rows) {
-    __shared__ float red[32];
-    const int h = blockIdx.x, row = blockIdx.y, t = threadIdx.x;
+// One warp per (row, head): RMSNorm over the head's Dv outputs * SiLU(z).  E = Dv / 32 contiguous values per lane.
+// grid = ceil(rows * Hv / 8), block = 256 threads
+template <int E>
+__global__ void __launch_bounds__(256) gdn_post_kernel(const float* o, const __nv_bfloat16* proj, int ld_proj, int z_off,
+                                                       const __nv_bfloat16* norm_w, float eps, int Hv, int rows, const int* row_slot,
+                                                       __nv_bfloat16* out, const GdnSeqDesc2* seqs, int n_seqs, int min_rows) {
+    constexpr int Dv = 32 * E;
+    const int item = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (item >= rows * Hv) return;
+    const int row = item / Hv, h = item % Hv;
     if (row_slot[row] < 0 || !row_is_chunked(seqs, n_seqs, min_rows, row)) return;
-    const float v = o[((size_t)row * Hv + h) * Dv + t];
-    const float ss = block_sum(v * v, red);
-    const float y = v * rsqrtf(ss / (float)Dv + eps) * bf16_to_f32(norm_w[t]);
-    const float z = bf16_to_f32(proj[(size_t)row * ld_proj + z_off + h * Dv + t]);
-    out[(size_t)row * (Hv * Dv) + h * Dv + t] = f32_to_bf16(y * silu_f(z));
+    float v[E], z[E], w[E];
+    const float* op = o + ((size_t)row * Hv + h) * Dv + lane * E;
+    const __nv_bfloat16* zp = proj + (size_t)row * ld_proj + z_off + h * Dv + lane * E;
+    if constexpr (E == 4) {
+        const float4 f = *reinterpret_cast<const float4*>(op);
+        v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+    } else {
+#pragma unroll
+        for (int e = 0; e < E; ++e) v[e] = op[e];
+    }
+#pragma unroll
+    for (int e = 0; e < E; ++e) { z[e] = bf16_to_f32(zp[e]); w[e] = bf16_to_f32(norm_w[lane * E + e]); }
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < E; ++e) ss = fmaf(v[e], v[e], ss);
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)Dv + eps);
+    __nv_bfloat16* dst = out + (size_t)row * (Hv * Dv) + h * Dv + lane * E;
+#pragma unroll
+    for (int e = 0; e < E; e += 2)
+        *reinterpret_cast<__nv_bfloat162*>(dst + e) = __floats2bfloat162_rn(v[e] * inv * w[e] * silu_f(z[e]), v[e + 1] * inv * w[e + 1] * silu_f(z[e + 1]));
 }
 
 }  // namespace ps
@@ -663,8 +748,8 @@ PS_API long long ps_gdn_chunked_scratch_floats(int rows, int n_seqs, int Hv, int
 namespace ps {
 template <int DK, int DV>
 static int launch_chunked(const GdnPrepArgs& p, const GdnScanArgs& s, int max_chunks, cudaStream_t stream) {
-    const size_t raw_b = (size_t)(kChunk + 3) * (2 * DK + DV) * 2, at_b = sizeof(float) * (kChunk * 65 + kChunk * kTP);
-    const size_t smem_a = sizeof(float) * (2 * kChunk * (DK + 4) + kChunk * (DV + 4) + 2 * kChunk) + (raw_b > at_b ? raw_b : at_b);
+    const size_t raw_b = (size_t)(kChunk + 3) * (2 * DK) * 2, at_b = sizeof(float) * (kChunk * 65 + kChunk * kTP + 3 * 16 * 17);
+    const size_t smem_a = sizeof(float) * (2 * kChunk * (DK + 4) + 2 * kChunk) + (raw_b > at_b ? raw_b : at_b);
     const size_t smem_b = sizeof(float) * (3 * kChunk * (DK + 4) + DK * (kSlice + 4) + kChunk * (kSlice + 4) + kChunk * 65);
     const size_t smem_t = sizeof(float) * (2 * kChunk * (DK + 4) + kChunk * (DK + 8) + DK * (kSlice + 8) + kChunk * (kSlice + 8) +
                                            kChunk * (kChunk + 4));
@@ -711,10 +796,14 @@ PS_API int ps_gdn_chunked(const void* proj, int ld_proj, int rows, int Hk, int H
     else if (Dk == 64 && Dv == 64) err = launch_chunked<64, 64>(p, s, max_chunks, stream);
     else return (int)cudaErrorInvalidValue;
     if (err) return err;
-    gdn_history_kernel<<<dim3(Hv, rows), 128, 0, stream>>>(p, rows);
+    gdn_history_kernel<<<dim3(Hv, ring, n_seqs), 128, 0, stream>>>(p);
     if ((err = PS_LAUNCH_CHECK())) return err;
-    gdn_post_kernel<<<dim3(Hv, rows), Dv, 0, stream>>>((const float*)o, (const __nv_bfloat16*)proj, ld_proj,
-                                                       2 * Hk * Dk + Hv * Dv, (const __nv_bfloat16*)norm_w, eps, Hv, Dv,
-                                                       (const int*)row_slot, (__nv_bfloat16*)out, p.seqs, n_seqs, min_rows);
+    const int post_grid = (rows * Hv + 7) / 8, z_off = 2 * Hk * Dk + Hv * Dv;
+    if (Dv == 128)
+        gdn_post_kernel<4><<<post_grid, 256, 0, stream>>>((const float*)o, (const __nv_bfloat16*)proj, ld_proj, z_off, (const __nv_bfloat16*)norm_w,
+                                                         eps, Hv, rows, (const int*)row_slot, (__nv_bfloat16*)out, p.seqs, n_seqs, min_rows);
+    else
+        gdn_post_kernel<2><<<post_grid, 256, 0, stream>>>((const float*)o, (const __nv_bfloat16*)proj, ld_proj, z_off, (const __nv_bfloat16*)norm_w,
+                                                         eps, Hv, rows, (const int*)row_slot, (__nv_bfloat16*)out, p.seqs, n_seqs, min_rows);
     return PS_LAUNCH_CHECK();
 }
