@@ -427,16 +427,27 @@ static int launch_prefill(const AttnPrefillArgs& a, int max_q_tiles, int n_seqs,
     return PS_LAUNCH_CHECK();
 }
 
+// attn_prefill_tc.cu: the tcgen05 kernel for head dim 256, bf16 pools and 16-token pages
+bool attn_prefill_tc_supported(int D, int page_tokens, int kv_fp8, const void* q, const void* k_pool, const void* v_pool,
+                               const void* gate, int ld_gate, int gate_head_stride, int gate_offset);
+int launch_attn_prefill_tc(const void* q, int q_rows, const void* k_pool, const void* v_pool, const void* block_table,
+                           int max_blocks, int num_pages, const void* seqs, int n_seqs, int max_seq_rows, int Hq, int Hkv,
+                           float sm_scale, const void* gate, int ld_gate, int gate_head_stride, int gate_offset, void* out,
+                           void* status, cudaStream_t stream);
+
 }  // namespace ps
 
-// `max_seq_rows`: upper bound of n_rows over the step's sequences (sizes the grid).
+// `max_seq_rows`: upper bound of n_rows over the step's sequences (sizes the grid); `q_rows`: rows of the q tensor.
 PS_API int ps_attn_prefill(const void* q, const void* k_pool, const void* v_pool, const void* k_scale, const void* v_scale,
                            const void* block_table, int max_blocks, int page_tokens, int num_pages, const void* seqs,
-                           int n_seqs, int max_seq_rows, int Hq, int Hkv, int D, float sm_scale, int kv_fp8,
+                           int n_seqs, int max_seq_rows, int q_rows, int Hq, int Hkv, int D, float sm_scale, int kv_fp8,
                            const void* gate, int ld_gate, int gate_head_stride, int gate_offset, void* out, void* status,
                            cudaStream_t stream) {
     using namespace ps;
-    if (n_seqs <= 0 || max_seq_rows <= 0 || Hkv <= 0 || (Hq % Hkv)) return (int)cudaErrorInvalidValue;
+    if (n_seqs <= 0 || max_seq_rows <= 0 || Hkv <= 0 || (Hq % Hkv) || q_rows < max_seq_rows) return (int)cudaErrorInvalidValue;
+    if (attn_prefill_tc_supported(D, page_tokens, kv_fp8, q, k_pool, v_pool, gate, ld_gate, gate_head_stride, gate_offset))
+        return launch_attn_prefill_tc(q, q_rows, k_pool, v_pool, block_table, max_blocks, num_pages, seqs, n_seqs, max_seq_rows, Hq, Hkv,
+                                      sm_scale, gate, ld_gate, gate_head_stride, gate_offset, out, status, stream);
     AttnPrefillArgs a;
     a.q = (const __nv_bfloat16*)q; a.k_pool = k_pool; a.v_pool = v_pool; a.k_scale = (const float*)k_scale;
     a.v_scale = (const float*)v_scale; a.block_table = (const int*)block_table; a.max_blocks = max_blocks;

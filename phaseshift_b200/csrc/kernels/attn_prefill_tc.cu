@@ -1,0 +1,424 @@
+// Causal paged attention for prefill-sized steps on the fifth-generation tensor cores (head dim 256, bf16 pools,
+// 16-token pages): one CTA = 128 consecutive query rows of one sequence and one query head.
+//
+//   warp 4   TMA producer for Q (once) and the K tiles: a 64-token tile is four pages, each fetched as four
+//            64-column boxes (128-byte swizzle) straight from the paged pool through a tensor map over
+//            [pages * kv heads * 16, D]; two stages.
+//   warp 5   TMA producer for the V tiles (same boxes, two stages).
+//   warp 6   one thread issues tcgen05.mma: S(t) = Q K(t)^T into one of two 64-column accumulators, and
+//            O += P(t) V(t) into a 256-column accumulator; S(t+1) is issued before P(t) is waited for, so the
+//            tensor core computes the next scores while the softmax warps work on the current ones.
+//            V is consumed as it lies in the pool (token rows, dims contiguous): an MN-major B operand.
+//   warps 0-3  softmax: thread i owns query row i = TMEM lane i.  Scores come back with tcgen05.ld, the running
+//            maximum needs no shuffles, probabilities go to shared memory as a bf16 K-major A operand (swizzled by
+//            hand), and the output accumulator is rescaled in tensor memory only when a row's maximum has grown
+//            by more than 2^8 since the reference used for its exponents (the sum absorbs the difference, so the
+//            result is the exact softmax).  The epilogue normalises, applies the sigmoid output gate and writes
+//            bf16 through shared memory with coalesced 16-byte stores.
+//
+// Every wait is bounded; a timeout raises the CTA's abort flag, every role unwinds, outstanding copies get a
+// bounded chance to land, tensor memory is freed and PS_DEV_WAIT_TIMEOUT is recorded.  Token rows of the last
+// tile that lie beyond the sequence's end are zeroed in shared memory before the P V product (their
+// probabilities are zero, but stale pool contents must not be able to inject NaNs).
+//
+// The reference's prefill attention (src/phaseshift/models/qwen35/kernels/optimized/attention/
+// paged_prefill.hip:408-874) tiles 16 query rows per wave on WMMA; FP8 pools, other head sizes and other page
+// sizes stay on the mma.sync kernel (attn_prefill.cu).
+#include <cuda.h>
+
+#include "ps_common.cuh"
+#include "ps_tcgen05.cuh"
+
+namespace ps {
+
+constexpr int kTcRows = 128, kTcTok = 64, kTcD = 256, kTcPage = 16;
+constexpr int kTcThreads = 224;
+constexpr int kTcQBytes = kTcRows * kTcD * 2;         // 64 KB: four 64-column boxes of 128 rows
+constexpr int kTcKvStage = kTcTok * kTcD * 2;         // 32 KB: four 64-column boxes of 64 tokens
+constexpr int kTcPBuf = kTcRows * kTcTok * 2;         // 16 KB: 128 rows x 64 tokens
+constexpr int kTcSmem = kTcQBytes + 4 * kTcKvStage + 2 * kTcPBuf;
+constexpr int kTcOutPitch = kTcD + 8;                 // staging pitch of the epilogue (elements)
+constexpr uint32_t kTcTmemCols = 512;                 // S0 | S1 (64 each) | O (256)
+
+struct AttnTcArgs {
+    const int* block_table; int max_blocks; int num_pages;
+    const int* seqs;             // [n_seqs][4] = row_start, n_rows, slot, pos_start
+    int Hq, Hkv; float scale_log2;
+    const __nv_bfloat16* gate; int ld_gate; int gate_head_stride; int gate_offset;
+    __nv_bfloat16* out;          // [rows, Hq * D]
+    uint32_t* status;
+    long long budget;
+};
+
+namespace tc {
+// Shared-memory descriptor of an MN-major operand (rows = K index, 128 bytes = 64 MN elements per row, 128-byte
+// swizzle): `lbo` bytes between 64-element groups along MN, `sbo` bytes between 8-row groups along K.
+__device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// kind::f16, A = bf16 K-major, B = bf16 MN-major, D = fp32.
+__host__ __device__ constexpr uint32_t idesc_bf16_f32_bmn(int M, int N) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+}  // namespace tc
+
+// grid = (q tiles of 128 rows, Hq, n_seqs); the heaviest (latest) query tiles are scheduled first.
+__global__ void __launch_bounds__(kTcThreads, 1)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, const AttnTcArgs a) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char* sQ = smem;
+    unsigned char* sK = sQ + kTcQBytes;
+    unsigned char* sV = sK + 2 * kTcKvStage;
+    unsigned char* sP = sV + 2 * kTcKvStage;
+    __shared__ __align__(8) uint64_t q_full, k_full[2], v_full[2], s_full[2], p_full[2], pv_done[2];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int s_abort, s_bad, k_issued, k_consumed, v_issued, v_consumed, q_issued, q_consumed;
+
+    const int* sd = a.seqs + 4 * blockIdx.z;
+    const int row_start = sd[0], n_rows = sd[1], slot = sd[2], pos_start = sd[3];
+    const int tile = (int)gridDim.x - 1 - (int)blockIdx.x;
+    const int r_begin = tile * kTcRows;
+    if (r_begin >= n_rows || slot < 0) return;
+    const int nq = min(kTcRows, n_rows - r_begin);
+    const int h = blockIdx.y, kvh = h / (a.Hq / a.Hkv);
+    const int pos_q0 = pos_start + r_begin;
+    const int kv_end = pos_q0 + nq;
+    const int T = (kv_end + kTcTok - 1) / kTcTok;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        tc::mbar_init(&q_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            tc::mbar_init(&k_full[s], 1); tc::mbar_init(&v_full[s], 1); tc::mbar_init(&s_full[s], 1);
+            tc::mbar_init(&p_full[s], kTcRows); tc::mbar_init(&pv_done[s], 1);
+        }
+        tc::fence_barrier_init();
+        s_abort = 0; s_bad = 0; k_issued = k_consumed = v_issued = v_consumed = q_issued = q_consumed = 0;
+        tc::tma_prefetch_desc(&map_q); tc::tma_prefetch_desc(&map_k); tc::tma_prefetch_desc(&map_v);
+    }
+    if (warp == 6) {
+        tc::tmem_alloc(&tmem_base_slot, kTcTmemCols);
+        tc::tmem_relinquish();
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem = tmem_base_slot;
+    const uint32_t tmem_o = tmem + 128;
+
+    if (warp == 4 || warp == 5) {
+        // ------------------------------------------------ TMA producers: warp 4 = Q and K, warp 5 = V
+        if (lane == 0) {
+            const bool isK = warp == 4;
+            if (isK) {
+                tc::mbar_expect_tx(&q_full, kTcQBytes);
+                for (int cb = 0; cb < 4; ++cb)
+                    tc::tma_load_2d(sQ + cb * (kTcRows * 128), &map_q, h * kTcD + cb * 64, row_start + r_begin, &q_full);
+                q_issued = 1;
+            }
+            const int* bt = a.block_table + (size_t)slot * a.max_blocks;
+            unsigned char* stage0 = isK ? sK : sV;
+            uint64_t* full = isK ? k_full : v_full;
+            uint64_t* freed = isK ? s_full : pv_done;        // a K stage is free once S(t) has read it, a V stage after P V(t)
+            const CUtensorMap* map = isK ? &map_k : &map_v;
+            for (int t = 0; t < T; ++t) {
+                const int b = t & 1;
+                int page[4];
+#pragma unroll
+                for (int pg = 0; pg < 4; ++pg) {
+                    const int blk = t * 4 + pg;
+                    int p = 0;
+                    if (blk * kTcPage < kv_end) {
+                        p = bt[blk];
+                        if (p < 0 || p >= a.num_pages) { s_bad = 1; p = 0; }
+                    }
+                    page[pg] = p;
+                }
+                if (t >= 2 && !tc::mbar_wait_abortable(&freed[b], (uint32_t)((t - 2) >> 1) & 1u, a.budget, &s_abort)) break;
+                tc::mbar_expect_tx(&full[b], kTcKvStage);
+                unsigned char* dst = stage0 + b * kTcKvStage;
+#pragma unroll
+                for (int pg = 0; pg < 4; ++pg)
+#pragma unroll
+                    for (int cb = 0; cb < 4; ++cb)
+                        tc::tma_load_2d(dst + cb * (kTcTok * 128) + pg * (kTcPage * 128), map, cb * 64,
+                                        (page[pg] * a.Hkv + kvh) * kTcPage, &full[b]);
+                if (isK) k_issued = t + 1; else v_issued = t + 1;
+            }
+        }
+    } else if (warp == 6) {
+        // ------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = tc::idesc_bf16_f32(kTcRows, kTcTok);
+            constexpr uint32_t idesc_o = tc::idesc_bf16_f32_bmn(kTcRows, kTcD);
+            const uint32_t q_addr = tc::smem_u32(sQ), k_addr = tc::smem_u32(sK), v_addr = tc::smem_u32(sV), p_addr = tc::smem_u32(sP);
+            auto issue_s = [&](int t) -> bool {
+                const int b = t & 1;
+                if (!tc::mbar_wait_abortable(&k_full[b], (uint32_t)(t >> 1) & 1u, a.budget, &s_abort)) return false;
+                k_consumed = t + 1;
+                tc::fence_after_sync();
+#pragma unroll
+                for (int ks = 0; ks < kTcD / 16; ++ks) {
+                    const uint64_t adesc = tc::smem_desc_sw128(q_addr + (ks >> 2) * (kTcRows * 128) + (ks & 3) * 32);
+                    const uint64_t bdesc = tc::smem_desc_sw128(k_addr + b * kTcKvStage + (ks >> 2) * (kTcTok * 128) + (ks & 3) * 32);
+                    tc::mma_bf16_ss(tmem + b * kTcTok, adesc, bdesc, idesc_s, ks > 0 ? 1u : 0u);
+                }
+                tc::mma_commit(&s_full[b]);
+                return true;
+            };
+            bool ok = tc::mbar_wait_abortable(&q_full, 0, a.budget, &s_abort);
+            if (ok) { q_consumed = 1; ok = issue_s(0); }
+            for (int t = 0; t < T && ok; ++t) {
+                const int b = t & 1;
+                const uint32_t ph = (uint32_t)(t >> 1) & 1u;
+                if (t + 1 < T && !issue_s(t + 1)) { ok = false; break; }
+                if (!tc::mbar_wait_abortable(&p_full[b], ph, a.budget, &s_abort)) { ok = false; break; }
+                if (!tc::mbar_wait_abortable(&v_full[b], ph, a.budget, &s_abort)) { ok = false; break; }
+                v_consumed = t + 1;
+                tc::fence_after_sync();
+#pragma unroll
+                for (int kk = 0; kk < kTcTok / 16; ++kk) {
+                    const uint64_t adesc = tc::smem_desc_sw128(p_addr + b * kTcPBuf + kk * 32);
+                    const uint64_t bdesc = tc::smem_desc_sw128_mn(v_addr + b * kTcKvStage + kk * (16 * 128), kTcTok * 128, 1024);
+                    tc::mma_bf16_ss(tmem_o, adesc, bdesc, idesc_o, (t > 0 || kk > 0) ? 1u : 0u);
+                }
+                tc::mma_commit(&pv_done[b]);
+            }
+        }
+    } else {
+        // ------------------------------------------------ softmax warps 0-3: thread = query row = TMEM lane
+        const int row = warp * 32 + lane;
+        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        const int rp = pos_q0 + row;
+        float m_ref = 0.f, l_run = 0.f;
+        bool ok = true;
+        for (int t = 0; t < T; ++t) {
+            const int b = t & 1;
+            const uint32_t ph = (uint32_t)(t >> 1) & 1u;
+            const int t0 = t * kTcTok;
+            ok = __all_sync(0xffffffffu, tc::mbar_wait_abortable(&s_full[b], ph, a.budget, &s_abort));
+            if (!ok) break;
+            tc::fence_after_sync();
+            uint32_t sr[kTcTok];
+            {
+                uint32_t lo[32], hi[32];
+                tc::tmem_ld_32x32(tmem + lane_base + b * kTcTok, lo);
+                tc::tmem_ld_32x32(tmem + lane_base + b * kTcTok + 32, hi);
+                tc::tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) { sr[j] = lo[j]; sr[32 + j] = hi[j]; }
+            }
+            const bool diag = t0 + kTcTok - 1 > pos_q0;              // some row of the tile does not see every token
+            float mx = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < kTcTok; ++j) {
+                float v = __uint_as_float(sr[j]) * a.scale_log2;
+                if (diag && t0 + j > rp) v = -INFINITY;
+                sr[j] = __float_as_uint(v);
+                mx = fmaxf(mx, v);
+            }
+            float alpha = 1.f;
+            if (t == 0) m_ref = mx;                                   // token 0 is visible to every row
+            else if (mx > m_ref + 8.f) { alpha = exp2f(m_ref - mx); m_ref = mx; }
+            const bool rescale = __any_sync(0xffffffffu, alpha != 1.f);
+            float sum = 0.f;
+            uint32_t pk[kTcTok / 2];
+#pragma unroll
+            for (int j = 0; j < kTcTok; j += 2) {
+                const float p0 = exp2f(__uint_as_float(sr[j]) - m_ref), p1 = exp2f(__uint_as_float(sr[j + 1]) - m_ref);
+                sum += p0 + p1;
+                pk[j >> 1] = f32x2_to_bf16x2_bits(p0, p1);
+            }
+            l_run = l_run * alpha + sum;
+            if (t >= 2) {                                             // P buffer b was read by P V(t - 2)
+                ok = __all_sync(0xffffffffu, tc::mbar_wait_abortable(&pv_done[b], (uint32_t)((t - 2) >> 1) & 1u, a.budget, &s_abort));
+                if (!ok) break;
+            }
+            unsigned char* prow = sP + b * kTcPBuf + row * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+            if (t == T - 1 && kv_end < t0 + kTcTok) {
+                // token rows of the last V tile beyond the sequence's end: zero them (whole 128-byte rows, so the swizzle
+                // does not matter)
+                ok = __all_sync(0xffffffffu, tc::mbar_wait_abortable(&v_full[b], ph, a.budget, &s_abort));
+                if (!ok) break;
+                const int jz = kv_end - t0;
+                unsigned char* vs = sV + b * kTcKvStage;
+                for (int i = row; i < (kTcTok - jz) * 32; i += kTcRows) {
+                    const int r = jz + (i >> 5), cb = (i & 31) >> 3, c = i & 7;
+                    *reinterpret_cast<uint4*>(vs + cb * (kTcTok * 128) + r * 128 + c * 16) = make_uint4(0, 0, 0, 0);
+                }
+            }
+            tc::fence_proxy_async_smem();
+            if (rescale) {                                            // t >= 1: O must be complete up to P V(t - 1)
+                ok = __all_sync(0xffffffffu, tc::mbar_wait_abortable(&pv_done[b ^ 1], (uint32_t)((t - 1) >> 1) & 1u, a.budget, &s_abort));
+                if (!ok) break;
+                tc::fence_after_sync();
+#pragma unroll 1
+                for (int c0 = 0; c0 < kTcD; c0 += 32) {
+                    uint32_t r[32];
+                    tc::tmem_ld_32x32(tmem_o + lane_base + c0, r);
+                    tc::tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * alpha);
+                    tc::tmem_st_32x32(tmem_o + lane_base + c0, r);
+                }
+                tc::tmem_st_wait();
+            }
+            tc::fence_before_sync();
+            tc::mbar_arrive(&p_full[b]);
+        }
+        // ---- epilogue: O / l -> bf16 rows staged in shared memory (Q and K stages are free once the last P V is done)
+        if (ok) ok = __all_sync(0xffffffffu, tc::mbar_wait_abortable(&pv_done[(T - 1) & 1], (uint32_t)((T - 1) >> 1) & 1u, a.budget, &s_abort));
+        if (ok) {
+            tc::fence_after_sync();
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(smem) + row * kTcOutPitch;
+#pragma unroll 1
+            for (int c0 = 0; c0 < kTcD; c0 += 32) {
+                uint32_t r[32];
+                tc::tmem_ld_32x32(tmem_o + lane_base + c0, r);
+                tc::tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        w[e] = f32x2_to_bf16x2_bits(__uint_as_float(r[j + 2 * e]) * inv, __uint_as_float(r[j + 2 * e + 1]) * inv);
+                    *reinterpret_cast<uint4*>(stg + c0 + j) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");               // the four softmax warps only
+        if (ok) {
+            const __nv_bfloat16* stg0 = reinterpret_cast<const __nv_bfloat16*>(smem);
+            for (int i = row; i < nq * (kTcD / 8); i += kTcRows) {
+                const int r = i >> 5, c = i & 31;
+                const size_t grow = (size_t)(row_start + r_begin + r);
+                uint4 v = *reinterpret_cast<const uint4*>(stg0 + r * kTcOutPitch + c * 8);
+                if (a.gate != nullptr) {
+                    const uint4 g = __ldg(reinterpret_cast<const uint4*>(a.gate + grow * a.ld_gate + (size_t)h * a.gate_head_stride + a.gate_offset + c * 8));
+                    const uint32_t vw[4] = {v.x, v.y, v.z, v.w}, gw[4] = {g.x, g.y, g.z, g.w};
+                    uint32_t o[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 vv = bf16x2_bits_to_f32x2(vw[e]), gg = bf16x2_bits_to_f32x2(gw[e]);
+                        o[e] = f32x2_to_bf16x2_bits(vv.x * sigmoid_f(gg.x), vv.y * sigmoid_f(gg.y));
+                    }
+                    v = make_uint4(o[0], o[1], o[2], o[3]);
+                }
+                *reinterpret_cast<uint4*>(a.out + (grow * a.Hq + h) * kTcD + c * 8) = v;
+            }
+        }
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (s_bad != 0) set_status(a.status, PS_DEV_BAD_INDEX);
+        if (s_abort != 0) {
+            set_status(a.status, PS_DEV_WAIT_TIMEOUT);
+            // copies still in flight get a bounded chance to land before the shared memory goes back to the next CTA
+            const long long bd = a.budget < 4000000ll ? a.budget : 4000000ll;
+            if (q_issued > q_consumed) tc::mbar_wait(&q_full, 0, bd);
+            for (int c = k_consumed; c < k_issued; ++c) tc::mbar_wait(&k_full[c & 1], (uint32_t)(c >> 1) & 1u, bd);
+            for (int c = v_consumed; c < v_issued; ++c) tc::mbar_wait(&v_full[c & 1], (uint32_t)(c >> 1) & 1u, bd);
+        }
+    }
+    __syncthreads();
+    if (warp == 6) {
+        tc::fence_after_sync();
+        tc::tmem_dealloc(tmem, kTcTmemCols);
+    }
+}
+
+typedef CUresult (*EncodeTiledFnA)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFnA attn_encode_fn() {
+    static EncodeTiledFnA fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFnA>(p);
+    }
+    return fn;
+}
+
+// bf16 row-major [rows, cols] (leading dimension in elements) with a (box_rows x 64) box and the 128-byte swizzle.
+static int attn_map_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld_elems, uint32_t box_rows) {
+    EncodeTiledFnA enc = attn_encode_fn();
+    if (enc == nullptr) return (int)cudaErrorNotSupported;
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {ld_elems * 2};
+    const cuuint32_t box[2] = {64, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+// True when the tensor-core kernel can take the call (the caller falls back to the mma.sync kernel otherwise).
+bool attn_prefill_tc_supported(int D, int page_tokens, int kv_fp8, const void* q, const void* k_pool, const void* v_pool,
+                               const void* gate, int ld_gate, int gate_head_stride, int gate_offset) {
+    static int enabled = -1;
+    if (enabled < 0) {
+        const char* e = getenv("PS_ATTN_PREFILL");                 // "legacy": always the mma.sync kernel
+        enabled = (e != nullptr && e[0] == 'l') ? 0 : 1;
+    }
+    if (!enabled || D != kTcD || page_tokens != kTcPage || kv_fp8) return false;
+    if (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool) % 16) return false;
+    if (gate != nullptr && (((uintptr_t)gate % 16) || (ld_gate % 8) || (gate_head_stride % 8) || (gate_offset % 8))) return false;
+    return true;
+}
+
+int launch_attn_prefill_tc(const void* q, int q_rows, const void* k_pool, const void* v_pool, const void* block_table,
+                           int max_blocks, int num_pages, const void* seqs, int n_seqs, int max_seq_rows, int Hq, int Hkv,
+                           float sm_scale, const void* gate, int ld_gate, int gate_head_stride, int gate_offset, void* out,
+                           void* status, cudaStream_t stream) {
+    CUtensorMap mq, mk, mv;
+    int err = attn_map_2d(&mq, q, (uint64_t)q_rows, (uint64_t)Hq * kTcD, (uint64_t)Hq * kTcD, kTcRows);
+    if (err) return err;
+    const uint64_t pool_rows = (uint64_t)num_pages * Hkv * kTcPage;
+    if ((err = attn_map_2d(&mk, k_pool, pool_rows, kTcD, kTcD, kTcPage))) return err;
+    if ((err = attn_map_2d(&mv, v_pool, pool_rows, kTcD, kTcD, kTcPage))) return err;
+    AttnTcArgs a;
+    a.block_table = (const int*)block_table; a.max_blocks = max_blocks; a.num_pages = num_pages; a.seqs = (const int*)seqs;
+    a.Hq = Hq; a.Hkv = Hkv; a.scale_log2 = sm_scale * 1.4426950408889634f;
+    a.gate = (const __nv_bfloat16*)gate; a.ld_gate = ld_gate; a.gate_head_stride = gate_head_stride; a.gate_offset = gate_offset;
+    a.out = (__nv_bfloat16*)out; a.status = (uint32_t*)status; a.budget = g_ps_wait_budget_cycles;
+    const size_t smem = (size_t)kTcSmem + 1024;
+    static bool set = false;
+    if (!set) {
+        cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        set = true;
+    }
+    const int tiles = (max_seq_rows + kTcRows - 1) / kTcRows;
+    attn_prefill_tc_kernel<<<dim3(tiles, Hq, n_seqs), kTcThreads, smem, stream>>>(mq, mk, mv, a);
+    return PS_LAUNCH_CHECK();
+}
+
+}  // namespace ps

@@ -358,10 +358,11 @@ class CudaOps(OpTrace):
         tiled = (not self.exact_rows and not b.graph_static and D in (64, 128, 256)
                  and any(len(sq.token_ids) > self.ATTN_PREFILL_MIN_ROWS for sq in b.seqs))
         if tiled:
-            # prefill-sized step: 64-row query tiles on the tensor cores
+            # prefill-sized step: query tiles on the tensor cores (tcgen05 for head dim 256 / bf16 pools / 16-token pages,
+            # mma.sync otherwise)
             _lib.call("ps_attn_prefill", ptr(q), ptr(kv.k), ptr(kv.v), ptr(kv.k_scale), ptr(kv.v_scale),
                       ptr(st.block_table), c_int(st.max_blocks), c_int(st.sc.page_tokens), c_int(st.num_pages),
-                      ptr(b.seq_desc), c_int(b.n_seqs), c_int(rows), c_int(hq), c_int(hkv), c_int(D), c_float(D ** -0.5),
+                      ptr(b.seq_desc), c_int(b.n_seqs), c_int(rows), c_int(q.shape[0]), c_int(hq), c_int(hkv), c_int(D), c_float(D ** -0.5),
                       c_int(1 if st.kv_fp8 else 0), ptr(qkv), c_int(qkv.stride(0)), c_int(2 * D), c_int(D), ptr(out),
                       ptr(st.status))
             self.launches += 1
