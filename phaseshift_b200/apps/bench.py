@@ -56,6 +56,7 @@ def build_parser() -> argparse.ArgumentParser:
     for name in ("rmsnorm", "kv-append", "paged-attention", "gdn-recurrence", "embedding", "sampling", "gpu-memory", "dflash2",
                  "activation-quantize", "elementwise") + tuple(FUSED_INTO):
         p = sub.add_parser(name); p.add_argument("--rows", type=int, default=1); p.add_argument("--context", type=int, default=4096)
+        p.add_argument("--page-tokens", type=int, default=16)
         p.add_argument("--samples", type=int, default=20); p.add_argument("--model", default="27b", choices=["tiny", "4b", "27b"])
         p.add_argument("--kv-cache-dtype", default="bf16", choices=["bf16", "fp8_e4m3"]); p.add_argument("--variant", default="optimized", choices=["optimized"])
     kl = sub.add_parser("kld", help="KL divergence of a quantised preset against the bf16 model of the same random weights"); _model_args(kl)
@@ -323,7 +324,7 @@ def cmd_kernel(a) -> int:
         return cmd_dflash2(a, cfg, dev)
     small = type(cfg)(**{**cfg.__dict__, "num_hidden_layers": 4, "layer_types": None, "vocab_size": min(cfg.vocab_size, 32768)})
     ew = build_engine_weights(small, random_getter(small, 0, dev), "bf16", dev)
-    eng = Engine(ew, dev, StateConfig(max_slots=1, max_seq_len=a.context + a.rows + 64, kv_dtype=a.kv_cache_dtype), use_graphs=False)
+    eng = Engine(ew, dev, StateConfig(max_slots=1, max_seq_len=a.context + a.rows + 64, kv_dtype=a.kv_cache_dtype, page_tokens=a.page_tokens), use_graphs=False)
     ops, st = eng.ops, eng.state
     s = eng.open_sequence()
     eng._reserve(s, a.context + a.rows + 1)

@@ -427,11 +427,11 @@ static int launch_prefill(const AttnPrefillArgs& a, int max_q_tiles, int n_seqs,
     return PS_LAUNCH_CHECK();
 }
 
-// attn_prefill_tc.cu: the tcgen05 kernel for head dim 256, bf16 pools and 16-token pages
+// attn_prefill_tc.cu: the tcgen05 kernel for head dim 256, bf16 pools and pages of 16 / 32 / 64 tokens
 bool attn_prefill_tc_supported(int D, int page_tokens, int kv_fp8, const void* q, const void* k_pool, const void* v_pool,
                                const void* gate, int ld_gate, int gate_head_stride, int gate_offset);
 int launch_attn_prefill_tc(const void* q, int q_rows, const void* k_pool, const void* v_pool, const void* block_table,
-                           int max_blocks, int num_pages, const void* seqs, int n_seqs, int max_seq_rows, int Hq, int Hkv,
+                           int max_blocks, int num_pages, int page_tokens, const void* seqs, int n_seqs, int max_seq_rows, int Hq, int Hkv,
                            float sm_scale, const void* gate, int ld_gate, int gate_head_stride, int gate_offset, void* out,
                            void* status, cudaStream_t stream);
 
@@ -446,7 +446,7 @@ PS_API int ps_attn_prefill(const void* q, const void* k_pool, const void* v_pool
     using namespace ps;
     if (n_seqs <= 0 || max_seq_rows <= 0 || Hkv <= 0 || (Hq % Hkv) || q_rows < max_seq_rows) return (int)cudaErrorInvalidValue;
     if (attn_prefill_tc_supported(D, page_tokens, kv_fp8, q, k_pool, v_pool, gate, ld_gate, gate_head_stride, gate_offset))
-        return launch_attn_prefill_tc(q, q_rows, k_pool, v_pool, block_table, max_blocks, num_pages, seqs, n_seqs, max_seq_rows, Hq, Hkv,
+        return launch_attn_prefill_tc(q, q_rows, k_pool, v_pool, block_table, max_blocks, num_pages, page_tokens, seqs, n_seqs, max_seq_rows, Hq, Hkv,
                                       sm_scale, gate, ld_gate, gate_head_stride, gate_offset, out, status, stream);
     AttnPrefillArgs a;
     a.q = (const __nv_bfloat16*)q; a.k_pool = k_pool; a.v_pool = v_pool; a.k_scale = (const float*)k_scale;

@@ -1,17 +1,20 @@
 // Causal paged attention for prefill-sized steps on the fifth-generation tensor cores (head dim 256, bf16 pools,
-// 16-token pages): one CTA = 128 consecutive query rows of one sequence and one query head.
+// pages of 16, 32 or 64 tokens): one CTA = 128 consecutive query rows of one sequence and one query head.
 //
-//   warp 4   TMA producer for Q (once) and the K tiles: a 64-token tile is four pages, each fetched as four
+//   warp 8   TMA producer for Q (once) and the K tiles: a 64-token tile is four pages, each fetched as four
 //            64-column boxes (128-byte swizzle) straight from the paged pool through a tensor map over
-//            [pages * kv heads * 16, D]; two stages.
-//   warp 5   TMA producer for the V tiles (same boxes, two stages).
-//   warp 6   one thread issues tcgen05.mma: S(t) = Q K(t)^T into one of two 64-column accumulators, and
-//            O += P(t) V(t) into a 256-column accumulator; S(t+1) is issued before P(t) is waited for, so the
-//            tensor core computes the next scores while the softmax warps work on the current ones.
-//            V is consumed as it lies in the pool (token rows, dims contiguous): an MN-major B operand.
-//   warps 0-3  softmax: thread i owns query row i = TMEM lane i.  Scores come back with tcgen05.ld, the running
-//            maximum needs no shuffles, probabilities go to shared memory as a bf16 K-major A operand (swizzled by
-//            hand), and the output accumulator is rescaled in tensor memory only when a row's maximum has grown
+//            [pages * kv heads * page tokens, D] (one, two or four pages per tile for 64-, 32-, 16-token pages); two stages.
+//   warp 9   TMA producer for the V tiles (same boxes, two stages).
+//   warps 10, 11  one thread each issues S(t) = Q K(t)^T (tcgen05.mma, 16 products of 128 x 64 x 16) into one of two
+//            64-column accumulators, warp 10 for even t and warp 11 for odd t, as soon as the K stage and the
+//            accumulator are free, so the tensor core computes the next scores while the softmax warps work on
+//            the current ones.
+//   warp 12  one thread issues O += P(t) V(t) into a 256-column accumulator.  V is consumed as it lies in the
+//            pool (token rows, dims contiguous): an MN-major B operand.
+//   warps 0-7  softmax: two threads own a query row (= TMEM lane), 32 score columns each.  Scores come back with
+//            tcgen05.ld (both threads read the whole row for its maximum: no shuffles, no exchange), probabilities go
+//            to shared memory as a bf16 K-major A operand (swizzled by hand), and the output accumulator is
+//            rescaled in tensor memory only when a row's maximum has grown
 //            by more than 2^8 since the reference used for its exponents (the sum absorbs the difference, so the
 //            result is the exact softmax).  The epilogue normalises, applies the sigmoid output gate and writes
 //            bf16 through shared memory with coalesced 16-byte stores.
@@ -31,8 +34,8 @@
 
 namespace ps {
 
-constexpr int kTcRows = 128, kTcTok = 64, kTcD = 256, kTcPage = 16;
-constexpr int kTcThreads = 224;
+constexpr int kTcRows = 128, kTcTok = 64, kTcD = 256;
+constexpr int kTcThreads = 416;                      // warps 0-7 softmax, 8 Q / K producer, 9 V producer, 10-11 S issuers, 12 P V issuer
 constexpr int kTcQBytes = kTcRows * kTcD * 2;         // 64 KB: four 64-column boxes of 128 rows
 constexpr int kTcKvStage = kTcTok * kTcD * 2;         // 32 KB: four 64-column boxes of 64 tokens
 constexpr int kTcPBuf = kTcRows * kTcTok * 2;         // 16 KB: 128 rows x 64 tokens
@@ -41,13 +44,14 @@ constexpr int kTcOutPitch = kTcD + 8;                 // staging pitch of the ep
 constexpr uint32_t kTcTmemCols = 512;                 // S0 | S1 (64 each) | O (256)
 
 struct AttnTcArgs {
-    const int* block_table; int max_blocks; int num_pages;
+    const int* block_table; int max_blocks; int num_pages; int page_tokens;     // page_tokens: 16, 32 or 64
     const int* seqs;             // [n_seqs][4] = row_start, n_rows, slot, pos_start
     int Hq, Hkv; float scale_log2;
     const __nv_bfloat16* gate; int ld_gate; int gate_head_stride; int gate_offset;
     __nv_bfloat16* out;          // [rows, Hq * D]
     uint32_t* status;
     long long budget;
+    long long* prof;             // optional cycle stamps of CTA (0, 0, 0): [32 tiles][16], softmax slots 0-7, issuer slots 8-12
 };
 
 namespace tc {
@@ -79,17 +83,39 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r
 }
 }  // namespace tc
 
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// sigmoid(x) = 0.5 + 0.5 tanh(x / 2) with the hardware tanh (one special-function operation instead of an exponential and a
+// reciprocal; absolute error about 5e-4, a fraction of the bf16 rounding step of the gated output).  A full-precision
+// division here made the epilogue the longest phase of a short CTA.
+__device__ __forceinline__ float sigmoid_fast(float x) {
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * x));
+    return fmaf(0.5f, t, 0.5f);
+}
+
 // grid = (q tiles of 128 rows, Hq, n_seqs); the heaviest (latest) query tiles are scheduled first.
 __global__ void __launch_bounds__(kTcThreads, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const AttnTcArgs a) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
-    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // Q, two K and two V stages, two P buffers: 224 KB, which with the static part below is the whole 227 KB of the SM;
+    // the swizzled tiles need the 1024-byte alignment that the declaration asks for (checked, not assumed)
+    unsigned char* smem = smem_raw;
+    if ((tc::smem_u32(smem) & 1023u) != 0) {
+        if (threadIdx.x == 0) set_status(a.status, PS_DEV_BAD_INDEX);
+        return;
+    }
     unsigned char* sQ = smem;
     unsigned char* sK = sQ + kTcQBytes;
     unsigned char* sV = sK + 2 * kTcKvStage;
     unsigned char* sP = sV + 2 * kTcKvStage;
     __shared__ __align__(8) uint64_t q_full, k_full[2], v_full[2], s_full[2], p_full[2], pv_done[2];
+    __shared__ float s_l[2][kTcRows];            // row sums of the two column halves, exchanged once at the end
     __shared__ uint32_t tmem_base_slot;
     __shared__ int s_abort, s_bad, k_issued, k_consumed, v_issued, v_consumed, q_issued, q_consumed;
 
@@ -104,18 +130,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int kv_end = pos_q0 + nq;
     const int T = (kv_end + kTcTok - 1) / kTcTok;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool cta_stamp = a.prof != nullptr && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+    if (cta_stamp) a.prof[15] = clock64();
 
     if (threadIdx.x == 0) {
         tc::mbar_init(&q_full, 1);
         for (int s = 0; s < 2; ++s) {
             tc::mbar_init(&k_full[s], 1); tc::mbar_init(&v_full[s], 1); tc::mbar_init(&s_full[s], 1);
-            tc::mbar_init(&p_full[s], kTcRows); tc::mbar_init(&pv_done[s], 1);
+            tc::mbar_init(&p_full[s], 8); tc::mbar_init(&pv_done[s], 1);
         }
         tc::fence_barrier_init();
         s_abort = 0; s_bad = 0; k_issued = k_consumed = v_issued = v_consumed = q_issued = q_consumed = 0;
         tc::tma_prefetch_desc(&map_q); tc::tma_prefetch_desc(&map_k); tc::tma_prefetch_desc(&map_v);
     }
-    if (warp == 6) {
+    if (warp == 12) {
         tc::tmem_alloc(&tmem_base_slot, kTcTmemCols);
         tc::tmem_relinquish();
     }
@@ -125,74 +153,82 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const uint32_t tmem = tmem_base_slot;
     const uint32_t tmem_o = tmem + 128;
 
-    if (warp == 4 || warp == 5) {
-        // ------------------------------------------------ TMA producers: warp 4 = Q and K, warp 5 = V
-        if (lane == 0) {
-            const bool isK = warp == 4;
-            if (isK) {
-                tc::mbar_expect_tx(&q_full, kTcQBytes);
-                for (int cb = 0; cb < 4; ++cb)
-                    tc::tma_load_2d(sQ + cb * (kTcRows * 128), &map_q, h * kTcD + cb * 64, row_start + r_begin, &q_full);
-                q_issued = 1;
-            }
-            const int* bt = a.block_table + (size_t)slot * a.max_blocks;
-            unsigned char* stage0 = isK ? sK : sV;
-            uint64_t* full = isK ? k_full : v_full;
-            uint64_t* freed = isK ? s_full : pv_done;        // a K stage is free once S(t) has read it, a V stage after P V(t)
-            const CUtensorMap* map = isK ? &map_k : &map_v;
-            for (int t = 0; t < T; ++t) {
-                const int b = t & 1;
-                int page[4];
-#pragma unroll
-                for (int pg = 0; pg < 4; ++pg) {
-                    const int blk = t * 4 + pg;
-                    int p = 0;
-                    if (blk * kTcPage < kv_end) {
-                        p = bt[blk];
-                        if (p < 0 || p >= a.num_pages) { s_bad = 1; p = 0; }
-                    }
-                    page[pg] = p;
-                }
-                if (t >= 2 && !tc::mbar_wait_abortable(&freed[b], (uint32_t)((t - 2) >> 1) & 1u, a.budget, &s_abort)) break;
-                tc::mbar_expect_tx(&full[b], kTcKvStage);
-                unsigned char* dst = stage0 + b * kTcKvStage;
-#pragma unroll
-                for (int pg = 0; pg < 4; ++pg)
-#pragma unroll
-                    for (int cb = 0; cb < 4; ++cb)
-                        tc::tma_load_2d(dst + cb * (kTcTok * 128) + pg * (kTcPage * 128), map, cb * 64,
-                                        (page[pg] * a.Hkv + kvh) * kTcPage, &full[b]);
-                if (isK) k_issued = t + 1; else v_issued = t + 1;
-            }
+    if (warp == 8 || warp == 9) {
+        // ------------------------------------------------ TMA producers: warp 8 = Q and K, warp 9 = V.  One lane per box (a
+        // tile is up to 16 boxes: pages x four 64-column groups): issuing them from one thread one after the other costs
+        // more than a thousand cycles, and the stage's consumer is waiting for them.
+        const bool isK = warp == 8;
+        if (isK) {
+            if (lane == 0) tc::mbar_expect_tx(&q_full, kTcQBytes);
+            __syncwarp();
+            if (lane < 4) tc::tma_load_2d(sQ + lane * (kTcRows * 128), &map_q, h * kTcD + lane * 64, row_start + r_begin, &q_full);
+            if (lane == 0) q_issued = 1;
         }
-    } else if (warp == 6) {
-        // ------------------------------------------------ MMA issuer
+        const int* bt = a.block_table + (size_t)slot * a.max_blocks;
+        const int pt = a.page_tokens, ppt = kTcTok / pt;            // a page is one box of pt token rows per 64-column group
+        const int pg = lane >> 2, cb = lane & 3;
+        const bool active = pg < ppt;
+        unsigned char* stage0 = isK ? sK : sV;
+        uint64_t* full = isK ? k_full : v_full;
+        uint64_t* freed = isK ? s_full : pv_done;                   // a K stage is free once S(t) has read it, a V stage after P V(t)
+        const CUtensorMap* map = isK ? &map_k : &map_v;
+        for (int t = 0; t < T; ++t) {
+            const int b = t & 1;
+            int page = 0;
+            const int blk = t * ppt + pg;
+            if (active && blk * pt < kv_end) {
+                page = bt[blk];
+                if (page < 0 || page >= a.num_pages) { s_bad = 1; page = 0; }
+            }
+            if (t >= 2 && !__all_sync(0xffffffffu, tc::mbar_wait_abortable(&freed[b], (uint32_t)((t - 2) >> 1) & 1u, a.budget, &s_abort))) break;
+            if (lane == 0) tc::mbar_expect_tx(&full[b], kTcKvStage);
+            __syncwarp();
+            if (active)
+                tc::tma_load_2d(stage0 + b * kTcKvStage + cb * (kTcTok * 128) + pg * (pt * 128), map, cb * 64, (page * a.Hkv + kvh) * pt, &full[b]);
+            if (lane == 0) { if (isK) k_issued = t + 1; else v_issued = t + 1; }
+        }
+    } else if (warp == 10 || warp == 11) {
+        // ------------------------------------------------ score issuers: warp 10 issues S(t) for even t, warp 11 for odd t.
+        // A tcgen05.mma costs its issuing thread about 80 cycles whatever its size, and a 128 x 64 x 16 product is only 32
+        // cycles of tensor work, so one thread cannot keep the pipe fed; two threads take turns.
         if (lane == 0) {
             constexpr uint32_t idesc_s = tc::idesc_bf16_f32(kTcRows, kTcTok);
-            constexpr uint32_t idesc_o = tc::idesc_bf16_f32_bmn(kTcRows, kTcD);
-            const uint32_t q_addr = tc::smem_u32(sQ), k_addr = tc::smem_u32(sK), v_addr = tc::smem_u32(sV), p_addr = tc::smem_u32(sP);
-            auto issue_s = [&](int t) -> bool {
-                const int b = t & 1;
-                if (!tc::mbar_wait_abortable(&k_full[b], (uint32_t)(t >> 1) & 1u, a.budget, &s_abort)) return false;
-                k_consumed = t + 1;
+            const int b = warp - 10;
+            const uint32_t q_addr = tc::smem_u32(sQ), k_addr = tc::smem_u32(sK) + b * kTcKvStage;
+            bool ok = tc::mbar_wait_abortable(&q_full, 0, a.budget, &s_abort);
+            if (ok) q_consumed = 1;
+            for (int t = b; t < T && ok; t += 2) {
+                const uint32_t ph = (uint32_t)(t >> 1) & 1u;
+                const bool stamp = a.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && t < 32;
+                if (stamp) a.prof[t * 16 + 8] = clock64();
+                // the score buffer is free once the softmax warps have read S(t - 2), which they signal with P(t - 2)
+                if (t >= 2 && !tc::mbar_wait_abortable(&p_full[b], ph ^ 1u, a.budget, &s_abort)) { ok = false; break; }
+                if (!tc::mbar_wait_abortable(&k_full[b], ph, a.budget, &s_abort)) { ok = false; break; }
+                if (stamp) a.prof[t * 16 + 9] = clock64();
+                atomicMax(&k_consumed, t + 1);
                 tc::fence_after_sync();
 #pragma unroll
                 for (int ks = 0; ks < kTcD / 16; ++ks) {
                     const uint64_t adesc = tc::smem_desc_sw128(q_addr + (ks >> 2) * (kTcRows * 128) + (ks & 3) * 32);
-                    const uint64_t bdesc = tc::smem_desc_sw128(k_addr + b * kTcKvStage + (ks >> 2) * (kTcTok * 128) + (ks & 3) * 32);
+                    const uint64_t bdesc = tc::smem_desc_sw128(k_addr + (ks >> 2) * (kTcTok * 128) + (ks & 3) * 32);
                     tc::mma_bf16_ss(tmem + b * kTcTok, adesc, bdesc, idesc_s, ks > 0 ? 1u : 0u);
                 }
                 tc::mma_commit(&s_full[b]);
-                return true;
-            };
-            bool ok = tc::mbar_wait_abortable(&q_full, 0, a.budget, &s_abort);
-            if (ok) { q_consumed = 1; ok = issue_s(0); }
-            for (int t = 0; t < T && ok; ++t) {
+                if (stamp) a.prof[t * 16 + 10] = clock64();
+            }
+        }
+    } else if (warp == 12) {
+        // ------------------------------------------------ output issuer: O += P(t) V(t)
+        if (lane == 0) {
+            constexpr uint32_t idesc_o = tc::idesc_bf16_f32_bmn(kTcRows, kTcD);
+            const uint32_t v_addr = tc::smem_u32(sV), p_addr = tc::smem_u32(sP);
+            for (int t = 0; t < T; ++t) {
                 const int b = t & 1;
                 const uint32_t ph = (uint32_t)(t >> 1) & 1u;
-                if (t + 1 < T && !issue_s(t + 1)) { ok = false; break; }
-                if (!tc::mbar_wait_abortable(&p_full[b], ph, a.budget, &s_abort)) { ok = false; break; }
-                if (!tc::mbar_wait_abortable(&v_full[b], ph, a.budget, &s_abort)) { ok = false; break; }
+                const bool stamp = a.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && t < 32;
+                if (!tc::mbar_wait_abortable(&p_full[b], ph, a.budget, &s_abort)) break;
+                if (stamp) a.prof[t * 16 + 11] = clock64();
+                if (!tc::mbar_wait_abortable(&v_full[b], ph, a.budget, &s_abort)) break;
                 v_consumed = t + 1;
                 tc::fence_after_sync();
 #pragma unroll
@@ -202,80 +238,97 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     tc::mma_bf16_ss(tmem_o, adesc, bdesc, idesc_o, (t > 0 || kk > 0) ? 1u : 0u);
                 }
                 tc::mma_commit(&pv_done[b]);
+                if (stamp) a.prof[t * 16 + 12] = clock64();
             }
         }
     } else {
-        // ------------------------------------------------ softmax warps 0-3: thread = query row = TMEM lane
-        const int row = warp * 32 + lane;
-        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        // ------------------------------------------------ softmax warps 0-7: two threads per query row.  Warp w works on
+        // TMEM lanes 32 (w % 4) .. + 31 (the quadrant a warp may touch) and on score columns 32 (w / 4) .. + 31 of the tile.
+        const int quad = warp & 3, half = warp >> 2;
+        const int row = quad * 32 + lane;
+        const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
         const int rp = pos_q0 + row;
+        const float sc = a.scale_log2;
         float m_ref = 0.f, l_run = 0.f;
         bool ok = true;
+        // the epilogue reads this tile's gate values (one 512-byte run per row): ask for them now, so that they come from
+        // L2 then
+        if (a.gate != nullptr && half == 0 && row < nq)
+            tc::bulk_prefetch_l2(a.gate + (size_t)(row_start + r_begin + row) * a.ld_gate + (size_t)h * a.gate_head_stride + a.gate_offset, kTcD * 2);
         for (int t = 0; t < T; ++t) {
             const int b = t & 1;
             const uint32_t ph = (uint32_t)(t >> 1) & 1u;
-            const int t0 = t * kTcTok;
+            const int t0 = t * kTcTok + half * 32;                    // first token of this thread's columns
+            const bool stamp = a.prof != nullptr && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && t < 32;
+            if (stamp) a.prof[t * 16 + 0] = clock64();
             ok = __all_sync(0xffffffffu, tc::mbar_wait_abortable(&s_full[b], ph, a.budget, &s_abort));
             if (!ok) break;
             tc::fence_after_sync();
-            uint32_t sr[kTcTok];
-            {
-                uint32_t lo[32], hi[32];
-                tc::tmem_ld_32x32(tmem + lane_base + b * kTcTok, lo);
-                tc::tmem_ld_32x32(tmem + lane_base + b * kTcTok + 32, hi);
-                tc::tmem_ld_wait();
+            if (stamp) a.prof[t * 16 + 1] = clock64();
+            // both threads of a row read all 64 scores and take the maximum themselves (cheaper than an exchange through
+            // shared memory); each then exponentiates its own 32 columns
+            uint32_t sr[32], so[32];
+            tc::tmem_ld_32x32(tmem + lane_base + b * kTcTok + half * 32, sr);
+            tc::tmem_ld_32x32(tmem + lane_base + b * kTcTok + (half ^ 1) * 32, so);
+            tc::tmem_ld_wait();
+            if (stamp) a.prof[t * 16 + 2] = clock64();
+            if (t * kTcTok + kTcTok - 1 > pos_q0) {                   // some row of the tile does not see every token
+                const int to = t * kTcTok + (half ^ 1) * 32;
 #pragma unroll
-                for (int j = 0; j < 32; ++j) { sr[j] = lo[j]; sr[32 + j] = hi[j]; }
+                for (int j = 0; j < 32; ++j) {
+                    if (t0 + j > rp) sr[j] = 0xff800000u;             // -inf
+                    if (to + j > rp) so[j] = 0xff800000u;
+                }
             }
-            const bool diag = t0 + kTcTok - 1 > pos_q0;              // some row of the tile does not see every token
-            float mx = -INFINITY;
+            float mq[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int j = 0; j < kTcTok; ++j) {
-                float v = __uint_as_float(sr[j]) * a.scale_log2;
-                if (diag && t0 + j > rp) v = -INFINITY;
-                sr[j] = __float_as_uint(v);
-                mx = fmaxf(mx, v);
-            }
+            for (int j = 0; j < 32; ++j) mq[j & 3] = fmaxf(mq[j & 3], fmaxf(__uint_as_float(sr[j]), __uint_as_float(so[j])));
+            float mx = fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3])) * sc;     // scale > 0, so the maximum commutes with it
+            if (stamp) a.prof[t * 16 + 3] = clock64();
             float alpha = 1.f;
             if (t == 0) m_ref = mx;                                   // token 0 is visible to every row
-            else if (mx > m_ref + 8.f) { alpha = exp2f(m_ref - mx); m_ref = mx; }
+            else if (mx > m_ref + 8.f) { alpha = ex2_approx(m_ref - mx); m_ref = mx; }
             const bool rescale = __any_sync(0xffffffffu, alpha != 1.f);
-            float sum = 0.f;
-            uint32_t pk[kTcTok / 2];
+            float sq[4] = {0.f, 0.f, 0.f, 0.f};
+            uint32_t pk[16];
 #pragma unroll
-            for (int j = 0; j < kTcTok; j += 2) {
-                const float p0 = exp2f(__uint_as_float(sr[j]) - m_ref), p1 = exp2f(__uint_as_float(sr[j + 1]) - m_ref);
-                sum += p0 + p1;
+            for (int j = 0; j < 32; j += 2) {
+                const float p0 = ex2_approx(fmaf(__uint_as_float(sr[j]), sc, -m_ref));
+                const float p1 = ex2_approx(fmaf(__uint_as_float(sr[j + 1]), sc, -m_ref));
+                sq[(j >> 1) & 3] += p0 + p1;
                 pk[j >> 1] = f32x2_to_bf16x2_bits(p0, p1);
             }
-            l_run = l_run * alpha + sum;
+            l_run = l_run * alpha + ((sq[0] + sq[1]) + (sq[2] + sq[3]));
             if (t >= 2) {                                             // P buffer b was read by P V(t - 2)
                 ok = __all_sync(0xffffffffu, tc::mbar_wait_abortable(&pv_done[b], (uint32_t)((t - 2) >> 1) & 1u, a.budget, &s_abort));
                 if (!ok) break;
             }
+            if (stamp) a.prof[t * 16 + 4] = clock64();
             unsigned char* prow = sP + b * kTcPBuf + row * 128;
 #pragma unroll
-            for (int c = 0; c < 8; ++c)
-                *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-            if (t == T - 1 && kv_end < t0 + kTcTok) {
+            for (int c = 0; c < 4; ++c)
+                *reinterpret_cast<uint4*>(prow + (((half * 4 + c) ^ (row & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+            if (t == T - 1 && kv_end < (t + 1) * kTcTok) {
                 // token rows of the last V tile beyond the sequence's end: zero them (whole 128-byte rows, so the swizzle
                 // does not matter)
                 ok = __all_sync(0xffffffffu, tc::mbar_wait_abortable(&v_full[b], ph, a.budget, &s_abort));
                 if (!ok) break;
-                const int jz = kv_end - t0;
+                const int jz = kv_end - t * kTcTok;
                 unsigned char* vs = sV + b * kTcKvStage;
-                for (int i = row; i < (kTcTok - jz) * 32; i += kTcRows) {
+                for (int i = (int)threadIdx.x; i < (kTcTok - jz) * 32; i += 2 * kTcRows) {
                     const int r = jz + (i >> 5), cb = (i & 31) >> 3, c = i & 7;
                     *reinterpret_cast<uint4*>(vs + cb * (kTcTok * 128) + r * 128 + c * 16) = make_uint4(0, 0, 0, 0);
                 }
             }
+            if (stamp) a.prof[t * 16 + 5] = clock64();
             tc::fence_proxy_async_smem();
+            if (stamp) a.prof[t * 16 + 6] = clock64();
             if (rescale) {                                            // t >= 1: O must be complete up to P V(t - 1)
                 ok = __all_sync(0xffffffffu, tc::mbar_wait_abortable(&pv_done[b ^ 1], (uint32_t)((t - 1) >> 1) & 1u, a.budget, &s_abort));
                 if (!ok) break;
                 tc::fence_after_sync();
 #pragma unroll 1
-                for (int c0 = 0; c0 < kTcD; c0 += 32) {
+                for (int c0 = half * (kTcD / 2); c0 < (half + 1) * (kTcD / 2); c0 += 32) {
                     uint32_t r[32];
                     tc::tmem_ld_32x32(tmem_o + lane_base + c0, r);
                     tc::tmem_ld_wait();
@@ -286,16 +339,23 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 tc::tmem_st_wait();
             }
             tc::fence_before_sync();
-            tc::mbar_arrive(&p_full[b]);
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(&p_full[b]);
+            if (stamp) a.prof[t * 16 + 7] = clock64();
         }
         // ---- epilogue: O / l -> bf16 rows staged in shared memory (Q and K stages are free once the last P V is done)
         if (ok) ok = __all_sync(0xffffffffu, tc::mbar_wait_abortable(&pv_done[(T - 1) & 1], (uint32_t)((T - 1) >> 1) & 1u, a.budget, &s_abort));
+        if (cta_stamp) a.prof[2 * 16 + 15] = clock64();
+        s_l[half][row] = l_run;
+        asm volatile("bar.sync 1, 256;" ::: "memory");               // the eight softmax warps only; every one of them gets here
+        if (cta_stamp) a.prof[3 * 16 + 15] = clock64();
         if (ok) {
             tc::fence_after_sync();
-            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            const float l = l_run + s_l[half ^ 1][row];
+            const float inv = l > 0.f ? 1.f / l : 0.f;
             __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(smem) + row * kTcOutPitch;
 #pragma unroll 1
-            for (int c0 = 0; c0 < kTcD; c0 += 32) {
+            for (int c0 = half * (kTcD / 2); c0 < (half + 1) * (kTcD / 2); c0 += 32) {
                 uint32_t r[32];
                 tc::tmem_ld_32x32(tmem_o + lane_base + c0, r);
                 tc::tmem_ld_wait();
@@ -309,28 +369,45 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 }
             }
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");               // the four softmax warps only
+        if (cta_stamp) a.prof[4 * 16 + 15] = clock64();
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (cta_stamp) a.prof[5 * 16 + 15] = clock64();
         if (ok) {
+            // 16-byte pieces, four per thread and pass so that the gate loads of a pass are in flight together
             const __nv_bfloat16* stg0 = reinterpret_cast<const __nv_bfloat16*>(smem);
-            for (int i = row; i < nq * (kTcD / 8); i += kTcRows) {
-                const int r = i >> 5, c = i & 31;
-                const size_t grow = (size_t)(row_start + r_begin + r);
-                uint4 v = *reinterpret_cast<const uint4*>(stg0 + r * kTcOutPitch + c * 8);
-                if (a.gate != nullptr) {
-                    const uint4 g = __ldg(reinterpret_cast<const uint4*>(a.gate + grow * a.ld_gate + (size_t)h * a.gate_head_stride + a.gate_offset + c * 8));
-                    const uint32_t vw[4] = {v.x, v.y, v.z, v.w}, gw[4] = {g.x, g.y, g.z, g.w};
-                    uint32_t o[4];
+            const int n_items = nq * (kTcD / 8);
+            for (int i0 = (int)threadIdx.x; i0 < n_items; i0 += 8 * kTcRows) {
+                uint4 g[4];
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float2 vv = bf16x2_bits_to_f32x2(vw[e]), gg = bf16x2_bits_to_f32x2(gw[e]);
-                        o[e] = f32x2_to_bf16x2_bits(vv.x * sigmoid_f(gg.x), vv.y * sigmoid_f(gg.y));
-                    }
-                    v = make_uint4(o[0], o[1], o[2], o[3]);
+                for (int u = 0; u < 4; ++u) {
+                    const int i = i0 + u * 2 * kTcRows;
+                    g[u] = make_uint4(0, 0, 0, 0);
+                    if (a.gate != nullptr && i < n_items)
+                        g[u] = __ldg(reinterpret_cast<const uint4*>(a.gate + (size_t)(row_start + r_begin + (i >> 5)) * a.ld_gate +
+                                                                    (size_t)h * a.gate_head_stride + a.gate_offset + (i & 31) * 8));
                 }
-                *reinterpret_cast<uint4*>(a.out + (grow * a.Hq + h) * kTcD + c * 8) = v;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int i = i0 + u * 2 * kTcRows;
+                    if (i >= n_items) break;
+                    const int r = i >> 5, c = i & 31;
+                    uint4 v = *reinterpret_cast<const uint4*>(stg0 + r * kTcOutPitch + c * 8);
+                    if (a.gate != nullptr) {
+                        const uint32_t vw[4] = {v.x, v.y, v.z, v.w}, gw[4] = {g[u].x, g[u].y, g[u].z, g[u].w};
+                        uint32_t o[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float2 vv = bf16x2_bits_to_f32x2(vw[e]), gg = bf16x2_bits_to_f32x2(gw[e]);
+                            o[e] = f32x2_to_bf16x2_bits(vv.x * sigmoid_fast(gg.x), vv.y * sigmoid_fast(gg.y));
+                        }
+                        v = make_uint4(o[0], o[1], o[2], o[3]);
+                    }
+                    *reinterpret_cast<uint4*>(a.out + ((size_t)(row_start + r_begin + r) * a.Hq + h) * kTcD + c * 8) = v;
+                }
             }
         }
     }
+    if (cta_stamp) a.prof[6 * 16 + 15] = clock64();
     tc::fence_before_sync();
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -345,7 +422,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
     }
     __syncthreads();
-    if (warp == 6) {
+    if (cta_stamp) a.prof[16 + 15] = clock64();
+    if (warp == 12) {
         tc::fence_after_sync();
         tc::tmem_dealloc(tmem, kTcTmemCols);
     }
@@ -381,6 +459,8 @@ static int attn_map_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64
     return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
+static long long* g_attn_tc_prof = nullptr;
+
 // True when the tensor-core kernel can take the call (the caller falls back to the mma.sync kernel otherwise).
 bool attn_prefill_tc_supported(int D, int page_tokens, int kv_fp8, const void* q, const void* k_pool, const void* v_pool,
                                const void* gate, int ld_gate, int gate_head_stride, int gate_offset) {
@@ -389,28 +469,28 @@ bool attn_prefill_tc_supported(int D, int page_tokens, int kv_fp8, const void* q
         const char* e = getenv("PS_ATTN_PREFILL");                 // "legacy": always the mma.sync kernel
         enabled = (e != nullptr && e[0] == 'l') ? 0 : 1;
     }
-    if (!enabled || D != kTcD || page_tokens != kTcPage || kv_fp8) return false;
+    if (!enabled || D != kTcD || (page_tokens != 16 && page_tokens != 32 && page_tokens != 64) || kv_fp8) return false;
     if (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool) % 16) return false;
     if (gate != nullptr && (((uintptr_t)gate % 16) || (ld_gate % 8) || (gate_head_stride % 8) || (gate_offset % 8))) return false;
     return true;
 }
 
 int launch_attn_prefill_tc(const void* q, int q_rows, const void* k_pool, const void* v_pool, const void* block_table,
-                           int max_blocks, int num_pages, const void* seqs, int n_seqs, int max_seq_rows, int Hq, int Hkv,
+                           int max_blocks, int num_pages, int page_tokens, const void* seqs, int n_seqs, int max_seq_rows, int Hq, int Hkv,
                            float sm_scale, const void* gate, int ld_gate, int gate_head_stride, int gate_offset, void* out,
                            void* status, cudaStream_t stream) {
     CUtensorMap mq, mk, mv;
     int err = attn_map_2d(&mq, q, (uint64_t)q_rows, (uint64_t)Hq * kTcD, (uint64_t)Hq * kTcD, kTcRows);
     if (err) return err;
-    const uint64_t pool_rows = (uint64_t)num_pages * Hkv * kTcPage;
-    if ((err = attn_map_2d(&mk, k_pool, pool_rows, kTcD, kTcD, kTcPage))) return err;
-    if ((err = attn_map_2d(&mv, v_pool, pool_rows, kTcD, kTcD, kTcPage))) return err;
+    const uint64_t pool_rows = (uint64_t)num_pages * Hkv * page_tokens;
+    if ((err = attn_map_2d(&mk, k_pool, pool_rows, kTcD, kTcD, (uint32_t)page_tokens))) return err;
+    if ((err = attn_map_2d(&mv, v_pool, pool_rows, kTcD, kTcD, (uint32_t)page_tokens))) return err;
     AttnTcArgs a;
-    a.block_table = (const int*)block_table; a.max_blocks = max_blocks; a.num_pages = num_pages; a.seqs = (const int*)seqs;
+    a.block_table = (const int*)block_table; a.max_blocks = max_blocks; a.num_pages = num_pages; a.page_tokens = page_tokens; a.seqs = (const int*)seqs;
     a.Hq = Hq; a.Hkv = Hkv; a.scale_log2 = sm_scale * 1.4426950408889634f;
     a.gate = (const __nv_bfloat16*)gate; a.ld_gate = ld_gate; a.gate_head_stride = gate_head_stride; a.gate_offset = gate_offset;
-    a.out = (__nv_bfloat16*)out; a.status = (uint32_t*)status; a.budget = g_ps_wait_budget_cycles;
-    const size_t smem = (size_t)kTcSmem + 1024;
+    a.out = (__nv_bfloat16*)out; a.status = (uint32_t*)status; a.budget = g_ps_wait_budget_cycles; a.prof = g_attn_tc_prof;
+    const size_t smem = (size_t)kTcSmem;
     static bool set = false;
     if (!set) {
         cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -422,3 +502,9 @@ int launch_attn_prefill_tc(const void* q, int q_rows, const void* k_pool, const 
 }
 
 }  // namespace ps
+
+// Timing aid: a device buffer of 32 x 16 int64 that CTA (0, 0, 0) of later launches fills with cycle stamps of its softmax
+// thread 0 (slots 0-7: tile start, scores ready, scores loaded, row maximum exchanged, probabilities computed, stored,
+// proxy fence done, arrived) and of the issuing threads (slots 8-10: score issuer at its tile's start, operands ready,
+// issued; 11-12: output issuer with probabilities ready, issued; slot 15 of tiles 0 and 1: start and end of the CTA).  nullptr switches it off.
+PS_API void ps_attn_prefill_tc_set_prof(void* buf) { ps::g_attn_tc_prof = (long long*)buf; }
