@@ -25,7 +25,7 @@ struct AttnPrefillArgs {
     const void* k_pool; const void* v_pool; const float* k_scale; const float* v_scale;
     const int* block_table; int max_blocks; int page_tokens; int num_pages;
     const int* seqs;             // [n_seqs][4] = row_start, n_rows, slot, pos_start
-    int Hq, Hkv; float scale_log2; int kv_fp8;
+    int Hq, Hkv; float scale_log2; int kv_fp8; int min_rows;
     const __nv_bfloat16* gate; int ld_gate; int gate_head_stride; int gate_offset;
     __nv_bfloat16* out;          // [rows, Hq*D]
     uint32_t* status;
@@ -116,7 +116,7 @@ __global__ void __launch_bounds__(kPfThreads) attn_prefill_kernel(const AttnPref
     const int row_start = sd[0], n_rows = sd[1], slot = sd[2], pos_start = sd[3];
     const int tile = (int)gridDim.x - 1 - (int)blockIdx.x;
     const int r_begin = tile * kPfRows;
-    if (r_begin >= n_rows || slot < 0) return;
+    if (r_begin >= n_rows || slot < 0 || n_rows <= a.min_rows) return;
     const int nq = min(kPfRows, n_rows - r_begin);
     const int h = blockIdx.y, G = a.Hq / a.Hkv, kvh = h / G;
     const int pos_q0 = pos_start + r_begin;
@@ -285,7 +285,7 @@ __global__ void __launch_bounds__(kPfThreads) attn_prefill_async_kernel(const At
     const int row_start = sd[0], n_rows = sd[1], slot = sd[2], pos_start = sd[3];
     const int tile = (int)gridDim.x - 1 - (int)blockIdx.x;
     const int r_begin = tile * kPfRows;
-    if (r_begin >= n_rows || slot < 0) return;
+    if (r_begin >= n_rows || slot < 0 || n_rows <= a.min_rows) return;
     const int nq = min(kPfRows, n_rows - r_begin);
     const int h = blockIdx.y, G = a.Hq / a.Hkv, kvh = h / G;
     const int pos_q0 = pos_start + r_begin;
@@ -427,34 +427,39 @@ static int launch_prefill(const AttnPrefillArgs& a, int max_q_tiles, int n_seqs,
     return PS_LAUNCH_CHECK();
 }
 
-// attn_prefill_tc.cu: the tcgen05 kernel for head dim 256, bf16 pools and pages of 16 / 32 / 64 tokens
+// attn_prefill_tc.cu: the tcgen05 kernel for head dim 256 and pages of 16 / 32 / 64 tokens (FP8 pools through a bf16 scratch pool)
 bool attn_prefill_tc_supported(int D, int page_tokens, int kv_fp8, const void* q, const void* k_pool, const void* v_pool,
-                               const void* gate, int ld_gate, int gate_head_stride, int gate_offset);
-int launch_attn_prefill_tc(const void* q, int q_rows, const void* k_pool, const void* v_pool, const void* block_table,
-                           int max_blocks, int num_pages, int page_tokens, const void* seqs, int n_seqs, int max_seq_rows, int Hq, int Hkv,
-                           float sm_scale, const void* gate, int ld_gate, int gate_head_stride, int gate_offset, void* out,
-                           void* status, cudaStream_t stream);
+                               const void* gate, int ld_gate, int gate_head_stride, int gate_offset, const void* deq_k);
+int launch_attn_prefill_tc(const void* q, int q_rows, const void* k_pool, const void* v_pool, const void* k_scale, const void* v_scale,
+                           int kv_fp8, const void* block_table, int max_blocks, int num_pages, int page_tokens, const void* seqs,
+                           int n_seqs, int max_seq_rows, int min_rows, int Hq, int Hkv, float sm_scale, const void* gate, int ld_gate,
+                           int gate_head_stride, int gate_offset, void* deq_k, void* deq_v, int deq_pages, void* deq_bt, void* deq_seqs,
+                           void* out, void* status, cudaStream_t stream);
 
 }  // namespace ps
 
-// `max_seq_rows`: upper bound of n_rows over the step's sequences (sizes the grid); `q_rows`: rows of the q tensor.
+// `max_seq_rows`: upper bound of n_rows over the step's sequences (sizes the grid); `q_rows`: rows of the q tensor;
+// `min_rows`: sequences with at most this many rows are skipped (the caller runs the split-KV kernel on their rows);
+// `deq_*`: optional bf16 scratch pool ([deq_pages, Hkv, page_tokens, D] twice), block table [n_seqs, max_blocks] and
+// sequence descriptors [n_seqs, 4] that let FP8 pools take the tensor-core kernel.
 PS_API int ps_attn_prefill(const void* q, const void* k_pool, const void* v_pool, const void* k_scale, const void* v_scale,
                            const void* block_table, int max_blocks, int page_tokens, int num_pages, const void* seqs,
-                           int n_seqs, int max_seq_rows, int q_rows, int Hq, int Hkv, int D, float sm_scale, int kv_fp8,
-                           const void* gate, int ld_gate, int gate_head_stride, int gate_offset, void* out, void* status,
-                           cudaStream_t stream) {
+                           int n_seqs, int max_seq_rows, int q_rows, int min_rows, int Hq, int Hkv, int D, float sm_scale, int kv_fp8,
+                           const void* gate, int ld_gate, int gate_head_stride, int gate_offset, void* deq_k, void* deq_v,
+                           int deq_pages, void* deq_bt, void* deq_seqs, void* out, void* status, cudaStream_t stream) {
     using namespace ps;
     if (n_seqs <= 0 || max_seq_rows <= 0 || Hkv <= 0 || (Hq % Hkv) || q_rows < max_seq_rows) return (int)cudaErrorInvalidValue;
-    if (attn_prefill_tc_supported(D, page_tokens, kv_fp8, q, k_pool, v_pool, gate, ld_gate, gate_head_stride, gate_offset))
-        return launch_attn_prefill_tc(q, q_rows, k_pool, v_pool, block_table, max_blocks, num_pages, page_tokens, seqs, n_seqs, max_seq_rows, Hq, Hkv,
-                                      sm_scale, gate, ld_gate, gate_head_stride, gate_offset, out, status, stream);
+    if (attn_prefill_tc_supported(D, page_tokens, kv_fp8, q, k_pool, v_pool, gate, ld_gate, gate_head_stride, gate_offset, deq_k))
+        return launch_attn_prefill_tc(q, q_rows, k_pool, v_pool, k_scale, v_scale, kv_fp8, block_table, max_blocks, num_pages, page_tokens,
+                                      seqs, n_seqs, max_seq_rows, min_rows, Hq, Hkv, sm_scale, gate, ld_gate, gate_head_stride, gate_offset,
+                                      deq_k, deq_v, deq_pages, deq_bt, deq_seqs, out, status, stream);
     AttnPrefillArgs a;
     a.q = (const __nv_bfloat16*)q; a.k_pool = k_pool; a.v_pool = v_pool; a.k_scale = (const float*)k_scale;
     a.v_scale = (const float*)v_scale; a.block_table = (const int*)block_table; a.max_blocks = max_blocks;
     a.page_tokens = page_tokens; a.num_pages = num_pages; a.seqs = (const int*)seqs; a.Hq = Hq; a.Hkv = Hkv;
     a.scale_log2 = sm_scale * 1.4426950408889634f; a.kv_fp8 = kv_fp8; a.gate = (const __nv_bfloat16*)gate;
     a.ld_gate = ld_gate; a.gate_head_stride = gate_head_stride; a.gate_offset = gate_offset;
-    a.out = (__nv_bfloat16*)out; a.status = (uint32_t*)status;
+    a.out = (__nv_bfloat16*)out; a.status = (uint32_t*)status; a.min_rows = min_rows;
     const int tiles = (max_seq_rows + kPfRows - 1) / kPfRows;
     if (D == 256) return launch_prefill<256>(a, tiles, n_seqs, stream);
     if (D == 128) return launch_prefill<128>(a, tiles, n_seqs, stream);

@@ -47,6 +47,7 @@ struct AttnTcArgs {
     const int* block_table; int max_blocks; int num_pages; int page_tokens;     // page_tokens: 16, 32 or 64
     const int* seqs;             // [n_seqs][4] = row_start, n_rows, slot, pos_start
     int Hq, Hkv; float scale_log2;
+    int min_rows;                // sequences with at most this many rows in the step are left to the split-KV kernel
     const __nv_bfloat16* gate; int ld_gate; int gate_head_stride; int gate_offset;
     __nv_bfloat16* out;          // [rows, Hq * D]
     uint32_t* status;
@@ -123,7 +124,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int row_start = sd[0], n_rows = sd[1], slot = sd[2], pos_start = sd[3];
     const int tile = (int)gridDim.x - 1 - (int)blockIdx.x;
     const int r_begin = tile * kTcRows;
-    if (r_begin >= n_rows || slot < 0) return;
+    if (r_begin >= n_rows || slot < 0 || n_rows <= a.min_rows) return;
     const int nq = min(kTcRows, n_rows - r_begin);
     const int h = blockIdx.y, kvh = h / (a.Hq / a.Hkv);
     const int pos_q0 = pos_start + r_begin;
@@ -429,6 +430,73 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
 }
 
+// FP8 pools: the sequences' pages are widened once per layer and step into a bf16 scratch pool of the same page shape
+// (values times their per-token scale), with its own block table (scratch page = running index) and sequence descriptors
+// (slot = sequence index), and the tensor-core kernel runs on that.  The copy moves 3 bytes per cached element; the
+// attention it feeds is an order of magnitude faster than the mma.sync kernel on FP8 pages.
+struct AttnDeqArgs {
+    const uint8_t* k_pool; const uint8_t* v_pool; const float* k_scale; const float* v_scale;
+    const int* block_table; int max_blocks; int num_pages; int page_tokens; int Hkv;
+    const int* seqs; int n_seqs; int min_rows;
+    __nv_bfloat16* k_out; __nv_bfloat16* v_out; int out_pages;
+    int* bt_out;                 // [n_seqs][max_blocks]
+    int* seqs_out;               // [n_seqs][4]
+    uint32_t* status;
+};
+
+// grid = (scratch pages, Hkv), block = 256
+__global__ void __launch_bounds__(256) attn_kv_dequant_kernel(const AttnDeqArgs a) {
+    const int p = blockIdx.x, kvh = blockIdx.y, pt = a.page_tokens;
+    // which sequence and block this scratch page belongs to
+    int base = 0, s = 0, blk = -1, kv_end = 0, slot = -1;
+    for (; s < a.n_seqs; ++s) {
+        const int* sd = a.seqs + 4 * s;
+        const int n_rows = sd[1];
+        if (sd[2] < 0 || n_rows <= a.min_rows) continue;
+        const int end = sd[3] + n_rows, np = (end + pt - 1) / pt;
+        if (p < base + np) { blk = p - base; kv_end = end; slot = sd[2]; break; }
+        base += np;
+    }
+    if (p == 0 && kvh == 0) {
+        for (int i = threadIdx.x; i < a.n_seqs; i += blockDim.x) {
+            const int* sd = a.seqs + 4 * i;
+            a.seqs_out[4 * i + 0] = sd[0]; a.seqs_out[4 * i + 1] = sd[1]; a.seqs_out[4 * i + 2] = sd[2] < 0 ? -1 : i; a.seqs_out[4 * i + 3] = sd[3];
+        }
+    }
+    if (blk < 0) return;
+    if (kvh == 0 && threadIdx.x == 0) a.bt_out[(size_t)s * a.max_blocks + blk] = p;
+    const int page = a.block_table[(size_t)slot * a.max_blocks + blk];
+    const bool ok = page >= 0 && page < a.num_pages;
+    if (!ok && threadIdx.x == 0) set_status(a.status, PS_DEV_BAD_INDEX);
+    const size_t src = ((size_t)(ok ? page : 0) * a.Hkv + kvh) * pt;          // token rows of the source page
+    const size_t dst = ((size_t)p * a.Hkv + kvh) * pt;
+    for (int i = threadIdx.x; i < pt * (kTcD / 16); i += blockDim.x) {
+        const int tok = i / (kTcD / 16), c = i % (kTcD / 16);
+        const bool live = ok && blk * pt + tok < kv_end;
+#pragma unroll
+        for (int which = 0; which < 2; ++which) {
+            const uint8_t* pool = which ? a.v_pool : a.k_pool;
+            const float* sp = which ? a.v_scale : a.k_scale;
+            __nv_bfloat16* out = which ? a.v_out : a.k_out;
+            uint32_t o[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            if (live) {
+                const uint4 v = __ldg(reinterpret_cast<const uint4*>(pool + (src + tok) * kTcD) + c);
+                const float sc = sp[src + tok];
+                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float lo = e4m3_to_f32((w[j >> 1] >> ((j & 1) * 16)) & 0xff) * sc;
+                    const float hi = e4m3_to_f32((w[j >> 1] >> ((j & 1) * 16 + 8)) & 0xff) * sc;
+                    o[j] = f32x2_to_bf16x2_bits(lo, hi);
+                }
+            }
+            uint4* d = reinterpret_cast<uint4*>(out + (dst + tok) * kTcD + c * 16);
+            d[0] = make_uint4(o[0], o[1], o[2], o[3]);
+            d[1] = make_uint4(o[4], o[5], o[6], o[7]);
+        }
+    }
+}
+
 typedef CUresult (*EncodeTiledFnA)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -463,22 +531,36 @@ static long long* g_attn_tc_prof = nullptr;
 
 // True when the tensor-core kernel can take the call (the caller falls back to the mma.sync kernel otherwise).
 bool attn_prefill_tc_supported(int D, int page_tokens, int kv_fp8, const void* q, const void* k_pool, const void* v_pool,
-                               const void* gate, int ld_gate, int gate_head_stride, int gate_offset) {
+                               const void* gate, int ld_gate, int gate_head_stride, int gate_offset, const void* deq_k) {
     static int enabled = -1;
     if (enabled < 0) {
         const char* e = getenv("PS_ATTN_PREFILL");                 // "legacy": always the mma.sync kernel
         enabled = (e != nullptr && e[0] == 'l') ? 0 : 1;
     }
-    if (!enabled || D != kTcD || (page_tokens != 16 && page_tokens != 32 && page_tokens != 64) || kv_fp8) return false;
+    if (!enabled || D != kTcD || (page_tokens != 16 && page_tokens != 32 && page_tokens != 64) || (kv_fp8 && deq_k == nullptr)) return false;
     if (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool) % 16) return false;
     if (gate != nullptr && (((uintptr_t)gate % 16) || (ld_gate % 8) || (gate_head_stride % 8) || (gate_offset % 8))) return false;
     return true;
 }
 
-int launch_attn_prefill_tc(const void* q, int q_rows, const void* k_pool, const void* v_pool, const void* block_table,
-                           int max_blocks, int num_pages, int page_tokens, const void* seqs, int n_seqs, int max_seq_rows, int Hq, int Hkv,
-                           float sm_scale, const void* gate, int ld_gate, int gate_head_stride, int gate_offset, void* out,
-                           void* status, cudaStream_t stream) {
+int launch_attn_prefill_tc(const void* q, int q_rows, const void* k_pool, const void* v_pool, const void* k_scale, const void* v_scale,
+                           int kv_fp8, const void* block_table, int max_blocks, int num_pages, int page_tokens, const void* seqs,
+                           int n_seqs, int max_seq_rows, int min_rows, int Hq, int Hkv, float sm_scale, const void* gate, int ld_gate,
+                           int gate_head_stride, int gate_offset, void* deq_k, void* deq_v, int deq_pages, void* deq_bt, void* deq_seqs,
+                           void* out, void* status, cudaStream_t stream) {
+    if (kv_fp8) {
+        // widen the step's pages into the bf16 scratch pool, then attend over that
+        if (deq_k == nullptr || deq_v == nullptr || deq_bt == nullptr || deq_seqs == nullptr || deq_pages <= 0) return (int)cudaErrorInvalidValue;
+        AttnDeqArgs d;
+        d.k_pool = (const uint8_t*)k_pool; d.v_pool = (const uint8_t*)v_pool; d.k_scale = (const float*)k_scale; d.v_scale = (const float*)v_scale;
+        d.block_table = (const int*)block_table; d.max_blocks = max_blocks; d.num_pages = num_pages; d.page_tokens = page_tokens; d.Hkv = Hkv;
+        d.seqs = (const int*)seqs; d.n_seqs = n_seqs; d.min_rows = min_rows; d.k_out = (__nv_bfloat16*)deq_k; d.v_out = (__nv_bfloat16*)deq_v;
+        d.out_pages = deq_pages; d.bt_out = (int*)deq_bt; d.seqs_out = (int*)deq_seqs; d.status = (uint32_t*)status;
+        attn_kv_dequant_kernel<<<dim3(deq_pages, Hkv), 256, 0, stream>>>(d);
+        int e = PS_LAUNCH_CHECK();
+        if (e) return e;
+        k_pool = deq_k; v_pool = deq_v; block_table = deq_bt; seqs = deq_seqs; num_pages = deq_pages;
+    }
     CUtensorMap mq, mk, mv;
     int err = attn_map_2d(&mq, q, (uint64_t)q_rows, (uint64_t)Hq * kTcD, (uint64_t)Hq * kTcD, kTcRows);
     if (err) return err;
@@ -487,7 +569,7 @@ int launch_attn_prefill_tc(const void* q, int q_rows, const void* k_pool, const 
     if ((err = attn_map_2d(&mv, v_pool, pool_rows, kTcD, kTcD, (uint32_t)page_tokens))) return err;
     AttnTcArgs a;
     a.block_table = (const int*)block_table; a.max_blocks = max_blocks; a.num_pages = num_pages; a.page_tokens = page_tokens; a.seqs = (const int*)seqs;
-    a.Hq = Hq; a.Hkv = Hkv; a.scale_log2 = sm_scale * 1.4426950408889634f;
+    a.Hq = Hq; a.Hkv = Hkv; a.scale_log2 = sm_scale * 1.4426950408889634f; a.min_rows = min_rows;
     a.gate = (const __nv_bfloat16*)gate; a.ld_gate = ld_gate; a.gate_head_stride = gate_head_stride; a.gate_offset = gate_offset;
     a.out = (__nv_bfloat16*)out; a.status = (uint32_t*)status; a.budget = g_ps_wait_budget_cycles; a.prof = g_attn_tc_prof;
     const size_t smem = (size_t)kTcSmem;

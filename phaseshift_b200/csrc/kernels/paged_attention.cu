@@ -220,6 +220,7 @@ __global__ void paged_attn_merge_kernel(const AttnMergeArgs a) {
     cudaGridDependencySynchronize();
     const int h = blockIdx.x, row = blockIdx.y, d = threadIdx.x;
     const int visible = a.row_pos[row] + 1;
+    if (visible < 0) return;                                            // position -2: a row another kernel of the step owns
     const int n = (visible + a.split_tokens - 1) / a.split_tokens;      // 0 for a padding row
     const float* ml = a.part_ml + ((size_t)row * a.Hq + h) * a.max_splits * 2;
     const float* pa = a.part_acc + ((size_t)row * a.Hq + h) * a.max_splits * a.D;

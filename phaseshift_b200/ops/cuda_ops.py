@@ -357,26 +357,51 @@ class CudaOps(OpTrace):
         # many sequences with a row or two each (batched decode) keep the per-row split-KV kernel
         tiled = (not self.exact_rows and not b.graph_static and D in (64, 128, 256)
                  and any(len(sq.token_ids) > self.ATTN_PREFILL_MIN_ROWS for sq in b.seqs))
+        row_pos = b.row_pos
         if tiled:
-            # prefill-sized step: query tiles on the tensor cores (tcgen05 for head dim 256 / bf16 pools / 16-token pages,
-            # mma.sync otherwise)
+            # prefill-sized step: the long sequences' query tiles on the tensor cores (tcgen05 for head dim 256 and pages of
+            # 16 / 32 / 64 tokens, FP8 pools through a bf16 scratch copy of the step's pages; mma.sync otherwise); sequences
+            # with a row or two (decode rows of other requests in the same step) stay on the per-row kernel below
+            T = self.ATTN_PREFILL_MIN_ROWS
+            pt = st.sc.page_tokens
+            any_short = T == StepBatch.SHORT_SEQ_ROWS and any(len(sq.token_ids) <= T for sq in b.seqs)
+            min_rows = T if any_short else 0
+            deq = (None, None, 0, None, None)
+            if st.kv_fp8 and D == 256 and pt in (16, 32, 64):
+                pages = sum(-(-(sq.pos_start + len(sq.token_ids)) // pt) for sq in b.seqs if len(sq.token_ids) > min_rows)
+                deq = self._attn_scratch(pages, hkv, pt, D, b.max_seqs, st.max_blocks)
             _lib.call("ps_attn_prefill", ptr(q), ptr(kv.k), ptr(kv.v), ptr(kv.k_scale), ptr(kv.v_scale),
-                      ptr(st.block_table), c_int(st.max_blocks), c_int(st.sc.page_tokens), c_int(st.num_pages),
-                      ptr(b.seq_desc), c_int(b.n_seqs), c_int(rows), c_int(q.shape[0]), c_int(hq), c_int(hkv), c_int(D), c_float(D ** -0.5),
-                      c_int(1 if st.kv_fp8 else 0), ptr(qkv), c_int(qkv.stride(0)), c_int(2 * D), c_int(D), ptr(out),
-                      ptr(st.status))
-            self.launches += 1
-            return out
+                      ptr(st.block_table), c_int(st.max_blocks), c_int(pt), c_int(st.num_pages),
+                      ptr(b.seq_desc), c_int(b.n_seqs), c_int(rows), c_int(q.shape[0]), c_int(min_rows), c_int(hq), c_int(hkv), c_int(D),
+                      c_float(D ** -0.5), c_int(1 if st.kv_fp8 else 0), ptr(qkv), c_int(qkv.stride(0)), c_int(2 * D), c_int(D),
+                      ptr(deq[0]), ptr(deq[1]), c_int(deq[2]), ptr(deq[3]), ptr(deq[4]), ptr(out), ptr(st.status))
+            self.launches += 2 if deq[0] is not None else 1
+            if not any_short:
+                return out
+            row_pos = b.row_pos_short
         pacc = self.buf("attn_part_acc", rows, hq * self.max_splits * D, torch.float32)
         pml = self.buf("attn_part_ml", rows, hq * self.max_splits * 2, torch.float32)
         _lib.call("ps_paged_attention", ptr(q), ptr(kv.k), ptr(kv.v), ptr(kv.k_scale), ptr(kv.v_scale),
                   ptr(st.block_table), c_int(st.max_blocks), c_int(st.sc.page_tokens), c_int(st.num_pages),
-                  ptr(b.row_slot), ptr(b.row_pos), c_int(rows), c_int(hq), c_int(hkv), c_int(D),
+                  ptr(b.row_slot), ptr(row_pos), c_int(rows), c_int(hq), c_int(hkv), c_int(D),
                   c_float(D ** -0.5), c_int(1 if st.kv_fp8 else 0), c_int(self.split_tokens),
                   c_int(self.max_splits), c_int(max_visible), ptr(pacc), ptr(pml), ptr(qkv), c_int(qkv.stride(0)),
                   c_int(2 * D), c_int(D), ptr(out), ptr(st.status))
         self.launches += 2
         return out
+
+    def _attn_scratch(self, pages: int, hkv: int, pt: int, D: int, max_seqs: int, max_blocks: int):
+        """bf16 scratch pool for the tiled attention over FP8 pages: (k, v, pages, block table, sequence descriptors).  One
+        allocation that grows to the largest step seen (by doubling)."""
+        cap = getattr(self, "_deq_cap", 0)
+        if pages > cap or getattr(self, "_deq_geom", None) != (hkv, pt, D, max_seqs, max_blocks):
+            cap = max(pages, 2 * cap, 64)
+            self._deq_k = torch.empty(cap, hkv, pt, D, dtype=torch.bfloat16, device=self.device)
+            self._deq_v = torch.empty_like(self._deq_k)
+            self._deq_bt = torch.zeros(max_seqs, max_blocks, dtype=torch.int32, device=self.device)
+            self._deq_seqs = torch.zeros(max_seqs, 4, dtype=torch.int32, device=self.device)
+            self._deq_cap, self._deq_geom = cap, (hkv, pt, D, max_seqs, max_blocks)
+        return self._deq_k, self._deq_v, pages, self._deq_bt, self._deq_seqs
 
     def gdn(self, proj: torch.Tensor, gw: GdnW, hk: int, hv: int, b: StepBatch, gs: GdnLayerState,
             st: ModelState, log=None, to_alt: bool = False, xn: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -45,11 +45,12 @@ SAMPLING_ROW_DTYPE = np.dtype([("mode", "<u4"), ("temperature", "<f4"), ("top_p"
 
 class StepBatch:
     """Host-side packed step + its device mirror."""
+    SHORT_SEQ_ROWS = 16          # = CudaOps.ATTN_PREFILL_MIN_ROWS: sequences with more rows take the tiled attention kernel
 
     def __init__(self, max_rows: int, max_seqs: int, device, pinned: Optional[bool] = None):
         self.max_rows, self.max_seqs, self.device = max_rows, max_seqs, device
         use_pin = (device.type == "cuda") if pinned is None else pinned
-        n_int = 3 * max_rows + 4 * max_seqs + max_rows        # ids, slot, pos | seq descs | output rows
+        n_int = 3 * max_rows + 4 * max_seqs + 2 * max_rows    # ids, slot, pos | seq descs | output rows | pos of short sequences' rows
         self.h_int = torch.zeros(n_int, dtype=torch.int32, pin_memory=use_pin)
         self.h_samp = torch.zeros(max_rows * SAMPLING_ROW_DTYPE.itemsize, dtype=torch.uint8, pin_memory=use_pin)
         self.d_int = torch.zeros(n_int, dtype=torch.int32, device=device)
@@ -66,7 +67,11 @@ class StepBatch:
         self.row_slot = self.d_int[o:o + max_rows]; o += max_rows
         self.row_pos = self.d_int[o:o + max_rows]; o += max_rows
         self.seq_desc = self.d_int[o:o + 4 * max_seqs].view(max_seqs, 4); o += 4 * max_seqs
-        self.out_rows = self.d_int[o:o + max_rows]
+        self.out_rows = self.d_int[o:o + max_rows]; o += max_rows
+        # positions of the rows of sequences with at most SHORT_SEQ_ROWS rows in the step, -2 for the rows of longer sequences
+        # (the per-row attention kernel leaves those rows' outputs alone: the tiled kernel of the same step wrote them) and
+        # -1 for padding rows
+        self.row_pos_short = self.d_int[o:o + max_rows]
         self._np = self.h_int.numpy()
         self._np_samp = self.h_samp.numpy().view(SAMPLING_ROW_DTYPE)
         self.seqs: List[SeqRows] = []
@@ -76,6 +81,8 @@ class StepBatch:
         a = self._np
         a[:] = 0
         a[mr:3 * mr] = -1          # padding rows of a bucket: slot -1 / position -1, skipped by the kernels
+        short0 = 3 * mr + 4 * ms + mr
+        a[short0:short0 + mr] = -1
         r = 0
         n_out = 0
         max_vis = 1
@@ -88,6 +95,7 @@ class StepBatch:
             a[r:r + n] = np.asarray(s.token_ids, dtype=np.int32)
             a[mr + r:mr + r + n] = s.slot
             a[2 * mr + r:2 * mr + r + n] = np.arange(s.pos_start, s.pos_start + n, dtype=np.int32)
+            a[short0 + r:short0 + r + n] = a[2 * mr + r:2 * mr + r + n] if n <= self.SHORT_SEQ_ROWS else -2
             a[3 * mr + 4 * i:3 * mr + 4 * i + 4] = (r, n, s.slot, s.pos_start)
             for j, orow in enumerate(s.output_rows):
                 a[3 * mr + 4 * ms + n_out] = r + orow

@@ -717,3 +717,57 @@ def test_long_context_prefill_and_decode_paths_agree_at_32k(kvd):
         t = tk[0]
         toks.append(t)
     assert len(toks) == 4 and int(eng.ops.status[0]) == 0 and int(eng.state.status[0]) == 0
+
+
+@pytest.mark.parametrize("kv_dtype", ["bf16", "fp8_e4m3"])
+def test_attention_mixed_step_long_rows_tiled_short_rows_per_row(kv_dtype):
+    """A serving-shaped step: one prefill chunk of 150 rows at position 200 next to two decode rows of sequences with 300
+    and 37 tokens of context.  The chunk runs on the tiled tensor-core kernel (FP8 pages through the bf16 scratch pool),
+    the decode rows on the per-row kernel; all rows against the fp32 reference and against the per-row kernel alone."""
+    cfg = Qwen35Config(vocab_size=1024, hidden_size=512, intermediate_size=512, num_hidden_layers=4,
+                       num_attention_heads=12, num_key_value_heads=2, head_dim=256)
+    cu, ref = _ops(cfg, 512)
+    sc = StateConfig(max_slots=3, max_seq_len=512, page_tokens=16, kv_dtype=kv_dtype, kv_capacity_tokens=2048)
+    st_c = ModelState(cfg, sc, _dev(), torch.bfloat16)
+    st_r = ModelState(cfg, sc, _dev(), torch.float32)
+    nb = st_c.max_blocks
+    for st in (st_c, st_r):
+        perm = torch.randperm(st.num_pages - 1, generator=torch.Generator().manual_seed(7))[:3 * nb] + 1
+        for s in range(3):
+            st.block_table[s, :nb] = perm[s * nb:(s + 1) * nb].int().to(_dev())
+    li = cfg.attn_layers[0]
+    hf = random_hf_weights(cfg, seed=3, device="cuda")
+    aw = build_engine_weights(cfg, lambda n: hf[n], "bf16", "cuda").layers[li].mixer
+    Hq, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    g = torch.Generator(device="cuda").manual_seed(11)
+    width = 2 * Hq * D + 2 * Hkv * D
+    tol = 2e-2 if kv_dtype == "bf16" else 6e-2
+
+    def run(seqs):
+        n = sum(len(s.token_ids) for s in seqs)
+        qkv = torch.randn(n, width, device="cuda", generator=g).to(torch.bfloat16)
+        b = StepBatch(512, 3, _dev())
+        b.fill(seqs); b.upload()
+        q_c = cu.attn_prep(qkv, aw, Hq, Hkv, b, st_c.kv[li], st_c)
+        q_r = ref.attn_prep(qkv.float(), aw, Hq, Hkv, b, st_r.kv[li], st_r)
+        o_c = cu.paged_attention(q_c, qkv, Hq, Hkv, b, st_c.kv[li], st_c, b.max_visible).clone()
+        o_r = ref.paged_attention(q_r, qkv.float(), Hq, Hkv, b, st_r.kv[li], st_r, b.max_visible)
+        cu.ATTN_PREFILL_MIN_ROWS = 1 << 30
+        try:
+            o_s = cu.paged_attention(q_c, qkv, Hq, Hkv, b, st_c.kv[li], st_c, b.max_visible).clone()
+        finally:
+            del cu.ATTN_PREFILL_MIN_ROWS
+        return n, o_c, o_r, o_s
+    # contexts: sequence 0 gets 200 tokens, sequence 1 300, sequence 2 37
+    for seqs in ([SeqRows(0, 0, [0] * 200, ())], [SeqRows(1, 0, [0] * 300, ())], [SeqRows(2, 0, [0] * 37, ())]):
+        run(seqs)
+    launches = cu.launches
+    n, o_c, o_r, o_s = run([SeqRows(1, 300, [0], ()), SeqRows(0, 200, [0] * 150, ()), SeqRows(2, 37, [0], ())])
+    torch.cuda.synchronize()
+    assert n == 152 and int(st_c.status[0]) == 0
+    assert _rel_err(o_c[:n], o_r[:n]) < tol
+    assert _rel_err(o_c[:n].float(), o_s[:n].float()) < (1.5e-2 if kv_dtype == "bf16" else 3e-2)
+    for r in (0, 151):                                   # the decode rows came from the per-row kernel: same bits
+        assert torch.equal(o_c[r], o_s[r])
+    # prep + (dequantise +) tiled + split + merge for the mixed call, prep excluded: 3 or 4 launches, then 2 for the per-row run
+    assert cu.launches - launches == 1 + (4 if kv_dtype != "bf16" else 3) + 2
