@@ -447,7 +447,7 @@ def main():
         # ---------------- device-timed arm: K graph replays, token fed back on the device
         pos0 = s.position
         eng._reserve(s, pos0 + K + max(W, 3) + 1)
-        graph_key = (1 * 4096 + 1) * 2 + 1            # bucket 1, one output row, identity output gather
+        graph_key = eng.graph_key(1, 1, True, greedy=eng.fused_argmax)     # bucket 1, one output row, identity output gather
         graph = eng.graphs[graph_key]
         gout = eng.graph_out[graph_key]
         b1.fill([SeqRows(s.slot, pos0, [tok], (0,))]); b1.graph_static = True; b1.upload()

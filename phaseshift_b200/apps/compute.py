@@ -158,12 +158,12 @@ def run_single_shot(a, rt: ComputeRuntime, out=None) -> int:
         s = rt.engine.open_sequence()
         rows, gen = [], []
         toks, o = rt.engine.step([SeqRows(s.slot, 0, ids, (len(ids) - 1,), temperature=a.temperature, top_p=a.top_p,
-                                          top_k=a.top_k, seed=a.seed)], [s])
+                                          top_k=a.top_k, seed=a.seed)], [s], want_logits=True)
         rows.append(o.logits[:1].float().cpu().numpy())
         gen.append(toks[0])
         while len(gen) < a.max_new_tokens and gen[-1] not in stop:
             toks, o = rt.engine.step([SeqRows(s.slot, s.position, [gen[-1]], (0,), temperature=a.temperature,
-                                              top_p=a.top_p, top_k=a.top_k, seed=a.seed, sample_index=len(gen))], [s])
+                                              top_p=a.top_p, top_k=a.top_k, seed=a.seed, sample_index=len(gen))], [s], want_logits=True)
             rows.append(o.logits[:1].float().cpu().numpy())
             gen.append(toks[0])
         np.concatenate(rows, 0).astype("<f4").tofile(a.dump_logits)

@@ -69,7 +69,20 @@ struct LinearSmallArgs {
     int out_f32;
     __nv_bfloat16* xn_out;    // optional [M, K]: the prologue's output row(s), written by CTA 0
     TpCombine tp;
+    // Optional fused greedy sampling (the lm_head of a decode step): every CTA folds the rows it produced into a running
+    // (value, index) best per batch row, the last CTA to finish writes the winners' indices and re-arms the state.
+    unsigned long long* amax_best;   // [8] packed keys, zero between launches
+    unsigned int* amax_ctl;          // [0] CTAs done, [1] a non-finite value was seen
+    int* amax_tokens;                // [M] winners (-1 when a non-finite value was seen)
 };
+
+// Packed arg-max key: the value's bits made monotonic, then the complement of the index, so that an unsigned 64-bit maximum
+// picks the larger value and, between equal values, the lower index (the sampling kernel's rule).
+__device__ __forceinline__ unsigned long long amax_key(float v, int n) {
+    uint32_t u = __float_as_uint(v);
+    u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    return ((unsigned long long)u << 32) | (unsigned long long)(0xffffffffu - (uint32_t)n);
+}
 
 constexpr int kQuadRows = 4;
 

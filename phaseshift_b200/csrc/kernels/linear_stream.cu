@@ -27,7 +27,9 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint3
                  ::"r"(tc::smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(tc::smem_u32(bar)) : "memory");
 }
 
-template <int WF, int MT>
+// AMAX: greedy sampling fused into the epilogue (ps_linear_stream_argmax); a template parameter, so that the kernel every
+// other projection uses is compiled without a trace of it
+template <int WF, int MT, bool AMAX = false>
 __global__ void __launch_bounds__(kStThreads, 1) linear_stream_kernel(const LinearSmallArgs a, uint32_t* status,
                                                                        const int n_slots, const long long budget) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -92,6 +94,8 @@ __global__ void __launch_bounds__(kStThreads, 1) linear_stream_kernel(const Line
 
     int consumed = 0;
     bool timed_out = false;
+    [[maybe_unused]] unsigned long long amax_mine = 0ull;      // AMAX: this thread's best key (its batch row is threadIdx.x % MT)
+    [[maybe_unused]] bool amax_bad = false;
     for (int wave_q0 = quad_begin; wave_q0 < quad_end; wave_q0 += kStWaveQuads) {
         const int wave_quads = min(kStWaveQuads, quad_end - wave_q0);
         const int total = wave_quads * steps;
@@ -161,7 +165,20 @@ __global__ void __launch_bounds__(kStThreads, 1) linear_stream_kernel(const Line
                     }
                     v[r] = s * (a.w_gscale * s_xscale_inv[m]);
                 }
-                if (m < a.M) quad_epilogue(a, (wave_q0 + ql) * R, m, v);
+                if (m < a.M) {
+                    if constexpr (AMAX) {
+#pragma unroll
+                        for (int r = 0; r < R; ++r) {
+                            const int n = (wave_q0 + ql) * R + r;
+                            if (n < a.N) {
+                                if (!(fabsf(v[r]) <= 3.0e38f)) amax_bad = true;
+                                const unsigned long long key = amax_key(v[r], n);
+                                if (key > amax_mine) amax_mine = key;
+                            }
+                        }
+                    }
+                    if (!AMAX || a.out != nullptr) quad_epilogue(a, (wave_q0 + ql) * R, m, v);
+                }
             }
         } else {
             // ---- tensor-parallel combine (see TpCombine)
@@ -227,6 +244,36 @@ __global__ void __launch_bounds__(kStThreads, 1) linear_stream_kernel(const Line
         // whichever thread's wait ran out, the whole CTA leaves and every warp's lane 0 reports and drains
         if (__syncthreads_or(timed_out ? 1 : 0)) { timed_out = true; break; }
     }
+    if constexpr (AMAX) {
+        // fused greedy sampling: CTA-level maximum per batch row in shared memory, one global atomic per row and CTA, and
+        // the last CTA to arrive publishes the winners and re-arms the state for the next launch (nobody waits)
+        __shared__ unsigned long long s_amax[8];
+        __shared__ int s_amax_last;
+        if (threadIdx.x < 8) s_amax[threadIdx.x] = 0ull;
+        __syncthreads();
+        if (amax_mine != 0ull) atomicMax(&s_amax[threadIdx.x % MT], amax_mine);      // a thread only ever sees row threadIdx.x % MT
+        const int any_bad = __syncthreads_or(amax_bad ? 1 : 0);
+        if ((int)threadIdx.x < a.M && s_amax[threadIdx.x] != 0ull) atomicMax(&a.amax_best[threadIdx.x], s_amax[threadIdx.x]);
+        if (threadIdx.x == 0 && any_bad) atomicOr(&a.amax_ctl[1], 1u);
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) s_amax_last = atomicAdd(&a.amax_ctl[0], 1u) == gridDim.x - 1 ? 1 : 0;
+        __syncthreads();
+        if (s_amax_last) {
+            __threadfence();
+            const unsigned int bad = *reinterpret_cast<volatile unsigned int*>(&a.amax_ctl[1]);
+            if ((int)threadIdx.x < a.M) {
+                const unsigned long long key = atomicMax(&a.amax_best[threadIdx.x], 0ull);
+                a.amax_tokens[threadIdx.x] = (bad || key == 0ull) ? -1 : (int)(0xffffffffu - (uint32_t)(key & 0xffffffffull));
+                a.amax_best[threadIdx.x] = 0ull;
+            }
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                if (bad) set_status(status, PS_DEV_NONFINITE);
+                a.amax_ctl[0] = 0u; a.amax_ctl[1] = 0u;
+            }
+        }
+    }
     if (timed_out && lane == 0) {
         // A copy never completed.  Report it and give copies still in flight a bounded chance to land
         // before the CTA (and its shared memory) goes away.
@@ -237,7 +284,7 @@ __global__ void __launch_bounds__(kStThreads, 1) linear_stream_kernel(const Line
 
 static int g_st_sm_count = 0, g_st_pdl = 1;
 
-template <int WF, int MT>
+template <int WF, int MT, bool AMAX = false>
 static int launch_stream(const LinearSmallArgs& a, uint32_t* status, cudaStream_t stream) {
     const int kpad = gemv_kpad<WF>(a.K);
     const size_t fixed = (size_t)kpad * MT * sizeof(typename WTraits<WF>::XS) +
@@ -249,7 +296,7 @@ static int launch_stream(const LinearSmallArgs& a, uint32_t* status, cudaStream_
     const size_t smem = fixed + (size_t)kStWarps * slots * slot_stride<WF>();
     static bool attr_set = false;
     if (!attr_set) {
-        cudaFuncSetAttribute(linear_stream_kernel<WF, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
+        cudaFuncSetAttribute(linear_stream_kernel<WF, MT, AMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
         attr_set = true;
     }
     const int n_quads = (a.N + kQuadRows - 1) / kQuadRows;
@@ -260,7 +307,7 @@ static int launch_stream(const LinearSmallArgs& a, uint32_t* status, cudaStream_
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = g_st_pdl ? 1 : 0;
-    return (int)cudaLaunchKernelEx(&cfg, linear_stream_kernel<WF, MT>, a, status, slots, g_ps_wait_budget_cycles);
+    return (int)cudaLaunchKernelEx(&cfg, linear_stream_kernel<WF, MT, AMAX>, a, status, slots, g_ps_wait_budget_cycles);
 }
 
 template <int WF>
@@ -269,6 +316,15 @@ static int stream_dispatch_m(const LinearSmallArgs& a, uint32_t* status, cudaStr
     if (a.M <= 2) return launch_stream<WF, 2>(a, status, stream);
     if (a.M <= 4) return launch_stream<WF, 4>(a, status, stream);
     if (a.M <= 8) return launch_stream<WF, 8>(a, status, stream);
+    return -1;
+}
+
+template <int WF>
+static int stream_dispatch_m_amax(const LinearSmallArgs& a, uint32_t* status, cudaStream_t stream) {
+    if (a.M <= 1) return launch_stream<WF, 1, true>(a, status, stream);
+    if (a.M <= 2) return launch_stream<WF, 2, true>(a, status, stream);
+    if (a.M <= 4) return launch_stream<WF, 4, true>(a, status, stream);
+    if (a.M <= 8) return launch_stream<WF, 8, true>(a, status, stream);
     return -1;
 }
 
@@ -301,6 +357,7 @@ PS_API int ps_linear_stream(int wfmt, const void* x, int M, int N, int K, int ld
     a.gate = (const __nv_bfloat16*)gate; a.ld_gate = ld_gate;
     a.epilogue = epilogue; a.residual = (const __nv_bfloat16*)residual; a.ld_res = ld_res;
     a.out = out; a.ldo = ldo; a.out_f32 = out_f32; a.xn_out = (__nv_bfloat16*)xn_out;
+    a.amax_best = nullptr; a.amax_ctl = nullptr; a.amax_tokens = nullptr;
     if (tp_combine != nullptr) {
         a.tp = *reinterpret_cast<const TpCombine*>(tp_combine);
         if (a.tp.size > kTpMaxRanks || M > a.tp.max_rows || ((N + 3) / 4 * 4) > a.tp.n_pad || epilogue == EPI_SWIGLU)
@@ -312,6 +369,33 @@ PS_API int ps_linear_stream(int wfmt, const void* x, int M, int N, int K, int ld
         case W_BF16: return stream_dispatch_m<W_BF16>(a, (uint32_t*)status, stream);
         case W_NVFP4: return stream_dispatch_m<W_NVFP4>(a, (uint32_t*)status, stream);
         case W_MXFP8: return stream_dispatch_m<W_MXFP8>(a, (uint32_t*)status, stream);
+    }
+    return (int)cudaErrorInvalidValue;
+}
+
+// The same projection with greedy sampling fused into it (the lm_head of a decode step): `tokens[m]` receives the index of
+// row m's largest output (ties to the lower index, -1 and PS_DEV_NONFINITE if a value is not finite), in the same launch.
+// `state` is 8 x uint64 + 2 x uint32 of device memory, zeroed once by the caller and kept zero between launches by the
+// kernel.  `out` may be null: the logits are then never written.  No tensor-parallel combine, store epilogue only.
+// Reference: src/phaseshift/models/qwen35/kernels/optimized/sampling.hip:114-204 (arg-max contract).
+PS_API int ps_linear_stream_argmax(int wfmt, const void* x, int M, int N, int K, int ldx, const void* w_tiled, float w_gscale,
+                                   int prologue, const void* norm_w, float eps, void* out, int ldo, void* state, void* tokens,
+                                   void* status, cudaStream_t stream) {
+    using namespace ps;
+    stream_init_once();
+    if (M < 1 || M > 8 || (K % 32) != 0 || (ldx % 8) != 0 || ((uintptr_t)w_tiled % 16) != 0 || state == nullptr || tokens == nullptr)
+        return (int)cudaErrorInvalidValue;
+    LinearSmallArgs a;
+    a.x = (const __nv_bfloat16*)x; a.M = M; a.N = N; a.K = K; a.ldx = ldx;
+    a.w = (const uint8_t*)w_tiled; a.w_gscale = w_gscale;
+    a.prologue = prologue; a.norm_w = (const __nv_bfloat16*)norm_w; a.eps = eps;
+    a.gate = nullptr; a.ld_gate = 0; a.epilogue = EPI_STORE; a.residual = nullptr; a.ld_res = 0;
+    a.out = out; a.ldo = ldo; a.out_f32 = 1; a.xn_out = nullptr; a.tp.size = 0;
+    a.amax_best = (unsigned long long*)state; a.amax_ctl = (unsigned int*)((unsigned long long*)state + 8); a.amax_tokens = (int*)tokens;
+    switch (wfmt) {
+        case W_BF16: return stream_dispatch_m_amax<W_BF16>(a, (uint32_t*)status, stream);
+        case W_NVFP4: return stream_dispatch_m_amax<W_NVFP4>(a, (uint32_t*)status, stream);
+        case W_MXFP8: return stream_dispatch_m_amax<W_MXFP8>(a, (uint32_t*)status, stream);
     }
     return (int)cudaErrorInvalidValue;
 }

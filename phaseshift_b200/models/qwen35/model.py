@@ -96,7 +96,9 @@ class Qwen35Runner:
 
     def forward(self, b: StepBatch, rows: int, n_out: int, *, tap_layers: Sequence[int] = (),
                 gdn_log: Optional[Dict[int, tuple]] = None, gdn_to_alt: bool = False,
-                mask=None, mask_active=None, sample: bool = True) -> StepOutput:
+                mask=None, mask_active=None, sample: bool = True, greedy_only: bool = False) -> StepOutput:
+        """``greedy_only``: every output row is sampled greedily, without a mask, and nobody reads the logits: the lm_head
+        may then produce the token ids itself (fused arg-max) and ``StepOutput.logits`` is None."""
         cfg, ops, st, w = self.cfg, self.ops, self.state, self.w
         eps = cfg.rms_norm_eps
         x_ssq = None
@@ -184,6 +186,11 @@ class Qwen35Runner:
             else:
                 hidden, h_ssq = ops.gather_rows(x, b.out_rows, n_out, "out_hidden", st.status), None
             self._tap(_P + "lm_head.weight", hidden, n_out, w.final_norm)
+            if (greedy_only and sample and mask is None and self.tp is None and hasattr(ops, "can_fuse_argmax")
+                    and ops.can_fuse_argmax(w.lm_head, n_out)):
+                with ops.range("head.lm_head"):
+                    tokens = ops.linear_argmax(hidden, w.lm_head, norm_w=w.final_norm, eps=eps)
+                return StepOutput(tokens, None, hidden, taps, taps_cat)
             with ops.range("head.lm_head"):
                 logits = ops.linear(hidden, w.lm_head, name="logits", norm_w=w.final_norm, eps=eps, out_f32=True,
                                     **({"ssq_in": h_ssq} if self.use_ssq else {}))

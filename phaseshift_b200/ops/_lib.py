@@ -25,6 +25,10 @@ def lib() -> ctypes.CDLL:
         from ..build import kernels_lib_path, build_kernels
         checked = os.environ.get("PS_CHECKED", "0") == "1"
         p = kernels_lib_path(checked)
+        override = os.environ.get("PS_KERNELS_LIB")            # load this library file instead (A/B runs of two builds)
+        if override:
+            from pathlib import Path
+            p = Path(override)
         if not p.exists():
             try:
                 build_kernels(checked=checked)

@@ -180,6 +180,32 @@ class CudaOps(OpTrace):
             self.launches += 1
         return out
 
+    def can_fuse_argmax(self, W: LinearW, M: int) -> bool:
+        """True when ``linear_argmax`` can serve these rows: the streaming kernel would be chosen and holds them in one launch."""
+        if M < 1 or M > SMALL_M_MAX or self.exact_rows or W.K % 32 or self.select_linear(W, M) != "stream":
+            return False
+        if M >= 2 and W.rowmajor_bf16 is not None and self.use_tc_gemm:
+            return False
+        L = _lib.lib()
+        L.ps_linear_stream_max_rows.restype = ctypes.c_int
+        return M <= L.ps_linear_stream_max_rows(c_int(WFMT[W.fmt]), c_int(W.k_padded))
+
+    def linear_argmax(self, x: torch.Tensor, W: LinearW, *, norm_w=None, eps: float = 1e-6) -> torch.Tensor:
+        """Greedy sampling fused into the projection (lm_head of a decode step): int32 [M] indices of each row's largest
+        output, ties to the lower index; the logits are never written.  One launch."""
+        M = x.shape[0]
+        if W.tiled is None:
+            W.make_tiled()
+        if getattr(self, "_amax_state", None) is None:
+            self._amax_state = torch.zeros(10, dtype=torch.int64, device=self.device)       # 8 keys + control words, kept zero by the kernel
+        tokens = self.buf("sampled", max(M, 1), 1, torch.int32)
+        _lib.call("ps_linear_stream_argmax", c_int(WFMT[W.fmt]), ptr(x), c_int(M), c_int(W.N), c_int(W.k_padded), c_int(x.stride(0)),
+                  ptr(W.tiled), c_float(W.tensor_scale), c_int(PRO_RMSNORM if norm_w is not None else PRO_NONE), ptr(norm_w),
+                  c_float(eps), ptr(None), c_int(0), ptr(self._amax_state), ptr(tokens), ptr(self.status))
+        self.launches += 1
+        self.sel_counts["stream"] += 1
+        return tokens.view(-1)[:M]
+
     def linear_large(self, x: torch.Tensor, W: LinearW, *, name: str, norm_w, eps, residual, swiglu, out_f32, out):
         """Prefill-sized projection: (RMSNorm kernel) -> weight expansion to a bf16 scratch matrix -> tcgen05
         GEMM with the residual / SwiGLU / dtype epilogue fused."""
@@ -258,6 +284,8 @@ class CudaOps(OpTrace):
         """A kernel gave up on a bounded wait: stream-K flags may be left raised; clear them."""
         if self.bs_flags is not None:
             self.bs_flags.zero_()
+        if getattr(self, "_amax_state", None) is not None:
+            self._amax_state.zero_()              # a fused arg-max launch that did not finish leaves its keys and counter
         self.status.zero_()
 
     def bs_resident_ok(self, W: LinearW, M: int) -> bool:

@@ -12,6 +12,7 @@ roll the reservation back and poison the sequences when the device reported a fa
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
 
@@ -134,6 +135,8 @@ class Engine:
         self._h_pages = torch.zeros(64, max(64, self.state.max_blocks), dtype=torch.int32, pin_memory=(self.device.type == "cuda"))
         self._h_pages_next = 0
         self.graph_variants = True      # verification / tapped steps replay captured graphs too
+        # greedy, unmasked steps whose logits nobody asked for sample inside the lm_head kernel (PS_FUSED_ARGMAX=0: never)
+        self.fused_argmax = self.backend == "cuda" and os.environ.get("PS_FUSED_ARGMAX", "1") != "0"
         self.graph_refs: Dict[object, object] = {}
         self.steps = 0
         self.status_errors = 0
@@ -364,7 +367,7 @@ class Engine:
         try:
             toks, out, status = self._execute(rows, n_rows, n_out, bucket, b, tap_layers=tap_layers, gdn_log=gdn_log,
                                               gdn_to_alt=gdn_to_alt, mask=mask, mask_active=mask_active, sample=sample,
-                                              exact=exact, device_ids=device_ids, read_back=read_back)
+                                              exact=exact, device_ids=device_ids, read_back=read_back, want_logits=want_logits)
         except RuntimeError as e:
             self._raise_if_peer_lost(e)
             raise
@@ -377,16 +380,30 @@ class Engine:
                 s.position = r.pos_start + len(r.token_ids)
         return toks, out
 
-    def _run_graph(self, bucket: int, b: StepBatch, n_out: int, variant=None) -> StepOutput:
+    GREEDY_KEY_BIT = 1 << 48
+
+    @classmethod
+    def graph_key(cls, bucket: int, n_out: int, identity_out: bool, greedy: bool = False) -> int:
+        """Key of a plain captured step in ``graphs`` / ``graph_out`` / ``launches_per_graph`` (variants wrap it in a tuple)."""
+        return ((bucket * 4096 + n_out) * 2 + (1 if identity_out else 0)) | (cls.GREEDY_KEY_BIT if greedy else 0)
+
+    @classmethod
+    def graph_key_bucket(cls, key) -> int:
+        k = key[0] if isinstance(key, tuple) else key
+        return ((k & (cls.GREEDY_KEY_BIT - 1)) // 2) // 4096
+
+    def _run_graph(self, bucket: int, b: StepBatch, n_out: int, variant=None, greedy: bool = False) -> StepOutput:
         """``variant`` = (tap layers, GDN log dict or None, to_alt, exact): steps that tap hidden states or log the
         recurrent updates get graphs of their own (the tap and log tensors are fixed buffers, so the capture stays
         valid; Exact mode only changes which kernels the host picks, which the capture bakes in)."""
-        key = (bucket * 4096 + n_out) * 2 + (1 if b.identity_out else 0)
+        key = self.graph_key(bucket, n_out, b.identity_out, greedy)
         kw = {}
         if variant is not None:
             taps, log, to_alt, exact = variant
             key = (key, tuple(taps), id(log) if log is not None else 0, to_alt, exact)
             kw = dict(tap_layers=taps, gdn_log=log, gdn_to_alt=to_alt)
+        if greedy:
+            kw["greedy_only"] = True          # a graph of its own: the sampling kernel is not in it
         g = self.graphs.get(key)
         if g is None:
             self.ops.exact_rows = bool(variant[3]) if variant is not None else False
@@ -427,7 +444,7 @@ class Engine:
             bt[u[:, 0], u[:, 1]] = vals
 
     def run_rows(self, rows: Sequence[SeqRows], *, mask=None, mask_active=None, tap_layers: Sequence[int] = (),
-                 gdn_log=None, gdn_to_alt: bool = False, sample: bool = True):
+                 gdn_log=None, gdn_to_alt: bool = False, sample: bool = True, want_logits: bool = False):
         """Execute one step for sequences whose slots/pages are managed by the caller (the batcher).
         Returns (tokens, StepOutput, device_status)."""
         if self.tp is not None:
@@ -438,13 +455,14 @@ class Engine:
         b = self._batch(bucket)
         try:
             return self._execute(rows, n_rows, n_out, bucket, b, tap_layers=tap_layers, gdn_log=gdn_log,
-                                 gdn_to_alt=gdn_to_alt, mask=mask, mask_active=mask_active, sample=sample, exact=False)
+                                 gdn_to_alt=gdn_to_alt, mask=mask, mask_active=mask_active, sample=sample, exact=False,
+                                 want_logits=want_logits)
         except RuntimeError as e:
             self._raise_if_peer_lost(e)
             raise
 
     def _execute(self, rows, n_rows: int, n_out: int, bucket: int, b: StepBatch, *, tap_layers, gdn_log, gdn_to_alt,
-                 mask, mask_active, sample: bool, exact: bool, device_ids=None, read_back=None):
+                 mask, mask_active, sample: bool, exact: bool, device_ids=None, read_back=None, want_logits: bool = False):
         """Fill and upload the batch descriptor, run the forward (graph replay for plain decode-sized steps, eager
         otherwise), read back sampled ids and every device status word with one stream synchronisation.  Returns
         (tokens, StepOutput, status); a non-zero status has already been cleared on the device (together with any
@@ -452,6 +470,9 @@ class Engine:
         Status words: the state's own (bad page / slot indices), the op set's (bounded waits of the projection and
         all-reduce kernels; the tensor-parallel transport writes into the same word)."""
         b.fill(rows)
+        # every output row greedy, unmasked, and the logits of no interest: the lm_head samples in its own epilogue
+        greedy = (self.fused_argmax and sample and mask is None and not want_logits and not exact and n_out > 0
+                  and all(r.temperature <= 0.0 for r in rows))
         plain = not tap_layers and gdn_log is None and not gdn_to_alt and mask is None and sample and not exact
         decode_batch = bucket <= GRAPH_MAX_DECODE_ROWS and all(len(r.token_ids) == 1 for r in rows)
         use_graph = self.use_graphs and plain and (bucket <= GRAPH_MAX_ROWS or decode_batch)
@@ -467,13 +488,13 @@ class Engine:
             r0, t = device_ids
             b.ids[r0:r0 + t.numel()].copy_(t, non_blocking=True)
         if use_graph:
-            out = self._run_graph(bucket, b, n_out, variant)
+            out = self._run_graph(bucket, b, n_out, variant, greedy)
         else:
             self.ops.exact_rows = exact
             try:
                 out = self.runner.forward(b, bucket if self.backend == "cuda" else n_rows, n_out, tap_layers=tap_layers,
                                           gdn_log=gdn_log, gdn_to_alt=gdn_to_alt, mask=mask, mask_active=mask_active,
-                                          sample=sample)
+                                          sample=sample, **({"greedy_only": True} if greedy else {}))
             finally:
                 self.ops.exact_rows = False
         toks: List[int] = []

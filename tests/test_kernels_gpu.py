@@ -678,7 +678,7 @@ def test_decode_batches_beyond_eight_rows_replay_from_graphs():
             hist.append(list(toks))
         outs.append(hist)
         if graphs:
-            assert any((k // 2) // 4096 == 16 for k in eng.graphs), "the 12-row decode batch must have been captured (bucket 16)"
+            assert any(eng.graph_key_bucket(k) == 16 for k in eng.graphs), "the 12-row decode batch must have been captured (bucket 16)"
     assert outs[0] == outs[1]
 
 
@@ -771,3 +771,69 @@ def test_attention_mixed_step_long_rows_tiled_short_rows_per_row(kv_dtype):
         assert torch.equal(o_c[r], o_s[r])
     # prep + (dequantise +) tiled + split + merge for the mixed call, prep excluded: 3 or 4 launches, then 2 for the per-row run
     assert cu.launches - launches == 1 + (4 if kv_dtype != "bf16" else 3) + 2
+
+
+@pytest.mark.parametrize("preset", ["nvfp4", "mxfp8", "bf16"])
+def test_lm_head_fused_argmax_matches_projection_then_sample(preset):
+    """The streaming projection with greedy sampling in its epilogue against the same projection followed by the sampling
+    kernel: identical token ids for 1, 3 and 8 rows (same values, same tie rule), over a 27B-sized vocabulary, the state
+    re-armed between launches; a non-finite activation fails closed (-1 and the status word)."""
+    from phaseshift_b200.models.qwen35.weights import LinearW
+    from phaseshift_b200.quant import formats
+    cfg = tiny_config()
+    cu, _ = _ops(cfg, 16)
+    N, K = 151936, 1024
+    g = torch.Generator(device="cuda").manual_seed(5)
+    w = torch.randn(N, K, device="cuda", generator=g) * 0.02
+    W = LinearW(formats.quantize(w, preset)) if preset != "bf16" else LinearW(formats.quantize(w, "bf16"))
+    W.make_tiled()
+    norm_w = (torch.randn(K, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    for M in (1, 3, 8, 1):
+        x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+        if not cu.can_fuse_argmax(W, M):
+            assert preset == "bf16" and M > 1          # batched bf16 rows prefer the tensor-core GEMM of the row-major weights
+            continue
+        logits = cu.linear(x, W, name="t_logits", norm_w=norm_w, eps=1e-6, out_f32=True)
+        want = logits[:M].argmax(-1).to(torch.int32)
+        n0 = cu.launches
+        got = cu.linear_argmax(x, W, norm_w=norm_w, eps=1e-6).clone()
+        assert cu.launches - n0 == 1
+        torch.cuda.synchronize()
+        assert torch.equal(got, want), (M, got.tolist(), want.tolist())
+    assert int(cu.status[0]) == 0 and int(cu._amax_state.abs().sum()) == 0
+    # ties go to the lower index: two identical weight rows that win
+    w2 = w.clone(); w2[777] = w2[123] = 3.0 * x[0].float() / x[0].float().norm()
+    W2 = LinearW(formats.quantize(w2, "bf16")); W2.make_tiled()
+    got = cu.linear_argmax(x[:1], W2)
+    torch.cuda.synchronize()
+    assert int(got[0]) == 123
+    xb = x.clone(); xb[0, 5] = float("inf")
+    got = cu.linear_argmax(xb, W, norm_w=norm_w, eps=1e-6)
+    torch.cuda.synchronize()
+    assert int(got[0]) == -1 and int(cu.status[0]) != 0
+    cu.reset_after_error()
+
+
+def test_engine_greedy_steps_use_the_fused_argmax_and_match_the_sampling_kernel():
+    """Decode through the engine with the fused arg-max (its own CUDA graph, one launch fewer) and with it switched off:
+    the same tokens; a step that asks for logits keeps the sampling kernel."""
+    from phaseshift_b200.runtime.engine import Engine
+    cfg = Qwen35Config(vocab_size=4096, hidden_size=512, intermediate_size=1024, num_hidden_layers=4,
+                       num_attention_heads=4, num_key_value_heads=2, head_dim=128)
+    hf = random_hf_weights(cfg, seed=4, device="cuda")
+    ew = build_engine_weights(cfg, lambda n: hf[n], "nvfp4", "cuda", layout="both")
+    prompt = torch.randint(0, cfg.vocab_size, (40,), generator=torch.Generator().manual_seed(1)).tolist()
+    outs, launches = [], []
+    for fused in (True, False):
+        eng = Engine(ew, _dev(), StateConfig(max_slots=2, max_seq_len=128))
+        eng.fused_argmax = fused
+        outs.append(eng.generate(prompt, 24))
+        launches.append(max(eng.launches_per_graph.values()))
+        if fused:
+            s = eng.open_sequence()
+            _, o = eng.step([SeqRows(s.slot, 0, prompt, (len(prompt) - 1,))], [s], want_logits=True)
+            assert o.logits is not None
+            _, o = eng.step([SeqRows(s.slot, s.position, [1], (0,))], [s])
+            assert o.logits is None
+    assert outs[0] == outs[1]
+    assert launches[0] == launches[1] - 1
