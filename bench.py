@@ -355,7 +355,7 @@ def serving_block(ew, cfg, dev, tp, world, args):
             "p50_ttft_ms": round(statistics.median(first.values()), 1) if first else None,
             "prefill_tokens_computed": srv.stats["prefill_tokens"],
             "prefix_hit_tokens": srv.prefix.stats["restored_tokens"] if srv.prefix is not None else 0,
-            "steps": srv.stats["steps"], "failed_steps": srv.stats["failed_steps"],
+            "steps": srv.stats["steps"], "failed_steps": srv.stats["failed_steps"], "last_status": srv.stats.get("last_status", 0),
             "tp": dict(tp.stats, transport=tp.transport) if tp is not None else None, "clocks": clocks,
             "timing": "CUDA events around the whole run, max over ranks; TTFT on the host clock of rank 0"}
 

@@ -749,7 +749,9 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 const bool tp_on = g.tp.size > 1;
                 const bool staged = !RES && !g.out_f32 && !tp_on;       // bf16 output of many rows: staged through shared memory
                 bool released = false;
-                const bool want_ssq = g.ssq_out != nullptr && g.epilogue != EPI_SWIGLU;
+                // the staged epilogue never forms the per-row sums, so it must not publish any (what is in s_ssq then is whatever
+                // the finisher test left there)
+                const bool want_ssq = g.ssq_out != nullptr && g.epilogue != EPI_SWIGLU && !staged;
                 uint32_t tp_val = 0; size_t tp_par = 0;
                 if (tp_on) {
                     tp_val = g.tp.counter[t] + 1u;

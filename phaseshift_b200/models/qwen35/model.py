@@ -69,7 +69,8 @@ class Qwen35Runner:
         them for the next fused RMSNorm, else None."""
         ops, tp = self.ops, self.tp
         ssq_out, ssq = None, None
-        if self.use_ssq and rows <= 32 and getattr(W, "sf_atoms", None) is not None:
+        if self.use_ssq and rows <= 32 and getattr(W, "sf_atoms", None) is not None and \
+                (not hasattr(ops, "leaves_row_stats") or ops.leaves_row_stats(W, rows)):
             ssq_out = ops.ssq_buf(name, rows)
             ssq = (ssq_out, -(-W.N // 128))
         kw = {"prefetch": nxt} if self.use_ssq else {}

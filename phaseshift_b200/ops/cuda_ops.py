@@ -288,6 +288,10 @@ class CudaOps(OpTrace):
             self._amax_state.zero_()              # a fused arg-max launch that did not finish leaves its keys and counter
         self.status.zero_()
 
+    def leaves_row_stats(self, W: LinearW, M: int) -> bool:
+        """Whether a residual projection of `M` rows through `W` hands the next fused RMSNorm its rows' sums of squares."""
+        return M <= 32 and getattr(W, "sf_atoms", None) is not None and self.select_linear(W, M) == "tc" and self.bs_resident_ok(W, M)
+
     def bs_resident_ok(self, W: LinearW, M: int) -> bool:
         """Whether `M` rows of this projection fit the kernel's resident-activation path (pure host arithmetic)."""
         if M > self.BS_RESIDENT_MAX_ROWS:
@@ -340,8 +344,8 @@ class CudaOps(OpTrace):
                 raise ValueError("xn_out is produced by the resident path only")
             xq, sf, rs = self.act_quant(x, W, norm_w, eps)
         ssq_t, ssq_n = ssq_in if (ssq_in is not None and resident and norm_w is not None) else (None, 0)
-        if M > 32 or swiglu:
-            ssq_out = None
+        if M > 32 or swiglu or (not resident and not out_f32 and tp_combine is None):
+            ssq_out = None          # the streamed kernel's staged bf16 epilogue leaves no row statistics
         nxt = prefetch if (prefetch is not None and prefetch.sf_atoms is not None and self.bs_prefetch) else None
         err = _lib.lib().ps_gemm_bs
         err.restype = ctypes.c_int

@@ -120,6 +120,7 @@ class ServingEngine:
         self.stats["steps"] += 1
         if status != 0:
             self.stats["failed_steps"] += 1
+            self.stats["last_status"] = int(status)
             for (kind, rid, tok) in b.fail(plan, f"device status {status}"):
                 events.append(ServeEvent("error", rid, info={"message": f"device status {status}"}))
             eng.apply_block_updates(b.take_release_updates())

@@ -837,3 +837,44 @@ def test_engine_greedy_steps_use_the_fused_argmax_and_match_the_sampling_kernel(
             assert o.logits is None
     assert outs[0] == outs[1]
     assert launches[0] == launches[1] - 1
+
+
+def test_steps_of_17_to_32_rows_match_smaller_steps_on_27b_shaped_layers():
+    """27B-sized projections, 17..32 rows: the down projection no longer fits the resident-activation path and runs the
+    streamed kernel, whose staged epilogue leaves no row statistics for the next layer's fused RMSNorm; the next layer must
+    then compute them itself.  (It once consumed whatever the statistics buffer held: activations of every fourth layer off
+    by an order of magnitude, laundered into finite values by the activation quantiser.)  Checked on the hidden states
+    after the second and the sixth layer (MXFP8, whose rounding noise stays small over a few layers): prefilling 20 and 31
+    tokens in one step against two steps of at most 16 rows, and finite recurrent state after prefill steps and a batched
+    decode step of 20 sequences."""
+    from phaseshift_b200.models.qwen35.config import PRESETS
+    from phaseshift_b200.models.qwen35.weights import random_getter
+    from phaseshift_b200.runtime.engine import Engine
+    base = PRESETS["27b"]()
+    cfg = type(base)(**{**base.__dict__, "num_hidden_layers": 8, "layer_types": None, "vocab_size": 8192})
+    ew = build_engine_weights(cfg, random_getter(cfg, 0, _dev()), "mxfp8", _dev(), layout="both")
+    eng = Engine(ew, _dev(), StateConfig(max_slots=24, max_seq_len=128), use_graphs=False)
+    g = torch.Generator().manual_seed(3)
+    taps = [1, 5]
+
+    def rel(x, y):
+        return float((x.float() - y.float()).norm() / y.float().norm())
+    for n in (20, 31):
+        ids = torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist()
+        a, b = eng.open_sequence(), eng.open_sequence()
+        _, oa = eng.step([SeqRows(a.slot, 0, ids, (n - 1,))], [a], tap_layers=taps)
+        ta = {li: oa.taps[li][n - 1].clone() for li in taps}
+        eng.step([SeqRows(b.slot, 0, ids[:16], ())], [b])
+        _, ob = eng.step([SeqRows(b.slot, 16, ids[16:], (n - 17,))], [b], tap_layers=taps)
+        errs = {li: rel(ta[li], ob.taps[li][n - 17]) for li in taps}
+        assert errs[1] < 0.2 and errs[5] < 0.4, (n, errs)          # 0.08 / 0.15 measured; an order of magnitude with wrong statistics
+        for li in cfg.gdn_layers:
+            assert bool(torch.isfinite(eng.state.gdn[li].rec[a.slot]).all()), (n, li)
+        eng.close_sequence(a); eng.close_sequence(b)
+    # a batched decode step of 20 sequences (one row each) leaves every recurrent state finite and samples valid tokens
+    seqs = [eng.open_sequence() for _ in range(20)]
+    toks = [eng.prefill(s, torch.randint(0, cfg.vocab_size, (18 + i,), generator=g).tolist(), 64) for i, s in enumerate(seqs)]
+    toks, _ = eng.step([SeqRows(s.slot, s.position, [t], (0,)) for s, t in zip(seqs, toks)], seqs)
+    assert all(t >= 0 for t in toks)
+    for li in cfg.gdn_layers:
+        assert bool(torch.isfinite(eng.state.gdn[li].rec).all()) and bool(torch.isfinite(eng.state.gdn[li].conv.float()).all()), li
