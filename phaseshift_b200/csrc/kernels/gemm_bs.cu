@@ -428,7 +428,13 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (prof && threadIdx.x == 32) g.prof[3] = clock64();
         if (norm) {
             if (g.ssq_in != nullptr) {
-                if (qtid >= 0 && qtid < g.M) s_inv_rms[qtid] = rsqrtf(ssq_acc / (float)g.K + g.eps);
+                if (qtid >= 0 && qtid < g.M) {
+                    s_inv_rms[qtid] = rsqrtf(ssq_acc / (float)g.K + g.eps);
+                    // statistics handed over by another kernel: a sum of squares is never negative, so a negative value means
+                    // that its producer did not write it (the quantiser below would turn the damage into finite codes).
+                    // Non-finite sums are left alone: padding rows of a bucket legitimately carry garbage through the layers.
+                    if (ssq_acc < 0.f && blockIdx.x == 0) set_status(g.status, PS_DEV_NONFINITE);
+                }
             } else {
                 // No partial sums from a producer: sweep the rows here.  Thread t always adds elements t, t + kThreads, ...
                 // of a row and the warp sums are added in warp order, so a row's statistics do not depend on how
