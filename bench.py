@@ -49,10 +49,10 @@ def _parse():
                     help="workload preset: 2 = the 4B-shaped model in bf16, prefill 2048 + 512 decode steps (pick the KV "
                          "dtype with --kv-dtype); 3 = prefill 4096 + 1024 decode steps; 4 = 8k-token prompt, 256 speculative "
                          "tokens; 5 = the full serving load (256 requests)")
-    ap.add_argument("--serving-requests", type=int, default=24,
+    ap.add_argument("--serving-requests", type=int, default=48,
                     help="continuous-batching block: concurrent requests with prompts U(512, 8192), outputs U(128, 1024), "
                          "FP8 KV, half of them sharing a 1024-token prefix (0 = skip; the full load is 256)")
-    ap.add_argument("--serving-slots", type=int, default=12,
+    ap.add_argument("--serving-slots", type=int, default=32,
                     help="sequence slots of the serving block (fewer than the requests, so that later admissions can hit "
                          "the prefix cache the earlier ones filled)")
     ap.add_argument("--watchdog", type=int, default=1500,

@@ -73,6 +73,15 @@ __device__ __forceinline__ void tile_fetch(const PagedAttnArgs& a, TileRegs& r, 
     }
 }
 
+// Two E4M3 codes (low byte first) -> two bf16 values (exact: three mantissa bits): one hardware conversion to f16x2, then
+// through fp32.  NaN codes stay NaN.
+__device__ __forceinline__ uint32_t e4m3x2_to_bf16x2(uint16_t two) {
+    uint32_t h2;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(two));
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h2));
+    return f32x2_to_bf16x2_bits(f.x, f.y);
+}
+
 // Registers -> shared memory as bf16 (fp8 codes widen exactly).  K rows are padded by 8 elements.
 __device__ __forceinline__ void tile_store(const PagedAttnArgs& a, const TileRegs& r, __nv_bfloat16* ks,
                                            __nv_bfloat16* vs, float* kscale, float* vscale) {
@@ -97,11 +106,17 @@ __device__ __forceinline__ void tile_store(const PagedAttnArgs& a, const TileReg
                 const int t = p / ppr, c = p % ppr;
                 const uint32_t kw[4] = {r.k[i].x, r.k[i].y, r.k[i].z, r.k[i].w};
                 const uint32_t vw[4] = {r.v[i].x, r.v[i].y, r.v[i].z, r.v[i].w};
+                // two codes per conversion instruction, sixteen values leave as two 16-byte stores per matrix
+                uint32_t ko[8], vo[8];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    ks[t * kpitch + c * 16 + j] = f32_to_bf16(e4m3_to_f32((kw[j >> 2] >> ((j & 3) * 8)) & 0xff));
-                    vs[t * a.D + c * 16 + j] = f32_to_bf16(e4m3_to_f32((vw[j >> 2] >> ((j & 3) * 8)) & 0xff));
+                for (int j = 0; j < 8; ++j) {
+                    ko[j] = e4m3x2_to_bf16x2((uint16_t)(kw[j >> 1] >> ((j & 1) * 16)));
+                    vo[j] = e4m3x2_to_bf16x2((uint16_t)(vw[j >> 1] >> ((j & 1) * 16)));
                 }
+                uint4* kd = reinterpret_cast<uint4*>(ks + t * kpitch + c * 16);
+                uint4* vd = reinterpret_cast<uint4*>(vs + t * a.D + c * 16);
+                kd[0] = make_uint4(ko[0], ko[1], ko[2], ko[3]); kd[1] = make_uint4(ko[4], ko[5], ko[6], ko[7]);
+                vd[0] = make_uint4(vo[0], vo[1], vo[2], vo[3]); vd[1] = make_uint4(vo[4], vo[5], vo[6], vo[7]);
             }
         }
         if (threadIdx.x < kAttnTile) { kscale[threadIdx.x] = r.ks; vscale[threadIdx.x] = r.vs; }
@@ -177,14 +192,25 @@ __global__ void __launch_bounds__(kAttnThreads) paged_attn_split_kernel(const Pa
         __syncthreads();
         // PV: thread = output dim, all heads
         if (t < D) {
+            // tokens outermost, four at a time: a value of V is read once for all heads and the heads' probabilities come
+            // as one broadcast 16-byte load each (the loop used to issue two shared-memory loads per multiply-add, which
+            // bounded batched decode); per head the additions still run in token order, so the result is unchanged
 #pragma unroll
-            for (int g = 0; g < kAttnMaxG; ++g) {
-                if (g < G) {
-                    float s = acc[g] * alpha[g];
-                    const float* pg = ps_ + g * kAttnTile;
-#pragma unroll 8
-                    for (int j = 0; j < kAttnTile; ++j) s = fmaf(pg[j], bf16_to_f32(vs[j * D + t]), s);
-                    acc[g] = s;
+            for (int g = 0; g < kAttnMaxG; ++g)
+                if (g < G) acc[g] *= alpha[g];
+#pragma unroll 2
+            for (int j0 = 0; j0 < kAttnTile; j0 += 4) {
+                float vv[4];
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) vv[jj] = bf16_to_f32(vs[(j0 + jj) * D + t]);
+#pragma unroll
+                for (int g = 0; g < kAttnMaxG; ++g) {
+                    if (g < G) {
+                        const float4 pq = *reinterpret_cast<const float4*>(ps_ + g * kAttnTile + j0);
+                        float s = acc[g];
+                        s = fmaf(pq.x, vv[0], s); s = fmaf(pq.y, vv[1], s); s = fmaf(pq.z, vv[2], s); s = fmaf(pq.w, vv[3], s);
+                        acc[g] = s;
+                    }
                 }
             }
         }

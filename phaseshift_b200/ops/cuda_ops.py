@@ -411,12 +411,19 @@ class CudaOps(OpTrace):
             if not any_short:
                 return out
             row_pos = b.row_pos_short
+        # Split length: 64 tokens give a single row enough CTAs to fill the GPU; a batch of many rows already does, and its
+        # CTAs should rather amortise their set-up over a longer run of tokens (about four CTAs per SM in total).  Exact mode
+        # and small batches keep the fixed length, so a row's summation order does not depend on its neighbours there.
+        split_tokens = self.split_tokens
+        if rows > SMALL_M_MAX and not self.exact_rows:
+            want = max(1, (4 * 148) // (rows * hkv))
+            split_tokens = max(split_tokens, -(-(-(-max_visible // want)) // 32) * 32)
         pacc = self.buf("attn_part_acc", rows, hq * self.max_splits * D, torch.float32)
         pml = self.buf("attn_part_ml", rows, hq * self.max_splits * 2, torch.float32)
         _lib.call("ps_paged_attention", ptr(q), ptr(kv.k), ptr(kv.v), ptr(kv.k_scale), ptr(kv.v_scale),
                   ptr(st.block_table), c_int(st.max_blocks), c_int(st.sc.page_tokens), c_int(st.num_pages),
                   ptr(b.row_slot), ptr(row_pos), c_int(rows), c_int(hq), c_int(hkv), c_int(D),
-                  c_float(D ** -0.5), c_int(1 if st.kv_fp8 else 0), c_int(self.split_tokens),
+                  c_float(D ** -0.5), c_int(1 if st.kv_fp8 else 0), c_int(split_tokens),
                   c_int(self.max_splits), c_int(max_visible), ptr(pacc), ptr(pml), ptr(qkv), c_int(qkv.stride(0)),
                   c_int(2 * D), c_int(D), ptr(out), ptr(st.status))
         self.launches += 2
