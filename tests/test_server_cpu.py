@@ -22,11 +22,11 @@ def _free_port():
 def server():
     import uvicorn
     from phaseshift_b200.apps import server as srv
-    a = srv.build_parser().parse_args(["--random-model", "tiny", "--device", "cpu", "--max-seq-len", "512",
+    a = srv.build_parser().parse_args(["--random-model", "tiny", "--device", "cpu", "--max-seq-len", "1024",
                                        "--max-concurrent-requests", "2", "--prefix-cache-capacity-tokens", "2048",
                                        "--default-max-output-tokens", "24"])
     rt, tok, stop = srv.build_runtime(a)
-    app = srv.create_app(rt.serving, tok, "tiny-test", 24, stop, 512)
+    app = srv.create_app(rt.serving, tok, "tiny-test", 24, stop, 1024)
     port = _free_port()
     cfg = uvicorn.Config(app, host="127.0.0.1", port=port, log_level="error")
     us = uvicorn.Server(cfg)
@@ -99,3 +99,125 @@ def test_json_schema_response_format_is_enforced(server):
         "response_format": {"type": "json_schema", "json_schema": {"name": "r", "schema": schema}}}).json()
     txt = j["choices"][0]["message"]["content"]
     assert isinstance(json.loads(txt)["ok"], bool)       # a random model produced schema-valid JSON
+
+
+@pytest.mark.timeout(300)
+def test_sampling_parameters_seed_determinism_and_limits(server):
+    """Same seed -> same stochastic completion, another seed may differ; max_tokens and max_completion_tokens cap the output;
+    the usage block adds up."""
+    url, rt = server
+    body = {"messages": [{"role": "user", "content": "sample"}], "max_tokens": 12, "temperature": 0.9, "top_p": 0.95, "top_k": 50,
+            "seed": 7}
+    a = requests.post(url + "/v1/chat/completions", json=body).json()
+    b = requests.post(url + "/v1/chat/completions", json=body).json()
+    assert a["choices"][0]["message"]["content"] == b["choices"][0]["message"]["content"]
+    u = a["usage"]
+    assert u["total_tokens"] == u["prompt_tokens"] + u["completion_tokens"] and 1 <= u["completion_tokens"] <= 12
+    c = requests.post(url + "/v1/chat/completions", json=dict(body, max_completion_tokens=3)).json()
+    assert c["usage"]["completion_tokens"] <= 3
+    g1 = requests.post(url + "/v1/chat/completions", json=dict(body, temperature=0)).json()
+    g2 = requests.post(url + "/v1/chat/completions", json=dict(body, temperature=0, seed=99)).json()
+    assert g1["choices"][0]["message"]["content"] == g2["choices"][0]["message"]["content"]     # greedy ignores the seed
+
+
+@pytest.mark.timeout(300)
+def test_concurrent_requests_are_batched_and_all_answered(server):
+    """More simultaneous requests than sequence slots: the scheduler queues the rest; every request gets its own answer and
+    equal prompts get equal greedy answers."""
+    url, rt = server
+    out = [None] * 5
+
+    def go(i):
+        out[i] = requests.post(url + "/v1/chat/completions", json={
+            "messages": [{"role": "user", "content": "same prompt" if i % 2 == 0 else f"prompt number {i}"}], "max_tokens": 6}).json()
+    ths = [threading.Thread(target=go, args=(i,)) for i in range(5)]
+    for t in ths:
+        t.start()
+    for t in ths:
+        t.join(timeout=120)
+    assert all(o is not None and o["choices"][0]["finish_reason"] in ("length", "stop") for o in out)
+    assert out[0]["choices"][0]["message"]["content"] == out[2]["choices"][0]["message"]["content"] == out[4]["choices"][0]["message"]["content"]
+    assert len({o["id"] for o in out}) == 5
+
+
+@pytest.mark.timeout(300)
+def test_context_window_and_malformed_bodies(server):
+    url, rt = server
+    r = requests.post(url + "/v1/chat/completions", json={"messages": [{"role": "user", "content": "x" * 4000}]})
+    assert r.status_code == 400 and "context window" in r.json()["error"]["message"]
+    r = requests.post(url + "/v1/chat/completions", data="{not json", headers={"content-type": "application/json"})
+    assert r.status_code == 400 and r.json()["error"]["type"] == "invalid_request_error"
+    r = requests.post(url + "/v1/chat/completions", json={"messages": "hello"})
+    assert r.status_code == 400
+    r = requests.post(url + "/v1/chat/completions", json={"messages": [{"role": "wizard", "content": "x"}]})
+    assert r.status_code == 400
+    # a prompt that nearly fills the window: the completion budget is clamped to what is left, not rejected
+    r = requests.post(url + "/v1/chat/completions", json={"messages": [{"role": "user", "content": "y" * 900}], "max_tokens": 500})
+    assert r.status_code == 200 and r.json()["usage"]["total_tokens"] <= 1024
+    assert requests.get(url + "/health").json() == {"status": "ok"}        # the engine thread survived all of it
+
+
+@pytest.mark.timeout(300)
+def test_tool_calls_forced_by_tool_choice(server):
+    """tool_choice = required / a named function constrains the output to a tool call whose arguments satisfy the schema;
+    tool_choice = none never returns one."""
+    url, rt = server
+    if rt.serving.constraints is None:
+        pytest.skip("grammar engine not available")
+    tools = [{"type": "function", "function": {"name": "set_flag", "description": "sets a flag", "parameters": {
+        "type": "object", "properties": {"on": {"type": "boolean"}}, "required": ["on"], "additionalProperties": False}}},
+        {"type": "function", "function": {"name": "other", "parameters": {"type": "object", "properties": {}, "additionalProperties": False}}}]
+    body = {"messages": [{"role": "user", "content": "call it"}], "tools": tools, "max_tokens": 300}
+    j = requests.post(url + "/v1/chat/completions", json=dict(body, tool_choice={"type": "function", "function": {"name": "set_flag"}})).json()
+    ch = j["choices"][0]
+    assert ch["finish_reason"] == "tool_calls" and ch["message"]["tool_calls"][0]["function"]["name"] == "set_flag"
+    assert isinstance(json.loads(ch["message"]["tool_calls"][0]["function"]["arguments"])["on"], bool)
+    assert ch["message"]["tool_calls"][0]["type"] == "function" and ch["message"]["tool_calls"][0]["id"]
+    j = requests.post(url + "/v1/chat/completions", json=dict(body, tool_choice="required")).json()
+    assert j["choices"][0]["finish_reason"] == "tool_calls"
+    assert j["choices"][0]["message"]["tool_calls"][0]["function"]["name"] in ("set_flag", "other")
+    j = requests.post(url + "/v1/chat/completions", json=dict(body, tool_choice="none", max_tokens=8)).json()
+    assert "tool_calls" not in j["choices"][0]["message"] and j["choices"][0]["finish_reason"] in ("length", "stop")
+
+
+@pytest.mark.timeout(300)
+def test_streaming_chunks_reassemble_to_the_non_streamed_answer(server):
+    url, rt = server
+    body = {"messages": [{"role": "user", "content": "stream me"}], "max_tokens": 10}
+    whole = requests.post(url + "/v1/chat/completions", json=body).json()["choices"][0]["message"]["content"]
+    with requests.post(url + "/v1/chat/completions", json=dict(body, stream=True), stream=True) as r:
+        assert r.headers["content-type"].startswith("text/event-stream")
+        chunks = [json.loads(l.decode()[6:]) for l in r.iter_lines() if l and l != b"data: [DONE]"]
+    text = "".join(c["choices"][0]["delta"].get("content", "") for c in chunks)
+    assert text == whole
+    assert len({c["id"] for c in chunks}) == 1 and all(c["object"] == "chat.completion.chunk" for c in chunks)
+    assert chunks[-1]["choices"][0]["finish_reason"] in ("length", "stop") and all(c["choices"][0]["finish_reason"] is None for c in chunks[:-1])
+
+
+@pytest.mark.timeout(300)
+def test_client_disconnect_cancels_the_request_and_frees_its_slot(server):
+    """A streaming client that goes away: the engine cancels the request; afterwards every slot serves again."""
+    url, rt = server
+    with requests.post(url + "/v1/chat/completions", json={"messages": [{"role": "user", "content": "long"}], "max_tokens": 400,
+                                                           "stream": True}, stream=True) as r:
+        it = r.iter_lines()
+        next(it)                      # the role chunk arrived: generation is under way
+    time.sleep(0.5)
+    ok = [requests.post(url + "/v1/chat/completions", json={"messages": [{"role": "user", "content": f"after {i}"}], "max_tokens": 4})
+          for i in range(3)]
+    assert all(o.status_code == 200 for o in ok)
+    deadline = time.time() + 20
+    while time.time() < deadline and not rt.serving.idle():
+        time.sleep(0.1)
+    assert rt.serving.idle()
+
+
+@pytest.mark.timeout(300)
+def test_responses_endpoint_with_instructions_and_message_list(server):
+    url, rt = server
+    r = requests.post(url + "/v1/responses", json={"instructions": "be brief", "input": [{"role": "user", "content": "hello"}],
+                                                   "max_output_tokens": 5})
+    j = r.json()
+    assert r.status_code == 200 and j["object"] == "response" and j["status"] == "completed"
+    assert j["usage"]["output_tokens"] <= 5 and j["usage"]["input_tokens"] > 0 and j["id"].startswith("resp_")
+    assert requests.post(url + "/v1/responses", json={"input": [{"role": "user", "content": [{"type": "image_url"}]}]}).status_code == 400
