@@ -23,6 +23,7 @@ def _ops(grid_override=0):
     from phaseshift_b200.ops.cuda_ops import CudaOps
     ops = CudaOps(tiny_config(), torch.device("cuda:0"))
     ops.bs_grid_override = grid_override
+    ops.BS_RESIDENT_MAX_ROWS = 32          # the kernel's own limit (the engine switches to the streamed path above 8 rows)
     return ops
 
 
