@@ -523,6 +523,10 @@ class Engine:
                 out.read_back = read_back.tolist()
         self.steps += 1
         if getattr(self.ops, "checked", False):
+            # checked mode also looks at the step's hidden rows: the block-scaled projections quantise their inputs, which
+            # turns a NaN from further up into finite codes, so a fault can pass the logits unseen on the tensor-core path
+            if out.hidden is not None and n_out and not bool(torch.isfinite(out.hidden[:n_out].float()).all()):
+                raise RuntimeError("checked build: non-finite hidden states at the output rows of this step")
             bad = self.ops.check_canaries()
             if bad:
                 raise RuntimeError("checked build: workspace guard bytes overwritten around " + ", ".join(sorted(set(bad))))
