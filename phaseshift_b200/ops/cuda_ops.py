@@ -48,8 +48,12 @@ class CudaOps(OpTrace):
         half = cfg.rotary_dim // 2
         inv = cfg.rope_theta ** (-np.arange(half, dtype=np.float64) * 2.0 / cfg.rotary_dim)
         self.inv_freq = torch.from_numpy(inv).to(device)
-        # split length is fixed per engine (never per batch) so attention results are batch-invariant
-        self.split_tokens = attn_split_tokens
+        # the split length is fixed per engine for steps of up to 8 rows and for Exact mode, so attention results there do not
+        # depend on the batch; larger Fast-mode batches lengthen it (see paged_attention).  PS_ATTN_SPLIT_TOKENS overrides the
+        # base length (a multiple of 32).
+        self.split_tokens = int(os.environ.get("PS_ATTN_SPLIT_TOKENS", attn_split_tokens))
+        if self.split_tokens < 32 or self.split_tokens % 32:
+            raise ValueError("the attention split length must be a positive multiple of 32")
         while -(-(max_seq_len + 1) // self.split_tokens) > 512:
             self.split_tokens *= 2
         self.max_splits = attn_max_splits or -(-(max_seq_len + 1) // self.split_tokens)
