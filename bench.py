@@ -407,7 +407,7 @@ def main():
     torch.cuda.synchronize()
     build_s = time.time() - t0
     K, W = args.steps, args.warmup
-    max_seq = args.context + 2 * (K + W) + 64
+    max_seq = args.context + max(2 * (K + W), (args.dflash2_tokens + 32) if args.dflash2 else 0) + 64
     eng = Engine(ew, dev, StateConfig(max_slots=1, max_seq_len=max_seq, page_tokens=16, kv_dtype=args.kv_dtype,
                                       conv_ring=16, spec_rows=8), tp=tp)
     g = torch.Generator().manual_seed(1234)
