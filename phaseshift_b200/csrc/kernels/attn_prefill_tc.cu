@@ -52,6 +52,9 @@ struct AttnTcArgs {
     __nv_bfloat16* out;          // [rows, Hq * D]
     uint32_t* status;
     long long budget;
+    // decode / verify variant (DEC): split-KV partials in the layout of the per-row kernel's merge pass
+    int split_tokens; int max_splits; int dec_max_rows;
+    float* part_acc; float* part_ml;
     long long* prof;             // optional cycle stamps of CTA (0, 0, 0): [32 tiles][16], softmax slots 0-7, issuer slots 8-12
 };
 
@@ -99,10 +102,15 @@ __device__ __forceinline__ float sigmoid_fast(float x) {
     return fmaf(0.5f, t, 0.5f);
 }
 
-// grid = (q tiles of 128 rows, Hq, n_seqs); the heaviest (latest) query tiles are scheduled first.
+// Prefill (DEC = false): grid = (q tiles of 128 rows, Hq, n_seqs); the heaviest (latest) query tiles are scheduled first.
+// Decode / verify (DEC = true): grid = (KV splits, Hkv, n_seqs).  A CTA serves one sequence with at most 16 rows in the step
+// and one KV head: tile row 8 r + g is query head g of that KV head for the sequence's row r (grouped-query packing: the G <= 8
+// heads that share the KV head ride in one MMA tile, so K and V are read once for all of them), over the tokens of its
+// split; it leaves unnormalised partial outputs and (maximum, sum) pairs for the merge pass of paged_attention.cu.
+template <bool DEC>
 __global__ void __launch_bounds__(kTcThreads, 1)
-attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                       const __grid_constant__ CUtensorMap map_v, const AttnTcArgs a) {
+attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+               const __grid_constant__ CUtensorMap map_v, const AttnTcArgs a) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // Q, two K and two V stages, two P buffers: 224 KB, which with the static part below is the whole 227 KB of the SM;
     // the swizzled tiles need the 1024-byte alignment that the declaration asks for (checked, not assumed)
@@ -122,14 +130,28 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
     const int* sd = a.seqs + 4 * blockIdx.z;
     const int row_start = sd[0], n_rows = sd[1], slot = sd[2], pos_start = sd[3];
-    const int tile = (int)gridDim.x - 1 - (int)blockIdx.x;
-    const int r_begin = tile * kTcRows;
-    if (r_begin >= n_rows || slot < 0 || n_rows <= a.min_rows) return;
-    const int nq = min(kTcRows, n_rows - r_begin);
-    const int h = blockIdx.y, kvh = h / (a.Hq / a.Hkv);
-    const int pos_q0 = pos_start + r_begin;
-    const int kv_end = pos_q0 + nq;
-    const int T = (kv_end + kTcTok - 1) / kTcTok;
+    const int G = a.Hq / a.Hkv;
+    int r_begin, nq, h, kvh, pos_q0, kv_end, t_first, T;
+    if constexpr (DEC) {
+        if (slot < 0 || n_rows <= 0 || n_rows > a.dec_max_rows) return;
+        r_begin = 0; nq = 8 * n_rows; kvh = blockIdx.y; h = kvh * G;
+        pos_q0 = pos_start; kv_end = pos_start + n_rows;
+        const int tps = a.split_tokens / kTcTok;                         // tiles per split
+        t_first = (int)blockIdx.x * tps;
+        const int t_end = min((kv_end + kTcTok - 1) / kTcTok, t_first + tps);
+        if (t_first >= t_end) return;
+        T = t_end - t_first;
+    } else {
+        const int tile = (int)gridDim.x - 1 - (int)blockIdx.x;
+        r_begin = tile * kTcRows;
+        if (r_begin >= n_rows || slot < 0 || n_rows <= a.min_rows) return;
+        nq = min(kTcRows, n_rows - r_begin);
+        h = blockIdx.y; kvh = h / G;
+        pos_q0 = pos_start + r_begin;
+        kv_end = pos_q0 + nq;
+        t_first = 0;
+        T = (kv_end + kTcTok - 1) / kTcTok;
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool cta_stamp = a.prof != nullptr && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
     if (cta_stamp) a.prof[15] = clock64();
@@ -160,9 +182,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         // more than a thousand cycles, and the stage's consumer is waiting for them.
         const bool isK = warp == 8;
         if (isK) {
-            if (lane == 0) tc::mbar_expect_tx(&q_full, kTcQBytes);
-            __syncwarp();
-            if (lane < 4) tc::tma_load_2d(sQ + lane * (kTcRows * 128), &map_q, h * kTcD + lane * 64, row_start + r_begin, &q_full);
+            if constexpr (DEC) {
+                // one 8-row box per (row of the sequence, 64-column group): the G heads of this KV head are consecutive rows
+                // of the [rows * Hq, D] view of q; tile rows 8 r + g with g >= G hold other heads' values and are never used
+                if (lane == 0) tc::mbar_expect_tx(&q_full, (uint32_t)n_rows * 4u * 1024u);
+                __syncwarp();
+                for (int i = lane; i < 4 * n_rows; i += 32) {
+                    const int r = i >> 2, c4 = i & 3;
+                    tc::tma_load_2d(sQ + c4 * (kTcRows * 128) + (8 * r) * 128, &map_q, c4 * 64, (row_start + r) * a.Hq + h, &q_full);
+                }
+            } else {
+                if (lane == 0) tc::mbar_expect_tx(&q_full, kTcQBytes);
+                __syncwarp();
+                if (lane < 4) tc::tma_load_2d(sQ + lane * (kTcRows * 128), &map_q, h * kTcD + lane * 64, row_start + r_begin, &q_full);
+            }
             if (lane == 0) q_issued = 1;
         }
         const int* bt = a.block_table + (size_t)slot * a.max_blocks;
@@ -176,7 +209,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         for (int t = 0; t < T; ++t) {
             const int b = t & 1;
             int page = 0;
-            const int blk = t * ppt + pg;
+            const int blk = (t_first + t) * ppt + pg;
             if (active && blk * pt < kv_end) {
                 page = bt[blk];
                 if (page < 0 || page >= a.num_pages) { s_bad = 1; page = 0; }
@@ -248,18 +281,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int quad = warp & 3, half = warp >> 2;
         const int row = quad * 32 + lane;
         const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
-        const int rp = pos_q0 + row;
+        const int rp = DEC ? pos_q0 + (row >> 3) : pos_q0 + row;     // position of this thread's query row
         const float sc = a.scale_log2;
         float m_ref = 0.f, l_run = 0.f;
         bool ok = true;
         // the epilogue reads this tile's gate values (one 512-byte run per row): ask for them now, so that they come from
         // L2 then
-        if (a.gate != nullptr && half == 0 && row < nq)
+        if (!DEC && a.gate != nullptr && half == 0 && row < nq)
             tc::bulk_prefetch_l2(a.gate + (size_t)(row_start + r_begin + row) * a.ld_gate + (size_t)h * a.gate_head_stride + a.gate_offset, kTcD * 2);
         for (int t = 0; t < T; ++t) {
             const int b = t & 1;
             const uint32_t ph = (uint32_t)(t >> 1) & 1u;
-            const int t0 = t * kTcTok + half * 32;                    // first token of this thread's columns
+            const int tt = t_first + t;                               // tile index within the sequence
+            const int t0 = tt * kTcTok + half * 32;                   // first token of this thread's columns
             const bool stamp = a.prof != nullptr && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && t < 32;
             if (stamp) a.prof[t * 16 + 0] = clock64();
             ok = __all_sync(0xffffffffu, tc::mbar_wait_abortable(&s_full[b], ph, a.budget, &s_abort));
@@ -273,8 +307,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             tc::tmem_ld_32x32(tmem + lane_base + b * kTcTok + (half ^ 1) * 32, so);
             tc::tmem_ld_wait();
             if (stamp) a.prof[t * 16 + 2] = clock64();
-            if (t * kTcTok + kTcTok - 1 > pos_q0) {                   // some row of the tile does not see every token
-                const int to = t * kTcTok + (half ^ 1) * 32;
+            if (tt * kTcTok + kTcTok - 1 > pos_q0) {                  // some row of the tile does not see every token
+                const int to = tt * kTcTok + (half ^ 1) * 32;
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     if (t0 + j > rp) sr[j] = 0xff800000u;             // -inf
@@ -287,7 +321,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             float mx = fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3])) * sc;     // scale > 0, so the maximum commutes with it
             if (stamp) a.prof[t * 16 + 3] = clock64();
             float alpha = 1.f;
-            if (t == 0) m_ref = mx;                                   // token 0 is visible to every row
+            if (t == 0) m_ref = mx == -INFINITY ? 0.f : mx;           // (a row that sees nothing here keeps a finite reference)
             else if (mx > m_ref + 8.f) { alpha = ex2_approx(m_ref - mx); m_ref = mx; }
             const bool rescale = __any_sync(0xffffffffu, alpha != 1.f);
             float sq[4] = {0.f, 0.f, 0.f, 0.f};
@@ -309,12 +343,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
             for (int c = 0; c < 4; ++c)
                 *reinterpret_cast<uint4*>(prow + (((half * 4 + c) ^ (row & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-            if (t == T - 1 && kv_end < (t + 1) * kTcTok) {
+            if (t == T - 1 && kv_end < (tt + 1) * kTcTok) {
                 // token rows of the last V tile beyond the sequence's end: zero them (whole 128-byte rows, so the swizzle
                 // does not matter)
                 ok = __all_sync(0xffffffffu, tc::mbar_wait_abortable(&v_full[b], ph, a.budget, &s_abort));
                 if (!ok) break;
-                const int jz = kv_end - t * kTcTok;
+                const int jz = kv_end - tt * kTcTok;
                 unsigned char* vs = sV + b * kTcKvStage;
                 for (int i = (int)threadIdx.x; i < (kTcTok - jz) * 32; i += 2 * kTcRows) {
                     const int r = jz + (i >> 5), cb = (i & 31) >> 3, c = i & 7;
@@ -350,6 +384,33 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         s_l[half][row] = l_run;
         asm volatile("bar.sync 1, 256;" ::: "memory");               // the eight softmax warps only; every one of them gets here
         if (cta_stamp) a.prof[3 * 16 + 15] = clock64();
+        if constexpr (DEC) {
+            // partial result of this split for query row (r, g): unnormalised output, reference maximum (natural-log units, as
+            // the merge pass expects) and sum
+            const int r = row >> 3, g = row & 7;
+            const bool mine = row < nq && g < G;
+            if (ok && quad * 32 < nq) {                              // warp-uniform: the tensor-memory loads are collective
+                tc::fence_after_sync();
+                const size_t idx = ((size_t)(row_start + (mine ? r : 0)) * a.Hq + h + (mine ? g : 0)) * a.max_splits + blockIdx.x;
+                float* dst = a.part_acc + idx * kTcD;
+#pragma unroll 1
+                for (int c0 = half * (kTcD / 2); c0 < (half + 1) * (kTcD / 2); c0 += 32) {
+                    uint32_t rr[32];
+                    tc::tmem_ld_32x32(tmem_o + lane_base + c0, rr);
+                    tc::tmem_ld_wait();
+                    if (mine) {
+#pragma unroll
+                        for (int jj = 0; jj < 32; jj += 4)
+                            *reinterpret_cast<uint4*>(dst + c0 + jj) = make_uint4(rr[jj], rr[jj + 1], rr[jj + 2], rr[jj + 3]);
+                    }
+                }
+                if (mine && half == 0) {
+                    const float l = l_run + s_l[1][row];
+                    a.part_ml[idx * 2] = l > 0.f ? m_ref * 0.6931471805599453f : -3.0e38f;
+                    a.part_ml[idx * 2 + 1] = l;
+                }
+            }
+        } else {
         if (ok) {
             tc::fence_after_sync();
             const float l = l_run + s_l[half ^ 1][row];
@@ -407,6 +468,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 }
             }
         }
+        }   // prefill epilogue
     }
     if (cta_stamp) a.prof[6 * 16 + 15] = clock64();
     tc::fence_before_sync();
@@ -572,18 +634,60 @@ int launch_attn_prefill_tc(const void* q, int q_rows, const void* k_pool, const 
     a.Hq = Hq; a.Hkv = Hkv; a.scale_log2 = sm_scale * 1.4426950408889634f; a.min_rows = min_rows;
     a.gate = (const __nv_bfloat16*)gate; a.ld_gate = ld_gate; a.gate_head_stride = gate_head_stride; a.gate_offset = gate_offset;
     a.out = (__nv_bfloat16*)out; a.status = (uint32_t*)status; a.budget = g_ps_wait_budget_cycles; a.prof = g_attn_tc_prof;
+    a.split_tokens = 0; a.max_splits = 0; a.dec_max_rows = 0; a.part_acc = nullptr; a.part_ml = nullptr;
     const size_t smem = (size_t)kTcSmem;
     static bool set = false;
     if (!set) {
-        cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(attn_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         set = true;
     }
     const int tiles = (max_seq_rows + kTcRows - 1) / kTcRows;
-    attn_prefill_tc_kernel<<<dim3(tiles, Hq, n_seqs), kTcThreads, smem, stream>>>(mq, mk, mv, a);
+    attn_tc_kernel<false><<<dim3(tiles, Hq, n_seqs), kTcThreads, smem, stream>>>(mq, mk, mv, a);
     return PS_LAUNCH_CHECK();
 }
 
 }  // namespace ps
+
+// Decode / verify attention on the tensor cores (bf16 pools, head dim 256, pages of 16 / 32 / 64 tokens, at most 8 query
+// heads per KV head): split-KV partials for every sequence of the step with at most `dec_max_rows` (<= 16) rows, in the
+// layout of ps_paged_attention's merge pass (`part_acc` [rows, Hq, max_splits, D] fp32, `part_ml` [rows, Hq, max_splits, 2]);
+// the caller runs ps_paged_attention_merge afterwards.  `split_tokens` is a multiple of 64, `q` is [q_rows, Hq, D] bf16.
+// Reference: src/phaseshift/models/qwen35/kernels/optimized/attention/paged_decode.hip (split-KV decode); the grouped-query
+// packing onto one MMA tile has no counterpart there.
+PS_API int ps_attn_decode_tc(const void* q, int q_rows, const void* k_pool, const void* v_pool, const void* block_table,
+                             int max_blocks, int page_tokens, int num_pages, const void* seqs, int n_seqs, int dec_max_rows,
+                             int Hq, int Hkv, int D, float sm_scale, int split_tokens, int max_splits, int max_visible,
+                             void* part_acc, void* part_ml, void* status, cudaStream_t stream) {
+    using namespace ps;
+    if (D != kTcD || (page_tokens != 16 && page_tokens != 32 && page_tokens != 64) || Hkv <= 0 || (Hq % Hkv) || Hq / Hkv > 8 ||
+        dec_max_rows < 1 || dec_max_rows > 16 || split_tokens < kTcTok || (split_tokens % kTcTok) || n_seqs <= 0 ||
+        (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)part_acc) % 16))
+        return (int)cudaErrorInvalidValue;
+    int n_splits = (max_visible + split_tokens - 1) / split_tokens;
+    if (n_splits < 1) n_splits = 1;
+    if (n_splits > max_splits) return (int)cudaErrorInvalidValue;
+    CUtensorMap mq, mk, mv;
+    int err = attn_map_2d(&mq, q, (uint64_t)q_rows * Hq, kTcD, kTcD, 8);                 // the [rows * Hq, D] view, 8-row boxes
+    if (err) return err;
+    const uint64_t pool_rows = (uint64_t)num_pages * Hkv * page_tokens;
+    if ((err = attn_map_2d(&mk, k_pool, pool_rows, kTcD, kTcD, (uint32_t)page_tokens))) return err;
+    if ((err = attn_map_2d(&mv, v_pool, pool_rows, kTcD, kTcD, (uint32_t)page_tokens))) return err;
+    AttnTcArgs a;
+    a.block_table = (const int*)block_table; a.max_blocks = max_blocks; a.num_pages = num_pages; a.page_tokens = page_tokens; a.seqs = (const int*)seqs;
+    a.Hq = Hq; a.Hkv = Hkv; a.scale_log2 = sm_scale * 1.4426950408889634f; a.min_rows = 0;
+    a.gate = nullptr; a.ld_gate = 0; a.gate_head_stride = 0; a.gate_offset = 0; a.out = nullptr;
+    a.status = (uint32_t*)status; a.budget = g_ps_wait_budget_cycles; a.prof = nullptr;
+    a.split_tokens = split_tokens; a.max_splits = max_splits; a.dec_max_rows = dec_max_rows;
+    a.part_acc = (float*)part_acc; a.part_ml = (float*)part_ml;
+    const size_t smem = (size_t)kTcSmem;
+    static bool set = false;
+    if (!set) {
+        cudaFuncSetAttribute(attn_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        set = true;
+    }
+    attn_tc_kernel<true><<<dim3(n_splits, Hkv, n_seqs), kTcThreads, smem, stream>>>(mq, mk, mv, a);
+    return PS_LAUNCH_CHECK();
+}
 
 // Timing aid: a device buffer of 32 x 16 int64 that CTA (0, 0, 0) of later launches fills with cycle stamps of its softmax
 // thread 0 (slots 0-7: tile start, scores ready, scores loaded, row maximum exchanged, probabilities computed, stored,

@@ -312,6 +312,21 @@ PS_API int ps_paged_attention(const void* q, const void* k_pool, const void* v_p
     return launch_pdl(paged_attn_merge_kernel, dim3(Hq, rows), dim3(D), 0, stream, m);
 }
 
+// The merge pass alone: for partials produced by another split-KV kernel (attn_prefill_tc.cu's decode variant) in the same
+// layout.  Same arguments as the tail of ps_paged_attention.
+PS_API int ps_paged_attention_merge(const void* part_acc, const void* part_ml, const void* row_pos, int rows, int Hq, int D,
+                                    int split_tokens, int max_splits, const void* gate, int ld_gate, int gate_head_stride,
+                                    int gate_offset, void* out, cudaStream_t stream) {
+    using namespace ps;
+    if (rows <= 0 || Hq <= 0 || D <= 0 || D > kAttnMaxD || max_splits > kAttnMaxSplits) return (int)cudaErrorInvalidValue;
+    AttnMergeArgs m;
+    m.part_acc = (const float*)part_acc; m.part_ml = (const float*)part_ml; m.row_pos = (const int*)row_pos; m.rows = rows; m.Hq = Hq; m.D = D;
+    m.split_tokens = split_tokens; m.max_splits = max_splits; m.gate = (const __nv_bfloat16*)gate;
+    m.ld_gate = ld_gate; m.gate_head_stride = gate_head_stride; m.gate_offset = gate_offset;
+    m.out = (__nv_bfloat16*)out;
+    return launch_pdl(paged_attn_merge_kernel, dim3(Hq, rows), dim3(D), 0, stream, m);
+}
+
 // ------------------------------------------------------------------------------------------------
 // Allocation-free variant: identical kernels, partial results in static device storage (ps_noalloc.h).
 namespace ps {

@@ -60,6 +60,7 @@ class CudaOps(OpTrace):
         self.launches = 0
         self.use_tc_gemm = True
         self.exact_rows = False     # verify steps: keep every projection on the batch-invariant small-M kernel
+        self.attn_decode_tc = os.environ.get("PS_ATTN_DECODE", "tc") != "legacy"
         self.wscratch = None
         self.status = torch.zeros(1, dtype=torch.int32, device=device)   # kernels' own bounded-wait status word
         # block-scaled tensor-core projections: stream-K partials + flags (flags must read 0 between launches)
@@ -428,6 +429,23 @@ class CudaOps(OpTrace):
             split_tokens = max(split_tokens, -(-(-(-max_visible // want)) // 32) * 32)
         pacc = self.buf("attn_part_acc", rows, hq * self.max_splits * D, torch.float32)
         pml = self.buf("attn_part_ml", rows, hq * self.max_splits * 2, torch.float32)
+        # Decode / verify rows on the tensor cores: bf16 pages, head dim 256, every sequence handled here has at most 16 rows
+        # (the query heads that share a KV head are packed into one MMA tile).  A row's result does not depend on the other
+        # rows of its tile (every tile row has its own scores, reference maximum and accumulator lane), so Exact mode -- whose
+        # verified rows must reproduce single-row decoding bit for bit -- uses it as well.  FP8 pages and other shapes keep the
+        # per-row kernel.  PS_ATTN_DECODE=legacy switches it off.
+        if (self.attn_decode_tc and D == 256 and not st.kv_fp8 and st.sc.page_tokens in (16, 32, 64) and hq // hkv <= 8
+                and (b.graph_static or row_pos is b.row_pos_short or all(len(sq.token_ids) <= 16 for sq in b.seqs))):
+            st_tok = -(-split_tokens // 64) * 64
+            n_seqs = b.max_seqs if b.graph_static else b.n_seqs
+            _lib.call("ps_attn_decode_tc", ptr(q), c_int(q.shape[0]), ptr(kv.k), ptr(kv.v), ptr(st.block_table),
+                      c_int(st.max_blocks), c_int(st.sc.page_tokens), c_int(st.num_pages), ptr(b.seq_desc), c_int(n_seqs),
+                      c_int(16), c_int(hq), c_int(hkv), c_int(D), c_float(D ** -0.5), c_int(st_tok), c_int(self.max_splits),
+                      c_int(max_visible), ptr(pacc), ptr(pml), ptr(st.status))
+            _lib.call("ps_paged_attention_merge", ptr(pacc), ptr(pml), ptr(row_pos), c_int(rows), c_int(hq), c_int(D),
+                      c_int(st_tok), c_int(self.max_splits), ptr(qkv), c_int(qkv.stride(0)), c_int(2 * D), c_int(D), ptr(out))
+            self.launches += 2
+            return out
         _lib.call("ps_paged_attention", ptr(q), ptr(kv.k), ptr(kv.v), ptr(kv.k_scale), ptr(kv.v_scale),
                   ptr(st.block_table), c_int(st.max_blocks), c_int(st.sc.page_tokens), c_int(st.num_pages),
                   ptr(b.row_slot), ptr(row_pos), c_int(rows), c_int(hq), c_int(hkv), c_int(D),

@@ -767,8 +767,11 @@ def test_attention_mixed_step_long_rows_tiled_short_rows_per_row(kv_dtype):
     assert n == 152 and int(st_c.status[0]) == 0
     assert _rel_err(o_c[:n], o_r[:n]) < tol
     assert _rel_err(o_c[:n].float(), o_s[:n].float()) < (1.5e-2 if kv_dtype == "bf16" else 3e-2)
-    for r in (0, 151):                                   # the decode rows came from the per-row kernel: same bits
-        assert torch.equal(o_c[r], o_s[r])
+    for r in (0, 151):                                   # FP8 pages: the decode rows came from the per-row kernel both times
+        if kv_dtype == "bf16":
+            assert _rel_err(o_c[r].float(), o_s[r].float()) < 1.5e-2        # tensor-core decode kernel against the per-row one
+        else:
+            assert torch.equal(o_c[r], o_s[r])
     # prep + (dequantise +) tiled + split + merge for the mixed call, prep excluded: 3 or 4 launches, then 2 for the per-row run
     assert cu.launches - launches == 1 + (4 if kv_dtype != "bf16" else 3) + 2
 
