@@ -881,3 +881,56 @@ def test_steps_of_17_to_32_rows_match_smaller_steps_on_27b_shaped_layers():
     assert all(t >= 0 for t in toks)
     for li in cfg.gdn_layers:
         assert bool(torch.isfinite(eng.state.gdn[li].rec).all()) and bool(torch.isfinite(eng.state.gdn[li].conv.float()).all()), li
+
+
+def test_tensor_core_decode_attention_rows_do_not_depend_on_their_tile_neighbours():
+    """bf16 pages, head dim 256, six query heads per KV head: a block of 8 new rows of one sequence (speculative
+    verification) through the grouped-query tensor-core decode kernel against the fp32 reference, and bit for bit against
+    the same rows computed one per step (what Exact-mode verification relies on); also two sequences with different
+    contexts in one step."""
+    cfg = Qwen35Config(vocab_size=1024, hidden_size=512, intermediate_size=512, num_hidden_layers=4,
+                       num_attention_heads=12, num_key_value_heads=2, head_dim=256)
+    cu, ref = _ops(cfg, 512)
+    assert cu.attn_decode_tc
+    sc = StateConfig(max_slots=2, max_seq_len=512, page_tokens=16, kv_dtype="bf16", kv_capacity_tokens=2048)
+    st_c = ModelState(cfg, sc, _dev(), torch.bfloat16)
+    st_r = ModelState(cfg, sc, _dev(), torch.float32)
+    nb = st_c.max_blocks
+    for st in (st_c, st_r):
+        perm = torch.randperm(st.num_pages - 1, generator=torch.Generator().manual_seed(3))[:2 * nb] + 1
+        st.block_table[0, :nb] = perm[:nb].int().to(_dev())
+        st.block_table[1, :nb] = perm[nb:2 * nb].int().to(_dev())
+    li = cfg.attn_layers[0]
+    hf = random_hf_weights(cfg, seed=3, device="cuda")
+    aw = build_engine_weights(cfg, lambda n: hf[n], "bf16", "cuda").layers[li].mixer
+    Hq, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    g = torch.Generator(device="cuda").manual_seed(21)
+    width = 2 * Hq * D + 2 * Hkv * D
+
+    def run(seqs, qkv):
+        n = qkv.shape[0]
+        b = StepBatch(16, 2, _dev())
+        b.fill(seqs); b.upload()
+        q_c = cu.attn_prep(qkv, aw, Hq, Hkv, b, st_c.kv[li], st_c)
+        q_r = ref.attn_prep(qkv.float(), aw, Hq, Hkv, b, st_r.kv[li], st_r)
+        o_c = cu.paged_attention(q_c, qkv, Hq, Hkv, b, st_c.kv[li], st_c, b.max_visible)[:n].clone()
+        o_r = ref.paged_attention(q_r, qkv.float(), Hq, Hkv, b, st_r.kv[li], st_r, b.max_visible)[:n]
+        return o_c, o_r
+    # contexts of 203 and 70 tokens through the tiled prefill kernel
+    for slot, n in ((0, 203), (1, 70)):
+        run_pre = torch.randn(n, width, device="cuda", generator=g).to(torch.bfloat16)
+        b = StepBatch(512, 2, _dev())
+        b.fill([SeqRows(slot, 0, [0] * n, ())]); b.upload()
+        cu.attn_prep(run_pre, aw, Hq, Hkv, b, st_c.kv[li], st_c)
+        ref.attn_prep(run_pre.float(), aw, Hq, Hkv, b, st_r.kv[li], st_r)
+    qkv8 = torch.randn(8, width, device="cuda", generator=g).to(torch.bfloat16)
+    o8, r8 = run([SeqRows(0, 203, [0] * 8, ())], qkv8)
+    torch.cuda.synchronize()
+    assert int(st_c.status[0]) == 0 and _rel_err(o8, r8) < 2e-2
+    for i in range(8):
+        o1, _ = run([SeqRows(0, 203 + i, [0], ())], qkv8[i:i + 1])
+        assert torch.equal(o1[0], o8[i]), i
+    # two sequences, one row each, in one step
+    qkv2 = torch.randn(2, width, device="cuda", generator=g).to(torch.bfloat16)
+    o2, r2 = run([SeqRows(1, 70, [0], ()), SeqRows(0, 211, [0], ())], qkv2)
+    assert _rel_err(o2, r2) < 2e-2 and int(st_c.status[0]) == 0
