@@ -323,7 +323,9 @@ class CudaOps(OpTrace):
         from ..quant.act_quant import ATOMS_PER_PANEL, PANEL_K
         M, K = x.shape
         P = -(-K // PANEL_K[W.fmt])
-        codes = self.buf(f"bs_xq{K}", M, P * 128, torch.uint8)
+        # one buffer per (K, format): a preset mixes formats at the same K, and a shared name would re-allocate the
+        # buffer at every change of format (inside a graph capture too)
+        codes = self.buf(f"bs_xq{K}_{W.fmt}", M, P * 128, torch.uint8)
         mblk = -(-M // 256) * 2
         sf = self.buf(f"bs_xsf{K}_{W.fmt}", mblk, P * ATOMS_PER_PANEL[W.fmt] * 512, torch.uint8)
         rs = self.buf("bs_xrs", M, 1, torch.float32)

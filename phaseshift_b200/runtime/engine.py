@@ -106,9 +106,7 @@ class Engine:
             from ..core.arena import ArenaSet
             self.arenas = ArenaSet(int(arena_gib * (1 << 30)), self.device.index or 0)
         self.state = ModelState(self.cfg, state_cfg, self.device, self.ops.act_dtype, geo, arenas=self.arenas)
-        if getattr(self.ops, "checked", False):
-            from ..ops import _lib as _klib
-            _klib.set_limits(state_cfg.max_slots, 1 << 20, self.state.status)
+        self._arm_checked_limits()
         self.runner = Qwen35Runner(weights, self.state, self.ops, tp)
         self.tp = tp
         if tp is not None and hasattr(self.ops, "status"):
@@ -392,6 +390,14 @@ class Engine:
         k = key[0] if isinstance(key, tuple) else key
         return ((k & (cls.GREEDY_KEY_BIT - 1)) // 2) // 4096
 
+    def _arm_checked_limits(self) -> None:
+        """Checked library: the descriptor limits and the status word its assertions report to live in one device symbol per
+        kernel file, shared by every engine of the process, so each engine registers its own before it launches (a second
+        engine with fewer slots would otherwise make the first one's kernels skip its higher slots, silently for it)."""
+        if getattr(self.ops, "checked", False):
+            from ..ops import _lib as _klib
+            _klib.set_limits(self.sc.max_slots, 1 << 20, self.state.status)
+
     def _run_graph(self, bucket: int, b: StepBatch, n_out: int, variant=None, greedy: bool = False) -> StepOutput:
         """``variant`` = (tap layers, GDN log dict or None, to_alt, exact): steps that tap hidden states or log the
         recurrent updates get graphs of their own (the tap and log tensors are fixed buffers, so the capture stays
@@ -469,6 +475,7 @@ class Engine:
         stream-K flags a kernel that gave up may have left raised) and it is the caller's job to poison sequences.
         Status words: the state's own (bad page / slot indices), the op set's (bounded waits of the projection and
         all-reduce kernels; the tensor-parallel transport writes into the same word)."""
+        self._arm_checked_limits()
         b.fill(rows)
         # every output row greedy, unmasked, and the logits of no interest: the lm_head samples in its own epilogue
         greedy = (self.fused_argmax and sample and mask is None and not want_logits and not exact and n_out > 0
