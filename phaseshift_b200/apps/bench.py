@@ -22,7 +22,7 @@ FUSED_INTO = {"l2-normalize": "gdn-recurrence",      # q/k L2 normalisation happ
 def _model_args(p):
     p.add_argument("--model-dir"); p.add_argument("--random-model", default=None, choices=["tiny", "4b", "27b"])
     p.add_argument("--preset", default=None); p.add_argument("--device", default=None)
-    p.add_argument("--kv-cache-dtype", default="bf16", choices=["bf16", "fp8_e4m3"])
+    p.add_argument("--kv-cache-dtype", default="bf16", choices=["bf16", "fp8_e4m3", "nvfp4"])
     p.add_argument("--runs", type=int, default=3); p.add_argument("--warmup", type=int, default=1); p.add_argument("--output")
     p.add_argument("--tp", type=int, default=1, choices=[1, 2, 4, 8], help="tensor-parallel ranks, one process per GPU")
 
@@ -58,7 +58,7 @@ def build_parser() -> argparse.ArgumentParser:
         p = sub.add_parser(name); p.add_argument("--rows", type=int, default=1); p.add_argument("--context", type=int, default=4096)
         p.add_argument("--page-tokens", type=int, default=16)
         p.add_argument("--samples", type=int, default=20); p.add_argument("--model", default="27b", choices=["tiny", "4b", "27b"])
-        p.add_argument("--kv-cache-dtype", default="bf16", choices=["bf16", "fp8_e4m3"]); p.add_argument("--variant", default="optimized", choices=["optimized"])
+        p.add_argument("--kv-cache-dtype", default="bf16", choices=["bf16", "fp8_e4m3", "nvfp4"]); p.add_argument("--variant", default="optimized", choices=["optimized"])
     kl = sub.add_parser("kld", help="KL divergence of a quantised preset against the bf16 model of the same random weights"); _model_args(kl)
     kl.add_argument("--tokens", type=int, default=512); kl.add_argument("--streams", type=int, default=2)
     kl.add_argument("--layout", default="both", choices=["both", "tc", "stream"])

@@ -35,7 +35,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--prefix-cache-max-entries", type=int, default=16)
     ap.add_argument("--constraint-tokenizer-info")
     ap.add_argument("--device", default=None)
-    ap.add_argument("--kv-cache-dtype", default="bf16", choices=["bf16", "fp8_e4m3", "psq4", "psq8"])
+    ap.add_argument("--kv-cache-dtype", default="bf16", choices=["bf16", "fp8_e4m3", "nvfp4", "psq4", "psq8"],
+                    help="storage of the paged key/value cache; psq4 / psq8 are the upstream names of the 4-bit (nvfp4) and 8-bit (fp8_e4m3) block formats")
     ap.add_argument("--decode-backend", default="host", choices=["host", "gpu-mcu"])
     ap.add_argument("--verify-weights", type=int, default=0, choices=[0, 1])
     ap.add_argument("--dump-logits")
@@ -62,8 +63,6 @@ def validate_args(a) -> Optional[str]:
         return "--model-dir is required"
     if a.decode_backend == "gpu-mcu":
         return "--decode-backend gpu-mcu is not implemented"
-    if a.kv_cache_dtype in ("psq4", "psq8"):
-        return f"--kv-cache-dtype {a.kv_cache_dtype} is not available on this backend (use bf16 or fp8_e4m3)"
     if a.max_new_tokens < 0 or a.max_seq_len <= 0 or a.page_tokens <= 0:
         return "token counts must be positive"
     if a.temperature < 0 or not (0 < a.top_p <= 1) or a.top_k < 0:
@@ -108,6 +107,8 @@ class ComputeRuntime:
                                      keep_canonical=self.device.type != "cuda", **tp_kw)
         self.cfg = ew.cfg
         spec = bool(a.dflash2_model_dir)
+        from ..runtime.state import KV_DTYPE_ALIASES
+        a.kv_cache_dtype = KV_DTYPE_ALIASES.get(a.kv_cache_dtype, a.kv_cache_dtype)
         sc = StateConfig(max_slots=a.max_concurrent_requests, max_seq_len=a.max_seq_len, page_tokens=a.page_tokens,
                          kv_capacity_tokens=a.kv_cache_capacity_tokens, kv_dtype=a.kv_cache_dtype,
                          conv_ring=32 if spec else 4, spec_rows=a.dflash2_drafts + 1 if spec else 0)

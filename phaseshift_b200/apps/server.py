@@ -36,7 +36,7 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--preset", default=None); ap.add_argument("--host", default="127.0.0.1")
     ap.add_argument("--port", type=int, default=8000); ap.add_argument("--max-seq-len", type=int, default=32768)
     ap.add_argument("--arena-gib", type=float, default=0); ap.add_argument("--device", default=None)
-    ap.add_argument("--kv-cache-dtype", default="bf16", choices=["bf16", "fp8_e4m3"])
+    ap.add_argument("--kv-cache-dtype", default="bf16", choices=["bf16", "fp8_e4m3", "nvfp4", "psq4", "psq8"])
     ap.add_argument("--page-tokens", type=int, default=16); ap.add_argument("--max-concurrent-requests", type=int, default=4)
     ap.add_argument("--kv-cache-capacity-tokens", type=int, default=0)
     ap.add_argument("--prefix-cache-capacity-tokens", type=int, default=16384)

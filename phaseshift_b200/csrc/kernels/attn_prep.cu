@@ -1,5 +1,5 @@
 // Fused attention prepare: per-head RMSNorm(1+w) on q and k, partial NeoX RoPE, and the paged
-// KV append (BF16 or FP8-E4M3 with one f32 scale per token x kv-head), in one launch.
+// KV append (BF16, FP8-E4M3 with one f32 scale per token x kv-head, or NVFP4 rows as laid out in kv_fp4.cuh), in one launch.
 //
 // The reference runs these as separate dispatches (split, two per-group RMSNorms, RoPE pair
 // kernel with an f64 inv_freq table, kv_append; src/phaseshift/models/qwen35/kernels/optimized/
@@ -10,9 +10,10 @@
 //   qkv      [rows, ld_qkv] bf16: per q-head h: [2hD, 2hD+D) = q, [2hD+D, 2hD+2D) = gate;
 //            then k heads at q_span + hk*D, then v heads at q_span + Hkv*D + hk*D.
 //   q_out    [rows, Hq, D] bf16
-//   k/v pool [num_pages, Hkv, page_tokens, D] (bf16 or e4m3), scales [num_pages, Hkv, page_tokens] f32
+//   k/v pool [num_pages, Hkv, page_tokens, D] (bf16 or e4m3) or [num_pages, Hkv, page_tokens, kv_fp4_row_bytes(D)] bytes
+//            (NVFP4, kv_fp8 == 2), scales [num_pages, Hkv, page_tokens] f32
 //   block_table [num_slots, max_blocks] int32; row_slot/row_pos give each row's sequence slot and position.
-#include "ps_common.cuh"
+#include "kv_fp4.cuh"
 
 namespace ps {
 
@@ -87,6 +88,19 @@ __global__ void attn_prep_kernel(const AttnPrepArgs a) {
     if (!a.kv_fp8) {
         __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(pool) + tok * D;
         dst[t] = f32_to_bf16(y0); dst[t + D / 2] = f32_to_bf16(y1);
+    } else if (a.kv_fp8 == 2) {
+        // NVFP4 row: token scale from the row maximum, then one thread per block of 16 values
+        const float ts = kv_fp4_token_scale(block_max(fmaxf(fabsf(y0), fabsf(y1)), red));
+        vals[t] = y0; vals[t + D / 2] = y1;          // each thread rewrites the two entries it alone has read
+        __syncthreads();
+        uint8_t* dst = reinterpret_cast<uint8_t*>(pool) + tok * kv_fp4_row_bytes(D);
+        if (t < D / 16) {
+            uint2 codes; uint8_t sf;
+            kv_fp4_quant16(vals + 16 * t, ts, codes, sf);
+            *reinterpret_cast<uint2*>(dst + 8 * t) = codes;
+            dst[D / 2 + t] = sf;
+        }
+        if (t == 0) (kind == 1 ? a.k_scale : a.v_scale)[tok] = ts;
     } else {
         const float amax = block_max(fmaxf(fabsf(y0), fabsf(y1)), red);
         const float sc = amax > 0.f ? amax / 448.f : 1.f;

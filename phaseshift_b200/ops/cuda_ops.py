@@ -387,7 +387,7 @@ class CudaOps(OpTrace):
                   c_int(cfg.rotary_dim), ptr(aw.q_norm), ptr(aw.k_norm), c_float(cfg.rms_norm_eps),
                   ptr(self.inv_freq), ptr(b.row_slot), ptr(b.row_pos), ptr(q), ptr(kv.k), ptr(kv.v),
                   ptr(kv.k_scale), ptr(kv.v_scale), ptr(st.block_table), c_int(st.max_blocks),
-                  c_int(st.sc.page_tokens), c_int(st.num_pages), c_int(1 if st.kv_fp8 else 0), ptr(st.status))
+                  c_int(st.sc.page_tokens), c_int(st.num_pages), c_int(st.kv_fmt), ptr(st.status))
         self.launches += 1
         return q
 
@@ -410,13 +410,23 @@ class CudaOps(OpTrace):
             any_short = T == StepBatch.SHORT_SEQ_ROWS and any(len(sq.token_ids) <= T for sq in b.seqs)
             min_rows = T if any_short else 0
             deq = (None, None, 0, None, None)
-            if st.kv_fp8 and D == 256 and pt in (16, 32, 64):
-                pages = sum(-(-(sq.pos_start + len(sq.token_ids)) // pt) for sq in b.seqs if len(sq.token_ids) > min_rows)
-                deq = self._attn_scratch(pages, hkv, pt, D, b.max_seqs, st.max_blocks)
-            _lib.call("ps_attn_prefill", ptr(q), ptr(kv.k), ptr(kv.v), ptr(kv.k_scale), ptr(kv.v_scale),
-                      ptr(st.block_table), c_int(st.max_blocks), c_int(pt), c_int(st.num_pages),
-                      ptr(b.seq_desc), c_int(b.n_seqs), c_int(rows), c_int(q.shape[0]), c_int(min_rows), c_int(hq), c_int(hkv), c_int(D),
-                      c_float(D ** -0.5), c_int(1 if st.kv_fp8 else 0), ptr(qkv), c_int(qkv.stride(0)), c_int(2 * D), c_int(D),
+            src = (kv.k, kv.v, kv.k_scale, kv.v_scale, st.block_table, st.num_pages, b.seq_desc, 1 if st.kv_fp8 else 0)
+            n_long_pages = lambda: sum(-(-(sq.pos_start + len(sq.token_ids)) // pt) for sq in b.seqs if len(sq.token_ids) > min_rows)
+            if st.kv_fmt == 2:
+                # NVFP4 pages: the step's pages are widened into the bf16 scratch pool, which then IS the pool of the tiled
+                # kernels (with its own block table and sequence descriptors), whatever the head size
+                dk, dv, n_pg, dbt, dsq = self._attn_scratch(n_long_pages(), hkv, pt, D, b.max_seqs, st.max_blocks)
+                _lib.call("ps_kv_fp4_dequant", ptr(kv.k), ptr(kv.v), ptr(kv.k_scale), ptr(kv.v_scale), ptr(st.block_table),
+                          c_int(st.max_blocks), c_int(st.num_pages), c_int(pt), c_int(hkv), c_int(D), ptr(b.seq_desc),
+                          c_int(b.n_seqs), c_int(min_rows), ptr(dk), ptr(dv), c_int(n_pg), ptr(dbt), ptr(dsq), ptr(st.status))
+                self.launches += 1
+                src = (dk, dv, None, None, dbt, dk.shape[0], dsq, 0)
+            elif st.kv_fp8 and D == 256 and pt in (16, 32, 64):
+                deq = self._attn_scratch(n_long_pages(), hkv, pt, D, b.max_seqs, st.max_blocks)
+            _lib.call("ps_attn_prefill", ptr(q), ptr(src[0]), ptr(src[1]), ptr(src[2]), ptr(src[3]),
+                      ptr(src[4]), c_int(st.max_blocks), c_int(pt), c_int(src[5]),
+                      ptr(src[6]), c_int(b.n_seqs), c_int(rows), c_int(q.shape[0]), c_int(min_rows), c_int(hq), c_int(hkv), c_int(D),
+                      c_float(D ** -0.5), c_int(src[7]), ptr(qkv), c_int(qkv.stride(0)), c_int(2 * D), c_int(D),
                       ptr(deq[0]), ptr(deq[1]), c_int(deq[2]), ptr(deq[3]), ptr(deq[4]), ptr(out), ptr(st.status))
             self.launches += 2 if deq[0] is not None else 1
             if not any_short:
@@ -436,7 +446,7 @@ class CudaOps(OpTrace):
         # rows of its tile (every tile row has its own scores, reference maximum and accumulator lane), so Exact mode -- whose
         # verified rows must reproduce single-row decoding bit for bit -- uses it as well.  FP8 pages and other shapes keep the
         # per-row kernel.  PS_ATTN_DECODE=legacy switches it off.
-        if (self.attn_decode_tc and D == 256 and not st.kv_fp8 and st.sc.page_tokens in (16, 32, 64) and hq // hkv <= 8
+        if (self.attn_decode_tc and D == 256 and st.kv_fmt == 0 and st.sc.page_tokens in (16, 32, 64) and hq // hkv <= 8
                 and (b.graph_static or row_pos is b.row_pos_short or all(len(sq.token_ids) <= 16 for sq in b.seqs))):
             st_tok = -(-split_tokens // 64) * 64
             n_seqs = b.max_seqs if b.graph_static else b.n_seqs
@@ -446,6 +456,15 @@ class CudaOps(OpTrace):
                       c_int(max_visible), ptr(pacc), ptr(pml), ptr(st.status))
             _lib.call("ps_paged_attention_merge", ptr(pacc), ptr(pml), ptr(row_pos), c_int(rows), c_int(hq), c_int(D),
                       c_int(st_tok), c_int(self.max_splits), ptr(qkv), c_int(qkv.stride(0)), c_int(2 * D), c_int(D), ptr(out))
+            self.launches += 2
+            return out
+        if st.kv_fmt == 2:
+            _lib.call("ps_paged_attention_fp4", ptr(q), ptr(kv.k), ptr(kv.v), ptr(kv.k_scale), ptr(kv.v_scale),
+                      ptr(st.block_table), c_int(st.max_blocks), c_int(st.sc.page_tokens), c_int(st.num_pages),
+                      ptr(b.row_slot), ptr(row_pos), c_int(rows), c_int(hq), c_int(hkv), c_int(D), c_float(D ** -0.5),
+                      c_int(split_tokens), c_int(self.max_splits), c_int(max_visible), ptr(pacc), ptr(pml), ptr(st.status))
+            _lib.call("ps_paged_attention_merge", ptr(pacc), ptr(pml), ptr(row_pos), c_int(rows), c_int(hq), c_int(D),
+                      c_int(split_tokens), c_int(self.max_splits), ptr(qkv), c_int(qkv.stride(0)), c_int(2 * D), c_int(D), ptr(out))
             self.launches += 2
             return out
         _lib.call("ps_paged_attention", ptr(q), ptr(kv.k), ptr(kv.v), ptr(kv.k_scale), ptr(kv.v_scale),

@@ -25,7 +25,19 @@ import torch
 from ..models.qwen35.config import Qwen35Config
 from ..models.qwen35.weights import TpGeometry
 
-KV_DTYPES = ("bf16", "fp8_e4m3")
+KV_DTYPES = ("bf16", "fp8_e4m3", "nvfp4")
+# names accepted on the command line for the reference's block-coded caches (src/apps/compute/main.hip:47-81): its 4-bit
+# format is served by the NVFP4 pools, its 8-bit format by the FP8 pools (same E4M3 codes, one scale per row instead of
+# one per 32 values)
+KV_DTYPE_ALIASES = {"psq4": "nvfp4", "psq8": "fp8_e4m3"}
+KV_FMT = {"bf16": 0, "fp8_e4m3": 1, "nvfp4": 2}
+
+
+def kv_row_bytes(kv_dtype: str, head_dim: int) -> int:
+    """Bytes of one cached row (a token of one KV head) in the pools of `kv_dtype`, without the fp32 row scale."""
+    if kv_dtype == "nvfp4":
+        return ((head_dim // 2 + head_dim // 16) + 15) & ~15          # codes, block scales, padded to 16 bytes
+    return head_dim * (1 if kv_dtype == "fp8_e4m3" else 2)
 
 
 @dataclass
@@ -82,11 +94,19 @@ class ModelState:
         D, pt = cfg.head_dim, sc.page_tokens
         fp8 = sc.kv_dtype == "fp8_e4m3"
         self.kv_fp8 = fp8
+        self.kv_fmt = KV_FMT[sc.kv_dtype]            # 0 bf16, 1 FP8-E4M3 + row scale, 2 NVFP4 rows + row scale
+        Drow = D                                     # last extent of the pools
         if act_dtype == torch.float32:
             kvt = torch.float32          # CPU reference keeps full precision
             fp8 = self.kv_fp8 = False
+            self.kv_fmt = 0
+        elif self.kv_fmt == 2:
+            if D % 32 or D > 256:
+                raise ValueError("NVFP4 key/value pages need a head size that is a multiple of 32, at most 256")
+            kvt, Drow = torch.uint8, kv_row_bytes("nvfp4", D)
         else:
             kvt = torch.uint8 if fp8 else torch.bfloat16
+        scaled = self.kv_fmt != 0                    # pools with an fp32 scale per (page, head, token)
         self.kv: List[Optional[KVLayer]] = []
         self.gdn: List[Optional[GdnLayerState]] = []
         Dk, Dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
@@ -94,7 +114,7 @@ class ModelState:
         esz = lambda dt: torch.empty(0, dtype=dt).element_size()
         n_attn = sum(1 for lt in cfg.layer_types if lt == 1)
         n_gdn = len(cfg.layer_types) - n_attn
-        kv_need = n_attn * (2 * self.num_pages * self.hkv * pt * D * esz(kvt) + (2 * self.num_pages * self.hkv * pt * 4 if fp8 else 0) + 1024)
+        kv_need = n_attn * (2 * self.num_pages * self.hkv * pt * Drow * esz(kvt) + (2 * self.num_pages * self.hkv * pt * 4 if scaled else 0) + 1024)
         st_need = n_gdn * (sc.max_slots * self.hv * (sc.conv_ring * (2 * Dk + Dv) * esz(act_dtype)
                                                       + Dk * Dv * 4 * (2 if sc.spec_rows > 0 else 1)) + 1024)
         kv_arena = arenas.get("kv", kv_need + (2 << 20)) if arenas is not None and n_attn else None
@@ -107,10 +127,10 @@ class ModelState:
             return t.fill_(fill) if fill else t.zero_()
         for lt in cfg.layer_types:
             if lt == 1:
-                k = pool(kv_arena, (self.num_pages, self.hkv, pt, D), kvt)
-                v = pool(kv_arena, (self.num_pages, self.hkv, pt, D), kvt)
+                k = pool(kv_arena, (self.num_pages, self.hkv, pt, Drow), kvt)
+                v = pool(kv_arena, (self.num_pages, self.hkv, pt, Drow), kvt)
                 ks = vs = None
-                if fp8:
+                if scaled:
                     ks = pool(kv_arena, (self.num_pages, self.hkv, pt), torch.float32, 1)
                     vs = pool(kv_arena, (self.num_pages, self.hkv, pt), torch.float32, 1)
                 self.kv.append(KVLayer(k, v, ks, vs))

@@ -28,7 +28,6 @@ def model_dir(tmp_path_factory):
 
 def test_invalid_flags_exit_2_before_load():
     assert compute.main(["--random-model", "tiny", "--decode-backend", "gpu-mcu"]) == 2
-    assert compute.main(["--random-model", "tiny", "--kv-cache-dtype", "psq4"]) == 2
     assert compute.main(["--max-new-tokens", "4"]) == 2
     assert compute.main(["--random-model", "tiny", "--dflash2-ngram-tail", "2"]) == 2
     with pytest.raises(SystemExit):
@@ -44,6 +43,10 @@ def test_single_shot_contract(model_dir, tmp_path, capsys):
     out = dict(l.split("=", 1) for l in capsys.readouterr().out.strip().splitlines())
     assert out["PROMPT_TOKENS"] == "12" and out["GENERATED_TOKENS"] == "6" and out["KV_CACHE_DTYPE"] == "bf16"
     assert [int(t) for t in out["GENERATED_IDS"].split(",")] == reference_greedy(cfg, hf, ids, 6)
+    # the upstream names of the block-coded caches select the 4-bit / 8-bit pools (the fp32 CPU oracle keeps full precision)
+    assert compute.main(["--model-dir", str(d), "--input-ids-file", str(f), "--max-new-tokens", "2", "--device", "cpu",
+                         "--kv-cache-dtype", "psq4"]) == 0
+    assert "KV_CACHE_DTYPE=nvfp4" in capsys.readouterr().out
     lg = tmp_path / "l.bin"
     assert compute.main(["--model-dir", str(d), "--input-ids-file", str(f), "--max-new-tokens", "3", "--device", "cpu",
                          "--dump-logits", str(lg)]) == 0
