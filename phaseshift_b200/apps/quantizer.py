@@ -26,12 +26,19 @@ def build_parser() -> argparse.ArgumentParser:
     k.add_argument("--report"); k.add_argument("--window", type=int, default=512); k.add_argument("--stride", type=int, default=512)
     k.add_argument("--max-eval-tokens", type=int, default=0); k.add_argument("--self", dest="self_check", action="store_true")
     k.add_argument("--device", default=None)
-    k.add_argument("--baseline-cache", default=None, help="directory that keeps the baseline model's logits between runs")
+    k.add_argument("--baseline-cache", "--cache-dir", dest="baseline_cache", default=None,
+                   help="directory that keeps the baseline model's logits between runs")
+    k.add_argument("--keep-logit-cache", action="store_true", help="accepted for compatibility: the logits cached in --cache-dir are always kept")
+    k.add_argument("--keep-shadow", action="store_true", help="accepted for compatibility: the bundle is evaluated directly, no shadow model is written")
+    k.add_argument("--batch-positions", type=int, default=512, help="rows per evaluation step")
+    k.add_argument("--arena-gib", type=float, default=0, help="accepted for compatibility: the evaluation engines size their own pools")
     i = sub.add_parser("imatrix", help="collect per-channel activation importance")
     i.add_argument("--input", help="unused alias of --model-dir"); i.add_argument("--model-dir", required=True)
     i.add_argument("--tokens", required=True); i.add_argument("--output", required=True)
     i.add_argument("--window", type=int, default=512); i.add_argument("--stride", type=int, default=512)
     i.add_argument("--max-calibration-tokens", type=int, default=0); i.add_argument("--device", default=None)
+    i.add_argument("--flush-windows", type=int, default=16, help="rewrite the output file every N windows (0: only at the end)")
+    i.add_argument("--arena-gib", type=float, default=0, help="accepted for compatibility")
     p = sub.add_parser("ppl", help="teacher-forced perplexity")
     p.add_argument("--model-dir", required=True); p.add_argument("--tokens", required=True)
     p.add_argument("--max-tokens", type=int, default=2048); p.add_argument("--device", default=None)
@@ -61,7 +68,7 @@ def main(argv: Optional[List[str]] = None) -> int:
             return 0 if not problems else 1
         elif a.cmd == "kld":
             rep = offline.evaluate_kld(a.input, a.bundle, offline.read_tokens(a.tokens), a.window, a.stride,
-                                       a.max_eval_tokens, _device(a.device), a.self_check, a.baseline_cache)
+                                       a.max_eval_tokens, _device(a.device), a.self_check, a.baseline_cache, a.batch_positions)
             if a.report:
                 open(a.report, "w").write(json.dumps(rep, indent=1))
             for k in ("positions", "mean", "p50", "p90", "p99", "p99_9", "max", "top1_agreement"):
@@ -70,8 +77,8 @@ def main(argv: Optional[List[str]] = None) -> int:
                 print(f"KLD_BASELINE_CACHE_HITS={rep['baseline_cache_hits']}"); print(f"KLD_BASELINE_CACHE_MISSES={rep['baseline_cache_misses']}")
         elif a.cmd == "imatrix":
             rep = offline.collect_imatrix(a.model_dir, offline.read_tokens(a.tokens), a.output, a.window, a.stride,
-                                          a.max_calibration_tokens, _device(a.device))
-            print(f"IMATRIX_SITES={rep['sites']}")
+                                          a.max_calibration_tokens, _device(a.device), a.flush_windows)
+            print(f"IMATRIX_SITES={rep['sites']}"); print(f"IMATRIX_WINDOWS={rep['windows']}"); print(f"IMATRIX_FLUSHES={rep['flushes']}")
         elif a.cmd == "ppl":
             rep = offline.evaluate_ppl(a.model_dir, offline.read_tokens(a.tokens), a.max_tokens, _device(a.device))
             print(f"PPL_TOKENS={rep['tokens']}"); print(f"NLL={rep['nll']}"); print(f"PPL={rep['ppl']}")

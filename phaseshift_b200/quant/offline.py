@@ -388,8 +388,12 @@ class BaselineLogitCache:
 
 
 def evaluate_kld(input_dir, bundle_dir, tokens: Sequence[int], window: int = 512, stride: int = 512,
-                 max_eval_tokens: int = 0, device="cpu", self_check: bool = False, baseline_cache=None) -> dict:
+                 max_eval_tokens: int = 0, device="cpu", self_check: bool = False, baseline_cache=None,
+                 batch_positions: int = 512) -> dict:
+    """``batch_positions``: rows per engine step while a window is evaluated (the reference's ``--batch-positions``,
+    docs/user/quantizer.md:5-96; here it bounds the logits held on the device at once)."""
     cache = BaselineLogitCache(baseline_cache, model_fingerprint(input_dir)) if baseline_cache else None
+    batch_positions = max(1, min(int(batch_positions), 2048))
     base = None                                   # built lazily: a fully cached run never loads the baseline model
     test = None if self_check else _engine_for(bundle_dir, device, window + 1)
     kls, agree, total = [], 0, 0
@@ -402,10 +406,10 @@ def evaluate_kld(input_dir, bundle_dir, tokens: Sequence[int], window: int = 512
         if lb is None:
             if base is None:
                 base = _engine_for(input_dir, device, window + 1)
-            lb = _window_logits(base, ids)
+            lb = _window_logits(base, ids, batch_positions)
             if cache is not None:
                 cache.put(w0, ids, lb)
-        lt = lb if self_check else _window_logits(test, ids)
+        lt = lb if self_check else _window_logits(test, ids, batch_positions)
         lb = lb.to(lt.device)
         kls.append(kl_divergence(lb, lt))
         agree += int((lb.argmax(-1) == lt.argmax(-1)).sum())
@@ -427,7 +431,7 @@ def evaluate_ppl(model_dir, tokens: Sequence[int], max_tokens: int = 2048, devic
 
 
 def collect_imatrix(model_dir, tokens: Sequence[int], output, window: int = 512, stride: int = 512,
-                    max_calibration_tokens: int = 0, device="cpu") -> dict:
+                    max_calibration_tokens: int = 0, device="cpu", flush_windows: int = 0) -> dict:
     """Accumulate sum(x^2) per input channel for every projection input (7 sites per layer + lm_head, the
     tags the reference places in its lowering, src/phaseshift/models/qwen35/model/lower_to_primitives.cpp:
     717-719,819-821,899-901,928-930,940-942,979-980)."""
@@ -456,10 +460,16 @@ def collect_imatrix(model_dir, tokens: Sequence[int], output, window: int = 512,
             counts[tag] = x.shape[0]
     eng.runner.imatrix_collector = collector
     n = len(tokens) if max_calibration_tokens <= 0 else min(len(tokens), max_calibration_tokens)
+    windows = flushes = 0
     for w0 in range(0, max(1, n - 1), stride):
         ids = tokens[w0:w0 + window]
         if len(ids) < 2:
             break
         _window_logits(eng, ids)
+        windows += 1
+        if flush_windows > 0 and windows % flush_windows == 0:
+            # a long calibration run leaves a usable file behind every `flush_windows` windows
+            save_imatrix(output, sums, counts, {"model": str(model_dir), "tokens": min(n, w0 + len(ids)), "partial": True})
+            flushes += 1
     save_imatrix(output, sums, counts, {"model": str(model_dir), "tokens": n})
-    return {"sites": len(sums), "tokens": n, "output": str(output)}
+    return {"sites": len(sums), "tokens": n, "output": str(output), "windows": windows, "flushes": flushes}

@@ -79,7 +79,21 @@ def test_imatrix_collect_and_weighted_quantize(model_dirs):
     im = d / "im.safetensors"
     rep = offline.collect_imatrix(src, toks, im, window=32, stride=32)
     assert rep["sites"] == 4 * cfg.num_hidden_layers + 1      # 4 projection inputs per layer + lm_head
+    assert rep["windows"] == 3 and rep["flushes"] == 0
     loaded = offline.load_imatrix(im)
+    # periodic flushes leave the same final file, and the command line carries the upstream flag names
+    from phaseshift_b200.apps import quantizer as qapp
+    tf = d / "cal.tokens"
+    tf.write_text(" ".join(map(str, toks)))
+    im2 = d / "im2.safetensors"
+    assert qapp.main(["imatrix", "--model-dir", str(src), "--tokens", str(tf), "--output", str(im2), "--window", "32",
+                      "--stride", "32", "--flush-windows", "1", "--arena-gib", "1", "--device", "cpu"]) == 0
+    loaded2 = offline.load_imatrix(im2)
+    assert set(loaded2) == set(loaded) and all(torch.equal(loaded2[k_], loaded[k_]) for k_ in loaded)
+    assert qapp.main(["kld", "--input", str(src), "--bundle", str(src), "--tokens", str(tf), "--window", "32", "--stride", "32",
+                      "--batch-positions", "8", "--cache-dir", str(d / "cd"), "--keep-logit-cache", "--keep-shadow",
+                      "--device", "cpu"]) == 0
+    assert any((d / "cd").iterdir())
     k = "model.language_model.layers.0.mlp.gate_proj.weight"
     assert loaded[k].shape == (cfg.hidden_size,) and float(loaded[k].min()) >= 0
     out = d / "nvfp4_im"
