@@ -45,6 +45,10 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--dflash2-model-dir"); ap.add_argument("--dflash2-drafts", type=int, default=7)
     ap.add_argument("--model-name", default="phaseshift"); ap.add_argument("--verify-weights", type=int, default=0)
     ap.add_argument("--startup-timeout", type=int, default=120)
+    # the upstream server is a front end that spawns the compute binary (docs/user/server.md:79-102); here the engine lives
+    # in the server process, so the two paths are accepted and unused
+    ap.add_argument("--compute", default=None, help="accepted for compatibility (the engine runs in this process)")
+    ap.add_argument("--localai-binary", default=None, help="accepted for compatibility")
     ap.add_argument("--tp", type=int, default=1, choices=[1, 2, 4, 8], help="tensor-parallel ranks, one process per GPU")
     return ap
 
