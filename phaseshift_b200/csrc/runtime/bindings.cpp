@@ -154,6 +154,20 @@ PYBIND11_MODULE(ps_runtime, m) {
                                (uint8_t*)codes + (size_t)r * k_padded, (uint8_t*)scales + (size_t)r * (k_padded / 32));
     });
 
+    m.def("kv_nvfp4_row_bytes", &kv_nvfp4_row_bytes);
+    m.def("kv_nvfp4_encode_rows", [](uintptr_t x, int n, int d, uintptr_t rows, uintptr_t scales) {
+        py::gil_scoped_release rel;
+        const int rb = kv_nvfp4_row_bytes(d);
+        for (int r = 0; r < n; ++r)
+            kv_nvfp4_encode_row((const float*)x + (size_t)r * d, d, (uint8_t*)rows + (size_t)r * rb, (float*)scales + r);
+    });
+    m.def("kv_nvfp4_decode_rows", [](uintptr_t rows, uintptr_t scales, int n, int d, uintptr_t out) {
+        py::gil_scoped_release rel;
+        const int rb = kv_nvfp4_row_bytes(d);
+        for (int r = 0; r < n; ++r)
+            kv_nvfp4_decode_row((const uint8_t*)rows + (size_t)r * rb, ((const float*)scales)[r], d, (float*)out + (size_t)r * d);
+    });
+
     // ---- sampling contract (host side of ps_sampling.h)
     m.def("sampling_bits", [](uint64_t seed, uint64_t idx, uint64_t attempt, uint64_t tok) { return ps::sampling_bits(seed, idx, attempt, tok); });
     m.def("sampling_uniform", [](uint64_t seed, uint64_t idx, uint64_t attempt, uint64_t tok) { return ps::sampling_uniform(seed, idx, attempt, tok); });

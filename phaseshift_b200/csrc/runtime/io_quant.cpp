@@ -353,4 +353,38 @@ void quantize_row_mxfp8(const float* w, int k, int k_padded, int search, const f
     }
 }
 
+// ---- NVFP4 key/value rows (device layout: csrc/include/kv_fp4.cuh; reference counterpart: the 4-bit KV block codec
+// include/phaseshift/quantization/psq/psq4_kv.h:1-79).  Row = D/2 code bytes | D/16 UE4M3 block scales | zero padding to a
+// multiple of 16 bytes; one fp32 row scale max|row| / (6 * 448) is kept beside it.  The arithmetic is the append kernel's:
+// single-precision, correctly rounded multiplications and divisions, nearest-even code rounding.
+int kv_nvfp4_row_bytes(int d) { return ((d / 2 + d / 16) + 15) & ~15; }
+
+void kv_nvfp4_encode_row(const float* x, int d, uint8_t* row, float* row_scale) {
+    float amax = 0.f;
+    for (int i = 0; i < d; ++i) amax = std::max(amax, std::fabs(x[i]));
+    const float ts = amax > 0.f ? amax * (1.0f / (6.0f * 448.0f)) : 1.0f;
+    memset(row, 0, (size_t)kv_nvfp4_row_bytes(d));
+    for (int b = 0; b < d / 16; ++b) {
+        float bmax = 0.f;
+        for (int i = 0; i < 16; ++i) bmax = std::max(bmax, std::fabs(x[16 * b + i]));
+        const uint8_t sf = e4m3_encode(bmax / (6.0f * ts));
+        const float sf_f = e4m3_decode(sf);
+        const float inv = sf_f > 0.f ? 1.0f / (sf_f * ts) : 0.f;
+        for (int i = 0; i < 16; i += 2) {
+            const float a = x[16 * b + i] * inv, c = x[16 * b + i + 1] * inv;
+            row[(16 * b + i) / 2] = (uint8_t)(e2m1_encode(a) | (e2m1_encode(c) << 4));
+        }
+        row[d / 2 + b] = sf;
+    }
+    *row_scale = ts;
+}
+
+void kv_nvfp4_decode_row(const uint8_t* row, float row_scale, int d, float* out) {
+    for (int i = 0; i < d; ++i) {
+        const uint8_t byte = row[i / 2];
+        const float sf = e4m3_decode(row[d / 2 + i / 16]);
+        out[i] = e2m1_decode((i & 1) ? (byte >> 4) : (byte & 0xF)) * sf * row_scale;
+    }
+}
+
 }  // namespace psrt

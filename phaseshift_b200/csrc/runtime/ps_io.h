@@ -71,6 +71,9 @@ float e2m1_decode(uint8_t nibble);
 uint8_t e2m1_encode(float x);
 float ue8m0_decode(uint8_t e);
 // One weight row -> canonical NVFP4 (codes k_padded/2 bytes, scales k_padded/16 bytes) / MXFP8 payload.
+int kv_nvfp4_row_bytes(int d);
+void kv_nvfp4_encode_row(const float* x, int d, uint8_t* row, float* row_scale);
+void kv_nvfp4_decode_row(const uint8_t* row, float row_scale, int d, float* out);
 void quantize_row_nvfp4(const float* w, int k, int k_padded, float tensor_scale, int search, const float* importance,
                         uint8_t* codes, uint8_t* scales);
 void quantize_row_mxfp8(const float* w, int k, int k_padded, int search, const float* importance, uint8_t* codes,

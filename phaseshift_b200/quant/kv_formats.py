@@ -49,7 +49,7 @@ def encode_nvfp4_rows(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     inv = torch.where(sf_f > 0, 1.0 / denom, torch.zeros_like(denom))
     scaled = blocks * inv.unsqueeze(-1)
     idx = _e2m1_index(scaled.abs()).to(torch.uint8)
-    nib = idx | ((scaled < 0) | ((scaled == 0) & torch.signbit(scaled))).to(torch.uint8) << 3
+    nib = idx | (((scaled < 0) & (idx != 0)).to(torch.uint8) << 3)      # no negative zero (the device may store one; it decodes to 0)
     nib = nib.reshape(*lead, D // 2, 2)
     codes = nib[..., 0] | (nib[..., 1] << 4)
     rows = torch.zeros(*lead, nvfp4_row_bytes(D), dtype=torch.uint8, device=x.device)

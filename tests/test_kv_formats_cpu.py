@@ -56,3 +56,23 @@ def test_state_config_accepts_the_four_bit_cache_and_the_upstream_names():
     assert st.kv_fmt == 0                                                      # the fp32 oracle keeps full-precision pages
     with pytest.raises(ValueError):
         ModelState(tiny_config(), StateConfig(kv_dtype="int3"), torch.device("cpu"), act_dtype=torch.float32)
+
+
+def test_native_codec_matches_the_tensor_codec_byte_for_byte():
+    from phaseshift_b200.core.native import runtime
+    rt = runtime()
+    g = torch.Generator().manual_seed(7)
+    for D in (64, 128, 256):
+        x = (torch.randn(37, D, generator=g) * torch.logspace(-2, 2, 37).unsqueeze(1)).contiguous()
+        x[5] = 0
+        x[6, ::3] = 0
+        rows_t, ts_t = encode_nvfp4_rows(x)
+        rb = rt.kv_nvfp4_row_bytes(D)
+        assert rb == nvfp4_row_bytes(D)
+        rows_n = torch.empty(37, rb, dtype=torch.uint8)
+        ts_n = torch.empty(37, dtype=torch.float32)
+        rt.kv_nvfp4_encode_rows(x.data_ptr(), 37, D, rows_n.data_ptr(), ts_n.data_ptr())
+        assert torch.equal(ts_n, ts_t) and torch.equal(rows_n, rows_t)
+        out = torch.empty(37, D, dtype=torch.float32)
+        rt.kv_nvfp4_decode_rows(rows_n.data_ptr(), ts_n.data_ptr(), 37, D, out.data_ptr())
+        assert torch.equal(out, decode_nvfp4_rows(rows_t, ts_t, D))
