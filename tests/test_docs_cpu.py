@@ -24,9 +24,9 @@ def _doc_flags(name: str):
 
 
 def test_every_app_flag_is_documented_and_no_documented_flag_is_missing():
-    from phaseshift_b200.apps import bench, compute, quantizer, server, tools
+    from phaseshift_b200.apps import bench, compute, gpu_test_runner, quantizer, server, tools
     for mod, doc in ((compute, "compute.md"), (server, "server.md"), (quantizer, "quantizer.md"), (bench, "bench.md"),
-                     (tools, "tools.md")):
+                     (tools, "tools.md"), (gpu_test_runner, "gpu_test_runner.md")):
         have, said = _flags(mod.build_parser()), _doc_flags(doc)
         assert have - said == set(), (doc, "undocumented", sorted(have - said))
         assert said - have == set(), (doc, "documented but absent", sorted(said - have))
@@ -46,5 +46,5 @@ def test_every_environment_variable_read_by_the_code_is_listed():
     internal = {"PS_TP_SPAWNED"}                      # set by the launcher for the ranks it starts, not a user setting
     assert read - listed - internal == set(), sorted(read - listed - internal)
     assert {v for v in listed if v.startswith("PS_DEV_")} <= {"PS_DEV_CHECK_FAILED", "PS_DEV_WAIT_TIMEOUT"}
-    stale = {v for v in listed if not v.startswith("PS_DEV_")} - read
+    stale = {v for v in listed if not v.startswith("PS_DEV_")} - read - {"PS_TEST_VRAM_GIB"}     # exported to tests, read by nobody here
     assert stale == set(), sorted(stale)
