@@ -101,3 +101,42 @@ def test_terminal_checkpoint_serves_the_next_turn_and_pool_is_bounded(tiny):
     s = srv.prefix.summary()
     assert srv.prefix.pool_bytes() == pool0 and s["entries"] <= 3 and s["evictions"] > 0
     assert s["pool_pages_free"] + sum(len(x.pages) for x in srv.prefix.snaps.values()) == srv.prefix.pool_pages
+
+
+def test_random_arrivals_budgets_and_shared_prefixes_stay_token_exact(tiny):
+    """Whatever the arrival order, step budget, slot count and prefix-cache state, every request's tokens are those of the
+    whole-sequence oracle run on its prompt alone (scheduling must never leak into the arithmetic of a sequence)."""
+    from hypothesis import HealthCheck, given, settings, strategies as st
+    cfg, hf, ew = tiny
+    oracle = {}
+
+    def ref(p, n):
+        key = (tuple(p), n)
+        if key not in oracle:
+            oracle[key] = reference_greedy(cfg, hf, p, n)
+        return oracle[key]
+
+    bases = [_prompt(cfg, 40, 100 + i) for i in range(2)]
+
+    @settings(max_examples=15, deadline=None, derandomize=True, suppress_health_check=list(HealthCheck))
+    @given(slots=st.integers(1, 3), budget=st.sampled_from([8, 24, 64]), cache=st.booleans(),
+           reqs=st.lists(st.tuples(st.integers(0, 1), st.integers(17, 40), st.integers(0, 9), st.integers(1, 5), st.integers(0, 3)),
+                         min_size=2, max_size=5))
+    def run(slots, budget, cache, reqs):
+        eng = Engine(ew, "cpu", StateConfig(max_slots=slots, max_seq_len=96, page_tokens=16))
+        kw = dict(prefix_cache_tokens=256, prefix_cache_entries=3, prefix_min_tokens=16) if cache else {}
+        srv = ServingEngine(eng, max_step_tokens=budget, **kw)
+        want, events = {}, []
+        for base, keep, tail, new, delay in reqs:
+            p = bases[base][:keep] + _prompt(cfg, tail, 200 + tail)
+            rid = srv.submit(p, new, checkpoint_position=16 if cache else 0)
+            want[rid] = ref(p, new)
+            for _ in range(delay):                       # later requests arrive while earlier ones are running
+                events += srv.step()
+        events += srv.run_until_idle()
+        toks, done = _collect(events)
+        for rid, w in want.items():
+            assert toks[rid] == w, (slots, budget, cache, rid)
+            assert done[rid].info["finish_reason"] == "length"
+        assert eng.state.block_table.max().item() == -1
+    run()
