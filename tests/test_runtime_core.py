@@ -217,3 +217,58 @@ def test_sampling_rng_host_bindings_match_python():
             assert rt.sampling_bits(seed, idx, att, int(t)) == int(bits[j])
             assert rt.sampling_uniform(seed, idx, att, int(t)) == pytest.approx(float(uni[j]), rel=0, abs=0)
             assert 0.0 < float(uni[j]) < 1.0
+
+
+@pytest.mark.parametrize("fmt", ["nvfp4", "mxfp8", "mxfp4", "fp8_block128"])
+def test_payload_round_trip_at_awkward_widths(fmt):
+    """Every format packs, pads and unpacks at widths around its block boundaries: the logical shape comes back, the
+    padding carries zeros, and the error stays that of the format."""
+    from phaseshift_b200.quant import formats
+    g = torch.Generator().manual_seed(3)
+    bound = {"nvfp4": 0.14, "mxfp8": 0.04, "mxfp4": 0.16, "fp8_block128": 0.05}[fmt]
+    for K in (1, 15, 16, 17, 31, 32, 33, 63, 64, 65, 127, 128, 129):
+        w = torch.randn(5, K, generator=g) * 0.1
+        q = formats.quantize(w, fmt)
+        assert q.shape == (5, K) and q.k_padded % 32 == 0 and q.k_padded >= K
+        d = formats.dequantize(q)
+        assert d.shape == (5, K)
+        # a handful of values is a noisy sample: the statistical bound applies from one full block on
+        assert float((d - w).norm() / w.norm()) < (bound if K >= 32 else 2.5 * bound), (fmt, K)
+        full = formats.dequantize(formats.QuantizedTensor(q.fmt, (5, q.k_padded), q.k_padded, q.codes, q.scales, q.tensor_scale))
+        assert float(full[:, K:].abs().sum()) == 0.0, (fmt, K)                         # the padded tail decodes to zero
+        kq = formats.to_kernel_format(q)
+        assert kq.fmt in ("nvfp4", "mxfp8") and formats.dequantize(kq).shape == (5, K)
+
+
+def test_prefix_index_random_operations_keep_its_invariants():
+    """Random inserts, lookups and erasures: the stored token count never exceeds the capacity, a hit is always the longest
+    stored strict prefix of the query, and evicted ids disappear."""
+    import random
+    rnd = random.Random(5)
+    cap, max_entries, min_tokens = 200, 4, 8
+    ix = rt.PrefixIndex(max_entries, cap, min_tokens)
+    stored = {}
+    stems = [[rnd.randrange(50) for _ in range(40)] for _ in range(3)]
+    for step in range(400):
+        seq = list(stems[rnd.randrange(3)][:rnd.randrange(4, 40)]) + [rnd.randrange(50) for _ in range(rnd.randrange(0, 6))]
+        op = rnd.random()
+        if op < 0.5:
+            eid, evicted = ix.insert(seq)
+            for e in evicted:
+                stored.pop(e, None)
+            if eid >= 0:
+                stored[eid] = seq
+            else:
+                assert len(seq) < min_tokens or len(seq) > cap or any(v == seq for v in stored.values())
+        elif op < 0.9:
+            hit = ix.lookup(seq)
+            best = max((len(v) for v in stored.values() if len(v) < len(seq) and seq[:len(v)] == v), default=0)
+            if hit is None or hit.entry < 0:
+                assert best == 0
+            else:
+                assert hit.tokens == best and stored[hit.entry] == seq[:hit.tokens]
+        elif stored:
+            e = rnd.choice(list(stored))
+            ix.erase(e); stored.pop(e)
+        assert ix.used_tokens() == sum(len(v) for v in stored.values()) <= cap
+        assert ix.entries() == len(stored) <= max_entries
