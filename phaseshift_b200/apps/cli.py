@@ -10,16 +10,28 @@ import tempfile
 from typing import List, Optional
 
 
-def main(argv: Optional[List[str]] = None) -> int:
+def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="phaseshift-cli")
     ap.add_argument("--model-dir", required=True); ap.add_argument("--binary", default=None)
     ap.add_argument("--prompt"); ap.add_argument("--max-new-tokens", type=int, default=128)
     ap.add_argument("--max-seq-len", type=int, default=4096); ap.add_argument("--arena-gib", type=float, default=16)
     ap.add_argument("--device", default=None); ap.add_argument("--dflash2-model-dir")
     ap.add_argument("--dflash2-drafts", type=int, default=7); ap.add_argument("--dflash2-stats", type=int, default=0)
-    a = ap.parse_args(argv)
-    from transformers import AutoTokenizer
-    tok = AutoTokenizer.from_pretrained(a.model_dir)
+    return ap
+
+
+def main(argv: Optional[List[str]] = None) -> int:
+    a = build_parser().parse_args(argv)
+    import json
+    import os
+    from .server import load_tokenizer
+    try:
+        vocab = int(json.load(open(os.path.join(a.model_dir, "config.json"))).get("vocab_size", 0)) or 259
+    except (OSError, ValueError):
+        vocab = 259
+    # the directory's own tokenizer and chat template; directories without tokenizer assets (random test models) get the
+    # byte tokenizer the server uses for them
+    tok = load_tokenizer(a.model_dir, vocab)
     history = []
 
     def turn(text: str) -> str:
@@ -29,7 +41,7 @@ def main(argv: Optional[List[str]] = None) -> int:
             f.write(" ".join(map(str, ids)))
         cmd = ([a.binary] if a.binary else [sys.executable, "-m", "phaseshift_b200.apps.compute"]) + [
             "--model-dir", a.model_dir, "--input-ids-file", f.name, "--max-new-tokens", str(a.max_new_tokens),
-            "--max-seq-len", str(a.max_seq_len)]
+            "--max-seq-len", str(a.max_seq_len), "--arena-gib", str(a.arena_gib)]
         if a.device:
             cmd += ["--device", a.device]
         if a.dflash2_model_dir:

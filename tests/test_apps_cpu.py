@@ -226,3 +226,16 @@ def test_bench_subcommands_help_and_cpu_runs(capsys):
         kld[preset] = dict(l.split("=", 1) for l in capsys.readouterr().out.strip().splitlines())
     assert 0 <= float(kld["mxfp8"]["kld_mean"]) < float(kld["nvfp4"]["kld_mean"]) < 0.05
     assert float(kld["nvfp4"]["kld_over_decorrelated"]) < 0.3
+
+
+def test_cli_single_turn_prints_the_decoded_continuation(model_dir, capsys):
+    """phaseshift-cli spawns the compute program for a turn; a directory without tokenizer assets gets the byte tokenizer."""
+    from phaseshift_b200.apps import cli
+    from phaseshift_b200.serving.chat import ByteTokenizer
+    cfg, hf, d = model_dir
+    assert cli.main(["--model-dir", str(d), "--prompt", "hi", "--max-new-tokens", "4", "--max-seq-len", "128", "--device", "cpu"]) == 0
+    printed = capsys.readouterr().out
+    tok = ByteTokenizer(cfg.vocab_size)
+    ids = tok.apply_chat_template([{"role": "user", "content": "hi"}], add_generation_prompt=True, tokenize=True)
+    want = tok.decode(reference_greedy(cfg, hf, ids, 4))
+    assert printed == want + "\n"
