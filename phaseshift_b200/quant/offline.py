@@ -34,7 +34,7 @@ ASSETS = ("config.json", "generation_config.json", "tokenizer.json", "tokenizer_
 
 
 def model_fingerprint(model_dir) -> str:
-    """sha256 over config + tensor names/shapes/CRC of the first and last KiB of every tensor (cheap, stable)."""
+    """sha256 over config.json and every tensor's name, dtype, shape and byte count (cheap, stable; reads no payload)."""
     h = hashlib.sha256()
     h.update((Path(model_dir) / "config.json").read_bytes())
     col = ShardCollection(model_dir)
