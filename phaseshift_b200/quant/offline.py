@@ -34,13 +34,22 @@ ASSETS = ("config.json", "generation_config.json", "tokenizer.json", "tokenizer_
 
 
 def model_fingerprint(model_dir) -> str:
-    """sha256 over config.json and every tensor's name, dtype, shape and byte count (cheap, stable; reads no payload)."""
+    """sha256 over config.json and, per tensor, its name, dtype, shape, byte count and the CRC32 of its first and last
+    64 KiB (cheap: a 27B directory costs a few hundred MB of reads; two checkpoints of one architecture still differ)."""
+    from ..core.native import runtime
+    rt = runtime()
     h = hashlib.sha256()
     h.update((Path(model_dir) / "config.json").read_bytes())
     col = ShardCollection(model_dir)
+    edge = 64 * 1024
     for n in sorted(col.names()):
         dt, shape, nbytes = col.spec(n)
         h.update(f"{n}:{dt}:{shape}:{nbytes}".encode())
+        if nbytes:
+            buf = col.readers[col.where[n]].data(n)                  # uint8 view of the file mapping
+            head = rt.crc32_ptr(buf.ctypes.data, min(edge, nbytes), 0)
+            tail = rt.crc32_ptr(buf.ctypes.data + max(0, nbytes - edge), min(edge, nbytes), 0)
+            h.update(f":{head}:{tail}".encode())
     col.close()
     return h.hexdigest()
 

@@ -189,3 +189,18 @@ def test_dflash2_adapter_quantizes_and_loads_a_drafter(tmp_path):
     victim = next(out.glob("model*.safetensors"))
     b = bytearray(victim.read_bytes()); b[-3] ^= 0xFF; victim.write_bytes(bytes(b))
     assert any("CRC" in p for p in offline.validate_model_dir(out))
+
+
+def test_fingerprint_separates_checkpoints_of_one_architecture(tmp_path):
+    """The baseline-logit cache is keyed by the fingerprint: two checkpoints with identical shapes must not share it."""
+    from phaseshift_b200.io.model_dir import save_hf_model
+    from phaseshift_b200.models.qwen35.config import tiny_config
+    from phaseshift_b200.models.qwen35.weights import random_hf_weights
+    from phaseshift_b200.quant import offline
+    cfg = tiny_config()
+    a, b, c = tmp_path / "a", tmp_path / "b", tmp_path / "c"
+    save_hf_model(a, cfg, random_hf_weights(cfg, seed=1))
+    save_hf_model(b, cfg, random_hf_weights(cfg, seed=2))
+    save_hf_model(c, cfg, random_hf_weights(cfg, seed=1))
+    fa, fb, fc = offline.model_fingerprint(a), offline.model_fingerprint(b), offline.model_fingerprint(c)
+    assert fa == fc and fa != fb and len(fa) == 64
