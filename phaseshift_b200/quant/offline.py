@@ -353,8 +353,8 @@ def kld_report(kl: torch.Tensor, top1_agree: float) -> dict:
 class BaselineLogitCache:
     """On-disk cache of the baseline model's logits, one file per evaluation window, keyed by the source model's
     fingerprint, the window's token ids and its position: repeated `kld` runs against different bundles of the same
-    source (the usual sweep over presets) run the BF16 baseline only once.  Logits are stored as bf16-rounded fp16
-    pairs would lose range, so they are kept in fp32; a 512-token window of a 152 k vocabulary is ~300 MB, hence
+    source (the usual sweep over presets) run the BF16 baseline only once.  Logits are kept in fp32 (half precision
+    would lose range or mantissa that the divergence needs); a 512-token window of a 152 k vocabulary is ~300 MB, hence
     the cache is opt-in (`--baseline-cache DIR`) and bounded by `max_bytes` (oldest files are evicted)."""
 
     def __init__(self, directory, fingerprint: str, max_bytes: int = 64 << 30):
