@@ -11,7 +11,7 @@ action = st.one_of(st.tuples(st.just("step"), st.integers(0, 0)), st.tuples(st.j
                    st.tuples(st.just("fail"), st.integers(0, 0)), st.tuples(st.just("submit"), st.integers(0, 63)))
 
 
-@settings(max_examples=120, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+@settings(max_examples=300, deadline=None, derandomize=True, suppress_health_check=[HealthCheck.too_slow])
 @given(reqs=st.lists(request, min_size=1, max_size=12), slots=st.integers(1, 4), pages=st.integers(12, 40),
        budget=st.sampled_from([16, 48, 200]), script=st.lists(action, max_size=40), stop_tok=st.integers(0, 3))
 def test_random_workloads_finish_within_budgets_and_leak_nothing(reqs, slots, pages, budget, script, stop_tok):
