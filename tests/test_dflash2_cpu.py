@@ -186,3 +186,36 @@ def test_speculative_serving_restores_prefixes_with_the_drafter_ring(setup):
     done = {e.request_id: e.info for e in ev if e.kind == "done"}
     assert done[c]["restored_tokens"] >= len(prompt) + 8
     assert done[c]["generated_ids"] == Engine(ew, "cpu", StateConfig(max_slots=1, max_seq_len=96)).generate(turn2, 5)
+
+
+def test_random_draft_counts_chunks_and_prompts_keep_the_greedy_stream(setup):
+    """Speculative rounds under random draft counts, prefill chunk sizes, prompt cuts and output lengths: the stream is
+    always the plain greedy one (whatever the drafter proposes, whatever gets rolled back)."""
+    from hypothesis import HealthCheck, given, settings, strategies as st
+    from phaseshift_b200.runtime.spec_serving import SpecServingEngine
+    cfg, ew, prompt, ref = setup
+    plain = Engine(ew, "cpu", StateConfig(max_slots=1, max_seq_len=96))
+    memo = {}
+
+    def greedy(p, n):
+        if (tuple(p), n) not in memo:
+            memo[(tuple(p), n)] = plain.generate(list(p), n)
+        return memo[(tuple(p), n)]
+
+    @settings(max_examples=10, deadline=None, derandomize=True, suppress_health_check=list(HealthCheck))
+    @given(k=st.integers(1, 7), chunk=st.sampled_from([4, 8, 32]), seed=st.integers(0, 3),
+           reqs=st.lists(st.tuples(st.integers(0, 6), st.integers(5, 21), st.integers(1, 14)), min_size=1, max_size=3))
+    def run(k, chunk, seed, reqs):
+        eng = Engine(ew, "cpu", StateConfig(max_slots=1, max_seq_len=96, conv_ring=16, spec_rows=8))
+        dcfg = tiny_drafter_config(cfg)
+        dec = DFlash2SpecDecoder(eng, DFlash2Drafter(dcfg, random_weights(dcfg, seed=seed), "cpu"), num_drafts=k)
+        srv = SpecServingEngine(dec, prefill_chunk=chunk)
+        want = {}
+        for lo, hi, n in reqs:
+            p = prompt[lo:max(hi, lo + 2)]
+            want[srv.submit(p, n)] = greedy(p, n)
+        ev = srv.run_until_idle()
+        for rid, w in want.items():
+            assert [e.token_id for e in ev if e.kind == "token" and e.request_id == rid] == w, (k, chunk, seed, rid)
+        assert srv.idle()
+    run()
