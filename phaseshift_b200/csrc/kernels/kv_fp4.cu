@@ -6,6 +6,8 @@
 //     same merge pass (ps_paged_attention_merge).  A tile of a 256-wide head is 32 x 144 bytes: every thread fetches one
 //     16-byte piece of codes (32 values) and the two block scales that belong to it, and widens them to bf16 on the way
 //     into shared memory (exact); the per-token fp32 scale multiplies the score and the probability, as for FP8 pages.
+//     It is a kernel of its own rather than a third branch of that one, so that adding the format left the code generated
+//     for the bf16 / FP8 kernel (whose timings are on record) exactly as it was.
 //   * ps_kv_fp4_dequant: widens the pages that a prefill step reads into a bf16 scratch pool with a block table and
 //     sequence descriptors of its own, on which the tiled tensor-core prefill kernels run unchanged (the same scheme the
 //     FP8 pools use).  4.6 bits are read and 16 written per cached value, once per layer and step.
