@@ -37,6 +37,9 @@ def build_parser() -> argparse.ArgumentParser:
     tg.add_argument("--mode", default="greedy", choices=["forward", "greedy"]); tg.add_argument("--context", type=int, default=128)
     tg.add_argument("--tokens", type=int, default=8); tg.add_argument("--prefill-chunk", type=int, default=2048)
     tg.add_argument("--compute-logits", type=int, default=1)
+    # upstream spells MTP speculative decoding as a mode of `tg` (docs/user/bench.md:5-216); `mtp` is the same measurement
+    tg.add_argument("--mtp", action="store_true", help="decode with the MTP head as a drafter (the `mtp` command)")
+    tg.add_argument("--draft-k", type=int, default=4); tg.add_argument("--mtp-chain", default="pre", choices=["pre", "post"])
     ba = sub.add_parser("batch", help="concurrent serving throughput"); _model_args(ba)
     ba.add_argument("--requests", type=int, default=8); ba.add_argument("--prompt-tokens", type=int, default=512)
     ba.add_argument("--tokens", type=int, default=64); ba.add_argument("--shared-prefix", type=int, default=0)
@@ -122,6 +125,9 @@ def cmd_pp(a) -> int:
 
 
 def cmd_tg(a) -> int:
+    if getattr(a, "mtp", False):
+        a.verify_mode, a.replay_check = "exact", False
+        return cmd_mtp(a)
     import torch
     eng, dev = _engine(a, a.context + a.tokens + 8)
     ids = torch.randint(0, eng.cfg.vocab_size, (a.context,), generator=torch.Generator().manual_seed(0)).tolist()

@@ -218,6 +218,9 @@ def test_bench_subcommands_help_and_cpu_runs(capsys):
                        "--runs", "1", "--warmup", "0", "--replay-check"]) == 0
     out = dict(l.split("=", 1) for l in capsys.readouterr().out.strip().splitlines())
     assert out["replay_match"] == "1" and int(out["proposed"]) >= int(out["accepted"]) and out["mtp_head"] == "random-init"
+    assert bench.main(["tg", "--mtp", "--draft-k", "2", "--random-model", "tiny", "--device", "cpu", "--context", "16", "--tokens", "6",
+                       "--runs", "1", "--warmup", "0"]) == 0                               # the upstream spelling of the same run
+    assert "proposed" in capsys.readouterr().out
     # quantised preset against the bf16 model of the same random weights: small divergence on a 4-layer model, and the
     # 8-bit preset closer than the 4-bit one
     kld = {}
