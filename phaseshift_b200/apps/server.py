@@ -251,35 +251,132 @@ def create_app(serving, tokenizer, model_name: str, default_max_output_tokens: i
                               "total_tokens": val["prompt_tokens"] + len(val["generated_ids"]),
                               "prompt_tokens_details": {"cached_tokens": val.get("restored_tokens", 0)}}}
 
+    def responses_to_chat(body: dict) -> dict:
+        """Responses-API request -> the chat request `prepare` understands: input items (messages, function calls and their
+        outputs), flat tool definitions, `text.format`, `reasoning.effort`."""
+        inp = body.get("input")
+        msgs: List[dict] = []
+        if isinstance(inp, str):
+            msgs.append({"role": "user", "content": inp})
+        else:
+            for it in list(inp or []):
+                if not isinstance(it, dict):
+                    raise chat.RequestError("input items must be objects")
+                kind = it.get("type", "message")
+                if kind == "message":
+                    msgs.append({"role": it.get("role", "user"), "content": it.get("content")})
+                elif kind == "function_call":
+                    msgs.append({"role": "assistant", "content": None, "tool_calls": [
+                        {"id": it.get("call_id"), "type": "function",
+                         "function": {"name": it.get("name"), "arguments": it.get("arguments", "{}")}}]})
+                elif kind == "function_call_output":
+                    out = it.get("output")
+                    msgs.append({"role": "tool", "tool_call_id": it.get("call_id"),
+                                 "content": out if isinstance(out, str) else json.dumps(out)})
+                else:
+                    raise chat.RequestError(f"unsupported input item type {kind!r}")
+        if body.get("instructions"):
+            msgs = [{"role": "system", "content": body["instructions"]}] + msgs
+        tools = None
+        if body.get("tools") is not None:
+            tools = []
+            for t in body["tools"]:
+                if isinstance(t, dict) and t.get("type") == "function" and "function" not in t:
+                    t = {"type": "function", "function": {k: v for k, v in t.items() if k != "type"}}
+                tools.append(t)
+        choice = body.get("tool_choice")
+        if isinstance(choice, dict) and choice.get("type") == "function" and "function" not in choice:
+            choice = {"type": "function", "function": {"name": choice.get("name")}}
+        fmt = (body.get("text") or {}).get("format")
+        rf = None
+        if isinstance(fmt, dict) and fmt.get("type") not in (None, "text"):
+            rf = {"type": "json_schema", "json_schema": {"name": fmt.get("name", "response"), "schema": fmt.get("schema")}} \
+                if fmt["type"] == "json_schema" else fmt
+        return {"messages": msgs, "max_tokens": body.get("max_output_tokens"), "temperature": body.get("temperature"),
+                "top_p": body.get("top_p"), "seed": body.get("seed"), "tools": tools, "tool_choice": choice,
+                "response_format": rf, "reasoning_effort": (body.get("reasoning") or {}).get("effort")}
+
+    def response_object(rid: str, created: int, val: dict, reasoning: bool, mode: str, status: Optional[str] = None) -> dict:
+        text = tokenizer.decode([i for i in val["generated_ids"] if i not in stop_ids], skip_special_tokens=True)
+        reasoning_text, answer = chat.split_reasoning(text, reasoning) if reasoning else ("", text)
+        answer, calls = chat.parse_tool_calls(answer) if mode != "none" else (answer, [])
+        output: List[dict] = []
+        if reasoning_text:
+            output.append({"type": "reasoning", "id": "rs_" + uuid.uuid4().hex[:24],
+                           "summary": [{"type": "summary_text", "text": reasoning_text}]})
+        if answer or not calls:
+            output.append({"type": "message", "id": "msg_" + uuid.uuid4().hex[:24], "role": "assistant", "status": "completed",
+                           "content": [{"type": "output_text", "text": answer, "annotations": []}]})
+        for c in calls:
+            output.append({"type": "function_call", "id": "fc_" + uuid.uuid4().hex[:24], "call_id": c["id"], "status": "completed",
+                           "name": c["function"]["name"], "arguments": c["function"]["arguments"]})
+        fr = val["finish_reason"]
+        obj = {"id": rid, "object": "response", "created_at": created, "model": model_name,
+               "status": status or {"stop": "completed", "length": "incomplete"}.get(fr, fr),
+               "output": output, "output_text": answer,
+               "usage": {"input_tokens": val["prompt_tokens"], "output_tokens": len(val["generated_ids"]),
+                         "total_tokens": val["prompt_tokens"] + len(val["generated_ids"]),
+                         "input_tokens_details": {"cached_tokens": val.get("restored_tokens", 0)}}}
+        if fr == "length":
+            obj["incomplete_details"] = {"reason": "max_output_tokens"}
+        return obj
+
     @app.post("/v1/responses")
     async def responses(request: Request):
         try:
             body = await request.json()
-            inp = body.get("input")
-            msgs = [{"role": "user", "content": inp}] if isinstance(inp, str) else list(inp or [])
-            if body.get("instructions"):
-                msgs = [{"role": "system", "content": body["instructions"]}] + msgs
-            kw, reasoning, mode = prepare({"messages": msgs, "max_tokens": body.get("max_output_tokens"),
-                                           "temperature": body.get("temperature"), "top_p": body.get("top_p"),
-                                           "tools": body.get("tools"), "tool_choice": body.get("tool_choice")})
+            kw, reasoning, mode = prepare(responses_to_chat(body))
         except chat.RequestError as e:
             return bad(str(e))
         except Exception as e:
             return bad(f"malformed request: {e}")
         t = eng.new_ticket()
         eng.cmd.put(("submit", t, kw))
+        q = eng.out[t]
+        rid, created = "resp_" + uuid.uuid4().hex[:24], int(time.time())
+        if body.get("stream"):
+            def sse(event: str, payload: dict) -> str:
+                return f"event: {event}\ndata: " + json.dumps(dict(payload, type=event)) + "\n\n"
+
+            async def gen():
+                ids: List[int] = []
+                sent, seq = 0, 0
+                shell = {"id": rid, "object": "response", "created_at": created, "model": model_name, "status": "in_progress",
+                         "output": []}
+                yield sse("response.created", {"sequence_number": seq, "response": shell})
+                while True:
+                    kind, val = await wait_item(q, request, t)
+                    if kind == "token":
+                        ids.append(val)
+                        text = tokenizer.decode([i for i in ids if i not in stop_ids], skip_special_tokens=True)
+                        if text.endswith("\ufffd"):
+                            continue                     # incomplete UTF-8 sequence: wait for more bytes
+                        delta, sent = text[sent:], len(text)
+                        if delta:
+                            seq += 1
+                            yield sse("response.output_text.delta", {"sequence_number": seq, "output_index": 0,
+                                                                     "content_index": 0, "delta": delta})
+                        continue
+                    eng.out.pop(t, None)
+                    seq += 1
+                    if kind == "error":
+                        yield sse("error", {"sequence_number": seq, "message": val.get("message", "error")})
+                        return
+                    obj = response_object(rid, created, val, reasoning, mode)
+                    yield sse("response.output_text.done", {"sequence_number": seq, "output_index": 0, "content_index": 0,
+                                                            "text": obj["output_text"]})
+                    final = "response.completed" if obj["status"] == "completed" else "response.incomplete"
+                    yield sse(final, {"sequence_number": seq + 1, "response": obj})
+                    return
+            return StreamingResponse(gen(), media_type="text/event-stream")
         while True:
-            kind, val = await wait_item(eng.out[t], request, t)
+            kind, val = await wait_item(q, request, t)
             if kind == "token":
                 continue
             eng.out.pop(t, None)
             if kind == "error":
                 return bad(val.get("message", "error"), 400 if val.get("bad_request") else 500)
-            text = tokenizer.decode([i for i in val["generated_ids"] if i not in stop_ids], skip_special_tokens=True)
-            return {"id": "resp_" + uuid.uuid4().hex[:24], "object": "response", "created_at": int(time.time()), "model": model_name,
-                    "status": "completed" if val["finish_reason"] in ("stop", "length") else val["finish_reason"],
-                    "output": [{"type": "message", "role": "assistant", "content": [{"type": "output_text", "text": text}]}],
-                    "usage": {"input_tokens": val["prompt_tokens"], "output_tokens": len(val["generated_ids"])}}
+            return response_object(rid, created, val, reasoning, mode)
 
     return app
 

@@ -218,6 +218,55 @@ def test_responses_endpoint_with_instructions_and_message_list(server):
     r = requests.post(url + "/v1/responses", json={"instructions": "be brief", "input": [{"role": "user", "content": "hello"}],
                                                    "max_output_tokens": 5})
     j = r.json()
-    assert r.status_code == 200 and j["object"] == "response" and j["status"] == "completed"
+    # five tokens cannot finish a random model's answer: the response is cut at the limit and says so
+    assert r.status_code == 200 and j["object"] == "response" and j["status"] in ("completed", "incomplete")
+    if j["status"] == "incomplete":
+        assert j["incomplete_details"] == {"reason": "max_output_tokens"}
     assert j["usage"]["output_tokens"] <= 5 and j["usage"]["input_tokens"] > 0 and j["id"].startswith("resp_")
     assert requests.post(url + "/v1/responses", json={"input": [{"role": "user", "content": [{"type": "image_url"}]}]}).status_code == 400
+
+
+@pytest.mark.timeout(300)
+def test_responses_endpoint_items_tools_structured_output_and_streaming(server):
+    """The Responses API surface: conversation items (function calls and their outputs), flat tool definitions with a forced
+    call, `text.format` JSON schemas, and the event stream, all agreeing with the non-streamed result."""
+    url, rt = server
+    # streaming: deltas concatenate to the final text, which equals the non-streamed answer (greedy)
+    body = {"input": "tell me", "max_output_tokens": 10}
+    plain = requests.post(url + "/v1/responses", json=body).json()
+    events = []
+    with requests.post(url + "/v1/responses", json=dict(body, stream=True), stream=True) as r:
+        assert r.status_code == 200 and r.headers["content-type"].startswith("text/event-stream")
+        for line in r.iter_lines(decode_unicode=True):
+            if line and line.startswith("data: "):
+                events.append(json.loads(line[6:]))
+    kinds = [e["type"] for e in events]
+    assert kinds[0] == "response.created" and kinds[-1] in ("response.completed", "response.incomplete")
+    assert kinds[-2] == "response.output_text.done"
+    deltas = "".join(e["delta"] for e in events if e["type"] == "response.output_text.delta")
+    assert deltas == events[-2]["text"] == plain["output_text"]
+    assert events[-1]["response"]["usage"] == plain["usage"]
+    assert [e["sequence_number"] for e in events] == sorted(e["sequence_number"] for e in events)
+    # conversation items: an earlier function call and its output are part of the prompt
+    items = [{"role": "user", "content": [{"type": "input_text", "text": "weather?"}]},
+             {"type": "function_call", "call_id": "call_0", "name": "get_weather", "arguments": "{\"city\": \"Oslo\"}"},
+             {"type": "function_call_output", "call_id": "call_0", "output": "4 degrees"}]
+    a = requests.post(url + "/v1/responses", json={"input": items, "max_output_tokens": 4}).json()
+    b = requests.post(url + "/v1/responses", json={"input": items[:1], "max_output_tokens": 4}).json()
+    assert a["usage"]["input_tokens"] > b["usage"]["input_tokens"]
+    assert requests.post(url + "/v1/responses", json={"input": [{"type": "computer_call"}]}).status_code == 400
+    if rt.serving.constraints is None:
+        return
+    # a forced call with the flat tool form comes back as a function_call item with schema-valid arguments
+    tool = {"type": "function", "name": "get_weather", "strict": True,
+            "parameters": {"type": "object", "properties": {"city": {"type": "string", "enum": ["Oslo", "Rome"]}},
+                           "required": ["city"], "additionalProperties": False}}
+    j = requests.post(url + "/v1/responses", json={"input": "weather?", "tools": [tool], "max_output_tokens": 300,
+                                                   "tool_choice": {"type": "function", "name": "get_weather"}}).json()
+    calls = [o for o in j["output"] if o["type"] == "function_call"]
+    assert len(calls) == 1 and calls[0]["name"] == "get_weather" and json.loads(calls[0]["arguments"])["city"] in ("Oslo", "Rome")
+    # structured output through text.format
+    schema = {"type": "object", "properties": {"ok": {"type": "boolean"}}, "required": ["ok"], "additionalProperties": False}
+    j = requests.post(url + "/v1/responses", json={"input": "json", "max_output_tokens": 40,
+                                                   "text": {"format": {"type": "json_schema", "name": "r", "schema": schema}}}).json()
+    assert isinstance(json.loads(j["output_text"])["ok"], bool)
