@@ -152,6 +152,7 @@ def create_app(serving, tokenizer, model_name: str, default_max_output_tokens: i
         if "json_schema" in cons:      # the serving loop takes grammar / structural_tag; wrap the schema as a tag-less format
             cons = {"structural_tag": json.dumps({"type": "structural_tag",
                                                   "format": {"type": "json_schema", "json_schema": json.loads(cons["json_schema"])}})}
+        stops = chat.parse_stop(body.get("stop"))
         rp = chat.render_prompt(tokenizer, msgs, tools if mode != "none" else None, reasoning)
         max_new = int(body.get("max_completion_tokens") or body.get("max_tokens") or default_max_output_tokens)
         if len(rp.ids) + 1 > max_seq_len:
@@ -161,6 +162,7 @@ def create_app(serving, tokenizer, model_name: str, default_max_output_tokens: i
                   top_p=float(body.get("top_p") or 1.0), top_k=int(body.get("top_k") or 0), seed=int(body.get("seed") or 0),
                   stop_tokens=stop_ids, checkpoint_position=rp.checkpoint_position, grammar=cons.get("grammar"),
                   structural_tag=cons.get("structural_tag"))
+        body["_stops"] = stops
         return kw, reasoning, mode
 
     def finish_reason(info, has_calls: bool) -> str:
@@ -194,6 +196,7 @@ def create_app(serving, tokenizer, model_name: str, default_max_output_tokens: i
             return bad(str(e))
         except Exception as e:
             return bad(f"malformed request: {e}")
+        watcher = chat.StopWatcher(body.get("_stops") or [])
         t = eng.new_ticket()
         eng.cmd.put(("submit", t, kw))
         q = eng.out[t]
@@ -202,16 +205,22 @@ def create_app(serving, tokenizer, model_name: str, default_max_output_tokens: i
             async def gen():
                 ids: List[int] = []
                 sent = 0
+                cut: Optional[int] = None                # position of a completed stop sequence
                 yield "data: " + json.dumps({"id": cid, "object": "chat.completion.chunk", "created": created, "model": model_name,
                                              "choices": [{"index": 0, "delta": {"role": "assistant"}, "finish_reason": None}]}) + "\n\n"
                 while True:
                     kind, val = await wait_item(q, request, t)
                     if kind == "token":
+                        if cut is not None:
+                            continue                     # the request is being cancelled: nothing after the stop is shown
                         ids.append(val)
                         text = tokenizer.decode([i for i in ids if i not in stop_ids], skip_special_tokens=True)
-                        if text.endswith("�"):
+                        if text.endswith("\ufffd"):
                             continue                     # incomplete UTF-8 sequence: wait for more bytes
-                        delta, sent = text[sent:], len(text)
+                        safe, cut = watcher.feed(text)
+                        if cut is not None:
+                            eng.cmd.put(("cancel", t))
+                        delta, sent = text[sent:safe], max(sent, safe)
                         if delta:
                             yield "data: " + json.dumps({"id": cid, "object": "chat.completion.chunk", "created": created,
                                                          "model": model_name, "choices": [{"index": 0, "delta": {"content": delta},
@@ -221,23 +230,47 @@ def create_app(serving, tokenizer, model_name: str, default_max_output_tokens: i
                             yield "data: " + json.dumps({"error": {"message": val.get("message", "error")}}) + "\n\n"
                         else:
                             text = tokenizer.decode([i for i in val["generated_ids"] if i not in stop_ids], skip_special_tokens=True)
+                            if cut is not None:
+                                text, val = text[:cut], dict(val, finish_reason="stop")
+                            elif len(text) > sent and not chat.parse_tool_calls(text)[1]:
+                                # characters held back as a possible beginning of a stop sequence that never completed
+                                yield "data: " + json.dumps({"id": cid, "object": "chat.completion.chunk", "created": created,
+                                                             "model": model_name, "choices": [{"index": 0, "delta": {"content": text[sent:]},
+                                                                                               "finish_reason": None}]}) + "\n\n"
                             _, calls = chat.parse_tool_calls(text)
                             yield "data: " + json.dumps({"id": cid, "object": "chat.completion.chunk", "created": created,
                                                          "model": model_name,
                                                          "choices": [{"index": 0, "delta": ({"tool_calls": calls} if calls else {}),
                                                                       "finish_reason": finish_reason(val, bool(calls))}]}) + "\n\n"
+                            if (body.get("stream_options") or {}).get("include_usage"):
+                                n_out = len(ids) if cut is not None else len(val["generated_ids"])
+                                yield "data: " + json.dumps({"id": cid, "object": "chat.completion.chunk", "created": created,
+                                                             "model": model_name, "choices": [],
+                                                             "usage": {"prompt_tokens": val["prompt_tokens"], "completion_tokens": n_out,
+                                                                       "total_tokens": val["prompt_tokens"] + n_out}}) + "\n\n"
                         yield "data: [DONE]\n\n"
                         eng.out.pop(t, None)
                         return
             return StreamingResponse(gen(), media_type="text/event-stream")
+        seen: List[int] = []
+        cut: Optional[int] = None
         while True:
             kind, val = await wait_item(q, request, t)
             if kind == "token":
+                if watcher.stops and cut is None:
+                    seen.append(val)
+                    _, cut = watcher.feed(tokenizer.decode([i for i in seen if i not in stop_ids], skip_special_tokens=True))
+                    if cut is not None:
+                        eng.cmd.put(("cancel", t))       # a stop sequence is complete: the rest is not needed
                 continue
             eng.out.pop(t, None)
             if kind == "error":
                 return bad(val.get("message", "error"), 400 if val.get("bad_request") else 500)
             text = tokenizer.decode([i for i in val["generated_ids"] if i not in stop_ids], skip_special_tokens=True)
+            if cut is None and watcher.stops:
+                _, cut = watcher.feed(text)
+            if cut is not None:
+                text, val = text[:cut], dict(val, finish_reason="stop", generated_ids=seen or val["generated_ids"])
             reasoning_text, answer = chat.split_reasoning(text, reasoning) if reasoning else ("", text)
             answer, calls = chat.parse_tool_calls(answer) if mode != "none" else (answer, [])
             msg = {"role": "assistant", "content": answer or None if calls else answer}

@@ -214,3 +214,39 @@ def response_format_constraint(rf: Optional[dict]) -> Dict[str, Optional[str]]:
             raise RequestError("response_format.grammar is required")
         return {"grammar": rf["grammar"]}
     raise RequestError(f"unsupported response_format type {rf['type']!r}")
+
+
+# ------------------------------------------------------------------------------------------------ stop sequences
+def parse_stop(stop) -> List[str]:
+    """OpenAI `stop`: a string or up to four strings."""
+    if stop is None:
+        return []
+    if isinstance(stop, str):
+        stop = [stop]
+    if not isinstance(stop, list) or len(stop) > 4 or not all(isinstance(x, str) and x for x in stop):
+        raise RequestError("stop must be a non-empty string or a list of up to 4 non-empty strings")
+    return list(stop)
+
+
+class StopWatcher:
+    """Text-level stop sequences over a growing decoded text.  `feed(text)` returns (safe, hit): `safe` = how many
+    characters may be shown (text that could still turn out to be the beginning of a stop sequence is held back), `hit` =
+    index of the earliest stop sequence once one is complete (the answer is text[:hit]), else None."""
+
+    def __init__(self, stops: Sequence[str]):
+        self.stops = list(stops)
+        self.hold = max((len(x) for x in self.stops), default=1) - 1
+
+    def feed(self, text: str) -> Tuple[int, Optional[int]]:
+        hits = [i for i in (text.find(x) for x in self.stops) if i >= 0]
+        if hits:
+            return min(hits), min(hits)
+        if not self.stops:
+            return len(text), None
+        safe = len(text)
+        for x in self.stops:                       # hold back the longest tail of `text` that is a proper prefix of a stop
+            for k in range(min(len(x) - 1, len(text)), 0, -1):
+                if text.endswith(x[:k]):
+                    safe = min(safe, len(text) - k)
+                    break
+        return safe, None

@@ -270,3 +270,50 @@ def test_responses_endpoint_items_tools_structured_output_and_streaming(server):
     j = requests.post(url + "/v1/responses", json={"input": "json", "max_output_tokens": 40,
                                                    "text": {"format": {"type": "json_schema", "name": "r", "schema": schema}}}).json()
     assert isinstance(json.loads(j["output_text"])["ok"], bool)
+
+
+@pytest.mark.timeout(300)
+def test_stop_sequences_cut_the_answer_and_streams_report_usage(server):
+    """`stop` strings end the answer at their first occurrence (not shown), in the plain and in the streamed form, with
+    characters that might begin a stop sequence held back; `stream_options.include_usage` adds a usage chunk."""
+    url, rt = server
+    if rt.serving.constraints is None:
+        pytest.skip("grammar engine not available")
+    # a grammar keeps the random model on letters, so that the answer is a text of 24 characters
+    body = {"messages": [{"role": "user", "content": "stop test"}], "max_tokens": 24,
+            "response_format": {"type": "grammar", "grammar": "root ::= [a-j]+"}}
+    full = requests.post(url + "/v1/chat/completions", json=body).json()["choices"][0]["message"]["content"]
+    pick = None
+    for i in range(2, max(2, len(full) - 2)):
+        sub = full[i:i + 2]
+        if "\\ufffd" not in sub and "\\ufffd" not in full[:i] and full.find(sub) == i:
+            pick = (i, sub)
+            break
+    if pick is None:
+        pytest.skip("the random model's answer has no usable substring")
+    i, sub = pick
+    j = requests.post(url + "/v1/chat/completions", json=dict(body, stop=[sub, "never-appears"])).json()
+    assert j["choices"][0]["message"]["content"] == full[:i] and j["choices"][0]["finish_reason"] == "stop"
+    chunks = []
+    with requests.post(url + "/v1/chat/completions", json=dict(body, stop=sub, stream=True, stream_options={"include_usage": True}),
+                       stream=True) as r:
+        for line in r.iter_lines(decode_unicode=True):
+            if line and line.startswith("data: ") and line != "data: [DONE]":
+                chunks.append(json.loads(line[6:]))
+    text = "".join(c["choices"][0]["delta"].get("content", "") for c in chunks if c.get("choices"))
+    assert text == full[:i]
+    assert [c["choices"][0]["finish_reason"] for c in chunks if c.get("choices")][-1] == "stop"
+    usage = [c["usage"] for c in chunks if "usage" in c]
+    assert len(usage) == 1 and usage[0]["total_tokens"] == usage[0]["prompt_tokens"] + usage[0]["completion_tokens"]
+    # a stop that never completes changes nothing, and held-back characters are delivered at the end
+    chunks = []
+    with requests.post(url + "/v1/chat/completions", json=dict(body, stop=full[-1] + "\\x00never", stream=True), stream=True) as r:
+        for line in r.iter_lines(decode_unicode=True):
+            if line and line.startswith("data: ") and line != "data: [DONE]":
+                chunks.append(json.loads(line[6:]))
+    assert "".join(c["choices"][0]["delta"].get("content", "") for c in chunks if c.get("choices")) == full
+    assert requests.post(url + "/v1/chat/completions", json=dict(body, stop=["a", "b", "c", "d", "e"])).status_code == 400
+    deadline = time.time() + 30
+    while time.time() < deadline and not rt.serving.idle():
+        time.sleep(0.1)
+    assert rt.serving.idle()
