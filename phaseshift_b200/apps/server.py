@@ -135,6 +135,17 @@ def create_app(serving, tokenizer, model_name: str, default_max_output_tokens: i
         msgs = body.get("messages")
         if not isinstance(msgs, list):
             raise chat.RequestError("messages must be a list")
+        # capabilities this server does not have are refused, not ignored (a client must not believe it got them)
+        if body.get("n") not in (None, 1):
+            raise chat.RequestError("n > 1 is not supported: one completion per request")
+        if body.get("logprobs") or body.get("top_logprobs"):
+            raise chat.RequestError("logprobs are not supported")
+        if body.get("audio") is not None or any(m_ != "text" for m_ in (body.get("modalities") or ["text"])):
+            raise chat.RequestError("only the text modality is supported")
+        for key in ("temperature", "top_p"):
+            v = body.get(key)
+            if v is not None and (not isinstance(v, (int, float)) or isinstance(v, bool) or v < 0 or (key == "top_p" and v > 1)):
+                raise chat.RequestError(f"{key} out of range")
         effort = body.get("reasoning_effort")
         if effort not in (None, "none", "low", "medium", "high"):
             raise chat.RequestError(f"unknown reasoning_effort {effort!r}")

@@ -317,3 +317,16 @@ def test_stop_sequences_cut_the_answer_and_streams_report_usage(server):
     while time.time() < deadline and not rt.serving.idle():
         time.sleep(0.1)
     assert rt.serving.idle()
+
+
+@pytest.mark.timeout(120)
+def test_capabilities_the_server_lacks_are_refused_not_ignored(server):
+    url, rt = server
+    base = {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 2}
+    for extra in ({"n": 2}, {"logprobs": True}, {"top_logprobs": 3}, {"modalities": ["text", "audio"]}, {"audio": {"voice": "x"}},
+                  {"temperature": -1}, {"top_p": 1.5}, {"temperature": "hot"}):
+        r = requests.post(url + "/v1/chat/completions", json=dict(base, **extra))
+        assert r.status_code == 400 and r.json()["error"]["type"] == "invalid_request_error", extra
+    assert requests.post(url + "/v1/chat/completions", json=dict(base, n=1, modalities=["text"], temperature=0, top_p=1)).status_code == 200
+    assert requests.get(url + "/v1/embeddings").status_code in (404, 405)
+    assert requests.post(url + "/v1/embeddings", json={"input": "x"}).status_code in (404, 405)
