@@ -212,77 +212,102 @@ def create_app(serving, tokenizer, model_name: str, default_max_output_tokens: i
         eng.cmd.put(("submit", t, kw))
         q = eng.out[t]
         cid, created = "chatcmpl-" + uuid.uuid4().hex[:24], int(time.time())
+        think, tools_open = chat.StopWatcher([chat.THINK_CLOSE]), chat.StopWatcher([chat.TOOL_OPEN])
+
+        def view(text: str, final: bool):
+            """Decoded text so far -> (reasoning to show, answer to show, stop sequence complete?).  With reasoning on, the
+            prompt ended with the opening tag: everything up to the closing tag is reasoning.  Stop sequences apply to
+            the answer.  Text that may still become the closing tag or a stop sequence is held back until `final`."""
+            r, ans = "", text
+            if reasoning:
+                k = text.find(chat.THINK_CLOSE)
+                if k < 0:
+                    return (text if final else text[:think.feed(text)[0]]).lstrip(), "", False
+                r, ans = text[:k].lstrip(), text[k + len(chat.THINK_CLOSE):].lstrip()
+            safe, hit = watcher.feed(ans)
+            if hit is None and final:
+                safe = len(ans)
+            return r, ans[:safe], hit is not None
+
+        def chunk(delta: dict, fin=None) -> str:
+            return "data: " + json.dumps({"id": cid, "object": "chat.completion.chunk", "created": created, "model": model_name,
+                                          "choices": [{"index": 0, "delta": delta, "finish_reason": fin}]}) + "\n\n"
+
         if body.get("stream"):
             async def gen():
                 ids: List[int] = []
-                sent = 0
-                cut: Optional[int] = None                # position of a completed stop sequence
-                yield "data: " + json.dumps({"id": cid, "object": "chat.completion.chunk", "created": created, "model": model_name,
-                                             "choices": [{"index": 0, "delta": {"role": "assistant"}, "finish_reason": None}]}) + "\n\n"
+                sent_r = sent_a = 0
+                cut = False                              # a stop sequence is complete
+                yield chunk({"role": "assistant"})
                 while True:
                     kind, val = await wait_item(q, request, t)
                     if kind == "token":
-                        if cut is not None:
+                        if cut:
                             continue                     # the request is being cancelled: nothing after the stop is shown
                         ids.append(val)
                         text = tokenizer.decode([i for i in ids if i not in stop_ids], skip_special_tokens=True)
                         if text.endswith("\ufffd"):
                             continue                     # incomplete UTF-8 sequence: wait for more bytes
-                        safe, cut = watcher.feed(text)
-                        if cut is not None:
+                        r, a, cut = view(text, False)
+                        if cut:
                             eng.cmd.put(("cancel", t))
-                        delta, sent = text[sent:safe], max(sent, safe)
-                        if delta:
-                            yield "data: " + json.dumps({"id": cid, "object": "chat.completion.chunk", "created": created,
-                                                         "model": model_name, "choices": [{"index": 0, "delta": {"content": delta},
-                                                                                           "finish_reason": None}]}) + "\n\n"
+                        if len(r) > sent_r:
+                            yield chunk({"reasoning_content": r[sent_r:]})
+                            sent_r = len(r)
+                        if mode != "none":               # tool-call markup is not content: show the text in front of it only
+                            a = a[:tools_open.feed(a)[0]]
+                        if len(a) > sent_a:
+                            yield chunk({"content": a[sent_a:]})
+                            sent_a = len(a)
+                        continue
+                    if kind == "error":
+                        yield "data: " + json.dumps({"error": {"message": val.get("message", "error")}}) + "\n\n"
                     else:
-                        if kind == "error":
-                            yield "data: " + json.dumps({"error": {"message": val.get("message", "error")}}) + "\n\n"
+                        n_out = len(ids) if cut else len(val["generated_ids"])
+                        if cut:
+                            val = dict(val, finish_reason="stop")
+                            text = tokenizer.decode([i for i in ids if i not in stop_ids], skip_special_tokens=True)
                         else:
                             text = tokenizer.decode([i for i in val["generated_ids"] if i not in stop_ids], skip_special_tokens=True)
-                            if cut is not None:
-                                text, val = text[:cut], dict(val, finish_reason="stop")
-                            elif len(text) > sent and not chat.parse_tool_calls(text)[1]:
-                                # characters held back as a possible beginning of a stop sequence that never completed
-                                yield "data: " + json.dumps({"id": cid, "object": "chat.completion.chunk", "created": created,
-                                                             "model": model_name, "choices": [{"index": 0, "delta": {"content": text[sent:]},
-                                                                                               "finish_reason": None}]}) + "\n\n"
-                            _, calls = chat.parse_tool_calls(text)
+                        r, a, _ = view(text, True)
+                        calls = chat.parse_tool_calls(a)[1] if mode != "none" else []
+                        if calls:
+                            a = a[:a.find(chat.TOOL_OPEN)]
+                        if len(r) > sent_r:
+                            yield chunk({"reasoning_content": r[sent_r:]})
+                        if len(a) > sent_a:              # what was held back as a possible tag or stop sequence
+                            yield chunk({"content": a[sent_a:]})
+                        yield chunk({"tool_calls": calls} if calls else {}, finish_reason(val, bool(calls)))
+                        if (body.get("stream_options") or {}).get("include_usage"):
                             yield "data: " + json.dumps({"id": cid, "object": "chat.completion.chunk", "created": created,
-                                                         "model": model_name,
-                                                         "choices": [{"index": 0, "delta": ({"tool_calls": calls} if calls else {}),
-                                                                      "finish_reason": finish_reason(val, bool(calls))}]}) + "\n\n"
-                            if (body.get("stream_options") or {}).get("include_usage"):
-                                n_out = len(ids) if cut is not None else len(val["generated_ids"])
-                                yield "data: " + json.dumps({"id": cid, "object": "chat.completion.chunk", "created": created,
-                                                             "model": model_name, "choices": [],
-                                                             "usage": {"prompt_tokens": val["prompt_tokens"], "completion_tokens": n_out,
-                                                                       "total_tokens": val["prompt_tokens"] + n_out}}) + "\n\n"
-                        yield "data: [DONE]\n\n"
-                        eng.out.pop(t, None)
-                        return
+                                                         "model": model_name, "choices": [],
+                                                         "usage": {"prompt_tokens": val["prompt_tokens"], "completion_tokens": n_out,
+                                                                   "total_tokens": val["prompt_tokens"] + n_out}}) + "\n\n"
+                    yield "data: [DONE]\n\n"
+                    eng.out.pop(t, None)
+                    return
             return StreamingResponse(gen(), media_type="text/event-stream")
         seen: List[int] = []
-        cut: Optional[int] = None
+        cut = False
         while True:
             kind, val = await wait_item(q, request, t)
             if kind == "token":
-                if watcher.stops and cut is None:
+                if watcher.stops and not cut:
                     seen.append(val)
-                    _, cut = watcher.feed(tokenizer.decode([i for i in seen if i not in stop_ids], skip_special_tokens=True))
-                    if cut is not None:
+                    cut = view(tokenizer.decode([i for i in seen if i not in stop_ids], skip_special_tokens=True), False)[2]
+                    if cut:
                         eng.cmd.put(("cancel", t))       # a stop sequence is complete: the rest is not needed
                 continue
             eng.out.pop(t, None)
             if kind == "error":
                 return bad(val.get("message", "error"), 400 if val.get("bad_request") else 500)
+            if cut:
+                val = dict(val, finish_reason="stop", generated_ids=seen)
             text = tokenizer.decode([i for i in val["generated_ids"] if i not in stop_ids], skip_special_tokens=True)
-            if cut is None and watcher.stops:
-                _, cut = watcher.feed(text)
-            if cut is not None:
-                text, val = text[:cut], dict(val, finish_reason="stop", generated_ids=seen or val["generated_ids"])
-            reasoning_text, answer = chat.split_reasoning(text, reasoning) if reasoning else ("", text)
+            reasoning_text, answer, hit = view(text, True)
+            if hit:
+                val = dict(val, finish_reason="stop")
+            reasoning_text = reasoning_text.strip()
             answer, calls = chat.parse_tool_calls(answer) if mode != "none" else (answer, [])
             msg = {"role": "assistant", "content": answer or None if calls else answer}
             if calls:

@@ -330,3 +330,42 @@ def test_capabilities_the_server_lacks_are_refused_not_ignored(server):
     assert requests.post(url + "/v1/chat/completions", json=dict(base, n=1, modalities=["text"], temperature=0, top_p=1)).status_code == 200
     assert requests.get(url + "/v1/embeddings").status_code in (404, 405)
     assert requests.post(url + "/v1/embeddings", json={"input": "x"}).status_code in (404, 405)
+
+
+def _stream(url, body):
+    chunks = []
+    with requests.post(url + "/v1/chat/completions", json=dict(body, stream=True), stream=True) as r:
+        assert r.status_code == 200
+        for line in r.iter_lines(decode_unicode=True):
+            if line and line.startswith("data: ") and line != "data: [DONE]":
+                chunks.append(json.loads(line[6:]))
+    return [c["choices"][0] for c in chunks if c.get("choices")]
+
+
+@pytest.mark.timeout(300)
+def test_streams_separate_reasoning_answer_and_tool_calls(server):
+    """With reasoning on, the text in front of the closing think tag streams as `reasoning_content`, the rest as `content`,
+    and the tag itself is never shown; tool-call markup never streams as content.  Both agree with the plain response."""
+    url, rt = server
+    if rt.serving.constraints is None:
+        pytest.skip("grammar engine not available")
+    g = 'root ::= [a-e] [a-e] [a-e] [a-e] "</think>" [f-j] [f-j] [f-j] [f-j] [f-j]'
+    body = {"messages": [{"role": "user", "content": "think"}], "max_tokens": 40, "reasoning_effort": "low",
+            "response_format": {"type": "grammar", "grammar": g}}
+    plain = requests.post(url + "/v1/chat/completions", json=body).json()["choices"][0]["message"]
+    assert len(plain["reasoning_content"]) == 4 and len(plain["content"]) == 5 and "think" not in plain["content"]
+    ch = _stream(url, body)
+    assert "".join(c["delta"].get("reasoning_content", "") for c in ch) == plain["reasoning_content"]
+    assert "".join(c["delta"].get("content", "") for c in ch) == plain["content"]
+    order = [("r" if "reasoning_content" in c["delta"] else "c") for c in ch if c["delta"].get("reasoning_content") or c["delta"].get("content")]
+    assert order == sorted(order, reverse=True)                                  # all reasoning comes first
+    # a forced tool call: the stream carries no markup, only the call at the end
+    tool = {"type": "function", "function": {"name": "get_weather", "strict": True, "parameters": {
+        "type": "object", "properties": {"city": {"type": "string", "enum": ["Oslo", "Rome"]}}, "required": ["city"],
+        "additionalProperties": False}}}
+    tb = {"messages": [{"role": "user", "content": "weather?"}], "tools": [tool], "max_tokens": 300,
+          "tool_choice": {"type": "function", "function": {"name": "get_weather"}}}
+    ch = _stream(url, tb)
+    shown = "".join(c["delta"].get("content", "") for c in ch)
+    assert "<tool_call>" not in shown and "get_weather" not in shown
+    assert ch[-1]["finish_reason"] == "tool_calls" and ch[-1]["delta"]["tool_calls"][0]["function"]["name"] == "get_weather"
