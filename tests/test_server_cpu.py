@@ -369,3 +369,28 @@ def test_streams_separate_reasoning_answer_and_tool_calls(server):
     shown = "".join(c["delta"].get("content", "") for c in ch)
     assert "<tool_call>" not in shown and "get_weather" not in shown
     assert ch[-1]["finish_reason"] == "tool_calls" and ch[-1]["delta"]["tool_calls"][0]["function"]["name"] == "get_weather"
+
+
+@pytest.mark.timeout(300)
+def test_agent_loop_tool_result_round_trip_reuses_the_prefix(server):
+    """An agent turn pair: forced tool call, then the call and its result go back in the history; the second request
+    restores the shared prefix (tools, system prompt, first user turn) from the cache instead of prefilling it again."""
+    url, rt = server
+    if rt.serving.constraints is None:
+        pytest.skip("grammar engine not available")
+    tool = {"type": "function", "function": {"name": "lookup", "strict": True, "parameters": {
+        "type": "object", "properties": {"key": {"type": "string", "enum": ["alpha", "beta"]}}, "required": ["key"],
+        "additionalProperties": False}}}
+    history = [{"role": "system", "content": "You are a careful assistant that always looks things up before answering. " * 6},
+               {"role": "user", "content": "what is alpha?"}]
+    first = requests.post(url + "/v1/chat/completions", json={
+        "messages": history, "tools": [tool], "max_tokens": 300,
+        "tool_choice": {"type": "function", "function": {"name": "lookup"}}}).json()
+    call = first["choices"][0]["message"]["tool_calls"][0]
+    assert first["choices"][0]["finish_reason"] == "tool_calls" and json.loads(call["function"]["arguments"])["key"] in ("alpha", "beta")
+    history += [{"role": "assistant", "content": None, "tool_calls": [call]},
+                {"role": "tool", "tool_call_id": call["id"], "content": "alpha is the first letter"}]
+    second = requests.post(url + "/v1/chat/completions", json={"messages": history, "tools": [tool], "max_tokens": 6}).json()
+    assert second["choices"][0]["finish_reason"] in ("stop", "length", "tool_calls")
+    assert second["usage"]["prompt_tokens"] > first["usage"]["prompt_tokens"]
+    assert second["usage"]["prompt_tokens_details"]["cached_tokens"] > 0
