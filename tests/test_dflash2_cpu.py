@@ -203,19 +203,23 @@ def test_random_draft_counts_chunks_and_prompts_keep_the_greedy_stream(setup):
         return memo[(tuple(p), n)]
 
     @settings(max_examples=10, deadline=None, derandomize=True, suppress_health_check=list(HealthCheck))
-    @given(k=st.integers(1, 7), chunk=st.sampled_from([4, 8, 32]), seed=st.integers(0, 3),
-           reqs=st.lists(st.tuples(st.integers(0, 6), st.integers(5, 21), st.integers(1, 14)), min_size=1, max_size=3))
-    def run(k, chunk, seed, reqs):
+    @given(k=st.integers(1, 7), chunk=st.sampled_from([4, 8, 32]), seed=st.integers(0, 3), cache=st.booleans(),
+           reqs=st.lists(st.tuples(st.integers(0, 6), st.integers(5, 21), st.integers(1, 14), st.booleans()), min_size=1, max_size=3))
+    def run(k, chunk, seed, cache, reqs):
         eng = Engine(ew, "cpu", StateConfig(max_slots=1, max_seq_len=96, conv_ring=16, spec_rows=8))
         dcfg = tiny_drafter_config(cfg)
         dec = DFlash2SpecDecoder(eng, DFlash2Drafter(dcfg, random_weights(dcfg, seed=seed), "cpu"), num_drafts=k)
-        srv = SpecServingEngine(dec, prefill_chunk=chunk)
-        want = {}
-        for lo, hi, n in reqs:
+        kw = dict(prefix_cache_tokens=256, prefix_cache_entries=3, prefix_min_tokens=8) if cache else {}
+        srv = SpecServingEngine(dec, prefill_chunk=chunk, **kw)
+        last = None
+        for lo, hi, n, follow in reqs:
             p = prompt[lo:max(hi, lo + 2)]
-            want[srv.submit(p, n)] = greedy(p, n)
-        ev = srv.run_until_idle()
-        for rid, w in want.items():
-            assert [e.token_id for e in ev if e.kind == "token" and e.request_id == rid] == w, (k, chunk, seed, rid)
+            if follow and last is not None and len(last) + 3 + n < 90:
+                p = last + [5, 6, 7]                     # a next turn of the previous conversation (terminal checkpoint)
+            rid = srv.submit(p, n, checkpoint_position=8 if cache and len(p) > 8 else 0)
+            ev = srv.run_until_idle()
+            got = [e.token_id for e in ev if e.kind == "token" and e.request_id == rid]
+            assert got == greedy(p, n), (k, chunk, seed, cache, len(p), n)
+            last = p + got
         assert srv.idle()
     run()
