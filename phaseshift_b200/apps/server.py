@@ -185,6 +185,34 @@ def create_app(serving, tokenizer, model_name: str, default_max_output_tokens: i
     def health():
         return {"status": "ok"}
 
+    @app.get("/metrics")
+    def metrics():
+        """Counters of the serving loop in the Prometheus text format (monitoring of a deployment; no upstream counterpart)."""
+        from fastapi.responses import PlainTextResponse
+        srv = getattr(serving, "srv", serving)                       # the tensor-parallel leader wraps the loop
+        st = dict(getattr(srv, "stats", {}) or {})
+        lines = []
+
+        def put(name: str, kind: str, value, help_: str) -> None:
+            lines.extend([f"# HELP phaseshift_{name} {help_}", f"# TYPE phaseshift_{name} {kind}", f"phaseshift_{name} {value}"])
+        put("steps_total", "counter", st.get("steps", 0), "engine steps executed")
+        put("generated_tokens_total", "counter", st.get("tokens", 0), "tokens sampled")
+        put("prefill_tokens_total", "counter", st.get("prefill_tokens", 0), "prompt tokens prefilled (restored prefixes excluded)")
+        put("failed_steps_total", "counter", st.get("failed_steps", 0), "steps that ended with a non-zero device status")
+        b = getattr(srv, "batcher", None)
+        if b is not None and hasattr(b, "active_count"):
+            put("requests_active", "gauge", b.active_count(), "requests holding a sequence slot")
+            put("requests_queued", "gauge", b.queued_count(), "requests waiting for admission")
+            put("kv_pages_free", "gauge", b.free_pages(), "free pages of the key/value cache")
+        pc = getattr(srv, "prefix", None)
+        if pc is not None:
+            sm = pc.summary()
+            put("prefix_cache_hits_total", "counter", sm.get("hits", 0), "prompts that restored a cached prefix")
+            put("prefix_cache_misses_total", "counter", sm.get("misses", 0), "prompts without a cached prefix")
+            put("prefix_cache_tokens", "gauge", sm.get("used_tokens", 0), "tokens held by the prefix cache")
+        put("requests_in_flight", "gauge", len(eng.ticket_of), "HTTP requests being generated")
+        return PlainTextResponse("\n".join(lines) + "\n", media_type="text/plain; version=0.0.4")
+
     @app.get("/v1/models")
     def models():
         return {"object": "list", "data": [{"id": model_name, "object": "model", "owned_by": "phaseshift-b200"}]}

@@ -394,3 +394,15 @@ def test_agent_loop_tool_result_round_trip_reuses_the_prefix(server):
     assert second["choices"][0]["finish_reason"] in ("stop", "length", "tool_calls")
     assert second["usage"]["prompt_tokens"] > first["usage"]["prompt_tokens"]
     assert second["usage"]["prompt_tokens_details"]["cached_tokens"] > 0
+
+
+def test_metrics_endpoint_exposes_the_serving_counters(server):
+    url, rt = server
+    requests.post(url + "/v1/chat/completions", json={"messages": [{"role": "user", "content": "count me"}], "max_tokens": 3})
+    r = requests.get(url + "/metrics")
+    assert r.status_code == 200 and r.headers["content-type"].startswith("text/plain")
+    vals = {l.split()[0]: float(l.split()[1]) for l in r.text.splitlines() if l and not l.startswith("#")}
+    assert vals["phaseshift_steps_total"] >= 1 and vals["phaseshift_generated_tokens_total"] >= 1
+    assert vals["phaseshift_prefill_tokens_total"] >= 1 and vals["phaseshift_requests_active"] == 0
+    assert vals["phaseshift_kv_pages_free"] > 0 and "phaseshift_prefix_cache_hits_total" in vals
+    assert all(l.startswith(("# HELP phaseshift_", "# TYPE phaseshift_", "phaseshift_")) for l in r.text.splitlines() if l)
