@@ -18,18 +18,19 @@ def _rank(rank, world, port, die_rank, q):
     from torch.distributed import TCPStore
     from phaseshift_b200.parallel.health import PeerMonitor, RankLostError
     store = TCPStore("127.0.0.1", port, world, is_master=(rank == 0), timeout=timedelta(seconds=20), wait_for_workers=True)
-    mon = PeerMonitor(store, rank, world, interval_s=0.05, timeout_s=0.6).start()
+    # the timeout leaves room for a loaded machine: a healthy rank whose thread is starved for a second must not be declared lost
+    mon = PeerMonitor(store, rank, world, interval_s=0.05, timeout_s=1.5).start()
     t0 = time.monotonic()
     steps = 0
     try:
-        while time.monotonic() - t0 < 8.0:
+        while time.monotonic() - t0 < 12.0:
             mon.assert_alive()               # "before the next launch"
             steps += 1
             time.sleep(0.02)
             if rank == die_rank and steps == 20:
                 mon.stop()                    # leaves between steps: no more heartbeats
                 q.put((rank, "left", steps))
-                time.sleep(3.0)               # keep the process (and a rank-0 store) alive while the others notice
+                time.sleep(5.0)               # keep the process (and a rank-0 store) alive while the others notice
                 return
         q.put((rank, "no-detection", steps))
     except RankLostError as e:
@@ -131,9 +132,10 @@ def _tp_rank(rank, world, port, q):
     cfg = tiny_config()
     hf = random_hf_weights(cfg, seed=0)
     tp = TensorParallel(dist.group.WORLD, "cpu")
-    tp.start_monitor(interval_s=0.05, timeout_s=0.8)
     eng = Engine(build_engine_weights(cfg, lambda n: hf[n], "bf16", "cpu", tp_rank=rank, tp_size=world), "cpu",
                  StateConfig(max_slots=1, max_seq_len=64), tp=tp)
+    dist.barrier()                            # every rank is past its (unevenly long) set-up before heartbeats are judged
+    tp.start_monitor(interval_s=0.05, timeout_s=1.5)
     s = eng.open_sequence()
     toks, _ = eng.step([SeqRows(s.slot, 0, [3, 4, 5, 6], (3,))], [s])
     try:
@@ -143,7 +145,7 @@ def _tp_rank(rank, world, port, q):
                 q.put((rank, "raised", i))
                 raise RuntimeError("rank 1 fails between steps")
             if i >= 3 and rank != 1:
-                time.sleep(0.3)              # between steps (waiting for requests): the heartbeat has time to lapse
+                time.sleep(0.6)              # between steps (waiting for requests): the heartbeat has time to lapse
             toks, _ = eng.step([SeqRows(s.slot, s.position, [toks[0]], (0,))], [s])
         q.put((rank, "no-detection", None))
     except RankLostError as e:
