@@ -217,6 +217,13 @@ def create_app(serving, tokenizer, model_name: str, default_max_output_tokens: i
     def models():
         return {"object": "list", "data": [{"id": model_name, "object": "model", "owned_by": "phaseshift-b200"}]}
 
+    @app.get("/v1/models/{model_id}")
+    def model_info(model_id: str):
+        if model_id != model_name:
+            return JSONResponse({"error": {"message": f"model {model_id!r} not found", "type": "invalid_request_error"}},
+                                status_code=404)
+        return {"id": model_name, "object": "model", "owned_by": "phaseshift-b200"}
+
     async def wait_item(q: "queue.Queue", request: Request, ticket: int):
         while True:
             try:

@@ -49,6 +49,8 @@ def server():
 def test_models_and_chat_completion(server):
     url, rt = server
     assert requests.get(url + "/v1/models").json()["data"][0]["id"] == "tiny-test"
+    assert requests.get(url + "/v1/models/tiny-test").json()["object"] == "model"
+    assert requests.get(url + "/v1/models/other").status_code == 404
     r = requests.post(url + "/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}], "max_tokens": 8})
     assert r.status_code == 200
     j = r.json()
