@@ -45,6 +45,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--dflash2-model-dir"); ap.add_argument("--dflash2-drafts", type=int, default=7)
     ap.add_argument("--model-name", default="phaseshift"); ap.add_argument("--verify-weights", type=int, default=0)
     ap.add_argument("--startup-timeout", type=int, default=120)
+    ap.add_argument("--max-queued-requests", type=int, default=0,
+                    help="requests that may wait for a slot; more are answered with HTTP 429 (0: unbounded queue)")
     # the upstream server is a front end that spawns the compute binary (docs/user/server.md:79-102); here the engine lives
     # in the server process, so the two paths are accepted and unused
     ap.add_argument("--compute", default=None, help="accepted for compatibility (the engine runs in this process)")
@@ -120,7 +122,9 @@ class EngineThread(threading.Thread):
             self.running = False
 
 
-def create_app(serving, tokenizer, model_name: str, default_max_output_tokens: int, stop_ids: List[int], max_seq_len: int):
+def create_app(serving, tokenizer, model_name: str, default_max_output_tokens: int, stop_ids: List[int], max_seq_len: int,
+               max_in_flight: int = 0):
+    """``max_in_flight`` > 0: requests beyond that many being generated or queued are answered with HTTP 429."""
     if FastAPI is None:
         raise RuntimeError("fastapi is required for phaseshift-server")
     app = FastAPI(title="phaseshift-b200")
@@ -130,6 +134,13 @@ def create_app(serving, tokenizer, model_name: str, default_max_output_tokens: i
 
     def bad(msg: str, code: int = 400):
         return JSONResponse({"error": {"message": msg, "type": "invalid_request_error"}}, status_code=code)
+
+    def overloaded():
+        """Admission at the door: a bounded queue instead of an unbounded backlog (the client retries)."""
+        if max_in_flight > 0 and len(eng.out) >= max_in_flight:
+            return JSONResponse({"error": {"message": f"server is at its limit of {max_in_flight} requests in flight",
+                                           "type": "rate_limit_error"}}, status_code=429, headers={"Retry-After": "1"})
+        return None
 
     def prepare(body: dict):
         msgs = body.get("messages")
@@ -242,6 +253,9 @@ def create_app(serving, tokenizer, model_name: str, default_max_output_tokens: i
             return bad(str(e))
         except Exception as e:
             return bad(f"malformed request: {e}")
+        busy = overloaded()
+        if busy is not None:
+            return busy
         watcher = chat.StopWatcher(body.get("_stops") or [])
         t = eng.new_ticket()
         eng.cmd.put(("submit", t, kw))
@@ -434,6 +448,9 @@ def create_app(serving, tokenizer, model_name: str, default_max_output_tokens: i
             return bad(str(e))
         except Exception as e:
             return bad(f"malformed request: {e}")
+        busy = overloaded()
+        if busy is not None:
+            return busy
         t = eng.new_ticket()
         eng.cmd.put(("submit", t, kw))
         q = eng.out[t]
@@ -541,7 +558,8 @@ def main(argv=None) -> int:
         import atexit
         rt.serving = TpServingLeader(rt.serving, rt.host_group)
         atexit.register(rt.serving.shutdown)
-    app = create_app(rt.serving, tok, a.model_name, a.default_max_output_tokens, stop, a.max_seq_len)
+    app = create_app(rt.serving, tok, a.model_name, a.default_max_output_tokens, stop, a.max_seq_len,
+                     max_in_flight=a.max_concurrent_requests + a.max_queued_requests if a.max_queued_requests > 0 else 0)
     print(f"phaseshift-server: model={a.model_name} ctx={a.max_seq_len} concurrency={a.max_concurrent_requests} "
           f"prefix_cache={a.prefix_cache_capacity_tokens}x{a.prefix_cache_max_entries} http://{a.host}:{a.port}", file=sys.stderr)
     uvicorn.run(app, host=a.host, port=a.port, log_level="warning")

@@ -408,3 +408,48 @@ def test_metrics_endpoint_exposes_the_serving_counters(server):
     assert vals["phaseshift_prefill_tokens_total"] >= 1 and vals["phaseshift_requests_active"] == 0
     assert vals["phaseshift_kv_pages_free"] > 0 and "phaseshift_prefix_cache_hits_total" in vals
     assert all(l.startswith(("# HELP phaseshift_", "# TYPE phaseshift_", "phaseshift_")) for l in r.text.splitlines() if l)
+
+
+@pytest.mark.timeout(300)
+def test_bounded_admission_answers_429_when_the_queue_is_full():
+    """One slot, one queued request allowed: while two requests are in flight a third is refused with 429 and a retry hint;
+    once they finish the server accepts again."""
+    import uvicorn
+    from phaseshift_b200.apps import server as srv
+    a = srv.build_parser().parse_args(["--random-model", "tiny", "--device", "cpu", "--max-seq-len", "256",
+                                       "--max-concurrent-requests", "1", "--prefix-cache-capacity-tokens", "0",
+                                       "--max-queued-requests", "1"])
+    rt, tok, stop = srv.build_runtime(a)
+    app = srv.create_app(rt.serving, tok, "tiny-429", 24, stop, 256, max_in_flight=2)
+    port = _free_port()
+    us = uvicorn.Server(uvicorn.Config(app, host="127.0.0.1", port=port, log_level="error"))
+    th = threading.Thread(target=us.run, daemon=True)
+    th.start()
+    url = f"http://127.0.0.1:{port}"
+    for _ in range(200):
+        try:
+            if requests.get(url + "/health", timeout=1).ok:
+                break
+        except Exception:
+            time.sleep(0.05)
+    try:
+        body = {"messages": [{"role": "user", "content": "long answer please"}], "max_tokens": 120}
+        results = []
+        ts = [threading.Thread(target=lambda: results.append(requests.post(url + "/v1/chat/completions", json=body).status_code))
+              for _ in range(2)]
+        for t in ts:
+            t.start()
+        deadline = time.time() + 30
+        while time.time() < deadline and len(app.state.engine_thread.out) < 2:
+            time.sleep(0.01)
+        r = requests.post(url + "/v1/chat/completions", json=dict(body, max_tokens=2))
+        assert r.status_code == 429 and r.headers["Retry-After"] == "1" and r.json()["error"]["type"] == "rate_limit_error"
+        assert requests.post(url + "/v1/responses", json={"input": "x", "max_output_tokens": 2}).status_code == 429
+        for t in ts:
+            t.join(120)
+        assert results == [200, 200]
+        assert requests.post(url + "/v1/chat/completions", json=dict(body, max_tokens=2)).status_code == 200
+    finally:
+        us.should_exit = True
+        app.state.engine_thread.cmd.put(("stop",))
+        th.join(timeout=10)
